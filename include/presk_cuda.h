@@ -1,0 +1,327 @@
+/* presk_cuda.h: the C ABI of the B200 executor for Presk's realized kernels.
+ *
+ * What this boundary replaces in the reference (paths within presk-lang/presk):
+ *
+ *   - the inner seam, `trait KernelExec` (crates/presk-kernel/src/host.rs:28-95):
+ *     `run(idx, &Kernel, inputs: &[&Buf], out: &mut Buf) -> Result<()>`, called
+ *     by one host thread, one launch per fusion group or tensor primitive;
+ *   - the raw kernel signature of the native executor,
+ *     `KernelFn = extern "C" fn(*const *mut u8, i64, i64)`
+ *     (crates/presk-cranelift/src/lib.rs:42) with its pointer-table order
+ *     (inputs, output, one scales pointer per quantised input, overflow flag:
+ *     lib.rs:1609-1629), which `psk_exec_run` keeps;
+ *   - the outer seam, `trait Backend { prepare; call }`
+ *     (crates/presk-rt/src/lib.rs:1274-1303), which `psk_host_*` stands in for.
+ *
+ * A launch is described by `psk_launch`, the resolved form of the reference's
+ * `Kernel` (crates/presk-kernel/src/ir.rs:300-322): the lowering table of
+ * crates/presk-kernel/src/lower.rs decides, per primitive, an iteration space
+ * (the output's axes, then the summed axes) and how each operand is indexed
+ * in it; here that indexing is carried as element strides, so that axis names
+ * are a matter of the host alone and an executor is name-free.
+ *
+ * Everything is plain C: pointers, sizes, fixed-size structs. No type of
+ * PyTorch or of the CUDA runtime appears in a signature.
+ */
+#ifndef PRESK_CUDA_H
+#define PRESK_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PSK_MAX_RANK 8    /* axes of the output of a launch */
+#define PSK_MAX_INNER 4   /* summed axes of a launch */
+#define PSK_MAX_AXES (PSK_MAX_RANK + PSK_MAX_INNER)
+#define PSK_MAX_INPUTS 8
+#define PSK_MAX_STEPS 64  /* the reference's MAX_TREE, presk-core/src/fusion.rs:79 */
+
+/* Machine types of a buffer. 0..5 are the reference's `presk_dtype`
+ * (crates/presk-export-c/c/presk_rt.h, "The machine type of a buffer"), in
+ * its order; the rest are storage formats of the realization's `quant` and
+ * `params` maps (presk-rt/src/quant.rs, presk-format/src/lib.rs:136). */
+typedef enum {
+    PSK_F64 = 0,
+    PSK_F32 = 1,
+    PSK_BF16 = 2,
+    PSK_I64 = 3,
+    PSK_F16 = 4,
+    PSK_E8M15 = 5, /* three bytes an element, little-endian */
+    PSK_I8 = 6,    /* integer weights; the scales travel beside them */
+    PSK_E4M3 = 7   /* e4m3fn codes, one byte */
+} psk_dtype;
+
+/* Status of a call: the reference's RtError codes (presk-rt/src/lib.rs:971-981). */
+typedef enum {
+    PSK_OK = 0,
+    PSK_E7001 = 7001,  /* runtime error (bad descriptor, shapes) */
+    PSK_E7005 = 7005,  /* a realization this executor does not run */
+    PSK_E7007 = 7007,  /* the overflow guard: a store rounded a finite value to an infinity */
+    PSK_E10001 = 10001 /* internal error of the backend (a CUDA call failed, a wait ran out) */
+} psk_status;
+
+/* What a launch computes. Each is a family of the reference's lowerings. */
+typedef enum {
+    PSK_OP_FUSED = 0,    /* lower.rs:309-372: a fusion group, a unary or a binary primitive */
+    PSK_OP_CONTRACT = 1, /* lower.rs:384-636, 906-1139: dot, ein, dot_vjp_l/r */
+    PSK_OP_REDUCE = 2,   /* lower.rs:1221-1255, 1693: sum, mean, sum_squares */
+    PSK_OP_SOFTMAX = 3,  /* lower.rs:1274-1419: softmax over one axis, masked or not */
+    PSK_OP_XENT = 4,     /* lower.rs:1459: cross_entropy */
+    PSK_OP_ARGMAX = 5,   /* lower.rs:1490 */
+    PSK_OP_EMBED = 6,    /* lower.rs:1421 */
+    PSK_OP_COPY = 7,     /* lower.rs:1554-1667: slice, concat, split_heads, merge_heads, index, broadcast_like */
+    PSK_OP_IOTA = 8,     /* lower.rs:1706-1750: positions, causal_mask, one_hot, fill */
+    PSK_OP_CONVERT = 9   /* host.rs:809-829: Buf::of(to, b.to_f64()) at a kernel's edge */
+} psk_op;
+
+/* Elementary operations of a fusion group's steps (lower.rs:184-226). */
+typedef enum {
+    PSK_ADD = 0, PSK_SUB, PSK_MUL, PSK_DIV, PSK_MAX, PSK_MIN,
+    PSK_NEG, PSK_EXP, PSK_LOG, PSK_TANH, PSK_SQRT, PSK_SIN, PSK_COS, PSK_ABS,
+    PSK_GELU, PSK_GELU_DERIV, PSK_RELU, PSK_HEAVISIDE, PSK_SIGN, PSK_SIGMOID,
+    PSK_POW, /* by repeated multiplication, exponent in `imm` */
+    PSK_REAL /* identity on a real; an index read as a real */
+} psk_prim;
+
+/* One step of a group (presk-core/src/fusion.rs:19-59): an operation on one or
+ * two sources, each an input of the launch (src >= 0) or an earlier step
+ * (src = -1 - step). */
+typedef struct {
+    int32_t prim;  /* psk_prim */
+    int32_t nargs; /* 1 or 2 */
+    int32_t src[2];
+    int32_t imm;   /* PSK_POW's exponent */
+} psk_step;
+
+/* How a sum is accumulated: the realization's `order`
+ * (presk-rt/src/lib.rs:251-285). SEQUENTIAL is the reference's default and is
+ * bit-defining; DEVICE is this executor's declared reassociation (tensor-core
+ * tiles for contractions, shuffle trees for row reductions), as `chunked` and
+ * `interleaved` are the reference's. */
+typedef enum { PSK_ORDER_SEQUENTIAL = 0, PSK_ORDER_DEVICE = 1 } psk_order;
+
+typedef enum {
+    PSK_REDUCE_SUM = 0, PSK_REDUCE_MEAN = 1, PSK_REDUCE_SUMSQ = 2
+} psk_reduce_kind;
+
+typedef enum {
+    PSK_IOTA_POSITIONS = 0, PSK_IOTA_CAUSAL = 1, PSK_IOTA_ONE_HOT = 2, PSK_IOTA_FILL = 3
+} psk_iota_kind;
+
+/* An operand as the launch indexes it: the element of the iteration point
+ * (o_0 .. o_{n_outer-1}, c_0 .. c_{n_inner-1}) is at
+ * offset + sum_a index_a * stride[a], in elements. A broadcast axis has
+ * stride 0. For integer weights (`quant`), `scale_stride` indexes the f32
+ * scales the same way (quant.rs:227-278: the scale is constant along the
+ * contracted axis). */
+typedef struct {
+    int32_t dtype;              /* psk_dtype of the stored elements */
+    int32_t is_index;           /* 1: an idx tensor (i64), read as an integer */
+    int64_t offset;
+    int64_t stride[PSK_MAX_AXES];
+    int64_t scale_stride[PSK_MAX_AXES];
+    int64_t numel;              /* elements of the whole buffer, for checks */
+} psk_operand;
+
+typedef struct {
+    const char *name;   /* the reference's kernel name: "dot", "ein[batch, seq, model]", "fused 2 steps" */
+    int32_t op;         /* psk_op */
+    int32_t dtype;      /* the kernel's type: its output's storage type; it computes in f32
+                           (presk-rt/src/lib.rs:147-152) */
+    int32_t order;      /* psk_order */
+    int32_t guarded;    /* 1: test f16/e8m15 stores for overflow (host.rs:144-177) */
+    int32_t n_inputs;
+    int32_t n_outer;    /* axes of the output */
+    int32_t n_inner;    /* summed axes, after the outer ones in every stride array */
+    int64_t dims[PSK_MAX_AXES];
+    psk_operand in[PSK_MAX_INPUTS];
+    psk_operand out;    /* stride over the outer axes; row-major unless the launch writes a part */
+    int32_t n_steps;
+    psk_step steps[PSK_MAX_STEPS];
+    int32_t kind;       /* psk_reduce_kind or psk_iota_kind */
+    int32_t masked;     /* softmax: input 1 is the mask */
+    int64_t iparam[4];  /* reduce: the divisor of a mean; copy/iota: see psk_host.cpp */
+    double fparam[2];   /* fill: the value */
+} psk_launch;
+
+/* Sizes of this header's structs as the library was compiled with them, for a
+ * binding in another language to check its own layout against: 0 psk_launch,
+ * 1 psk_operand, 2 psk_step, 3 psk_gemm, 4 psk_value, 5 psk_exec_vtable. */
+size_t psk_abi_sizeof(int which);
+
+/* ---------------------------------------------------------------------------
+ * The executor (KernelExec). One per device and host thread.
+ * ------------------------------------------------------------------------- */
+typedef struct psk_exec psk_exec;
+
+/* An executor on CUDA device `device`. NULL when the device cannot be used;
+ * psk_last_error(NULL) then says why. Never falls back to the CPU. */
+psk_exec *psk_exec_create(int device);
+void psk_exec_destroy(psk_exec *e);
+
+/* KernelExec::name, workers, emulates, codes (host.rs:28-95): "cuda"; no host
+ * workers; runs the native float types and their codes, emulates nothing. */
+const char *psk_exec_name(const psk_exec *e);
+
+/* The message of the last call that did not return PSK_OK. */
+const char *psk_last_error(const psk_exec *e);
+
+/* Device buffers. Contents of a fresh buffer are arbitrary, as the
+ * reference's pooled buffers are (presk-rt/src/elems.rs:57-72). */
+void *psk_exec_alloc(psk_exec *e, size_t bytes);
+void psk_exec_free(psk_exec *e, void *p);
+int psk_exec_upload(psk_exec *e, void *dst, const void *src_host, size_t bytes);
+int psk_exec_download(psk_exec *e, void *dst_host, const void *src, size_t bytes);
+int psk_exec_sync(psk_exec *e);
+/* Bytes in use and the most there have been (presk-kernel/src/memory.rs). */
+void psk_exec_memory(const psk_exec *e, size_t *live, size_t *peak);
+
+/* KernelExec::run. `table` is the native executor's pointer table
+ * (presk-cranelift/src/lib.rs:1609-1629): the n_inputs inputs, the output,
+ * then one `const float *` of scales for each input whose dtype is PSK_I8, in
+ * input order. All are device pointers of this executor. The launch is
+ * queued on the executor's stream; PSK_E7007 of a guarded launch is
+ * reported by the next psk_exec_sync, psk_exec_download or psk_exec_overflow,
+ * naming the first launch whose store overflowed, and later launches still
+ * run (presk_rt.h:296-310). */
+int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table);
+
+/* The overflow guard's flag since the last call, cleared by it: 0, or
+ * 1 + the serial number of the first guarded launch that overflowed. */
+int64_t psk_exec_overflow(psk_exec *e);
+
+/* Launches queued, and how many kernels of this library they started. */
+void psk_exec_counts(const psk_exec *e, int64_t *launches, int64_t *kernels);
+
+/* KernelExec::set_profiling / overhead (host.rs:45): device time of the last
+ * psk_exec_run in milliseconds, timed with events on the stream, or < 0. */
+void psk_exec_set_profiling(psk_exec *e, int on);
+double psk_exec_last_ms(psk_exec *e);
+
+/* The raw CUDA stream the executor launches on (a cudaStream_t), for a
+ * caller that times it with its own events. */
+void *psk_exec_stream(psk_exec *e);
+
+/* A tensor-core contraction on its own, outside a launch: C[b] = A[b]·B[b]
+ * with bf16/f16 operands and f32 sums; what PSK_OP_CONTRACT dispatches to
+ * under PSK_ORDER_DEVICE. See psk_gemm in csrc/gemm_tc.cuh. */
+typedef struct {
+    int32_t in_dtype;  /* PSK_BF16 or PSK_F16, both operands */
+    int32_t out_dtype; /* PSK_F32, PSK_BF16, PSK_F16 or PSK_E8M15 */
+    int32_t b_n_major; /* 0: B[batch][n][k], k contiguous; 1: B[batch][k][n], n contiguous */
+    int32_t guarded;
+    int64_t m, n, k;
+    int64_t batch, batch_lo;                 /* batch index = hi * batch_lo + lo */
+    int64_t a_row, a_lo, a_hi;               /* element strides of A: row, batch lo, batch hi */
+    int64_t b_row, b_lo, b_hi;
+    int64_t c_row_lo_count, c_row_lo, c_row_hi; /* row r at (r / count) * hi + (r % count) * lo */
+    int64_t c_col_lo_count, c_col_hi;        /* col c at (c / count) * hi + (c % count) */
+    int64_t c_lo, c_hi;                      /* batch strides of C */
+    float scale;                             /* the output is acc * scale when scale_on (a fused `div`/`mul`) */
+    int32_t scale_on;
+} psk_gemm;
+int psk_exec_gemm(psk_exec *e, const psk_gemm *g, const void *a, const void *b, void *c);
+
+/* ---------------------------------------------------------------------------
+ * The executor as a table of functions, so that the host program can run
+ * over another one (KernelBackend::with_exec, host.rs:466). The library's
+ * own is the CUDA executor; tests hand the host a CPU one.
+ * ------------------------------------------------------------------------- */
+typedef struct {
+    void *self;
+    const char *(*name)(void *self);
+    void *(*alloc)(void *self, size_t bytes);
+    void (*free)(void *self, void *p);
+    int (*upload)(void *self, void *dst, const void *src_host, size_t bytes);
+    int (*download)(void *self, void *dst_host, const void *src, size_t bytes);
+    int (*run)(void *self, const psk_launch *l, void *const *table);
+    int (*sync)(void *self);
+    int64_t (*overflow)(void *self);
+    const char *(*last_error)(void *self);
+    /* Integer weights made from reals on the executor (presk-rt/src/quant.rs:128-167):
+     * w is outer x k x inner reals of type `from` (PSK_F32 or PSK_F64), q its
+     * int8 codes, s one f32 scale per (outer, inner) channel, absmax scheme. */
+    int (*quantize)(void *self, const void *w, int32_t from, int8_t *q, float *s, int64_t outer, int64_t k, int64_t inner);
+    /* n elements of type `to` drawn on the executor; may be NULL. */
+    int (*init_normal)(void *self, void *dst, int32_t to, int64_t n, uint64_t seed, double std);
+} psk_exec_vtable;
+
+/* The two device helpers of the table, on the CUDA executor. */
+int psk_exec_quantize(psk_exec *e, const void *w, int32_t from, int8_t *q, float *s, int64_t outer, int64_t k, int64_t inner);
+int psk_exec_init_normal(psk_exec *e, void *dst, int32_t to, int64_t n, uint64_t seed, double std);
+
+/* The CUDA executor `e` as such a table. */
+void psk_exec_as_vtable(psk_exec *e, psk_exec_vtable *out);
+
+/* ---------------------------------------------------------------------------
+ * The host program (Backend: prepare, call). It walks a model's lets in the
+ * reference's order, one launch per fusion group or tensor primitive
+ * (presk-kernel/src/host.rs:887-1039), each at its site's storage type
+ * (Realization::dtype_at, presk-rt/src/lib.rs:459-471).
+ * ------------------------------------------------------------------------- */
+typedef struct psk_host psk_host;
+
+/* A host over an executor. `realization` is the text of a realization file
+ * (presk-rt/src/lib.rs:374-434): {"default": "bf16", "storage": {site: type},
+ * "params": {path: type}, "quant": {path: {"bits": 8, "over": -2}},
+ * "order": {"kind": "sequential" | "device"}}, or a bare type name as
+ * `--realize f32` gives. NULL on a realization that does not parse;
+ * psk_host_error(NULL) says why. */
+psk_host *psk_host_create(const psk_exec_vtable *exec, const char *realization);
+void psk_host_destroy(psk_host *h);
+const char *psk_host_error(const psk_host *h);
+
+/* The models of the five benchmark configurations. `model` is one of
+ * "mlp" (Linear{784,256}, ReLU, Linear{256,10}, cross-entropy loss),
+ * "gpt" (examples/corpus/nlp/05_gpt.psk), "llama" (examples/coverage/llama.psk),
+ * "contract_ln" (x·w then LayerNorm), "layernorm", "rmsnorm"
+ * (examples/spec/layernorm/layernorm.psk). `consts` are the program's
+ * constants and dimensions as "V=32000 D=4096 H=32 G=32 FF=11008 L=32 B=8 T=2048".
+ * Backend::prepare (presk-rt/src/lib.rs:1276). */
+int psk_host_prepare(psk_host *h, const char *model, const char *consts);
+
+/* Parameters, by path ("blocks.attn.wq", "tok"; a stacked parameter's
+ * leading axis is its layers), given as f64 or f32 host reals and stored as
+ * the realization says (Realization::store_params, lib.rs:711): rounded once
+ * to the path's `params` type, quantised per channel under `quant`, else the
+ * default type. Parameters stay on the executor across calls. */
+int psk_host_set_param(psk_host *h, const char *path, const void *host, int32_t host_dtype, const int64_t *dims, int32_t rank);
+/* The same, drawn on the executor's side of the boundary from a seed:
+ * normal(0, std) or, std < 0, ones. For models whose parameters would not
+ * fit a host copy in reasonable time. The draw is a counter-based hash, not
+ * the reference's ChaCha keys. */
+int psk_host_init_param(psk_host *h, const char *path, uint64_t seed, double std, const int64_t *dims, int32_t rank);
+
+/* Backend::call on `entry` ("apply", "loss"): inputs are host buffers in the
+ * entry's order (reals as f32 or f64, indices as i64), the result is written
+ * to a host buffer of `out_dtype` (PSK_F32 or PSK_F64). Host-to-device and
+ * device-to-host copies happen inside. Returns a psk_status. */
+typedef struct {
+    const void *data;
+    int32_t dtype;
+    int32_t rank;
+    int64_t dims[PSK_MAX_RANK];
+} psk_value;
+int psk_host_call(psk_host *h, const char *entry, const psk_value *inputs, int32_t n_inputs, void *out_host, int32_t out_dtype, int64_t out_capacity, int64_t *out_numel);
+
+/* The same with the inputs already on the executor (`inputs[i].data` is a
+ * device pointer of the host's executor) and the result left there: what a
+ * caller that shards a batch over several executors times. `*out` points at
+ * the result, which belongs to the host until its next call. The launches are
+ * queued, not waited for: psk_exec_sync (or the table's `sync`) ends them and
+ * reports the overflow guard. */
+int psk_host_call_device(psk_host *h, const char *entry, const psk_value *inputs, int32_t n_inputs, void **out, int32_t *out_dtype, int64_t *out_numel);
+
+/* Launch statistics of the last call (Backend::launch_stats): launches, and
+ * the kernel names in order, newline-separated (for the launch-list tests). */
+int64_t psk_host_launches(const psk_host *h);
+const char *psk_host_launch_log(const psk_host *h);
+void psk_host_set_logging(psk_host *h, int on);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,650 @@
+/* psk_oracle.c: TEST INFRASTRUCTURE. A CPU restatement of the reference's
+ * kernel semantics for the launches of include/presk_cuda.h, used only by
+ * tests/, by __graft_entry__.smoke() and by bench.py's CPU legs as the checker
+ * and the timed CPU baseline. The product (presk_b200/) never links, loads or
+ * calls it.
+ *
+ * What it follows, in presk-lang/presk:
+ *   - crates/presk-kernel/src/exec.rs:146-183 (`impl Elem for f32`): one IEEE
+ *     operation in f32 per Bin/Un, musl's transcendental functions;
+ *     :642-662 loads widen exactly; :758-782 stores round once; :847-859
+ *     f32, bf16, binary16 and e8m15 kernels all compute in f32;
+ *   - crates/presk-kernel/src/lower.rs, per primitive (cited at each function);
+ *   - crates/presk-rt/src/lib.rs:228-241 (bf16), crates/presk-rt/src/codes.rs
+ *     (binary16, e8m15, the overflow guard), presk-rt/src/quant.rs:128-167.
+ *
+ * The transcendental functions are the reference's own C
+ * (crates/presk-export-c/c/presk_libm.c), compiled where it lies into
+ * oracle/_ref/libpresk_ref.so by oracle/Makefile and linked here: the same
+ * bits the reference's executors compute (its tests/libm.rs pins that C to
+ * the `libm` crate on 10^6 inputs a function). Everything else in this file
+ * is a restatement, pinned by tests/test_oracle_*.py against that library's
+ * conversions and against the reference's golden vectors.
+ *
+ * Build: cc -std=c11 -O2 -ffp-contract=off (never -ffast-math), as the
+ * reference builds its C (crates/presk-export-c/src/lib.rs:90). -fopenmp
+ * divides the outermost loop of a launch among the host's cores, as the
+ * native executor divides one parallel loop among its workers
+ * (crates/presk-cranelift/src/lib.rs:1636-1691); the bits do not depend on it.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "../include/presk_cuda.h"
+
+/* the reference's libm, from oracle/_ref/libpresk_ref.so */
+float presk_expf(float);
+float presk_logf(float);
+float presk_tanhf(float);
+float presk_sinf(float);
+float presk_cosf(float);
+float presk_erff(float);
+
+static inline uint32_t f2u(float x) { uint32_t u; memcpy(&u, &x, 4); return u; }
+static inline float u2f(uint32_t u) { float x; memcpy(&x, &u, 4); return x; }
+
+/* ---- storage formats -------------------------------------------------------- */
+float psk_o_bf16_to_f32(uint16_t h) { return u2f((uint32_t)h << 16); }
+
+/* presk-rt/src/lib.rs:228-236: to nearest, ties to even; a NaN quiet */
+uint16_t psk_o_f32_to_bf16(float x)
+{
+    uint32_t b = f2u(x);
+    if (x != x) return (uint16_t)((b >> 16) | 0x40u);
+    return (uint16_t)((b + 0x7fffu + ((b >> 16) & 1u)) >> 16);
+}
+
+/* binary16 widened exactly; a NaN keeps sign and payload, made quiet (codes.rs) */
+float psk_o_f16_to_f32(uint16_t c)
+{
+    uint32_t sign = (uint32_t)(c & 0x8000u) << 16, e = (c >> 10) & 0x1fu, m = c & 0x3ffu;
+    if (e == 0x1f) return u2f(sign | 0x7f800000u | (m ? 0x400000u | (m << 13) : 0u));
+    if (e == 0) {
+        float v = (float)m * 0x1p-24f; /* subnormal: m·2^-24, exact */
+        return u2f(f2u(v) | sign);
+    }
+    return u2f(sign | ((e + 112u) << 23) | (m << 13));
+}
+
+/* The code of the IEEE format with t fraction bits and w exponent bits
+ * nearest a finite magnitude given as an integer significand `sig` (its top
+ * bit set at position `top`) times 2^(exp - top): ties to even, overflow to
+ * the infinity's code. The one rounding of codes.rs `narrow`. */
+static uint32_t round_to_format(uint64_t sig, int top, int exp, unsigned t, unsigned w)
+{
+    const int bias = (1 << (w - 1)) - 1, emin = 1 - bias;
+    const uint32_t inf = ((1u << w) - 1u) << t;
+    /* the result keeps t+1 significant bits where normal, fewer below emin */
+    int drop = top - (int)t;
+    if (exp < emin) drop += emin - exp;
+    uint64_t q, rem, half;
+    if (drop <= 0) {
+        q = sig << -drop;
+        rem = 0;
+        half = 1;
+    } else if (drop > 63) {
+        q = 0;
+        rem = sig != 0;
+        half = 2; /* below half of the least subnormal */
+    } else {
+        q = sig >> drop;
+        rem = sig & (((uint64_t)1 << drop) - 1);
+        half = (uint64_t)1 << (drop - 1);
+    }
+    if (rem > half || (rem == half && (q & 1u))) q += 1;
+    uint64_t code;
+    if (exp >= emin) code = ((uint64_t)(exp + bias - 1) << t) + q; /* the leading one adds into the exponent */
+    else code = q;
+    return code < inf ? (uint32_t)code : inf;
+}
+
+uint16_t psk_o_f32_to_f16(float x)
+{
+    uint32_t b = f2u(x), sign = (b >> 16) & 0x8000u, a = b & 0x7fffffffu;
+    if (a > 0x7f800000u) return (uint16_t)(sign | (((a >> 13) | 0x7e00u) & 0x7fffu));
+    if (a == 0x7f800000u) return (uint16_t)(sign | 0x7c00u);
+    uint32_t e = a >> 23, m = a & 0x7fffffu;
+    if (e == 0) return (uint16_t)sign; /* an f32 subnormal is far below half of binary16's least */
+    return (uint16_t)(sign | round_to_format((uint64_t)m | 0x800000u, 23, (int)e - 127, 10, 5));
+}
+
+static uint32_t narrow_f64(double x, unsigned t, unsigned w)
+{
+    uint64_t b;
+    memcpy(&b, &x, 8);
+    uint32_t sign = (uint32_t)(b >> 63) << (t + w);
+    uint64_t a = b & ~((uint64_t)1 << 63);
+    const uint32_t inf = ((1u << w) - 1u) << t;
+    if (a > (uint64_t)0x7ff << 52) return sign | inf | (1u << (t - 1)) | (uint32_t)((a >> (52 - t)) & ((1u << (t - 1)) - 1u));
+    if (a == (uint64_t)0x7ff << 52) return sign | inf;
+    int e = (int)(a >> 52);
+    if (e == 0) return sign;
+    return sign | round_to_format((a & (((uint64_t)1 << 52) - 1)) | ((uint64_t)1 << 52), 52, e - 1023, t, w);
+}
+
+uint16_t psk_o_f64_to_f16(double x) { return (uint16_t)narrow_f64(x, 10, 5); }
+uint32_t psk_o_f64_to_e8m15(double x) { return narrow_f64(x, 15, 8); }
+
+float psk_o_e8m15_to_f32(uint32_t code) { return u2f(code << 8); }
+
+/* codes.rs:96-102 */
+uint32_t psk_o_f32_to_e8m15(float x)
+{
+    uint32_t b = f2u(x);
+    if (x != x) return (b >> 8) | 0x4000u;
+    return (b + 0x7fu + ((b >> 8) & 1u)) >> 8;
+}
+
+/* presk-format/src/lib.rs:136: e4m3fn, bias 7, no infinity, one NaN, max 448 */
+float psk_o_e4m3_to_f32(uint8_t c)
+{
+    uint32_t sign = (uint32_t)(c & 0x80u) << 24, e = (c >> 3) & 0xfu, m = c & 7u;
+    if ((c & 0x7fu) == 0x7fu) return u2f(sign | 0x7fc00000u);
+    float v = e == 0 ? (float)m * 0x1p-9f : ldexpf(1.0f + (float)m / 8.0f, (int)e - 7);
+    return u2f(f2u(v) | sign);
+}
+
+uint8_t psk_o_f32_to_e4m3(float x)
+{
+    uint32_t b = f2u(x), sign = (b >> 24) & 0x80u, a = b & 0x7fffffffu;
+    if (a > 0x7f800000u) return (uint8_t)(sign | 0x7fu);
+    if (a == 0x7f800000u) return (uint8_t)(sign | 0x7fu); /* no infinity: the NaN */
+    uint32_t e = a >> 23, m = a & 0x7fffffu;
+    if (e == 0) return (uint8_t)sign;
+    /* as an IEEE format of 3 fraction and 4 exponent bits, then the top code is the NaN */
+    const int bias = 7, emin = 1 - bias, t = 3;
+    int exp = (int)e - 127, drop = 23 - t;
+    if (exp < emin) drop += emin - exp;
+    uint64_t sig = (uint64_t)m | 0x800000u, q, rem, half;
+    if (drop > 63) { q = 0; rem = 1; half = 2; }
+    else { q = sig >> drop; rem = sig & (((uint64_t)1 << drop) - 1); half = (uint64_t)1 << (drop - 1); }
+    if (rem > half || (rem == half && (q & 1u))) q += 1;
+    uint64_t code = exp >= emin ? ((uint64_t)(exp + bias - 1) << t) + q : q;
+    if (code >= 0x7f) return (uint8_t)(sign | 0x7fu);
+    return (uint8_t)(sign | code);
+}
+
+/* codes.rs `overflows`: a finite value the store turns into an infinity */
+uint32_t psk_o_overflows(int dtype, float x)
+{
+    uint32_t a = f2u(x) & 0x7fffffffu;
+    if (dtype == PSK_F16) return a >= 0x477ff000u && a < 0x7f800000u;
+    if (dtype == PSK_E8M15) return a >= 0x7f7fff80u && a < 0x7f800000u;
+    return 0;
+}
+
+static size_t elem_bytes(int dtype)
+{
+    switch (dtype) {
+    case PSK_F64: case PSK_I64: return 8;
+    case PSK_F32: return 4;
+    case PSK_BF16: case PSK_F16: return 2;
+    case PSK_E8M15: return 3;
+    default: return 1;
+    }
+}
+
+/* exec.rs:642-662: a load in a kernel of arithmetic f32 */
+static float load_real(const void *p, int dtype, int64_t i)
+{
+    switch (dtype) {
+    case PSK_F32: return ((const float *)p)[i];
+    case PSK_BF16: return psk_o_bf16_to_f32(((const uint16_t *)p)[i]);
+    case PSK_F16: return psk_o_f16_to_f32(((const uint16_t *)p)[i]);
+    case PSK_E8M15: {
+        const uint8_t *q = (const uint8_t *)p + 3 * i;
+        return psk_o_e8m15_to_f32((uint32_t)q[0] | (uint32_t)q[1] << 8 | (uint32_t)q[2] << 16);
+    }
+    case PSK_F64: return (float)((const double *)p)[i];
+    case PSK_I64: return (float)(double)((const int64_t *)p)[i];
+    case PSK_E4M3: return psk_o_e4m3_to_f32(((const uint8_t *)p)[i]);
+    case PSK_I8: return (float)((const int8_t *)p)[i];
+    default: return 0.0f;
+    }
+}
+
+/* presk_rt.h `presk_f64_to_i64`: toward zero, saturating, 0 for a NaN */
+static int64_t f32_to_i64(float x)
+{
+    if (x != x) return 0;
+    if (x >= 9223372036854775808.0f) return INT64_MAX;
+    if (x < -9223372036854775808.0f) return INT64_MIN;
+    return (int64_t)x;
+}
+
+/* exec.rs:758-782: a store, rounded once; returns the guard's test */
+static uint32_t store_real(void *p, int dtype, int64_t i, float x)
+{
+    switch (dtype) {
+    case PSK_F32: ((float *)p)[i] = x; return 0;
+    case PSK_BF16: ((uint16_t *)p)[i] = psk_o_f32_to_bf16(x); return 0;
+    case PSK_F16: ((uint16_t *)p)[i] = psk_o_f32_to_f16(x); return psk_o_overflows(PSK_F16, x);
+    case PSK_E8M15: {
+        uint32_t c = psk_o_f32_to_e8m15(x);
+        uint8_t *q = (uint8_t *)p + 3 * i;
+        q[0] = (uint8_t)c; q[1] = (uint8_t)(c >> 8); q[2] = (uint8_t)(c >> 16);
+        return psk_o_overflows(PSK_E8M15, x);
+    }
+    case PSK_F64: ((double *)p)[i] = (double)x; return 0;
+    case PSK_I64: ((int64_t *)p)[i] = f32_to_i64(x); return 0;
+    case PSK_E4M3: ((uint8_t *)p)[i] = psk_o_f32_to_e4m3(x); return 0;
+    default: return 0;
+    }
+}
+
+/* host.rs:809-829: an input of another type than the kernel's is converted at
+ * its edge, Buf::of(kdtype, b.to_f64()); a widening is exact, so only a
+ * narrowing changes a value. Done here element by element as it is loaded. */
+static float edge_round(float x, int kdtype, int dtype, uint32_t *ovf)
+{
+    if (dtype == kdtype || dtype == PSK_I64 || dtype == PSK_I8) return x;
+    switch (kdtype) {
+    case PSK_BF16:
+        return (dtype == PSK_F32 || dtype == PSK_F64 || dtype == PSK_F16 || dtype == PSK_E8M15) ? psk_o_bf16_to_f32(psk_o_f32_to_bf16(x)) : x;
+    case PSK_F16:
+        if (dtype == PSK_E4M3) return x;
+        *ovf |= psk_o_overflows(PSK_F16, x);
+        return psk_o_f16_to_f32(psk_o_f32_to_f16(x));
+    case PSK_E8M15:
+        if (dtype == PSK_BF16 || dtype == PSK_F16 || dtype == PSK_E4M3) return x;
+        *ovf |= psk_o_overflows(PSK_E8M15, x);
+        return psk_o_e8m15_to_f32(psk_o_f32_to_e8m15(x));
+    default: return x;
+    }
+}
+
+/* ---- a launch's operands ------------------------------------------------------ */
+typedef struct {
+    const uint8_t *p;
+    const float *scales;
+    const psk_operand *o;
+} operand;
+
+static int64_t offset_of(const int64_t *stride, const int64_t *dims, int first, int n, int64_t lin)
+{
+    int64_t off = 0;
+    for (int a = first + n - 1; a >= first; --a) {
+        int64_t d = dims[a], i = lin % d;
+        lin /= d;
+        off += i * stride[a];
+    }
+    return off;
+}
+
+static float load_operand(const operand *x, int64_t off, int64_t soff, int kdtype, uint32_t *ovf)
+{
+    if (x->o->dtype == PSK_I8) return (float)((const int8_t *)x->p)[off] * x->scales[soff]; /* quant.rs:250-252 */
+    return edge_round(load_real(x->p, x->o->dtype, off), kdtype, x->o->dtype, ovf);
+}
+
+/* lower.rs:184-226, exec.rs:146-183 */
+static float prim_unary(int prim, float x, int imm)
+{
+    switch (prim) {
+    case PSK_NEG: return -x;
+    case PSK_EXP: return presk_expf(x);
+    case PSK_LOG: return presk_logf(x);
+    case PSK_TANH: return presk_tanhf(x);
+    case PSK_SQRT: return sqrtf(x);
+    case PSK_SIN: return presk_sinf(x);
+    case PSK_COS: return presk_cosf(x);
+    case PSK_ABS: return fabsf(x);
+    case PSK_GELU: {
+        float phi = (1.0f + presk_erff(x / (float)1.4142135623730951)) / 2.0f;
+        return x * phi;
+    }
+    case PSK_GELU_DERIV: {
+        float phi = (1.0f + presk_erff(x / (float)1.4142135623730951)) / 2.0f;
+        float dens = presk_expf((-(x * x)) / 2.0f) / (float)2.5066282746310002;
+        return phi + x * dens;
+    }
+    case PSK_RELU: return x < 0.0f ? 0.0f : x;
+    case PSK_HEAVISIDE: return x > 0.0f ? 1.0f : 0.0f;
+    case PSK_SIGN: return x < 0.0f ? -1.0f : (x > 0.0f ? 1.0f : 0.0f);
+    case PSK_SIGMOID: return 1.0f / (1.0f + presk_expf(-x));
+    case PSK_POW: {
+        if (imm == 0) return 1.0f;
+        float e = x;
+        for (int i = 1; i < imm; ++i) e = e * x;
+        return e;
+    }
+    default: return x;
+    }
+}
+
+static float prim_binary(int prim, float x, float y)
+{
+    switch (prim) {
+    case PSK_ADD: return x + y;
+    case PSK_SUB: return x - y;
+    case PSK_MUL: return x * y;
+    case PSK_DIV: return x / y;
+    case PSK_MAX: return x > y ? x : y;
+    default: return x < y ? x : y;
+    }
+}
+
+/* ---- the launches ------------------------------------------------------------- */
+int psk_oracle_run(const psk_launch *l, void *const *table, uint32_t *overflow)
+{
+    const int no = l->n_outer, ni = l->n_inner, kd = l->dtype;
+    operand in[PSK_MAX_INPUTS];
+    int scale_slot = l->n_inputs + 1;
+    for (int i = 0; i < l->n_inputs; ++i) {
+        in[i].o = &l->in[i];
+        in[i].p = (const uint8_t *)table[i] + l->in[i].offset * (int64_t)elem_bytes(l->in[i].dtype);
+        in[i].scales = l->in[i].dtype == PSK_I8 ? (const float *)table[scale_slot++] : NULL;
+    }
+    uint8_t *outp = (uint8_t *)table[l->n_inputs] + l->out.offset * (int64_t)elem_bytes(l->out.dtype);
+    int64_t total = 1, inner = 1;
+    for (int a = 0; a < no; ++a) total *= l->dims[a];
+    for (int c = 0; c < ni; ++c) inner *= l->dims[no + c];
+    uint32_t ovf_all = 0;
+    if (kd == PSK_F64) return PSK_E7005;
+
+    switch (l->op) {
+    case PSK_OP_FUSED: /* lower.rs:328-360 */
+#pragma omp parallel for schedule(static) reduction(| : ovf_all)
+        for (int64_t lin = 0; lin < total; ++lin) {
+            uint32_t ovf = 0;
+            float vals[PSK_MAX_STEPS];
+            for (int s = 0; s < l->n_steps; ++s) {
+                const psk_step *st = &l->steps[s];
+                float a[2] = {0, 0};
+                for (int j = 0; j < st->nargs; ++j) {
+                    int src = st->src[j];
+                    a[j] = src >= 0 ? load_operand(&in[src], offset_of(l->in[src].stride, l->dims, 0, no, lin), offset_of(l->in[src].scale_stride, l->dims, 0, no, lin), kd, &ovf) : vals[-1 - src];
+                }
+                vals[s] = st->nargs == 1 ? prim_unary(st->prim, a[0], st->imm) : prim_binary(st->prim, a[0], a[1]);
+            }
+            ovf |= store_real(outp, l->out.dtype, offset_of(l->out.stride, l->dims, 0, no, lin), vals[l->n_steps - 1]);
+            ovf_all |= ovf;
+        }
+        break;
+    case PSK_OP_CONTRACT: /* lower.rs:465-474, 586-636: acc = acc + (x·w), the terms in lexicographic order */
+#pragma omp parallel for schedule(static) reduction(| : ovf_all)
+        for (int64_t lin = 0; lin < total; ++lin) {
+            uint32_t ovf = 0;
+            int64_t base[PSK_MAX_INPUTS], sbase[PSK_MAX_INPUTS];
+            for (int i = 0; i < l->n_inputs; ++i) {
+                base[i] = offset_of(l->in[i].stride, l->dims, 0, no, lin);
+                sbase[i] = offset_of(l->in[i].scale_stride, l->dims, 0, no, lin);
+            }
+            float acc = 0.0f;
+            if (ni == 1 && l->n_inputs == 2) {
+                const int64_t s0 = l->in[0].stride[no], s1 = l->in[1].stride[no], q0 = l->in[0].scale_stride[no], q1 = l->in[1].scale_stride[no];
+                for (int64_t c = 0; c < inner; ++c) {
+                    float x = load_operand(&in[0], base[0] + c * s0, sbase[0] + c * q0, kd, &ovf);
+                    float w = load_operand(&in[1], base[1] + c * s1, sbase[1] + c * q1, kd, &ovf);
+                    float prod = x * w;
+                    acc = acc + prod;
+                }
+            } else {
+                for (int64_t c = 0; c < inner; ++c) {
+                    float prod = 1.0f;
+                    for (int i = 0; i < l->n_inputs; ++i)
+                        prod = prod * load_operand(&in[i], base[i] + offset_of(l->in[i].stride, l->dims, no, ni, c), sbase[i] + offset_of(l->in[i].scale_stride, l->dims, no, ni, c), kd, &ovf);
+                    acc = acc + prod;
+                }
+            }
+            ovf |= store_real(outp, l->out.dtype, offset_of(l->out.stride, l->dims, 0, no, lin), acc);
+            ovf_all |= ovf;
+        }
+        break;
+    case PSK_OP_REDUCE: /* lower.rs:1221-1255, 1693 */
+#pragma omp parallel for schedule(static) reduction(| : ovf_all)
+        for (int64_t lin = 0; lin < total; ++lin) {
+            uint32_t ovf = 0;
+            int64_t base = offset_of(l->in[0].stride, l->dims, 0, no, lin);
+            float acc = 0.0f;
+            for (int64_t c = 0; c < inner; ++c) {
+                float x = load_operand(&in[0], base + offset_of(l->in[0].stride, l->dims, no, ni, c), 0, kd, &ovf);
+                acc = acc + (l->kind == PSK_REDUCE_SUMSQ ? x * x : x);
+            }
+            if (l->kind == PSK_REDUCE_MEAN) acc = acc / (float)(double)l->iparam[0];
+            ovf |= store_real(outp, l->out.dtype, offset_of(l->out.stride, l->dims, 0, no, lin), acc);
+            ovf_all |= ovf;
+        }
+        break;
+    case PSK_OP_SOFTMAX: { /* lower.rs:1274-1311 and 1368-1419 (three passes) */
+        const int64_t n = inner, s = l->in[0].stride[no], os = l->out.stride[no];
+        if (n == 0) break;
+#pragma omp parallel for schedule(static) reduction(| : ovf_all)
+        for (int64_t row = 0; row < total; ++row) {
+            uint32_t ovf = 0;
+            int64_t base = offset_of(l->in[0].stride, l->dims, 0, no, row), obase = offset_of(l->out.stride, l->dims, 0, no, row);
+#define X(k) load_operand(&in[0], base + (k) * s, 0, kd, &ovf)
+            if (!l->masked) {
+                float m = X(0);
+                for (int64_t k = 0; k < n; ++k) if (X(k) > m) m = X(k);
+                float z = 0.0f;
+                for (int64_t k = 0; k < n; ++k) z = z + presk_expf(X(k) - m);
+                for (int64_t k = 0; k < n; ++k) ovf |= store_real(outp, l->out.dtype, obase + k * os, presk_expf(X(k) - m) / z);
+            } else {
+                int64_t mbase = offset_of(l->in[1].stride, l->dims, 0, no, row), ms = l->in[1].stride[no];
+                const int64_t *mk = (const int64_t *)in[1].p;
+#define ALLOWED(k) ((float)(double)mk[mbase + (k) * ms] > 0.5f)
+                float mx = 0.0f, first = 1.0f;
+                for (int64_t k = 0; k < n; ++k) {
+                    mx = ALLOWED(k) ? (first > 0.5f ? X(k) : (X(k) > mx ? X(k) : mx)) : mx;
+                    first = ALLOWED(k) ? 0.0f : first;
+                }
+                float z = 0.0f;
+                for (int64_t k = 0; k < n; ++k) z = z + (ALLOWED(k) ? presk_expf(X(k) - mx) : 0.0f);
+                for (int64_t k = 0; k < n; ++k) ovf |= store_real(outp, l->out.dtype, obase + k * os, ALLOWED(k) ? presk_expf(X(k) - mx) / z : 0.0f);
+#undef ALLOWED
+            }
+#undef X
+            ovf_all |= ovf;
+        }
+        break;
+    }
+    case PSK_OP_XENT: { /* lower.rs:1459-1470: ln z + m - x[y] */
+        const int64_t n = inner, s = l->in[0].stride[no];
+        int bad = 0;
+#pragma omp parallel for schedule(static) reduction(| : ovf_all, bad)
+        for (int64_t row = 0; row < total; ++row) {
+            uint32_t ovf = 0;
+            int64_t base = offset_of(l->in[0].stride, l->dims, 0, no, row);
+            float m = load_operand(&in[0], base, 0, kd, &ovf);
+            for (int64_t k = 0; k < n; ++k) {
+                float x = load_operand(&in[0], base + k * s, 0, kd, &ovf);
+                if (x > m) m = x;
+            }
+            float z = 0.0f;
+            for (int64_t k = 0; k < n; ++k) z = z + presk_expf(load_operand(&in[0], base + k * s, 0, kd, &ovf) - m);
+            int64_t y = ((const int64_t *)in[1].p)[offset_of(l->in[1].stride, l->dims, 0, no, row)];
+            float xy = 0.0f;
+            if (y >= 0 && y < n) xy = load_operand(&in[0], base + y * s, 0, kd, &ovf);
+            else bad |= 1;
+            ovf |= store_real(outp, l->out.dtype, offset_of(l->out.stride, l->dims, 0, no, row), (presk_logf(z) + m) - xy);
+            ovf_all |= ovf;
+        }
+        if (bad) return PSK_E7001;
+        break;
+    }
+    case PSK_OP_ARGMAX: { /* lower.rs:1490: the last of equal maxima */
+        const int64_t n = inner, s = l->in[0].stride[no];
+        for (int64_t row = 0; row < total; ++row) {
+            uint32_t ovf = 0;
+            int64_t base = offset_of(l->in[0].stride, l->dims, 0, no, row);
+            float m = load_operand(&in[0], base, 0, kd, &ovf);
+            int64_t best = 0;
+            for (int64_t k = 0; k < n; ++k) {
+                float x = load_operand(&in[0], base + k * s, 0, kd, &ovf);
+                if (x >= m) { m = x; best = k; }
+            }
+            ((int64_t *)outp)[offset_of(l->out.stride, l->dims, 0, no, row)] = best;
+        }
+        break;
+    }
+    case PSK_OP_EMBED: { /* lower.rs:1421-1437 */
+        const int last = no - 1;
+        const int64_t d = l->dims[last], rows = total / (d ? d : 1);
+        int bad = 0;
+#pragma omp parallel for schedule(static) reduction(| : ovf_all, bad)
+        for (int64_t row = 0; row < rows; ++row) {
+            uint32_t ovf = 0;
+            int64_t id = ((const int64_t *)in[1].p)[offset_of(l->in[1].stride, l->dims, 0, last, row)];
+            int64_t obase = offset_of(l->out.stride, l->dims, 0, last, row);
+            if (id < 0 || id >= l->iparam[0]) { bad |= 1; id = 0; }
+            for (int64_t j = 0; j < d; ++j)
+                ovf |= store_real(outp, l->out.dtype, obase + j * l->out.stride[last], load_operand(&in[0], id * l->in[0].stride[0] + j * l->in[0].stride[1], 0, kd, &ovf));
+            ovf_all |= ovf;
+        }
+        if (bad) return PSK_E7001;
+        break;
+    }
+    case PSK_OP_COPY: /* lower.rs:1554-1667: Store(Load) through the index maps */
+#pragma omp parallel for schedule(static) reduction(| : ovf_all)
+        for (int64_t lin = 0; lin < total; ++lin) {
+            uint32_t ovf = 0;
+            int64_t off = offset_of(l->in[0].stride, l->dims, 0, no, lin), ooff = offset_of(l->out.stride, l->dims, 0, no, lin);
+            if (l->in[0].is_index) ((int64_t *)outp)[ooff] = ((const int64_t *)in[0].p)[off];
+            else ovf |= store_real(outp, l->out.dtype, ooff, load_operand(&in[0], off, 0, kd, &ovf));
+            ovf_all |= ovf;
+        }
+        break;
+    case PSK_OP_IOTA: /* lower.rs:1706-1750 */
+        for (int64_t lin = 0; lin < total; ++lin) {
+            switch (l->kind) {
+            case PSK_IOTA_POSITIONS: ((int64_t *)outp)[lin] = lin; break;
+            case PSK_IOTA_CAUSAL: {
+                int64_t n = l->dims[1], i = lin / n, j = lin % n;
+                ((int64_t *)outp)[lin] = (float)(double)j <= (float)(double)i ? 1 : 0;
+                break;
+            }
+            case PSK_IOTA_ONE_HOT: {
+                int64_t v = l->dims[no - 1], row = lin / v, j = lin % v;
+                int64_t id = ((const int64_t *)in[0].p)[offset_of(l->in[0].stride, l->dims, 0, no - 1, row)];
+                ovf_all |= store_real(outp, l->out.dtype, lin, (float)(double)id == (float)(double)j ? 1.0f : 0.0f);
+                break;
+            }
+            default: ovf_all |= store_real(outp, l->out.dtype, lin, (float)l->fparam[0]); break;
+            }
+        }
+        break;
+    case PSK_OP_CONVERT: /* presk-rt/src/lib.rs:868-876, presk_rt.c `presk_convert` */
+        for (int64_t i = 0; i < total; ++i) {
+            if (l->in[0].dtype == PSK_F64) {
+                double x = ((const double *)in[0].p)[i];
+                switch (l->out.dtype) {
+                case PSK_F64: ((double *)outp)[i] = x; break;
+                case PSK_F16: ((uint16_t *)outp)[i] = psk_o_f64_to_f16(x); ovf_all |= (fabs(x) >= 65520.0 && fabs(x) < INFINITY); break;
+                case PSK_E8M15: {
+                    uint32_t c = psk_o_f64_to_e8m15(x);
+                    uint8_t *q = outp + 3 * i;
+                    q[0] = (uint8_t)c; q[1] = (uint8_t)(c >> 8); q[2] = (uint8_t)(c >> 16);
+                    ovf_all |= (fabs(x) >= 0x1.ffffp127 && fabs(x) < INFINITY);
+                    break;
+                }
+                default: ovf_all |= store_real(outp, l->out.dtype, i, (float)x); break; /* to bf16 by way of f32 */
+                }
+            } else {
+                ovf_all |= store_real(outp, l->out.dtype, i, load_real(in[0].p, l->in[0].dtype, i));
+            }
+        }
+        break;
+    default:
+        return PSK_E7001;
+    }
+    int guarded = l->guarded && (l->out.dtype == PSK_F16 || l->out.dtype == PSK_E8M15 || kd == PSK_F16 || kd == PSK_E8M15);
+    if (overflow) *overflow = guarded ? ovf_all : 0;
+    return PSK_OK;
+}
+
+/* presk-rt/src/quant.rs:128-167 (absmax): per channel m = max|w| over k, s =
+ * f32(m / qmax), q = clamp(rne(w / s), +-qmax), 0 when s is 0 or w / s a NaN. */
+void psk_oracle_quantize(const void *w, int from, int8_t *q, float *s, int64_t outer, int64_t k, int64_t inner)
+{
+#define W(e) (from == PSK_F64 ? ((const double *)w)[e] : (double)((const float *)w)[e])
+    for (int64_t o = 0; o < outer; ++o)
+        for (int64_t in = 0; in < inner; ++in) {
+            double m = 0.0;
+            for (int64_t kk = 0; kk < k; ++kk) {
+                double a = fabs(W((o * k + kk) * inner + in));
+                if (a > m) m = a;
+            }
+            float sc = (float)(m / 127.0);
+            s[o * inner + in] = sc;
+            for (int64_t kk = 0; kk < k; ++kk) {
+                int64_t e = (o * k + kk) * inner + in;
+                double r = W(e) / (double)sc;
+                int v = 0;
+                if (sc != 0.0f && r == r) {
+                    double t = nearbyint(r);
+                    t = t > 127.0 ? 127.0 : (t < -127.0 ? -127.0 : t);
+                    v = (int)t;
+                }
+                q[e] = (int8_t)v;
+            }
+        }
+#undef W
+}
+
+/* ---- the oracle as an executor, so that the host program can run over it -------- */
+typedef struct {
+    char error[256];
+    int64_t launches;
+    int64_t first_overflow; /* 1 + the launch */
+} oracle_exec;
+
+static const char *o_name(void *s) { (void)s; return "oracle"; }
+static void *o_alloc(void *s, size_t b) { (void)s; return malloc(b ? b : 1); }
+static void o_free(void *s, void *p) { (void)s; free(p); }
+static int o_upload(void *s, void *d, const void *h, size_t b) { (void)s; memcpy(d, h, b); return PSK_OK; }
+static int o_download(void *s, void *h, const void *d, size_t b) { (void)s; memcpy(h, d, b); return PSK_OK; }
+static int o_run(void *s, const psk_launch *l, void *const *t)
+{
+    oracle_exec *e = (oracle_exec *)s;
+    uint32_t ovf = 0;
+    int rc = psk_oracle_run(l, t, &ovf);
+    if (rc != PSK_OK) snprintf(e->error, sizeof e->error, "%s: the oracle does not run this launch (%d)", l->name ? l->name : "?", rc);
+    if (ovf && !e->first_overflow) e->first_overflow = e->launches + 1;
+    e->launches += 1;
+    return rc;
+}
+static int64_t o_overflow(void *s)
+{
+    oracle_exec *e = (oracle_exec *)s;
+    int64_t r = e->first_overflow;
+    e->first_overflow = 0;
+    return r;
+}
+static int o_sync(void *s)
+{
+    oracle_exec *e = (oracle_exec *)s;
+    int64_t o = o_overflow(s);
+    if (o) {
+        snprintf(e->error, sizeof e->error, "launch %lld: a store rounded a finite value to an infinity", (long long)(o - 1));
+        return PSK_E7007;
+    }
+    return PSK_OK;
+}
+static const char *o_error(void *s) { return ((oracle_exec *)s)->error; }
+static int o_quantize(void *s, const void *w, int32_t from, int8_t *q, float *sc, int64_t outer, int64_t k, int64_t inner)
+{
+    (void)s;
+    psk_oracle_quantize(w, from, q, sc, outer, k, inner);
+    return PSK_OK;
+}
+
+void psk_oracle_vtable(psk_exec_vtable *out)
+{
+    oracle_exec *e = (oracle_exec *)calloc(1, sizeof *e);
+    out->self = e;
+    out->name = o_name;
+    out->alloc = o_alloc;
+    out->free = o_free;
+    out->upload = o_upload;
+    out->download = o_download;
+    out->run = o_run;
+    out->sync = o_sync;
+    out->overflow = o_overflow;
+    out->last_error = o_error;
+    out->quantize = o_quantize;
+    out->init_normal = NULL;
+}

@@ -1,0 +1,216 @@
+"""Executor and Host: numpy-facing wrappers over the C ABI."""
+import ctypes as C
+
+import numpy as np
+
+from . import abi
+
+_NP_OF = {abi.F64: np.float64, abi.F32: np.float32, abi.BF16: np.uint16, abi.I64: np.int64, abi.F16: np.uint16, abi.E8M15: np.uint8, abi.I8: np.int8, abi.E4M3: np.uint8}
+
+
+class PreskError(RuntimeError):
+    """A call of the library that did not return PSK_OK; `code` is the reference's E-number."""
+
+    def __init__(self, code, message):
+        super().__init__(f"E{code}: {message}")
+        self.code = code
+        self.message = message
+
+
+def _dtype_of_array(a):
+    if a.dtype == np.float64:
+        return abi.F64
+    if a.dtype == np.float32:
+        return abi.F32
+    if a.dtype == np.int64:
+        return abi.I64
+    raise TypeError(f"host values are float32, float64 or int64 arrays, not {a.dtype}")
+
+
+class Executor:
+    """`KernelExec` on one CUDA device. Buffers are raw device pointers (ints)."""
+
+    def __init__(self, device=0):
+        self.lib = abi.load()
+        self.handle = self.lib.psk_exec_create(device)
+        if not self.handle:
+            raise PreskError(abi.E10001, self.lib.psk_last_error(None).decode())
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self.lib.psk_exec_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, rc):
+        if rc != abi.OK:
+            raise PreskError(rc, self.lib.psk_last_error(self.handle).decode())
+
+    def alloc(self, nbytes):
+        p = self.lib.psk_exec_alloc(self.handle, nbytes)
+        if not p:
+            raise PreskError(abi.E10001, self.lib.psk_last_error(self.handle).decode())
+        return p
+
+    def free(self, p):
+        self.lib.psk_exec_free(self.handle, p)
+
+    def upload(self, array):
+        """A device buffer holding the bytes of `array`."""
+        a = np.ascontiguousarray(array)
+        p = self.alloc(max(a.nbytes, 1))
+        if a.nbytes:
+            self._check(self.lib.psk_exec_upload(self.handle, p, a.ctypes.data, a.nbytes))
+        return p
+
+    def download(self, p, nbytes):
+        out = np.empty(nbytes, dtype=np.uint8)
+        if nbytes:
+            self._check(self.lib.psk_exec_download(self.handle, out.ctypes.data, p, nbytes))
+        return out
+
+    def run(self, launch, table):
+        arr = (C.c_void_p * len(table))(*table)
+        self._check(self.lib.psk_exec_run(self.handle, C.byref(launch), arr))
+
+    def gemm(self, g, a, b, c):
+        self._check(self.lib.psk_exec_gemm(self.handle, C.byref(g), a, b, c))
+
+    def sync(self):
+        self._check(self.lib.psk_exec_sync(self.handle))
+
+    def overflow(self):
+        return self.lib.psk_exec_overflow(self.handle)
+
+    def counts(self):
+        a, b = C.c_int64(), C.c_int64()
+        self.lib.psk_exec_counts(self.handle, C.byref(a), C.byref(b))
+        return a.value, b.value
+
+    def memory(self):
+        a, b = C.c_size_t(), C.c_size_t()
+        self.lib.psk_exec_memory(self.handle, C.byref(a), C.byref(b))
+        return a.value, b.value
+
+    def stream(self):
+        return self.lib.psk_exec_stream(self.handle)
+
+    def vtable(self):
+        vt = abi.ExecVtable()
+        self.lib.psk_exec_as_vtable(self.handle, C.byref(vt))
+        return vt
+
+
+class Host:
+    """`Backend`: prepare a model under a realization, give it parameters, call an entry.
+
+    `executor` is an `Executor`, or an `abi.ExecVtable` of another executor
+    (tests hand it the CPU oracle's, loaded from oracle/; the product never does).
+    """
+
+    def __init__(self, executor, realization="f32", lib=None):
+        self.executor = executor
+        if isinstance(executor, Executor):
+            self.lib = executor.lib
+            self._vt = executor.vtable()
+        else:
+            self.lib = lib if lib is not None else abi.load()
+            self._vt = executor
+        text = realization if isinstance(realization, str) else __import__("json").dumps(realization)
+        self.handle = self.lib.psk_host_create(C.byref(self._vt), text.encode())
+        if not self.handle:
+            raise PreskError(abi.E7001, self.lib.psk_host_error(None).decode())
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self.lib.psk_host_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, rc):
+        if rc != abi.OK:
+            raise PreskError(rc, self.lib.psk_host_error(self.handle).decode())
+
+    def prepare(self, model, **consts):
+        text = " ".join(f"{k}={int(v)}" for k, v in consts.items())
+        self._check(self.lib.psk_host_prepare(self.handle, model.encode(), text.encode()))
+        return self
+
+    def set_param(self, path, array):
+        a = np.ascontiguousarray(array)
+        dims = (C.c_int64 * max(a.ndim, 1))(*a.shape)
+        self._check(self.lib.psk_host_set_param(self.handle, path.encode(), a.ctypes.data, _dtype_of_array(a), dims, a.ndim))
+
+    def init_param(self, path, seed, std, shape):
+        dims = (C.c_int64 * max(len(shape), 1))(*shape)
+        self._check(self.lib.psk_host_init_param(self.handle, path.encode(), seed, std, dims, len(shape)))
+
+    @staticmethod
+    def _values(inputs, device_ptrs=None):
+        vals = (abi.Value * max(len(inputs), 1))()
+        keep = []
+        for i, x in enumerate(inputs):
+            if device_ptrs is not None:
+                ptr, dtype, shape = x
+                vals[i].data, vals[i].dtype, vals[i].rank = ptr, dtype, len(shape)
+                for k, d in enumerate(shape):
+                    vals[i].dims[k] = d
+            else:
+                a = np.ascontiguousarray(x)
+                keep.append(a)
+                vals[i].data, vals[i].dtype, vals[i].rank = a.ctypes.data, _dtype_of_array(a), a.ndim
+                for k, d in enumerate(a.shape):
+                    vals[i].dims[k] = d
+        return vals, keep
+
+    def call(self, entry, inputs, out_shape, out_dtype=np.float32):
+        """Backend::call with host arrays; returns the result as a numpy array of `out_shape`."""
+        vals, keep = self._values(inputs)
+        out = np.empty(out_shape, dtype=out_dtype)
+        n = C.c_int64()
+        code = {np.dtype(np.float32): abi.F32, np.dtype(np.float64): abi.F64, np.dtype(np.int64): abi.I64}[np.dtype(out_dtype)]
+        self._check(self.lib.psk_host_call(self.handle, entry.encode(), vals, len(inputs), out.ctypes.data, code, out.size, C.byref(n)))
+        if n.value != out.size:
+            raise PreskError(abi.E7001, f"the result has {n.value} elements, not {out.size}")
+        return out
+
+    def call_device(self, entry, inputs):
+        """Backend::call with device inputs [(ptr, dtype, shape)]; returns (ptr, dtype, numel), queued."""
+        vals, _ = self._values(inputs, device_ptrs=True)
+        out, dt, n = C.c_void_p(), C.c_int32(), C.c_int64()
+        self._check(self.lib.psk_host_call_device(self.handle, entry.encode(), vals, len(inputs), C.byref(out), C.byref(dt), C.byref(n)))
+        return out.value, dt.value, n.value
+
+    def launches(self):
+        return self.lib.psk_host_launches(self.handle)
+
+    def set_logging(self, on=True):
+        self.lib.psk_host_set_logging(self.handle, 1 if on else 0)
+
+    def launch_log(self):
+        return self.lib.psk_host_launch_log(self.handle).decode().splitlines()
+
+
+def launch_desc(op, dtype, dims_outer, dims_inner=(), order=abi.ORDER_SEQUENTIAL, name=b"launch"):
+    """An empty `psk_launch` over an iteration space; the caller fills the operands."""
+    l = abi.Launch()
+    l.name = name
+    l.op = op
+    l.dtype = dtype
+    l.order = order
+    l.guarded = 1
+    l.n_outer = len(dims_outer)
+    l.n_inner = len(dims_inner)
+    for i, d in enumerate(list(dims_outer) + list(dims_inner)):
+        l.dims[i] = d
+    return l

@@ -1,0 +1,761 @@
+// The CUDA executor behind include/presk_cuda.h: device buffers, the dispatch
+// of a launch to a kernel of this library, the overflow guard's flags.
+//
+// It stands where the reference's `NativeExec` stands
+// (crates/presk-cranelift/src/lib.rs:1544-1693): given a kernel and its
+// buffers it runs the loop nest. Where the native executor compiles the nest
+// it is given, this one recognises which of its ahead-of-time kernels the
+// launch is (by operation, strides and types) and refuses what it has none
+// for; it never computes on the host.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/presk_cuda.h"
+#include "psk_gemm_tc.cuh"
+#include "psk_kernels.cuh"
+
+using namespace psk;
+
+namespace {
+
+constexpr int kFlagSlots = 4096;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+std::string g_create_error;
+
+} // namespace
+
+struct psk_exec {
+    int device = 0;
+    int sms = 148;
+    cudaStream_t stream = nullptr;
+    std::string error;
+    size_t live = 0, peak = 0;
+    std::unordered_map<void *, size_t> sizes;          // every live buffer and its bytes
+    std::map<size_t, std::vector<void *>> pool;        // freed buffers by exact size
+    std::unordered_map<void *, int64_t> causal;        // buffers a causal_mask launch wrote: its n
+    uint32_t *flags = nullptr;                         // kFlagSlots words of the overflow guard
+    uint32_t *status = nullptr;                        // one word: kernel-side trouble
+    std::vector<int64_t> flag_serial;                  // the launch each slot was last given to
+    int64_t guarded_since = 0;
+    int64_t launches = 0, kernels = 0;
+    std::string overflow_name;
+    bool profiling = false;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    double last_ms = -1.0;
+    EncodeTiledFn encode = nullptr;
+    bool tc_attr_set = false;
+};
+
+namespace {
+
+int fail(psk_exec *e, int code, const std::string &msg)
+{
+    if (e) e->error = msg;
+    else g_create_error = msg;
+    return code;
+}
+
+#define CUDA_TRY(e, call)                                                                   \
+    do {                                                                                    \
+        cudaError_t err__ = (call);                                                         \
+        if (err__ != cudaSuccess)                                                           \
+            return fail(e, PSK_E10001, std::string(#call) + ": " + cudaGetErrorString(err__)); \
+    } while (0)
+
+size_t elem_bytes(int dtype)
+{
+    switch (dtype) {
+    case PSK_F64: case PSK_I64: return 8;
+    case PSK_F32: return 4;
+    case PSK_BF16: case PSK_F16: return 2;
+    case PSK_E8M15: return 3;
+    default: return 1;
+    }
+}
+
+int grid_for(const psk_exec *e, int64_t work, int block, int per_sm)
+{
+    int64_t blocks = (work + block - 1) / block;
+    int64_t cap = (int64_t)e->sms * per_sm;
+    return (int)std::max<int64_t>(1, std::min(blocks, cap));
+}
+
+// ---- the device form of a launch ------------------------------------------
+void fill_operand(DevOperand &d, const psk_operand &o, void *base, const float *scales, int naxes)
+{
+    d.p = (const uint8_t *)base + o.offset * (int64_t)elem_bytes(o.dtype);
+    d.scales = scales;
+    d.dtype = o.dtype;
+    d.is_index = o.is_index;
+    for (int a = 0; a < PSK_MAX_AXES; ++a) {
+        d.stride[a] = a < naxes ? o.stride[a] : 0;
+        d.sstride[a] = a < naxes ? o.scale_stride[a] : 0;
+    }
+}
+
+// Merges adjacent outer axes every operand walks as one, and drops axes of
+// length one: fewer divisions a thread, longer contiguous runs.
+void coalesce_outer(DevLaunch &L)
+{
+    const int n = L.n_outer, ni = L.n_inner;
+    auto move_axis = [&](int to, int from) {
+        if (to == from) return;
+        L.dims[to] = L.dims[from];
+        L.out.stride[to] = L.out.stride[from];
+        for (int i = 0; i < L.n_in; ++i) {
+            L.in[i].stride[to] = L.in[i].stride[from];
+            L.in[i].sstride[to] = L.in[i].sstride[from];
+        }
+    };
+    // drop axes of length one (keeping one axis when there is nothing else)
+    int kept = 0;
+    for (int a = 0; a < n; ++a)
+        if (L.dims[a] != 1) move_axis(kept++, a);
+    if (kept == 0 && n > 0) {
+        move_axis(0, n - 1);
+        kept = 1;
+    }
+    // merge axis a into the one before when everyone walks them as one
+    int r = 0;
+    for (int a = 1; a < kept; ++a) {
+        bool ok = L.out.stride[r] == L.out.stride[a] * L.dims[a];
+        for (int i = 0; ok && i < L.n_in; ++i)
+            ok = L.in[i].stride[r] == L.in[i].stride[a] * L.dims[a] && L.in[i].sstride[r] == L.in[i].sstride[a] * L.dims[a];
+        if (ok) {
+            int64_t d = L.dims[r] * L.dims[a];
+            move_axis(r, a);
+            L.dims[r] = d;
+        } else {
+            move_axis(++r, a);
+        }
+    }
+    const int new_outer = kept == 0 ? 0 : r + 1;
+    for (int c = 0; c < ni; ++c) move_axis(new_outer + c, n + c);
+    L.n_outer = new_outer;
+}
+
+bool aligned16(const void *p) { return ((uintptr_t)p & 15u) == 0; }
+
+// Whether the operand can be read eight last-axis elements at a time.
+bool vec8_operand(const DevOperand &o, const int64_t *dims, int n_outer, bool is_out)
+{
+    const int last = n_outer - 1;
+    if (o.dtype == PSK_E8M15 || o.dtype == PSK_E4M3 || o.dtype == PSK_I8 || o.dtype == PSK_F64 || o.dtype == PSK_I64) {
+        // read element by element inside the vector path: any alignment will do,
+        // but an integer weight's scales must walk with it
+        if (is_out) return o.stride[last] == 1;
+        return o.stride[last] == 0 || o.stride[last] == 1;
+    }
+    if (o.stride[last] == 0 && !is_out) return true;
+    if (o.stride[last] != 1) return false;
+    const size_t eb = elem_bytes(o.dtype);
+    if (((uintptr_t)o.p % (8 * eb > 16 ? 16 : 8 * eb)) != 0) return false;
+    for (int a = 0; a < last; ++a)
+        if (o.stride[a] % 8 != 0) return false;
+    (void)dims;
+    return true;
+}
+
+// ---- a contraction seen as a batched matrix product ------------------------
+struct GemmMap {
+    int64_t m = 1, n = 1, k = 1, batch = 1, batch_lo = 1;
+    int64_t a_row = 0, a_k = 0, a_lo = 0, a_hi = 0;
+    int64_t b_k = 0, b_n = 0, b_lo = 0, b_hi = 0;
+    int64_t bs_n = 0, bs_lo = 0, bs_hi = 0;
+    int64_t c_row_lo_count = 1, c_row_lo = 0, c_row_hi = 0;
+    int64_t c_col_lo_count = 1, c_col_lo = 0, c_col_hi = 0;
+    int64_t c_lo = 0, c_hi = 0;
+};
+
+struct Level {
+    int64_t count, stride;
+};
+
+// The axes `ax` (in iteration order, outermost first) as at most `max_levels`
+// strided levels of one operand, outermost first.
+bool levels_of(const int64_t *dims, const int64_t *stride, const std::vector<int> &ax, size_t max_levels, std::vector<Level> &out)
+{
+    out.clear();
+    for (int a : ax) {
+        if (dims[a] == 1) continue;
+        if (!out.empty() && out.back().stride == stride[a] * dims[a]) {
+            out.back().count *= dims[a];
+            out.back().stride = stride[a];
+        } else {
+            out.push_back({dims[a], stride[a]});
+        }
+    }
+    return out.size() <= max_levels;
+}
+
+bool map_gemm(const DevLaunch &L, GemmMap &g)
+{
+    if (L.n_in != 2) return false;
+    const DevOperand &A = L.in[0], &B = L.in[1];
+    std::vector<int> ax_b, ax_m, ax_n, ax_k;
+    for (int a = 0; a < L.n_outer; ++a) {
+        if (L.dims[a] == 1) continue;
+        bool ina = A.stride[a] != 0, inb = B.stride[a] != 0;
+        if (ina && inb) ax_b.push_back(a);
+        else if (ina) ax_m.push_back(a);
+        else if (inb) ax_n.push_back(a);
+        else return false; // an output axis no operand carries
+    }
+    for (int c = 0; c < L.n_inner; ++c) {
+        int a = L.n_outer + c;
+        if (L.dims[a] == 1) continue;
+        if (A.stride[a] == 0 || B.stride[a] == 0) return false;
+        ax_k.push_back(a);
+    }
+    std::vector<Level> lv;
+    auto prod = [&](const std::vector<int> &ax) { int64_t p = 1; for (int a : ax) p *= L.dims[a]; return p; };
+    g.m = prod(ax_m); g.n = prod(ax_n); g.k = prod(ax_k); g.batch = prod(ax_b);
+    // K: one level in both operands
+    if (!levels_of(L.dims, A.stride, ax_k, 1, lv)) return false;
+    g.a_k = lv.empty() ? 1 : lv[0].stride;
+    if (!levels_of(L.dims, B.stride, ax_k, 1, lv)) return false;
+    g.b_k = lv.empty() ? 1 : lv[0].stride;
+    // M: one level in A, two in C
+    if (!levels_of(L.dims, A.stride, ax_m, 1, lv)) return false;
+    g.a_row = lv.empty() ? 0 : lv[0].stride;
+    if (!levels_of(L.dims, L.out.stride, ax_m, 2, lv)) return false;
+    if (lv.size() == 2) { g.c_row_hi = lv[0].stride; g.c_row_lo_count = lv[1].count; g.c_row_lo = lv[1].stride; }
+    else if (lv.size() == 1) { g.c_row_hi = 0; g.c_row_lo_count = lv[0].count; g.c_row_lo = lv[0].stride; }
+    // N: one level in B (and its scales), two in C
+    if (!levels_of(L.dims, B.stride, ax_n, 1, lv)) return false;
+    g.b_n = lv.empty() ? 0 : lv[0].stride;
+    if (B.dtype == PSK_I8) {
+        if (!levels_of(L.dims, B.sstride, ax_n, 1, lv)) return false;
+        g.bs_n = lv.empty() ? 0 : lv[0].stride;
+        for (int a : ax_k) if (B.sstride[a] != 0) return false;
+    }
+    if (!levels_of(L.dims, L.out.stride, ax_n, 2, lv)) return false;
+    if (lv.size() == 2) { g.c_col_hi = lv[0].stride; g.c_col_lo_count = lv[1].count; g.c_col_lo = lv[1].stride; }
+    else if (lv.size() == 1) { g.c_col_hi = 0; g.c_col_lo_count = lv[0].count; g.c_col_lo = lv[0].stride; }
+    // batch: two levels everywhere, split at the same place
+    std::vector<Level> la, lb, lc, ls;
+    if (!levels_of(L.dims, A.stride, ax_b, 2, la) || !levels_of(L.dims, B.stride, ax_b, 2, lb) || !levels_of(L.dims, L.out.stride, ax_b, 2, lc)) return false;
+    // choose the split: the lowest level count any operand needs
+    int64_t lo = g.batch;
+    for (auto *v : {&la, &lb, &lc}) if (v->size() == 2) lo = std::min(lo, (*v)[1].count);
+    auto split = [&](const std::vector<Level> &v, int64_t &s_lo, int64_t &s_hi) {
+        if (v.empty()) { s_lo = s_hi = 0; return true; }
+        if (v.size() == 1) { s_lo = v[0].stride; s_hi = v[0].stride * lo; return true; }
+        if (v[1].count != lo) return false;
+        s_lo = v[1].stride; s_hi = v[0].stride;
+        return true;
+    };
+    g.batch_lo = lo;
+    if (!split(la, g.a_lo, g.a_hi) || !split(lb, g.b_lo, g.b_hi) || !split(lc, g.c_lo, g.c_hi)) return false;
+    if (B.dtype == PSK_I8) {
+        if (!levels_of(L.dims, B.sstride, ax_b, 2, ls) || !split(ls, g.bs_lo, g.bs_hi)) return false;
+    }
+    return true;
+}
+
+// ---- tensor maps ------------------------------------------------------------
+bool make_map(psk_exec *e, CUtensorMap *map, const void *base, int f16, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t d3, uint64_t s1, uint64_t s2, uint64_t s3, uint32_t box0, uint32_t box1)
+{
+    // strides in elements on entry; the driver wants bytes, multiples of 16
+    cuuint64_t dims[4] = {d0, d1, d2, d3};
+    cuuint64_t strides[3] = {s1 * 2, s2 * 2, s3 * 2};
+    for (int i = 0; i < 3; ++i) {
+        if (dims[i + 1] == 1 && strides[i] == 0) strides[i] = (i == 0 ? d0 * 2 : strides[i - 1] * dims[i]);
+        if (strides[i] % 16 != 0 || strides[i] == 0) return false;
+    }
+    cuuint32_t box[4] = {box0, box1, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = e->encode(map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+int launch_tc(psk_exec *e, const psk_gemm &g, const void *a, const void *b, void *c, uint32_t *flag)
+{
+    if (!e->encode) return fail(e, PSK_E10001, "cuTensorMapEncodeTiled is not available from this driver");
+    const bool f16 = g.in_dtype == PSK_F16;
+    const int bn = g.n >= 256 || g.n % 128 != 0 ? 256 : 128;
+    const int64_t batch_hi = g.batch / g.batch_lo;
+    CUtensorMap ma, mb;
+    if (!make_map(e, &ma, a, f16, (uint64_t)g.k, (uint64_t)g.m, (uint64_t)g.batch_lo, (uint64_t)batch_hi, (uint64_t)g.a_row, (uint64_t)g.a_lo, (uint64_t)g.a_hi, tc::BK, tc::BM))
+        return fail(e, PSK_E7001, "tensor-core contraction: operand 0's strides do not make a tensor map");
+    bool okb = g.b_n_major
+        ? make_map(e, &mb, b, f16, (uint64_t)g.n, (uint64_t)g.k, (uint64_t)g.batch_lo, (uint64_t)batch_hi, (uint64_t)g.b_row, (uint64_t)g.b_lo, (uint64_t)g.b_hi, 64, tc::BK)
+        : make_map(e, &mb, b, f16, (uint64_t)g.k, (uint64_t)g.n, (uint64_t)g.batch_lo, (uint64_t)batch_hi, (uint64_t)g.b_row, (uint64_t)g.b_lo, (uint64_t)g.b_hi, tc::BK, (uint32_t)bn);
+    if (!okb) return fail(e, PSK_E7001, "tensor-core contraction: operand 1's strides do not make a tensor map");
+    tc::Params P;
+    P.m = g.m; P.n = g.n; P.k = g.k; P.batch = g.batch; P.batch_lo = g.batch_lo;
+    P.tiles_m = (g.m + tc::BM - 1) / tc::BM;
+    P.tiles_n = (g.n + bn - 1) / bn;
+    P.c_row_lo_count = g.c_row_lo_count; P.c_row_lo = g.c_row_lo; P.c_row_hi = g.c_row_hi;
+    P.c_col_lo_count = g.c_col_lo_count; P.c_col_hi = g.c_col_hi;
+    P.c_lo = g.c_lo; P.c_hi = g.c_hi;
+    P.c = c; P.out_dtype = g.out_dtype; P.in_f16 = f16; P.b_n_major = g.b_n_major; P.guarded = g.guarded;
+    const int64_t va = g.out_dtype == PSK_F32 ? 4 : 8; // elements in 16 bytes
+    P.vec_ok = aligned16(c) && g.c_row_lo % va == 0 && g.c_row_hi % va == 0 && g.c_col_hi % va == 0 && g.c_lo % va == 0 && g.c_hi % va == 0 && g.c_col_lo_count % 32 == 0 && g.out_dtype != PSK_E8M15;
+    P.scale = g.scale; P.scale_on = g.scale_on;
+    P.ovf = flag; P.status = e->status;
+    if (!e->tc_attr_set) {
+        CUDA_TRY(e, cudaFuncSetAttribute(tc::k_gemm_tc<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::Smem<256>::TOTAL));
+        CUDA_TRY(e, cudaFuncSetAttribute(tc::k_gemm_tc<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::Smem<128>::TOTAL));
+        e->tc_attr_set = true;
+    }
+    const int64_t tiles = P.tiles_m * P.tiles_n * g.batch;
+    const int grid = (int)std::min<int64_t>(tiles, e->sms);
+    if (bn == 256) tc::k_gemm_tc<256><<<grid, tc::THREADS, tc::Smem<256>::TOTAL, e->stream>>>(ma, mb, P);
+    else tc::k_gemm_tc<128><<<grid, tc::THREADS, tc::Smem<128>::TOTAL, e->stream>>>(ma, mb, P);
+    CUDA_TRY(e, cudaGetLastError());
+    e->kernels += 1;
+    return PSK_OK;
+}
+
+uint32_t *next_flag(psk_exec *e, const psk_launch *l)
+{
+    int slot = (int)(e->guarded_since % kFlagSlots);
+    e->flag_serial[slot] = e->launches;
+    if (e->guarded_since < kFlagSlots) { /* first use since the last check: still zero */ }
+    e->guarded_since += 1;
+    (void)l;
+    return e->flags + slot;
+}
+
+} // namespace
+
+// ===========================================================================
+extern "C" {
+
+psk_exec *psk_exec_create(int device)
+{
+    int count = 0;
+    cudaError_t err = cudaGetDeviceCount(&count);
+    if (err != cudaSuccess || device < 0 || device >= count) {
+        g_create_error = err != cudaSuccess ? std::string("no CUDA device: ") + cudaGetErrorString(err) : "no CUDA device of that number";
+        return nullptr;
+    }
+    cudaDeviceProp prop;
+    if (cudaSetDevice(device) != cudaSuccess || cudaGetDeviceProperties(&prop, device) != cudaSuccess) {
+        g_create_error = "cannot select the CUDA device";
+        return nullptr;
+    }
+    if (prop.major != 10) {
+        g_create_error = "this library's kernels are built for sm_100a only; the device is sm_" + std::to_string(prop.major) + std::to_string(prop.minor);
+        return nullptr;
+    }
+    psk_exec *e = new psk_exec;
+    e->device = device;
+    e->sms = prop.multiProcessorCount;
+    bool ok = cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) == cudaSuccess
+        && cudaMalloc(&e->flags, kFlagSlots * sizeof(uint32_t)) == cudaSuccess
+        && cudaMalloc(&e->status, sizeof(uint32_t)) == cudaSuccess
+        && cudaMemset(e->flags, 0, kFlagSlots * sizeof(uint32_t)) == cudaSuccess
+        && cudaMemset(e->status, 0, sizeof(uint32_t)) == cudaSuccess
+        && cudaEventCreate(&e->ev0) == cudaSuccess && cudaEventCreate(&e->ev1) == cudaSuccess;
+    if (!ok) {
+        g_create_error = std::string("cannot set the executor up: ") + cudaGetErrorString(cudaGetLastError());
+        delete e;
+        return nullptr;
+    }
+    e->flag_serial.assign(kFlagSlots, -1);
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &fn, 12000, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+        e->encode = (EncodeTiledFn)fn;
+    return e;
+}
+
+void psk_exec_destroy(psk_exec *e)
+{
+    if (!e) return;
+    cudaSetDevice(e->device);
+    cudaStreamSynchronize(e->stream);
+    for (auto &kv : e->sizes) cudaFree(kv.first);
+    cudaFree(e->flags);
+    cudaFree(e->status);
+    cudaEventDestroy(e->ev0);
+    cudaEventDestroy(e->ev1);
+    cudaStreamDestroy(e->stream);
+    delete e;
+}
+
+const char *psk_exec_name(const psk_exec *) { return "cuda"; }
+
+const char *psk_last_error(const psk_exec *e) { return e ? e->error.c_str() : g_create_error.c_str(); }
+
+void *psk_exec_alloc(psk_exec *e, size_t bytes)
+{
+    if (bytes == 0) bytes = 16;
+    bytes = (bytes + 255) & ~(size_t)255;
+    cudaSetDevice(e->device);
+    void *p = nullptr;
+    auto it = e->pool.find(bytes);
+    if (it != e->pool.end() && !it->second.empty()) {
+        p = it->second.back();
+        it->second.pop_back();
+    } else {
+        cudaError_t err = cudaMalloc(&p, bytes);
+        if (err != cudaSuccess) {
+            // give the pool back to the driver and try once more
+            for (auto &kv : e->pool) {
+                for (void *q : kv.second) { cudaFree(q); e->sizes.erase(q); }
+                kv.second.clear();
+            }
+            cudaGetLastError();
+            err = cudaMalloc(&p, bytes);
+            if (err != cudaSuccess) {
+                fail(e, PSK_E10001, std::string("cudaMalloc of ") + std::to_string(bytes) + " bytes: " + cudaGetErrorString(err));
+                cudaGetLastError();
+                return nullptr;
+            }
+        }
+        e->sizes[p] = bytes;
+    }
+    e->live += bytes;
+    e->peak = std::max(e->peak, e->live);
+    return p;
+}
+
+void psk_exec_free(psk_exec *e, void *p)
+{
+    if (!p) return;
+    auto it = e->sizes.find(p);
+    if (it == e->sizes.end()) return;
+    e->live -= it->second;
+    e->causal.erase(p);
+    // The stream is in order and every kernel of this executor runs on it, so
+    // a buffer handed out again is written only after its last reader ran.
+    e->pool[it->second].push_back(p);
+}
+
+int psk_exec_upload(psk_exec *e, void *dst, const void *src_host, size_t bytes)
+{
+    cudaSetDevice(e->device);
+    CUDA_TRY(e, cudaMemcpyAsync(dst, src_host, bytes, cudaMemcpyHostToDevice, e->stream));
+    CUDA_TRY(e, cudaStreamSynchronize(e->stream)); // the host buffer is the caller's again
+    return PSK_OK;
+}
+
+static int check_status(psk_exec *e)
+{
+    uint32_t st = 0;
+    CUDA_TRY(e, cudaMemcpyAsync(&st, e->status, sizeof st, cudaMemcpyDeviceToHost, e->stream));
+    CUDA_TRY(e, cudaStreamSynchronize(e->stream));
+    if (st) {
+        cudaMemsetAsync(e->status, 0, sizeof st, e->stream);
+        char buf[256];
+        if (st & 0x100u) snprintf(buf, sizeof buf, "a bounded wait ran out in the tensor-core contraction (role %u); its results are not valid", st & 0xffu);
+        else if (st & 2u) snprintf(buf, sizeof buf, "an index outside its bound reached a gather");
+        else snprintf(buf, sizeof buf, "sin or cos of an argument at or beyond 2^28*pi/2 is not supported by this executor");
+        return fail(e, (st & 0x100u) ? PSK_E10001 : PSK_E7001, buf);
+    }
+    return PSK_OK;
+}
+
+int64_t psk_exec_overflow(psk_exec *e)
+{
+    if (e->guarded_since == 0) return 0;
+    cudaSetDevice(e->device);
+    std::vector<uint32_t> host(kFlagSlots);
+    if (cudaMemcpyAsync(host.data(), e->flags, kFlagSlots * sizeof(uint32_t), cudaMemcpyDeviceToHost, e->stream) != cudaSuccess) return 0;
+    cudaStreamSynchronize(e->stream);
+    int64_t first = -1;
+    int64_t used = std::min<int64_t>(e->guarded_since, kFlagSlots);
+    for (int64_t s = 0; s < used; ++s)
+        if (host[s] && (first < 0 || e->flag_serial[s] < first)) first = e->flag_serial[s];
+    cudaMemsetAsync(e->flags, 0, kFlagSlots * sizeof(uint32_t), e->stream);
+    e->guarded_since = 0;
+    return first < 0 ? 0 : first + 1;
+}
+
+int psk_exec_sync(psk_exec *e)
+{
+    cudaSetDevice(e->device);
+    CUDA_TRY(e, cudaStreamSynchronize(e->stream));
+    int st = check_status(e);
+    if (st != PSK_OK) return st;
+    int64_t o = psk_exec_overflow(e);
+    if (o) return fail(e, PSK_E7007, "launch " + std::to_string(o - 1) + ": a store rounded a finite value to an infinity");
+    return PSK_OK;
+}
+
+int psk_exec_download(psk_exec *e, void *dst_host, const void *src, size_t bytes)
+{
+    cudaSetDevice(e->device);
+    CUDA_TRY(e, cudaMemcpyAsync(dst_host, src, bytes, cudaMemcpyDeviceToHost, e->stream));
+    CUDA_TRY(e, cudaStreamSynchronize(e->stream));
+    return PSK_OK;
+}
+
+void psk_exec_memory(const psk_exec *e, size_t *live, size_t *peak)
+{
+    if (live) *live = e->live;
+    if (peak) *peak = e->peak;
+}
+
+void psk_exec_counts(const psk_exec *e, int64_t *launches, int64_t *kernels)
+{
+    if (launches) *launches = e->launches;
+    if (kernels) *kernels = e->kernels;
+}
+
+void psk_exec_set_profiling(psk_exec *e, int on) { e->profiling = on != 0; }
+
+double psk_exec_last_ms(psk_exec *e)
+{
+    if (!e->profiling) return -1.0;
+    if (cudaEventSynchronize(e->ev1) != cudaSuccess) return -1.0;
+    float ms = 0;
+    if (cudaEventElapsedTime(&ms, e->ev0, e->ev1) != cudaSuccess) return -1.0;
+    return ms;
+}
+
+void *psk_exec_stream(psk_exec *e) { return (void *)e->stream; }
+
+int psk_exec_gemm(psk_exec *e, const psk_gemm *g, const void *a, const void *b, void *c)
+{
+    cudaSetDevice(e->device);
+    if (g->in_dtype != PSK_BF16 && g->in_dtype != PSK_F16) return fail(e, PSK_E7005, "tensor-core contraction: operands are bf16 or f16");
+    if (!aligned16(a) || !aligned16(b)) return fail(e, PSK_E7001, "tensor-core contraction: operands must be 16-byte aligned");
+    uint32_t *flag = e->flags;
+    if (g->guarded) {
+        psk_launch dummy;
+        flag = next_flag(e, &dummy);
+    }
+    if (e->profiling) cudaEventRecord(e->ev0, e->stream);
+    int r = launch_tc(e, *g, a, b, c, flag);
+    if (e->profiling) cudaEventRecord(e->ev1, e->stream);
+    e->launches += 1;
+    return r;
+}
+
+int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
+{
+    cudaSetDevice(e->device);
+    if (l->n_inputs < 0 || l->n_inputs > PSK_MAX_INPUTS || l->n_outer < 0 || l->n_outer > PSK_MAX_RANK || l->n_inner < 0 || l->n_inner > PSK_MAX_INNER)
+        return fail(e, PSK_E7001, std::string(l->name ? l->name : "?") + ": a launch of too many inputs or axes");
+    if (l->dtype == PSK_F64)
+        return fail(e, PSK_E7005, std::string(l->name ? l->name : "?") + ": this executor computes in f32; a site realised f64 is not runnable by it");
+    const int naxes = l->n_outer + l->n_inner;
+    DevLaunch L;
+    memset(&L, 0, sizeof L);
+    L.n_in = l->n_inputs; L.n_outer = l->n_outer; L.n_inner = l->n_inner; L.kdtype = l->dtype;
+    L.n_steps = l->n_steps; L.kind = l->kind; L.masked = l->masked; L.guarded = l->guarded && (l->out.dtype == PSK_F16 || l->out.dtype == PSK_E8M15 || l->dtype == PSK_F16 || l->dtype == PSK_E8M15);
+    for (int a = 0; a < naxes; ++a) L.dims[a] = l->dims[a];
+    int scale_slot = l->n_inputs + 1;
+    for (int i = 0; i < l->n_inputs; ++i) {
+        const float *sc = nullptr;
+        if (l->in[i].dtype == PSK_I8) sc = (const float *)table[scale_slot++];
+        fill_operand(L.in[i], l->in[i], table[i], sc, naxes);
+    }
+    fill_operand(L.out, l->out, table[l->n_inputs], nullptr, naxes);
+    memcpy(L.steps, l->steps, sizeof(psk_step) * (size_t)std::max(0, std::min(l->n_steps, PSK_MAX_STEPS)));
+    for (int i = 0; i < 4; ++i) L.iparam[i] = l->iparam[i];
+    L.fparam = (float)l->fparam[0];
+    L.status = e->status;
+    L.ovf = L.guarded ? next_flag(e, l) : e->flags;
+    if (l->op != PSK_OP_EMBED && l->op != PSK_OP_IOTA) coalesce_outer(L);
+    L.total = 1;
+    for (int a = 0; a < L.n_outer; ++a) L.total *= L.dims[a];
+    L.inner = 1;
+    for (int c = 0; c < L.n_inner; ++c) L.inner *= L.dims[L.n_outer + c];
+    const bool device_order = l->order == PSK_ORDER_DEVICE;
+    if (e->profiling) cudaEventRecord(e->ev0, e->stream);
+    int rc = PSK_OK;
+    if (L.total == 0) {
+        // an empty result: nothing to store
+    } else switch (l->op) {
+    case PSK_OP_FUSED: {
+        if (l->n_steps < 1 || l->n_steps > PSK_MAX_STEPS) { rc = fail(e, PSK_E7001, "fused: a group of no step or of too many"); break; }
+        bool vec = L.n_outer >= 1 && l->n_steps <= 8 && L.dims[L.n_outer - 1] % 8 == 0 && vec8_operand(L.out, L.dims, L.n_outer, true);
+        for (int i = 0; vec && i < L.n_in; ++i) vec = vec8_operand(L.in[i], L.dims, L.n_outer, false);
+        if (vec) k_fused_vec8<<<grid_for(e, L.total / 8, 256, 8), 256, 0, e->stream>>>(L);
+        else k_fused<<<grid_for(e, L.total, 256, 8), 256, 0, e->stream>>>(L);
+        e->kernels += 1;
+        break;
+    }
+    case PSK_OP_COPY: {
+        if (L.n_in != 1) { rc = fail(e, PSK_E7001, "copy: one input a launch"); break; }
+        bool vec = L.n_outer >= 1 && !L.in[0].is_index && L.dims[L.n_outer - 1] % 8 == 0 && L.in[0].stride[L.n_outer - 1] == 1 && vec8_operand(L.out, L.dims, L.n_outer, true) && vec8_operand(L.in[0], L.dims, L.n_outer, false)
+            && (L.in[0].dtype == PSK_BF16 || L.in[0].dtype == PSK_F32 || L.in[0].dtype == PSK_F16) ;
+        if (vec) k_copy_vec8<<<grid_for(e, L.total / 8, 256, 8), 256, 0, e->stream>>>(L);
+        else k_copy<<<grid_for(e, L.total, 256, 8), 256, 0, e->stream>>>(L);
+        e->kernels += 1;
+        break;
+    }
+    case PSK_OP_CONTRACT: {
+        GemmMap g;
+        bool mapped = map_gemm(L, g);
+        const DevOperand &A = L.in[0], &B = L.in[1];
+        bool tc_ok = mapped && device_order && e->encode && A.dtype == B.dtype && (A.dtype == PSK_BF16 || A.dtype == PSK_F16)
+            && (L.kdtype == A.dtype || L.kdtype == PSK_F32 || (L.kdtype == PSK_E8M15))
+            && g.a_k == 1 && (g.b_k == 1 || g.b_n == 1) && aligned16(A.p) && aligned16(B.p) && g.c_col_lo == 1 && g.m >= 1 && g.n >= 8 && g.k >= 8;
+        if (tc_ok) {
+            psk_gemm pg;
+            memset(&pg, 0, sizeof pg);
+            pg.in_dtype = A.dtype; pg.out_dtype = L.out.dtype; pg.b_n_major = g.b_k == 1 ? 0 : 1; pg.guarded = L.guarded;
+            pg.m = g.m; pg.n = g.n; pg.k = g.k; pg.batch = g.batch; pg.batch_lo = g.batch_lo;
+            pg.a_row = g.a_row; pg.a_lo = g.a_lo; pg.a_hi = g.a_hi;
+            pg.b_row = pg.b_n_major ? g.b_k : g.b_n; pg.b_lo = g.b_lo; pg.b_hi = g.b_hi;
+            pg.c_row_lo_count = g.c_row_lo_count; pg.c_row_lo = g.c_row_lo; pg.c_row_hi = g.c_row_hi;
+            pg.c_col_lo_count = g.c_col_lo_count; pg.c_col_hi = g.c_col_hi; pg.c_lo = g.c_lo; pg.c_hi = g.c_hi;
+            if (g.m == 1) pg.a_row = g.k; // a single row: any stride of 16 bytes will do
+            if (g.n == 1) pg.b_row = g.k;
+            std::string keep = e->error;
+            rc = launch_tc(e, pg, A.p, B.p, const_cast<void *>(L.out.p), L.ovf);
+            if (rc == PSK_E7001) { rc = PSK_OK; e->error = keep; tc_ok = false; } // strides no tensor map takes: the exact kernel
+        }
+        if (!tc_ok && rc == PSK_OK) {
+            if (mapped && g.k >= 1) {
+                DevGemmExact G;
+                memset(&G, 0, sizeof G);
+                G.a = A.p; G.b = B.p; G.c = const_cast<void *>(L.out.p);
+                G.a_dtype = A.dtype; G.b_dtype = B.dtype; G.c_dtype = L.out.dtype; G.kdtype = L.kdtype;
+                G.m = g.m; G.n = g.n; G.k = g.k;
+                G.a_i = g.a_row; G.a_k = g.a_k; G.b_k = g.b_k; G.b_j = g.b_n;
+                G.batch_lo = g.batch_lo; G.a_lo = g.a_lo; G.a_hi = g.a_hi; G.b_lo = g.b_lo; G.b_hi = g.b_hi; G.c_lo = g.c_lo; G.c_hi = g.c_hi;
+                G.c_row_lo_count = g.c_row_lo_count; G.c_row_lo = g.c_row_lo; G.c_row_hi = g.c_row_hi;
+                G.c_col_lo_count = g.c_col_lo_count; G.c_col_lo = g.c_col_lo; G.c_col_hi = g.c_col_hi;
+                G.b_scales = B.scales; G.b_sj = g.bs_n; G.b_slo = g.bs_lo; G.b_shi = g.bs_hi;
+                G.ovf = L.ovf; G.guarded = L.guarded;
+                dim3 grid((unsigned)((g.n + 63) / 64), (unsigned)((g.m + 63) / 64), (unsigned)g.batch);
+                if (grid.y > 65535 || grid.z > 65535) k_contract_generic<<<grid_for(e, L.total, 256, 8), 256, 0, e->stream>>>(L);
+                else k_gemm_exact<<<grid, 256, 0, e->stream>>>(G);
+            } else {
+                k_contract_generic<<<grid_for(e, L.total, 256, 8), 256, 0, e->stream>>>(L);
+            }
+            e->kernels += 1;
+        }
+        break;
+    }
+    case PSK_OP_REDUCE: {
+        if (device_order && L.n_outer == 0) k_reduce_all_tree<<<1, 1024, 0, e->stream>>>(L);
+        else if (device_order && L.n_inner == 1 && L.in[0].stride[L.n_outer] == 1 && L.inner >= 64 && (L.inner % 8 != 0 || vec8_operand(L.in[0], L.dims, L.n_outer + 1, false) ))
+            k_reduce_rows_tree<<<grid_for(e, L.total * 32, 256, 8), 256, 0, e->stream>>>(L);
+        else k_reduce_seq<<<grid_for(e, L.total, 128, 16), 128, 0, e->stream>>>(L);
+        e->kernels += 1;
+        break;
+    }
+    case PSK_OP_SOFTMAX: {
+        if (L.n_inner != 1) { rc = fail(e, PSK_E7001, "softmax: one axis"); break; }
+        if (L.masked) {
+            auto it = e->causal.find(table[1]);
+            const int64_t n = L.inner;
+            bool causal = it != e->causal.end() && it->second == n && l->in[1].offset == 0 && L.in[1].stride[L.n_outer] == 1;
+            for (int a = 0; causal && a < L.n_outer; ++a) causal = L.in[1].stride[a] % n == 0 && L.in[1].stride[a] / n <= 1;
+            L.iparam[0] = causal ? 1 : 0;
+            L.iparam[1] = n;
+        }
+        const int64_t n = L.inner;
+        bool rows = device_order && L.in[0].stride[L.n_outer] == 1 && L.out.stride[L.n_outer] == 1 && n % 8 == 0 && n <= 4096
+            && vec8_operand(L.in[0], L.dims, L.n_outer + 1, false) && vec8_operand(L.out, L.dims, L.n_outer + 1, true)
+            && (!L.masked || L.iparam[0] == 1 || L.in[1].stride[L.n_outer] == 1);
+        if (rows) {
+            int g = grid_for(e, L.total * 32, 128, 16);
+            if (n <= 1024) k_softmax_rows_tree<32><<<g, 128, 0, e->stream>>>(L);
+            else if (n <= 2048) k_softmax_rows_tree<64><<<g, 128, 0, e->stream>>>(L);
+            else k_softmax_rows_tree<128><<<g, 128, 0, e->stream>>>(L);
+        } else {
+            k_softmax_seq<<<grid_for(e, L.total, 128, 16), 128, 0, e->stream>>>(L);
+        }
+        e->kernels += 1;
+        break;
+    }
+    case PSK_OP_XENT: {
+        if (L.n_inner != 1 || L.n_in != 2) { rc = fail(e, PSK_E7001, "cross_entropy: logits and labels"); break; }
+        bool vec_ok = L.in[0].stride[L.n_outer] != 1 || L.inner % 8 != 0 || vec8_operand(L.in[0], L.dims, L.n_outer + 1, false);
+        if (device_order && L.inner >= 256 && vec_ok) k_xent_rows_tree<<<(int)std::min<int64_t>(L.total, (int64_t)e->sms * 8), 256, 0, e->stream>>>(L);
+        else k_xent_seq<<<grid_for(e, L.total, 128, 16), 128, 0, e->stream>>>(L);
+        e->kernels += 1;
+        break;
+    }
+    case PSK_OP_ARGMAX:
+        k_argmax<<<grid_for(e, L.total, 128, 16), 128, 0, e->stream>>>(L);
+        e->kernels += 1;
+        break;
+    case PSK_OP_EMBED: {
+        const int last = L.n_outer - 1;
+        int64_t work = L.total / (L.dims[last] % 8 == 0 ? 8 : 1);
+        k_embed<<<grid_for(e, work, 256, 8), 256, 0, e->stream>>>(L);
+        e->kernels += 1;
+        break;
+    }
+    case PSK_OP_IOTA:
+        k_iota<<<grid_for(e, L.total, 256, 8), 256, 0, e->stream>>>(L);
+        e->kernels += 1;
+        if (l->kind == PSK_IOTA_CAUSAL && l->out.offset == 0) e->causal[table[l->n_inputs]] = l->dims[1];
+        break;
+    case PSK_OP_CONVERT: {
+        int64_t n = L.total;
+        k_convert<<<grid_for(e, n, 256, 8), 256, 0, e->stream>>>(L.in[0].p, L.in[0].dtype, const_cast<void *>(L.out.p), L.out.dtype, n, L.guarded, L.ovf);
+        e->kernels += 1;
+        break;
+    }
+    default:
+        rc = fail(e, PSK_E7001, std::string(l->name ? l->name : "?") + ": no such operation");
+    }
+    if (rc == PSK_OK) {
+        cudaError_t err = cudaGetLastError();
+        if (err != cudaSuccess) rc = fail(e, PSK_E10001, std::string(l->name ? l->name : "?") + ": " + cudaGetErrorString(err));
+    }
+    if (e->profiling) cudaEventRecord(e->ev1, e->stream);
+    e->launches += 1;
+    return rc;
+}
+
+// ---- helpers of the host program that are device work -----------------------
+int psk_exec_quantize(psk_exec *e, const void *w, int from, int8_t *q, float *s, int64_t outer, int64_t k, int64_t inner)
+{
+    cudaSetDevice(e->device);
+    k_quant_scales<<<grid_for(e, outer * inner, 256, 8), 256, 0, e->stream>>>(w, from, s, outer, k, inner);
+    k_quant_codes<<<grid_for(e, outer * k * inner, 256, 8), 256, 0, e->stream>>>(w, from, s, q, outer, k, inner);
+    CUDA_TRY(e, cudaGetLastError());
+    e->kernels += 2;
+    return PSK_OK;
+}
+
+int psk_exec_init_normal(psk_exec *e, void *dst, int to, int64_t n, uint64_t seed, double std)
+{
+    cudaSetDevice(e->device);
+    k_init_normal<<<grid_for(e, n, 256, 8), 256, 0, e->stream>>>(dst, to, n, seed, (float)std);
+    CUDA_TRY(e, cudaGetLastError());
+    e->kernels += 1;
+    return PSK_OK;
+}
+
+// ---- the executor as a table -------------------------------------------------
+static const char *vt_name(void *s) { return psk_exec_name((psk_exec *)s); }
+static void *vt_alloc(void *s, size_t b) { return psk_exec_alloc((psk_exec *)s, b); }
+static void vt_free(void *s, void *p) { psk_exec_free((psk_exec *)s, p); }
+static int vt_upload(void *s, void *d, const void *h, size_t b) { return psk_exec_upload((psk_exec *)s, d, h, b); }
+static int vt_download(void *s, void *h, const void *d, size_t b) { return psk_exec_download((psk_exec *)s, h, d, b); }
+static int vt_run(void *s, const psk_launch *l, void *const *t) { return psk_exec_run((psk_exec *)s, l, t); }
+static int vt_sync(void *s) { return psk_exec_sync((psk_exec *)s); }
+static int64_t vt_overflow(void *s) { return psk_exec_overflow((psk_exec *)s); }
+static const char *vt_error(void *s) { return psk_last_error((psk_exec *)s); }
+static int vt_quantize(void *s, const void *w, int from, int8_t *q, float *sc, int64_t outer, int64_t k, int64_t inner) { return psk_exec_quantize((psk_exec *)s, w, from, q, sc, outer, k, inner); }
+static int vt_init_normal(void *s, void *dst, int to, int64_t n, uint64_t seed, double std) { return psk_exec_init_normal((psk_exec *)s, dst, to, n, seed, std); }
+
+void psk_exec_as_vtable(psk_exec *e, psk_exec_vtable *out)
+{
+    out->self = e;
+    out->name = vt_name;
+    out->alloc = vt_alloc;
+    out->free = vt_free;
+    out->upload = vt_upload;
+    out->download = vt_download;
+    out->run = vt_run;
+    out->sync = vt_sync;
+    out->overflow = vt_overflow;
+    out->last_error = vt_error;
+    out->quantize = vt_quantize;
+    out->init_normal = vt_init_normal;
+}
+
+} // extern "C"

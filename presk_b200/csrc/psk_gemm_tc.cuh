@@ -1,0 +1,361 @@
+// The tensor-core contraction: C[b] = A[b]·B[b], bf16 or binary16 operands,
+// f32 sums in tensor memory, for sm_100a.
+//
+// This is what a contraction nest of the reference (presk-kernel/src/lower.rs
+// `emit_contraction_with`, :906-1139, and the generic `ein`, :586-636) becomes
+// under the declared order PSK_ORDER_DEVICE. The products of two bf16 or two
+// binary16 numbers are exact in f32; the sums are the tensor core's, grouped
+// by its tiles and not in index order, so a result agrees with the kernel
+// interpreter's within a tolerance and not bit for bit. The store rounds once
+// to the site's storage type with the bits of psk_formats.cuh, and tests the
+// overflow guard where the type is binary16 or e8m15.
+//
+// Shape of the kernel: one persistent CTA per SM, 192 threads.
+//   warp 0      one lane issues the TMA loads of A and B tiles (128 x 64 and
+//               BN x 64 elements, 128-byte swizzle) into a ring of STAGES
+//               shared-memory stages;
+//   warp 1      allocates tensor memory; one lane issues tcgen05.mma
+//               (cta_group::1, kind::f16, M = 128, N = BN, K = 16) four times
+//               per stage into one of two accumulators of BN columns;
+//   warps 2-5   the epilogue: tcgen05.ld of 32 columns a time, rounding, and
+//               128-bit global stores, of one accumulator while the other is
+//               being computed.
+// No multicast, no cluster: every CTA loads its own tiles, and reuse between
+// CTAs comes from the L2 through the order tiles are handed out in.
+//
+// Every wait on an mbarrier is bounded: when it runs out the kernel records
+// where in `status`, raises a flag in shared memory that ends every other
+// loop, frees its tensor memory and returns.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include "psk_formats.cuh"
+
+namespace psk {
+namespace tc {
+
+constexpr int BM = 128;
+constexpr int BK = 64; // elements: one 128-byte swizzle row of 16-bit elements
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;
+constexpr long long WAIT_CYCLES = 4000000000ll; // about two seconds
+
+struct Params {
+    int64_t m, n, k;
+    int64_t batch, batch_lo;
+    int64_t tiles_m, tiles_n;
+    int64_t c_row_lo_count, c_row_lo, c_row_hi;
+    int64_t c_col_lo_count, c_col_hi;
+    int64_t c_lo, c_hi;
+    void *c;
+    int out_dtype;
+    int in_f16; // 1: binary16 operands; 0: bf16
+    int b_n_major;
+    int guarded;
+    int vec_ok; // 128-bit stores are aligned
+    float scale;
+    int scale_on;
+    uint32_t *ovf;
+    uint32_t *status;
+};
+
+PSK_DEV uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+PSK_DEV void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+
+PSK_DEV void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+PSK_DEV void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// A bounded wait: false when it gave up or another role already had.
+PSK_DEV bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, uint32_t *status, uint32_t where)
+{
+    const long long t0 = clock64();
+    for (uint32_t it = 0;; ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        if (*abort_flag) return false;
+        if ((it & 255u) == 255u && clock64() - t0 > WAIT_CYCLES) {
+            *abort_flag = 1;
+            atomicOr(status, 0x100u | where);
+            return false;
+        }
+    }
+}
+
+PSK_DEV void tma_load_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2, int c3)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+
+// A shared-memory matrix descriptor for 128-byte-swizzled tiles: start
+// address, leading and stride byte offsets in units of 16 bytes, version 1
+// (sm_100), layout type 2 (128-byte swizzle).
+PSK_DEV uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3fffu);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// The instruction descriptor of kind::f16: f32 accumulator, both operands
+// bf16 or both binary16, A K-major, B K-major or N-major, M = 128, N = bn.
+PSK_DEV uint32_t instr_desc(int in_f16, int b_n_major, int bn)
+{
+    uint32_t d = 0;
+    d |= 1u << 4;                        // accumulator f32
+    d |= (in_f16 ? 0u : 1u) << 7;        // A: 0 binary16, 1 bf16
+    d |= (in_f16 ? 0u : 1u) << 10;       // B
+    d |= (b_n_major ? 1u : 0u) << 16;    // B major: 0 K, 1 MN
+    d |= (uint32_t)(bn >> 3) << 17;
+    d |= (uint32_t)(BM >> 4) << 24;
+    return d;
+}
+
+PSK_DEV void umma(uint32_t tmem_c, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_c), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+PSK_DEV void umma_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+PSK_DEV void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+template <int BN>
+struct Smem {
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGES = (BN == 256) ? 4 : 6;
+    static constexpr int TILE_BYTES = STAGES * (A_BYTES + B_BYTES);
+    static constexpr int BAR_BYTES = 256;
+    static constexpr int TOTAL = TILE_BYTES + BAR_BYTES + 1024; // slack to align the base to 1024
+};
+
+// One element of the accumulator on its way to memory: the optional fused
+// scaling as the reference's separate nest would compute it (round to the
+// site's type, then one IEEE division... the caller passes the reciprocal
+// only when that is exact), then the store's rounding.
+template <int BN>
+__global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ Params P)
+{
+    using S = Smem<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t *smem_a = smem;
+    uint8_t *smem_b = smem + S::STAGES * S::A_BYTES;
+    uint64_t *bars = (uint64_t *)(smem + S::TILE_BYTES);
+    // bars: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]
+    uint32_t *tmem_slot = (uint32_t *)(bars + 2 * S::STAGES + 4);
+    volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + S::STAGES);
+    const uint32_t tfull0 = smem_u32(bars + 2 * S::STAGES), tempty0 = smem_u32(bars + 2 * S::STAGES + 2);
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int s = 0; s < S::STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(tfull0 + 8 * s, 1);
+            mbar_init(tempty0 + 8 * s, 4); // one arrival per epilogue warp
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int64_t tiles_per_batch = P.tiles_m * P.tiles_n;
+    const int64_t total_tiles = tiles_per_batch * P.batch;
+    const int num_kb = (int)((P.k + BK - 1) / BK);
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (int64_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                const int64_t b = t / tiles_per_batch, r = t % tiles_per_batch;
+                const int m0 = (int)(r / P.tiles_n) * BM, n0 = (int)(r % P.tiles_n) * BN;
+                const int blo = (int)(b % P.batch_lo), bhi = (int)(b / P.batch_lo);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    ok = mbar_wait(empty0 + 8 * stage, phase ^ 1u, abort_flag, P.status, 1u);
+                    if (!ok) break;
+                    const uint32_t fb = full0 + 8 * stage;
+                    mbar_expect_tx(fb, S::A_BYTES + S::B_BYTES);
+                    tma_load_4d(smem_u32(smem_a + stage * S::A_BYTES), &map_a, fb, kb * BK, m0, blo, bhi);
+                    if (!P.b_n_major) {
+                        tma_load_4d(smem_u32(smem_b + stage * S::B_BYTES), &map_b, fb, kb * BK, n0, blo, bhi);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < BN / 64; ++c)
+                            tma_load_4d(smem_u32(smem_b + stage * S::B_BYTES + c * 8192), &map_b, fb, n0 + c * 64, kb * BK, blo, bhi);
+                    }
+                    if (++stage == S::STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = instr_desc(P.in_f16, P.b_n_major, BN);
+            uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+            bool ok = true;
+            for (int64_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                ok = mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1u, abort_flag, P.status, 2u);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t tacc = tmem_base + acc * BN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    ok = mbar_wait(full0 + 8 * stage, phase, abort_flag, P.status, 3u);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_addr = smem_u32(smem_a + stage * S::A_BYTES);
+                    const uint32_t b_addr = smem_u32(smem_b + stage * S::B_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        const uint64_t ad = smem_desc(a_addr + k * 32, 16, 1024);
+                        const uint64_t bd = P.b_n_major ? smem_desc(b_addr + k * 2048, 8192, 1024) : smem_desc(b_addr + k * 32, 16, 1024);
+                        umma(tacc, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(empty0 + 8 * stage); // the stage is free once these have read it
+                    if (++stage == S::STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                umma_commit(tfull0 + 8 * acc);
+                if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+            }
+        }
+    } else {
+        const int quad = warp & 3; // the tensor-memory lanes this warp may read: 32·quad ..
+        uint32_t acc = 0, acc_phase = 0, ovf = 0;
+        bool ok = true;
+        for (int64_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+            const int64_t b = t / tiles_per_batch, r = t % tiles_per_batch;
+            const int64_t m0 = (r / P.tiles_n) * BM, n0 = (r % P.tiles_n) * BN;
+            const int64_t blo = b % P.batch_lo, bhi = b / P.batch_lo;
+            ok = mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, P.status, 4u);
+            ok = __all_sync(0xffffffffu, ok); // the loads below want the whole warp
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int64_t row = m0 + quad * 32 + lane;
+            const int64_t row_off = blo * P.c_lo + bhi * P.c_hi + (row / P.c_row_lo_count) * P.c_row_hi + (row % P.c_row_lo_count) * P.c_row_lo;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN + c0, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                const int64_t col = n0 + c0;
+                if (row < P.m && col < P.n) {
+                    const int64_t off = row_off + (col / P.c_col_lo_count) * P.c_col_hi + (col % P.c_col_lo_count);
+                    float x[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) x[i] = __uint_as_float(v[i]);
+                    if (P.scale_on) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) x[i] = __fmul_rn(x[i], P.scale);
+                    }
+                    const bool full = col + 32 <= P.n && P.vec_ok;
+                    if (full && P.out_dtype == PSK_BF16) {
+                        uint4 *dst = reinterpret_cast<uint4 *>((uint16_t *)P.c + off);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            uint32_t u[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) u[i] = (uint32_t)f32_to_bf16(x[q * 8 + 2 * i]) | ((uint32_t)f32_to_bf16(x[q * 8 + 2 * i + 1]) << 16);
+                            dst[q] = make_uint4(u[0], u[1], u[2], u[3]);
+                        }
+                    } else if (full && P.out_dtype == PSK_F16) {
+                        uint4 *dst = reinterpret_cast<uint4 *>((uint16_t *)P.c + off);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            uint32_t u[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                ovf |= overflows(x[q * 8 + 2 * i], kF16Overflow) | overflows(x[q * 8 + 2 * i + 1], kF16Overflow);
+                                u[i] = (uint32_t)f32_to_f16(x[q * 8 + 2 * i]) | ((uint32_t)f32_to_f16(x[q * 8 + 2 * i + 1]) << 16);
+                            }
+                            dst[q] = make_uint4(u[0], u[1], u[2], u[3]);
+                        }
+                    } else if (full && P.out_dtype == PSK_F32) {
+                        float4 *dst = reinterpret_cast<float4 *>((float *)P.c + off);
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) dst[q] = make_float4(x[4 * q], x[4 * q + 1], x[4 * q + 2], x[4 * q + 3]);
+                    } else {
+                        for (int i = 0; i < 32; ++i)
+                            if (col + i < P.n) {
+                                const int64_t cc = col + i;
+                                const int64_t o = row_off + (cc / P.c_col_lo_count) * P.c_col_hi + (cc % P.c_col_lo_count);
+                                ovf |= store_real(P.c, P.out_dtype, o, x[i]);
+                            }
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
+            if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        }
+        if (P.guarded && ovf) atomicOr(P.ovf, 1u);
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
+    }
+}
+
+} // namespace tc
+} // namespace psk

@@ -1,0 +1,1349 @@
+// The host program: what the reference's `KernelBackend` does between
+// `Backend::call` and the executor (crates/presk-kernel/src/host.rs:436-457,
+// 742-868, 887-1039). It walks a model's lets in the reference's order, forms
+// the fusion groups of presk-core/src/fusion.rs:138-, looks each site's
+// storage type up in the realization (presk-rt/src/lib.rs:459-471), allocates
+// the output, and hands the executor one launch per group or tensor primitive.
+// It runs over any executor given as a table of functions, as
+// `KernelBackend::with_exec` does (host.rs:466).
+//
+// The reference walks PSK-Core, which its front end produces from a `.psk`
+// source; that front end is not part of this library, so the models this file
+// knows are written out here let by let, each function numbering its
+// parameters and then every let as presk-core's lowering does
+// (crates/presk-core/tests/snapshots/lower__core_minigpt.snap shows the rule),
+// so that a site is "<function>/%<let>" as in the reference's realization
+// files.
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <memory>
+#include <sstream>
+#include <string>
+#include <vector>
+
+#include "../../include/presk_cuda.h"
+
+namespace {
+
+std::string g_host_error;
+
+struct HostError {
+    int code;
+    std::string msg;
+};
+
+[[noreturn]] void raise(int code, const std::string &m) { throw HostError{code, m}; }
+
+size_t elem_bytes(int dtype)
+{
+    switch (dtype) {
+    case PSK_F64: case PSK_I64: return 8;
+    case PSK_F32: return 4;
+    case PSK_BF16: case PSK_F16: return 2;
+    case PSK_E8M15: return 3;
+    default: return 1;
+    }
+}
+
+int dtype_of_name(const std::string &s)
+{
+    if (s == "f64") return PSK_F64;
+    if (s == "f32") return PSK_F32;
+    if (s == "bf16") return PSK_BF16;
+    if (s == "f16") return PSK_F16;
+    if (s == "e8m15") return PSK_E8M15;
+    if (s == "e4m3fn" || s == "e4m3") return PSK_E4M3;
+    return -1;
+}
+
+// ---- a reader of the realization's JSON: objects, strings, numbers ----------
+struct Json {
+    enum Kind { Null, Str, Num, Obj } kind = Null;
+    std::string str;
+    double num = 0;
+    std::vector<std::pair<std::string, Json>> obj;
+    const Json *get(const std::string &k) const
+    {
+        for (auto &kv : obj)
+            if (kv.first == k) return &kv.second;
+        return nullptr;
+    }
+};
+
+struct JsonReader {
+    const char *p;
+    explicit JsonReader(const char *s) : p(s) {}
+    void ws() { while (*p == ' ' || *p == '\n' || *p == '\t' || *p == '\r') ++p; }
+    std::string string()
+    {
+        std::string s;
+        ++p;
+        while (*p && *p != '"') {
+            if (*p == '\\' && p[1]) ++p;
+            s.push_back(*p++);
+        }
+        if (*p != '"') raise(PSK_E7001, "realization: an unterminated string");
+        ++p;
+        return s;
+    }
+    Json value()
+    {
+        ws();
+        Json j;
+        if (*p == '{') {
+            j.kind = Json::Obj;
+            ++p;
+            ws();
+            if (*p == '}') { ++p; return j; }
+            for (;;) {
+                ws();
+                if (*p != '"') raise(PSK_E7001, "realization: a key was expected");
+                std::string k = string();
+                ws();
+                if (*p != ':') raise(PSK_E7001, "realization: `:` was expected after a key");
+                ++p;
+                j.obj.emplace_back(k, value());
+                ws();
+                if (*p == ',') { ++p; continue; }
+                if (*p == '}') { ++p; break; }
+                raise(PSK_E7001, "realization: `,` or `}` was expected");
+            }
+        } else if (*p == '"') {
+            j.kind = Json::Str;
+            j.str = string();
+        } else if (*p == '-' || (*p >= '0' && *p <= '9')) {
+            char *end;
+            j.kind = Json::Num;
+            j.num = strtod(p, &end);
+            p = end;
+        } else if (!strncmp(p, "null", 4)) {
+            p += 4;
+        } else if (!strncmp(p, "true", 4)) {
+            p += 4; j.kind = Json::Num; j.num = 1;
+        } else if (!strncmp(p, "false", 5)) {
+            p += 5; j.kind = Json::Num; j.num = 0;
+        } else {
+            raise(PSK_E7001, "realization: not JSON this reader takes");
+        }
+        return j;
+    }
+};
+
+struct QuantSpec {
+    int bits = 8;
+    int over = 0;
+};
+
+// presk-rt/src/lib.rs:374-434, the fields this executor reads.
+struct Realization {
+    int dflt = PSK_F32;
+    std::map<std::string, int> storage, functions, params;
+    std::map<std::string, QuantSpec> quant;
+    int order = PSK_ORDER_SEQUENTIAL;
+
+    static Realization parse(const char *text)
+    {
+        Realization r;
+        std::string t(text ? text : "f32");
+        size_t a = t.find_first_not_of(" \n\t\r");
+        if (a == std::string::npos) raise(PSK_E7001, "realization: empty");
+        if (t[a] != '{') {
+            size_t b = t.find_last_not_of(" \n\t\r");
+            int d = dtype_of_name(t.substr(a, b - a + 1));
+            if (d < 0) raise(PSK_E7001, "realization: no type `" + t + "`");
+            r.dflt = d;
+            return r;
+        }
+        JsonReader rd(t.c_str());
+        Json j = rd.value();
+        auto dt = [](const Json &v, const std::string &what) {
+            int d = v.kind == Json::Str ? dtype_of_name(v.str) : -1;
+            if (d < 0) raise(PSK_E7001, "realization: " + what + " names no type this executor stores");
+            return d;
+        };
+        if (auto *d = j.get("default")) r.dflt = dt(*d, "default");
+        for (auto key : {"storage", "functions", "params"}) {
+            if (auto *m = j.get(key)) {
+                auto &dst = std::string(key) == "storage" ? r.storage : std::string(key) == "functions" ? r.functions : r.params;
+                for (auto &kv : m->obj) dst[kv.first] = dt(kv.second, std::string(key) + "[" + kv.first + "]");
+            }
+        }
+        if (auto *q = j.get("quant"))
+            for (auto &kv : q->obj) {
+                QuantSpec s;
+                if (auto *b = kv.second.get("bits")) s.bits = (int)b->num;
+                if (auto *o = kv.second.get("over")) s.over = (int)o->num;
+                if (s.bits != 8) raise(PSK_E7005, "realization: quant[" + kv.first + "]: this executor stores int8 weights only");
+                r.quant[kv.first] = s;
+            }
+        if (auto *o = j.get("order")) {
+            const Json *k = o->get("kind");
+            std::string kind = k ? k->str : "sequential";
+            if (kind == "sequential" || kind == "blocked") r.order = PSK_ORDER_SEQUENTIAL;
+            else if (kind == "device") r.order = PSK_ORDER_DEVICE;
+            else raise(PSK_E7005, "realization: the order `" + kind + "` is not one this executor has kernels for (sequential, device)");
+        }
+        for (auto key : {"arith", "product", "accum", "scaled"})
+            if (auto *m = j.get(key))
+                if (!m->obj.empty()) raise(PSK_E7005, std::string("realization: `") + key + "` formats are the kernel interpreter's; this executor computes in f32 (E7005)");
+        return r;
+    }
+
+    // Realization::dtype_at: the site's own type, else its function's, else the default.
+    int dtype_at(const std::string &site) const
+    {
+        auto it = storage.find(site);
+        if (it != storage.end()) return it->second;
+        size_t slash = site.rfind('/');
+        if (slash != std::string::npos) {
+            auto f = functions.find(site.substr(0, slash));
+            if (f != functions.end()) return f->second;
+        }
+        return dflt;
+    }
+};
+
+// ---- values -------------------------------------------------------------------
+struct Storage {
+    const psk_exec_vtable *vt;
+    void *p;
+    size_t bytes;
+    Storage(const psk_exec_vtable *v, size_t b) : vt(v), p(v->alloc(v->self, b)), bytes(b)
+    {
+        if (!p) raise(PSK_E10001, std::string("the executor could not allocate ") + std::to_string(b) + " bytes: " + v->last_error(v->self));
+    }
+    ~Storage() { vt->free(vt->self, p); }
+    Storage(const Storage &) = delete;
+};
+
+struct Axis {
+    std::string name; // empty: unnamed
+    int64_t len;
+};
+
+typedef std::vector<Axis> Axes;
+
+// A tensor on the executor: row-major over its axes from an element offset.
+struct Tensor {
+    std::shared_ptr<Storage> st;
+    int64_t off = 0;
+    Axes axes;
+    int dtype = PSK_F32;
+    bool is_index = false;
+    int64_t bound = 0;
+    // integer weights: scales over the axes without `q_over`
+    std::shared_ptr<Storage> scales;
+    int64_t soff = 0;
+    int q_over = -1; // the first axis of the contracted one, and how many axes it has been split into
+    int q_span = 1;
+    bool borrowed = false;
+    void *raw = nullptr; // a caller's device buffer (psk_host_call_device)
+
+    int64_t numel() const { int64_t n = 1; for (auto &a : axes) n *= a.len; return n; }
+    void *ptr() const { return raw ? raw : st->p; }
+    std::vector<int64_t> strides() const
+    {
+        std::vector<int64_t> s(axes.size());
+        int64_t acc = 1;
+        for (int i = (int)axes.size() - 1; i >= 0; --i) { s[i] = acc; acc *= axes[i].len; }
+        return s;
+    }
+    std::vector<int64_t> scale_strides() const
+    {
+        std::vector<int64_t> s(axes.size(), 0);
+        if (q_over < 0) return s;
+        int64_t acc = 1;
+        for (int i = (int)axes.size() - 1; i >= 0; --i) {
+            if (i >= q_over && i < q_over + q_span) continue;
+            s[i] = acc;
+            acc *= axes[i].len;
+        }
+        return s;
+    }
+};
+
+std::string show(const Axes &a)
+{
+    std::string s = "[";
+    for (size_t i = 0; i < a.size(); ++i) {
+        if (i) s += ", ";
+        s += a[i].name.empty() ? std::to_string(a[i].len) : a[i].name + ": " + std::to_string(a[i].len);
+    }
+    return s + "]";
+}
+
+// lower.rs:37-56: trailing positions when the names agree, else by name.
+bool align(const Axes &src, const Axes &target, std::vector<int> &map)
+{
+    map.clear();
+    if (src.size() > target.size()) return false;
+    size_t off = target.size() - src.size();
+    bool positional = true;
+    for (size_t i = 0; i < src.size() && positional; ++i) {
+        const Axis &t = target[off + i];
+        positional = src[i].len == t.len && (src[i].name.empty() || t.name.empty() || src[i].name == t.name);
+    }
+    if (positional) {
+        for (size_t i = 0; i < src.size(); ++i) map.push_back((int)(off + i));
+        return true;
+    }
+    for (auto &a : src) {
+        if (a.name.empty()) return false;
+        int p = -1;
+        for (size_t k = 0; k < target.size(); ++k)
+            if (target[k].name == a.name && target[k].len == a.len) { p = (int)k; break; }
+        if (p < 0) return false;
+        map.push_back(p);
+    }
+    return true;
+}
+
+// lower.rs:59-70
+bool result_axes(const Axes &a, const Axes &b, Axes &out)
+{
+    const Axes &lng = a.size() >= b.size() ? a : b, &sht = a.size() >= b.size() ? b : a;
+    std::vector<int> map;
+    if (!align(sht, lng, map)) return false;
+    out = lng;
+    for (size_t i = 0; i < map.size(); ++i)
+        if (out[map[i]].name.empty()) out[map[i]].name = sht[i].name;
+    return true;
+}
+
+const char *prim_name(int p)
+{
+    static const char *n[] = {"add", "sub", "mul", "div", "max", "min", "neg", "exp", "log", "tanh", "sqrt", "sin", "cos", "abs", "gelu", "gelu_deriv", "relu", "heaviside", "sign", "sigmoid", "pow", "real"};
+    return n[p];
+}
+
+struct StepSpec {
+    int prim;
+    int a, b; // sources: >= 0 an input of the group, < 0 step -1-k; b unused when unary
+    int imm;
+    bool unary;
+};
+
+StepSpec U(int prim, int a, int imm = 0) { return {prim, a, 0, imm, true}; }
+StepSpec Bn(int prim, int a, int b) { return {prim, a, b, 0, false}; }
+inline int S(int k) { return -1 - k; } // the value of step k
+
+} // namespace
+
+// ===========================================================================
+struct psk_host {
+    const psk_exec_vtable *vt;
+    psk_exec_vtable vt_copy;
+    Realization rz;
+    std::string error;
+    std::string model;
+    std::map<std::string, int64_t> consts;
+    std::map<std::string, Tensor> params;
+    int64_t launches = 0;
+    bool logging = false;
+    std::string log;
+    Tensor last_result;
+
+    int64_t C(const std::string &k) const
+    {
+        auto it = consts.find(k);
+        if (it == consts.end()) raise(PSK_E7001, "the constant `" + k + "` was not given");
+        return it->second;
+    }
+    int64_t C(const std::string &k, int64_t dflt) const
+    {
+        auto it = consts.find(k);
+        return it == consts.end() ? dflt : it->second;
+    }
+
+    // ---- buffers --------------------------------------------------------------
+    Tensor fresh(const Axes &axes, int dtype, bool is_index = false, int64_t bound = 0)
+    {
+        Tensor t;
+        t.axes = axes;
+        t.dtype = is_index ? PSK_I64 : dtype;
+        t.is_index = is_index;
+        t.bound = bound;
+        t.st = std::make_shared<Storage>(vt, (size_t)std::max<int64_t>(1, t.numel()) * elem_bytes(t.dtype));
+        return t;
+    }
+
+    void check(int rc, const char *what)
+    {
+        if (rc != PSK_OK) raise(rc, std::string(what) + ": " + vt->last_error(vt->self));
+    }
+
+    // ---- one launch -------------------------------------------------------------
+    void set_operand(psk_operand &o, const Tensor &t, const std::vector<int64_t> &stride, const std::vector<int64_t> &sstride)
+    {
+        memset(&o, 0, sizeof o);
+        o.dtype = t.dtype;
+        o.is_index = t.is_index ? 1 : 0;
+        o.offset = t.off;
+        o.numel = t.numel();
+        for (size_t a = 0; a < stride.size(); ++a) o.stride[a] = stride[a];
+        for (size_t a = 0; a < sstride.size(); ++a) o.scale_stride[a] = sstride[a];
+    }
+
+    void run(psk_launch &l, const std::string &name, const std::vector<const Tensor *> &ins, const Tensor &out)
+    {
+        l.name = name.c_str();
+        l.order = rz.order;
+        l.guarded = 1;
+        l.n_inputs = (int)ins.size();
+        std::vector<void *> table;
+        for (auto *t : ins) table.push_back(t->ptr());
+        table.push_back(out.ptr());
+        for (auto *t : ins)
+            if (t->dtype == PSK_I8) table.push_back((uint8_t *)t->scales->p + t->soff * 4);
+        check(vt->run(vt->self, &l, table.data()), name.c_str());
+        launches += 1;
+        if (logging) { log += name; log += '\n'; }
+    }
+
+    // An operand's strides over an iteration space, given where each of its
+    // axes sits in it (`map[i]` = position of axis i).
+    void view(const Tensor &t, const std::vector<int> &map, int naxes, std::vector<int64_t> &stride, std::vector<int64_t> &sstride)
+    {
+        stride.assign(naxes, 0);
+        sstride.assign(naxes, 0);
+        auto st = t.strides(), ss = t.scale_strides();
+        for (size_t i = 0; i < map.size(); ++i) {
+            stride[map[i]] += st[i];
+            sstride[map[i]] += ss[i];
+        }
+    }
+
+    std::vector<int64_t> contiguous(const Axes &axes)
+    {
+        Tensor t;
+        t.axes = axes;
+        return t.strides();
+    }
+
+    void set_space(psk_launch &l, const Axes &outer, const std::vector<int64_t> &inner)
+    {
+        if (outer.size() > PSK_MAX_RANK || inner.size() > PSK_MAX_INNER) raise(PSK_E7001, "a launch of more axes than the executor's descriptor holds");
+        l.n_outer = (int)outer.size();
+        l.n_inner = (int)inner.size();
+        for (size_t a = 0; a < outer.size(); ++a) l.dims[a] = outer[a].len;
+        for (size_t c = 0; c < inner.size(); ++c) l.dims[outer.size() + c] = inner[c];
+    }
+
+    // ---- host scalars (host.rs:563-591: `self.scalar(x)` = Buf::of(dtype, [x])) --
+    std::map<std::pair<std::string, double>, Tensor> scalars;
+    Tensor scalar(const std::string &site, double x)
+    {
+        auto hit = scalars.find({site, x});
+        if (hit != scalars.end()) return hit->second;
+        int d = rz.dtype_at(site);
+        Tensor tmp = fresh({}, PSK_F64);
+        check(vt->upload(vt->self, tmp.ptr(), &x, 8), "scalar");
+        Tensor out = fresh({}, d);
+        convert_into(tmp, out);
+        scalars[{site, x}] = out;
+        return out;
+    }
+
+    void convert_into(const Tensor &src, const Tensor &dst)
+    {
+        psk_launch l;
+        memset(&l, 0, sizeof l);
+        l.op = PSK_OP_CONVERT;
+        l.dtype = dst.dtype;
+        Axes flat = {{"", src.numel()}};
+        set_space(l, flat, {});
+        set_operand(l.in[0], src, {1}, {0});
+        set_operand(l.out, dst, {1}, {0});
+        l.order = rz.order;
+        l.guarded = 1;
+        l.n_inputs = 1;
+        l.name = "convert";
+        void *table[2] = {src.ptr(), dst.ptr()};
+        check(vt->run(vt->self, &l, table), "convert");
+    }
+
+    // ---- elementwise (lower.rs:309-372) -------------------------------------------
+    Tensor fused(const std::string &site, const std::vector<StepSpec> &steps, const std::vector<const Tensor *> &ins, const std::string &name_override = "")
+    {
+        // the result's axes: the steps' broadcasts replayed (host.rs:1117-1137)
+        std::vector<Axes> shapes;
+        for (auto &s : steps) {
+            auto of = [&](int src) -> Axes { return src >= 0 ? ins[src]->axes : shapes[-1 - src]; };
+            if (s.unary) shapes.push_back(of(s.a));
+            else {
+                Axes r;
+                if (!result_axes(of(s.a), of(s.b), r)) raise(PSK_E7001, std::string("fused: `") + prim_name(s.prim) + "` cannot broadcast " + show(of(s.a)) + " with " + show(of(s.b)));
+                shapes.push_back(r);
+            }
+        }
+        Axes out_axes = shapes.back();
+        int d = rz.dtype_at(site);
+        Tensor out = fresh(out_axes, d);
+        psk_launch l;
+        memset(&l, 0, sizeof l);
+        l.op = PSK_OP_FUSED;
+        l.dtype = d;
+        set_space(l, out_axes, {});
+        for (size_t i = 0; i < ins.size(); ++i) {
+            std::vector<int> map;
+            if (!align(ins[i]->axes, out_axes, map)) raise(PSK_E7001, "fused: operand " + std::to_string(i) + " of shape " + show(ins[i]->axes) + " does not broadcast into " + show(out_axes));
+            std::vector<int64_t> st, ss;
+            view(*ins[i], map, (int)out_axes.size(), st, ss);
+            set_operand(l.in[i], *ins[i], st, ss);
+        }
+        set_operand(l.out, out, contiguous(out_axes), {});
+        l.n_steps = (int)steps.size();
+        for (size_t k = 0; k < steps.size(); ++k) {
+            l.steps[k].prim = steps[k].prim;
+            l.steps[k].nargs = steps[k].unary ? 1 : 2;
+            l.steps[k].src[0] = steps[k].a;
+            l.steps[k].src[1] = steps[k].unary ? 0 : steps[k].b;
+            l.steps[k].imm = steps[k].imm;
+        }
+        std::string name = !name_override.empty() ? name_override : steps.size() == 1 ? std::string(prim_name(steps[0].prim)) + (steps[0].prim == PSK_POW ? " " + std::to_string(steps[0].imm) : "") : "fused " + std::to_string(steps.size()) + " steps";
+        run(l, name, ins, out);
+        return out;
+    }
+
+    Tensor unary(const std::string &site, int prim, const Tensor &x, int imm = 0) { return fused(site, {U(prim, 0, imm)}, {&x}); }
+    Tensor binary(const std::string &site, int prim, const Tensor &a, const Tensor &b) { return fused(site, {Bn(prim, 0, 1)}, {&a, &b}); }
+
+    // ---- contractions ---------------------------------------------------------------
+    // lower.rs:586-636: the iteration space is the output's axes, then the summed
+    // ones in the order the operands first name them.
+    Tensor ein(const std::string &site, const std::vector<std::string> &output, const std::vector<std::vector<std::string>> &operands, const std::vector<const Tensor *> &ins, const std::string &name_override = "")
+    {
+        std::vector<std::pair<std::string, int64_t>> names;
+        for (size_t t = 0; t < ins.size(); ++t) {
+            if (operands[t].size() != ins[t]->axes.size()) raise(PSK_E7001, "ein: operand " + std::to_string(t) + " has " + std::to_string(ins[t]->axes.size()) + " axes and " + std::to_string(operands[t].size()) + " names");
+            for (size_t i = 0; i < operands[t].size(); ++i) {
+                bool found = false;
+                for (auto &n : names)
+                    if (n.first == operands[t][i]) {
+                        if (n.second != ins[t]->axes[i].len) raise(PSK_E7001, "ein: axis `" + n.first + "` has lengths " + std::to_string(n.second) + " and " + std::to_string(ins[t]->axes[i].len));
+                        found = true;
+                    }
+                if (!found) names.emplace_back(operands[t][i], ins[t]->axes[i].len);
+            }
+        }
+        Axes out_axes;
+        std::vector<std::string> all = output;
+        std::vector<int64_t> inner;
+        for (auto &o : output) {
+            int64_t len = -1;
+            for (auto &n : names) if (n.first == o) len = n.second;
+            if (len < 0) raise(PSK_E7001, "ein: output axis `" + o + "` appears in no operand");
+            out_axes.push_back({o, len});
+        }
+        for (auto &n : names) {
+            bool in_out = false;
+            for (auto &o : output) in_out |= o == n.first;
+            if (!in_out) { all.push_back(n.first); inner.push_back(n.second); }
+        }
+        int d = rz.dtype_at(site);
+        Tensor out = fresh(out_axes, d);
+        psk_launch l;
+        memset(&l, 0, sizeof l);
+        l.op = PSK_OP_CONTRACT;
+        l.dtype = d;
+        set_space(l, out_axes, inner);
+        for (size_t t = 0; t < ins.size(); ++t) {
+            std::vector<int> map;
+            for (auto &n : operands[t])
+                for (size_t k = 0; k < all.size(); ++k)
+                    if (all[k] == n) { map.push_back((int)k); break; }
+            std::vector<int64_t> st, ss;
+            view(*ins[t], map, (int)all.size(), st, ss);
+            set_operand(l.in[t], *ins[t], st, ss);
+        }
+        set_operand(l.out, out, contiguous(out_axes), {});
+        std::string name = name_override;
+        if (name.empty()) {
+            name = "ein[";
+            for (size_t i = 0; i < output.size(); ++i) name += (i ? ", " : "") + output[i];
+            name += "]";
+        }
+        run(l, name, ins, out);
+        return out;
+    }
+
+    // lower.rs:481-513: x[..., K] · w[K, rest...]
+    Tensor dot(const std::string &site, const Tensor &x, const Tensor &w)
+    {
+        if (x.axes.empty() || w.axes.empty()) raise(PSK_E7001, "dot: both operands need at least one axis");
+        if (x.axes.back().len != w.axes[0].len) raise(PSK_E7001, "dot: contracted axes differ (" + std::to_string(x.axes.back().len) + " vs " + std::to_string(w.axes[0].len) + ")");
+        // as an ein over fresh names: the output keeps x's leading axes and w's trailing ones
+        std::vector<std::string> xs, ws, os;
+        Axes out_axes;
+        for (size_t i = 0; i + 1 < x.axes.size(); ++i) { xs.push_back("x" + std::to_string(i)); os.push_back(xs.back()); out_axes.push_back(x.axes[i]); }
+        xs.push_back("k");
+        ws.push_back("k");
+        for (size_t i = 1; i < w.axes.size(); ++i) { ws.push_back("w" + std::to_string(i)); os.push_back(ws.back()); out_axes.push_back(w.axes[i]); }
+        Tensor out = ein(site, os, {xs, ws}, {&x, &w}, "dot");
+        out.axes = out_axes;
+        return out;
+    }
+
+    // ---- reductions (lower.rs:1221-1255) -----------------------------------------------
+    Tensor reduce_axis(const std::string &site, int kind, const std::string &axis, const Tensor &x)
+    {
+        int p = -1;
+        for (size_t i = 0; i < x.axes.size(); ++i) if (x.axes[i].name == axis) { p = (int)i; break; }
+        if (p < 0) raise(PSK_E7001, "no axis `" + axis + "` in " + show(x.axes));
+        Axes out_axes = x.axes;
+        int64_t n = out_axes[p].len;
+        out_axes.erase(out_axes.begin() + p);
+        int d = rz.dtype_at(site);
+        Tensor out = fresh(out_axes, d);
+        psk_launch l;
+        memset(&l, 0, sizeof l);
+        l.op = PSK_OP_REDUCE;
+        l.dtype = d;
+        l.kind = kind;
+        l.iparam[0] = n;
+        set_space(l, out_axes, {n});
+        std::vector<int> map;
+        for (int i = 0, o = 0; i < (int)x.axes.size(); ++i) map.push_back(i == p ? (int)out_axes.size() : o++);
+        std::vector<int64_t> st, ss;
+        view(x, map, (int)out_axes.size() + 1, st, ss);
+        set_operand(l.in[0], x, st, ss);
+        set_operand(l.out, out, contiguous(out_axes), {});
+        run(l, std::string(kind == PSK_REDUCE_MEAN ? "mean" : "sum") + " axis " + axis, {&x}, out);
+        return out;
+    }
+
+    Tensor reduce_all(const std::string &site, int kind, const Tensor &x)
+    {
+        int d = rz.dtype_at(site);
+        Tensor out = fresh({}, d);
+        psk_launch l;
+        memset(&l, 0, sizeof l);
+        l.op = PSK_OP_REDUCE;
+        l.dtype = d;
+        l.kind = kind;
+        l.iparam[0] = x.numel();
+        // every axis is summed, in row-major order: one summed axis of the whole length
+        set_space(l, {}, {x.numel()});
+        set_operand(l.in[0], x, {1}, {0});
+        set_operand(l.out, out, {}, {});
+        run(l, kind == PSK_REDUCE_MEAN ? "mean" : kind == PSK_REDUCE_SUMSQ ? "sum_squares" : "sum", {&x}, out);
+        return out;
+    }
+
+    // ---- softmax, cross-entropy (lower.rs:1274-1470) -----------------------------------
+    Tensor softmax(const std::string &site, const std::string &axis, const Tensor &x, const Tensor *mask)
+    {
+        int p = -1;
+        for (size_t i = 0; i < x.axes.size(); ++i) if (x.axes[i].name == axis) { p = (int)i; break; }
+        if (p < 0) raise(PSK_E7001, "no axis `" + axis + "` in " + show(x.axes));
+        Axes outer = x.axes;
+        int64_t n = outer[p].len;
+        outer.erase(outer.begin() + p);
+        int d = rz.dtype_at(site);
+        Tensor out = fresh(x.axes, d);
+        psk_launch l;
+        memset(&l, 0, sizeof l);
+        l.op = PSK_OP_SOFTMAX;
+        l.dtype = d;
+        l.masked = mask ? 1 : 0;
+        set_space(l, outer, {n});
+        std::vector<int> map;
+        for (int i = 0, o = 0; i < (int)x.axes.size(); ++i) map.push_back(i == p ? (int)outer.size() : o++);
+        std::vector<int64_t> st, ss;
+        view(x, map, (int)outer.size() + 1, st, ss);
+        set_operand(l.in[0], x, st, ss);
+        set_operand(l.out, out, st, {});
+        std::vector<const Tensor *> ins = {&x};
+        if (mask) {
+            std::vector<int> mm, m2;
+            if (!align(mask->axes, x.axes, mm)) raise(PSK_E7001, "softmax: the mask " + show(mask->axes) + " does not broadcast into " + show(x.axes));
+            for (int q : mm) m2.push_back(map[q]);
+            std::vector<int64_t> mst, mss;
+            view(*mask, m2, (int)outer.size() + 1, mst, mss);
+            set_operand(l.in[1], *mask, mst, mss);
+            ins.push_back(mask);
+        }
+        run(l, "softmax axis " + axis + (mask ? " where" : ""), ins, out);
+        return out;
+    }
+
+    Tensor cross_entropy(const std::string &site, const Tensor &logits, const Tensor &y)
+    {
+        Axes outer = y.axes;
+        int64_t v = logits.axes.back().len;
+        if (logits.axes.size() != y.axes.size() + 1) raise(PSK_E7001, "cross_entropy: " + show(logits.axes) + " against labels " + show(y.axes));
+        int d = rz.dtype_at(site);
+        Tensor out = fresh(outer, d);
+        psk_launch l;
+        memset(&l, 0, sizeof l);
+        l.op = PSK_OP_XENT;
+        l.dtype = d;
+        set_space(l, outer, {v});
+        std::vector<int> map;
+        for (int i = 0; i < (int)logits.axes.size(); ++i) map.push_back(i);
+        std::vector<int64_t> st, ss;
+        view(logits, map, (int)outer.size() + 1, st, ss);
+        set_operand(l.in[0], logits, st, ss);
+        std::vector<int> ym;
+        for (int i = 0; i < (int)y.axes.size(); ++i) ym.push_back(i);
+        view(y, ym, (int)outer.size() + 1, st, ss);
+        set_operand(l.in[1], y, st, ss);
+        set_operand(l.out, out, contiguous(outer), {});
+        run(l, "cross_entropy", {&logits, &y}, out);
+        return out;
+    }
+
+    // ---- indexing (lower.rs:1421-1437, 1554-1750) ------------------------------------------
+    Tensor embed(const std::string &site, const Tensor &table, const Tensor &ids)
+    {
+        if (table.axes.size() != 2) raise(PSK_E7001, "embed: the table must have rank 2");
+        Axes out_axes = ids.axes;
+        out_axes.push_back({"", table.axes[1].len});
+        int d = rz.dtype_at(site);
+        Tensor out = fresh(out_axes, d);
+        psk_launch l;
+        memset(&l, 0, sizeof l);
+        l.op = PSK_OP_EMBED;
+        l.dtype = d;
+        l.iparam[0] = table.axes[0].len;
+        set_space(l, out_axes, {});
+        std::vector<int64_t> ts(out_axes.size(), 0);
+        ts[0] = table.axes[1].len; // a row of the table
+        if (out_axes.size() > 1) ts[1] = 1; else raise(PSK_E7001, "embed: indices need an axis");
+        set_operand(l.in[0], table, ts, {});
+        std::vector<int> im;
+        for (int i = 0; i < (int)ids.axes.size(); ++i) im.push_back(i);
+        std::vector<int64_t> st, ss;
+        view(ids, im, (int)out_axes.size(), st, ss);
+        set_operand(l.in[1], ids, st, ss);
+        set_operand(l.out, out, contiguous(out_axes), {});
+        run(l, "embed", {&table, &ids}, out);
+        return out;
+    }
+
+    // A strided copy of `src` read through `stride`/`off` into `dst` at `dst_off`
+    // with `dst_stride`, over `space`.
+    void copy_part(const std::string &name, int d, const Axes &space, const Tensor &src, const std::vector<int64_t> &stride, int64_t extra_off, const Tensor &dst, const std::vector<int64_t> &dst_stride, int64_t dst_off, bool count)
+    {
+        psk_launch l;
+        memset(&l, 0, sizeof l);
+        l.op = PSK_OP_COPY;
+        l.dtype = d;
+        set_space(l, space, {});
+        set_operand(l.in[0], src, stride, {});
+        l.in[0].offset += extra_off;
+        set_operand(l.out, dst, dst_stride, {});
+        l.out.offset += dst_off;
+        int64_t before = launches;
+        std::string keep = log;
+        run(l, name, {&src}, dst);
+        if (!count) { launches = before; log = keep; }
+    }
+
+    Tensor slice(const std::string &site, const std::string &axis, int64_t lo, int64_t hi, const Tensor &x)
+    {
+        int p = -1;
+        for (size_t i = 0; i < x.axes.size(); ++i) if (x.axes[i].name == axis) { p = (int)i; break; }
+        if (p < 0) raise(PSK_E7001, "no axis `" + axis + "` in " + show(x.axes));
+        if (lo > hi || hi > x.axes[p].len) raise(PSK_E7001, "slice " + std::to_string(lo) + ".." + std::to_string(hi) + " outside the axis `" + axis + "`, of length " + std::to_string(x.axes[p].len));
+        Axes out_axes = x.axes;
+        out_axes[p].len = hi - lo;
+        int d = x.is_index ? PSK_I64 : rz.dtype_at(site);
+        Tensor out = fresh(out_axes, d, x.is_index, x.bound);
+        auto st = x.strides();
+        copy_part("slice " + axis + ": " + std::to_string(lo) + ".." + std::to_string(hi), d, out_axes, x, st, lo * st[p], out, contiguous(out_axes), 0, true);
+        return out;
+    }
+
+    Tensor concat(const std::string &site, const std::string &axis, const Tensor &x, const Tensor &y)
+    {
+        int p = -1;
+        for (size_t i = 0; i < x.axes.size(); ++i) if (x.axes[i].name == axis) { p = (int)i; break; }
+        bool same = p >= 0 && x.axes.size() == y.axes.size() && y.axes[p].name == axis;
+        for (size_t k = 0; same && k < x.axes.size(); ++k) same = (int)k == p || x.axes[k].len == y.axes[k].len;
+        if (!same) raise(PSK_E7001, "concat " + axis + ": " + show(x.axes) + " and " + show(y.axes));
+        Axes out_axes = x.axes;
+        out_axes[p].len += y.axes[p].len;
+        int d = rz.dtype_at(site);
+        Tensor out = fresh(out_axes, d);
+        auto os = contiguous(out_axes);
+        // one nest of two loops in the reference (lower.rs:1592); two kernels here, one launch
+        copy_part("concat " + axis, d, x.axes, x, x.strides(), 0, out, os, 0, true);
+        copy_part("concat " + axis, d, y.axes, y, y.strides(), 0, out, os, x.axes[p].len * os[p], false);
+        return out;
+    }
+
+    // out[lead.., hh, s, d] = in[lead.., s, hh·hd + d] (lower.rs:1614)
+    Tensor split_heads(const std::string &site, int64_t h, int64_t hd, const Tensor &x)
+    {
+        size_t r = x.axes.size();
+        if (r < 2 || x.axes[r - 1].len != h * hd) raise(PSK_E7001, "split_heads: expected a trailing axis of length " + std::to_string(h * hd));
+        Axes out_axes(x.axes.begin(), x.axes.end() - 2);
+        out_axes.push_back({"heads", h});
+        out_axes.push_back(x.axes[r - 2]);
+        out_axes.push_back({"hd", hd});
+        int d = rz.dtype_at(site);
+        Tensor out = fresh(out_axes, d);
+        auto xs = x.strides();
+        std::vector<int64_t> st(xs.begin(), xs.end() - 2);
+        st.push_back(hd);        // heads
+        st.push_back(xs[r - 2]); // seq
+        st.push_back(1);         // hd
+        copy_part("split_heads " + std::to_string(h) + "x" + std::to_string(hd), d, out_axes, x, st, 0, out, contiguous(out_axes), 0, true);
+        return out;
+    }
+
+    // out[lead.., s, hh·hd + d] = in[lead.., hh, s, d] (lower.rs:1639)
+    Tensor merge_heads(const std::string &site, int64_t h, int64_t hd, const Tensor &x)
+    {
+        size_t r = x.axes.size();
+        if (r < 3) raise(PSK_E7001, "merge_heads: expected [..., heads, seq, hd]");
+        Axes out_axes(x.axes.begin(), x.axes.end() - 3);
+        out_axes.push_back(x.axes[r - 2]);
+        out_axes.push_back({"model", h * hd});
+        int d = rz.dtype_at(site);
+        Tensor out = fresh(out_axes, d);
+        // iterate (lead.., s, hh, d): the output is contiguous over it
+        Axes space(x.axes.begin(), x.axes.end() - 3);
+        space.push_back(x.axes[r - 2]);
+        space.push_back({"", h});
+        space.push_back({"", hd});
+        auto xs = x.strides();
+        std::vector<int64_t> st(xs.begin(), xs.end() - 3);
+        st.push_back(xs[r - 2]);
+        st.push_back(xs[r - 3]);
+        st.push_back(1);
+        copy_part("merge_heads " + std::to_string(h) + "x" + std::to_string(hd), d, space, x, st, 0, out, contiguous(space), 0, true);
+        return out;
+    }
+
+    Tensor iota(int kind, const std::string &name, const Axes &out_axes, bool is_index, int64_t bound, int d)
+    {
+        Tensor out = fresh(out_axes, d, is_index, bound);
+        psk_launch l;
+        memset(&l, 0, sizeof l);
+        l.op = PSK_OP_IOTA;
+        l.kind = kind;
+        l.dtype = d;
+        set_space(l, out_axes, {});
+        set_operand(l.out, out, contiguous(out_axes), {});
+        run(l, name, {}, out);
+        return out;
+    }
+    Tensor positions(const std::string &site, const std::string &axis, int64_t n) { return iota(PSK_IOTA_POSITIONS, "positions " + axis, {{axis, n}}, true, n, rz.dtype_at(site)); }
+    Tensor causal_mask(const std::string &site, const std::string &axis, int64_t n) { return iota(PSK_IOTA_CAUSAL, "causal_mask " + axis, {{axis, n}, {axis + "2", n}}, true, 2, rz.dtype_at(site)); }
+
+    // ---- retags: split and merge of an axis are the host's (host.rs:1510-1544) ------------
+    Tensor split(const Tensor &x, const std::string &axis, const std::vector<Axis> &parts)
+    {
+        Tensor t = x;
+        for (size_t i = 0; i < t.axes.size(); ++i)
+            if (t.axes[i].name == axis) {
+                int64_t n = 1;
+                for (auto &p : parts) n *= p.len;
+                if (n != t.axes[i].len) raise(PSK_E7001, "split: the parts of `" + axis + "` do not multiply to its length");
+                if (t.q_over >= 0) {
+                    // the contracted axis read as several (BufKind::Quant's span, presk-kernel/src/ir.rs:20-30)
+                    if ((int)i < t.q_over) t.q_over += (int)parts.size() - 1;
+                    else if ((int)i < t.q_over + t.q_span) t.q_span += (int)parts.size() - 1;
+                }
+                t.axes.erase(t.axes.begin() + i);
+                t.axes.insert(t.axes.begin() + i, parts.begin(), parts.end());
+                return t;
+            }
+        raise(PSK_E7001, "split: no axis `" + axis + "` in " + show(x.axes));
+    }
+    Tensor merge(const Tensor &x, const std::string &a, const std::string &b)
+    {
+        Tensor t = x;
+        for (size_t i = 0; i + 1 < t.axes.size(); ++i)
+            if (t.axes[i].name == a && t.axes[i + 1].name == b) {
+                t.axes[i] = {"", t.axes[i].len * t.axes[i + 1].len};
+                t.axes.erase(t.axes.begin() + i + 1);
+                return t;
+            }
+        raise(PSK_E7001, "merge: `" + a + "`, `" + b + "` are not adjacent axes of " + show(x.axes));
+    }
+    Tensor rename_last(const Tensor &x, const std::string &name)
+    {
+        Tensor t = x;
+        t.axes.back().name = name;
+        return t;
+    }
+
+    // ---- parameters ---------------------------------------------------------------------------
+    const Tensor &param(const std::string &path) const
+    {
+        auto it = params.find(path);
+        if (it == params.end()) raise(PSK_E7001, "the parameter `" + path + "` was not given");
+        return it->second;
+    }
+    // Layer l of a stacked parameter: a view, nothing copied (host.rs:2118-2151).
+    Tensor layer(const Tensor &t, int64_t l) const
+    {
+        Tensor v = t;
+        int64_t chunk = t.numel() / t.axes[0].len;
+        v.off += l * chunk;
+        v.axes.erase(v.axes.begin());
+        if (t.q_over >= 0) {
+            int64_t klen = 1;
+            for (int i = t.q_over; i < t.q_over + t.q_span; ++i) klen *= t.axes[i].len;
+            int64_t schunk = chunk / klen;
+            v.soff += l * schunk;
+            v.q_over -= 1;
+        }
+        return v;
+    }
+
+    int param_dtype(const std::string &path, bool &quant, QuantSpec &qs) const
+    {
+        quant = false;
+        auto q = rz.quant.find(path);
+        if (q != rz.quant.end()) { quant = true; qs = q->second; return PSK_I8; }
+        auto p = rz.params.find(path);
+        if (p != rz.params.end()) return p->second;
+        return rz.dflt;
+    }
+
+    void store_param(const std::string &path, const Tensor &raw)
+    {
+        bool quant;
+        QuantSpec qs;
+        int d = param_dtype(path, quant, qs);
+        Tensor t;
+        if (quant) {
+            int rank = (int)raw.axes.size();
+            int over = qs.over < 0 ? rank + qs.over : qs.over;
+            if (over < 0 || over >= rank) raise(PSK_E7001, "quant[" + path + "]: no axis " + std::to_string(qs.over));
+            int64_t outer = 1, inner = 1, k = raw.axes[over].len;
+            for (int i = 0; i < over; ++i) outer *= raw.axes[i].len;
+            for (int i = over + 1; i < rank; ++i) inner *= raw.axes[i].len;
+            t = fresh(raw.axes, PSK_I8);
+            t.dtype = PSK_I8;
+            t.scales = std::make_shared<Storage>(vt, (size_t)(outer * inner) * 4);
+            t.q_over = over;
+            if (!vt->quantize) raise(PSK_E7005, "this executor does not quantise weights");
+            check(vt->quantize(vt->self, raw.ptr(), raw.dtype, (int8_t *)t.ptr(), (float *)t.scales->p, outer, k, inner), "quantize");
+        } else if (d == raw.dtype) {
+            t = raw;
+        } else {
+            t = fresh(raw.axes, d);
+            convert_into(raw, t);
+        }
+        params[path] = t;
+    }
+
+    // ===========================================================================
+    // The models. Each function below is one function of the source program.
+    // ===========================================================================
+
+    // examples/coverage/llama.psk:34-40. %0 θ, %1 x.
+    Tensor llama_rmsnorm(const Tensor &gamma, const Tensor &x)
+    {
+        const std::string f = "RMSNorm.apply";
+        Tensor x2 = binary(f + "/%2", PSK_MUL, x, x);
+        Tensor ms = reduce_axis(f + "/%3", PSK_REDUCE_MEAN, "model", x2);
+        Tensor eps = scalar(f + "/%5", 1e-5);
+        Tensor rt = fused(f + "/%7", {Bn(PSK_ADD, 0, 1), U(PSK_SQRT, S(0))}, {&ms, &eps});
+        return fused(f + "/%10", {Bn(PSK_DIV, 0, 1), Bn(PSK_MUL, S(0), 2)}, {&x, &rt, &gamma});
+    }
+
+    // llama.psk:55-59
+    Tensor llama_frequencies()
+    {
+        const std::string f = "frequencies";
+        int64_t hd = C("D") / C("H");
+        Tensor two = scalar(f + "/%1", 2.0);
+        Tensor neg = unary(f + "/%2", PSK_NEG, two);
+        Tensor pos = positions(f + "/%3", "rot", hd / 2);
+        Tensor rp = unary(f + "/%4", PSK_REAL, pos);
+        Tensor hdr = scalar(f + "/%7", (double)hd);
+        Tensor base = scalar(f + "/%10", 1e4);
+        Tensor lg = unary(f + "/%11", PSK_LOG, base);
+        return fused(f + "/%13", {Bn(PSK_MUL, 0, 1), Bn(PSK_DIV, S(0), 2), Bn(PSK_MUL, S(1), 3), U(PSK_EXP, S(2))}, {&neg, &rp, &hdr, &lg});
+    }
+
+    // llama.psk:61-62
+    Tensor llama_angles(int64_t T)
+    {
+        const std::string f = "angles";
+        Tensor pos = positions(f + "/%0", "seq", T);
+        Tensor rp = unary(f + "/%1", PSK_REAL, pos);
+        Tensor fr = llama_frequencies();
+        return ein(f + "/%3", {"seq", "rot"}, {{"seq"}, {"rot"}}, {&rp, &fr});
+    }
+
+    // llama.psk:66-72. %0 φ, %1 x.
+    Tensor llama_rope(const Tensor &phi, const Tensor &x)
+    {
+        const std::string f = "rope";
+        int64_t hd = x.axes.back().len;
+        Tensor p = split(x, "hd", {{"pair", 2}, {"rot", hd / 2}});
+        Tensor x0 = slice(f + "/%3", "pair", 0, 1, p);
+        Tensor x1 = slice(f + "/%4", "pair", 1, 2, p);
+        Tensor c = unary(f + "/%5", PSK_COS, phi);
+        Tensor s = unary(f + "/%6", PSK_SIN, phi);
+        Tensor a = fused(f + "/%9", {Bn(PSK_MUL, 0, 1), Bn(PSK_MUL, 2, 3), Bn(PSK_SUB, S(0), S(1))}, {&x0, &c, &x1, &s});
+        Tensor b = fused(f + "/%12", {Bn(PSK_MUL, 0, 1), Bn(PSK_MUL, 2, 3), Bn(PSK_ADD, S(0), S(1))}, {&x1, &c, &x0, &s});
+        Tensor cat = concat(f + "/%13", "pair", a, b);
+        Tensor m = merge(cat, "pair", "rot");
+        m.axes.back().name = "hd";
+        return m;
+    }
+
+    // llama.psk:86-110. %0 θ, %1 x, %2 mask, %3 φ.
+    Tensor llama_attention(int64_t l, const Tensor &x, const Tensor &mask, const Tensor &phi)
+    {
+        const std::string f = "Attention.apply";
+        const int64_t D = C("D"), H = C("H"), G = C("G", H), HD = D / H, P = H / G;
+        Tensor wq = layer(param("blocks.attn.wq"), l), wk = layer(param("blocks.attn.wk"), l), wv = layer(param("blocks.attn.wv"), l), wo = layer(param("blocks.attn.wo"), l);
+        wq.axes = {{"model", D}, {"qout", D}};
+        wk.axes = {{"model", D}, {"kvout", G * HD}};
+        wv.axes = {{"model", D}, {"kvout", G * HD}};
+        wo.axes = {{"headhd", D}, {"model", D}};
+        Tensor wq3 = split(split(wq, "qout", {{"groups", G}, {"rest", P * HD}}), "rest", {{"per", P}, {"hd", HD}});
+        Tensor qe = ein(f + "/%7", {"batch", "groups", "per", "seq", "hd"}, {{"batch", "seq", "model"}, {"model", "groups", "per", "hd"}}, {&x, &wq3});
+        Tensor q = llama_rope(phi, qe);
+        Tensor wk3 = split(wk, "kvout", {{"groups", G}, {"hd", HD}});
+        Tensor ke = ein(f + "/%11", {"batch", "groups", "seq", "hd"}, {{"batch", "seq", "model"}, {"model", "groups", "hd"}}, {&x, &wk3});
+        Tensor k = llama_rope(phi, ke);
+        Tensor vd = dot(f + "/%14", x, wv);
+        vd.axes.back().name = "kvout";
+        Tensor v = split(vd, "kvout", {{"groups", G}, {"hd", HD}});
+        Tensor se = ein(f + "/%16", {"batch", "groups", "per", "seq", "seq2"}, {{"batch", "groups", "per", "seq", "hd"}, {"batch", "groups", "seq2", "hd"}}, {&q, &k});
+        Tensor hdr = scalar(f + "/%18", (double)HD);
+        Tensor rt = unary(f + "/%19", PSK_SQRT, hdr);
+        Tensor s = binary(f + "/%20", PSK_DIV, se, rt);
+        Tensor a = softmax(f + "/%21", "seq2", s, &mask);
+        Tensor o = ein(f + "/%22", {"batch", "seq", "groups", "per", "hd"}, {{"batch", "groups", "per", "seq", "seq2"}, {"batch", "seq2", "groups", "hd"}}, {&a, &v});
+        Tensor w2 = split(split(wo, "headhd", {{"groups", G}, {"rest", P * HD}}), "rest", {{"per", P}, {"hd", HD}});
+        return ein(f + "/%26", {"batch", "seq", "model"}, {{"batch", "seq", "groups", "per", "hd"}, {"groups", "per", "hd", "model"}}, {&o, &w2});
+    }
+
+    // llama.psk:43,45-50. silu: %0 x, %1 sigmoid, %2 mul.
+    Tensor llama_swiglu(int64_t l, const Tensor &x)
+    {
+        const std::string f = "SwiGLU.apply";
+        Tensor wg = layer(param("blocks.ff.gate.w"), l), wu = layer(param("blocks.ff.up.w"), l), wd = layer(param("blocks.ff.down.w"), l);
+        Tensor g = dot("Dense.apply/%3", x, wg);
+        Tensor sg = fused("silu/%2", {U(PSK_SIGMOID, 0), Bn(PSK_MUL, 0, S(0))}, {&g});
+        Tensor u = dot("Dense.apply/%3", x, wu);
+        Tensor h = binary(f + "/%7", PSK_MUL, sg, u);
+        return dot("Dense.apply/%3", h, wd);
+    }
+
+    // llama.psk:112-119. %0 θ, %1 x, %2 mask, %3 φ.
+    Tensor llama_block(int64_t l, const Tensor &x, const Tensor &mask, const Tensor &phi)
+    {
+        const std::string f = "Block.apply";
+        Tensor n1 = llama_rmsnorm(layer(param("blocks.n1.γ"), l), x);
+        Tensor at = llama_attention(l, n1, mask, phi);
+        Tensor x1 = binary(f + "/%8", PSK_ADD, x, at);
+        Tensor n2 = llama_rmsnorm(layer(param("blocks.n2.γ"), l), x1);
+        Tensor ff = llama_swiglu(l, n2);
+        return binary(f + "/%13", PSK_ADD, x1, ff);
+    }
+
+    // llama.psk:121-134. %0 θ, %1 ids.
+    Tensor llama_apply(const Tensor &ids)
+    {
+        const std::string f = "Llama.apply";
+        const int64_t T = ids.axes[1].len, L = C("L");
+        Tensor mask = causal_mask(f + "/%2", "seq", T);
+        Tensor e = embed(f + "/%4", param("tok"), ids);
+        e.axes.back().name = "model";
+        Tensor phi = llama_angles(T);
+        Tensor x = e;
+        for (int64_t l = 0; l < L; ++l) x = llama_block(l, x, mask, phi);
+        Tensor h = llama_rmsnorm(param("norm.γ"), x);
+        Tensor logits = dot(f + "/%11", h, param("head"));
+        logits.axes.back().name = "vocab";
+        return logits;
+    }
+
+    // llama.psk:140-142. %0 θ, %1 batch, %2 x, %3 y.
+    Tensor llama_loss(const Tensor &ids, const Tensor &y)
+    {
+        Tensor logits = llama_apply(ids);
+        Tensor ce = cross_entropy("loss/%5", logits, y);
+        return reduce_all("loss/%6", PSK_REDUCE_MEAN, ce);
+    }
+
+    // examples/spec/layernorm/layernorm.psk; numbering of
+    // presk-core/tests/snapshots/lower__core_minigpt.snap. %0 θ, %1 x, %2 eps.
+    Tensor layernorm(const Tensor &gamma, const Tensor &beta, const Tensor &x, double eps_v)
+    {
+        const std::string f = "LayerNorm.apply";
+        Tensor mu = reduce_axis(f + "/%3", PSK_REDUCE_MEAN, "model", x);
+        Tensor d2 = fused(f + "/%5", {Bn(PSK_SUB, 0, 1), U(PSK_POW, S(0), 2)}, {&x, &mu});
+        Tensor var = reduce_axis(f + "/%6", PSK_REDUCE_MEAN, "model", d2);
+        Tensor eps = scalar(f + "/%8", eps_v);
+        Tensor sd = fused(f + "/%10", {Bn(PSK_ADD, 0, 1), U(PSK_SQRT, S(0))}, {&var, &eps});
+        return fused(f + "/%15", {Bn(PSK_SUB, 0, 1), Bn(PSK_DIV, S(0), 2), Bn(PSK_MUL, S(1), 3), Bn(PSK_ADD, S(2), 4)}, {&x, &mu, &sd, &gamma, &beta});
+    }
+
+    // The spec's RMSNorm: `pow 2` where Llama's writes `x * x`. %0 θ, %1 x, %2 eps.
+    Tensor rmsnorm_spec(const Tensor &gamma, const Tensor &x, double eps_v)
+    {
+        const std::string f = "RMSNorm.apply";
+        Tensor x2 = unary(f + "/%3", PSK_POW, x, 2);
+        Tensor ms = reduce_axis(f + "/%4", PSK_REDUCE_MEAN, "model", x2);
+        Tensor eps = scalar(f + "/%5", eps_v);
+        Tensor rt = fused(f + "/%7", {Bn(PSK_ADD, 0, 1), U(PSK_SQRT, S(0))}, {&ms, &eps});
+        return fused(f + "/%10", {Bn(PSK_DIV, 0, 1), Bn(PSK_MUL, S(0), 2)}, {&x, &rt, &gamma});
+    }
+
+    // Linear.apply of the snapshot: %2 w, %3 dot, %4 b, %5 add.
+    Tensor linear(const std::string &prefix, const Tensor &x)
+    {
+        Tensor y = dot("Linear.apply/%3", x, param(prefix + ".w"));
+        return binary("Linear.apply/%5", PSK_ADD, y, param(prefix + ".b"));
+    }
+
+    // Linear{784,256} · ReLU · Linear{256,10}: %0 θ, %1 x; %3 call, %4 relu, %6 call.
+    Tensor mlp_apply(const Tensor &x)
+    {
+        Tensor h = linear("l1", x);
+        Tensor r = unary("MLP.apply/%4", PSK_RELU, h);
+        return linear("l2", r);
+    }
+    Tensor mlp_loss(const Tensor &x, const Tensor &y)
+    {
+        Tensor logits = mlp_apply(x);
+        Tensor ce = cross_entropy("loss/%5", logits, y);
+        return reduce_all("loss/%6", PSK_REDUCE_MEAN, ce);
+    }
+
+    // x·w then a row LayerNorm: %0 θ, %1 x, %2 w; %3 dot; LayerNorm.apply on it.
+    Tensor contract_ln(const Tensor &x, const Tensor &w)
+    {
+        Tensor y = dot("contract_ln/%3", x, w);
+        y.axes.back().name = "model";
+        return layernorm(param("ln.γ"), param("ln.β"), y, 1e-5);
+    }
+
+    Tensor call(const std::string &entry, const std::vector<Tensor> &in)
+    {
+        auto need = [&](size_t n) { if (in.size() != n) raise(PSK_E7001, model + "." + entry + " takes " + std::to_string(n) + " inputs"); };
+        if (model == "llama") {
+            if (entry == "apply") { need(1); return llama_apply(in[0]); }
+            if (entry == "loss") { need(2); return llama_loss(in[0], in[1]); }
+        } else if (model == "mlp") {
+            if (entry == "apply") { need(1); return mlp_apply(in[0]); }
+            if (entry == "loss") { need(2); return mlp_loss(in[0], in[1]); }
+        } else if (model == "layernorm") {
+            need(1);
+            return layernorm(param("γ"), param("β"), in[0], 1e-5);
+        } else if (model == "rmsnorm") {
+            need(1);
+            return rmsnorm_spec(param("γ"), in[0], 1e-6);
+        } else if (model == "contract_ln") {
+            need(2);
+            return contract_ln(in[0], in[1]);
+        }
+        raise(PSK_E7001, "no entry `" + entry + "` of the model `" + model + "`");
+    }
+
+    // The axes an entry's input has, by position (the source's types).
+    Axes input_axes(const std::string &entry, int i, const psk_value &v)
+    {
+        std::vector<std::string> names;
+        if (model == "llama") names = {"batch", "seq"};
+        else if (model == "mlp") names = i == 0 ? std::vector<std::string>{"batch", "model"} : std::vector<std::string>{"batch"};
+        else if (model == "layernorm" || model == "rmsnorm") { names.assign(v.rank, ""); if (v.rank) names.back() = "model"; if (v.rank > 1) names[0] = "batch"; }
+        else if (model == "contract_ln") names = i == 0 ? std::vector<std::string>{"batch", "k"} : std::vector<std::string>{"k", "model"};
+        (void)entry;
+        Axes a;
+        for (int k = 0; k < v.rank; ++k) a.push_back({k < (int)names.size() ? names[k] : "", v.dims[k]});
+        return a;
+    }
+};
+
+// ===========================================================================
+extern "C" {
+
+size_t psk_abi_sizeof(int which)
+{
+    switch (which) {
+    case 0: return sizeof(psk_launch);
+    case 1: return sizeof(psk_operand);
+    case 2: return sizeof(psk_step);
+    case 3: return sizeof(psk_gemm);
+    case 4: return sizeof(psk_value);
+    case 5: return sizeof(psk_exec_vtable);
+    default: return 0;
+    }
+}
+
+const char *psk_host_error(const psk_host *h) { return h ? h->error.c_str() : g_host_error.c_str(); }
+
+psk_host *psk_host_create(const psk_exec_vtable *exec, const char *realization)
+{
+    if (!exec || !exec->run) { g_host_error = "no executor"; return nullptr; }
+    try {
+        psk_host *h = new psk_host;
+        h->vt_copy = *exec;
+        h->vt = &h->vt_copy;
+        h->rz = Realization::parse(realization);
+        return h;
+    } catch (const HostError &e) {
+        g_host_error = e.msg;
+        return nullptr;
+    }
+}
+
+void psk_host_destroy(psk_host *h) { delete h; }
+
+#define HOST_TRY(h, ...)                       \
+    try {                                      \
+        __VA_ARGS__;                           \
+    } catch (const HostError &e) {             \
+        (h)->error = e.msg;                    \
+        return e.code;                         \
+    }
+
+int psk_host_prepare(psk_host *h, const char *model, const char *consts)
+{
+    HOST_TRY(h, {
+        h->model = model ? model : "";
+        static const char *known[] = {"llama", "mlp", "layernorm", "rmsnorm", "contract_ln"};
+        bool ok = false;
+        for (auto k : known) ok |= h->model == k;
+        if (!ok) raise(PSK_E7001, "no model `" + h->model + "`");
+        h->consts.clear();
+        std::istringstream ss(consts ? consts : "");
+        std::string tok;
+        while (ss >> tok) {
+            size_t eq = tok.find('=');
+            if (eq == std::string::npos) raise(PSK_E7001, "a constant is NAME=N, not `" + tok + "`");
+            h->consts[tok.substr(0, eq)] = strtoll(tok.c_str() + eq + 1, nullptr, 10);
+        }
+        // Realization::check_params (presk-rt/src/lib.rs:688-703): a path that names no parameter is refused
+        if (h->model == "llama") {
+            static const char *paths[] = {"tok", "head", "norm.γ", "blocks.n1.γ", "blocks.n2.γ", "blocks.attn.wq", "blocks.attn.wk", "blocks.attn.wv", "blocks.attn.wo", "blocks.ff.gate.w", "blocks.ff.up.w", "blocks.ff.down.w"};
+            for (auto *m : {&h->rz.params})
+                for (auto &kv : *m) {
+                    bool found = false;
+                    for (auto p : paths) found |= kv.first == p;
+                    if (!found) raise(PSK_E7001, "the realization's `params` names `" + kv.first + "`, which is no parameter of Llama");
+                }
+            for (auto &kv : h->rz.quant) {
+                bool found = false;
+                for (auto p : paths) found |= kv.first == p;
+                if (!found) raise(PSK_E7001, "the realization's `quant` names `" + kv.first + "`, which is no parameter of Llama");
+            }
+        }
+    });
+    return PSK_OK;
+}
+
+int psk_host_set_param(psk_host *h, const char *path, const void *host, int32_t host_dtype, const int64_t *dims, int32_t rank)
+{
+    HOST_TRY(h, {
+        if (host_dtype != PSK_F32 && host_dtype != PSK_F64) raise(PSK_E7001, "a parameter is given as f32 or f64 reals");
+        Axes axes;
+        for (int i = 0; i < rank; ++i) axes.push_back({"", dims[i]});
+        Tensor raw = h->fresh(axes, host_dtype);
+        h->check(h->vt->upload(h->vt->self, raw.ptr(), host, (size_t)raw.numel() * elem_bytes(host_dtype)), "upload");
+        h->store_param(path, raw);
+    });
+    return PSK_OK;
+}
+
+int psk_host_init_param(psk_host *h, const char *path, uint64_t seed, double std, const int64_t *dims, int32_t rank)
+{
+    HOST_TRY(h, {
+        if (!h->vt->init_normal) raise(PSK_E7005, "this executor draws no parameters");
+        Axes axes;
+        for (int i = 0; i < rank; ++i) axes.push_back({"", dims[i]});
+        bool quant;
+        QuantSpec qs;
+        int d = h->param_dtype(path, quant, qs);
+        // drawn as f32, then stored as the realization says; a type narrower than f32 that is not
+        // quantised is drawn directly, which rounds the same f32 once
+        Tensor raw = h->fresh(axes, quant ? PSK_F32 : d);
+        h->check(h->vt->init_normal(h->vt->self, raw.ptr(), raw.dtype, raw.numel(), seed, std), "init");
+        h->store_param(path, raw);
+    });
+    return PSK_OK;
+}
+
+static Tensor upload_value(psk_host *h, const char *entry, int i, const psk_value &v)
+{
+    bool is_index = v.dtype == PSK_I64;
+    Axes axes = h->input_axes(entry, i, v);
+    Tensor t = h->fresh(axes, v.dtype, is_index, 0);
+    h->check(h->vt->upload(h->vt->self, t.ptr(), v.data, (size_t)t.numel() * elem_bytes(t.dtype)), "upload");
+    if (is_index || v.dtype == h->rz.dflt) return t;
+    // Backend::call realizes every real leaf at the default type (host.rs:654-666)
+    Tensor r = h->fresh(axes, h->rz.dflt);
+    h->convert_into(t, r);
+    return r;
+}
+
+int psk_host_call(psk_host *h, const char *entry, const psk_value *inputs, int32_t n_inputs, void *out_host, int32_t out_dtype, int64_t out_capacity, int64_t *out_numel)
+{
+    HOST_TRY(h, {
+        h->launches = 0;
+        h->log.clear();
+        std::vector<Tensor> in;
+        for (int i = 0; i < n_inputs; ++i) in.push_back(upload_value(h, entry, i, inputs[i]));
+        Tensor r = h->call(entry, in);
+        if (out_numel) *out_numel = r.numel();
+        if (r.numel() > out_capacity) raise(PSK_E7001, "the result has " + std::to_string(r.numel()) + " elements and the buffer holds " + std::to_string(out_capacity));
+        if (r.is_index) {
+            h->check(h->vt->download(h->vt->self, out_host, (uint8_t *)r.ptr() + r.off * 8, (size_t)r.numel() * 8), "download");
+        } else {
+            if (out_dtype != PSK_F32 && out_dtype != PSK_F64) raise(PSK_E7001, "a result is read as f32 or f64");
+            Tensor o = r;
+            if (r.dtype != out_dtype || r.off != 0) {
+                o = h->fresh(r.axes, out_dtype);
+                h->convert_into(r, o);
+            }
+            h->check(h->vt->download(h->vt->self, out_host, o.ptr(), (size_t)o.numel() * elem_bytes(out_dtype)), "download");
+        }
+        h->check(h->vt->sync(h->vt->self), entry);
+        h->last_result = Tensor();
+    });
+    return PSK_OK;
+}
+
+// Backend::call with inputs already on the executor: `inputs[i].data` is a
+// device pointer of this host's executor. The result stays on the executor
+// until the next call; `*out` points at it.
+int psk_host_call_device(psk_host *h, const char *entry, const psk_value *inputs, int32_t n_inputs, void **out, int32_t *out_dtype, int64_t *out_numel)
+{
+    HOST_TRY(h, {
+        h->launches = 0;
+        h->log.clear();
+        std::vector<Tensor> in;
+        for (int i = 0; i < n_inputs; ++i) {
+            Tensor t;
+            t.axes = h->input_axes(entry, i, inputs[i]);
+            t.dtype = inputs[i].dtype;
+            t.is_index = inputs[i].dtype == PSK_I64;
+            t.raw = const_cast<void *>(inputs[i].data);
+            t.borrowed = true;
+            if (!t.is_index && t.dtype != h->rz.dflt) {
+                Tensor r = h->fresh(t.axes, h->rz.dflt);
+                h->convert_into(t, r);
+                t = r;
+            }
+            in.push_back(t);
+        }
+        h->last_result = h->call(entry, in);
+        if (out) *out = (uint8_t *)h->last_result.ptr() + h->last_result.off * (int64_t)elem_bytes(h->last_result.dtype);
+        if (out_dtype) *out_dtype = h->last_result.dtype;
+        if (out_numel) *out_numel = h->last_result.numel();
+    });
+    return PSK_OK;
+}
+
+int64_t psk_host_launches(const psk_host *h) { return h->launches; }
+const char *psk_host_launch_log(const psk_host *h) { return h->log.c_str(); }
+void psk_host_set_logging(psk_host *h, int on) { h->logging = on != 0; }
+
+} // extern "C"

@@ -1,0 +1,900 @@
+// The generic kernels: one family per psk_op, every one a restatement for the
+// GPU of a lowering of presk-kernel/src/lower.rs under the arithmetic of
+// presk-kernel/src/exec.rs (`impl Elem for f32`): each operation rounded once
+// in f32, products rounded before they are added, loads widened exactly,
+// stores rounded once. Under PSK_ORDER_SEQUENTIAL every sum adds its terms in
+// index order from +0 and the results are the kernel interpreter's bits.
+// Under PSK_ORDER_DEVICE row sums are shuffle trees (a declared
+// reassociation); everything that is not a sum keeps its bits.
+#pragma once
+#include "psk_dev.cuh"
+
+namespace psk {
+
+// ---------------------------------------------------------------------------
+// elementary operations (lower.rs:184-226)
+// ---------------------------------------------------------------------------
+PSK_DEV float prim_unary(int prim, float x, int imm, uint32_t *status)
+{
+    switch (prim) {
+    case PSK_NEG: return -x;
+    case PSK_EXP: return lm_expf(x);
+    case PSK_LOG: return lm_logf(x);
+    case PSK_TANH: return lm_tanhf(x);
+    case PSK_SQRT: return __fsqrt_rn(x);
+    case PSK_SIN: { int b = 0; float r = lm_sinf(x, &b); if (b) atomicOr(status, 1u); return r; }
+    case PSK_COS: { int b = 0; float r = lm_cosf(x, &b); if (b) atomicOr(status, 1u); return r; }
+    case PSK_ABS: return fabsf(x);
+    case PSK_GELU: {
+        float phi = __fdiv_rn(__fadd_rn(1.0f, lm_erff(__fdiv_rn(x, 1.41421354f))), 2.0f);
+        return __fmul_rn(x, phi);
+    }
+    case PSK_GELU_DERIV: {
+        float phi = __fdiv_rn(__fadd_rn(1.0f, lm_erff(__fdiv_rn(x, 1.41421354f))), 2.0f);
+        float dens = __fdiv_rn(lm_expf(__fdiv_rn(-__fmul_rn(x, x), 2.0f)), 2.50662827f);
+        return __fadd_rn(phi, __fmul_rn(x, dens));
+    }
+    case PSK_RELU: return x < 0.0f ? 0.0f : x;
+    case PSK_HEAVISIDE: return x > 0.0f ? 1.0f : 0.0f;
+    case PSK_SIGN: return x < 0.0f ? -1.0f : (x > 0.0f ? 1.0f : 0.0f);
+    case PSK_SIGMOID: return __fdiv_rn(1.0f, __fadd_rn(1.0f, lm_expf(-x)));
+    case PSK_POW: {
+        if (imm == 0) return 1.0f;
+        float e = x;
+        for (int i = 1; i < imm; ++i) e = __fmul_rn(e, x);
+        return e;
+    }
+    default: return x; // PSK_REAL
+    }
+}
+
+PSK_DEV float prim_binary(int prim, float x, float y)
+{
+    switch (prim) {
+    case PSK_ADD: return __fadd_rn(x, y);
+    case PSK_SUB: return __fsub_rn(x, y);
+    case PSK_MUL: return __fmul_rn(x, y);
+    case PSK_DIV: return __fdiv_rn(x, y);
+    case PSK_MAX: return x > y ? x : y; // the second operand at a tie
+    default: return x < y ? x : y;      // PSK_MIN
+    }
+}
+
+// ---------------------------------------------------------------------------
+// PSK_OP_FUSED, generic: one thread per output element.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) k_fused(const __grid_constant__ DevLaunch L)
+{
+    uint32_t ovf = 0;
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t lin = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; lin < L.total; lin += step) {
+        int64_t off[PSK_MAX_INPUTS], soff[PSK_MAX_INPUTS], ooff = 0;
+        for (int i = 0; i < L.n_in; ++i) off[i] = soff[i] = 0;
+        int64_t r = lin;
+        for (int a = L.n_outer - 1; a >= 0; --a) {
+            int64_t d = L.dims[a], ix = r % d;
+            r /= d;
+            ooff += ix * L.out.stride[a];
+            for (int i = 0; i < L.n_in; ++i) {
+                off[i] += ix * L.in[i].stride[a];
+                soff[i] += ix * L.in[i].sstride[a];
+            }
+        }
+        float vals[PSK_MAX_STEPS];
+        for (int s = 0; s < L.n_steps; ++s) {
+            const psk_step st = L.steps[s];
+            float a[2];
+            for (int j = 0; j < st.nargs; ++j) {
+                int src = st.src[j];
+                a[j] = src >= 0 ? load_operand(L.in[src], off[src], soff[src], L.kdtype, &ovf) : vals[-1 - src];
+            }
+            vals[s] = st.nargs == 1 ? prim_unary(st.prim, a[0], st.imm, L.status) : prim_binary(st.prim, a[0], a[1]);
+        }
+        ovf |= store_real(const_cast<void *>(L.out.p), L.out.dtype, ooff, vals[L.n_steps - 1]);
+    }
+    if (L.guarded && ovf) atomicOr(L.ovf, 1u);
+}
+
+// Eight consecutive elements of the last axis in one 128-bit access.
+template <int V>
+PSK_DEV void load_vec(const DevOperand &o, int64_t off, int64_t soff, int last_stride, int64_t slast, int kdtype, float (&x)[V], uint32_t *ovf)
+{
+    if (last_stride == 0) {
+        float v = load_operand(o, off, soff, kdtype, ovf);
+#pragma unroll
+        for (int i = 0; i < V; ++i) x[i] = v;
+        return;
+    }
+    if (o.dtype == PSK_BF16 && V == 8) {
+        uint4 w = *reinterpret_cast<const uint4 *>((const uint16_t *)o.p + off);
+        uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            x[2 * i] = bits_f32(u[i] << 16);
+            x[2 * i + 1] = bits_f32(u[i] & 0xffff0000u);
+        }
+        if (kdtype != PSK_BF16) {
+#pragma unroll
+            for (int i = 0; i < V; ++i) x[i] = edge_round(x[i], kdtype, PSK_BF16, ovf);
+        }
+        return;
+    }
+    if (o.dtype == PSK_F32 && V == 8) {
+        const float4 *q = reinterpret_cast<const float4 *>((const float *)o.p + off);
+        float4 a = q[0], b = q[1];
+        x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
+        x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+        if (kdtype != PSK_F32) {
+#pragma unroll
+            for (int i = 0; i < V; ++i) x[i] = edge_round(x[i], kdtype, PSK_F32, ovf);
+        }
+        return;
+    }
+#pragma unroll
+    for (int i = 0; i < V; ++i) x[i] = load_operand(o, off + i, soff + i * slast, kdtype, ovf);
+}
+
+template <int V>
+PSK_DEV uint32_t store_vec(const DevOperand &o, int64_t off, const float (&x)[V])
+{
+    if (o.dtype == PSK_BF16 && V == 8) {
+        uint32_t u[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) u[i] = (uint32_t)f32_to_bf16(x[2 * i]) | ((uint32_t)f32_to_bf16(x[2 * i + 1]) << 16);
+        *reinterpret_cast<uint4 *>((uint16_t *)const_cast<void *>(o.p) + off) = make_uint4(u[0], u[1], u[2], u[3]);
+        return 0u;
+    }
+    if (o.dtype == PSK_F32 && V == 8) {
+        float4 *q = reinterpret_cast<float4 *>((float *)const_cast<void *>(o.p) + off);
+        q[0] = make_float4(x[0], x[1], x[2], x[3]);
+        q[1] = make_float4(x[4], x[5], x[6], x[7]);
+        return 0u;
+    }
+    uint32_t ovf = 0;
+#pragma unroll
+    for (int i = 0; i < V; ++i) ovf |= store_real(const_cast<void *>(o.p), o.dtype, off + i, x[i]);
+    return ovf;
+}
+
+// PSK_OP_FUSED, vectorised: the last axis is contiguous (stride 1) or
+// broadcast (stride 0) in every operand, a multiple of 8 long, and every
+// base and outer stride is a multiple of 8 elements; at most 8 steps.
+__global__ void __launch_bounds__(256) k_fused_vec8(const __grid_constant__ DevLaunch L)
+{
+    uint32_t ovf = 0;
+    const int last = L.n_outer - 1;
+    const int64_t nvec = L.total / 8, lastv = L.dims[last] / 8;
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t lin = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; lin < nvec; lin += step) {
+        int64_t off[PSK_MAX_INPUTS], soff[PSK_MAX_INPUTS], ooff;
+        int64_t r = lin / lastv, c = (lin % lastv) * 8;
+        ooff = c * L.out.stride[last];
+        for (int i = 0; i < L.n_in; ++i) {
+            off[i] = c * L.in[i].stride[last];
+            soff[i] = c * L.in[i].sstride[last];
+        }
+        for (int a = last - 1; a >= 0; --a) {
+            int64_t d = L.dims[a], ix = r % d;
+            r /= d;
+            ooff += ix * L.out.stride[a];
+            for (int i = 0; i < L.n_in; ++i) {
+                off[i] += ix * L.in[i].stride[a];
+                soff[i] += ix * L.in[i].sstride[a];
+            }
+        }
+        float vals[8][8];
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+            if (s < L.n_steps) {
+                const psk_step st = L.steps[s];
+                float a[2][8];
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    if (j < st.nargs) {
+                        int src = st.src[j];
+                        if (src >= 0) {
+                            load_vec<8>(L.in[src], off[src], soff[src], (int)L.in[src].stride[last], L.in[src].sstride[last], L.kdtype, a[j], &ovf);
+                        } else {
+#pragma unroll
+                            for (int t = 0; t < 8; ++t) {
+                                // a step reads an earlier one: s' < s <= 7
+                                float v = 0.0f;
+#pragma unroll
+                                for (int q = 0; q < 7; ++q)
+                                    if (q == -1 - src) v = vals[q][t];
+                                a[j][t] = v;
+                            }
+                        }
+                    }
+                }
+#pragma unroll
+                for (int t = 0; t < 8; ++t)
+                    vals[s][t] = st.nargs == 1 ? prim_unary(st.prim, a[0][t], st.imm, L.status) : prim_binary(st.prim, a[0][t], a[1][t]);
+            }
+        }
+        float res[8];
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+            float v = 0.0f;
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                if (q == L.n_steps - 1) v = vals[q][t];
+            res[t] = v;
+        }
+        ovf |= store_vec<8>(L.out, ooff, res);
+    }
+    if (L.guarded && ovf) atomicOr(L.ovf, 1u);
+}
+
+// ---------------------------------------------------------------------------
+// PSK_OP_CONTRACT, exact and generic: one thread per output element, the
+// terms added in the lexicographic order of the summed axes, acc = acc + x·w
+// with the product rounded first (lower.rs:465-474, 586-636).
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) k_contract_generic(const __grid_constant__ DevLaunch L)
+{
+    uint32_t ovf = 0;
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t lin = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; lin < L.total; lin += step) {
+        int64_t base[PSK_MAX_INPUTS], sbase[PSK_MAX_INPUTS];
+        for (int i = 0; i < L.n_in; ++i) {
+            base[i] = operand_offset(L.in[i], L.dims, 0, L.n_outer, lin);
+            sbase[i] = scale_offset(L.in[i], L.dims, 0, L.n_outer, lin);
+        }
+        int64_t ooff = operand_offset(L.out, L.dims, 0, L.n_outer, lin);
+        float acc = 0.0f;
+        for (int64_t c = 0; c < L.inner; ++c) {
+            float prod = 1.0f;
+            for (int i = 0; i < L.n_in; ++i) {
+                int64_t o = base[i] + operand_offset(L.in[i], L.dims, L.n_outer, L.n_inner, c);
+                int64_t so = sbase[i] + scale_offset(L.in[i], L.dims, L.n_outer, L.n_inner, c);
+                prod = __fmul_rn(prod, load_operand(L.in[i], o, so, L.kdtype, &ovf));
+            }
+            acc = __fadd_rn(acc, prod);
+        }
+        ovf |= store_real(const_cast<void *>(L.out.p), L.out.dtype, ooff, acc);
+    }
+    if (L.guarded && ovf) atomicOr(L.ovf, 1u);
+}
+
+// PSK_OP_CONTRACT, exact, for a matrix product with strides: C[b][i][j] =
+// sum_k A[b][i][k]·B[b][k][j], batch b = blockIdx.z, 64x64 tiles of C, 16 of
+// k at a time through shared memory, 4x4 outputs a thread. Every output still
+// adds its own terms in increasing k from +0, each product rounded first: the
+// tiling moves data, never an addition (the reference's layout space has the
+// same property, presk-rt/src/layout.rs:6-11).
+struct DevGemmExact {
+    const void *a, *b;
+    void *c;
+    int a_dtype, b_dtype, c_dtype, kdtype;
+    int64_t m, n, k;
+    int64_t a_i, a_k, b_k, b_j;           // element strides of the operands
+    int64_t batch_lo;                     // batch = hi * batch_lo + lo
+    int64_t a_lo, a_hi, b_lo, b_hi, c_lo, c_hi;
+    // row i of C at (i / c_row_lo_count) * c_row_hi + (i % c_row_lo_count) * c_row_lo, columns alike
+    int64_t c_row_lo_count, c_row_lo, c_row_hi;
+    int64_t c_col_lo_count, c_col_lo, c_col_hi;
+    const float *b_scales;                // integer weights: the scale of column j is b_scales[... + j * b_sj]
+    int64_t b_sj, b_slo, b_shi;
+    uint32_t *ovf;
+    int guarded;
+};
+
+__global__ void __launch_bounds__(256) k_gemm_exact(const __grid_constant__ DevGemmExact G)
+{
+    __shared__ float As[16][64 + 4];
+    __shared__ float Bs[16][64 + 4];
+    const int tid = threadIdx.x, tx = tid % 16, ty = tid / 16;
+    const int64_t i0 = (int64_t)blockIdx.y * 64, j0 = (int64_t)blockIdx.x * 64;
+    const int64_t bz = blockIdx.z, blo = bz % G.batch_lo, bhi = bz / G.batch_lo;
+    const int64_t aoff = blo * G.a_lo + bhi * G.a_hi, boff = blo * G.b_lo + bhi * G.b_hi, coff = blo * G.c_lo + bhi * G.c_hi;
+    const int64_t soff = blo * G.b_slo + bhi * G.b_shi;
+    uint32_t ovf = 0;
+    float acc[4][4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[r][c] = 0.0f;
+    for (int64_t k0 = 0; k0 < G.k; k0 += 16) {
+        // A tile: 64 rows x 16 k; B tile: 16 k x 64 columns; 4 elements a thread each
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            int e = tid + t * 256;
+            {
+                int kk, ii;
+                if (G.a_k == 1) { kk = e % 16; ii = e / 16; } else { ii = e % 64; kk = e / 64; }
+                int64_t i = i0 + ii, k = k0 + kk;
+                float v = 0.0f;
+                if (i < G.m && k < G.k) v = edge_round(load_real(G.a, G.a_dtype, aoff + i * G.a_i + k * G.a_k), G.kdtype, G.a_dtype, &ovf);
+                As[kk][ii] = v;
+            }
+            {
+                int kk, jj;
+                if (G.b_k == 1) { kk = e % 16; jj = e / 16; } else { jj = e % 64; kk = e / 64; }
+                int64_t j = j0 + jj, k = k0 + kk;
+                float v = 0.0f;
+                if (j < G.n && k < G.k) {
+                    int64_t o = boff + k * G.b_k + j * G.b_j;
+                    if (G.b_dtype == PSK_I8) v = (float)((const int8_t *)G.b)[o] * G.b_scales[soff + j * G.b_sj];
+                    else v = edge_round(load_real(G.b, G.b_dtype, o), G.kdtype, G.b_dtype, &ovf);
+                }
+                Bs[kk][jj] = v;
+            }
+        }
+        __syncthreads();
+        const int kmax = (int)((G.k - k0) < 16 ? (G.k - k0) : 16);
+        for (int kk = 0; kk < kmax; ++kk) {
+            float a[4], b[4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) a[r] = As[kk][ty * 4 + r];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) b[c] = Bs[kk][tx * 4 + c];
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) acc[r][c] = __fadd_rn(acc[r][c], __fmul_rn(a[r], b[c]));
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            int64_t i = i0 + ty * 4 + r, j = j0 + tx * 4 + c;
+            if (i < G.m && j < G.n) {
+                int64_t o = coff + (i / G.c_row_lo_count) * G.c_row_hi + (i % G.c_row_lo_count) * G.c_row_lo + (j / G.c_col_lo_count) * G.c_col_hi + (j % G.c_col_lo_count) * G.c_col_lo;
+                ovf |= store_real(G.c, G.c_dtype, o, acc[r][c]);
+            }
+        }
+    if (G.guarded && ovf) atomicOr(G.ovf, 1u);
+}
+
+// ---------------------------------------------------------------------------
+// PSK_OP_REDUCE (lower.rs:1221-1255, 1693): sum, mean (sum / n), sum of
+// squares; exact: one thread per output, the terms in lexicographic order.
+// ---------------------------------------------------------------------------
+PSK_DEV float reduce_finish(const DevLaunch &L, float acc)
+{
+    return L.kind == PSK_REDUCE_MEAN ? __fdiv_rn(acc, (float)(double)L.iparam[0]) : acc;
+}
+
+__global__ void __launch_bounds__(128) k_reduce_seq(const __grid_constant__ DevLaunch L)
+{
+    uint32_t ovf = 0;
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t lin = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; lin < L.total; lin += step) {
+        int64_t base = operand_offset(L.in[0], L.dims, 0, L.n_outer, lin);
+        int64_t ooff = operand_offset(L.out, L.dims, 0, L.n_outer, lin);
+        float acc = 0.0f;
+        if (L.n_inner == 1) {
+            const int64_t s = L.in[0].stride[L.n_outer];
+            for (int64_t c = 0; c < L.inner; ++c) {
+                float x = load_operand(L.in[0], base + c * s, 0, L.kdtype, &ovf);
+                acc = __fadd_rn(acc, L.kind == PSK_REDUCE_SUMSQ ? __fmul_rn(x, x) : x);
+            }
+        } else {
+            for (int64_t c = 0; c < L.inner; ++c) {
+                float x = load_operand(L.in[0], base + operand_offset(L.in[0], L.dims, L.n_outer, L.n_inner, c), 0, L.kdtype, &ovf);
+                acc = __fadd_rn(acc, L.kind == PSK_REDUCE_SUMSQ ? __fmul_rn(x, x) : x);
+            }
+        }
+        ovf |= store_real(const_cast<void *>(L.out.p), L.out.dtype, ooff, reduce_finish(L, acc));
+    }
+    if (L.guarded && ovf) atomicOr(L.ovf, 1u);
+}
+
+PSK_DEV float warp_sum(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+PSK_DEV float warp_max(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// A block's sum or maximum, every thread receiving it. `red` holds 32 floats.
+template <bool MAX>
+PSK_DEV float block_reduce(float v, float *red)
+{
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = MAX ? warp_max(v) : warp_sum(v);
+    __syncthreads();
+    if (lane == 0) red[w] = v;
+    __syncthreads();
+    float r = lane < nw ? red[lane] : (MAX ? -INFINITY : 0.0f);
+    r = MAX ? warp_max(r) : warp_sum(r);
+    return r;
+}
+
+// PSK_OP_REDUCE under PSK_ORDER_DEVICE over one contiguous summed axis: a
+// warp a row, eight elements a lane a step, a shuffle tree at the end. The
+// grouping of the additions differs from index order (declared).
+__global__ void __launch_bounds__(256) k_reduce_rows_tree(const __grid_constant__ DevLaunch L)
+{
+    uint32_t ovf = 0;
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    const int64_t n = L.inner;
+    const bool vec = (n % 8 == 0);
+    for (int64_t row = warp; row < L.total; row += nwarps) {
+        int64_t base = operand_offset(L.in[0], L.dims, 0, L.n_outer, row);
+        float acc = 0.0f;
+        if (vec) {
+            for (int64_t c = (int64_t)lane * 8; c < n; c += 256) {
+                float x[8];
+                load_vec<8>(L.in[0], base + c, 0, 1, 0, L.kdtype, x, &ovf);
+#pragma unroll
+                for (int t = 0; t < 8; ++t) acc += L.kind == PSK_REDUCE_SUMSQ ? __fmul_rn(x[t], x[t]) : x[t];
+            }
+        } else {
+            for (int64_t c = lane; c < n; c += 32) {
+                float x = load_operand(L.in[0], base + c, 0, L.kdtype, &ovf);
+                acc += L.kind == PSK_REDUCE_SUMSQ ? __fmul_rn(x, x) : x;
+            }
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) {
+            int64_t ooff = operand_offset(L.out, L.dims, 0, L.n_outer, row);
+            ovf |= store_real(const_cast<void *>(L.out.p), L.out.dtype, ooff, reduce_finish(L, acc));
+        }
+    }
+    if (L.guarded && ovf) atomicOr(L.ovf, 1u);
+}
+
+// A whole tensor summed to one number under PSK_ORDER_DEVICE: one block.
+__global__ void __launch_bounds__(1024) k_reduce_all_tree(const __grid_constant__ DevLaunch L)
+{
+    __shared__ float red[32];
+    uint32_t ovf = 0;
+    float acc = 0.0f;
+    for (int64_t c = threadIdx.x; c < L.inner; c += blockDim.x) {
+        float x = load_operand(L.in[0], operand_offset(L.in[0], L.dims, L.n_outer, L.n_inner, c), 0, L.kdtype, &ovf);
+        acc += L.kind == PSK_REDUCE_SUMSQ ? __fmul_rn(x, x) : x;
+    }
+    acc = block_reduce<false>(acc, red);
+    if (threadIdx.x == 0) ovf |= store_real(const_cast<void *>(L.out.p), L.out.dtype, 0, reduce_finish(L, acc));
+    if (L.guarded && ovf) atomicOr(L.ovf, 1u);
+}
+
+// ---------------------------------------------------------------------------
+// PSK_OP_SOFTMAX (lower.rs:1274-1419), three passes, exact: a thread a row.
+// Input 1, when masked, is indices 0 or 1 broadcast into the scores; iparam[0]
+// = 1 says it is the causal mask of lower.rs:1718 (allowed iff k <= i), whose
+// row i is iparam[1]-strided: then it is computed, not read.
+// ---------------------------------------------------------------------------
+PSK_DEV bool mask_allows(const DevLaunch &L, int64_t mbase, int64_t k, int64_t ms)
+{
+    if (L.iparam[0] == 1) return k <= mbase; // mbase is the row's position
+    return (float)(double)((const int64_t *)L.in[1].p)[mbase + k * ms] > 0.5f;
+}
+
+__global__ void __launch_bounds__(128) k_softmax_seq(const __grid_constant__ DevLaunch L)
+{
+    uint32_t ovf = 0;
+    const int64_t n = L.inner, s = L.in[0].stride[L.n_outer], os = L.out.stride[L.n_outer];
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t row = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; row < L.total; row += step) {
+        if (n == 0) continue;
+        int64_t base = operand_offset(L.in[0], L.dims, 0, L.n_outer, row);
+        int64_t obase = operand_offset(L.out, L.dims, 0, L.n_outer, row);
+        if (!L.masked) {
+            float m = load_operand(L.in[0], base, 0, L.kdtype, &ovf);
+            for (int64_t k = 0; k < n; ++k) {
+                float x = load_operand(L.in[0], base + k * s, 0, L.kdtype, &ovf);
+                if (x > m) m = x;
+            }
+            float z = 0.0f;
+            for (int64_t k = 0; k < n; ++k) z = __fadd_rn(z, lm_expf(__fsub_rn(load_operand(L.in[0], base + k * s, 0, L.kdtype, &ovf), m)));
+            for (int64_t k = 0; k < n; ++k)
+                ovf |= store_real(const_cast<void *>(L.out.p), L.out.dtype, obase + k * os, __fdiv_rn(lm_expf(__fsub_rn(load_operand(L.in[0], base + k * s, 0, L.kdtype, &ovf), m)), z));
+        } else {
+            int64_t mbase = operand_offset(L.in[1], L.dims, 0, L.n_outer, row);
+            const int64_t ms = L.in[1].stride[L.n_outer];
+            if (L.iparam[0] == 1) mbase = mbase / L.iparam[1];
+            float mx = 0.0f;
+            bool first = true;
+            for (int64_t k = 0; k < n; ++k) {
+                if (mask_allows(L, mbase, k, ms)) {
+                    float x = load_operand(L.in[0], base + k * s, 0, L.kdtype, &ovf);
+                    mx = first ? x : (x > mx ? x : mx);
+                    first = false;
+                }
+            }
+            float z = 0.0f;
+            for (int64_t k = 0; k < n; ++k) {
+                float e = mask_allows(L, mbase, k, ms) ? lm_expf(__fsub_rn(load_operand(L.in[0], base + k * s, 0, L.kdtype, &ovf), mx)) : 0.0f;
+                z = __fadd_rn(z, e);
+            }
+            for (int64_t k = 0; k < n; ++k) {
+                float v = mask_allows(L, mbase, k, ms) ? __fdiv_rn(lm_expf(__fsub_rn(load_operand(L.in[0], base + k * s, 0, L.kdtype, &ovf), mx)), z) : 0.0f;
+                ovf |= store_real(const_cast<void *>(L.out.p), L.out.dtype, obase + k * os, v);
+            }
+        }
+    }
+    if (L.guarded && ovf) atomicOr(L.ovf, 1u);
+}
+
+// PSK_OP_SOFTMAX under PSK_ORDER_DEVICE over a contiguous axis: a warp a row,
+// the row's exponentials kept in registers between the sum and the division
+// (the same bits as computing them twice), the sum a shuffle tree. CACHE
+// floats a lane: rows of up to 32·CACHE elements.
+template <int CACHE>
+__global__ void __launch_bounds__(128) k_softmax_rows_tree(const __grid_constant__ DevLaunch L)
+{
+    uint32_t ovf = 0;
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    const int64_t n = L.inner;
+    for (int64_t row = warp; row < L.total; row += nwarps) {
+        int64_t base = operand_offset(L.in[0], L.dims, 0, L.n_outer, row);
+        int64_t obase = operand_offset(L.out, L.dims, 0, L.n_outer, row);
+        int64_t mbase = 0, ms = 0;
+        if (L.masked) {
+            mbase = operand_offset(L.in[1], L.dims, 0, L.n_outer, row);
+            ms = L.in[1].stride[L.n_outer];
+            if (L.iparam[0] == 1) mbase = mbase / L.iparam[1];
+        }
+        // element (c, t) of this lane is column (c·32 + lane)·8 + t
+        float x[CACHE];
+        uint32_t allow[CACHE / 8];
+        float m = -INFINITY;
+        bool any = false;
+#pragma unroll
+        for (int c = 0; c < CACHE / 8; ++c) {
+            int64_t col = ((int64_t)c * 32 + lane) * 8;
+            allow[c] = 0;
+            if (col < n) {
+                bool live = !(L.masked && L.iparam[0] == 1 && col > mbase);
+                float v[8];
+                if (live) load_vec<8>(L.in[0], base + col, 0, 1, 0, L.kdtype, v, &ovf);
+#pragma unroll
+                for (int t = 0; t < 8; ++t) {
+                    bool ok = live && (!L.masked || mask_allows(L, mbase, col + t, ms));
+                    x[c * 8 + t] = ok ? v[t] : 0.0f;
+                    if (ok) {
+                        allow[c] |= 1u << t;
+                        m = fmaxf(m, v[t]);
+                        any = true;
+                    }
+                }
+            }
+        }
+        m = warp_max(m);
+        any = __any_sync(0xffffffffu, any);
+        float z = 0.0f;
+#pragma unroll
+        for (int c = 0; c < CACHE / 8; ++c)
+#pragma unroll
+            for (int t = 0; t < 8; ++t) {
+                float e = (allow[c] >> t & 1u) ? lm_expf(__fsub_rn(x[c * 8 + t], m)) : 0.0f;
+                x[c * 8 + t] = e;
+                z += e;
+            }
+        z = warp_sum(z);
+#pragma unroll
+        for (int c = 0; c < CACHE / 8; ++c) {
+            int64_t col = ((int64_t)c * 32 + lane) * 8;
+            if (col < n) {
+                float r[8];
+#pragma unroll
+                for (int t = 0; t < 8; ++t) r[t] = (allow[c] >> t & 1u) ? __fdiv_rn(x[c * 8 + t], z) : 0.0f;
+                ovf |= store_vec<8>(L.out, obase + col, r);
+            }
+        }
+        (void)any;
+    }
+    if (L.guarded && ovf) atomicOr(L.ovf, 1u);
+}
+
+// ---------------------------------------------------------------------------
+// PSK_OP_XENT (lower.rs:1459): ln z + m - x[y] over the last axis.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) k_xent_seq(const __grid_constant__ DevLaunch L)
+{
+    uint32_t ovf = 0;
+    const int64_t n = L.inner, s = L.in[0].stride[L.n_outer];
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t row = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; row < L.total; row += step) {
+        int64_t base = operand_offset(L.in[0], L.dims, 0, L.n_outer, row);
+        int64_t ybase = operand_offset(L.in[1], L.dims, 0, L.n_outer, row);
+        int64_t obase = operand_offset(L.out, L.dims, 0, L.n_outer, row);
+        float m = load_operand(L.in[0], base, 0, L.kdtype, &ovf);
+        for (int64_t k = 0; k < n; ++k) {
+            float x = load_operand(L.in[0], base + k * s, 0, L.kdtype, &ovf);
+            if (x > m) m = x;
+        }
+        float z = 0.0f;
+        for (int64_t k = 0; k < n; ++k) z = __fadd_rn(z, lm_expf(__fsub_rn(load_operand(L.in[0], base + k * s, 0, L.kdtype, &ovf), m)));
+        int64_t y = ((const int64_t *)L.in[1].p)[ybase];
+        float xy = 0.0f;
+        if (y >= 0 && y < n) xy = load_operand(L.in[0], base + y * s, 0, L.kdtype, &ovf);
+        else atomicOr(L.status, 2u);
+        ovf |= store_real(const_cast<void *>(L.out.p), L.out.dtype, obase, __fsub_rn(__fadd_rn(lm_logf(z), m), xy));
+    }
+    if (L.guarded && ovf) atomicOr(L.ovf, 1u);
+}
+
+// Under PSK_ORDER_DEVICE: a block a row, z a tree sum.
+__global__ void __launch_bounds__(256) k_xent_rows_tree(const __grid_constant__ DevLaunch L)
+{
+    __shared__ float red[32];
+    uint32_t ovf = 0;
+    const int64_t n = L.inner;
+    const bool vec = (n % 8 == 0) && L.in[0].stride[L.n_outer] == 1;
+    for (int64_t row = blockIdx.x; row < L.total; row += gridDim.x) {
+        int64_t base = operand_offset(L.in[0], L.dims, 0, L.n_outer, row);
+        float m = -INFINITY;
+        if (vec) {
+            for (int64_t c = (int64_t)threadIdx.x * 8; c < n; c += (int64_t)blockDim.x * 8) {
+                float x[8];
+                load_vec<8>(L.in[0], base + c, 0, 1, 0, L.kdtype, x, &ovf);
+#pragma unroll
+                for (int t = 0; t < 8; ++t) m = fmaxf(m, x[t]);
+            }
+        } else {
+            for (int64_t c = threadIdx.x; c < n; c += blockDim.x) m = fmaxf(m, load_operand(L.in[0], base + c * L.in[0].stride[L.n_outer], 0, L.kdtype, &ovf));
+        }
+        m = block_reduce<true>(m, red);
+        float z = 0.0f;
+        if (vec) {
+            for (int64_t c = (int64_t)threadIdx.x * 8; c < n; c += (int64_t)blockDim.x * 8) {
+                float x[8];
+                load_vec<8>(L.in[0], base + c, 0, 1, 0, L.kdtype, x, &ovf);
+#pragma unroll
+                for (int t = 0; t < 8; ++t) z += lm_expf(__fsub_rn(x[t], m));
+            }
+        } else {
+            for (int64_t c = threadIdx.x; c < n; c += blockDim.x) z += lm_expf(__fsub_rn(load_operand(L.in[0], base + c * L.in[0].stride[L.n_outer], 0, L.kdtype, &ovf), m));
+        }
+        z = block_reduce<false>(z, red);
+        if (threadIdx.x == 0) {
+            int64_t ybase = operand_offset(L.in[1], L.dims, 0, L.n_outer, row);
+            int64_t obase = operand_offset(L.out, L.dims, 0, L.n_outer, row);
+            int64_t y = ((const int64_t *)L.in[1].p)[ybase];
+            float xy = 0.0f;
+            if (y >= 0 && y < n) xy = load_operand(L.in[0], base + y * L.in[0].stride[L.n_outer], 0, L.kdtype, &ovf);
+            else atomicOr(L.status, 2u);
+            ovf |= store_real(const_cast<void *>(L.out.p), L.out.dtype, obase, __fsub_rn(__fadd_rn(lm_logf(z), m), xy));
+        }
+    }
+    if (L.guarded && ovf) atomicOr(L.ovf, 1u);
+}
+
+// ---------------------------------------------------------------------------
+// PSK_OP_ARGMAX (lower.rs:1490): the last of equal maxima.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) k_argmax(const __grid_constant__ DevLaunch L)
+{
+    uint32_t ovf = 0;
+    const int64_t n = L.inner, s = L.in[0].stride[L.n_outer];
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t row = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; row < L.total; row += step) {
+        int64_t base = operand_offset(L.in[0], L.dims, 0, L.n_outer, row);
+        int64_t obase = operand_offset(L.out, L.dims, 0, L.n_outer, row);
+        float m = load_operand(L.in[0], base, 0, L.kdtype, &ovf);
+        int64_t best = 0;
+        for (int64_t k = 0; k < n; ++k) {
+            float x = load_operand(L.in[0], base + k * s, 0, L.kdtype, &ovf);
+            if (x >= m) { m = x; best = k; }
+        }
+        ((int64_t *)const_cast<void *>(L.out.p))[obase] = best;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// PSK_OP_EMBED (lower.rs:1421): out[iv, j] = table[idx[iv], j]. dims =
+// (idx dims..., d); input 0 the table (stride over its two axes in stride[0],
+// stride[1]), input 1 the indices. iparam[0] = rows of the table.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) k_embed(const __grid_constant__ DevLaunch L)
+{
+    uint32_t ovf = 0;
+    const int last = L.n_outer - 1;
+    const int64_t d = L.dims[last], rows = L.total / d;
+    const bool vec = d % 8 == 0 && L.in[0].stride[1] == 1 && L.out.stride[last] == 1 && L.in[0].stride[0] % 8 == 0;
+    const int64_t per = vec ? d / 8 : d;
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t lin = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; lin < rows * per; lin += step) {
+        int64_t row = lin / per, c = lin % per;
+        int64_t ioff = operand_offset(L.in[1], L.dims, 0, last, row);
+        int64_t obase = operand_offset(L.out, L.dims, 0, last, row);
+        int64_t id = ((const int64_t *)L.in[1].p)[ioff];
+        bool ok = id >= 0 && id < L.iparam[0];
+        if (!ok) { atomicOr(L.status, 2u); id = 0; }
+        if (vec) {
+            float x[8];
+            load_vec<8>(L.in[0], id * L.in[0].stride[0] + c * 8, 0, 1, 0, L.kdtype, x, &ovf);
+            ovf |= store_vec<8>(L.out, obase + c * 8, x);
+        } else {
+            float x = load_operand(L.in[0], id * L.in[0].stride[0] + c * L.in[0].stride[1], 0, L.kdtype, &ovf);
+            ovf |= store_real(const_cast<void *>(L.out.p), L.out.dtype, obase + c * L.out.stride[last], x);
+        }
+    }
+    if (L.guarded && ovf) atomicOr(L.ovf, 1u);
+}
+
+// ---------------------------------------------------------------------------
+// PSK_OP_COPY: out[o] = in[o] through strides (slice, a part of a concat,
+// split_heads, merge_heads, index, broadcast_like). Reals pass through the
+// kernel's arithmetic as the reference's `Store(Load)` does; indices are
+// copied as integers.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) k_copy(const __grid_constant__ DevLaunch L)
+{
+    uint32_t ovf = 0;
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t lin = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; lin < L.total; lin += step) {
+        int64_t off = 0, ooff = 0, r = lin;
+        for (int a = L.n_outer - 1; a >= 0; --a) {
+            int64_t d = L.dims[a], ix = r % d;
+            r /= d;
+            off += ix * L.in[0].stride[a];
+            ooff += ix * L.out.stride[a];
+        }
+        if (L.in[0].is_index) ((int64_t *)const_cast<void *>(L.out.p))[ooff] = ((const int64_t *)L.in[0].p)[off];
+        else ovf |= store_real(const_cast<void *>(L.out.p), L.out.dtype, ooff, load_operand(L.in[0], off, 0, L.kdtype, &ovf));
+    }
+    if (L.guarded && ovf) atomicOr(L.ovf, 1u);
+}
+
+// The same, eight elements of a contiguous last axis at a time.
+__global__ void __launch_bounds__(256) k_copy_vec8(const __grid_constant__ DevLaunch L)
+{
+    uint32_t ovf = 0;
+    const int last = L.n_outer - 1;
+    const int64_t nvec = L.total / 8, lastv = L.dims[last] / 8;
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t lin = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; lin < nvec; lin += step) {
+        int64_t r = lin / lastv, c = (lin % lastv) * 8;
+        int64_t off = c, ooff = c;
+        for (int a = last - 1; a >= 0; --a) {
+            int64_t d = L.dims[a], ix = r % d;
+            r /= d;
+            off += ix * L.in[0].stride[a];
+            ooff += ix * L.out.stride[a];
+        }
+        float x[8];
+        load_vec<8>(L.in[0], off, 0, 1, 0, L.kdtype, x, &ovf);
+        ovf |= store_vec<8>(L.out, ooff, x);
+    }
+    if (L.guarded && ovf) atomicOr(L.ovf, 1u);
+}
+
+// ---------------------------------------------------------------------------
+// PSK_OP_IOTA (lower.rs:1706-1750).
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) k_iota(const __grid_constant__ DevLaunch L)
+{
+    uint32_t ovf = 0;
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t lin = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; lin < L.total; lin += step) {
+        switch (L.kind) {
+        case PSK_IOTA_POSITIONS: ((int64_t *)const_cast<void *>(L.out.p))[lin] = lin; break;
+        case PSK_IOTA_CAUSAL: {
+            int64_t n = L.dims[1], i = lin / n, j = lin % n;
+            ((int64_t *)const_cast<void *>(L.out.p))[lin] = (float)(double)j <= (float)(double)i ? 1 : 0;
+            break;
+        }
+        case PSK_IOTA_ONE_HOT: {
+            int64_t v = L.dims[L.n_outer - 1], row = lin / v, j = lin % v;
+            int64_t ioff = operand_offset(L.in[0], L.dims, 0, L.n_outer - 1, row);
+            float hit = (float)(double)((const int64_t *)L.in[0].p)[ioff] == (float)(double)j ? 1.0f : 0.0f;
+            ovf |= store_real(const_cast<void *>(L.out.p), L.out.dtype, lin, hit);
+            break;
+        }
+        default: ovf |= store_real(const_cast<void *>(L.out.p), L.out.dtype, lin, L.fparam); break;
+        }
+    }
+    if (L.guarded && ovf) atomicOr(L.ovf, 1u);
+}
+
+// ---------------------------------------------------------------------------
+// PSK_OP_CONVERT: n reals of one type stored as another, through f64 as the
+// host converts a buffer at a kernel's edge (presk-rt/src/lib.rs:868-876;
+// presk-export-c/c/presk_rt.c `presk_convert`): a widening is exact; to f32
+// rounds once; to bf16 rounds to f32 and then to bf16; to binary16 or e8m15
+// rounds once, also from an f64.
+// ---------------------------------------------------------------------------
+// An f64 rounded to f32 toward zero with the lost bits or-ed into the last
+// place ("to odd"): rounding that to a narrower format gives the f64's own
+// correctly rounded value, since f32 has more than two bits to spare.
+PSK_DEV float f64_to_f32_odd(double x)
+{
+    float r = __double2float_rz(x);
+    if (x == x && (double)r != x && fabsf(r) != INFINITY) r = bits_f32(f32_bits(r) | 1u);
+    return r;
+}
+
+__global__ void __launch_bounds__(256) k_convert(const void *src, int from, void *dst, int to, int64_t n, int guarded, uint32_t *flag)
+{
+    uint32_t ovf = 0;
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) {
+        if (from == PSK_F64) {
+            double x = ((const double *)src)[i];
+            if (to == PSK_F64) ((double *)dst)[i] = x;
+            else if (to == PSK_F32 || to == PSK_BF16) ovf |= store_real(dst, to, i, (float)x);
+            else ovf |= store_real(dst, to, i, f64_to_f32_odd(x));
+        } else {
+            float x = load_real(src, from, i);
+            ovf |= store_real(dst, to, i, x);
+        }
+    }
+    if (guarded && ovf) atomicOr(flag, 1u);
+}
+
+// ---------------------------------------------------------------------------
+// Integer weights (presk-rt/src/quant.rs:128-167; presk_rt.c `presk_quantize`):
+// a tensor read as outer x k x inner, one scale per (outer, inner) channel:
+// m = max|w| over k (a NaN passed over), s = f32(m / 127) (absmax), q =
+// clamp(rne(w / s), ±127), 0 when s is 0 or w / s is a NaN. The reference
+// quantises f64 reals; this kernel takes f32 or f64 and computes in f64.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) k_quant_scales(const void *w, int from, float *s, int64_t outer, int64_t k, int64_t inner)
+{
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t ch = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; ch < outer * inner; ch += step) {
+        int64_t o = ch / inner, in = ch % inner;
+        double m = 0.0;
+        for (int64_t kk = 0; kk < k; ++kk) {
+            int64_t e = (o * k + kk) * inner + in;
+            double x = from == PSK_F64 ? ((const double *)w)[e] : (double)((const float *)w)[e];
+            double a = fabs(x);
+            if (a > m) m = a;
+        }
+        s[ch] = (float)(m / 127.0);
+    }
+}
+
+__global__ void __launch_bounds__(256) k_quant_codes(const void *w, int from, const float *s, int8_t *q, int64_t outer, int64_t k, int64_t inner)
+{
+    const int64_t n = outer * k * inner, step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += step) {
+        int64_t ch = (e / (k * inner)) * inner + e % inner;
+        double x = from == PSK_F64 ? ((const double *)w)[e] : (double)((const float *)w)[e];
+        double sc = (double)s[ch];
+        double r = x / sc;
+        int v = 0;
+        if (sc != 0.0 && r == r) {
+            double t = rint(r); // to nearest, ties to even
+            t = t > 127.0 ? 127.0 : (t < -127.0 ? -127.0 : t);
+            v = (int)t;
+        }
+        q[e] = (int8_t)v;
+    }
+}
+
+// Normal draws for parameters made on the device: a counter-based hash
+// (splitmix64) and Box-Muller in f32 with CUDA's own logf/cosf. These are not
+// the reference's keys; they only have to be the same on every run.
+PSK_DEV uint64_t mix64(uint64_t z)
+{
+    z += 0x9e3779b97f4a7c15ull;
+    z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull;
+    z = (z ^ (z >> 27)) * 0x94d049bb133111ebull;
+    return z ^ (z >> 31);
+}
+
+__global__ void __launch_bounds__(256) k_init_normal(void *dst, int to, int64_t n, uint64_t seed, float std)
+{
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) {
+        float v;
+        if (std < 0.0f) {
+            v = 1.0f;
+        } else {
+            uint64_t h = mix64(seed * 0x2545f4914f6cdd1dull + (uint64_t)i);
+            float u1 = ((float)(uint32_t)(h >> 40) + 1.0f) * (1.0f / 16777216.0f);
+            float u2 = (float)(uint32_t)((h >> 8) & 0xffffffu) * (1.0f / 16777216.0f);
+            v = std * sqrtf(-2.0f * logf(u1)) * cosf(6.28318530718f * u2);
+        }
+        store_real(dst, to, i, v);
+    }
+}
+
+} // namespace psk
