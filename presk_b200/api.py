@@ -121,10 +121,12 @@ class Host:
         else:
             self.lib = lib if lib is not None else abi.load()
             self._vt = executor
-        text = realization if isinstance(realization, str) else __import__("json").dumps(realization)
+        text = realization if isinstance(realization, str) else __import__("json").dumps(realization, ensure_ascii=False)
         self.handle = self.lib.psk_host_create(C.byref(self._vt), text.encode())
         if not self.handle:
-            raise PreskError(abi.E7001, self.lib.psk_host_error(None).decode())
+            msg = self.lib.psk_host_error(None).decode()
+            m = __import__("re").match(r"\[E(\d+)\] (.*)", msg, __import__("re").S)
+            raise PreskError(int(m.group(1)), m.group(2)) if m else PreskError(abi.E7001, msg)
 
     def close(self):
         if getattr(self, "handle", None):

@@ -82,6 +82,15 @@ struct JsonReader {
         std::string s;
         ++p;
         while (*p && *p != '"') {
+            if (*p == '\\' && p[1] == 'u' && p[2] && p[3] && p[4] && p[5]) {
+                // a \uXXXX escape of the basic plane, as UTF-8 (parameter paths hold γ and β)
+                unsigned cp = (unsigned)strtoul(std::string(p + 2, 4).c_str(), nullptr, 16);
+                if (cp < 0x80) s.push_back((char)cp);
+                else if (cp < 0x800) { s.push_back((char)(0xc0 | (cp >> 6))); s.push_back((char)(0x80 | (cp & 0x3f))); }
+                else { s.push_back((char)(0xe0 | (cp >> 12))); s.push_back((char)(0x80 | ((cp >> 6) & 0x3f))); s.push_back((char)(0x80 | (cp & 0x3f))); }
+                p += 6;
+                continue;
+            }
             if (*p == '\\' && p[1]) ++p;
             s.push_back(*p++);
         }
@@ -1190,7 +1199,7 @@ psk_host *psk_host_create(const psk_exec_vtable *exec, const char *realization)
         h->rz = Realization::parse(realization);
         return h;
     } catch (const HostError &e) {
-        g_host_error = e.msg;
+        g_host_error = "[E" + std::to_string(e.code) + "] " + e.msg; // the code travels in the text: there is no handle to ask
         return nullptr;
     }
 }

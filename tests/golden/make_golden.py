@@ -1,0 +1,28 @@
+"""Writes tests/golden/reference_vectors.json from the reference's own test
+fixtures, so that the suite can run where the reference tree is not mounted.
+
+Sources (paths within presk-lang/presk, read as text):
+  tests/run/layernorm_apply.snap, rmsnorm_apply.snap   seed-0 outputs of the exact interpreter, 12 digits
+  crates/presk-interp/src/key.rs:86-93                  the first four normal draws of the key seed 0 names
+Run:  python tests/golden/make_golden.py [/root/reference]
+"""
+import json
+import os
+import re
+import sys
+
+ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+out = {}
+for name in ("layernorm_apply", "rmsnorm_apply"):
+    text = open(os.path.join(ref, "tests", "run", name + ".snap")).read()
+    body = text.split("---")[-1]
+    m = re.search(r"\[batch: (\d+), model: (\d+)\] (\[\[.*\]\])", body)
+    out[name] = {"shape": [int(m.group(1)), int(m.group(2))], "values": json.loads(m.group(3))}
+key_rs = open(os.path.join(ref, "crates", "presk-interp", "src", "key.rs")).read()
+m = re.search(r"assert_eq!\(first, \[([^\]]+)\]\)", key_rs)
+out["seed0_first_normals_bits"] = [int(x.strip(), 16) for x in m.group(1).split(",")]
+m = re.search(r"assert_eq!\(fold, (0x[0-9a-f]+)\)", key_rs)
+out["seed0_next_100000_fnv"] = int(m.group(1), 16)
+with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_vectors.json"), "w") as f:
+    json.dump(out, f, indent=1)
+print("wrote", list(out))

@@ -1,0 +1,125 @@
+"""Parity of the CUDA executor with the CPU oracle through the host program:
+the same model, realization, parameters and seeded inputs run over both.
+Under `order: sequential` the results must be the same bits; under
+`order: device` (tensor-core contractions, tree row sums) within the stated
+tolerance of the oracle."""
+import numpy as np
+import pytest
+
+import models
+from presk_b200 import Host, PreskError
+
+pytestmark = pytest.mark.gpu
+
+
+def both(cuda, oracle, realization, model, consts, params, entry, inputs, out_shape):
+    outs = []
+    for ex in (cuda, oracle.vtable()):
+        h = models.give(Host(ex, realization).prepare(model, **consts), params)
+        outs.append(h.call(entry, inputs, out_shape))
+    return outs
+
+
+def assert_same_bits(got, want):
+    a, b = np.ascontiguousarray(got).view(np.uint32), np.ascontiguousarray(want).view(np.uint32)
+    bad = np.nonzero(a != b)
+    assert bad[0].size == 0, f"{bad[0].size} of {a.size} elements differ, first at {tuple(x[0] for x in bad)}: {got[tuple(x[0] for x in bad)]!r} vs {want[tuple(x[0] for x in bad)]!r}"
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16", "f16", "e8m15"])
+@pytest.mark.parametrize("model", ["layernorm", "rmsnorm"])
+def test_norms_bit_exact(cuda, oracle, model, dtype):
+    rng = np.random.default_rng(7)
+    for shape in [(3, 8), (5, 7, 40), (2, 1000), (1, 4096)]:
+        d = shape[-1]
+        x = rng.standard_normal(shape).astype(np.float32)
+        params = {"γ": rng.standard_normal(d).astype(np.float32)}
+        if model == "layernorm":
+            params["β"] = rng.standard_normal(d).astype(np.float32)
+        got, want = both(cuda, oracle, dtype, model, {}, params, "apply", [x], shape)
+        assert_same_bits(got, want)
+
+
+def test_mlp_config1_bit_exact(cuda, oracle):
+    """BASELINE config 1 at full size: Linear{784,256} · ReLU · Linear{256,10} + cross-entropy, B = 4096, all f32."""
+    p = models.mlp_params()
+    x, y = models.mlp_inputs(4096)
+    got, want = both(cuda, oracle, "f32", "mlp", {}, p, "apply", [x], (4096, 10))
+    assert_same_bits(got, want)
+    got, want = both(cuda, oracle, "f32", "mlp", {}, p, "loss", [x, y], ())
+    assert_same_bits(got, want)
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16", "f16", "e8m15"])
+def test_llama_tiny_bit_exact_under_sequential_order(cuda, oracle, dtype):
+    c = models.LLAMA_TINY
+    p = models.llama_params(c)
+    rng = np.random.default_rng(3)
+    ids = rng.integers(0, c["V"], size=(2, 16), dtype=np.int64)
+    y = rng.integers(0, c["V"], size=(2, 16), dtype=np.int64)
+    got, want = both(cuda, oracle, dtype, "llama", c, p, "apply", [ids], (2, 16, c["V"]))
+    assert_same_bits(got, want)
+    got, want = both(cuda, oracle, dtype, "llama", c, p, "loss", [ids, y], ())
+    assert_same_bits(got, want)
+
+
+def test_llama_gqa_and_int8_bit_exact(cuda, oracle):
+    c = dict(V=64, D=64, H=4, G=2, FF=96, L=2)
+    p = models.llama_params(c)
+    ids = np.random.default_rng(4).integers(0, c["V"], size=(3, 24), dtype=np.int64)
+    q = {k: {"bits": 8, "over": -2} for k in ("blocks.attn.wq", "blocks.attn.wk", "blocks.attn.wv", "blocks.attn.wo", "blocks.ff.gate.w", "blocks.ff.up.w", "blocks.ff.down.w")}
+    rz = {"default": "bf16", "storage": {"RMSNorm.apply/%3": "f32", "RMSNorm.apply/%7": "f32"}, "params": {"tok": "bf16", "head": "bf16"}, "quant": q}
+    got, want = both(cuda, oracle, rz, "llama", c, p, "apply", [ids], (3, 24, c["V"]))
+    assert_same_bits(got, want)
+
+
+def test_llama_device_order_within_tolerance(cuda, oracle):
+    """Tensor-core contractions and tree sums: bf16 sites, shapes that reach the tcgen05 kernel
+    (every contracted axis a multiple of 8, hd = 64)."""
+    c = dict(V=512, D=256, H=4, G=4, FF=512, L=2)
+    p = models.llama_params(c)
+    rng = np.random.default_rng(5)
+    ids = rng.integers(0, c["V"], size=(2, 128), dtype=np.int64)
+    y = rng.integers(0, c["V"], size=(2, 128), dtype=np.int64)
+    rz = {"default": "bf16", "order": {"kind": "device"}, "params": {k: "bf16" for k in p}, "storage": {"Llama.apply/%11": "f32", "loss/%5": "f32", "loss/%6": "f32"}}
+    rs = dict(rz, order={"kind": "sequential"})
+    outs = []
+    for ex, r in ((cuda, rz), (oracle.vtable(), rs)):
+        h = models.give(Host(ex, r).prepare("llama", **c), p)
+        outs.append((h.call("apply", [ids], (2, 128, c["V"])), h.call("loss", [ids, y], ())))
+    (lg, ls), (lw, lsw) = outs
+    # bf16 activations: an element of a site may land on the neighbouring bf16 number when a sum's
+    # last bits differ; across two layers that is within a few bf16 ulps of the logits' scale
+    assert np.abs(lg - lw).max() <= 2.0**-6 * np.abs(lw).max()
+    assert abs(float(ls) - float(lsw)) <= 2e-3 * abs(float(lsw))
+    # and both stay close to the exact model
+    want = models.llama_numpy(p, c, ids)
+    assert np.abs(lg - want).max() <= 0.05 * np.abs(want).max()
+
+
+@pytest.mark.parametrize("dtype,scale,overflows", [("f16", 1.0, False), ("f16", 2.0**20, True), ("e8m15", 2.0**20, False)])
+@pytest.mark.parametrize("order", ["sequential", "device"])
+def test_contract_ln_config3_and_overflow_guard(cuda, oracle, dtype, scale, overflows, order):
+    """BASELINE config 3 at N = 1024: x·w stored in f16 / e8m15 then a row LayerNorm; inputs scaled
+    by 2^20 overflow the f16 store of the `dot` and stop the run with E7007."""
+    n = 1024 if order == "device" else 256
+    rng = np.random.default_rng(6)
+    x, w = (rng.standard_normal((n, n)) * scale).astype(np.float32), (rng.standard_normal((n, n)) * scale).astype(np.float32)
+    params = {"ln.γ": np.ones(n, np.float32), "ln.β": np.zeros(n, np.float32)}
+    rz = {"default": dtype, "order": {"kind": order}}
+    if overflows:
+        h = models.give(Host(cuda, rz).prepare("contract_ln"), params)
+        with pytest.raises(PreskError, match="E7007"):
+            h.call("apply", [x, w], (n, n))
+        return
+    rs = {"default": dtype, "order": {"kind": "sequential"}}
+    h = models.give(Host(cuda, rz).prepare("contract_ln"), params)
+    got = h.call("apply", [x, w], (n, n))
+    h = models.give(Host(oracle.vtable(), rs).prepare("contract_ln"), params)
+    want = h.call("apply", [x, w], (n, n))
+    if order == "sequential":
+        assert_same_bits(got, want)
+    else:
+        # LayerNorm outputs are O(1); the dot's sums differ in their last bits and each site rounds to 11 or 16 bits
+        tol = 2.0**-8 if dtype == "f16" else 2.0**-12
+        assert np.abs(got - want).max() <= tol * max(1.0, np.abs(want).max())

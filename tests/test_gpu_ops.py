@@ -1,0 +1,265 @@
+"""Single launches through psk_exec_run against the oracle's psk_oracle_run on the same
+descriptor and the same bytes: elementwise steps (every primitive, the device library's
+transcendental functions), conversions of every storage format, reductions, softmax,
+cross-entropy, gathers and copies; empty and ragged shapes."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from presk_b200 import abi, launch_desc
+
+pytestmark = pytest.mark.gpu
+
+
+def contiguous(shape):
+    s, acc = [], 1
+    for d in reversed(shape):
+        s.append(acc)
+        acc *= d
+    return list(reversed(s))
+
+
+def set_operand(op, dtype, shape, positions, offset=0, is_index=False):
+    """`shape` contiguous; axis i of it sits at iteration axis positions[i]."""
+    op.dtype = abi.I64 if is_index else dtype
+    op.is_index = 1 if is_index else 0
+    op.offset = offset
+    n = 1
+    for d in shape:
+        n *= d
+    op.numel = n
+    for st, p in zip(contiguous(shape), positions):
+        op.stride[p] += st
+
+
+def run_both(cuda, oracle, l, host_inputs, out_bytes):
+    """Runs `l` on the GPU and on the oracle; returns (gpu bytes, oracle bytes, gpu flag, oracle flag)."""
+    dev = [cuda.upload(a) for a in host_inputs]
+    pout = cuda.alloc(max(out_bytes, 1))
+    cuda.run(l, dev + [pout])
+    flag = cuda.overflow()
+    cuda.sync()
+    got = cuda.download(pout, out_bytes)
+    for p in dev + [pout]:
+        cuda.free(p)
+    want = np.full(out_bytes, 0xA5, dtype=np.uint8)
+    oflag = oracle.run(l, [np.ascontiguousarray(a) for a in host_inputs] + [want])
+    return got, want, 1 if flag else 0, oflag
+
+
+UNARY = [abi.NEG, abi.EXP, abi.LOG, abi.TANH, abi.SQRT, abi.SIN, abi.COS, abi.ABS, abi.GELU, abi.GELU_DERIV, abi.RELU, abi.HEAVISIDE, abi.SIGN, abi.SIGMOID, abi.REAL]
+
+
+@pytest.mark.parametrize("prim", UNARY)
+def test_unary_primitives_bit_exact_on_many_inputs(cuda, oracle, prim):
+    rng = np.random.default_rng(prim)
+    n = 1 << 20
+    x = np.concatenate([
+        rng.integers(0, 2**32, size=n, dtype=np.uint64).astype(np.uint32).view(np.float32),
+        rng.uniform(-100, 100, size=n).astype(np.float32),
+        np.array([0.0, -0.0, np.inf, -np.inf, np.nan, 1.0, -1.0, 88.7, -104.0], np.float32),
+    ])
+    if prim in (abi.SIN, abi.COS):
+        x = x[np.abs(x) < 4e8]  # beyond 2^28·π/2 the executor declines (reported, never wrong)
+    x = np.ascontiguousarray(x[: (x.size // 8) * 8 + 1])  # an odd length: the scalar kernel
+    for count in (x.size, (x.size // 8) * 8):
+        l = launch_desc(abi.OP_FUSED, abi.F32, [count])
+        l.n_inputs, l.n_steps = 1, 1
+        l.steps[0].prim, l.steps[0].nargs, l.steps[0].src[0] = prim, 1, 0
+        set_operand(l.inputs[0], abi.F32, [count], [0])
+        set_operand(l.out, abi.F32, [count], [0])
+        got, want, _, _ = run_both(cuda, oracle, l, [x[:count]], count * 4)
+        a, b = got.view(np.uint32), want.view(np.uint32)
+        nan = np.isnan(got.view(np.float32)) & np.isnan(want.view(np.float32))
+        bad = np.nonzero((a != b) & ~nan)[0]
+        assert bad.size == 0, f"{bad.size} differ; x={x[bad[0]]!r}: {a[bad[0]]:#x} vs {b[bad[0]]:#x}"
+
+
+@pytest.mark.parametrize("prim", [abi.ADD, abi.SUB, abi.MUL, abi.DIV, abi.MAX, abi.MIN])
+def test_binary_primitives_with_broadcast(cuda, oracle, prim):
+    rng = np.random.default_rng(prim + 50)
+    a = rng.standard_normal((6, 5, 24)).astype(np.float32)
+    b = rng.standard_normal((5, 1)).astype(np.float32)  # broadcast over the first and the last axis
+    a.ravel()[:7] = [0.0, -0.0, np.inf, -np.inf, 1e-45, -1e-45, 3.0]
+    l = launch_desc(abi.OP_FUSED, abi.F32, [6, 5, 24])
+    l.n_inputs, l.n_steps = 2, 1
+    l.steps[0].prim, l.steps[0].nargs, l.steps[0].src[0], l.steps[0].src[1] = prim, 2, 0, 1
+    set_operand(l.inputs[0], abi.F32, [6, 5, 24], [0, 1, 2])
+    set_operand(l.inputs[1], abi.F32, [5], [1])
+    set_operand(l.out, abi.F32, [6, 5, 24], [0, 1, 2])
+    got, want, _, _ = run_both(cuda, oracle, l, [a, b], a.size * 4)
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("to", [abi.F32, abi.BF16, abi.F16, abi.E8M15, abi.E4M3])
+@pytest.mark.parametrize("frm", [abi.F32, abi.F64, abi.BF16, abi.F16, abi.E8M15])
+def test_conversions_of_every_storage_format(cuda, oracle, frm, to):
+    rng = np.random.default_rng(frm * 10 + to)
+    n = 1 << 18
+    if frm == abi.F64:
+        src = np.concatenate([rng.standard_normal(n) * 10.0 ** rng.integers(-42, 39, n), [1.0 + 2.0**-11 + 2.0**-40, 65519.999, 65520.0, 1e-50, 1e300, np.inf, -np.inf, 0.0, -0.0]])
+    else:
+        f = rng.integers(0, 2**32, size=n, dtype=np.uint64).astype(np.uint32).view(np.float32)
+        f = f[~np.isnan(f)]  # payloads of NaNs are compared in the CPU suite; here numbers and infinities
+        src = f if frm == abi.F32 else np.frombuffer(oracle.convert(f, frm).tobytes(), dtype=np.uint8)
+    count = src.size if frm in (abi.F32, abi.F64) else src.size // abi.DTYPE_BYTES[frm]
+    l = launch_desc(abi.OP_CONVERT, to, [count])
+    l.n_inputs = 1
+    set_operand(l.inputs[0], frm, [count], [0])
+    set_operand(l.out, to, [count], [0])
+    got, want, gf, of = run_both(cuda, oracle, l, [np.ascontiguousarray(src)], count * abi.DTYPE_BYTES[to])
+    assert np.array_equal(got, want)
+    assert gf == of
+
+
+@pytest.mark.parametrize("order", [abi.ORDER_SEQUENTIAL, abi.ORDER_DEVICE])
+@pytest.mark.parametrize("shape,axis", [((7, 33), 1), ((4, 2048), 1), ((3, 5, 64), 1), ((16, 4096), 1), ((5, 0), 1), ((9, 1), 1)])
+def test_reduce_axis(cuda, oracle, shape, axis, order):
+    rng = np.random.default_rng(11)
+    x = rng.standard_normal(shape).astype(np.float32)
+    outer = [d for i, d in enumerate(shape) if i != axis]
+    for kind in (abi.REDUCE_SUM, abi.REDUCE_MEAN):
+        l = launch_desc(abi.OP_REDUCE, abi.F32, outer, [shape[axis]], order=order)
+        l.n_inputs, l.kind = 1, kind
+        l.iparam[0] = shape[axis]
+        pos = []
+        o = 0
+        for i in range(len(shape)):
+            if i == axis:
+                pos.append(len(outer))
+            else:
+                pos.append(o)
+                o += 1
+        set_operand(l.inputs[0], abi.F32, list(shape), pos)
+        set_operand(l.out, abi.F32, outer, list(range(len(outer))))
+        nout = int(np.prod(outer))
+        got, want, _, _ = run_both(cuda, oracle, l, [x], nout * 4)
+        g, w = got.view(np.float32), want.view(np.float32)
+        if order == abi.ORDER_SEQUENTIAL:
+            assert np.array_equal(got, want)
+        else:
+            np.testing.assert_allclose(g, w, rtol=1e-5, atol=1e-5, equal_nan=True)
+
+
+@pytest.mark.parametrize("dtype", [abi.F32, abi.BF16])
+@pytest.mark.parametrize("order", [abi.ORDER_SEQUENTIAL, abi.ORDER_DEVICE])
+@pytest.mark.parametrize("masked", [0, 1, 2])
+@pytest.mark.parametrize("rows,n", [(5, 8), (64, 256), (33, 2048), (3, 40), (2, 1)])
+def test_softmax(cuda, oracle, rows, n, masked, order, dtype):
+    """masked: 0 no mask, 1 a random mask with an empty row, 2 the causal mask a `causal_mask` launch wrote."""
+    rng = np.random.default_rng(rows * 31 + n)
+    if masked == 2:
+        rows = n
+    x32 = (rng.standard_normal((2, rows, n)) * 4).astype(np.float32)
+    x = x32 if dtype == abi.F32 else np.frombuffer(oracle.convert(x32, dtype).tobytes(), dtype=np.uint16).reshape(x32.shape)
+    l = launch_desc(abi.OP_SOFTMAX, dtype, [2, rows], [n], order=order)
+    l.n_inputs, l.masked = (2 if masked else 1), (1 if masked else 0)
+    set_operand(l.inputs[0], dtype, [2, rows, n], [0, 1, 2])
+    set_operand(l.out, dtype, [2, rows, n], [0, 1, 2])
+    ins = [x]
+    dev_mask = None
+    if masked == 1:
+        m = (rng.uniform(size=(rows, n)) < 0.7).astype(np.int64)
+        m[0, :] = 0  # a row the mask empties gives zeros
+        set_operand(l.inputs[1], abi.I64, [rows, n], [1, 2], is_index=True)
+        ins.append(m)
+    elif masked == 2:
+        m = np.tril(np.ones((n, n), np.int64))
+        set_operand(l.inputs[1], abi.I64, [n, n], [1, 2], is_index=True)
+        ins.append(m)
+    nbytes = x.size * abi.DTYPE_BYTES[dtype]
+    if masked == 2:
+        # let the executor write the mask itself, so that it knows it for the causal one
+        lm = launch_desc(abi.OP_IOTA, abi.F32, [n, n])
+        lm.kind = abi.IOTA_CAUSAL
+        set_operand(lm.out, abi.I64, [n, n], [0, 1], is_index=True)
+        dev_mask = cuda.alloc(n * n * 8)
+        cuda.run(lm, [dev_mask])
+        px, pout = cuda.upload(x), cuda.alloc(nbytes)
+        cuda.run(l, [px, dev_mask, pout])
+        cuda.sync()
+        got = cuda.download(pout, nbytes)
+        assert np.array_equal(cuda.download(dev_mask, n * n * 8).view(np.int64).reshape(n, n), m)
+        for p in (px, pout, dev_mask):
+            cuda.free(p)
+        want = np.zeros(nbytes, np.uint8)
+        oracle.run(l, [x, m, want])
+    else:
+        got, want, _, _ = run_both(cuda, oracle, l, ins, nbytes)
+    if order == abi.ORDER_SEQUENTIAL:
+        assert np.array_equal(got, want)
+    else:
+        g = oracle.widen(got, dtype, x.size)
+        w = oracle.widen(want, dtype, x.size)
+        tol = 2e-6 if dtype == abi.F32 else 2.0**-8
+        assert np.abs(g - w).max() <= tol
+
+
+@pytest.mark.parametrize("order", [abi.ORDER_SEQUENTIAL, abi.ORDER_DEVICE])
+@pytest.mark.parametrize("rows,v", [(64, 10), (16, 1000), (8, 32000), (3, 65)])
+def test_cross_entropy(cuda, oracle, rows, v, order):
+    rng = np.random.default_rng(v)
+    x = (rng.standard_normal((rows, v)) * 3).astype(np.float32)
+    y = rng.integers(0, v, size=(rows,), dtype=np.int64)
+    l = launch_desc(abi.OP_XENT, abi.F32, [rows], [v], order=order)
+    l.n_inputs = 2
+    set_operand(l.inputs[0], abi.F32, [rows, v], [0, 1])
+    set_operand(l.inputs[1], abi.I64, [rows], [0], is_index=True)
+    set_operand(l.out, abi.F32, [rows], [0])
+    got, want, _, _ = run_both(cuda, oracle, l, [x, y], rows * 4)
+    if order == abi.ORDER_SEQUENTIAL:
+        assert np.array_equal(got, want)
+    else:
+        np.testing.assert_allclose(got.view(np.float32), want.view(np.float32), rtol=2e-6, atol=2e-6)
+
+
+def test_embed_and_argmax(cuda, oracle):
+    rng = np.random.default_rng(12)
+    for d in (24, 30):
+        table = rng.standard_normal((50, d)).astype(np.float32)
+        ids = rng.integers(0, 50, size=(3, 7), dtype=np.int64)
+        l = launch_desc(abi.OP_EMBED, abi.F32, [3, 7, d])
+        l.n_inputs = 2
+        l.iparam[0] = 50
+        l.inputs[0].dtype, l.inputs[0].numel = abi.F32, table.size
+        l.inputs[0].stride[0], l.inputs[0].stride[1] = d, 1
+        set_operand(l.inputs[1], abi.I64, [3, 7], [0, 1], is_index=True)
+        set_operand(l.out, abi.F32, [3, 7, d], [0, 1, 2])
+        got, want, _, _ = run_both(cuda, oracle, l, [table, ids], 3 * 7 * d * 4)
+        assert np.array_equal(got, want)
+        assert np.array_equal(got.view(np.float32).reshape(3, 7, d), table[ids])
+    x = rng.integers(0, 4, size=(9, 17)).astype(np.float32)  # many ties: the last maximum wins
+    l = launch_desc(abi.OP_ARGMAX, abi.F32, [9], [17])
+    l.n_inputs = 1
+    set_operand(l.inputs[0], abi.F32, [9, 17], [0, 1])
+    set_operand(l.out, abi.I64, [9], [0], is_index=True)
+    got, want, _, _ = run_both(cuda, oracle, l, [x], 9 * 8)
+    assert np.array_equal(got, want)
+    assert np.array_equal(got.view(np.int64), 16 - np.argmax(x[:, ::-1], axis=1))
+
+
+def test_contraction_exact_generic_strides(cuda, oracle):
+    """A generic `ein` with permuted operands, and a matrix product with ragged edges: bit-exact."""
+    rng = np.random.default_rng(13)
+    # out[b, g, s, h] = sum_m x[b, s, m] * w[m, g, h]   (llama's key projection)
+    B, S, M, G, H = 2, 9, 20, 3, 5
+    x = rng.standard_normal((B, S, M)).astype(np.float32)
+    w = rng.standard_normal((M, G, H)).astype(np.float32)
+    l = launch_desc(abi.OP_CONTRACT, abi.F32, [B, G, S, H], [M])
+    l.n_inputs = 2
+    set_operand(l.inputs[0], abi.F32, [B, S, M], [0, 2, 4])
+    set_operand(l.inputs[1], abi.F32, [M, G, H], [4, 1, 3])
+    set_operand(l.out, abi.F32, [B, G, S, H], [0, 1, 2, 3])
+    got, want, _, _ = run_both(cuda, oracle, l, [x, w], B * G * S * H * 4)
+    assert np.array_equal(got, want)
+    np.testing.assert_allclose(got.view(np.float32).reshape(B, G, S, H), np.einsum("bsm,mgh->bgsh", x, w), rtol=1e-5, atol=1e-5)
+    # an outer product: no summed axis
+    a, b = rng.standard_normal(13).astype(np.float32), rng.standard_normal(6).astype(np.float32)
+    l = launch_desc(abi.OP_CONTRACT, abi.F32, [13, 6], [])
+    l.n_inputs = 2
+    set_operand(l.inputs[0], abi.F32, [13], [0])
+    set_operand(l.inputs[1], abi.F32, [6], [1])
+    set_operand(l.out, abi.F32, [13, 6], [0, 1])
+    got, want, _, _ = run_both(cuda, oracle, l, [a, b], 13 * 6 * 4)
+    assert np.array_equal(got, want)

@@ -1,0 +1,117 @@
+"""The host program over the CPU oracle: launch sequences, realizations, errors.
+No GPU: the executor under the host is the oracle's table of functions."""
+import numpy as np
+import pytest
+
+import models
+from presk_b200 import Host, PreskError, abi
+
+
+def test_llama_tiny_matches_an_independent_numpy_statement(oracle):
+    c = models.LLAMA_TINY
+    p = models.llama_params(c)
+    rng = np.random.default_rng(3)
+    ids = rng.integers(0, c["V"], size=(2, 16), dtype=np.int64)
+    y = rng.integers(0, c["V"], size=(2, 16), dtype=np.int64)
+    h = models.give(Host(oracle.vtable(), "f32").prepare("llama", **c), p)
+    logits = h.call("apply", [ids], (2, 16, c["V"]))
+    want = models.llama_numpy(p, c, ids)
+    np.testing.assert_allclose(logits, want, rtol=0, atol=2e-5 * np.abs(want).max() + 1e-6)
+    loss = h.call("loss", [ids, y], ())
+    np.testing.assert_allclose(loss, models.llama_numpy(p, c, ids, y), rtol=2e-6)
+
+
+def test_llama_launch_list(oracle):
+    """The launches of one call, by the reference's kernel names: prologue, 2 blocks, epilogue."""
+    c = models.LLAMA_TINY
+    h = models.give(Host(oracle.vtable(), "f32").prepare("llama", **c), models.llama_params(c))
+    h.set_logging(True)
+    ids = np.zeros((2, 16), np.int64)
+    h.call("apply", [ids], (2, 16, c["V"]))
+    log = h.launch_log()
+    norm = ["mul", "mean axis model", "fused 2 steps", "fused 2 steps"]
+    rope = ["slice pair: 0..1", "slice pair: 1..2", "cos", "sin", "fused 3 steps", "fused 3 steps", "concat pair"]
+    block = (norm + ["ein[batch, groups, per, seq, hd]"] + rope + ["ein[batch, groups, seq, hd]"] + rope + ["dot"]
+             + ["ein[batch, groups, per, seq, seq2]", "sqrt", "div", "softmax axis seq2 where", "ein[batch, seq, groups, per, hd]", "ein[batch, seq, model]", "add"]
+             + norm + ["dot", "fused 2 steps", "dot", "mul", "dot", "add"])
+    prologue = ["causal_mask seq", "embed", "positions seq", "real", "neg", "positions rot", "real", "log", "fused 4 steps", "ein[seq, rot]"]
+    assert log == prologue + block * c["L"] + norm + ["dot"]
+    assert h.launches() == len(log)
+
+
+def test_mixed_realization_sites(oracle):
+    """A site named in `storage` is stored in its own type; the rest in the default."""
+    c = models.LLAMA_TINY
+    p = models.llama_params(c)
+    ids = np.arange(32, dtype=np.int64).reshape(2, 16) % c["V"]
+    rz = {"default": "bf16", "order": {"kind": "sequential"}, "storage": {"RMSNorm.apply/%3": "f32", "RMSNorm.apply/%7": "f32", "Llama.apply/%11": "f32"},
+          "params": {k: "bf16" for k in p}}
+    h = models.give(Host(oracle.vtable(), rz).prepare("llama", **c), p)
+    logits = h.call("apply", [ids], (2, 16, c["V"]))
+    want = models.llama_numpy(p, c, ids)
+    assert np.abs(logits - want).max() < 0.05 * np.abs(want).max()
+    assert np.any(logits.view(np.uint32) & 0xFFFF)  # the logits site is f32: not every value is a bf16 number
+
+
+def test_int8_weights(oracle):
+    """`quant` paths are stored as int8 with one f32 scale a channel (quant.rs:128-167)."""
+    c = models.LLAMA_TINY
+    p = models.llama_params(c)
+    ids = np.arange(32, dtype=np.int64).reshape(2, 16) % c["V"]
+    q = {k: {"bits": 8, "over": -2} for k in ("blocks.attn.wq", "blocks.attn.wk", "blocks.attn.wv", "blocks.attn.wo", "blocks.ff.gate.w", "blocks.ff.up.w", "blocks.ff.down.w")}
+    h = models.give(Host(oracle.vtable(), {"default": "f32", "quant": q}).prepare("llama", **c), p)
+    logits = h.call("apply", [ids], (2, 16, c["V"]))
+    # against numpy with the weights dequantised by the same rule
+    pq = dict(p)
+    for k in q:
+        w = p[k].astype(np.float64)
+        s = (np.abs(w).max(axis=-2, keepdims=True) / 127.0).astype(np.float32)
+        codes = np.clip(np.rint(w / s.astype(np.float64)), -127, 127)
+        pq[k] = (codes.astype(np.float32) * s).astype(np.float32)
+    want = models.llama_numpy(pq, c, ids)
+    np.testing.assert_allclose(logits, want, rtol=0, atol=3e-5 * np.abs(want).max() + 1e-6)
+
+
+def test_realization_errors(oracle):
+    with pytest.raises(PreskError, match="no type"):
+        Host(oracle.vtable(), "f33")
+    with pytest.raises(PreskError, match="E7005"):
+        Host(oracle.vtable(), {"default": "f32", "order": {"kind": "interleaved", "partials": 4}})
+    with pytest.raises(PreskError, match="E7005"):
+        Host(oracle.vtable(), {"default": "f32", "accum": {"Dense.apply/%3": "i32"}})
+    h = Host(oracle.vtable(), {"default": "f32", "params": {"blocks.attn.wz": "bf16"}})
+    with pytest.raises(PreskError, match="no parameter of Llama"):
+        h.prepare("llama", **models.LLAMA_TINY)
+    h = Host(oracle.vtable(), "f32").prepare("mlp")
+    with pytest.raises(PreskError, match="was not given"):
+        h.call("apply", [np.zeros((4, 784), np.float32)], (4, 10))
+
+
+def test_overflow_guard_stops_the_run(oracle):
+    """Inputs scaled by 2^20 overflow the binary16 store of the `dot` (BASELINE config 3): E7007."""
+    rng = np.random.default_rng(5)
+    n = 64
+    x, w = rng.standard_normal((n, n)).astype(np.float32), rng.standard_normal((n, n)).astype(np.float32)
+    for dtype, scale, overflows in [("f16", 1.0, False), ("f16", 2.0**20, True), ("e8m15", 2.0**20, False), ("bf16", 2.0**20, False)]:
+        h = Host(oracle.vtable(), dtype).prepare("contract_ln")
+        h.set_param("ln.γ", np.ones(n, np.float32))
+        h.set_param("ln.β", np.zeros(n, np.float32))
+        if overflows:
+            with pytest.raises(PreskError, match="E7007"):
+                h.call("apply", [x * scale, w * scale], (n, n))
+        else:
+            out = h.call("apply", [x * scale, w * scale], (n, n))
+            assert np.all(np.isfinite(out))
+
+
+def test_mlp_config1_shapes(oracle):
+    p = models.mlp_params()
+    x, y = models.mlp_inputs(64)
+    h = models.give(Host(oracle.vtable(), "f32").prepare("mlp"), p)
+    h.set_logging(True)
+    loss = h.call("loss", [x, y], ())
+    assert h.launch_log() == ["dot", "add", "relu", "dot", "add", "cross_entropy", "mean"]
+    hid = np.maximum(x.astype(np.float64) @ p["l1.w"], 0)
+    lg = hid @ p["l2.w"]
+    want = (np.log(np.exp(lg - lg.max(-1, keepdims=True)).sum(-1)) + lg.max(-1) - lg[np.arange(64), y]).mean()
+    np.testing.assert_allclose(loss, want, rtol=1e-5)
