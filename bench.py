@@ -1,0 +1,292 @@
+"""bench.py: tokens/s of a Llama-7B-shaped prefill on N B200s (one process a GPU).
+
+A step is one call of the model's `loss` entry (prefill + next-token loss) on one
+batch of synthetic token ids, through the host program of libpresk_cuda.so.
+
+  value   tokens/s over all ranks with the ids already on the device, timed with
+          CUDA events on the executor's stream, the maximum over ranks
+  e2e     the same through psk_host_call with pinned HOST buffers: the host-to-device
+          copy of the ids and labels and the device-to-host read of the loss are
+          inside the timed region of every step
+  roofline  the tensor-core contraction kernel: its floating-point operations over its
+          own time (events around every launch of the timed steps), against the
+          measured cuBLAS bf16 rate of MEASURED_PEAKS.json
+  cpu_baseline  the CPU restatement of the same launches (oracle/, OpenMP over the
+          host's cores) on a bounded sample, rank 0 and N = 1 only
+
+`--impl reference` times that CPU path alone, on the same metric.
+
+The batch axis is sharded over the ranks with no collective on the data path; the
+per-rank losses are summed with one NCCL all-reduce after the timed region.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # BASELINE.json configs[3]: 32 layers, d 4096, 32 heads of 128, SwiGLU 11008, vocab 32000, seq 2048, batch 8 a GPU
+    "llama7b_prefill_b8_t2048": dict(consts=dict(V=32000, D=4096, H=32, G=32, FF=11008, L=32), B=8, T=2048),
+    # a small shape of the same program, for trying the script out
+    "llama_small": dict(consts=dict(V=4096, D=1024, H=8, G=8, FF=2816, L=4), B=4, T=512),
+}
+
+
+def realization(paths):
+    """A solved-style mixed bf16/f32 assignment: bf16 storage, f32 where a sum's result is reused
+    widely (the norms' mean and root, the logits and the loss)."""
+    return {
+        "default": "bf16",
+        "order": {"kind": "device"},
+        "params": {p: "bf16" for p in paths},
+        "storage": {"RMSNorm.apply/%3": "f32", "RMSNorm.apply/%7": "f32", "Llama.apply/%11": "f32", "loss/%5": "f32", "loss/%6": "f32"},
+    }
+
+
+def param_shapes(c):
+    V, D, FF, L, H = c["V"], c["D"], c["FF"], c["L"], c["H"]
+    G = c.get("G", H)
+    HD = D // H
+    return {
+        "tok": ((V, D), 0.02), "head": ((D, V), 0.02), "norm.γ": ((D,), -1.0),
+        "blocks.n1.γ": ((L, D), -1.0), "blocks.n2.γ": ((L, D), -1.0),
+        "blocks.attn.wq": ((L, D, D), 0.02), "blocks.attn.wk": ((L, D, G * HD), 0.02), "blocks.attn.wv": ((L, D, G * HD), 0.02), "blocks.attn.wo": ((L, D, D), 0.02),
+        "blocks.ff.gate.w": ((L, D, FF), 0.02), "blocks.ff.up.w": ((L, D, FF), 0.02), "blocks.ff.down.w": ((L, FF, D), 0.02),
+    }
+
+
+def flops_per_token(c, T):
+    D, FF, L, V = c["D"], c["FF"], c["L"], c["V"]
+    return L * (8 * D * D + 6 * D * FF + 4 * T * D) + 2 * D * V
+
+
+class ClockSampler:
+    """nvidia-smi sampled every 200 ms while the timed region runs."""
+
+    def __init__(self, index):
+        self.index = index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        q = "clocks.sm,clocks.max.sm,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + q, "--format=csv,noheader,nounits", "-lms", "200"], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm = [int(r[0]) for r in self.rows if r and r[0].isdigit()]
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        reasons = set()
+        for r in self.rows:
+            for name, v in zip(["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"], r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": int(statistics.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_prefill_tokens_per_s(consts, T, B, threads):
+    """The CPU restatement on a bounded sample: one and two layers at a short sequence, one
+    batch row; the per-layer time and the rest extrapolate to the whole depth."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib
+    from presk_b200 import Host
+
+    os.environ.setdefault("OMP_NUM_THREADS", str(threads))
+    orc = oracle_lib.load()
+    times = {}
+    Ts, Bs = min(T, 32), 1
+    rng = np.random.default_rng(0)
+    for L in (1, 2):
+        c = dict(consts, L=L)
+        shapes = param_shapes(c)
+        rz = realization(shapes)
+        rz["order"] = {"kind": "sequential"}
+        h = Host(orc.vtable(), rz).prepare("llama", **c)
+        for path, (shape, std) in shapes.items():
+            h.set_param(path, np.ones(shape, np.float32) if std < 0 else (rng.standard_normal(shape, dtype=np.float32) * np.float32(std)))
+        ids = rng.integers(0, c["V"], size=(Bs, Ts), dtype=np.int64)
+        y = rng.integers(0, c["V"], size=(Bs, Ts), dtype=np.int64)
+        t0 = time.perf_counter()
+        h.call("loss", [ids, y], ())
+        times[L] = time.perf_counter() - t0
+        h.close()
+    per_layer = max(times[2] - times[1], 1e-9)
+    rest = max(times[1] - per_layer, 0.0)
+    full = rest + consts["L"] * per_layer
+    sample = f"L=1 and L=2 at B={Bs}, T={Ts} ({times[1]:.2f} s, {times[2]:.2f} s); per layer {per_layer:.2f} s, extrapolated to L={consts['L']}; attention's T-dependent share is that of T={Ts}"
+    return Bs * Ts / full, sample
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="llama7b_prefill_b8_t2048", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    consts, B, T = w["consts"], w["B"], w["T"]
+    rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
+    threads = os.cpu_count() or 1
+    config = {"workload": args.workload, **{k: v for k, v in consts.items()}, "batch_per_gpu": B, "seq_len": T, "global_batch": B * world, "parallelism": f"dp{world}", "realization": "bf16 storage, f32 norm statistics/logits/loss, order device", "l2": "inputs_larger_than_l2 (13.5 GB of weights stream through every step)"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        vals = []
+        sample = ""
+        for _ in range(max(1, min(args.steps, 2))):
+            v, sample = cpu_prefill_tokens_per_s(consts, T, B, threads)
+            vals.append(v)
+        v = statistics.median(vals)
+        print(json.dumps({
+            "impl": "reference", "metric": "tokens/sec Llama-7B-shape prefill", "value": v, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": 1e3 * B * T / v, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 storage, f32 arithmetic", "data": "synthetic",
+            "config": config, "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "note": "the reference's Rust executors cannot be built on this box (no cargo/rustc); this is the C restatement of the same loop nests (oracle/), OpenMP over the host's cores",
+        }))
+        return
+
+    import torch
+    import torch.distributed as dist
+    from presk_b200 import Executor, Host, abi
+
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    ex = Executor(local)
+    shapes = param_shapes(consts)
+    host = Host(ex, realization(shapes)).prepare("llama", **consts)
+    for i, (path, (shape, std)) in enumerate(shapes.items()):
+        host.init_param(path, 1000 + i, std, shape)
+    ex.sync()
+
+    rng = np.random.default_rng(rank)
+    ids_pinned = torch.from_numpy(rng.integers(0, consts["V"], size=(B, T), dtype=np.int64)).pin_memory()
+    y_pinned = torch.from_numpy(rng.integers(0, consts["V"], size=(B, T), dtype=np.int64)).pin_memory()
+    ids_np, y_np = ids_pinned.numpy(), y_pinned.numpy()
+    ids_dev, y_dev = ex.upload(ids_np), ex.upload(y_np)
+    dev_inputs = [(ids_dev, abi.I64, (B, T)), (y_dev, abi.I64, (B, T))]
+    stream = torch.cuda.ExternalStream(ex.stream(), device=torch.device("cuda", local))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        ex.sync()
+        torch.cuda.synchronize()
+
+    def step_device():
+        return host.call_device("loss", dev_inputs)
+
+    for _ in range(max(args.warmup, 3)):
+        step_device()
+    ex.sync()
+    launches_before, kernels_before = ex.counts()
+
+    # ---- value: inputs resident, events on the executor's stream ----
+    sampler = ClockSampler(local)
+    barrier()
+    sampler.start()
+    ex.set_profiling(True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        out_ptr, _, _ = step_device()
+    e1.record(stream)
+    barrier()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1)
+    rows = ex.profile()
+    ex.set_profiling(False)
+    launches_after, kernels_after = ex.counts()
+    loss = float(np.frombuffer(ex.download(out_ptr, 4).tobytes(), dtype=np.float32)[0])
+
+    # ---- e2e: host buffers in, loss out, every step ----
+    for _ in range(2):
+        host.call("loss", [ids_np, y_np], ())
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        host.call("loss", [ids_np, y_np], ())
+    barrier()
+    e2e_s = time.perf_counter() - t0
+
+    t_ms = torch.tensor([ms, e2e_s * 1e3], device="cuda", dtype=torch.float64)
+    loss_t = torch.tensor([loss], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
+        dist.all_reduce(loss_t, op=dist.ReduceOp.SUM)  # the final loss gather: per-shard means, summed
+    ms, e2e_ms = float(t_ms[0]), float(t_ms[1])
+    tokens = B * T * world * args.steps
+    value = tokens / (ms * 1e-3)
+    e2e = tokens / (e2e_ms * 1e-3)
+
+    if rank == 0:
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except OSError:
+            pass
+        tf_peak = peaks.get("bf16_tflops_sustained") or 1400.0
+        hbm_peak = peaks.get("hbm_gbs") or 6650.0
+        peak_kind = "measured (MEASURED_PEAKS.json, sustained cuBLAS bf16)" if peaks else "fallback"
+        by = {}
+        for k, name, kms, fl, bts in rows:
+            d = by.setdefault(k, [0, 0.0, 0.0, 0.0])
+            d[0] += 1; d[1] += kms; d[2] += fl; d[3] += bts
+        total_kernel_ms = sum(d[1] for d in by.values()) or 1.0
+        tc = by.get("k_gemm_tc", [0, 0.0, 0.0, 0.0])
+        achieved = tc[2] / (tc[1] * 1e-3) / 1e12 if tc[1] > 0 else 0.0
+        shares = {k: {"launches": d[0], "ms": round(d[1], 3), "share": round(d[1] / total_kernel_ms, 4), "GB/s": round(d[3] / (d[1] * 1e-3) / 1e9, 1) if d[1] > 0 else None} for k, d in sorted(by.items(), key=lambda kv: -kv[1][1])}
+        out = {
+            "metric": "tokens/sec Llama-7B-shape prefill", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 storage, f32 accumulation", "data": "synthetic",
+            "config": config,
+            "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": int(ids_np.nbytes + y_np.nbytes), "d2h_bytes_per_step": 4},
+            "gpu_launches": int(kernels_after - kernels_before),
+            "clocks": clocks,
+            "roofline": {"bound": "tensor", "kernel": "k_gemm_tc", "achieved": achieved, "peak": tf_peak, "unit": "TFLOP/s", "frac": achieved / tf_peak, "traffic": None, "peak_source": peak_kind,
+                         "model_tflops": flops_per_token(consts, T) * B * T * args.steps / (ms * 1e-3) / 1e12, "hbm_peak_gbs": hbm_peak},
+            "kernel_shares": shares,
+            "loss": float(loss_t[0]) / world,
+            "launches_per_step": int((launches_after - launches_before) / args.steps),
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            try:
+                v, sample = cpu_prefill_tokens_per_s(consts, T, B, threads)
+                out["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample}
+            except Exception as e:  # the baseline is reported, never the product's path
+                out["cpu_baseline"] = {"value": None, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": f"failed: {e}"}
+        print(json.dumps(out))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

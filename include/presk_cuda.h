@@ -201,6 +201,14 @@ void psk_exec_counts(const psk_exec *e, int64_t *launches, int64_t *kernels);
 void psk_exec_set_profiling(psk_exec *e, int on);
 double psk_exec_last_ms(psk_exec *e);
 
+/* While profiling is on every psk_exec_run is bracketed by two events on the
+ * stream. This waits for the stream and returns one line a launch since the
+ * last call: kernel family, the launch's name, milliseconds, its floating-point
+ * operations (contractions) and its algorithmic bytes (each operand once at
+ * its stored width, the reference's Q, presk-kernel/src/cost.rs:92-95),
+ * tab-separated. The text belongs to the executor until the next call. */
+const char *psk_exec_profile(psk_exec *e);
+
 /* The raw CUDA stream the executor launches on (a cudaStream_t), for a
  * caller that times it with its own events. */
 void *psk_exec_stream(psk_exec *e);

@@ -97,6 +97,17 @@ class Executor:
         self.lib.psk_exec_memory(self.handle, C.byref(a), C.byref(b))
         return a.value, b.value
 
+    def set_profiling(self, on=True):
+        self.lib.psk_exec_set_profiling(self.handle, 1 if on else 0)
+
+    def profile(self):
+        """[(kernel family, launch name, ms, flops, bytes)] of the launches since the last call."""
+        rows = []
+        for line in self.lib.psk_exec_profile(self.handle).decode().splitlines():
+            k, n, ms, fl, by = line.split("\t")
+            rows.append((k, n, float(ms), float(fl), float(by)))
+        return rows
+
     def stream(self):
         return self.lib.psk_exec_stream(self.handle)
 

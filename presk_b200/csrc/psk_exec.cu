@@ -51,6 +51,13 @@ struct psk_exec {
     bool profiling = false;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     double last_ms = -1.0;
+    // per-launch records while profiling: two pooled events, what ran, its algorithmic work
+    struct ProfRec { std::string name; const char *kernel; double flops, bytes; cudaEvent_t a, b; };
+    std::vector<ProfRec> prof;
+    std::vector<cudaEvent_t> event_pool;
+    std::string prof_text;
+    const char *last_kernel = "";
+    double last_flops = 0;
     EncodeTiledFn encode = nullptr;
     bool tc_attr_set = false;
 };
@@ -518,6 +525,24 @@ double psk_exec_last_ms(psk_exec *e)
 
 void *psk_exec_stream(psk_exec *e) { return (void *)e->stream; }
 
+const char *psk_exec_profile(psk_exec *e)
+{
+    cudaSetDevice(e->device);
+    cudaStreamSynchronize(e->stream);
+    e->prof_text.clear();
+    char line[512];
+    for (auto &r : e->prof) {
+        float ms = -1.0f;
+        cudaEventElapsedTime(&ms, r.a, r.b);
+        snprintf(line, sizeof line, "%s\t%s\t%.6f\t%.0f\t%.0f\n", r.kernel, r.name.c_str(), ms, r.flops, r.bytes);
+        e->prof_text += line;
+        e->event_pool.push_back(r.a);
+        e->event_pool.push_back(r.b);
+    }
+    e->prof.clear();
+    return e->prof_text.c_str();
+}
+
 int psk_exec_gemm(psk_exec *e, const psk_gemm *g, const void *a, const void *b, void *c)
 {
     cudaSetDevice(e->device);
@@ -566,12 +591,21 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
     L.inner = 1;
     for (int c = 0; c < L.n_inner; ++c) L.inner *= L.dims[L.n_outer + c];
     const bool device_order = l->order == PSK_ORDER_DEVICE;
-    if (e->profiling) cudaEventRecord(e->ev0, e->stream);
+    cudaEvent_t pa = nullptr, pb = nullptr;
+    if (e->profiling) {
+        cudaEventRecord(e->ev0, e->stream);
+        auto take = [&]() { cudaEvent_t ev; if (e->event_pool.empty()) cudaEventCreate(&ev); else { ev = e->event_pool.back(); e->event_pool.pop_back(); } return ev; };
+        pa = take(); pb = take();
+        cudaEventRecord(pa, e->stream);
+    }
+    e->last_kernel = "other";
+    e->last_flops = 0;
     int rc = PSK_OK;
     if (L.total == 0) {
         // an empty result: nothing to store
     } else switch (l->op) {
     case PSK_OP_FUSED: {
+        e->last_kernel = "k_fused";
         if (l->n_steps < 1 || l->n_steps > PSK_MAX_STEPS) { rc = fail(e, PSK_E7001, "fused: a group of no step or of too many"); break; }
         bool vec = L.n_outer >= 1 && l->n_steps <= 8 && L.dims[L.n_outer - 1] % 8 == 0 && vec8_operand(L.out, L.dims, L.n_outer, true);
         for (int i = 0; vec && i < L.n_in; ++i) vec = vec8_operand(L.in[i], L.dims, L.n_outer, false);
@@ -581,6 +615,7 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
         break;
     }
     case PSK_OP_COPY: {
+        e->last_kernel = "k_copy";
         if (L.n_in != 1) { rc = fail(e, PSK_E7001, "copy: one input a launch"); break; }
         bool vec = L.n_outer >= 1 && !L.in[0].is_index && L.dims[L.n_outer - 1] % 8 == 0 && L.in[0].stride[L.n_outer - 1] == 1 && vec8_operand(L.out, L.dims, L.n_outer, true) && vec8_operand(L.in[0], L.dims, L.n_outer, false)
             && (L.in[0].dtype == PSK_BF16 || L.in[0].dtype == PSK_F32 || L.in[0].dtype == PSK_F16) ;
@@ -609,6 +644,8 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
             if (g.n == 1) pg.b_row = g.k;
             std::string keep = e->error;
             rc = launch_tc(e, pg, A.p, B.p, const_cast<void *>(L.out.p), L.ovf);
+            e->last_kernel = "k_gemm_tc";
+            e->last_flops = 2.0 * (double)g.m * (double)g.n * (double)g.k * (double)g.batch;
             if (rc == PSK_E7001) { rc = PSK_OK; e->error = keep; tc_ok = false; } // strides no tensor map takes: the exact kernel
         }
         if (!tc_ok && rc == PSK_OK) {
@@ -625,16 +662,20 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
                 G.b_scales = B.scales; G.b_sj = g.bs_n; G.b_slo = g.bs_lo; G.b_shi = g.bs_hi;
                 G.ovf = L.ovf; G.guarded = L.guarded;
                 dim3 grid((unsigned)((g.n + 63) / 64), (unsigned)((g.m + 63) / 64), (unsigned)g.batch);
-                if (grid.y > 65535 || grid.z > 65535) k_contract_generic<<<grid_for(e, L.total, 256, 8), 256, 0, e->stream>>>(L);
-                else k_gemm_exact<<<grid, 256, 0, e->stream>>>(G);
+                e->last_flops = 2.0 * (double)g.m * (double)g.n * (double)g.k * (double)g.batch;
+                if (grid.y > 65535 || grid.z > 65535) { k_contract_generic<<<grid_for(e, L.total, 256, 8), 256, 0, e->stream>>>(L); e->last_kernel = "k_contract_generic"; }
+                else { k_gemm_exact<<<grid, 256, 0, e->stream>>>(G); e->last_kernel = "k_gemm_exact"; }
             } else {
                 k_contract_generic<<<grid_for(e, L.total, 256, 8), 256, 0, e->stream>>>(L);
+                e->last_kernel = "k_contract_generic";
+                e->last_flops = 2.0 * (double)L.total * (double)L.inner;
             }
             e->kernels += 1;
         }
         break;
     }
     case PSK_OP_REDUCE: {
+        e->last_kernel = "k_reduce";
         if (device_order && L.n_outer == 0) k_reduce_all_tree<<<1, 1024, 0, e->stream>>>(L);
         else if (device_order && L.n_inner == 1 && L.in[0].stride[L.n_outer] == 1 && L.inner >= 64 && (L.inner % 8 != 0 || vec8_operand(L.in[0], L.dims, L.n_outer + 1, false) ))
             k_reduce_rows_tree<<<grid_for(e, L.total * 32, 256, 8), 256, 0, e->stream>>>(L);
@@ -643,6 +684,7 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
         break;
     }
     case PSK_OP_SOFTMAX: {
+        e->last_kernel = "k_softmax";
         if (L.n_inner != 1) { rc = fail(e, PSK_E7001, "softmax: one axis"); break; }
         if (L.masked) {
             auto it = e->causal.find(table[1]);
@@ -668,6 +710,7 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
         break;
     }
     case PSK_OP_XENT: {
+        e->last_kernel = "k_xent";
         if (L.n_inner != 1 || L.n_in != 2) { rc = fail(e, PSK_E7001, "cross_entropy: logits and labels"); break; }
         bool vec_ok = L.in[0].stride[L.n_outer] != 1 || L.inner % 8 != 0 || vec8_operand(L.in[0], L.dims, L.n_outer + 1, false);
         if (device_order && L.inner >= 256 && vec_ok) k_xent_rows_tree<<<(int)std::min<int64_t>(L.total, (int64_t)e->sms * 8), 256, 0, e->stream>>>(L);
@@ -680,6 +723,7 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
         e->kernels += 1;
         break;
     case PSK_OP_EMBED: {
+        e->last_kernel = "k_embed";
         const int last = L.n_outer - 1;
         int64_t work = L.total / (L.dims[last] % 8 == 0 ? 8 : 1);
         k_embed<<<grid_for(e, work, 256, 8), 256, 0, e->stream>>>(L);
@@ -704,7 +748,14 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
         cudaError_t err = cudaGetLastError();
         if (err != cudaSuccess) rc = fail(e, PSK_E10001, std::string(l->name ? l->name : "?") + ": " + cudaGetErrorString(err));
     }
-    if (e->profiling) cudaEventRecord(e->ev1, e->stream);
+    if (e->profiling) {
+        cudaEventRecord(e->ev1, e->stream);
+        cudaEventRecord(pb, e->stream);
+        // algorithmic bytes: every operand once at its stored width (the reference's Q, presk-kernel/src/cost.rs:92-95)
+        double bytes = (double)l->out.numel * (double)elem_bytes(l->out.dtype);
+        for (int i = 0; i < l->n_inputs; ++i) bytes += (double)l->in[i].numel * (double)elem_bytes(l->in[i].dtype);
+        e->prof.push_back({l->name ? l->name : "?", e->last_kernel, e->last_flops, bytes, pa, pb});
+    }
     e->launches += 1;
     return rc;
 }

@@ -1162,7 +1162,13 @@ struct psk_host {
         std::vector<std::string> names;
         if (model == "llama") names = {"batch", "seq"};
         else if (model == "mlp") names = i == 0 ? std::vector<std::string>{"batch", "model"} : std::vector<std::string>{"batch"};
-        else if (model == "layernorm" || model == "rmsnorm") { names.assign(v.rank, ""); if (v.rank) names.back() = "model"; if (v.rank > 1) names[0] = "batch"; }
+        else if (model == "layernorm" || model == "rmsnorm") {
+            // ℝ[..., model: D] with a prefix of named axes
+            static const char *prefix[] = {"batch", "seq", "a2", "a3", "a4", "a5", "a6"};
+            names.assign(v.rank, "");
+            for (int k = 0; k + 1 < v.rank; ++k) names[k] = prefix[k];
+            if (v.rank) names.back() = "model";
+        }
         else if (model == "contract_ln") names = i == 0 ? std::vector<std::string>{"batch", "k"} : std::vector<std::string>{"k", "model"};
         (void)entry;
         Axes a;

@@ -63,6 +63,8 @@ def test_gemm_output_types_round_once(cuda, oracle, in_dtype, out_dtype, tol):
     assert np.abs(got - want).max() <= tol * np.abs(want).max() + 1e-4
     # and the stored value is the nearest number of the format to the f32 sum, for almost every element:
     # round the exact result the same way and count disagreements (a sum's last bit may flip a tie)
+    if out_dtype == abi.F32:
+        return
     raw = oracle.convert(want.astype(np.float32), out_dtype)
     rounded = oracle.widen(raw, out_dtype, want.size).reshape(want.shape)
     assert np.mean(got != rounded) < 0.02
