@@ -20,6 +20,7 @@
 #include "../../include/presk_cuda.h"
 #include "psk_gemm_tc.cuh"
 #include "psk_kernels.cuh"
+#include "psk_hot.cuh"
 
 using namespace psk;
 
@@ -60,6 +61,7 @@ struct psk_exec {
     double last_flops = 0;
     EncodeTiledFn encode = nullptr;
     bool tc_attr_set = false;
+    bool softmax_attr_set = false;
 };
 
 namespace {
@@ -609,7 +611,31 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
         if (l->n_steps < 1 || l->n_steps > PSK_MAX_STEPS) { rc = fail(e, PSK_E7001, "fused: a group of no step or of too many"); break; }
         bool vec = L.n_outer >= 1 && l->n_steps <= 8 && L.dims[L.n_outer - 1] % 8 == 0 && vec8_operand(L.out, L.dims, L.n_outer, true);
         for (int i = 0; vec && i < L.n_in; ++i) vec = vec8_operand(L.in[i], L.dims, L.n_outer, false);
-        if (vec) k_fused_vec8<<<grid_for(e, L.total / 8, 256, 8), 256, 0, e->stream>>>(L);
+        bool hot = vec && L.n_outer <= 2 && L.n_in <= 4 && l->n_steps <= 4 && L.total / 8 < 0xffffffffll;
+        for (int i = 0; hot && i < L.n_in; ++i) hot = L.in[i].dtype != PSK_I8;
+        if (hot) {
+            EwParams E;
+            memset(&E, 0, sizeof E);
+            const int last = L.n_outer - 1;
+            for (int i = 0; i < L.n_in; ++i) {
+                E.in[i] = L.in[i].p; E.dt[i] = L.in[i].dtype; E.cs[i] = (int32_t)L.in[i].stride[last];
+                E.rs[i] = L.n_outer == 2 ? L.in[i].stride[0] : 0;
+            }
+            E.out = const_cast<void *>(L.out.p); E.odt = L.out.dtype; E.kdt = L.kdtype;
+            E.ors = L.n_outer == 2 ? L.out.stride[0] : 0;
+            E.rows = L.n_outer == 2 ? (uint32_t)L.dims[0] : 1u;
+            E.colv = (uint32_t)(L.dims[last] / 8);
+            E.n_in = L.n_in; E.guarded = L.guarded; E.ovf = L.ovf; E.status = L.status;
+            for (int k = 0; k < l->n_steps; ++k) E.steps[k] = l->steps[k];
+            const int g = grid_for(e, (int64_t)E.rows * E.colv, 256, 16);
+            switch (l->n_steps) {
+            case 1: k_ew<1><<<g, 256, 0, e->stream>>>(E); break;
+            case 2: k_ew<2><<<g, 256, 0, e->stream>>>(E); break;
+            case 3: k_ew<3><<<g, 256, 0, e->stream>>>(E); break;
+            default: k_ew<4><<<g, 256, 0, e->stream>>>(E); break;
+            }
+        }
+        else if (vec) k_fused_vec8<<<grid_for(e, L.total / 8, 256, 8), 256, 0, e->stream>>>(L);
         else k_fused<<<grid_for(e, L.total, 256, 8), 256, 0, e->stream>>>(L);
         e->kernels += 1;
         break;
@@ -695,14 +721,17 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
             L.iparam[1] = n;
         }
         const int64_t n = L.inner;
-        bool rows = device_order && L.in[0].stride[L.n_outer] == 1 && L.out.stride[L.n_outer] == 1 && n % 8 == 0 && n <= 4096
+        bool rows = device_order && L.in[0].stride[L.n_outer] == 1 && L.out.stride[L.n_outer] == 1 && n % 8 == 0 && n <= 6144
             && vec8_operand(L.in[0], L.dims, L.n_outer + 1, false) && vec8_operand(L.out, L.dims, L.n_outer + 1, true)
             && (!L.masked || L.iparam[0] == 1 || L.in[1].stride[L.n_outer] == 1);
-        if (rows) {
-            int g = grid_for(e, L.total * 32, 128, 16);
-            if (n <= 1024) k_softmax_rows_tree<32><<<g, 128, 0, e->stream>>>(L);
-            else if (n <= 2048) k_softmax_rows_tree<64><<<g, 128, 0, e->stream>>>(L);
-            else k_softmax_rows_tree<128><<<g, 128, 0, e->stream>>>(L);
+        if (rows && n * 4 * 4 <= 96 * 1024) {
+            if (!e->softmax_attr_set) {
+                CUDA_TRY(e, cudaFuncSetAttribute(k_softmax_rows_smem<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+                e->softmax_attr_set = true;
+            }
+            const size_t smem = (size_t)n * 4 * 4;
+            const int per_sm = (int)std::max<size_t>(1, std::min<size_t>(8, (200 * 1024) / std::max<size_t>(smem, 1)));
+            k_softmax_rows_smem<4><<<grid_for(e, L.total * 32, 128, per_sm), 128, smem, e->stream>>>(L);
         } else {
             k_softmax_seq<<<grid_for(e, L.total, 128, 16), 128, 0, e->stream>>>(L);
         }

@@ -1,0 +1,242 @@
+// The memory-bound launches of a transformer prefill, written for HBM
+// bandwidth: 128-bit accesses, 32-bit index arithmetic, no local memory, many
+// resident warps. They compute exactly what the generic kernels of
+// psk_kernels.cuh compute (the same operations in the same order on each
+// element; row sums as shuffle trees under PSK_ORDER_DEVICE only); the
+// executor picks them when a launch's strides and sizes allow.
+#pragma once
+#include "psk_kernels.cuh"
+
+namespace psk {
+
+// ---------------------------------------------------------------------------
+// Elementwise groups of up to four steps over up to four inputs, seen as a
+// matrix of `rows` x `cols`: each operand walks a row contiguously or holds
+// one value for it (stride 1 or 0 along the columns) and moves from row to row
+// by its own stride (0 for an operand every row shares, such as a gain).
+// ---------------------------------------------------------------------------
+struct EwParams {
+    const void *in[4];
+    void *out;
+    int32_t dt[4], odt, kdt;
+    int32_t cs[4];      // stride along the columns: 0 or 1
+    int64_t rs[4], ors; // stride from row to row, in elements
+    uint32_t rows, colv; // colv = cols / 8
+    int32_t n_in, guarded;
+    psk_step steps[4];
+    uint32_t *ovf, *status;
+};
+
+// Eight consecutive stored elements widened to f32, or one broadcast to all eight.
+PSK_DEV void ew_load8(const void *p, int dt, int64_t off, int cs, int kdt, float (&x)[8], uint32_t *ovf)
+{
+    if (cs == 0) {
+        const float v = edge_round(load_real(p, dt, off), kdt, dt, ovf);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = v;
+        return;
+    }
+    if (dt == PSK_BF16) {
+        const uint4 w = *reinterpret_cast<const uint4 *>((const uint16_t *)p + off);
+        x[0] = bits_f32(w.x << 16); x[1] = bits_f32(w.x & 0xffff0000u);
+        x[2] = bits_f32(w.y << 16); x[3] = bits_f32(w.y & 0xffff0000u);
+        x[4] = bits_f32(w.z << 16); x[5] = bits_f32(w.z & 0xffff0000u);
+        x[6] = bits_f32(w.w << 16); x[7] = bits_f32(w.w & 0xffff0000u);
+    } else if (dt == PSK_F32) {
+        const float4 *q = reinterpret_cast<const float4 *>((const float *)p + off);
+        const float4 a = q[0], b = q[1];
+        x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
+        x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = load_real(p, dt, off + i);
+    }
+    if (dt != kdt) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = edge_round(x[i], kdt, dt, ovf);
+    }
+}
+
+PSK_DEV uint32_t ew_store8(void *p, int dt, int64_t off, const float (&x)[8])
+{
+    if (dt == PSK_BF16) {
+        uint4 w;
+        w.x = (uint32_t)f32_to_bf16(x[0]) | ((uint32_t)f32_to_bf16(x[1]) << 16);
+        w.y = (uint32_t)f32_to_bf16(x[2]) | ((uint32_t)f32_to_bf16(x[3]) << 16);
+        w.z = (uint32_t)f32_to_bf16(x[4]) | ((uint32_t)f32_to_bf16(x[5]) << 16);
+        w.w = (uint32_t)f32_to_bf16(x[6]) | ((uint32_t)f32_to_bf16(x[7]) << 16);
+        *reinterpret_cast<uint4 *>((uint16_t *)p + off) = w;
+        return 0u;
+    }
+    if (dt == PSK_F32) {
+        float4 *q = reinterpret_cast<float4 *>((float *)p + off);
+        q[0] = make_float4(x[0], x[1], x[2], x[3]);
+        q[1] = make_float4(x[4], x[5], x[6], x[7]);
+        return 0u;
+    }
+    uint32_t ovf = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ovf |= store_real(p, dt, off + i, x[i]);
+    return ovf;
+}
+
+// The rarer unary operations, out of line so that the kernel's body stays small
+// and its values stay in registers.
+__device__ __noinline__ float prim_unary_call(int prim, float x, int imm, uint32_t *status) { return prim_unary(prim, x, imm, status); }
+
+template <int NSTEPS>
+__global__ void __launch_bounds__(256, 2) k_ew(const __grid_constant__ EwParams E)
+{
+    uint32_t ovf = 0;
+    const uint32_t total = E.rows * E.colv;
+    for (uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
+        const uint32_t r = idx / E.colv, c = (idx - r * E.colv) * 8u;
+        float iv[4][8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            if (i < E.n_in) ew_load8(E.in[i], E.dt[i], (int64_t)r * E.rs[i] + (int64_t)c * E.cs[i], E.cs[i], E.kdt, iv[i], &ovf);
+        float sv[NSTEPS][8];
+#pragma unroll
+        for (int s = 0; s < NSTEPS; ++s) {
+            const psk_step st = E.steps[s];
+            float a[2][8];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int src = st.src[j];
+#pragma unroll
+                for (int t = 0; t < 8; ++t) {
+                    float v = iv[0][t];
+                    if (src == 1) v = iv[1][t];
+                    if (src == 2) v = iv[2][t];
+                    if (src == 3) v = iv[3][t];
+#pragma unroll
+                    for (int q = 0; q < s; ++q)
+                        if (src == -1 - q) v = sv[q][t];
+                    a[j][t] = v;
+                }
+            }
+            if (st.nargs == 2) {
+                switch (st.prim) {
+                case PSK_ADD:
+#pragma unroll
+                    for (int t = 0; t < 8; ++t) sv[s][t] = __fadd_rn(a[0][t], a[1][t]);
+                    break;
+                case PSK_SUB:
+#pragma unroll
+                    for (int t = 0; t < 8; ++t) sv[s][t] = __fsub_rn(a[0][t], a[1][t]);
+                    break;
+                case PSK_MUL:
+#pragma unroll
+                    for (int t = 0; t < 8; ++t) sv[s][t] = __fmul_rn(a[0][t], a[1][t]);
+                    break;
+                case PSK_DIV:
+#pragma unroll
+                    for (int t = 0; t < 8; ++t) sv[s][t] = __fdiv_rn(a[0][t], a[1][t]);
+                    break;
+                default:
+#pragma unroll
+                    for (int t = 0; t < 8; ++t) sv[s][t] = prim_binary(st.prim, a[0][t], a[1][t]);
+                }
+            } else {
+                switch (st.prim) {
+                case PSK_SIGMOID:
+#pragma unroll
+                    for (int t = 0; t < 8; ++t) sv[s][t] = __fdiv_rn(1.0f, __fadd_rn(1.0f, lm_expf(-a[0][t])));
+                    break;
+                case PSK_SQRT:
+#pragma unroll
+                    for (int t = 0; t < 8; ++t) sv[s][t] = __fsqrt_rn(a[0][t]);
+                    break;
+                default:
+#pragma unroll
+                    for (int t = 0; t < 8; ++t) sv[s][t] = prim_unary_call(st.prim, a[0][t], st.imm, E.status);
+                }
+            }
+        }
+        ovf |= ew_store8(E.out, E.odt, (int64_t)r * E.ors + c, sv[NSTEPS - 1]);
+    }
+    if (E.guarded && ovf) atomicOr(E.ovf, 1u);
+}
+
+// ---------------------------------------------------------------------------
+// Softmax over a contiguous axis under PSK_ORDER_DEVICE: a warp a row, the
+// row held in shared memory between the passes, the exponentials computed
+// once (the bits of computing them twice), the maximum and the sum shuffle
+// trees. With the causal mask only the allowed prefix of a row is read or
+// exponentiated; the refused tail is written as zeros, which is what the
+// reference's selections give it (lower.rs:1368-1419).
+// ---------------------------------------------------------------------------
+template <int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) k_softmax_rows_smem(const __grid_constant__ DevLaunch L)
+{
+    extern __shared__ float s_rows[];
+    uint32_t ovf = 0;
+    const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+    const int64_t n = L.inner;
+    float *row = s_rows + (int64_t)wib * n;
+    const int64_t nwarps = (int64_t)gridDim.x * WARPS;
+    const uint32_t nv = (uint32_t)(n / 8);
+    const bool causal = L.masked && L.iparam[0] == 1;
+    for (int64_t r = (int64_t)blockIdx.x * WARPS + wib; r < L.total; r += nwarps) {
+        const int64_t base = operand_offset(L.in[0], L.dims, 0, L.n_outer, r);
+        const int64_t obase = operand_offset(L.out, L.dims, 0, L.n_outer, r);
+        int64_t mbase = 0, ms = 0;
+        if (L.masked) {
+            mbase = operand_offset(L.in[1], L.dims, 0, L.n_outer, r);
+            ms = L.in[1].stride[L.n_outer];
+            if (causal) mbase = mbase / L.iparam[1];
+        }
+        const uint32_t live = causal ? (uint32_t)min((int64_t)nv, mbase / 8 + 1) : nv;
+        float m = -INFINITY;
+        for (uint32_t v = lane; v < live; v += 32) {
+            float x[8];
+            ew_load8(L.in[0].p, L.in[0].dtype, base + (int64_t)v * 8, 1, L.kdtype, x, &ovf);
+#pragma unroll
+            for (int t = 0; t < 8; ++t) {
+                const bool ok = !L.masked || mask_allows(L, mbase, (int64_t)v * 8 + t, ms);
+                if (ok) m = fmaxf(m, x[t]);
+            }
+            float4 *dst = reinterpret_cast<float4 *>(row + v * 8);
+            dst[0] = make_float4(x[0], x[1], x[2], x[3]);
+            dst[1] = make_float4(x[4], x[5], x[6], x[7]);
+        }
+        m = warp_max(m);
+        float z = 0.0f;
+        for (uint32_t v = lane; v < live; v += 32) {
+            float4 *p = reinterpret_cast<float4 *>(row + v * 8);
+            float4 a = p[0], b = p[1];
+            float x[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int t = 0; t < 8; ++t) {
+                const bool ok = !L.masked || mask_allows(L, mbase, (int64_t)v * 8 + t, ms);
+                float e = 0.0f;
+                if (ok) e = lm_expf(__fsub_rn(x[t], m));
+                x[t] = e;
+                z += e;
+            }
+            p[0] = make_float4(x[0], x[1], x[2], x[3]);
+            p[1] = make_float4(x[4], x[5], x[6], x[7]);
+        }
+        z = warp_sum(z);
+        for (uint32_t v = lane; v < nv; v += 32) {
+            float y[8];
+            if (v < live) {
+                const float4 *p = reinterpret_cast<const float4 *>(row + v * 8);
+                float4 a = p[0], b = p[1];
+                float x[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+                for (int t = 0; t < 8; ++t) {
+                    const bool ok = !L.masked || mask_allows(L, mbase, (int64_t)v * 8 + t, ms);
+                    y[t] = ok ? __fdiv_rn(x[t], z) : 0.0f;
+                }
+            } else {
+#pragma unroll
+                for (int t = 0; t < 8; ++t) y[t] = 0.0f;
+            }
+            ovf |= ew_store8(const_cast<void *>(L.out.p), L.out.dtype, obase + (int64_t)v * 8, y);
+        }
+    }
+    if (L.guarded && ovf) atomicOr(L.ovf, 1u);
+}
+
+} // namespace psk
