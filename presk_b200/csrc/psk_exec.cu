@@ -627,12 +627,25 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
             E.colv = (uint32_t)(L.dims[last] / 8);
             E.n_in = L.n_in; E.guarded = L.guarded; E.ovf = L.ovf; E.status = L.status;
             for (int k = 0; k < l->n_steps; ++k) E.steps[k] = l->steps[k];
-            const int g = grid_for(e, (int64_t)E.rows * E.colv, 256, 16);
-            switch (l->n_steps) {
-            case 1: k_ew<1><<<g, 256, 0, e->stream>>>(E); break;
-            case 2: k_ew<2><<<g, 256, 0, e->stream>>>(E); break;
-            case 3: k_ew<3><<<g, 256, 0, e->stream>>>(E); break;
-            default: k_ew<4><<<g, 256, 0, e->stream>>>(E); break;
+            bool all_bf16 = L.out.dtype == PSK_BF16 && L.kdtype == PSK_BF16;
+            for (int i = 0; i < L.n_in; ++i) all_bf16 = all_bf16 && L.in[i].dtype == PSK_BF16;
+            const int64_t work = (int64_t)E.rows * E.colv;
+            if (all_bf16) {
+                const int g = grid_for(e, (work + 3) / 4, 128, 12);
+                switch (l->n_steps) {
+                case 1: k_ew_bf16<1, 4><<<g, 128, 0, e->stream>>>(E); break;
+                case 2: k_ew_bf16<2, 4><<<g, 128, 0, e->stream>>>(E); break;
+                case 3: k_ew_bf16<3, 4><<<g, 128, 0, e->stream>>>(E); break;
+                default: k_ew_bf16<4, 4><<<g, 128, 0, e->stream>>>(E); break;
+                }
+            } else {
+                const int g = grid_for(e, work, 256, 16);
+                switch (l->n_steps) {
+                case 1: k_ew<1><<<g, 256, 0, e->stream>>>(E); break;
+                case 2: k_ew<2><<<g, 256, 0, e->stream>>>(E); break;
+                case 3: k_ew<3><<<g, 256, 0, e->stream>>>(E); break;
+                default: k_ew<4><<<g, 256, 0, e->stream>>>(E); break;
+                }
             }
         }
         else if (vec) k_fused_vec8<<<grid_for(e, L.total / 8, 256, 8), 256, 0, e->stream>>>(L);

@@ -158,6 +158,116 @@ __global__ void __launch_bounds__(256, 2) k_ew(const __grid_constant__ EwParams 
     if (E.guarded && ovf) atomicOr(E.ovf, 1u);
 }
 
+// The same for the case that matters in a bf16 realization: every operand and
+// the result stored as bf16, the kernel's type bf16. Each thread takes UNR
+// vectors of eight elements a round and issues all of their loads before it
+// computes on any, so that enough bytes are in flight to fill the memory
+// system at a modest number of resident warps.
+template <int NSTEPS, int UNR>
+__global__ void __launch_bounds__(128, 3) k_ew_bf16(const __grid_constant__ EwParams E)
+{
+    const uint32_t total = E.rows * E.colv;
+    const uint32_t stride = gridDim.x * blockDim.x;
+    for (uint32_t idx0 = blockIdx.x * blockDim.x + threadIdx.x; idx0 < total; idx0 += stride * UNR) {
+        uint4 raw[UNR][4];
+        uint32_t rr[UNR], cc[UNR];
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+            const uint32_t idx = idx0 + u * stride;
+            rr[u] = idx / E.colv;
+            cc[u] = (idx - rr[u] * E.colv) * 8u;
+            if (idx < total) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    if (i < E.n_in) {
+                        const uint16_t *p = (const uint16_t *)E.in[i] + (int64_t)rr[u] * E.rs[i];
+                        if (E.cs[i]) raw[u][i] = *reinterpret_cast<const uint4 *>(p + cc[u]);
+                        else raw[u][i].x = *p;
+                    }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+            if (idx0 + u * stride >= total) break;
+            float iv[4][8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                if (i < E.n_in) {
+                    if (E.cs[i]) {
+                        const uint4 w = raw[u][i];
+                        iv[i][0] = bits_f32(w.x << 16); iv[i][1] = bits_f32(w.x & 0xffff0000u);
+                        iv[i][2] = bits_f32(w.y << 16); iv[i][3] = bits_f32(w.y & 0xffff0000u);
+                        iv[i][4] = bits_f32(w.z << 16); iv[i][5] = bits_f32(w.z & 0xffff0000u);
+                        iv[i][6] = bits_f32(w.w << 16); iv[i][7] = bits_f32(w.w & 0xffff0000u);
+                    } else {
+                        const float v = bits_f32(raw[u][i].x << 16);
+#pragma unroll
+                        for (int t = 0; t < 8; ++t) iv[i][t] = v;
+                    }
+                }
+            float sv[NSTEPS][8];
+#pragma unroll
+            for (int s = 0; s < NSTEPS; ++s) {
+                const psk_step st = E.steps[s];
+                float a[2][8];
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int src = st.src[j];
+#pragma unroll
+                    for (int t = 0; t < 8; ++t) {
+                        float v = iv[0][t];
+                        if (src == 1) v = iv[1][t];
+                        if (src == 2) v = iv[2][t];
+                        if (src == 3) v = iv[3][t];
+#pragma unroll
+                        for (int q = 0; q < s; ++q)
+                            if (src == -1 - q) v = sv[q][t];
+                        a[j][t] = v;
+                    }
+                }
+                if (st.nargs == 2) {
+                    switch (st.prim) {
+                    case PSK_ADD:
+#pragma unroll
+                        for (int t = 0; t < 8; ++t) sv[s][t] = __fadd_rn(a[0][t], a[1][t]);
+                        break;
+                    case PSK_SUB:
+#pragma unroll
+                        for (int t = 0; t < 8; ++t) sv[s][t] = __fsub_rn(a[0][t], a[1][t]);
+                        break;
+                    case PSK_MUL:
+#pragma unroll
+                        for (int t = 0; t < 8; ++t) sv[s][t] = __fmul_rn(a[0][t], a[1][t]);
+                        break;
+                    case PSK_DIV:
+#pragma unroll
+                        for (int t = 0; t < 8; ++t) sv[s][t] = __fdiv_rn(a[0][t], a[1][t]);
+                        break;
+                    default:
+#pragma unroll
+                        for (int t = 0; t < 8; ++t) sv[s][t] = prim_binary(st.prim, a[0][t], a[1][t]);
+                    }
+                } else {
+                    switch (st.prim) {
+                    case PSK_SIGMOID:
+#pragma unroll
+                        for (int t = 0; t < 8; ++t) sv[s][t] = __fdiv_rn(1.0f, __fadd_rn(1.0f, lm_expf(-a[0][t])));
+                        break;
+                    case PSK_SQRT:
+#pragma unroll
+                        for (int t = 0; t < 8; ++t) sv[s][t] = __fsqrt_rn(a[0][t]);
+                        break;
+                    default:
+#pragma unroll
+                        for (int t = 0; t < 8; ++t) sv[s][t] = prim_unary_call(st.prim, a[0][t], st.imm, E.status);
+                    }
+                }
+            }
+            ew_store8(E.out, PSK_BF16, (int64_t)rr[u] * E.ors + cc[u], sv[NSTEPS - 1]);
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------
 // Softmax over a contiguous axis under PSK_ORDER_DEVICE: a warp a row, the
 // row held in shared memory between the passes, the exponentials computed
@@ -188,6 +298,33 @@ __global__ void __launch_bounds__(WARPS * 32) k_softmax_rows_smem(const __grid_c
         }
         const uint32_t live = causal ? (uint32_t)min((int64_t)nv, mbase / 8 + 1) : nv;
         float m = -INFINITY;
+        if (L.in[0].dtype == PSK_BF16 && L.kdtype == PSK_BF16 && nv <= 256) {
+            // all of the row's loads first, then the arithmetic
+            uint4 raw[8];
+            const uint16_t *src = (const uint16_t *)L.in[0].p + base;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const uint32_t v = lane + 32u * j;
+                if (v < live) raw[j] = *reinterpret_cast<const uint4 *>(src + (int64_t)v * 8);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const uint32_t v = lane + 32u * j;
+                if (v < live) {
+                    const uint4 w = raw[j];
+                    float x[8] = {bits_f32(w.x << 16), bits_f32(w.x & 0xffff0000u), bits_f32(w.y << 16), bits_f32(w.y & 0xffff0000u),
+                                  bits_f32(w.z << 16), bits_f32(w.z & 0xffff0000u), bits_f32(w.w << 16), bits_f32(w.w & 0xffff0000u)};
+#pragma unroll
+                    for (int t = 0; t < 8; ++t) {
+                        const bool ok = !L.masked || mask_allows(L, mbase, (int64_t)v * 8 + t, ms);
+                        if (ok) m = fmaxf(m, x[t]);
+                    }
+                    float4 *dst = reinterpret_cast<float4 *>(row + v * 8);
+                    dst[0] = make_float4(x[0], x[1], x[2], x[3]);
+                    dst[1] = make_float4(x[4], x[5], x[6], x[7]);
+                }
+            }
+        } else
         for (uint32_t v = lane; v < live; v += 32) {
             float x[8];
             ew_load8(L.in[0].p, L.in[0].dtype, base + (int64_t)v * 8, 1, L.kdtype, x, &ovf);
