@@ -139,15 +139,92 @@ def cpu_prefill_tokens_per_s(consts, T, B, threads):
     return Bs * Ts / full, sample
 
 
+def microbench(args):
+    """One kernel alone on synthetic operands, for tuning and for profiler captures:
+    `--micro gemm --shape M,N,K[,batch[,b_n_major]]`, `--micro softmax --shape rows,n`,
+    `--micro ew --shape rows,cols`. Prints one JSON line (not the benchmark's)."""
+    import torch
+    from presk_b200 import Executor, abi, launch_desc
+
+    ex = Executor(0)
+    stream = torch.cuda.ExternalStream(ex.stream())
+    dims = [int(x) for x in args.shape.split(",")]
+    rng = np.random.default_rng(0)
+
+    def bf16(shape):
+        a = rng.standard_normal(shape).astype(np.float32)
+        return (a.view(np.uint32) >> 16).astype(np.uint16)
+
+    def timed(fn, reps):
+        for _ in range(3):
+            fn()
+        ex.sync()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(reps):
+            fn()
+        e1.record(stream)
+        ex.sync()
+        return e0.elapsed_time(e1) / reps
+
+    if args.micro == "gemm":
+        m, n, k = dims[:3]
+        batch = dims[3] if len(dims) > 3 else 1
+        bnm = dims[4] if len(dims) > 4 else 0
+        a, b = ex.upload(bf16((batch, m, k))), ex.upload(bf16((batch, n, k)))
+        c = ex.alloc(batch * m * n * 2)
+        g = abi.Gemm()
+        g.in_dtype, g.out_dtype, g.b_n_major = abi.BF16, abi.BF16, bnm
+        g.m, g.n, g.k, g.batch, g.batch_lo = m, n, k, batch, batch
+        g.a_row, g.a_lo, g.a_hi = k, m * k, m * k * batch
+        g.b_row, g.b_lo, g.b_hi = (n if bnm else k), n * k, n * k * batch
+        g.c_row_lo_count, g.c_row_lo, g.c_col_lo_count = m, n, n
+        g.c_lo, g.c_hi = m * n, m * n * batch
+        ms = timed(lambda: ex.gemm(g, a, b, c), args.steps)
+        fl = 2.0 * m * n * k * batch
+        print(json.dumps({"micro": "gemm", "shape": dims, "ms": ms, "TFLOP/s": fl / ms / 1e9, "GB/s": (batch * (m * k + n * k + m * n) * 2) / ms / 1e6}))
+    elif args.micro in ("softmax", "ew"):
+        rows, n = dims[:2]
+        x = ex.upload(bf16((rows, n)))
+        out = ex.alloc(rows * n * 2)
+        if args.micro == "softmax":
+            t = n  # rows are (batch·heads, seq): the causal mask is [n, n]
+            lm = launch_desc(abi.OP_IOTA, abi.F32, [t, t])
+            lm.kind = abi.IOTA_CAUSAL
+            lm.out.dtype, lm.out.is_index, lm.out.stride[0], lm.out.stride[1] = abi.I64, 1, t, 1
+            mask = ex.alloc(t * t * 8)
+            ex.run(lm, [mask])
+            l = launch_desc(abi.OP_SOFTMAX, abi.BF16, [rows // t, t], [n], order=abi.ORDER_DEVICE)
+            l.n_inputs, l.masked = 2, 1
+            for o in (l.inputs[0], l.out):
+                o.dtype, o.stride[0], o.stride[1], o.stride[2], o.numel = abi.BF16, t * n, n, 1, rows * n
+            l.inputs[1].dtype, l.inputs[1].is_index, l.inputs[1].stride[1], l.inputs[1].stride[2], l.inputs[1].numel = abi.I64, 1, n, 1, t * t
+            ms = timed(lambda: ex.run(l, [x, mask, out]), args.steps)
+        else:
+            l = launch_desc(abi.OP_FUSED, abi.BF16, [rows, n], order=abi.ORDER_DEVICE)
+            l.n_inputs, l.n_steps = 2, 1
+            l.steps[0].prim, l.steps[0].nargs, l.steps[0].src[0], l.steps[0].src[1] = abi.ADD, 2, 0, 1
+            for o in (l.inputs[0], l.inputs[1], l.out):
+                o.dtype, o.stride[0], o.stride[1], o.numel = abi.BF16, n, 1, rows * n
+            ms = timed(lambda: ex.run(l, [x, x, out]), args.steps)
+        traffic = rows * n * 2 * (2 if args.micro == "softmax" else 3)
+        print(json.dumps({"micro": args.micro, "shape": dims, "ms": ms, "GB/s": traffic / ms / 1e6}))
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--micro", default=None, choices=["gemm", "softmax", "ew"])
+    ap.add_argument("--shape", default="8192,8192,8192")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="llama7b_prefill_b8_t2048", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--dump-profile", default=None, help="write the per-launch-name times of the timed steps to this file")
     args = ap.parse_args()
+    if args.micro:
+        return microbench(args)
     w = WORKLOADS[args.workload]
     consts, B, T = w["consts"], w["B"], w["T"]
     rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
@@ -260,6 +337,15 @@ def main():
             d = by.setdefault(k, [0, 0.0, 0.0, 0.0])
             d[0] += 1; d[1] += kms; d[2] += fl; d[3] += bts
         total_kernel_ms = sum(d[1] for d in by.values()) or 1.0
+        if args.dump_profile:
+            names = {}
+            for k, name, kms, fl, bts in rows:
+                d = names.setdefault(k + " | " + name, [0, 0.0, 0.0, 0.0])
+                d[0] += 1; d[1] += kms; d[2] += fl; d[3] += bts
+            with open(args.dump_profile, "w") as f:
+                f.write("kernel | launch name\tlaunches\ttotal ms\tshare\tms/launch\tGB/s (algorithmic)\tTFLOP/s\n")
+                for key, d in sorted(names.items(), key=lambda kv: -kv[1][1]):
+                    f.write(f"{key}\t{d[0]}\t{d[1]:.3f}\t{d[1] / total_kernel_ms:.4f}\t{d[1] / d[0]:.4f}\t{d[3] / (d[1] * 1e-3) / 1e9:.1f}\t{d[2] / (d[1] * 1e-3) / 1e12:.1f}\n")
         tc = by.get("k_gemm_tc", [0, 0.0, 0.0, 0.0])
         achieved = tc[2] / (tc[1] * 1e-3) / 1e12 if tc[1] > 0 else 0.0
         shares = {k: {"launches": d[0], "ms": round(d[1], 3), "share": round(d[1] / total_kernel_ms, 4), "GB/s": round(d[3] / (d[1] * 1e-3) / 1e9, 1) if d[1] > 0 else None} for k, d in sorted(by.items(), key=lambda kv: -kv[1][1])}

@@ -194,8 +194,9 @@ def test_softmax(cuda, oracle, rows, n, masked, order, dtype):
     else:
         g = oracle.widen(got, dtype, x.size)
         w = oracle.widen(want, dtype, x.size)
-        tol = 2e-6 if dtype == abi.F32 else 2.0**-8
-        assert np.abs(g - w).max() <= tol
+        # the row's sum is a tree, not a chain: its last bits differ, by a relative 2048·2^-24 at the very most
+        tol = 3e-5 if dtype == abi.F32 else 2.0**-8
+        assert np.abs(g - w).max() <= tol * max(float(w.max()), 1e-3)
 
 
 @pytest.mark.parametrize("order", [abi.ORDER_SEQUENTIAL, abi.ORDER_DEVICE])
