@@ -309,7 +309,7 @@ int launch_tc(psk_exec *e, const psk_gemm &g, const void *a, const void *b, void
     P.c_lo = g.c_lo; P.c_hi = g.c_hi;
     P.c = c; P.out_dtype = g.out_dtype; P.in_f16 = f16; P.b_n_major = g.b_n_major; P.guarded = g.guarded;
     const int64_t va = g.out_dtype == PSK_F32 ? 4 : 8; // elements in 16 bytes
-    P.vec_ok = aligned16(c) && g.c_row_lo % va == 0 && g.c_row_hi % va == 0 && g.c_col_hi % va == 0 && g.c_lo % va == 0 && g.c_hi % va == 0 && g.c_col_lo_count % 32 == 0 && g.out_dtype != PSK_E8M15;
+    P.vec_ok = aligned16(c) && g.c_row_lo % va == 0 && g.c_row_hi % va == 0 && g.c_col_hi % va == 0 && g.c_lo % va == 0 && g.c_hi % va == 0 && g.c_col_lo_count % (g.out_dtype == PSK_F32 ? 32 : 64) == 0 && g.n % va == 0 && g.out_dtype != PSK_E8M15;
     P.scale = g.scale; P.scale_on = g.scale_on;
     P.ovf = flag; P.status = e->status;
     if (!e->tc_attr_set) {

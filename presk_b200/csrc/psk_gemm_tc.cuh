@@ -165,6 +165,20 @@ PSK_DEV void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
         : "memory");
 }
 
+// Where tile `r` of a batch lies. Tiles are handed out in panels of PANEL
+// tile-columns, down every tile-row of a panel before the next panel: the
+// CTAs running at one time then share a few columns of B and a band of rows of
+// A that together fit the L2, instead of sweeping all of B for a few rows of A.
+constexpr int PANEL = 8;
+PSK_DEV void tile_of(int64_t r, int64_t tiles_m, int64_t tiles_n, int64_t &mt, int64_t &nt)
+{
+    const int64_t per_panel = (int64_t)PANEL * tiles_m;
+    const int64_t panel = r / per_panel, in_panel = r - panel * per_panel;
+    const int64_t width = tiles_n - panel * PANEL < PANEL ? tiles_n - panel * PANEL : PANEL;
+    mt = in_panel / width;
+    nt = panel * PANEL + (in_panel - mt * width);
+}
+
 template <int BN>
 struct Smem {
     static constexpr int A_BYTES = BM * BK * 2;
@@ -172,7 +186,8 @@ struct Smem {
     static constexpr int STAGES = (BN == 256) ? 4 : 6;
     static constexpr int TILE_BYTES = STAGES * (A_BYTES + B_BYTES);
     static constexpr int BAR_BYTES = 256;
-    static constexpr int TOTAL = TILE_BYTES + BAR_BYTES + 1024; // slack to align the base to 1024
+    static constexpr int STAGE_OUT = 4 * 32 * 128; // the epilogue's staging: 32 rows of 128 bytes a warp
+    static constexpr int TOTAL = TILE_BYTES + BAR_BYTES + STAGE_OUT + 1024; // slack to align the base to 1024
 };
 
 // One element of the accumulator on its way to memory: the optional fused
@@ -227,7 +242,9 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
             bool ok = true;
             for (int64_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 const int64_t b = t / tiles_per_batch, r = t % tiles_per_batch;
-                const int m0 = (int)(r / P.tiles_n) * BM, n0 = (int)(r % P.tiles_n) * BN;
+                int64_t mt, nt;
+                tile_of(r, P.tiles_m, P.tiles_n, mt, nt);
+                const int m0 = (int)mt * BM, n0 = (int)nt * BN;
                 const int blo = (int)(b % P.batch_lo), bhi = (int)(b / P.batch_lo);
                 for (int kb = 0; kb < num_kb; ++kb) {
                     ok = mbar_wait(empty0 + 8 * stage, phase ^ 1u, abort_flag, P.status, 1u);
@@ -280,63 +297,99 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
         const int quad = warp & 3; // the tensor-memory lanes this warp may read: 32·quad ..
         uint32_t acc = 0, acc_phase = 0, ovf = 0;
         bool ok = true;
+        // this warp's staging tile: 32 rows of 128 bytes, 16-byte units swizzled by the row
+        uint4 *stage_out = reinterpret_cast<uint4 *>(smem + S::TILE_BYTES + S::BAR_BYTES) + quad * 32 * 8;
+        const bool staged = P.vec_ok && (P.out_dtype == PSK_BF16 || P.out_dtype == PSK_F16 || P.out_dtype == PSK_F32);
+        const int group_cols = P.out_dtype == PSK_F32 ? 32 : 64; // columns in 128 bytes
         for (int64_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
             const int64_t b = t / tiles_per_batch, r = t % tiles_per_batch;
-            const int64_t m0 = (r / P.tiles_n) * BM, n0 = (r % P.tiles_n) * BN;
+            int64_t mt, nt;
+            tile_of(r, P.tiles_m, P.tiles_n, mt, nt);
+            const int64_t m0 = mt * BM, n0 = nt * BN;
             const int64_t blo = b % P.batch_lo, bhi = b / P.batch_lo;
             ok = mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, P.status, 4u);
             ok = __all_sync(0xffffffffu, ok); // the loads below want the whole warp
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int64_t row = m0 + quad * 32 + lane;
-            const int64_t row_off = blo * P.c_lo + bhi * P.c_hi + (row / P.c_row_lo_count) * P.c_row_hi + (row % P.c_row_lo_count) * P.c_row_lo;
+            const int64_t row0 = m0 + quad * 32;
+            const int64_t boff = blo * P.c_lo + bhi * P.c_hi;
+            const int64_t row = row0 + lane;
+            const int64_t row_off = boff + (row / P.c_row_lo_count) * P.c_row_hi + (row % P.c_row_lo_count) * P.c_row_lo;
+            const uint32_t tbase = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
+            if (staged) {
+                // 128 bytes of every row at a time: through shared memory, so that a store
+                // instruction writes whole 128-byte lines (8 lanes a row, 4 rows an instruction)
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                uint32_t v[32];
-                tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN + c0, v);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                const int64_t col = n0 + c0;
-                if (row < P.m && col < P.n) {
-                    const int64_t off = row_off + (col / P.c_col_lo_count) * P.c_col_hi + (col % P.c_col_lo_count);
-                    float x[32];
+                for (int c0 = 0; c0 < BN; c0 += group_cols) {
+                    const int64_t col = n0 + c0;
+                    if (P.out_dtype == PSK_F32) {
+                        uint32_t v[32];
+                        tmem_ld32(tbase + c0, v);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) x[i] = __uint_as_float(v[i]);
-                    if (P.scale_on) {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) x[i] = __fmul_rn(x[i], P.scale);
-                    }
-                    const bool full = col + 32 <= P.n && P.vec_ok;
-                    if (full && P.out_dtype == PSK_BF16) {
-                        uint4 *dst = reinterpret_cast<uint4 *>((uint16_t *)P.c + off);
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            uint32_t u[4];
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) u[i] = (uint32_t)f32_to_bf16(x[q * 8 + 2 * i]) | ((uint32_t)f32_to_bf16(x[q * 8 + 2 * i + 1]) << 16);
-                            dst[q] = make_uint4(u[0], u[1], u[2], u[3]);
+                        for (int q = 0; q < 8; ++q) {
+                            float x0 = __uint_as_float(v[4 * q]), x1 = __uint_as_float(v[4 * q + 1]), x2 = __uint_as_float(v[4 * q + 2]), x3 = __uint_as_float(v[4 * q + 3]);
+                            if (P.scale_on) { x0 = __fmul_rn(x0, P.scale); x1 = __fmul_rn(x1, P.scale); x2 = __fmul_rn(x2, P.scale); x3 = __fmul_rn(x3, P.scale); }
+                            stage_out[lane * 8 + (q ^ (lane & 7))] = make_uint4(__float_as_uint(x0), __float_as_uint(x1), __float_as_uint(x2), __float_as_uint(x3));
                         }
-                    } else if (full && P.out_dtype == PSK_F16) {
-                        uint4 *dst = reinterpret_cast<uint4 *>((uint16_t *)P.c + off);
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            uint32_t u[4];
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                ovf |= overflows(x[q * 8 + 2 * i], kF16Overflow) | overflows(x[q * 8 + 2 * i + 1], kF16Overflow);
-                                u[i] = (uint32_t)f32_to_f16(x[q * 8 + 2 * i]) | ((uint32_t)f32_to_f16(x[q * 8 + 2 * i + 1]) << 16);
-                            }
-                            dst[q] = make_uint4(u[0], u[1], u[2], u[3]);
-                        }
-                    } else if (full && P.out_dtype == PSK_F32) {
-                        float4 *dst = reinterpret_cast<float4 *>((float *)P.c + off);
-#pragma unroll
-                        for (int q = 0; q < 8; ++q) dst[q] = make_float4(x[4 * q], x[4 * q + 1], x[4 * q + 2], x[4 * q + 3]);
                     } else {
+#pragma unroll
+                        for (int half = 0; half < 2; ++half) {
+                            uint32_t v[32];
+                            tmem_ld32(tbase + c0 + half * 32, v);
+                            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                uint32_t u[4];
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    float x0 = __uint_as_float(v[q * 8 + 2 * i]), x1 = __uint_as_float(v[q * 8 + 2 * i + 1]);
+                                    if (P.scale_on) { x0 = __fmul_rn(x0, P.scale); x1 = __fmul_rn(x1, P.scale); }
+                                    if (P.out_dtype == PSK_BF16) {
+                                        u[i] = (uint32_t)f32_to_bf16(x0) | ((uint32_t)f32_to_bf16(x1) << 16);
+                                    } else {
+                                        ovf |= overflows(x0, kF16Overflow) | overflows(x1, kF16Overflow);
+                                        u[i] = (uint32_t)f32_to_f16(x0) | ((uint32_t)f32_to_f16(x1) << 16);
+                                    }
+                                }
+                                stage_out[lane * 8 + ((half * 4 + q) ^ (lane & 7))] = make_uint4(u[0], u[1], u[2], u[3]);
+                            }
+                        }
+                    }
+                    __syncwarp();
+                    if (col < P.n) {
+                        const int64_t col_off = (col / P.c_col_lo_count) * P.c_col_hi + (col % P.c_col_lo_count);
+                        const int unit = lane & 7;
+                        const int units_live = (int)((P.n - col) >= group_cols ? 8 : ((P.n - col) * (P.out_dtype == PSK_F32 ? 4 : 2)) / 16);
+#pragma unroll
+                        for (int it = 0; it < 8; ++it) {
+                            const int rr = it * 4 + (lane >> 3);
+                            const int64_t grow = row0 + rr;
+                            if (grow < P.m && unit < units_live) {
+                                const int64_t off = boff + (grow / P.c_row_lo_count) * P.c_row_hi + (grow % P.c_row_lo_count) * P.c_row_lo + col_off;
+                                const uint4 w = stage_out[rr * 8 + (unit ^ (rr & 7))];
+                                uint8_t *dst = (uint8_t *)P.c + off * (P.out_dtype == PSK_F32 ? 4 : 2) + unit * 16;
+                                *reinterpret_cast<uint4 *>(dst) = w;
+                            }
+                        }
+                    }
+                    __syncwarp();
+                }
+            } else {
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(tbase + c0, v);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    const int64_t col = n0 + c0;
+                    if (row < P.m && col < P.n) {
                         for (int i = 0; i < 32; ++i)
                             if (col + i < P.n) {
                                 const int64_t cc = col + i;
                                 const int64_t o = row_off + (cc / P.c_col_lo_count) * P.c_col_hi + (cc % P.c_col_lo_count);
-                                ovf |= store_real(P.c, P.out_dtype, o, x[i]);
+                                float x = __uint_as_float(v[i]);
+                                if (P.scale_on) x = __fmul_rn(x, P.scale);
+                                ovf |= store_real(P.c, P.out_dtype, o, x);
                             }
                     }
                 }
