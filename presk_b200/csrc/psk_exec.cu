@@ -154,6 +154,36 @@ void coalesce_outer(DevLaunch &L)
 
 bool aligned16(const void *p) { return ((uintptr_t)p & 15u) == 0; }
 
+// Which compile-time program a group's steps are, or -1 (psk_hot.cuh `EwProg`).
+int match_program(const psk_launch *l)
+{
+    auto is = [&](int k, int prim, int nargs, int a, int b) {
+        const psk_step &s = l->steps[k];
+        return s.prim == prim && s.nargs == nargs && s.src[0] == a && (nargs == 1 || s.src[1] == b);
+    };
+    if (l->n_steps == 1 && l->n_inputs == 2) {
+        if (is(0, PSK_ADD, 2, 0, 1)) return EW_ADD;
+        if (is(0, PSK_SUB, 2, 0, 1)) return EW_SUB;
+        if (is(0, PSK_MUL, 2, 0, 1)) return EW_MUL;
+        if (is(0, PSK_DIV, 2, 0, 1)) return EW_DIV;
+    }
+    if (l->n_steps == 2 && l->n_inputs == 3 && is(0, PSK_DIV, 2, 0, 1) && is(1, PSK_MUL, 2, -1, 2)) return EW_DIV_MUL;
+    if (l->n_steps == 2 && l->n_inputs == 1 && is(0, PSK_SIGMOID, 1, 0, 0) && is(1, PSK_MUL, 2, 0, -1)) return EW_SILU;
+    if (l->n_steps == 3 && l->n_inputs == 4 && is(0, PSK_MUL, 2, 0, 1) && is(1, PSK_MUL, 2, 2, 3)) {
+        if (is(2, PSK_SUB, 2, -1, -2)) return EW_MUL_MUL_SUB;
+        if (is(2, PSK_ADD, 2, -1, -2)) return EW_MUL_MUL_ADD;
+    }
+    return -1;
+}
+
+template <int PROG>
+void launch_prog(psk_exec *e, const EwParams &E)
+{
+    const int64_t work = (int64_t)E.rows * E.colv;
+    const int g = grid_for(e, (work + 3) / 4, 256, 8);
+    k_ew_prog<PROG, 4><<<g, 256, 0, e->stream>>>(E);
+}
+
 // Whether the operand can be read eight last-axis elements at a time.
 bool vec8_operand(const DevOperand &o, const int64_t *dims, int n_outer, bool is_out)
 {
@@ -630,7 +660,19 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
             bool all_bf16 = L.out.dtype == PSK_BF16 && L.kdtype == PSK_BF16;
             for (int i = 0; i < L.n_in; ++i) all_bf16 = all_bf16 && L.in[i].dtype == PSK_BF16;
             const int64_t work = (int64_t)E.rows * E.colv;
-            if (all_bf16) {
+            const int prog = all_bf16 ? match_program(l) : -1;
+            if (prog >= 0) {
+                switch (prog) {
+                case EW_ADD: launch_prog<EW_ADD>(e, E); break;
+                case EW_SUB: launch_prog<EW_SUB>(e, E); break;
+                case EW_MUL: launch_prog<EW_MUL>(e, E); break;
+                case EW_DIV: launch_prog<EW_DIV>(e, E); break;
+                case EW_DIV_MUL: launch_prog<EW_DIV_MUL>(e, E); break;
+                case EW_SILU: launch_prog<EW_SILU>(e, E); break;
+                case EW_MUL_MUL_SUB: launch_prog<EW_MUL_MUL_SUB>(e, E); break;
+                default: launch_prog<EW_MUL_MUL_ADD>(e, E); break;
+                }
+            } else if (all_bf16) {
                 const int g = grid_for(e, (work + 3) / 4, 128, 12);
                 switch (l->n_steps) {
                 case 1: k_ew_bf16<1, 4><<<g, 128, 0, e->stream>>>(E); break;

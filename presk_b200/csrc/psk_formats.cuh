@@ -30,6 +30,31 @@ PSK_DEV uint16_t f32_to_bf16(float x)
     return (uint16_t)((b + 0x7fffu + ((b >> 16) & 1u)) >> 16);
 }
 
+// Two f32 rounded to bf16 and packed, the first in the low half. The hardware's
+// conversion is the same rounding for every number and infinity; it makes any
+// NaN the canonical one, where the reference keeps sign and payload, so a pair
+// that holds a NaN is redone by the integer form.
+PSK_DEV uint32_t pack_bf16x2_hw(float lo, float hi)
+{
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+PSK_DEV uint32_t pack_bf16x2(float lo, float hi)
+{
+    uint32_t r = pack_bf16x2_hw(lo, hi);
+    if (lo != lo || hi != hi) r = (uint32_t)f32_to_bf16(lo) | ((uint32_t)f32_to_bf16(hi) << 16);
+    return r;
+}
+
+PSK_DEV uint32_t pack_f16x2_hw(float lo, float hi)
+{
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
 // ---- binary16 ------------------------------------------------------------
 // The hardware conversions are IEEE's for every number; only NaNs need care,
 // since cvt gives a canonical NaN where the reference keeps sign and payload.

@@ -10,16 +10,17 @@
 // to the site's storage type with the bits of psk_formats.cuh, and tests the
 // overflow guard where the type is binary16 or e8m15.
 //
-// Shape of the kernel: one persistent CTA per SM, 192 threads.
+// Shape of the kernel: one persistent CTA per SM, 320 threads.
 //   warp 0      one lane issues the TMA loads of A and B tiles (128 x 64 and
 //               BN x 64 elements, 128-byte swizzle) into a ring of STAGES
 //               shared-memory stages;
 //   warp 1      allocates tensor memory; one lane issues tcgen05.mma
 //               (cta_group::1, kind::f16, M = 128, N = BN, K = 16) four times
 //               per stage into one of two accumulators of BN columns;
-//   warps 2-5   the epilogue: tcgen05.ld of 32 columns a time, rounding, and
-//               128-bit global stores, of one accumulator while the other is
-//               being computed.
+//   warps 2-9   the epilogue: tcgen05.ld of 32 columns a time, rounding, a
+//               transposition through shared memory and 128-bit global stores
+//               of whole 128-byte lines, of one accumulator while the other is
+//               being computed; two warps a quadrant of tensor memory.
 // No multicast, no cluster: every CTA loads its own tiles, and reuse between
 // CTAs comes from the L2 through the order tiles are handed out in.
 //
@@ -38,7 +39,7 @@ namespace tc {
 constexpr int BM = 128;
 constexpr int BK = 64; // elements: one 128-byte swizzle row of 16-bit elements
 constexpr int UMMA_K = 16;
-constexpr int THREADS = 192;
+constexpr int THREADS = 320; // a TMA warp, an MMA warp, eight epilogue warps
 constexpr long long WAIT_CYCLES = 4000000000ll; // about two seconds
 
 struct Params {
@@ -186,7 +187,7 @@ struct Smem {
     static constexpr int STAGES = (BN == 256) ? 4 : 6;
     static constexpr int TILE_BYTES = STAGES * (A_BYTES + B_BYTES);
     static constexpr int BAR_BYTES = 256;
-    static constexpr int STAGE_OUT = 4 * 32 * 128; // the epilogue's staging: 32 rows of 128 bytes a warp
+    static constexpr int STAGE_OUT = 8 * 32 * 128; // the epilogue's staging: 32 rows of 128 bytes a warp
     static constexpr int TOTAL = TILE_BYTES + BAR_BYTES + STAGE_OUT + 1024; // slack to align the base to 1024
 };
 
@@ -219,7 +220,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(tfull0 + 8 * s, 1);
-            mbar_init(tempty0 + 8 * s, 4); // one arrival per epilogue warp
+            mbar_init(tempty0 + 8 * s, 8); // one arrival per epilogue warp
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -298,7 +299,9 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
         uint32_t acc = 0, acc_phase = 0, ovf = 0;
         bool ok = true;
         // this warp's staging tile: 32 rows of 128 bytes, 16-byte units swizzled by the row
-        uint4 *stage_out = reinterpret_cast<uint4 *>(smem + S::TILE_BYTES + S::BAR_BYTES) + quad * 32 * 8;
+        // two warps share a quadrant of tensor memory and take alternate column groups
+        const int half_id = (warp - 2) >> 2;
+        uint4 *stage_out = reinterpret_cast<uint4 *>(smem + S::TILE_BYTES + S::BAR_BYTES) + (warp - 2) * 32 * 8;
         const bool staged = P.vec_ok && (P.out_dtype == PSK_BF16 || P.out_dtype == PSK_F16 || P.out_dtype == PSK_F32);
         const int group_cols = P.out_dtype == PSK_F32 ? 32 : 64; // columns in 128 bytes
         for (int64_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
@@ -320,7 +323,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
                 // 128 bytes of every row at a time: through shared memory, so that a store
                 // instruction writes whole 128-byte lines (8 lanes a row, 4 rows an instruction)
 #pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += group_cols) {
+                for (int c0 = half_id * group_cols; c0 < BN; c0 += 2 * group_cols) {
                     const int64_t col = n0 + c0;
                     if (P.out_dtype == PSK_F32) {
                         uint32_t v[32];
@@ -345,11 +348,13 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
                                 for (int i = 0; i < 4; ++i) {
                                     float x0 = __uint_as_float(v[q * 8 + 2 * i]), x1 = __uint_as_float(v[q * 8 + 2 * i + 1]);
                                     if (P.scale_on) { x0 = __fmul_rn(x0, P.scale); x1 = __fmul_rn(x1, P.scale); }
+                                    // the hardware's rounding: the reference's for every number; a NaN
+                                    // comes out canonical (its sign and payload are not kept on this path)
                                     if (P.out_dtype == PSK_BF16) {
-                                        u[i] = (uint32_t)f32_to_bf16(x0) | ((uint32_t)f32_to_bf16(x1) << 16);
+                                        u[i] = pack_bf16x2_hw(x0, x1);
                                     } else {
                                         ovf |= overflows(x0, kF16Overflow) | overflows(x1, kF16Overflow);
-                                        u[i] = (uint32_t)f32_to_f16(x0) | ((uint32_t)f32_to_f16(x1) << 16);
+                                        u[i] = pack_f16x2_hw(x0, x1);
                                     }
                                 }
                                 stage_out[lane * 8 + ((half * 4 + q) ^ (lane & 7))] = make_uint4(u[0], u[1], u[2], u[3]);
@@ -377,7 +382,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
                 }
             } else {
 #pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 32) {
+                for (int c0 = half_id * 32; c0 < BN; c0 += 64) {
                     uint32_t v[32];
                     tmem_ld32(tbase + c0, v);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");

@@ -61,10 +61,10 @@ PSK_DEV uint32_t ew_store8(void *p, int dt, int64_t off, const float (&x)[8])
 {
     if (dt == PSK_BF16) {
         uint4 w;
-        w.x = (uint32_t)f32_to_bf16(x[0]) | ((uint32_t)f32_to_bf16(x[1]) << 16);
-        w.y = (uint32_t)f32_to_bf16(x[2]) | ((uint32_t)f32_to_bf16(x[3]) << 16);
-        w.z = (uint32_t)f32_to_bf16(x[4]) | ((uint32_t)f32_to_bf16(x[5]) << 16);
-        w.w = (uint32_t)f32_to_bf16(x[6]) | ((uint32_t)f32_to_bf16(x[7]) << 16);
+        w.x = pack_bf16x2(x[0], x[1]);
+        w.y = pack_bf16x2(x[2], x[3]);
+        w.z = pack_bf16x2(x[4], x[5]);
+        w.w = pack_bf16x2(x[6], x[7]);
         *reinterpret_cast<uint4 *>((uint16_t *)p + off) = w;
         return 0u;
     }
@@ -268,6 +268,77 @@ __global__ void __launch_bounds__(128, 3) k_ew_bf16(const __grid_constant__ EwPa
     }
 }
 
+// The groups a transformer's forward pass is made of, with their steps fixed at
+// compile time: no routing of step arguments at run time, a handful of
+// instructions an element. A launch whose steps are exactly one of these (the
+// executor compares them) and whose operands are all bf16 takes this kernel.
+enum EwProg { EW_ADD = 0, EW_SUB, EW_MUL, EW_DIV, EW_DIV_MUL, EW_SILU, EW_MUL_MUL_SUB, EW_MUL_MUL_ADD, EW_NPROG };
+
+template <int PROG>
+PSK_DEV float ew_eval(float a, float b, float c, float d)
+{
+    if constexpr (PROG == EW_ADD) return __fadd_rn(a, b);
+    else if constexpr (PROG == EW_SUB) return __fsub_rn(a, b);
+    else if constexpr (PROG == EW_MUL) return __fmul_rn(a, b);
+    else if constexpr (PROG == EW_DIV) return __fdiv_rn(a, b);
+    else if constexpr (PROG == EW_DIV_MUL) return __fmul_rn(__fdiv_rn(a, b), c);                              // [div 0,1; mul s0,2]
+    else if constexpr (PROG == EW_SILU) return __fmul_rn(a, __fdiv_rn(1.0f, __fadd_rn(1.0f, lm_expf(-a))));    // [sigmoid 0; mul 0,s0]
+    else if constexpr (PROG == EW_MUL_MUL_SUB) return __fsub_rn(__fmul_rn(a, b), __fmul_rn(c, d));            // [mul 0,1; mul 2,3; sub s0,s1]
+    else return __fadd_rn(__fmul_rn(a, b), __fmul_rn(c, d));                                                  // [mul 0,1; mul 2,3; add s0,s1]
+}
+
+template <int PROG>
+struct EwArity {
+    static constexpr int value = (PROG == EW_SILU) ? 1 : (PROG == EW_DIV_MUL) ? 3 : (PROG == EW_MUL_MUL_SUB || PROG == EW_MUL_MUL_ADD) ? 4 : 2;
+};
+
+template <int PROG, int UNR>
+__global__ void __launch_bounds__(256, 2) k_ew_prog(const __grid_constant__ EwParams E)
+{
+    constexpr int NIN = EwArity<PROG>::value;
+    const uint32_t total = E.rows * E.colv;
+    const uint32_t stride = gridDim.x * blockDim.x;
+    for (uint32_t idx0 = blockIdx.x * blockDim.x + threadIdx.x; idx0 < total; idx0 += stride * UNR) {
+        uint4 raw[UNR][NIN];
+        uint32_t rr[UNR], cc[UNR];
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+            const uint32_t idx = idx0 + u * stride;
+            if (E.rows == 1) { rr[u] = 0; cc[u] = idx * 8u; }
+            else { rr[u] = idx / E.colv; cc[u] = (idx - rr[u] * E.colv) * 8u; }
+            if (idx < total) {
+#pragma unroll
+                for (int i = 0; i < NIN; ++i) {
+                    const uint16_t *p = (const uint16_t *)E.in[i] + (int64_t)rr[u] * E.rs[i];
+                    if (E.cs[i]) raw[u][i] = *reinterpret_cast<const uint4 *>(p + cc[u]);
+                    else { const uint32_t h = *p; raw[u][i] = make_uint4(h | (h << 16), h | (h << 16), h | (h << 16), h | (h << 16)); }
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+            if (idx0 + u * stride >= total) break;
+            uint32_t out[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                float lo[4], hi[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    if (i < NIN) {
+                        const uint32_t w = q == 0 ? raw[u][i].x : q == 1 ? raw[u][i].y : q == 2 ? raw[u][i].z : raw[u][i].w;
+                        lo[i] = bits_f32(w << 16);
+                        hi[i] = bits_f32(w & 0xffff0000u);
+                    } else {
+                        lo[i] = hi[i] = 0.0f;
+                    }
+                }
+                out[q] = pack_bf16x2(ew_eval<PROG>(lo[0], lo[1], lo[2], lo[3]), ew_eval<PROG>(hi[0], hi[1], hi[2], hi[3]));
+            }
+            *reinterpret_cast<uint4 *>((uint16_t *)E.out + (int64_t)rr[u] * E.ors + cc[u]) = make_uint4(out[0], out[1], out[2], out[3]);
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------
 // Softmax over a contiguous axis under PSK_ORDER_DEVICE: a warp a row, the
 // row held in shared memory between the passes, the exponentials computed
@@ -276,6 +347,19 @@ __global__ void __launch_bounds__(128, 3) k_ew_bf16(const __grid_constant__ EwPa
 // exponentiated; the refused tail is written as zeros, which is what the
 // reference's selections give it (lower.rs:1368-1419).
 // ---------------------------------------------------------------------------
+// a / b for positive finite b, given r = the correctly rounded 1 / b: the
+// quotient to nearest by one multiplication and two fused operations
+// (Markstein's correction), which is the division's own result whenever no
+// intermediate leaves the normal range; outside it, the division itself.
+PSK_DEV float div_by(float a, float b, float r)
+{
+    const uint32_t ea = (f32_bits(a) >> 23) & 0xffu;
+    if (ea < 40u || ea > 210u) return __fdiv_rn(a, b); // zero, tiny, huge, infinite or NaN numerator
+    const float q = __fmul_rn(a, r);
+    const float rem = __fmaf_rn(-b, q, a);
+    return __fmaf_rn(rem, r, q);
+}
+
 template <int WARPS>
 __global__ void __launch_bounds__(WARPS * 32) k_softmax_rows_smem(const __grid_constant__ DevLaunch L)
 {
@@ -287,6 +371,8 @@ __global__ void __launch_bounds__(WARPS * 32) k_softmax_rows_smem(const __grid_c
     const int64_t nwarps = (int64_t)gridDim.x * WARPS;
     const uint32_t nv = (uint32_t)(n / 8);
     const bool causal = L.masked && L.iparam[0] == 1;
+    const bool general_mask = L.masked && !causal;
+    const bool bf16_io = L.in[0].dtype == PSK_BF16 && L.kdtype == PSK_BF16 && L.out.dtype == PSK_BF16;
     for (int64_t r = (int64_t)blockIdx.x * WARPS + wib; r < L.total; r += nwarps) {
         const int64_t base = operand_offset(L.in[0], L.dims, 0, L.n_outer, r);
         const int64_t obase = operand_offset(L.out, L.dims, 0, L.n_outer, r);
@@ -296,16 +382,18 @@ __global__ void __launch_bounds__(WARPS * 32) k_softmax_rows_smem(const __grid_c
             ms = L.in[1].stride[L.n_outer];
             if (causal) mbase = mbase / L.iparam[1];
         }
-        const uint32_t live = causal ? (uint32_t)min((int64_t)nv, mbase / 8 + 1) : nv;
+        // under the causal mask the allowed elements are 0 .. count-1
+        const uint32_t count = causal ? (uint32_t)min(n, mbase + 1) : (uint32_t)n;
+        const uint32_t live = (count + 7u) / 8u;
+        // pass 1: the row into shared memory as f32 (a refused element as -inf), and its maximum
         float m = -INFINITY;
-        if (L.in[0].dtype == PSK_BF16 && L.kdtype == PSK_BF16 && nv <= 256) {
-            // all of the row's loads first, then the arithmetic
+        if (bf16_io && nv <= 256) {
             uint4 raw[8];
             const uint16_t *src = (const uint16_t *)L.in[0].p + base;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 const uint32_t v = lane + 32u * j;
-                if (v < live) raw[j] = *reinterpret_cast<const uint4 *>(src + (int64_t)v * 8);
+                if (v < live) raw[j] = *reinterpret_cast<const uint4 *>(src + (size_t)v * 8);
             }
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
@@ -314,64 +402,67 @@ __global__ void __launch_bounds__(WARPS * 32) k_softmax_rows_smem(const __grid_c
                     const uint4 w = raw[j];
                     float x[8] = {bits_f32(w.x << 16), bits_f32(w.x & 0xffff0000u), bits_f32(w.y << 16), bits_f32(w.y & 0xffff0000u),
                                   bits_f32(w.z << 16), bits_f32(w.z & 0xffff0000u), bits_f32(w.w << 16), bits_f32(w.w & 0xffff0000u)};
+                    if (v * 8u + 8u > count || general_mask) {
 #pragma unroll
-                    for (int t = 0; t < 8; ++t) {
-                        const bool ok = !L.masked || mask_allows(L, mbase, (int64_t)v * 8 + t, ms);
-                        if (ok) m = fmaxf(m, x[t]);
+                        for (int t = 0; t < 8; ++t) {
+                            const bool ok = v * 8u + t < count && (!general_mask || mask_allows(L, mbase, (int64_t)v * 8 + t, ms));
+                            if (!ok) x[t] = -INFINITY;
+                        }
                     }
+#pragma unroll
+                    for (int t = 0; t < 8; ++t) m = fmaxf(m, x[t]);
                     float4 *dst = reinterpret_cast<float4 *>(row + v * 8);
                     dst[0] = make_float4(x[0], x[1], x[2], x[3]);
                     dst[1] = make_float4(x[4], x[5], x[6], x[7]);
                 }
             }
-        } else
-        for (uint32_t v = lane; v < live; v += 32) {
-            float x[8];
-            ew_load8(L.in[0].p, L.in[0].dtype, base + (int64_t)v * 8, 1, L.kdtype, x, &ovf);
+        } else {
+            for (uint32_t v = lane; v < live; v += 32) {
+                float x[8];
+                ew_load8(L.in[0].p, L.in[0].dtype, base + (int64_t)v * 8, 1, L.kdtype, x, &ovf);
 #pragma unroll
-            for (int t = 0; t < 8; ++t) {
-                const bool ok = !L.masked || mask_allows(L, mbase, (int64_t)v * 8 + t, ms);
-                if (ok) m = fmaxf(m, x[t]);
+                for (int t = 0; t < 8; ++t) {
+                    const bool ok = v * 8u + t < count && (!general_mask || mask_allows(L, mbase, (int64_t)v * 8 + t, ms));
+                    if (!ok) x[t] = -INFINITY;
+                    m = fmaxf(m, x[t]);
+                }
+                float4 *dst = reinterpret_cast<float4 *>(row + v * 8);
+                dst[0] = make_float4(x[0], x[1], x[2], x[3]);
+                dst[1] = make_float4(x[4], x[5], x[6], x[7]);
             }
-            float4 *dst = reinterpret_cast<float4 *>(row + v * 8);
-            dst[0] = make_float4(x[0], x[1], x[2], x[3]);
-            dst[1] = make_float4(x[4], x[5], x[6], x[7]);
         }
         m = warp_max(m);
+        __syncwarp();
+        // pass 2: one element a lane a turn, consecutive lanes on consecutive words. A refused element
+        // holds -inf: it adds 0 and gives 0, as the reference's selections do.
         float z = 0.0f;
-        for (uint32_t v = lane; v < live; v += 32) {
-            float4 *p = reinterpret_cast<float4 *>(row + v * 8);
-            float4 a = p[0], b = p[1];
-            float x[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-#pragma unroll
-            for (int t = 0; t < 8; ++t) {
-                const bool ok = !L.masked || mask_allows(L, mbase, (int64_t)v * 8 + t, ms);
-                float e = 0.0f;
-                if (ok) e = lm_expf(__fsub_rn(x[t], m));
-                x[t] = e;
-                z += e;
-            }
-            p[0] = make_float4(x[0], x[1], x[2], x[3]);
-            p[1] = make_float4(x[4], x[5], x[6], x[7]);
+        const uint32_t padded = live * 8u;
+        for (uint32_t k = lane; k < padded; k += 32) {
+            const float x = row[k];
+            float e = 0.0f;
+            if (x != -INFINITY) e = lm_expf(__fsub_rn(x, m));
+            row[k] = e;
+            z += e;
         }
         z = warp_sum(z);
+        __syncwarp();
+        // pass 3: e / z, eight a lane, stored as whole vectors; zeros past the allowed prefix
+        const float rz = __frcp_rn(z);
         for (uint32_t v = lane; v < nv; v += 32) {
             float y[8];
             if (v < live) {
                 const float4 *p = reinterpret_cast<const float4 *>(row + v * 8);
-                float4 a = p[0], b = p[1];
-                float x[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+                const float4 a = p[0], b = p[1];
+                const float x[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
 #pragma unroll
-                for (int t = 0; t < 8; ++t) {
-                    const bool ok = !L.masked || mask_allows(L, mbase, (int64_t)v * 8 + t, ms);
-                    y[t] = ok ? __fdiv_rn(x[t], z) : 0.0f;
-                }
+                for (int t = 0; t < 8; ++t) y[t] = x[t] == 0.0f ? 0.0f : div_by(x[t], z, rz);
             } else {
 #pragma unroll
                 for (int t = 0; t < 8; ++t) y[t] = 0.0f;
             }
             ovf |= ew_store8(const_cast<void *>(L.out.p), L.out.dtype, obase + (int64_t)v * 8, y);
         }
+        __syncwarp();
     }
     if (L.guarded && ovf) atomicOr(L.ovf, 1u);
 }
