@@ -336,17 +336,19 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
                             stage_out[lane * 8 + (q ^ (lane & 7))] = make_uint4(__float_as_uint(x0), __float_as_uint(x1), __float_as_uint(x2), __float_as_uint(x3));
                         }
                     } else {
+                        uint32_t va[32], vb[32];
+                        tmem_ld32(tbase + c0, va);
+                        tmem_ld32(tbase + c0 + 32, vb);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                         for (int half = 0; half < 2; ++half) {
-                            uint32_t v[32];
-                            tmem_ld32(tbase + c0 + half * 32, v);
-                            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                             for (int q = 0; q < 4; ++q) {
                                 uint32_t u[4];
 #pragma unroll
                                 for (int i = 0; i < 4; ++i) {
-                                    float x0 = __uint_as_float(v[q * 8 + 2 * i]), x1 = __uint_as_float(v[q * 8 + 2 * i + 1]);
+                                    float x0 = __uint_as_float(half ? vb[q * 8 + 2 * i] : va[q * 8 + 2 * i]);
+                                    float x1 = __uint_as_float(half ? vb[q * 8 + 2 * i + 1] : va[q * 8 + 2 * i + 1]);
                                     if (P.scale_on) { x0 = __fmul_rn(x0, P.scale); x1 = __fmul_rn(x1, P.scale); }
                                     // the hardware's rounding: the reference's for every number; a NaN
                                     // comes out canonical (its sign and payload are not kept on this path)

@@ -361,7 +361,7 @@ PSK_DEV float div_by(float a, float b, float r)
 }
 
 template <int WARPS>
-__global__ void __launch_bounds__(WARPS * 32) k_softmax_rows_smem(const __grid_constant__ DevLaunch L)
+__global__ void __launch_bounds__(WARPS * 32, 6) k_softmax_rows_smem(const __grid_constant__ DevLaunch L)
 {
     extern __shared__ float s_rows[];
     uint32_t ovf = 0;
@@ -437,6 +437,7 @@ __global__ void __launch_bounds__(WARPS * 32) k_softmax_rows_smem(const __grid_c
         // holds -inf: it adds 0 and gives 0, as the reference's selections do.
         float z = 0.0f;
         const uint32_t padded = live * 8u;
+#pragma unroll 4
         for (uint32_t k = lane; k < padded; k += 32) {
             const float x = row[k];
             float e = 0.0f;

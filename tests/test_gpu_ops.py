@@ -214,7 +214,8 @@ def test_cross_entropy(cuda, oracle, rows, v, order):
     if order == abi.ORDER_SEQUENTIAL:
         assert np.array_equal(got, want)
     else:
-        np.testing.assert_allclose(got.view(np.float32), want.view(np.float32), rtol=2e-6, atol=2e-6)
+        # z is a sum of v terms: a chain and a tree differ by up to ~v·2^-24 relative, and ln z by as much absolutely
+        np.testing.assert_allclose(got.view(np.float32), want.view(np.float32), rtol=3e-5, atol=3e-5)
 
 
 def test_embed_and_argmax(cuda, oracle):
