@@ -233,6 +233,34 @@ typedef struct {
 } psk_gemm;
 int psk_exec_gemm(psk_exec *e, const psk_gemm *g, const void *a, const void *b, void *c);
 
+/* The tensor-core contraction for a caller that may not allocate device
+ * memory at all: one that gave this library a fixed arena, runs under a fixed
+ * memory budget, or calls from a place where the driver's allocator must not
+ * be entered. An executor allocates when it is created (guard flags, status
+ * word, buffer pool), so such a caller cannot have one; this entry point
+ * needs none. It has no counterpart in the reference.
+ *
+ * Same arithmetic and the same kernel as psk_exec_gemm, so the same bytes in
+ * `c`. The scratch the kernel writes besides `c` (its status word and the
+ * overflow guard's flags, here one flag a batch entry) lives in one static
+ * array of 1 + PSK_NOALLOC_MAX_BATCH words on each device that loads the
+ * library, held until the process exits; a `batch` above that maximum is
+ * refused with PSK_E7001. `a`, `b`, `c` are device pointers the caller owns;
+ * `stream` is a cudaStream_t (NULL: the default stream). The call clears the
+ * words it uses, launches, copies them back and waits for the stream, so it
+ * is synchronous; it calls no cudaMalloc, cudaFree or allocating library
+ * routine. Returns PSK_OK, or PSK_E7007 with `*overflowed_batch` the first
+ * batch entry a guarded store overflowed in (else -1), or another status
+ * with a message in `err` (may be NULL).
+ *
+ * The array is shared by every call on a device and keeps the last call's
+ * contents: two calls that overlap on one GPU (two host threads, or a second
+ * route to the same kernel) race on it. The first call on a device looks the
+ * array's device address up and sets the kernel's attributes; make that first
+ * call before any stream capture begins. */
+#define PSK_NOALLOC_MAX_BATCH 1023
+int psk_gemm_noalloc(const psk_gemm *g, const void *a, const void *b, void *c, void *stream, int64_t *overflowed_batch, char *err, size_t err_cap);
+
 /* ---------------------------------------------------------------------------
  * The executor as a table of functions, so that the host program can run
  * over another one (KernelBackend::with_exec, host.rs:466). The library's

@@ -98,6 +98,7 @@ PROTOTYPES = {
     "psk_exec_stream": (C.c_void_p, [C.c_void_p]),
     "psk_exec_profile": (C.c_char_p, [C.c_void_p]),
     "psk_exec_gemm": (C.c_int, [C.c_void_p, C.POINTER(Gemm), C.c_void_p, C.c_void_p, C.c_void_p]),
+    "psk_gemm_noalloc": (C.c_int, [C.POINTER(Gemm), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(C.c_int64), C.c_char_p, C.c_size_t]),
     "psk_exec_quantize": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64]),
     "psk_exec_init_normal": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_uint64, C.c_double]),
     "psk_exec_as_vtable": (None, [C.c_void_p, C.POINTER(ExecVtable)]),

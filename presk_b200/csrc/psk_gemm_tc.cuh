@@ -195,7 +195,9 @@ struct Smem {
 // scaling as the reference's separate nest would compute it (round to the
 // site's type, then one IEEE division... the caller passes the reciprocal
 // only when that is exact), then the store's rounding.
-template <int BN>
+// PER_BATCH: the guard's flag is one word a batch entry (P.ovf[b]) instead of
+// one word a launch, for a caller that wants to know which entry overflowed.
+template <int BN, bool PER_BATCH = false>
 __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ Params P)
 {
     using S = Smem<BN>;
@@ -400,6 +402,10 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
                             }
                     }
                 }
+            }
+            if constexpr (PER_BATCH) {
+                if (P.guarded && ovf) atomicOr(P.ovf + b, 1u);
+                ovf = 0;
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
