@@ -116,7 +116,7 @@ def cpu_prefill_tokens_per_s(consts, T, B, threads):
     os.environ.setdefault("OMP_NUM_THREADS", str(threads))
     orc = oracle_lib.load()
     times = {}
-    Ts, Bs = min(T, 32), 1
+    Ts, Bs = min(T, 128), 1
     rng = np.random.default_rng(0)
     for L in (1, 2):
         c = dict(consts, L=L)

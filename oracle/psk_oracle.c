@@ -32,6 +32,7 @@
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
+#include <time.h>
 
 #include "../include/presk_cuda.h"
 
@@ -256,6 +257,17 @@ static float edge_round(float x, int kdtype, int dtype, uint32_t *ovf)
     }
 }
 
+/* Whether a kernel of type kd reads an input stored as `dtype` without rounding it. */
+static int edge_is_identity(int kd, int dtype)
+{
+    uint32_t ovf = 0;
+    (void)ovf;
+    if (dtype == kd || dtype == PSK_I8 || dtype == PSK_I64) return 1;
+    if (kd == PSK_F32) return 1;
+    if (kd == PSK_E8M15) return dtype == PSK_BF16 || dtype == PSK_F16 || dtype == PSK_E4M3;
+    return 0;
+}
+
 /* ---- a launch's operands ------------------------------------------------------ */
 typedef struct {
     const uint8_t *p;
@@ -328,7 +340,36 @@ static float prim_binary(int prim, float x, float y)
 }
 
 /* ---- the launches ------------------------------------------------------------- */
+static int psk_oracle_run_merged(const psk_launch *l, void *const *table, uint32_t *overflow);
+
+/* Summed axes that every operand walks as one (stride[a] = stride[a+1]·dims[a+1]) are one axis:
+ * the terms come in the same lexicographic order either way, so a contraction over several
+ * contiguous axes (the output projection's groups, per, hd) is the nest over their product. */
 int psk_oracle_run(const psk_launch *l, void *const *table, uint32_t *overflow)
+{
+    if (l->op == PSK_OP_CONTRACT && l->n_inner > 1) {
+        psk_launch m = *l;
+        int no = l->n_outer, w = 0;
+        for (int c = 1; c < l->n_inner; ++c) {
+            int a = no + w, b = no + c, ok = 1;
+            for (int i = 0; i < l->n_inputs; ++i)
+                ok = ok && m.in[i].stride[a] == l->in[i].stride[b] * l->dims[b] && m.in[i].scale_stride[a] == l->in[i].scale_stride[b] * l->dims[b];
+            if (ok) {
+                m.dims[a] *= l->dims[b];
+                for (int i = 0; i < l->n_inputs; ++i) { m.in[i].stride[a] = l->in[i].stride[b]; m.in[i].scale_stride[a] = l->in[i].scale_stride[b]; }
+            } else {
+                ++w;
+                m.dims[no + w] = l->dims[b];
+                for (int i = 0; i < l->n_inputs; ++i) { m.in[i].stride[no + w] = l->in[i].stride[b]; m.in[i].scale_stride[no + w] = l->in[i].scale_stride[b]; }
+            }
+        }
+        m.n_inner = w + 1;
+        return psk_oracle_run_merged(&m, table, overflow);
+    }
+    return psk_oracle_run_merged(l, table, overflow);
+}
+
+static int psk_oracle_run_merged(const psk_launch *l, void *const *table, uint32_t *overflow)
 {
     const int no = l->n_outer, ni = l->n_inner, kd = l->dtype;
     operand in[PSK_MAX_INPUTS];
@@ -365,6 +406,77 @@ int psk_oracle_run(const psk_launch *l, void *const *table, uint32_t *overflow)
         }
         break;
     case PSK_OP_CONTRACT: /* lower.rs:465-474, 586-636: acc = acc + (x·w), the terms in lexicographic order */
+        /* The tiled form of a contraction nest (lower.rs:906-1139, tile (1, JB)): when the last output axis
+         * is carried by operand 1 alone, contiguously, a block of JB results is summed at once, each still
+         * adding its own terms in increasing k, so the bits are those of the loop below. It is the form the
+         * reference's executors run, and what makes this restatement a fair CPU baseline. */
+        if (ni == 1 && l->n_inputs == 2 && no >= 1 && l->in[0].stride[no - 1] == 0 && l->in[1].stride[no - 1] == 1 && l->out.stride[no - 1] == 1
+            && l->in[0].dtype != PSK_I8 && (l->in[1].dtype == PSK_BF16 || l->in[1].dtype == PSK_F32 || l->in[1].dtype == PSK_I8)
+            && edge_is_identity(kd, l->in[1].dtype) && inner > 0) {
+            enum { JB = 64, RB = 8 };
+            const int64_t K = inner, N = l->dims[no - 1], rows = total / N;
+            const int64_t s0 = l->in[0].stride[no], s1 = l->in[1].stride[no], q1 = l->in[1].scale_stride[no];
+            const int64_t sj = l->in[1].scale_stride[no - 1];
+            const int64_t row_blocks = (rows + RB - 1) / RB, col_blocks = (N + JB - 1) / JB;
+            /* rows that share operand 1 (the same offsets into it) can share a pass over it */
+#pragma omp parallel reduction(| : ovf_all)
+            {
+                float *arow = (float *)malloc((size_t)K * RB * sizeof(float));
+                uint32_t ovf = 0;
+#pragma omp for schedule(dynamic, 1)
+                for (int64_t rb = 0; rb < row_blocks; ++rb) {
+                    int nr = (int)(rows - rb * RB < RB ? rows - rb * RB : RB);
+                    int64_t b1[RB], sb1[RB], ob[RB];
+                    for (int r = 0; r < nr; ++r) {
+                        const int64_t row = rb * RB + r;
+                        const int64_t b0 = offset_of(l->in[0].stride, l->dims, 0, no - 1, row);
+                        b1[r] = offset_of(l->in[1].stride, l->dims, 0, no - 1, row);
+                        sb1[r] = offset_of(l->in[1].scale_stride, l->dims, 0, no - 1, row);
+                        ob[r] = offset_of(l->out.stride, l->dims, 0, no - 1, row);
+                        for (int64_t k = 0; k < K; ++k) arow[r * K + k] = load_operand(&in[0], b0 + k * s0, 0, kd, &ovf);
+                    }
+                    /* a block shares the pass only while its rows read the same part of operand 1 */
+                    int shared = 1;
+                    for (int r = 1; r < nr; ++r) shared = shared && b1[r] == b1[0] && sb1[r] == sb1[0];
+                    for (int r0 = 0; r0 < nr; r0 += shared ? nr : 1) {
+                        const int rn = shared ? nr : 1;
+                        for (int64_t cb = 0; cb < col_blocks; ++cb) {
+                            const int64_t j0 = cb * JB;
+                            const int jb = (int)(N - j0 < JB ? N - j0 : JB);
+                            float acc[RB][JB];
+                            for (int r = 0; r < rn; ++r)
+                                for (int jj = 0; jj < JB; ++jj) acc[r][jj] = 0.0f;
+                            for (int64_t k = 0; k < K; ++k) {
+                                float wv[JB];
+                                if (l->in[1].dtype == PSK_BF16) {
+                                    const uint16_t *wr = (const uint16_t *)in[1].p + b1[r0] + j0 + k * s1;
+                                    for (int jj = 0; jj < jb; ++jj) wv[jj] = u2f((uint32_t)wr[jj] << 16);
+                                } else if (l->in[1].dtype == PSK_F32) {
+                                    const float *wr = (const float *)in[1].p + b1[r0] + j0 + k * s1;
+                                    for (int jj = 0; jj < jb; ++jj) wv[jj] = wr[jj];
+                                } else { /* integer weights: f32(q)·s, one multiplication, as the value is loaded */
+                                    const int8_t *wr = (const int8_t *)in[1].p + b1[r0] + j0 + k * s1;
+                                    const float *sk = in[1].scales + sb1[r0] + j0 * sj + k * q1;
+                                    for (int jj = 0; jj < jb; ++jj) wv[jj] = (float)wr[jj] * sk[jj * sj];
+                                }
+                                for (int r = 0; r < rn; ++r) {
+                                    const float a = arow[(r0 + r) * K + k];
+                                    for (int jj = 0; jj < jb; ++jj) {
+                                        const float prod = a * wv[jj];
+                                        acc[r][jj] = acc[r][jj] + prod;
+                                    }
+                                }
+                            }
+                            for (int r = 0; r < rn; ++r)
+                                for (int jj = 0; jj < jb; ++jj) ovf |= store_real(outp, l->out.dtype, ob[r0 + r] + j0 + jj, acc[r][jj]);
+                        }
+                    }
+                }
+                ovf_all |= ovf;
+                free(arow);
+            }
+            break;
+        }
 #pragma omp parallel for schedule(static) reduction(| : ovf_all)
         for (int64_t lin = 0; lin < total; ++lin) {
             uint32_t ovf = 0;
@@ -601,7 +713,14 @@ static int o_run(void *s, const psk_launch *l, void *const *t)
 {
     oracle_exec *e = (oracle_exec *)s;
     uint32_t ovf = 0;
+    struct timespec t0, t1;
+    const int trace = getenv("PSK_ORACLE_TRACE") != NULL;
+    if (trace) clock_gettime(CLOCK_MONOTONIC, &t0);
     int rc = psk_oracle_run(l, t, &ovf);
+    if (trace) {
+        clock_gettime(CLOCK_MONOTONIC, &t1);
+        fprintf(stderr, "oracle\t%s\t%.3f ms\n", l->name ? l->name : "?", (t1.tv_sec - t0.tv_sec) * 1e3 + (t1.tv_nsec - t0.tv_nsec) * 1e-6);
+    }
     if (rc != PSK_OK) snprintf(e->error, sizeof e->error, "%s: the oracle does not run this launch (%d)", l->name ? l->name : "?", rc);
     if (ovf && !e->first_overflow) e->first_overflow = e->launches + 1;
     e->launches += 1;
