@@ -313,12 +313,10 @@ def main():
     barrier()
     e2e_s = time.perf_counter() - t0
 
-    t_ms = torch.tensor([ms, e2e_s * 1e3], device="cuda", dtype=torch.float64)
-    loss_t = torch.tensor([loss], device="cuda", dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
-        dist.all_reduce(loss_t, op=dist.ReduceOp.SUM)  # the final loss gather: per-shard means, summed
-    ms, e2e_ms = float(t_ms[0]), float(t_ms[1])
+    from presk_b200 import shard
+    ms = shard.max_over_ranks(ms, device="cuda")
+    e2e_ms = shard.max_over_ranks(e2e_s * 1e3, device="cuda")
+    loss_all = shard.combine_mean(loss, B * T, device="cuda")  # the final loss gather: one all-reduce
     tokens = B * T * world * args.steps
     value = tokens / (ms * 1e-3)
     e2e = tokens / (e2e_ms * 1e-3)
@@ -359,7 +357,7 @@ def main():
             "roofline": {"bound": "tensor", "kernel": "k_gemm_tc", "achieved": achieved, "peak": tf_peak, "unit": "TFLOP/s", "frac": achieved / tf_peak, "traffic": None, "peak_source": peak_kind,
                          "model_tflops": flops_per_token(consts, T) * B * T * args.steps / (ms * 1e-3) / 1e12, "hbm_peak_gbs": hbm_peak},
             "kernel_shares": shares,
-            "loss": float(loss_t[0]) / world,
+            "loss": loss_all,
             "launches_per_step": int((launches_after - launches_before) / args.steps),
         }
         if world == 1 and not args.no_cpu_baseline:

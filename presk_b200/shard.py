@@ -1,0 +1,35 @@
+"""Sharding of the batch axis over ranks (one process a GPU) and the one exchange the
+forward pass needs: the final loss.
+
+Every launch of a forward pass carries `batch` as an outer parallel axis with disjoint
+outputs (presk-kernel/src/ir.rs:345-375), so a rank runs the whole model on its own rows
+with no data-path collective. The loss of the whole batch is the mean over all rows; each
+rank holds the mean over its rows, and the means are combined weighted by their row counts
+with one all-reduce (a declared two-level order of the sum: rows within a shard, then shards
+in rank order).
+"""
+import torch
+import torch.distributed as dist
+
+
+def shard_rows(n_rows, rank, world):
+    """The contiguous slice [lo, hi) of `n_rows` batch rows that `rank` of `world` owns."""
+    base, extra = divmod(n_rows, world)
+    lo = rank * base + min(rank, extra)
+    return lo, lo + base + (1 if rank < extra else 0)
+
+
+def combine_mean(local_mean, local_count, device="cpu", group=None):
+    """The mean over all ranks' rows from each rank's mean and row count."""
+    t = torch.tensor([float(local_mean) * float(local_count), float(local_count)], dtype=torch.float64, device=device)
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group)
+    return float(t[0] / t[1])
+
+
+def max_over_ranks(value, device="cpu", group=None):
+    """A timing taken on every rank, as the slowest rank saw it."""
+    t = torch.tensor([float(value)], dtype=torch.float64, device=device)
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+    return float(t[0])
