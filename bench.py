@@ -113,7 +113,9 @@ def cpu_prefill_tokens_per_s(consts, T, B, threads):
     import oracle_lib
     from presk_b200 import Host
 
-    os.environ.setdefault("OMP_NUM_THREADS", str(threads))
+    # all the host's cores, also under torchrun (which sets OMP_NUM_THREADS=1 for its workers);
+    # set before the OpenMP runtime of the oracle's library is loaded
+    os.environ["OMP_NUM_THREADS"] = str(threads)
     orc = oracle_lib.load()
     times = {}
     Ts, Bs = min(T, 128), 1
