@@ -660,7 +660,11 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
             bool all_bf16 = L.out.dtype == PSK_BF16 && L.kdtype == PSK_BF16;
             for (int i = 0; i < L.n_in; ++i) all_bf16 = all_bf16 && L.in[i].dtype == PSK_BF16;
             const int64_t work = (int64_t)E.rows * E.colv;
-            const int prog = all_bf16 ? match_program(l) : -1;
+            // a compile-time program also takes row-wise scalars of another real type (a norm's f32 root)
+            bool prog_ok = L.out.dtype == PSK_BF16 && L.kdtype == PSK_BF16;
+            for (int i = 0; i < L.n_in; ++i)
+                prog_ok = prog_ok && (L.in[i].dtype == PSK_BF16 || (E.cs[i] == 0 && (L.in[i].dtype == PSK_F32 || L.in[i].dtype == PSK_F16 || L.in[i].dtype == PSK_E8M15)));
+            const int prog = prog_ok ? match_program(l) : -1;
             if (prog >= 0) {
                 switch (prog) {
                 case EW_ADD: launch_prog<EW_ADD>(e, E); break;

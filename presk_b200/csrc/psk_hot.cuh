@@ -311,7 +311,14 @@ __global__ void __launch_bounds__(256, 2) k_ew_prog(const __grid_constant__ EwPa
                 for (int i = 0; i < NIN; ++i) {
                     const uint16_t *p = (const uint16_t *)E.in[i] + (int64_t)rr[u] * E.rs[i];
                     if (E.cs[i]) raw[u][i] = *reinterpret_cast<const uint4 *>(p + cc[u]);
-                    else { const uint32_t h = *p; raw[u][i] = make_uint4(h | (h << 16), h | (h << 16), h | (h << 16), h | (h << 16)); }
+                    else {
+                        // one value for the whole row, of any real type: the kernel's type is bf16, so the
+                        // value it sees is the stored one rounded to bf16 at the kernel's edge
+                        uint32_t dummy = 0;
+                        const float v = edge_round(load_real(E.in[i], E.dt[i], (int64_t)rr[u] * E.rs[i]), PSK_BF16, E.dt[i], &dummy);
+                        const uint32_t h = f32_bits(v) >> 16;
+                        raw[u][i] = make_uint4(h | (h << 16), h | (h << 16), h | (h << 16), h | (h << 16));
+                    }
                 }
             }
         }

@@ -62,39 +62,39 @@ PSK_LIBM_DEV float lm_scalbnf(float x, int n)
     return y * lm_bits_f((uint32_t)(0x7f + n) << 23);
 }
 
+// exp, written with selections where the original branches on the argument's
+// range, so that the lanes of a warp stay together: the three cases of the
+// reduction (k = 0, k = -1 or 1, k computed) share one sequence of operations,
+// because with k = 0 that sequence leaves x as it is (x - 0·ln2hi = x, lo = 0);
+// y·2^0 = y stands for "no scaling"; |x| <= 2^-14 selects 1 + x at the end.
+// Only the rare cases branch: NaN, overflow, the results below 2^-126.
 PSK_LIBM_DEV float lm_expf(float x)
 {
     const float ln2hi = 6.9314575195e-1f, ln2lo = 1.4286067653e-6f, invln2 = 1.4426950216e+0f;
     const float P1 = 1.6666625440e-1f, P2 = -2.7667332906e-3f;
-    uint32_t hx = lm_f_bits(x);
-    int sign = (int)(hx >> 31);
-    hx &= 0x7fffffffu;
+    const uint32_t ux = lm_f_bits(x);
+    const int sign = (int)(ux >> 31);
+    const uint32_t hx = ux & 0x7fffffffu;
     if (hx >= 0x42aeac50u) { // |x| >= 87.33655 or NaN
         if (hx > 0x7f800000u) return x;
         if (hx >= 0x42b17218u && !sign) return x * 0x1p127f; // overflow
         if (sign && hx >= 0x42cff1b5u) return 0.0f;          // underflow
     }
-    float hi, lo;
-    int k;
-    if (hx > 0x3eb17218u) { // |x| > 0.5 ln2
-        if (hx > 0x3f851592u) // |x| > 1.5 ln2
-            k = (int)(invln2 * x + (sign ? -0.5f : 0.5f));
-        else
-            k = 1 - sign - sign;
-        hi = x - (float)k * ln2hi;
-        lo = (float)k * ln2lo;
-        x = hi - lo;
-    } else if (hx > 0x39000000u) { // |x| > 2^-14
-        k = 0;
-        hi = x;
-        lo = 0.0f;
-    } else {
-        return 1.0f + x;
-    }
-    float xx = x * x;
-    float c = x - xx * (P1 + xx * P2);
-    float y = 1.0f + (x * c / (2.0f - c) - lo + hi);
-    return k == 0 ? y : lm_scalbnf(y, k);
+    const float half = sign ? -0.5f : 0.5f;
+    int k = (int)(invln2 * x + half);
+    k = hx > 0x3f851592u ? k : 1 - sign - sign; // |x| <= 1.5 ln2
+    k = hx > 0x3eb17218u ? k : 0;               // |x| <= 0.5 ln2
+    const float fk = (float)k;
+    const float hi = x - fk * ln2hi;
+    const float lo = fk * ln2lo;
+    const float xr = hi - lo;
+    const float xx = xr * xr;
+    const float c = xr - xx * (P1 + xx * P2);
+    const float y = 1.0f + (xr * c / (2.0f - c) - lo + hi);
+    float r;
+    if (k >= -126 && k <= 127) r = y * lm_bits_f((uint32_t)(0x7f + k) << 23);
+    else r = lm_scalbnf(y, k);
+    return hx > 0x39000000u ? r : 1.0f + x; // |x| <= 2^-14
 }
 
 PSK_LIBM_DEV float lm_logf(float x)
