@@ -298,6 +298,17 @@ __global__ void __launch_bounds__(256, 2) k_ew_prog(const __grid_constant__ EwPa
     constexpr int NIN = EwArity<PROG>::value;
     const uint32_t total = E.rows * E.colv;
     const uint32_t stride = gridDim.x * blockDim.x;
+    // an operand that is one value for the whole launch (a rank-0 divisor) is read once
+    uint32_t whole[NIN];
+#pragma unroll
+    for (int i = 0; i < NIN; ++i) {
+        whole[i] = 0;
+        if (E.cs[i] == 0 && E.rs[i] == 0) {
+            uint32_t dummy = 0;
+            const uint32_t h = f32_bits(edge_round(load_real(E.in[i], E.dt[i], 0), PSK_BF16, E.dt[i], &dummy)) >> 16;
+            whole[i] = h | (h << 16);
+        }
+    }
     for (uint32_t idx0 = blockIdx.x * blockDim.x + threadIdx.x; idx0 < total; idx0 += stride * UNR) {
         uint4 raw[UNR][NIN];
         uint32_t rr[UNR], cc[UNR];
@@ -311,6 +322,7 @@ __global__ void __launch_bounds__(256, 2) k_ew_prog(const __grid_constant__ EwPa
                 for (int i = 0; i < NIN; ++i) {
                     const uint16_t *p = (const uint16_t *)E.in[i] + (int64_t)rr[u] * E.rs[i];
                     if (E.cs[i]) raw[u][i] = *reinterpret_cast<const uint4 *>(p + cc[u]);
+                    else if (E.rs[i] == 0) raw[u][i] = make_uint4(whole[i], whole[i], whole[i], whole[i]);
                     else {
                         // one value for the whole row, of any real type: the kernel's type is bf16, so the
                         // value it sees is the stored one rounded to bf16 at the kernel's edge
