@@ -1134,12 +1134,131 @@ struct psk_host {
         return layernorm(param("ln.γ"), param("ln.β"), y, 1e-5);
     }
 
+
+    // ===========================================================================
+    // examples/corpus/nlp/05_gpt.psk (BASELINE config 2). Outside training a dropout is
+    // a mask of ones, made by the host, and the product with it is still a launch
+    // (host.rs:1626).
+    // ===========================================================================
+    std::map<std::string, Tensor> ones_cache;
+    Tensor ones_like(const std::string &site, const Tensor &x)
+    {
+        int d = rz.dtype_at(site);
+        std::string key = show(x.axes) + "|" + std::to_string(d);
+        auto hit = ones_cache.find(key);
+        if (hit != ones_cache.end()) return hit->second;
+        Tensor out = fresh(x.axes, d);
+        psk_launch l;
+        memset(&l, 0, sizeof l);
+        l.op = PSK_OP_IOTA;
+        l.kind = PSK_IOTA_FILL;
+        l.dtype = d;
+        l.fparam[0] = 1.0;
+        set_space(l, x.axes, {});
+        set_operand(l.out, out, contiguous(x.axes), {});
+        int64_t before = launches;
+        std::string keep = log;
+        run(l, "dropout_mask", {}, out);
+        launches = before;
+        log = keep;
+        ones_cache[key] = out;
+        return out;
+    }
+
+    // 05_gpt.psk LayerNorm: %0 θ, %1 x; μ %2, sub %3, pow %4, σ2 %5, sub %6, lit %7, real %8, add %9, sqrt %10, div %11, γ %12, mul %13, β %14, add %15
+    Tensor gpt_layernorm(const Tensor &gamma, const Tensor &beta, const Tensor &x)
+    {
+        const std::string f = "LayerNorm.apply";
+        Tensor mu = reduce_axis(f + "/%2", PSK_REDUCE_MEAN, "model", x);
+        Tensor d2 = fused(f + "/%4", {Bn(PSK_SUB, 0, 1), U(PSK_POW, S(0), 2)}, {&x, &mu});
+        Tensor var = reduce_axis(f + "/%5", PSK_REDUCE_MEAN, "model", d2);
+        Tensor eps = scalar(f + "/%8", 1e-5);
+        Tensor sd = fused(f + "/%10", {Bn(PSK_ADD, 0, 1), U(PSK_SQRT, S(0))}, {&var, &eps});
+        return fused(f + "/%15", {Bn(PSK_SUB, 0, 1), Bn(PSK_DIV, S(0), 2), Bn(PSK_MUL, S(1), 3), Bn(PSK_ADD, S(2), 4)}, {&x, &mu, &sd, &gamma, &beta});
+    }
+
+    Tensor gpt_linear(const std::string &prefix, int64_t l, const Tensor &x)
+    {
+        Tensor y = dot("Linear.apply/%3", x, layer(param(prefix + ".w"), l));
+        return binary("Linear.apply/%5", PSK_ADD, y, layer(param(prefix + ".b"), l));
+    }
+
+    // SelfAttention.apply: %0 θ, %1 x, %2 mask, %3 kd
+    Tensor gpt_attention(int64_t l, const Tensor &x, const Tensor &mask)
+    {
+        const std::string f = "SelfAttention.apply";
+        const int64_t D = C("D"), H = C("H"), HD = D / H;
+        Tensor q = split_heads(f + "/%6", H, HD, gpt_linear("blocks.attn.wq", l, x));
+        Tensor k = split_heads(f + "/%9", H, HD, gpt_linear("blocks.attn.wk", l, x));
+        Tensor v = split_heads(f + "/%12", H, HD, gpt_linear("blocks.attn.wv", l, x));
+        Tensor se = ein(f + "/%13", {"batch", "heads", "seq", "seq2"}, {{"batch", "heads", "seq", "hd"}, {"batch", "heads", "seq2", "hd"}}, {&q, &k});
+        Tensor hdr = scalar(f + "/%15", (double)HD);
+        Tensor rt = unary(f + "/%16", PSK_SQRT, hdr);
+        Tensor s = binary(f + "/%17", PSK_DIV, se, rt);
+        Tensor sm = softmax(f + "/%18", "seq2", s, &mask);
+        Tensor ones = ones_like(f + "/%20", sm);
+        Tensor a = binary(f + "/%21", PSK_MUL, sm, ones);
+        Tensor o = ein(f + "/%22", {"batch", "heads", "seq", "hd"}, {{"batch", "heads", "seq", "seq2"}, {"batch", "heads", "seq2", "hd"}}, {&a, &v});
+        Tensor m = merge_heads(f + "/%23", H, HD, o);
+        return gpt_linear("blocks.attn.wo", l, m);
+    }
+
+    // Block.apply: %0 θ, %1 s, %2 mask
+    Tensor gpt_block(int64_t l, const Tensor &x, const Tensor &mask)
+    {
+        const std::string f = "Block.apply";
+        Tensor n1 = gpt_layernorm(layer(param("blocks.ln1.γ"), l), layer(param("blocks.ln1.β"), l), x);
+        Tensor at = gpt_attention(l, n1, mask);
+        Tensor ones = ones_like(f + "/%19", at);
+        Tensor h = fused(f + "/%21", {Bn(PSK_MUL, 0, 1), Bn(PSK_ADD, 2, S(0))}, {&at, &ones, &x});
+        Tensor n2 = gpt_layernorm(layer(param("blocks.ln2.γ"), l), layer(param("blocks.ln2.β"), l), h);
+        Tensor up = gpt_linear("blocks.ff.up", l, n2);
+        Tensor g = unary("FeedForward.apply/%4", PSK_GELU, up);
+        Tensor dn = gpt_linear("blocks.ff.down", l, g);
+        Tensor ones2 = ones_like(f + "/%27", dn);
+        return fused(f + "/%29", {Bn(PSK_MUL, 0, 1), Bn(PSK_ADD, 2, S(0))}, {&dn, &ones2, &h});
+    }
+
+    // GPT.apply: %0 θ, %1 ids, %2 k
+    Tensor gpt_apply(const Tensor &ids)
+    {
+        const std::string f = "GPT.apply";
+        const int64_t T = ids.axes[1].len, L = C("L");
+        Tensor mask = causal_mask(f + "/%3", "seq", T);
+        Tensor et = embed(f + "/%5", param("tok"), ids);
+        Tensor pos = positions(f + "/%7", "seq", T);
+        Tensor posw = param("pos");
+        if (posw.axes[0].len < T) raise(PSK_E7001, "GPT: the position table has " + std::to_string(posw.axes[0].len) + " rows and the sequence " + std::to_string(T));
+        Tensor ep = embed(f + "/%8", posw, pos);
+        Tensor ones = ones_like(f + "/%14", et);
+        Tensor x = fused(f + "/%15", {Bn(PSK_ADD, 0, 1), Bn(PSK_MUL, S(0), 2)}, {&et, &ep, &ones});
+        x.axes.back().name = "model";
+        for (int64_t l = 0; l < L; ++l) {
+            x = gpt_block(l, x, mask);
+            x.axes.back().name = "model";
+        }
+        Tensor h = gpt_layernorm(param("lnf.γ"), param("lnf.β"), x);
+        Tensor logits = dot(f + "/%24", h, param("head"));
+        logits.axes.back().name = "vocab";
+        return logits;
+    }
+
+    Tensor gpt_loss(const Tensor &ids, const Tensor &y)
+    {
+        Tensor logits = gpt_apply(ids);
+        Tensor ce = cross_entropy("loss/%6", logits, y);
+        return reduce_all("loss/%7", PSK_REDUCE_MEAN, ce);
+    }
+
     Tensor call(const std::string &entry, const std::vector<Tensor> &in)
     {
         auto need = [&](size_t n) { if (in.size() != n) raise(PSK_E7001, model + "." + entry + " takes " + std::to_string(n) + " inputs"); };
         if (model == "llama") {
             if (entry == "apply") { need(1); return llama_apply(in[0]); }
             if (entry == "loss") { need(2); return llama_loss(in[0], in[1]); }
+        } else if (model == "gpt") {
+            if (entry == "apply") { need(1); return gpt_apply(in[0]); }
+            if (entry == "loss") { need(2); return gpt_loss(in[0], in[1]); }
         } else if (model == "mlp") {
             if (entry == "apply") { need(1); return mlp_apply(in[0]); }
             if (entry == "loss") { need(2); return mlp_loss(in[0], in[1]); }
@@ -1160,7 +1279,7 @@ struct psk_host {
     Axes input_axes(const std::string &entry, int i, const psk_value &v)
     {
         std::vector<std::string> names;
-        if (model == "llama") names = {"batch", "seq"};
+        if (model == "llama" || model == "gpt") names = {"batch", "seq"};
         else if (model == "mlp") names = i == 0 ? std::vector<std::string>{"batch", "model"} : std::vector<std::string>{"batch"};
         else if (model == "layernorm" || model == "rmsnorm") {
             // ℝ[..., model: D] with a prefix of named axes
@@ -1224,7 +1343,7 @@ int psk_host_prepare(psk_host *h, const char *model, const char *consts)
 {
     HOST_TRY(h, {
         h->model = model ? model : "";
-        static const char *known[] = {"llama", "mlp", "layernorm", "rmsnorm", "contract_ln"};
+        static const char *known[] = {"llama", "gpt", "mlp", "layernorm", "rmsnorm", "contract_ln"};
         bool ok = false;
         for (auto k : known) ok |= h->model == k;
         if (!ok) raise(PSK_E7001, "no model `" + h->model + "`");

@@ -76,3 +76,68 @@ def give(host, params):
     for k, v in params.items():
         host.set_param(k, v)
     return host
+
+
+GPT_TINY = dict(V=65, D=32, H=4, L=2)
+
+
+def gpt_params(c, T, seed=0):
+    """examples/corpus/nlp/05_gpt.psk's parameters: normal(0.02) tables, xavier linear maps, zero biases;
+    the head drawn normal(0.02) too so that the logits are not all zero (BASELINE config 2)."""
+    rng = np.random.default_rng(seed)
+    V, D, L = c["V"], c["D"], c["L"]
+    n = lambda *s: (rng.standard_normal(s) * 0.02).astype(np.float32)
+
+    def xav(*s):
+        b = np.sqrt(6.0 / (s[-2] + s[-1]))
+        return rng.uniform(-b, b, size=s).astype(np.float32)
+
+    p = {"tok": n(V, D), "pos": n(T, D), "head": n(D, V), "lnf.γ": np.ones(D, np.float32), "lnf.β": np.zeros(D, np.float32)}
+    for ln in ("ln1", "ln2"):
+        p[f"blocks.{ln}.γ"] = (1 + 0.1 * rng.standard_normal((L, D))).astype(np.float32)
+        p[f"blocks.{ln}.β"] = (0.1 * rng.standard_normal((L, D))).astype(np.float32)
+    for w in ("wq", "wk", "wv", "wo"):
+        p[f"blocks.attn.{w}.w"] = xav(L, D, D)
+        p[f"blocks.attn.{w}.b"] = (0.01 * rng.standard_normal((L, D))).astype(np.float32)
+    p["blocks.ff.up.w"], p["blocks.ff.up.b"] = xav(L, D, 4 * D), np.zeros((L, 4 * D), np.float32)
+    p["blocks.ff.down.w"], p["blocks.ff.down.b"] = xav(L, 4 * D, D), np.zeros((L, D), np.float32)
+    return p
+
+
+def gpt_numpy(p, c, ids, y=None):
+    """05_gpt.psk in float64 numpy (outside training: dropout is the identity)."""
+    from math import erf
+    D, H, L = c["D"], c["H"], c["L"]
+    HD = D // H
+    B, T = ids.shape
+    f = lambda a: np.asarray(a, np.float64)
+
+    def ln(g, b, x):
+        mu = x.mean(-1, keepdims=True)
+        var = ((x - mu) ** 2).mean(-1, keepdims=True)
+        return (x - mu) / np.sqrt(var + 1e-5) * f(g) + f(b)
+
+    verf = np.vectorize(erf)
+    x = f(p["tok"])[ids] + f(p["pos"])[np.arange(T)]
+    mask = np.tril(np.ones((T, T), bool))
+    for l in range(L):
+        h = ln(p["blocks.ln1.γ"][l], p["blocks.ln1.β"][l], x)
+        lin = lambda w, z: z @ f(p[f"blocks.attn.{w}.w"][l]) + f(p[f"blocks.attn.{w}.b"][l])
+        sh = lambda z: z.reshape(B, T, H, HD).transpose(0, 2, 1, 3)
+        q, k, v = sh(lin("wq", h)), sh(lin("wk", h)), sh(lin("wv", h))
+        s = np.einsum("bhsd,bhtd->bhst", q, k) / np.sqrt(HD)
+        s = np.where(mask, s, -np.inf)
+        a = np.exp(s - s.max(-1, keepdims=True))
+        a = a / a.sum(-1, keepdims=True)
+        o = np.einsum("bhst,bhtd->bhsd", a, v).transpose(0, 2, 1, 3).reshape(B, T, D)
+        x = x + lin("wo", o)
+        h = ln(p["blocks.ln2.γ"][l], p["blocks.ln2.β"][l], x)
+        u = h @ f(p["blocks.ff.up.w"][l]) + f(p["blocks.ff.up.b"][l])
+        g = u * (1 + verf(u / np.sqrt(2.0))) / 2
+        x = x + g @ f(p["blocks.ff.down.w"][l]) + f(p["blocks.ff.down.b"][l])
+    logits = ln(p["lnf.γ"], p["lnf.β"], x) @ f(p["head"])
+    if y is None:
+        return logits
+    m = logits.max(-1, keepdims=True)
+    lse = np.log(np.exp(logits - m).sum(-1)) + m[..., 0]
+    return (lse - np.take_along_axis(logits, y[..., None], -1)[..., 0]).mean()

@@ -123,3 +123,39 @@ def test_contract_ln_config3_and_overflow_guard(cuda, oracle, dtype, scale, over
         # LayerNorm outputs are O(1); the dot's sums differ in their last bits and each site rounds to 11 or 16 bits
         tol = 2.0**-8 if dtype == "f16" else 2.0**-12
         assert np.abs(got - want).max() <= tol * max(1.0, np.abs(want).max())
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_gpt_config2_bit_exact_under_sequential_order(cuda, oracle, dtype):
+    """BASELINE config 2's program (05_gpt.psk) at reduced constants; its full shape runs under device order below."""
+    c = models.GPT_TINY
+    T = 16
+    p = models.gpt_params(c, T)
+    rng = np.random.default_rng(8)
+    ids = rng.integers(0, c["V"], size=(3, T), dtype=np.int64)
+    y = rng.integers(0, c["V"], size=(3, T), dtype=np.int64)
+    got, want = both(cuda, oracle, dtype, "gpt", c, p, "apply", [ids], (3, T, c["V"]))
+    assert_same_bits(got, want)
+    got, want = both(cuda, oracle, dtype, "gpt", c, p, "loss", [ids, y], ())
+    assert_same_bits(got, want)
+
+
+def test_gpt_config2_full_shape_mixed_realization(cuda, oracle):
+    """Config 2 at its stated shape: 4 layers, d_model 128, 4 heads, ctx 64, vocab 65, batch 256 (a
+    quarter of it on the CPU side of the comparison), a mixed bf16/f32 assignment, device order."""
+    c = dict(V=65, D=128, H=4, L=4)
+    T, B = 64, 256
+    p = models.gpt_params(c, T)
+    rng = np.random.default_rng(2)
+    ids = rng.integers(0, c["V"], size=(B, T), dtype=np.int64)
+    y = rng.integers(0, c["V"], size=(B, T), dtype=np.int64)
+    rz = {"default": "bf16", "order": {"kind": "device"}, "storage": {"LayerNorm.apply/%2": "f32", "LayerNorm.apply/%5": "f32", "LayerNorm.apply/%10": "f32", "GPT.apply/%24": "f32", "loss/%6": "f32", "loss/%7": "f32"}}
+    h = models.give(Host(cuda, rz).prepare("gpt", **c), p)
+    loss = float(h.call("loss", [ids, y], ()))
+    logits = h.call("apply", [ids[:64]], (64, T, c["V"]))
+    ho = models.give(Host(oracle.vtable(), dict(rz, order={"kind": "sequential"})).prepare("gpt", **c), p)
+    want = ho.call("apply", [ids[:64]], (64, T, c["V"]))
+    assert np.abs(logits - want).max() <= 2.0**-5 * np.abs(want).max()
+    exact = models.gpt_numpy(p, c, ids[:16])
+    assert np.abs(logits[:16] - exact).max() <= 1e-3 * max(1.0, np.abs(exact).max()) * 50  # the budget's order of magnitude at bf16
+    assert abs(loss - float(models.gpt_numpy(p, c, ids[:64], y[:64]))) < 0.05

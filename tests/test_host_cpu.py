@@ -115,3 +115,26 @@ def test_mlp_config1_shapes(oracle):
     lg = hid @ p["l2.w"]
     want = (np.log(np.exp(lg - lg.max(-1, keepdims=True)).sum(-1)) + lg.max(-1) - lg[np.arange(64), y]).mean()
     np.testing.assert_allclose(loss, want, rtol=1e-5)
+
+
+def test_gpt_config2_matches_numpy_and_its_launch_list(oracle):
+    """examples/corpus/nlp/05_gpt.psk at small constants: LayerNorm, biased linear maps, split_heads and
+    merge_heads, masked softmax, GELU, learned positions, dropout masks of ones."""
+    c = models.GPT_TINY
+    T = 16
+    p = models.gpt_params(c, T)
+    rng = np.random.default_rng(8)
+    ids = rng.integers(0, c["V"], size=(3, T), dtype=np.int64)
+    y = rng.integers(0, c["V"], size=(3, T), dtype=np.int64)
+    h = models.give(Host(oracle.vtable(), "f32").prepare("gpt", **c), p)
+    h.set_logging(True)
+    logits = h.call("apply", [ids], (3, T, c["V"]))
+    want = models.gpt_numpy(p, c, ids)
+    np.testing.assert_allclose(logits, want, rtol=0, atol=3e-5 * np.abs(want).max() + 1e-6)
+    ln = ["mean axis model", "fused 2 steps", "mean axis model", "fused 2 steps", "fused 4 steps"]
+    lin = ["dot", "add"]
+    block = (ln + (lin + ["split_heads 4x8"]) * 3 + ["ein[batch, heads, seq, seq2]", "sqrt", "div", "softmax axis seq2 where", "mul", "ein[batch, heads, seq, hd]", "merge_heads 4x8"]
+             + lin + ["fused 2 steps"] + ln + lin + ["gelu"] + lin + ["fused 2 steps"])
+    assert h.launch_log() == ["causal_mask seq", "embed", "positions seq", "embed", "fused 2 steps"] + block * c["L"] + ln + ["dot"]
+    loss = h.call("loss", [ids, y], ())
+    np.testing.assert_allclose(loss, models.gpt_numpy(p, c, ids, y), rtol=3e-6)
