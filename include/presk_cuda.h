@@ -74,7 +74,14 @@ typedef enum {
     PSK_OP_EMBED = 6,    /* lower.rs:1421 */
     PSK_OP_COPY = 7,     /* lower.rs:1554-1667: slice, concat, split_heads, merge_heads, index, broadcast_like */
     PSK_OP_IOTA = 8,     /* lower.rs:1706-1750: positions, causal_mask, one_hot, fill */
-    PSK_OP_CONVERT = 9   /* host.rs:809-829: Buf::of(to, b.to_f64()) at a kernel's edge */
+    PSK_OP_CONVERT = 9,  /* host.rs:809-829: Buf::of(to, b.to_f64()) at a kernel's edge */
+    PSK_OP_MAGNITUDE = 10 /* presk-precision/src/envelope.rs:29-127: a site's max |x|, least non-zero |x|, least
+                             and greatest x. Output: four u32 words, merged into what they hold (so that one
+                             slot collects several launches and several ranks): [0] bits of max |x|, start 0;
+                             [1] bits of the least non-zero |x|, start 0x7f800000; [2], [3] least and greatest
+                             x under the order-preserving map u = b ^ (b >> 31 ? 0xffffffff : 0x80000000) of
+                             its bits b, start 0xff800000 and 0x007fffff. NaNs are passed over. No counterpart
+                             among the reference's kernels: it measures envelopes on its exact interpreter. */
 } psk_op;
 
 /* Elementary operations of a fusion group's steps (lower.rs:184-226). */
@@ -350,6 +357,15 @@ int psk_host_call(psk_host *h, const char *entry, const psk_value *inputs, int32
  * queued, not waited for: psk_exec_sync (or the table's `sync`) ends them and
  * reports the overflow guard. */
 int psk_host_call_device(psk_host *h, const char *entry, const psk_value *inputs, int32_t n_inputs, void **out, int32_t *out_dtype, int64_t *out_numel);
+
+/* `presk calibrate` on this executor (presk-driver/src/precision.rs:65-117 measures on the exact
+ * interpreter; this measures the values of the realization being run): while on, every launch's
+ * real output is folded into its site's magnitudes. psk_host_envelope returns one line a site,
+ * "site\tmax|x|\tmin non-zero |x|\tlo\thi", sorted by site, of everything seen since calibration was
+ * switched on; the text belongs to the host until the next call. Ranks that shard a batch merge
+ * their envelopes with one max-reduction (presk_b200/shard.py). */
+void psk_host_set_calibrating(psk_host *h, int on);
+const char *psk_host_envelope(psk_host *h);
 
 /* Launch statistics of the last call (Backend::launch_stats): launches, and
  * the kernel names in order, newline-separated (for the launch-list tests). */

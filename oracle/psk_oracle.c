@@ -660,6 +660,19 @@ static int psk_oracle_run_merged(const psk_launch *l, void *const *table, uint32
             }
         }
         break;
+    case PSK_OP_MAGNITUDE: { /* presk-precision/src/envelope.rs: max |x|, least non-zero |x|, least and greatest x */
+        uint32_t *o = (uint32_t *)outp;
+        for (int64_t i = 0; i < l->in[0].numel; ++i) {
+            float x = load_real(in[0].p, l->in[0].dtype, i);
+            if (x != x) continue;
+            uint32_t b = f2u(x), a = b & 0x7fffffffu, ord = b ^ ((b >> 31) ? 0xffffffffu : 0x80000000u);
+            if (a > o[0]) o[0] = a;
+            if (a != 0 && a < o[1]) o[1] = a;
+            if (ord < o[2]) o[2] = ord;
+            if (ord > o[3]) o[3] = ord;
+        }
+        break;
+    }
     default:
         return PSK_E7001;
     }

@@ -21,7 +21,7 @@ DTYPE_BYTES = {F64: 8, F32: 4, BF16: 2, I64: 8, F16: 2, E8M15: 3, I8: 1, E4M3: 1
 OK, E7001, E7005, E7007, E10001 = 0, 7001, 7005, 7007, 10001
 
 # psk_op
-OP_FUSED, OP_CONTRACT, OP_REDUCE, OP_SOFTMAX, OP_XENT, OP_ARGMAX, OP_EMBED, OP_COPY, OP_IOTA, OP_CONVERT = range(10)
+OP_FUSED, OP_CONTRACT, OP_REDUCE, OP_SOFTMAX, OP_XENT, OP_ARGMAX, OP_EMBED, OP_COPY, OP_IOTA, OP_CONVERT, OP_MAGNITUDE = range(11)
 
 # psk_prim
 (ADD, SUB, MUL, DIV, MAX, MIN, NEG, EXP, LOG, TANH, SQRT, SIN, COS, ABS, GELU, GELU_DERIV, RELU, HEAVISIDE, SIGN, SIGMOID, POW, REAL) = range(22)
@@ -110,6 +110,8 @@ PROTOTYPES = {
     "psk_host_init_param": (C.c_int, [C.c_void_p, C.c_char_p, C.c_uint64, C.c_double, C.POINTER(C.c_int64), C.c_int32]),
     "psk_host_call": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(Value), C.c_int32, C.c_void_p, C.c_int32, C.c_int64, C.POINTER(C.c_int64)]),
     "psk_host_call_device": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(Value), C.c_int32, C.POINTER(C.c_void_p), C.POINTER(C.c_int32), C.POINTER(C.c_int64)]),
+    "psk_host_set_calibrating": (None, [C.c_void_p, C.c_int]),
+    "psk_host_envelope": (C.c_char_p, [C.c_void_p]),
     "psk_host_launches": (C.c_int64, [C.c_void_p]),
     "psk_host_launch_log": (C.c_char_p, [C.c_void_p]),
     "psk_host_set_logging": (None, [C.c_void_p, C.c_int]),

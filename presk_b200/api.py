@@ -204,6 +204,18 @@ class Host:
         self._check(self.lib.psk_host_call_device(self.handle, entry.encode(), vals, len(inputs), C.byref(out), C.byref(dt), C.byref(n)))
         return out.value, dt.value, n.value
 
+    def set_calibrating(self, on=True):
+        """`presk calibrate`: fold every launch's output into its site's magnitudes from now on."""
+        self.lib.psk_host_set_calibrating(self.handle, 1 if on else 0)
+
+    def envelope(self):
+        """{site: (max |x|, least non-zero |x|, lo, hi)} of everything seen while calibrating."""
+        out = {}
+        for line in self.lib.psk_host_envelope(self.handle).decode().splitlines():
+            site, mx, mn, lo, hi = line.split("\t")
+            out[site] = (float(mx), float(mn), float(lo), float(hi))
+        return out
+
     def launches(self):
         return self.lib.psk_host_launches(self.handle)
 

@@ -617,7 +617,7 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
     L.fparam = (float)l->fparam[0];
     L.status = e->status;
     L.ovf = L.guarded ? next_flag(e, l) : e->flags;
-    if (l->op != PSK_OP_EMBED && l->op != PSK_OP_IOTA) coalesce_outer(L);
+    if (l->op != PSK_OP_EMBED && l->op != PSK_OP_IOTA && l->op != PSK_OP_MAGNITUDE) coalesce_outer(L);
     L.total = 1;
     for (int a = 0; a < L.n_outer; ++a) L.total *= L.dims[a];
     L.inner = 1;
@@ -633,7 +633,7 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
     e->last_kernel = "other";
     e->last_flops = 0;
     int rc = PSK_OK;
-    if (L.total == 0) {
+    if (L.total == 0 && l->op != PSK_OP_MAGNITUDE) {
         // an empty result: nothing to store
     } else switch (l->op) {
     case PSK_OP_FUSED: {
@@ -784,6 +784,22 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
             && vec8_operand(L.in[0], L.dims, L.n_outer + 1, false) && vec8_operand(L.out, L.dims, L.n_outer + 1, true)
             && (!L.masked || L.iparam[0] == 1 || L.in[1].stride[L.n_outer] == 1);
         if (rows && n * 4 * 4 <= 96 * 1024) {
+            // flat rows: every outer axis of the scores walks contiguous rows; the causal mask's row is the
+            // position along the last outer axis
+            bool flat = L.total < 0x7fffffffll;
+            {
+                int64_t expect = n;
+                for (int a = L.n_outer - 1; a >= 0 && flat; --a) {
+                    flat = L.in[0].stride[a] == expect && L.out.stride[a] == expect;
+                    expect *= L.dims[a];
+                }
+                if (flat && L.masked) {
+                    flat = L.iparam[0] == 1 && L.n_outer >= 1 && L.in[1].stride[L.n_outer - 1] == n;
+                    for (int a = 0; a + 1 < L.n_outer && flat; ++a) flat = L.in[1].stride[a] == 0;
+                    L.iparam[3] = L.n_outer >= 1 ? L.dims[L.n_outer - 1] : 1;
+                }
+            }
+            L.iparam[2] = flat ? 1 : 0;
             if (!e->softmax_attr_set) {
                 CUDA_TRY(e, cudaFuncSetAttribute(k_softmax_rows_smem<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
                 e->softmax_attr_set = true;
@@ -826,6 +842,13 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
     case PSK_OP_CONVERT: {
         int64_t n = L.total;
         k_convert<<<grid_for(e, n, 256, 8), 256, 0, e->stream>>>(L.in[0].p, L.in[0].dtype, const_cast<void *>(L.out.p), L.out.dtype, n, L.guarded, L.ovf);
+        e->kernels += 1;
+        break;
+    }
+    case PSK_OP_MAGNITUDE: {
+        // the input is read flat: its `numel` elements from its offset
+        const int64_t n = l->in[0].numel;
+        if (n > 0) k_magnitude<<<grid_for(e, n, 256, 8), 256, 0, e->stream>>>(L.in[0].p, L.in[0].dtype, n, (uint32_t *)const_cast<void *>(L.out.p));
         e->kernels += 1;
         break;
     }

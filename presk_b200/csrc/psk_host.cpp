@@ -351,6 +351,13 @@ struct psk_host {
     std::map<std::string, int64_t> consts;
     std::map<std::string, Tensor> params;
     int64_t launches = 0;
+    // calibration: one slot of four words a site, on the executor (PSK_OP_MAGNITUDE)
+    bool calibrating = false;
+    std::map<std::string, int> slot_of;
+    std::shared_ptr<Storage> slots;
+    static constexpr int kMaxSites = 4096;
+    std::string current_site;
+    std::string envelope_text;
     bool logging = false;
     std::string log;
     Tensor last_result;
@@ -410,6 +417,44 @@ struct psk_host {
         check(vt->run(vt->self, &l, table.data()), name.c_str());
         launches += 1;
         if (logging) { log += name; log += '\n'; }
+        if (calibrating && !out.is_index && out.numel() > 0 && !current_site.empty()) observe(out);
+    }
+
+    // Folds a launch's output into its site's magnitudes.
+    void observe(const Tensor &out)
+    {
+        if (!slots) {
+            slots = std::make_shared<Storage>(vt, (size_t)kMaxSites * 16);
+            std::vector<uint32_t> init((size_t)kMaxSites * 4);
+            for (int i = 0; i < kMaxSites; ++i) { init[4 * i] = 0u; init[4 * i + 1] = 0x7f800000u; init[4 * i + 2] = 0xff800000u; init[4 * i + 3] = 0x007fffffu; }
+            check(vt->upload(vt->self, slots->p, init.data(), init.size() * 4), "calibrate");
+        }
+        auto it = slot_of.find(current_site);
+        if (it == slot_of.end()) {
+            if ((int)slot_of.size() >= kMaxSites) raise(PSK_E7001, "calibrate: more sites than the envelope holds");
+            it = slot_of.emplace(current_site, (int)slot_of.size()).first;
+        }
+        psk_launch m;
+        memset(&m, 0, sizeof m);
+        m.name = "magnitude";
+        m.op = PSK_OP_MAGNITUDE;
+        m.dtype = PSK_F32;
+        m.n_inputs = 1;
+        m.n_outer = 1;
+        m.dims[0] = 4;
+        set_operand(m.in[0], out, {0}, {0});
+        m.out.dtype = PSK_I64; // four raw words; read as integers, never rounded
+        m.out.offset = 0;
+        m.out.numel = 4;
+        m.out.stride[0] = 1;
+        void *table[2] = {out.ptr(), (uint8_t *)slots->p + (size_t)it->second * 16};
+        check(vt->run(vt->self, &m, table), "magnitude");
+    }
+
+    int site_dtype(const std::string &site)
+    {
+        current_site = site;
+        return rz.dtype_at(site);
     }
 
     // An operand's strides over an iteration space, given where each of its
@@ -447,7 +492,7 @@ struct psk_host {
     {
         auto hit = scalars.find({site, x});
         if (hit != scalars.end()) return hit->second;
-        int d = rz.dtype_at(site);
+        int d = site_dtype(site);
         Tensor tmp = fresh({}, PSK_F64);
         check(vt->upload(vt->self, tmp.ptr(), &x, 8), "scalar");
         Tensor out = fresh({}, d);
@@ -489,7 +534,7 @@ struct psk_host {
             }
         }
         Axes out_axes = shapes.back();
-        int d = rz.dtype_at(site);
+        int d = site_dtype(site);
         Tensor out = fresh(out_axes, d);
         psk_launch l;
         memset(&l, 0, sizeof l);
@@ -552,7 +597,7 @@ struct psk_host {
             for (auto &o : output) in_out |= o == n.first;
             if (!in_out) { all.push_back(n.first); inner.push_back(n.second); }
         }
-        int d = rz.dtype_at(site);
+        int d = site_dtype(site);
         Tensor out = fresh(out_axes, d);
         psk_launch l;
         memset(&l, 0, sizeof l);
@@ -605,7 +650,7 @@ struct psk_host {
         Axes out_axes = x.axes;
         int64_t n = out_axes[p].len;
         out_axes.erase(out_axes.begin() + p);
-        int d = rz.dtype_at(site);
+        int d = site_dtype(site);
         Tensor out = fresh(out_axes, d);
         psk_launch l;
         memset(&l, 0, sizeof l);
@@ -626,7 +671,7 @@ struct psk_host {
 
     Tensor reduce_all(const std::string &site, int kind, const Tensor &x)
     {
-        int d = rz.dtype_at(site);
+        int d = site_dtype(site);
         Tensor out = fresh({}, d);
         psk_launch l;
         memset(&l, 0, sizeof l);
@@ -651,7 +696,7 @@ struct psk_host {
         Axes outer = x.axes;
         int64_t n = outer[p].len;
         outer.erase(outer.begin() + p);
-        int d = rz.dtype_at(site);
+        int d = site_dtype(site);
         Tensor out = fresh(x.axes, d);
         psk_launch l;
         memset(&l, 0, sizeof l);
@@ -684,7 +729,7 @@ struct psk_host {
         Axes outer = y.axes;
         int64_t v = logits.axes.back().len;
         if (logits.axes.size() != y.axes.size() + 1) raise(PSK_E7001, "cross_entropy: " + show(logits.axes) + " against labels " + show(y.axes));
-        int d = rz.dtype_at(site);
+        int d = site_dtype(site);
         Tensor out = fresh(outer, d);
         psk_launch l;
         memset(&l, 0, sizeof l);
@@ -711,7 +756,7 @@ struct psk_host {
         if (table.axes.size() != 2) raise(PSK_E7001, "embed: the table must have rank 2");
         Axes out_axes = ids.axes;
         out_axes.push_back({"", table.axes[1].len});
-        int d = rz.dtype_at(site);
+        int d = site_dtype(site);
         Tensor out = fresh(out_axes, d);
         psk_launch l;
         memset(&l, 0, sizeof l);
@@ -760,7 +805,7 @@ struct psk_host {
         if (lo > hi || hi > x.axes[p].len) raise(PSK_E7001, "slice " + std::to_string(lo) + ".." + std::to_string(hi) + " outside the axis `" + axis + "`, of length " + std::to_string(x.axes[p].len));
         Axes out_axes = x.axes;
         out_axes[p].len = hi - lo;
-        int d = x.is_index ? PSK_I64 : rz.dtype_at(site);
+        int d = x.is_index ? PSK_I64 : site_dtype(site);
         Tensor out = fresh(out_axes, d, x.is_index, x.bound);
         auto st = x.strides();
         copy_part("slice " + axis + ": " + std::to_string(lo) + ".." + std::to_string(hi), d, out_axes, x, st, lo * st[p], out, contiguous(out_axes), 0, true);
@@ -776,11 +821,14 @@ struct psk_host {
         if (!same) raise(PSK_E7001, "concat " + axis + ": " + show(x.axes) + " and " + show(y.axes));
         Axes out_axes = x.axes;
         out_axes[p].len += y.axes[p].len;
-        int d = rz.dtype_at(site);
+        int d = site_dtype(site);
         Tensor out = fresh(out_axes, d);
         auto os = contiguous(out_axes);
         // one nest of two loops in the reference (lower.rs:1592); two kernels here, one launch
+        const bool was = calibrating;
+        calibrating = false; // the output is whole only after the second part
         copy_part("concat " + axis, d, x.axes, x, x.strides(), 0, out, os, 0, true);
+        calibrating = was;
         copy_part("concat " + axis, d, y.axes, y, y.strides(), 0, out, os, x.axes[p].len * os[p], false);
         return out;
     }
@@ -794,7 +842,7 @@ struct psk_host {
         out_axes.push_back({"heads", h});
         out_axes.push_back(x.axes[r - 2]);
         out_axes.push_back({"hd", hd});
-        int d = rz.dtype_at(site);
+        int d = site_dtype(site);
         Tensor out = fresh(out_axes, d);
         auto xs = x.strides();
         std::vector<int64_t> st(xs.begin(), xs.end() - 2);
@@ -813,7 +861,7 @@ struct psk_host {
         Axes out_axes(x.axes.begin(), x.axes.end() - 3);
         out_axes.push_back(x.axes[r - 2]);
         out_axes.push_back({"model", h * hd});
-        int d = rz.dtype_at(site);
+        int d = site_dtype(site);
         Tensor out = fresh(out_axes, d);
         // iterate (lead.., s, hh, d): the output is contiguous over it
         Axes space(x.axes.begin(), x.axes.end() - 3);
@@ -842,8 +890,8 @@ struct psk_host {
         run(l, name, {}, out);
         return out;
     }
-    Tensor positions(const std::string &site, const std::string &axis, int64_t n) { return iota(PSK_IOTA_POSITIONS, "positions " + axis, {{axis, n}}, true, n, rz.dtype_at(site)); }
-    Tensor causal_mask(const std::string &site, const std::string &axis, int64_t n) { return iota(PSK_IOTA_CAUSAL, "causal_mask " + axis, {{axis, n}, {axis + "2", n}}, true, 2, rz.dtype_at(site)); }
+    Tensor positions(const std::string &site, const std::string &axis, int64_t n) { return iota(PSK_IOTA_POSITIONS, "positions " + axis, {{axis, n}}, true, n, site_dtype(site)); }
+    Tensor causal_mask(const std::string &site, const std::string &axis, int64_t n) { return iota(PSK_IOTA_CAUSAL, "causal_mask " + axis, {{axis, n}, {axis + "2", n}}, true, 2, site_dtype(site)); }
 
     // ---- retags: split and merge of an axis are the host's (host.rs:1510-1544) ------------
     Tensor split(const Tensor &x, const std::string &axis, const std::vector<Axis> &parts)
@@ -1143,7 +1191,7 @@ struct psk_host {
     std::map<std::string, Tensor> ones_cache;
     Tensor ones_like(const std::string &site, const Tensor &x)
     {
-        int d = rz.dtype_at(site);
+        int d = site_dtype(site);
         std::string key = show(x.axes) + "|" + std::to_string(d);
         auto hit = ones_cache.find(key);
         if (hit != ones_cache.end()) return hit->second;
@@ -1474,6 +1522,35 @@ int psk_host_call_device(psk_host *h, const char *entry, const psk_value *inputs
         if (out_numel) *out_numel = h->last_result.numel();
     });
     return PSK_OK;
+}
+
+void psk_host_set_calibrating(psk_host *h, int on)
+{
+    h->calibrating = on != 0;
+    if (on) { h->slot_of.clear(); h->slots.reset(); }
+}
+
+const char *psk_host_envelope(psk_host *h)
+{
+    h->envelope_text.clear();
+    try {
+        if (!h->slots || h->slot_of.empty()) return "";
+        std::vector<uint32_t> words(h->slot_of.size() * 4);
+        h->check(h->vt->sync(h->vt->self), "calibrate");
+        h->check(h->vt->download(h->vt->self, words.data(), h->slots->p, words.size() * 4), "calibrate");
+        auto unorder = [](uint32_t u) { uint32_t b = (u >> 31) ? (u ^ 0x80000000u) : ~u; float x; memcpy(&x, &b, 4); return x; };
+        auto asf = [](uint32_t b) { float x; memcpy(&x, &b, 4); return x; };
+        for (auto &kv : h->slot_of) { // std::map: sorted by site
+            const uint32_t *w = &words[(size_t)kv.second * 4];
+            char line[256];
+            snprintf(line, sizeof line, "%s\t%.9g\t%.9g\t%.9g\t%.9g\n", kv.first.c_str(), asf(w[0]), asf(w[1]), unorder(w[2]), unorder(w[3]));
+            h->envelope_text += line;
+        }
+    } catch (const HostError &e) {
+        h->error = e.msg;
+        return "";
+    }
+    return h->envelope_text.c_str();
 }
 
 int64_t psk_host_launches(const psk_host *h) { return h->launches; }

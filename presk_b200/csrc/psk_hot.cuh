@@ -392,14 +392,22 @@ __global__ void __launch_bounds__(WARPS * 32, 6) k_softmax_rows_smem(const __gri
     const bool causal = L.masked && L.iparam[0] == 1;
     const bool general_mask = L.masked && !causal;
     const bool bf16_io = L.in[0].dtype == PSK_BF16 && L.kdtype == PSK_BF16 && L.out.dtype == PSK_BF16;
+    // iparam[2] = 1: the rows lie one after the other in the input and in the output, and under the
+    // causal mask row r is position r mod iparam[3] of its sequence: no index arithmetic a row
+    const bool flat = L.iparam[2] == 1;
     for (int64_t r = (int64_t)blockIdx.x * WARPS + wib; r < L.total; r += nwarps) {
-        const int64_t base = operand_offset(L.in[0], L.dims, 0, L.n_outer, r);
-        const int64_t obase = operand_offset(L.out, L.dims, 0, L.n_outer, r);
-        int64_t mbase = 0, ms = 0;
-        if (L.masked) {
-            mbase = operand_offset(L.in[1], L.dims, 0, L.n_outer, r);
-            ms = L.in[1].stride[L.n_outer];
-            if (causal) mbase = mbase / L.iparam[1];
+        int64_t base, obase, mbase = 0, ms = 0;
+        if (flat) {
+            base = obase = r * n;
+            if (causal) mbase = (int64_t)((uint32_t)r % (uint32_t)L.iparam[3]);
+        } else {
+            base = operand_offset(L.in[0], L.dims, 0, L.n_outer, r);
+            obase = operand_offset(L.out, L.dims, 0, L.n_outer, r);
+            if (L.masked) {
+                mbase = operand_offset(L.in[1], L.dims, 0, L.n_outer, r);
+                ms = L.in[1].stride[L.n_outer];
+                if (causal) mbase = mbase / L.iparam[1];
+            }
         }
         // under the causal mask the allowed elements are 0 .. count-1
         const uint32_t count = causal ? (uint32_t)min(n, mbase + 1) : (uint32_t)n;

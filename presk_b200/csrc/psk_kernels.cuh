@@ -869,6 +869,42 @@ __global__ void __launch_bounds__(256) k_quant_codes(const void *w, int from, co
     }
 }
 
+// PSK_OP_MAGNITUDE: a tensor's max |x|, least non-zero |x|, least and greatest x, merged into four
+// words by atomic max and min on order-preserving integer views of the floats. Order-free, so exact.
+PSK_DEV uint32_t ordered_bits(float x)
+{
+    const uint32_t b = f32_bits(x);
+    return b ^ ((b >> 31) ? 0xffffffffu : 0x80000000u);
+}
+
+__global__ void __launch_bounds__(256) k_magnitude(const void *src, int dtype, int64_t n, uint32_t *out)
+{
+    uint32_t mx = 0u, mn = 0x7f800000u, lo = 0xff800000u, hi = 0x007fffffu;
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) {
+        const float x = load_real(src, dtype, i);
+        if (x != x) continue;
+        const uint32_t a = f32_bits(x) & 0x7fffffffu, o = ordered_bits(x);
+        mx = max(mx, a);
+        if (a != 0u) mn = min(mn, a);
+        lo = min(lo, o);
+        hi = max(hi, o);
+    }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) {
+        mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, s));
+        mn = min(mn, __shfl_xor_sync(0xffffffffu, mn, s));
+        lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, s));
+        hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, s));
+    }
+    if ((threadIdx.x & 31) == 0) {
+        atomicMax(out + 0, mx);
+        atomicMin(out + 1, mn);
+        atomicMin(out + 2, lo);
+        atomicMax(out + 3, hi);
+    }
+}
+
 // Normal draws for parameters made on the device: a counter-based hash
 // (splitmix64) and Box-Muller in f32 with CUDA's own logf/cosf. These are not
 // the reference's keys; they only have to be the same on every run.

@@ -33,3 +33,15 @@ def max_over_ranks(value, device="cpu", group=None):
     if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
     return float(t[0])
+
+
+def combine_envelopes(envelope, device="cpu", group=None):
+    """`presk calibrate` over a sharded batch: each rank's {site: (max |x|, least non-zero |x|, lo, hi)}
+    merged into the whole batch's with ONE max-reduction (the minima travel negated). Every rank
+    runs the same program, so the sites and their order are the same everywhere."""
+    sites = sorted(envelope)
+    t = torch.tensor([[envelope[s][0], -envelope[s][1], -envelope[s][2], envelope[s][3]] for s in sites], dtype=torch.float64, device=device).reshape(-1, 4)
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+    t = t.cpu()
+    return {s: (float(t[i, 0]), float(-t[i, 1]), float(-t[i, 2]), float(t[i, 3])) for i, s in enumerate(sites)}

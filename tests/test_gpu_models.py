@@ -159,3 +159,17 @@ def test_gpt_config2_full_shape_mixed_realization(cuda, oracle):
     exact = models.gpt_numpy(p, c, ids[:16])
     assert np.abs(logits[:16] - exact).max() <= 1e-3 * max(1.0, np.abs(exact).max()) * 50  # the budget's order of magnitude at bf16
     assert abs(loss - float(models.gpt_numpy(p, c, ids[:64], y[:64]))) < 0.05
+
+
+def test_calibrate_envelope_matches_the_oracle(cuda, oracle):
+    """The magnitudes of every site, measured on the GPU, are the oracle's (order-free reductions of equal values)."""
+    c = models.LLAMA_TINY
+    p = models.llama_params(c)
+    ids = np.random.default_rng(3).integers(0, c["V"], size=(2, 16), dtype=np.int64)
+    envs = []
+    for ex in (cuda, oracle.vtable()):
+        h = models.give(Host(ex, "bf16").prepare("llama", **c), p)
+        h.set_calibrating(True)
+        h.call("apply", [ids], (2, 16, c["V"]))
+        envs.append(h.envelope())
+    assert envs[0] == envs[1] and len(envs[0]) > 25

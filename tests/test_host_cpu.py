@@ -138,3 +138,25 @@ def test_gpt_config2_matches_numpy_and_its_launch_list(oracle):
     assert h.launch_log() == ["causal_mask seq", "embed", "positions seq", "embed", "fused 2 steps"] + block * c["L"] + ln + ["dot"]
     loss = h.call("loss", [ids, y], ())
     np.testing.assert_allclose(loss, models.gpt_numpy(p, c, ids, y), rtol=3e-6)
+
+
+def test_calibrate_envelope(oracle):
+    """`presk calibrate` on the executor: per-site max |x|, least non-zero |x| and range of what was run."""
+    c = models.LLAMA_TINY
+    p = models.llama_params(c)
+    ids = np.random.default_rng(3).integers(0, c["V"], size=(2, 16), dtype=np.int64)
+    h = models.give(Host(oracle.vtable(), "f32").prepare("llama", **c), p)
+    h.set_calibrating(True)
+    logits = h.call("apply", [ids], (2, 16, c["V"]))
+    env = h.envelope()
+    mx, mn, lo, hi = env["Llama.apply/%11"]
+    assert mx == np.abs(logits).max() and lo == logits.min() and hi == logits.max()
+    assert mn == np.abs(logits)[logits != 0].min()
+    emb = p["tok"][ids]
+    assert env["Llama.apply/%4"][0] == np.abs(emb).max()
+    # a site run once per layer holds the largest of its launches; the softmax's values lie in [0, 1]
+    assert env["Attention.apply/%21"][2] == 0.0 and 0.99 < env["Attention.apply/%21"][3] <= 1.0
+    assert len(env) > 25
+    # a second call folds into the same envelope
+    h.call("apply", [(ids + 1) % c["V"]], (2, 16, c["V"]))
+    assert h.envelope()["Llama.apply/%11"][0] >= mx

@@ -39,12 +39,14 @@ WORKER = textwrap.dedent("""
     y = rng.integers(0, c["V"], size=(6, 16), dtype=np.int64)
     lo, hi = shard.shard_rows(6, rank, world)
     h = models.give(Host(oracle_lib.load().vtable(), "f32").prepare("llama", **c), p)
+    h.set_calibrating(True)
     local = float(h.call("loss", [ids[lo:hi], y[lo:hi]], ()))
+    env = shard.combine_envelopes(h.envelope())
     total = shard.combine_mean(local, (hi - lo) * 16)
     slowest = shard.max_over_ranks(rank + 1.0)
     dist.barrier()
     if rank == 0:
-        print(json.dumps({{"loss": total, "slowest": slowest}}))
+        print(json.dumps({{"loss": total, "slowest": slowest, "envelope": env}}))
     dist.destroy_process_group()
 """)
 
@@ -64,6 +66,14 @@ def test_two_ranks_give_the_whole_batch_loss(oracle, tmp_path):
     ids = rng.integers(0, c["V"], size=(6, 16), dtype=np.int64)
     y = rng.integers(0, c["V"], size=(6, 16), dtype=np.int64)
     h = models.give(Host(oracle.vtable(), "f32").prepare("llama", **c), p)
+    h.set_calibrating(True)
     whole = float(h.call("loss", [ids, y], ()))
     assert abs(got["loss"] - whole) <= 2e-6 * abs(whole)
+    # calibrate's max-magnitude reduction: the merged envelope of the two shards is the whole batch's,
+    # at every site whose values do not depend on how the batch is cut (all but the final mean)
+    whole_env = h.envelope()
+    for site, v in whole_env.items():
+        if site == "loss/%6":
+            continue
+        assert tuple(got["envelope"][site]) == v, site
     assert got["slowest"] == 2.0
