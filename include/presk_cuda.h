@@ -50,8 +50,9 @@ typedef enum {
     PSK_I64 = 3,
     PSK_F16 = 4,
     PSK_E8M15 = 5, /* three bytes an element, little-endian */
-    PSK_I8 = 6,    /* integer weights; the scales travel beside them */
-    PSK_E4M3 = 7   /* e4m3fn codes, one byte */
+    PSK_I8 = 6,    /* integer weights (the scales travel beside them), or the codes of an affine i8 format */
+    PSK_E4M3 = 7,  /* e4m3fn codes, one byte */
+    PSK_U8 = 8     /* the codes of an affine u8 format */
 } psk_dtype;
 
 /* Status of a call: the reference's RtError codes (presk-rt/src/lib.rs:971-981). */
@@ -59,6 +60,7 @@ typedef enum {
     PSK_OK = 0,
     PSK_E7001 = 7001,  /* runtime error (bad descriptor, shapes) */
     PSK_E7005 = 7005,  /* a realization this executor does not run */
+    PSK_E7006 = 7006,  /* a scaled site whose scale is not computed yet */
     PSK_E7007 = 7007,  /* the overflow guard: a store rounded a finite value to an infinity */
     PSK_E10001 = 10001 /* internal error of the backend (a CUDA call failed, a wait ran out) */
 } psk_status;
@@ -131,6 +133,13 @@ typedef struct {
     int64_t stride[PSK_MAX_AXES];
     int64_t scale_stride[PSK_MAX_AXES];
     int64_t numel;              /* elements of the whole buffer, for checks */
+    /* A value stored in an affine format (the realization's `scaled` map, presk-rt/src/lib.rs:287-360;
+     * presk-format/src/lib.rs:865-954): codes q of dtype PSK_I8 (`i8/sat`, affine = 1) or PSK_U8
+     * (`u8/sat`, affine = 2) denoting (q - zero)·scale, the scale a positive normal f32. 0: not affine. */
+    int32_t affine;
+    int32_t affine_zero;
+    float affine_scale;
+    int32_t reserved;
 } psk_operand;
 
 typedef struct {
@@ -150,6 +159,11 @@ typedef struct {
     psk_step steps[PSK_MAX_STEPS];
     int32_t kind;       /* psk_reduce_kind or psk_iota_kind */
     int32_t masked;     /* softmax: input 1 is the mask */
+    int32_t int_accum;  /* contraction: 1 = `product: i32, accum: i32` (presk-kernel/src/exec.rs:493-526): both
+                           operands are read as integer counts in their scales' unit, the products and the
+                           sum are exact integers wrapped to 32 bits, and the store rounds the exact value
+                           sum·s0·s1 once into the output's format */
+    int32_t reserved;
     int64_t iparam[4];  /* reduce: the divisor of a mean; copy/iota: see psk_host.cpp */
     double fparam[2];   /* fill: the value */
 } psk_launch;
@@ -188,8 +202,8 @@ void psk_exec_memory(const psk_exec *e, size_t *live, size_t *peak);
 
 /* KernelExec::run. `table` is the native executor's pointer table
  * (presk-cranelift/src/lib.rs:1609-1629): the n_inputs inputs, the output,
- * then one `const float *` of scales for each input whose dtype is PSK_I8, in
- * input order. All are device pointers of this executor. The launch is
+ * then one `const float *` of scales for each input that holds integer weights
+ * (dtype PSK_I8, not affine), in input order. All are device pointers of this executor. The launch is
  * queued on the executor's stream; PSK_E7007 of a guarded launch is
  * reported by the next psk_exec_sync, psk_exec_download or psk_exec_overflow,
  * naming the first launch whose store overflowed, and later launches still

@@ -257,6 +257,87 @@ static float edge_round(float x, int kdtype, int dtype, uint32_t *ovf)
     }
 }
 
+/* ---- affine formats and exact integer sums (presk-format/src/lib.rs:865-954, 1148-1193;
+ *      presk-kernel/src/exec.rs:493-526, 601-616) ------------------------------------- */
+typedef unsigned __int128 u128;
+
+static int64_t affine_min(int kind) { return kind == 2 ? 0 : -128; }
+static int64_t affine_max(int kind) { return kind == 2 ? 255 : 127; }
+
+/* x = m·2^e with m an integer: a finite double taken apart. */
+static void take_apart(double x, int64_t *m, int *e)
+{
+    uint64_t b;
+    memcpy(&b, &x, 8);
+    int field = (int)((b >> 52) & 0x7ff);
+    uint64_t frac = b & (((uint64_t)1 << 52) - 1);
+    int64_t mag = field ? (int64_t)(frac | ((uint64_t)1 << 52)) : (int64_t)frac;
+    *e = (field ? field : 1) - 1075;
+    *m = (b >> 63) ? -mag : mag;
+}
+
+/* The integer nearest (mag·2^e) / s with the sign given, ties to even, for mag < 2^90 and s a
+ * positive normal f32: the exact quotient's rounding (presk-format `quotient_round`), saturated
+ * at +-2^62. */
+static int64_t quotient_round_exact(int neg, u128 mag, int e, float s)
+{
+    if (mag == 0) return 0;
+    int64_t ms64;
+    int es;
+    take_apart((double)s, &ms64, &es);
+    while ((ms64 & 1) == 0) { ms64 >>= 1; ++es; } /* s = ms·2^es with ms odd, below 2^24 */
+    const u128 ms = (u128)ms64;
+    int bits = 0;
+    for (u128 t = mag; t; t >>= 1) ++bits;
+    const int k = e - es; /* the quotient is mag·2^k / ms */
+    u128 num = mag, den = ms;
+    if (k >= 0) {
+        if (bits + k > 120) return neg ? -((int64_t)1 << 62) : ((int64_t)1 << 62);
+        num = mag << k;
+    } else {
+        if (-k > bits + 2) return 0; /* below a quarter */
+        den = ms << -k;              /* below 2^(24 + 92) */
+    }
+    u128 q = num / den, r = num % den, twice = r << 1;
+    if (twice > den || (twice == den && (q & 1))) q += 1;
+    if (q > ((u128)1 << 62)) q = (u128)1 << 62;
+    return neg ? -(int64_t)q : (int64_t)q;
+}
+
+/* A real stored in an affine format: q = clamp(rne(x / s) + z), the quotient exact
+ * (Affine::round_scaled with quotient None, zero added after). A NaN is the zero point. */
+int64_t psk_o_affine_code(double x, int kind, float scale, int zero)
+{
+    if (x != x) return zero;
+    if (isinf(x)) return x > 0 ? affine_max(kind) : affine_min(kind);
+    int64_t m;
+    int e;
+    take_apart(x, &m, &e);
+    int64_t n = quotient_round_exact(m < 0, (u128)(m < 0 ? -m : m), e, scale);
+    int64_t q = n + zero;
+    return q < affine_min(kind) ? affine_min(kind) : (q > affine_max(kind) ? affine_max(kind) : q);
+}
+
+/* The exact value n·base (base the product of two f32 scales, exact in a double) rounded once
+ * into the IEEE format of t fraction and w exponent bits: its code. */
+static uint32_t round_count_to_float(int64_t n, double base, unsigned t, unsigned w)
+{
+    if (n == 0) return 0;
+    int64_t mb;
+    int eb;
+    take_apart(base, &mb, &eb);
+    u128 mag = (u128)(n < 0 ? -n : n) * (u128)mb;
+    int bits = 0;
+    for (u128 v = mag; v; v >>= 1) ++bits;
+    /* keep 62 bits and a sticky one: the rounding position is far above */
+    int drop = bits > 62 ? bits - 62 : 0;
+    uint64_t sig = (uint64_t)(mag >> drop);
+    if (drop && (mag & ((((u128)1) << drop) - 1))) sig |= 1;
+    int top = bits - drop - 1;
+    uint32_t code = round_to_format(sig, top, eb + drop + top, t, w);
+    return (n < 0 ? (1u << (t + w)) : 0u) | code;
+}
+
 /* Whether a kernel of type kd reads an input stored as `dtype` without rounding it. */
 static int edge_is_identity(int kd, int dtype)
 {
@@ -286,8 +367,24 @@ static int64_t offset_of(const int64_t *stride, const int64_t *dims, int first, 
     return off;
 }
 
+/* The integer a counted nest reads of an operand, and its unit (exec.rs `from_scaled`). */
+static int32_t load_count(const operand *x, int64_t off, int64_t soff, double *unit)
+{
+    if (x->o->affine) {
+        *unit = (double)x->o->affine_scale;
+        int q = x->o->affine == 2 ? (int)((const uint8_t *)x->p)[off] : (int)((const int8_t *)x->p)[off];
+        return q - x->o->affine_zero;
+    }
+    *unit = (double)x->scales[soff];
+    return (int)((const int8_t *)x->p)[off];
+}
+
 static float load_operand(const operand *x, int64_t off, int64_t soff, int kdtype, uint32_t *ovf)
 {
+    if (x->o->affine) { /* (q - z)·s, exact in a double, read by an f32 nest: rounded to f32 */
+        int q = x->o->affine == 2 ? (int)((const uint8_t *)x->p)[off] : (int)((const int8_t *)x->p)[off];
+        return (float)((double)(q - x->o->affine_zero) * (double)x->o->affine_scale);
+    }
     if (x->o->dtype == PSK_I8) return (float)((const int8_t *)x->p)[off] * x->scales[soff]; /* quant.rs:250-252 */
     return edge_round(load_real(x->p, x->o->dtype, off), kdtype, x->o->dtype, ovf);
 }
@@ -339,6 +436,18 @@ static float prim_binary(int prim, float x, float y)
     }
 }
 
+/* A store into the launch's output: its float type, or its affine format (exec.rs:758-782). */
+static uint32_t store_out(const psk_launch *l, uint8_t *outp, int64_t off, float x)
+{
+    if (l->out.affine) {
+        int64_t q = psk_o_affine_code((double)x, l->out.affine, l->out.affine_scale, l->out.affine_zero);
+        if (l->out.affine == 2) ((uint8_t *)outp)[off] = (uint8_t)q;
+        else ((int8_t *)outp)[off] = (int8_t)q;
+        return 0;
+    }
+    return store_real(outp, l->out.dtype, off, x);
+}
+
 /* ---- the launches ------------------------------------------------------------- */
 static int psk_oracle_run_merged(const psk_launch *l, void *const *table, uint32_t *overflow);
 
@@ -377,14 +486,14 @@ static int psk_oracle_run_merged(const psk_launch *l, void *const *table, uint32
     for (int i = 0; i < l->n_inputs; ++i) {
         in[i].o = &l->in[i];
         in[i].p = (const uint8_t *)table[i] + l->in[i].offset * (int64_t)elem_bytes(l->in[i].dtype);
-        in[i].scales = l->in[i].dtype == PSK_I8 ? (const float *)table[scale_slot++] : NULL;
+        in[i].scales = (l->in[i].dtype == PSK_I8 && !l->in[i].affine) ? (const float *)table[scale_slot++] : NULL;
     }
     uint8_t *outp = (uint8_t *)table[l->n_inputs] + l->out.offset * (int64_t)elem_bytes(l->out.dtype);
     int64_t total = 1, inner = 1;
     for (int a = 0; a < no; ++a) total *= l->dims[a];
     for (int c = 0; c < ni; ++c) inner *= l->dims[no + c];
     uint32_t ovf_all = 0;
-    if (kd == PSK_F64) return PSK_E7005;
+    if (kd == PSK_F64 && l->op != PSK_OP_CONVERT) return PSK_E7005;
 
     switch (l->op) {
     case PSK_OP_FUSED: /* lower.rs:328-360 */
@@ -401,11 +510,61 @@ static int psk_oracle_run_merged(const psk_launch *l, void *const *table, uint32
                 }
                 vals[s] = st->nargs == 1 ? prim_unary(st->prim, a[0], st->imm) : prim_binary(st->prim, a[0], a[1]);
             }
-            ovf |= store_real(outp, l->out.dtype, offset_of(l->out.stride, l->dims, 0, no, lin), vals[l->n_steps - 1]);
+            ovf |= store_out(l, outp, offset_of(l->out.stride, l->dims, 0, no, lin), vals[l->n_steps - 1]);
             ovf_all |= ovf;
         }
         break;
-    case PSK_OP_CONTRACT: /* lower.rs:465-474, 586-636: acc = acc + (x·w), the terms in lexicographic order */
+    case PSK_OP_CONTRACT:
+        if (l->int_accum) { /* exec.rs:493-526: counts in the scales' unit, i32 that wraps; :601-616 the store */
+            if (l->n_inputs != 2) return PSK_E7005;
+            for (int i = 0; i < 2; ++i) if (!l->in[i].affine && l->in[i].dtype != PSK_I8) return PSK_E7005;
+            for (int64_t lin = 0; lin < total; ++lin) {
+                int64_t b0 = offset_of(l->in[0].stride, l->dims, 0, no, lin), b1 = offset_of(l->in[1].stride, l->dims, 0, no, lin);
+                int64_t q0 = offset_of(l->in[0].scale_stride, l->dims, 0, no, lin), q1 = offset_of(l->in[1].scale_stride, l->dims, 0, no, lin);
+                uint32_t acc = 0;
+                double u0 = 1.0, u1 = 1.0;
+                for (int64_t c = 0; c < inner; ++c) {
+                    int64_t o0 = offset_of(l->in[0].stride, l->dims, no, ni, c), o1 = offset_of(l->in[1].stride, l->dims, no, ni, c);
+                    int64_t s0 = offset_of(l->in[0].scale_stride, l->dims, no, ni, c), s1 = offset_of(l->in[1].scale_stride, l->dims, no, ni, c);
+                    int32_t a = load_count(&in[0], b0 + o0, q0 + s0, &u0), b = load_count(&in[1], b1 + o1, q1 + s1, &u1);
+                    acc += (uint32_t)(a * b); /* the product fits; the sum wraps */
+                }
+                if (inner == 0) { load_count(&in[0], b0, q0, &u0); load_count(&in[1], b1, q1, &u1); }
+                int64_t n = (int32_t)acc;
+                double base = u0 * u1; /* exact: two 24-bit significands */
+                int64_t ooff = offset_of(l->out.stride, l->dims, 0, no, lin);
+                if (l->out.affine) {
+                    int64_t mb;
+                    int eb;
+                    take_apart(base, &mb, &eb);
+                    int64_t nq = quotient_round_exact(n < 0, (u128)(n < 0 ? -n : n) * (u128)mb, eb, l->out.affine_scale);
+                    int64_t q = nq + l->out.affine_zero;
+                    q = q < affine_min(l->out.affine) ? affine_min(l->out.affine) : (q > affine_max(l->out.affine) ? affine_max(l->out.affine) : q);
+                    if (l->out.affine == 2) ((uint8_t *)outp)[ooff] = (uint8_t)q;
+                    else ((int8_t *)outp)[ooff] = (int8_t)q;
+                } else {
+                    switch (l->out.dtype) {
+                    case PSK_F32: ((uint32_t *)outp)[ooff] = round_count_to_float(n, base, 23, 8); break;
+                    case PSK_BF16: ((uint16_t *)outp)[ooff] = (uint16_t)round_count_to_float(n, base, 7, 8); break;
+                    case PSK_F16: {
+                        uint32_t c = round_count_to_float(n, base, 10, 5);
+                        ((uint16_t *)outp)[ooff] = (uint16_t)c;
+                        if ((c & 0x7fffu) == 0x7c00u) ovf_all |= 1; /* a count is finite: an infinity here is an overflow */
+                        break;
+                    }
+                    case PSK_E8M15: {
+                        uint32_t c = round_count_to_float(n, base, 15, 8);
+                        uint8_t *q = outp + 3 * ooff;
+                        q[0] = (uint8_t)c; q[1] = (uint8_t)(c >> 8); q[2] = (uint8_t)(c >> 16);
+                        if ((c & 0x7fffffu) == 0x7f8000u) ovf_all |= 1;
+                        break;
+                    }
+                    default: return PSK_E7005;
+                    }
+                }
+            }
+            break;
+        } /* lower.rs:465-474, 586-636: acc = acc + (x·w), the terms in lexicographic order */
         /* The tiled form of a contraction nest (lower.rs:906-1139, tile (1, JB)): when the last output axis
          * is carried by operand 1 alone, contiguously, a block of JB results is summed at once, each still
          * adding its own terms in increasing k, so the bits are those of the loop below. It is the form the
@@ -641,7 +800,12 @@ static int psk_oracle_run_merged(const psk_launch *l, void *const *table, uint32
         break;
     case PSK_OP_CONVERT: /* presk-rt/src/lib.rs:868-876, presk_rt.c `presk_convert` */
         for (int64_t i = 0; i < total; ++i) {
-            if (l->in[0].dtype == PSK_F64) {
+            if (l->in[0].affine) {
+                int q = l->in[0].affine == 2 ? (int)((const uint8_t *)in[0].p)[i] : (int)((const int8_t *)in[0].p)[i];
+                double x = (double)(q - l->in[0].affine_zero) * (double)l->in[0].affine_scale;
+                if (l->out.dtype == PSK_F64) ((double *)outp)[i] = x;
+                else ovf_all |= store_real(outp, l->out.dtype, i, (float)x);
+            } else if (l->in[0].dtype == PSK_F64) {
                 double x = ((const double *)in[0].p)[i];
                 switch (l->out.dtype) {
                 case PSK_F64: ((double *)outp)[i] = x; break;

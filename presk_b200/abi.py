@@ -13,12 +13,12 @@ MAX_INPUTS = 8
 MAX_STEPS = 64
 
 # psk_dtype
-F64, F32, BF16, I64, F16, E8M15, I8, E4M3 = range(8)
-DTYPE_NAMES = {F64: "f64", F32: "f32", BF16: "bf16", I64: "i64", F16: "f16", E8M15: "e8m15", I8: "int8", E4M3: "e4m3fn"}
-DTYPE_BYTES = {F64: 8, F32: 4, BF16: 2, I64: 8, F16: 2, E8M15: 3, I8: 1, E4M3: 1}
+F64, F32, BF16, I64, F16, E8M15, I8, E4M3, U8 = range(9)
+DTYPE_NAMES = {F64: "f64", F32: "f32", BF16: "bf16", I64: "i64", F16: "f16", E8M15: "e8m15", I8: "int8", E4M3: "e4m3fn", U8: "uint8"}
+DTYPE_BYTES = {F64: 8, F32: 4, BF16: 2, I64: 8, F16: 2, E8M15: 3, I8: 1, E4M3: 1, U8: 1}
 
 # psk_status
-OK, E7001, E7005, E7007, E10001 = 0, 7001, 7005, 7007, 10001
+OK, E7001, E7005, E7006, E7007, E10001 = 0, 7001, 7005, 7006, 7007, 10001
 
 # psk_op
 OP_FUSED, OP_CONTRACT, OP_REDUCE, OP_SOFTMAX, OP_XENT, OP_ARGMAX, OP_EMBED, OP_COPY, OP_IOTA, OP_CONVERT, OP_MAGNITUDE = range(11)
@@ -39,6 +39,7 @@ class Operand(C.Structure):
     _fields_ = [
         ("dtype", C.c_int32), ("is_index", C.c_int32), ("offset", C.c_int64),
         ("stride", C.c_int64 * MAX_AXES), ("scale_stride", C.c_int64 * MAX_AXES), ("numel", C.c_int64),
+        ("affine", C.c_int32), ("affine_zero", C.c_int32), ("affine_scale", C.c_float), ("reserved", C.c_int32),
     ]
 
 
@@ -48,7 +49,7 @@ class Launch(C.Structure):
         ("n_inputs", C.c_int32), ("n_outer", C.c_int32), ("n_inner", C.c_int32),
         ("dims", C.c_int64 * MAX_AXES), ("inputs", Operand * MAX_INPUTS), ("out", Operand),
         ("n_steps", C.c_int32), ("steps", Step * MAX_STEPS),
-        ("kind", C.c_int32), ("masked", C.c_int32), ("iparam", C.c_int64 * 4), ("fparam", C.c_double * 2),
+        ("kind", C.c_int32), ("masked", C.c_int32), ("int_accum", C.c_int32), ("reserved", C.c_int32), ("iparam", C.c_int64 * 4), ("fparam", C.c_double * 2),
     ]
 
 

@@ -5,7 +5,7 @@ import numpy as np
 
 from . import abi
 
-_NP_OF = {abi.F64: np.float64, abi.F32: np.float32, abi.BF16: np.uint16, abi.I64: np.int64, abi.F16: np.uint16, abi.E8M15: np.uint8, abi.I8: np.int8, abi.E4M3: np.uint8}
+_NP_OF = {abi.F64: np.float64, abi.F32: np.float32, abi.BF16: np.uint16, abi.I64: np.int64, abi.F16: np.uint16, abi.E8M15: np.uint8, abi.I8: np.int8, abi.E4M3: np.uint8, abi.U8: np.uint8}
 
 
 class PreskError(RuntimeError):

@@ -105,6 +105,9 @@ void fill_operand(DevOperand &d, const psk_operand &o, void *base, const float *
     d.scales = scales;
     d.dtype = o.dtype;
     d.is_index = o.is_index;
+    d.affine = o.affine;
+    d.affine_zero = o.affine_zero;
+    d.affine_scale = o.affine_scale;
     for (int a = 0; a < PSK_MAX_AXES; ++a) {
         d.stride[a] = a < naxes ? o.stride[a] : 0;
         d.sstride[a] = a < naxes ? o.scale_stride[a] : 0;
@@ -597,18 +600,19 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
     cudaSetDevice(e->device);
     if (l->n_inputs < 0 || l->n_inputs > PSK_MAX_INPUTS || l->n_outer < 0 || l->n_outer > PSK_MAX_RANK || l->n_inner < 0 || l->n_inner > PSK_MAX_INNER)
         return fail(e, PSK_E7001, std::string(l->name ? l->name : "?") + ": a launch of too many inputs or axes");
-    if (l->dtype == PSK_F64)
+    if (l->dtype == PSK_F64 && l->op != PSK_OP_CONVERT)
         return fail(e, PSK_E7005, std::string(l->name ? l->name : "?") + ": this executor computes in f32; a site realised f64 is not runnable by it");
     const int naxes = l->n_outer + l->n_inner;
     DevLaunch L;
     memset(&L, 0, sizeof L);
     L.n_in = l->n_inputs; L.n_outer = l->n_outer; L.n_inner = l->n_inner; L.kdtype = l->dtype;
+    L.int_accum = l->int_accum;
     L.n_steps = l->n_steps; L.kind = l->kind; L.masked = l->masked; L.guarded = l->guarded && (l->out.dtype == PSK_F16 || l->out.dtype == PSK_E8M15 || l->dtype == PSK_F16 || l->dtype == PSK_E8M15);
     for (int a = 0; a < naxes; ++a) L.dims[a] = l->dims[a];
     int scale_slot = l->n_inputs + 1;
     for (int i = 0; i < l->n_inputs; ++i) {
         const float *sc = nullptr;
-        if (l->in[i].dtype == PSK_I8) sc = (const float *)table[scale_slot++];
+        if (l->in[i].dtype == PSK_I8 && !l->in[i].affine) sc = (const float *)table[scale_slot++];
         fill_operand(L.in[i], l->in[i], table[i], sc, naxes);
     }
     fill_operand(L.out, l->out, table[l->n_inputs], nullptr, naxes);
@@ -623,6 +627,12 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
     L.inner = 1;
     for (int c = 0; c < L.n_inner; ++c) L.inner *= L.dims[L.n_outer + c];
     const bool device_order = l->order == PSK_ORDER_DEVICE;
+    bool any_affine = l->out.affine != 0;
+    for (int i = 0; i < l->n_inputs; ++i) any_affine = any_affine || l->in[i].affine != 0;
+    if (any_affine && l->op != PSK_OP_FUSED && l->op != PSK_OP_CONTRACT && l->op != PSK_OP_CONVERT)
+        return fail(e, PSK_E7005, std::string(l->name ? l->name : "?") + ": values in an affine format are read and written by elementwise groups, contractions and conversions only");
+    if (any_affine && l->op == PSK_OP_CONTRACT && !l->int_accum)
+        return fail(e, PSK_E7005, std::string(l->name ? l->name : "?") + ": a contraction over affine values counts its sums in integers (product and accum i32) on this executor");
     cudaEvent_t pa = nullptr, pb = nullptr;
     if (e->profiling) {
         cudaEventRecord(e->ev0, e->stream);
@@ -639,7 +649,7 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
     case PSK_OP_FUSED: {
         e->last_kernel = "k_fused";
         if (l->n_steps < 1 || l->n_steps > PSK_MAX_STEPS) { rc = fail(e, PSK_E7001, "fused: a group of no step or of too many"); break; }
-        bool vec = L.n_outer >= 1 && l->n_steps <= 8 && L.dims[L.n_outer - 1] % 8 == 0 && vec8_operand(L.out, L.dims, L.n_outer, true);
+        bool vec = !any_affine && L.n_outer >= 1 && l->n_steps <= 8 && L.dims[L.n_outer - 1] % 8 == 0 && vec8_operand(L.out, L.dims, L.n_outer, true);
         for (int i = 0; vec && i < L.n_in; ++i) vec = vec8_operand(L.in[i], L.dims, L.n_outer, false);
         bool hot = vec && L.n_outer <= 2 && L.n_in <= 4 && l->n_steps <= 4 && L.total / 8 < 0xffffffffll;
         for (int i = 0; hot && i < L.n_in; ++i) hot = L.in[i].dtype != PSK_I8;
@@ -710,6 +720,16 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
         break;
     }
     case PSK_OP_CONTRACT: {
+        if (l->int_accum) {
+            bool ok = L.n_in == 2;
+            for (int i = 0; ok && i < 2; ++i) ok = L.in[i].affine != 0 || (L.in[i].dtype == PSK_I8 && L.in[i].scales != nullptr);
+            if (!ok) { rc = fail(e, PSK_E7005, std::string(l->name ? l->name : "?") + ": integer sums need two operands that are affine values or integer weights"); break; }
+            k_contract_int<<<grid_for(e, L.total, 128, 16), 128, 0, e->stream>>>(L);
+            e->last_kernel = "k_contract_int";
+            e->last_flops = 2.0 * (double)L.total * (double)L.inner;
+            e->kernels += 1;
+            break;
+        }
         GemmMap g;
         bool mapped = map_gemm(L, g);
         const DevOperand &A = L.in[0], &B = L.in[1];
@@ -841,7 +861,7 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
         break;
     case PSK_OP_CONVERT: {
         int64_t n = L.total;
-        k_convert<<<grid_for(e, n, 256, 8), 256, 0, e->stream>>>(L.in[0].p, L.in[0].dtype, const_cast<void *>(L.out.p), L.out.dtype, n, L.guarded, L.ovf);
+        k_convert<<<grid_for(e, n, 256, 8), 256, 0, e->stream>>>(L.in[0].p, L.in[0].dtype, const_cast<void *>(L.out.p), L.out.dtype, n, L.guarded, L.ovf, L.in[0].affine, L.in[0].affine_zero, L.in[0].affine_scale);
         e->kernels += 1;
         break;
     }

@@ -151,6 +151,9 @@ struct Realization {
     int dflt = PSK_F32;
     std::map<std::string, int> storage, functions, params;
     std::map<std::string, QuantSpec> quant;
+    struct AffineSpec { int kind; float scale; int zero; };
+    std::map<std::string, AffineSpec> scaled;  // sites stored in an affine format (presk-rt/src/lib.rs:287-360)
+    std::map<std::string, int> int_sums;        // sites whose `product` and `accum` are i32: 1 product, 2 accum, 3 both
     int order = PSK_ORDER_SEQUENTIAL;
 
     static Realization parse(const char *text)
@@ -195,9 +198,33 @@ struct Realization {
             else if (kind == "device") r.order = PSK_ORDER_DEVICE;
             else raise(PSK_E7005, "realization: the order `" + kind + "` is not one this executor has kernels for (sequential, device)");
         }
-        for (auto key : {"arith", "product", "accum", "scaled"})
+        if (auto *m = j.get("arith"))
+            if (!m->obj.empty()) raise(PSK_E7005, "realization: `arith` formats are the kernel interpreter's; this executor computes in f32 (E7005)");
+        for (auto key : {"product", "accum"})
             if (auto *m = j.get(key))
-                if (!m->obj.empty()) raise(PSK_E7005, std::string("realization: `") + key + "` formats are the kernel interpreter's; this executor computes in f32 (E7005)");
+                for (auto &kv : m->obj) {
+                    if (kv.second.kind != Json::Str || kv.second.str != "i32")
+                        raise(PSK_E7005, std::string("realization: ") + key + "[" + kv.first + "]: this executor counts sums in i32 (wrapping) only (E7005)");
+                    r.int_sums[kv.first] |= std::string(key) == "product" ? 1 : 2;
+                }
+        for (auto &kv : r.int_sums)
+            if (kv.second != 3) raise(PSK_E7005, "realization: " + kv.first + ": `product` and `accum` are i32 together on this executor (E7005)");
+        if (auto *m = j.get("scaled"))
+            for (auto &kv : m->obj) {
+                const Json *i = kv.second.get("int"), *sc = kv.second.get("scale"), *z = kv.second.get("zero");
+                // a scheme whose scale is not computed yet is refused by every executor (E7006, presk-rt/src/lib.rs:544-549)
+                if (!sc || sc->kind != Json::Num) raise(PSK_E7006, "realization: scaled[" + kv.first + "] has no scale yet: `presk scales` computes it from an envelope (E7006)");
+                AffineSpec a;
+                std::string in = i && i->kind == Json::Str ? i->str : "";
+                if (in == "i8/sat") a.kind = 1;
+                else if (in == "u8/sat") a.kind = 2;
+                else raise(PSK_E7005, "realization: scaled[" + kv.first + "]: the codes are i8/sat or u8/sat on this executor (E7005)");
+                a.scale = (float)sc->num;
+                a.zero = z ? (int)z->num : 0;
+                if (!(a.scale > 0.0f) || !std::isnormal(a.scale)) raise(PSK_E7001, "realization: scaled[" + kv.first + "]: the scale is a positive normal binary32 number");
+                if (a.zero < (a.kind == 2 ? 0 : -128) || a.zero > (a.kind == 2 ? 255 : 127)) raise(PSK_E7001, "realization: scaled[" + kv.first + "]: the zero point is not one of its codes");
+                r.scaled[kv.first] = a;
+            }
         return r;
     }
 
@@ -246,6 +273,9 @@ struct Tensor {
     // integer weights: scales over the axes without `q_over`
     std::shared_ptr<Storage> scales;
     int64_t soff = 0;
+    int affine = 0;  // the value is stored in an affine format: 1 i8/sat, 2 u8/sat
+    int affine_zero = 0;
+    float affine_scale = 0.0f;
     int q_over = -1; // the first axis of the contracted one, and how many axes it has been split into
     int q_span = 1;
     bool borrowed = false;
@@ -386,6 +416,19 @@ struct psk_host {
         return t;
     }
 
+    // The buffer of a site's value: in its storage type, or in its affine format's codes.
+    Tensor fresh_at(const std::string &site, const Axes &axes)
+    {
+        int d = site_dtype(site);
+        auto a = rz.scaled.find(site);
+        if (a == rz.scaled.end()) return fresh(axes, d);
+        Tensor t = fresh(axes, a->second.kind == 2 ? PSK_U8 : PSK_I8);
+        t.affine = a->second.kind;
+        t.affine_zero = a->second.zero;
+        t.affine_scale = a->second.scale;
+        return t;
+    }
+
     void check(int rc, const char *what)
     {
         if (rc != PSK_OK) raise(rc, std::string(what) + ": " + vt->last_error(vt->self));
@@ -399,6 +442,9 @@ struct psk_host {
         o.is_index = t.is_index ? 1 : 0;
         o.offset = t.off;
         o.numel = t.numel();
+        o.affine = t.affine;
+        o.affine_zero = t.affine_zero;
+        o.affine_scale = t.affine_scale;
         for (size_t a = 0; a < stride.size(); ++a) o.stride[a] = stride[a];
         for (size_t a = 0; a < sstride.size(); ++a) o.scale_stride[a] = sstride[a];
     }
@@ -413,7 +459,7 @@ struct psk_host {
         for (auto *t : ins) table.push_back(t->ptr());
         table.push_back(out.ptr());
         for (auto *t : ins)
-            if (t->dtype == PSK_I8) table.push_back((uint8_t *)t->scales->p + t->soff * 4);
+            if (t->dtype == PSK_I8 && !t->affine) table.push_back((uint8_t *)t->scales->p + t->soff * 4);
         check(vt->run(vt->self, &l, table.data()), name.c_str());
         launches += 1;
         if (logging) { log += name; log += '\n'; }
@@ -535,7 +581,7 @@ struct psk_host {
         }
         Axes out_axes = shapes.back();
         int d = site_dtype(site);
-        Tensor out = fresh(out_axes, d);
+        Tensor out = fresh_at(site, out_axes);
         psk_launch l;
         memset(&l, 0, sizeof l);
         l.op = PSK_OP_FUSED;
@@ -598,11 +644,12 @@ struct psk_host {
             if (!in_out) { all.push_back(n.first); inner.push_back(n.second); }
         }
         int d = site_dtype(site);
-        Tensor out = fresh(out_axes, d);
+        Tensor out = fresh_at(site, out_axes);
         psk_launch l;
         memset(&l, 0, sizeof l);
         l.op = PSK_OP_CONTRACT;
         l.dtype = d;
+        l.int_accum = rz.int_sums.count(site) ? 1 : 0;
         set_space(l, out_axes, inner);
         for (size_t t = 0; t < ins.size(); ++t) {
             std::vector<int> map;
@@ -1298,6 +1345,13 @@ struct psk_host {
         return reduce_all("loss/%7", PSK_REDUCE_MEAN, ce);
     }
 
+    // examples/tests/formats/w8a8.psk: Dense.apply %0 θ, %1 x; a %2 = relu x; w %3; %4 = dot a, w.
+    Tensor dense_w8a8(const Tensor &x)
+    {
+        Tensor a = unary("Dense.apply/%2", PSK_RELU, x);
+        return dot("Dense.apply/%4", a, param("w"));
+    }
+
     Tensor call(const std::string &entry, const std::vector<Tensor> &in)
     {
         auto need = [&](size_t n) { if (in.size() != n) raise(PSK_E7001, model + "." + entry + " takes " + std::to_string(n) + " inputs"); };
@@ -1319,6 +1373,9 @@ struct psk_host {
         } else if (model == "contract_ln") {
             need(2);
             return contract_ln(in[0], in[1]);
+        } else if (model == "dense") {
+            need(1);
+            return dense_w8a8(in[0]);
         }
         raise(PSK_E7001, "no entry `" + entry + "` of the model `" + model + "`");
     }
@@ -1337,6 +1394,7 @@ struct psk_host {
             if (v.rank) names.back() = "model";
         }
         else if (model == "contract_ln") names = i == 0 ? std::vector<std::string>{"batch", "k"} : std::vector<std::string>{"k", "model"};
+        else if (model == "dense") names = {"", ""};
         (void)entry;
         Axes a;
         for (int k = 0; k < v.rank; ++k) a.push_back({k < (int)names.size() ? names[k] : "", v.dims[k]});
@@ -1391,7 +1449,7 @@ int psk_host_prepare(psk_host *h, const char *model, const char *consts)
 {
     HOST_TRY(h, {
         h->model = model ? model : "";
-        static const char *known[] = {"llama", "gpt", "mlp", "layernorm", "rmsnorm", "contract_ln"};
+        static const char *known[] = {"llama", "gpt", "mlp", "layernorm", "rmsnorm", "contract_ln", "dense"};
         bool ok = false;
         for (auto k : known) ok |= h->model == k;
         if (!ok) raise(PSK_E7001, "no model `" + h->model + "`");
@@ -1481,7 +1539,7 @@ int psk_host_call(psk_host *h, const char *entry, const psk_value *inputs, int32
         } else {
             if (out_dtype != PSK_F32 && out_dtype != PSK_F64) raise(PSK_E7001, "a result is read as f32 or f64");
             Tensor o = r;
-            if (r.dtype != out_dtype || r.off != 0) {
+            if (r.dtype != out_dtype || r.off != 0 || r.affine) {
                 o = h->fresh(r.axes, out_dtype);
                 h->convert_into(r, o);
             }

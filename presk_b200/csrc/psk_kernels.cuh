@@ -61,6 +61,178 @@ PSK_DEV float prim_binary(int prim, float x, float y)
 }
 
 // ---------------------------------------------------------------------------
+// Exact integer sums over scaled values and affine stores
+// (presk-kernel/src/exec.rs:493-526, 601-616; presk-format/src/lib.rs:865-954,
+// 1148-1193). A value stored in an affine format is a code q denoting
+// (q - z)·s. Under `product: i32, accum: i32` a contraction reads both operands
+// as integers in their scales' unit, sums the exact products in 32 bits that
+// wrap, and rounds the exact value sum·s0·s1 once into the output's format:
+// a float's, or another affine format's by the exact quotient. 128-bit
+// integers carry the exact values.
+// ---------------------------------------------------------------------------
+typedef unsigned __int128 u128_t;
+
+PSK_DEV void take_apart(double x, int64_t &m, int &e)
+{
+    const uint64_t b = (uint64_t)__double_as_longlong(x);
+    const int field = (int)((b >> 52) & 0x7ff);
+    const uint64_t frac = b & ((1ull << 52) - 1);
+    const int64_t mag = field ? (int64_t)(frac | (1ull << 52)) : (int64_t)frac;
+    e = (field ? field : 1) - 1075;
+    m = (b >> 63) ? -mag : mag;
+}
+
+PSK_DEV int bit_length(u128_t v)
+{
+    const uint64_t hi = (uint64_t)(v >> 64), lo = (uint64_t)v;
+    return hi ? 128 - __clzll((long long)hi) : (lo ? 64 - __clzll((long long)lo) : 0);
+}
+
+// The integer nearest (mag·2^e) / s with the sign given, ties to even, saturated at +-2^62.
+PSK_DEV int64_t quotient_round_exact(bool neg, u128_t mag, int e, float s)
+{
+    if (mag == 0) return 0;
+    int64_t ms64;
+    int es;
+    take_apart((double)s, ms64, es);
+    const int tz = __ffsll(ms64) - 1;
+    ms64 >>= tz;
+    es += tz;
+    const u128_t ms = (u128_t)ms64;
+    const int bits = bit_length(mag), k = e - es;
+    u128_t num = mag, den = ms;
+    if (k >= 0) {
+        if (bits + k > 120) return neg ? -(1ll << 62) : (1ll << 62);
+        num = mag << k;
+    } else {
+        if (-k > bits + 2) return 0;
+        den = ms << -k;
+    }
+    u128_t q = num / den;
+    const u128_t r = num % den, twice = r << 1;
+    if (twice > den || (twice == den && (q & 1))) q += 1;
+    if (q > ((u128_t)1 << 62)) q = (u128_t)1 << 62;
+    return neg ? -(int64_t)q : (int64_t)q;
+}
+
+PSK_DEV int64_t affine_clamp(int64_t q, int kind)
+{
+    const int64_t lo = kind == 2 ? 0 : -128, hi = kind == 2 ? 255 : 127;
+    return q < lo ? lo : (q > hi ? hi : q);
+}
+
+// A real stored in an affine format: clamp(rne(x / s) + z), the quotient exact; a NaN is the zero point.
+PSK_DEV int64_t affine_code_of(double x, int kind, float scale, int zero)
+{
+    if (x != x) return zero;
+    if (isinf(x)) return x > 0 ? (kind == 2 ? 255 : 127) : (kind == 2 ? 0 : -128);
+    int64_t m;
+    int e;
+    take_apart(x, m, e);
+    const int64_t n = quotient_round_exact(m < 0, (u128_t)(m < 0 ? -m : m), e, scale);
+    return affine_clamp(n + zero, kind);
+}
+
+// The code of the IEEE format of t fraction and w exponent bits nearest sig·2^(exp - top), sig's leading
+// bit at position top: ties to even, overflow to the infinity's code.
+PSK_DEV uint32_t round_sig_to_format(uint64_t sig, int top, int exp, int t, int w)
+{
+    const int bias = (1 << (w - 1)) - 1, emin = 1 - bias;
+    const uint32_t inf = ((1u << w) - 1u) << t;
+    int drop = top - t;
+    if (exp < emin) drop += emin - exp;
+    uint64_t q, rem, half;
+    if (drop <= 0) { q = sig << -drop; rem = 0; half = 1; }
+    else if (drop > 63) { q = 0; rem = sig != 0; half = 2; }
+    else { q = sig >> drop; rem = sig & ((1ull << drop) - 1); half = 1ull << (drop - 1); }
+    if (rem > half || (rem == half && (q & 1ull))) q += 1;
+    const uint64_t code = exp >= emin ? ((uint64_t)(exp + bias - 1) << t) + q : q;
+    return code < inf ? (uint32_t)code : inf;
+}
+
+// n·base, exactly, rounded once into the float format (t, w): its code.
+PSK_DEV uint32_t round_count_to_float(int64_t n, double base, int t, int w)
+{
+    if (n == 0) return 0u;
+    int64_t mb;
+    int eb;
+    take_apart(base, mb, eb);
+    const u128_t mag = (u128_t)(n < 0 ? -n : n) * (u128_t)mb;
+    const int bits = bit_length(mag), drop = bits > 62 ? bits - 62 : 0;
+    uint64_t sig = (uint64_t)(mag >> drop);
+    if (drop && (mag & ((((u128_t)1) << drop) - 1))) sig |= 1ull;
+    const int top = bits - drop - 1;
+    return (n < 0 ? (1u << (t + w)) : 0u) | round_sig_to_format(sig, top, eb + drop + top, t, w);
+}
+
+PSK_DEV int32_t load_count(const DevOperand &o, int64_t off, int64_t soff, double &unit)
+{
+    if (o.affine) {
+        unit = (double)o.affine_scale;
+        return affine_code_at(o, off) - o.affine_zero;
+    }
+    unit = (double)o.scales[soff];
+    return (int)((const int8_t *)o.p)[off];
+}
+
+// A store into the launch's output: its float type, or its affine format.
+PSK_DEV uint32_t store_out(const DevOperand &o, int64_t off, float x)
+{
+    if (o.affine) {
+        const int64_t q = affine_code_of((double)x, o.affine, o.affine_scale, o.affine_zero);
+        if (o.affine == 2) ((uint8_t *)const_cast<void *>(o.p))[off] = (uint8_t)q;
+        else ((int8_t *)const_cast<void *>(o.p))[off] = (int8_t)q;
+        return 0u;
+    }
+    return store_real(const_cast<void *>(o.p), o.dtype, off, x);
+}
+
+__global__ void __launch_bounds__(128) k_contract_int(const __grid_constant__ DevLaunch L)
+{
+    uint32_t ovf = 0;
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t lin = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; lin < L.total; lin += step) {
+        const int64_t b0 = operand_offset(L.in[0], L.dims, 0, L.n_outer, lin), b1 = operand_offset(L.in[1], L.dims, 0, L.n_outer, lin);
+        const int64_t q0 = L.in[0].affine ? 0 : scale_offset(L.in[0], L.dims, 0, L.n_outer, lin), q1 = L.in[1].affine ? 0 : scale_offset(L.in[1], L.dims, 0, L.n_outer, lin);
+        uint32_t acc = 0;
+        double u0 = 1.0, u1 = 1.0;
+        for (int64_t c = 0; c < L.inner; ++c) {
+            const int64_t o0 = operand_offset(L.in[0], L.dims, L.n_outer, L.n_inner, c), o1 = operand_offset(L.in[1], L.dims, L.n_outer, L.n_inner, c);
+            const int64_t s0 = L.in[0].affine ? 0 : scale_offset(L.in[0], L.dims, L.n_outer, L.n_inner, c), s1 = L.in[1].affine ? 0 : scale_offset(L.in[1], L.dims, L.n_outer, L.n_inner, c);
+            const int32_t a = load_count(L.in[0], b0 + o0, q0 + s0, u0), b = load_count(L.in[1], b1 + o1, q1 + s1, u1);
+            acc += (uint32_t)(a * b); // the product of two 9-bit integers fits; the sum wraps
+        }
+        if (L.inner == 0) { load_count(L.in[0], b0, q0, u0); load_count(L.in[1], b1, q1, u1); }
+        const int64_t n = (int32_t)acc;
+        const double base = u0 * u1; // exact: two 24-bit significands
+        const int64_t ooff = operand_offset(L.out, L.dims, 0, L.n_outer, lin);
+        void *outp = const_cast<void *>(L.out.p);
+        if (L.out.affine) {
+            int64_t mb;
+            int eb;
+            take_apart(base, mb, eb);
+            const int64_t nq = quotient_round_exact(n < 0, (u128_t)(n < 0 ? -n : n) * (u128_t)mb, eb, L.out.affine_scale);
+            const int64_t q = affine_clamp(nq + L.out.affine_zero, L.out.affine);
+            if (L.out.affine == 2) ((uint8_t *)outp)[ooff] = (uint8_t)q;
+            else ((int8_t *)outp)[ooff] = (int8_t)q;
+        } else if (L.out.dtype == PSK_F32) {
+            ((uint32_t *)outp)[ooff] = round_count_to_float(n, base, 23, 8);
+        } else if (L.out.dtype == PSK_BF16) {
+            ((uint16_t *)outp)[ooff] = (uint16_t)round_count_to_float(n, base, 7, 8);
+        } else if (L.out.dtype == PSK_F16) {
+            const uint32_t c = round_count_to_float(n, base, 10, 5);
+            ((uint16_t *)outp)[ooff] = (uint16_t)c;
+            if ((c & 0x7fffu) == 0x7c00u) ovf |= 1u; // a count is finite: an infinity here is the store's overflow
+        } else if (L.out.dtype == PSK_E8M15) {
+            const uint32_t c = round_count_to_float(n, base, 15, 8);
+            store_e8m15((uint8_t *)outp, ooff, c);
+            if ((c & 0x7fffffu) == 0x7f8000u) ovf |= 1u;
+        }
+    }
+    if (L.guarded && ovf) atomicOr(L.ovf, 1u);
+}
+
+// ---------------------------------------------------------------------------
 // PSK_OP_FUSED, generic: one thread per output element.
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) k_fused(const __grid_constant__ DevLaunch L)
@@ -90,7 +262,7 @@ __global__ void __launch_bounds__(256) k_fused(const __grid_constant__ DevLaunch
             }
             vals[s] = st.nargs == 1 ? prim_unary(st.prim, a[0], st.imm, L.status) : prim_binary(st.prim, a[0], a[1]);
         }
-        ovf |= store_real(const_cast<void *>(L.out.p), L.out.dtype, ooff, vals[L.n_steps - 1]);
+        ovf |= store_out(L.out, ooff, vals[L.n_steps - 1]);
     }
     if (L.guarded && ovf) atomicOr(L.ovf, 1u);
 }
@@ -810,12 +982,17 @@ PSK_DEV float f64_to_f32_odd(double x)
     return r;
 }
 
-__global__ void __launch_bounds__(256) k_convert(const void *src, int from, void *dst, int to, int64_t n, int guarded, uint32_t *flag)
+__global__ void __launch_bounds__(256) k_convert(const void *src, int from, void *dst, int to, int64_t n, int guarded, uint32_t *flag, int affine, int zero, float scale)
 {
     uint32_t ovf = 0;
     const int64_t step = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) {
-        if (from == PSK_F64) {
+        if (affine) { // the codes' values, (q - z)·s: exact in a double
+            const int q = affine == 2 ? (int)((const uint8_t *)src)[i] : (int)((const int8_t *)src)[i];
+            const double x = (double)(q - zero) * (double)scale;
+            if (to == PSK_F64) ((double *)dst)[i] = x;
+            else ovf |= store_real(dst, to, i, (float)x);
+        } else if (from == PSK_F64) {
             double x = ((const double *)src)[i];
             if (to == PSK_F64) ((double *)dst)[i] = x;
             else if (to == PSK_F32 || to == PSK_BF16) ovf |= store_real(dst, to, i, (float)x);

@@ -173,3 +173,14 @@ def test_calibrate_envelope_matches_the_oracle(cuda, oracle):
         h.call("apply", [ids], (2, 16, c["V"]))
         envs.append(h.envelope())
     assert envs[0] == envs[1] and len(envs[0]) > 25
+
+
+def test_w8a8_dense_is_exact_on_the_gpu(cuda, oracle):
+    """examples/tests/formats/w8a8.psk under w8a8.json with static scales: the integer path end to end."""
+    from test_oracle_w8a8 import w8a8_dense_case
+    for seed, shape in [(0, (4, 16, 8)), (1, (33, 130, 17))]:
+        rz, x, w, want = w8a8_dense_case(seed, *shape)
+        h = Host(cuda, rz).prepare("dense")
+        h.set_param("w", w)
+        got = h.call("apply", [x], want.shape, np.float64)
+        assert np.array_equal(got, want)

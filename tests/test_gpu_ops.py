@@ -267,3 +267,22 @@ def test_contraction_exact_generic_strides(cuda, oracle):
     set_operand(l.out, abi.F32, [13, 6], [0, 1])
     got, want, _, _ = run_both(cuda, oracle, l, [a, b], 13 * 6 * 4)
     assert np.array_equal(got, want)
+
+
+def test_integer_sums_over_scaled_values_are_exact(cuda, oracle):
+    """`product: i32, accum: i32`: affine activations times int8 weights summed in 32 bits that wrap,
+    stored once from the exact value into f16, bf16, f32, e8m15 or an affine format: the bits of
+    exact arithmetic written out in Python integers (tests/exact.py), 120 random trials."""
+    import w8a8_cases
+    rng = np.random.default_rng(0x180004)
+    for trial in range(120):
+        l, ins, sw, out_bytes, view, want = w8a8_cases.make_case(rng, trial)
+        dev = [cuda.upload(a) for a in ins]
+        pout, psw = cuda.alloc(out_bytes), cuda.upload(sw)
+        cuda.run(l, dev + [pout, psw])
+        cuda.overflow()
+        cuda.sync()
+        got = w8a8_cases.decode(cuda.download(pout, out_bytes), view, *want.shape)
+        for p in dev + [pout, psw]:
+            cuda.free(p)
+        assert np.array_equal(got, want), f"trial {trial}"
