@@ -36,20 +36,30 @@ sys.path.insert(0, ROOT)
 WORKLOADS = {
     # BASELINE.json configs[3]: 32 layers, d 4096, 32 heads of 128, SwiGLU 11008, vocab 32000, seq 2048, batch 8 a GPU
     "llama7b_prefill_b8_t2048": dict(consts=dict(V=32000, D=4096, H=32, G=32, FF=11008, L=32), B=8, T=2048),
+    # BASELINE.json configs[4], int8 half: the same architecture, projection and FFN weights int8 with one f32 scale a
+    # channel, bf16 activations, seq 1024, batch 16 a GPU
+    "llama7b_int8_prefill_b16_t1024": dict(consts=dict(V=32000, D=4096, H=32, G=32, FF=11008, L=32), B=16, T=1024, int8=True),
     # a small shape of the same program, for trying the script out
     "llama_small": dict(consts=dict(V=4096, D=1024, H=8, G=8, FF=2816, L=4), B=4, T=512),
 }
 
 
-def realization(paths):
+QUANTISED = ("blocks.attn.wq", "blocks.attn.wk", "blocks.attn.wv", "blocks.attn.wo", "blocks.ff.gate.w", "blocks.ff.up.w", "blocks.ff.down.w")
+
+
+def realization(paths, int8=False):
     """A solved-style mixed bf16/f32 assignment: bf16 storage, f32 where a sum's result is reused
-    widely (the norms' mean and root, the logits and the loss)."""
-    return {
+    widely (the norms' mean and root, the logits and the loss); with `int8`, the projection and
+    FFN weights as integers with one scale a channel (`quant`, over the contracted axis)."""
+    rz = {
         "default": "bf16",
         "order": {"kind": "device"},
-        "params": {p: "bf16" for p in paths},
+        "params": {p: "bf16" for p in paths if not (int8 and p in QUANTISED)},
         "storage": {"RMSNorm.apply/%3": "f32", "RMSNorm.apply/%7": "f32", "Llama.apply/%11": "f32", "loss/%5": "f32", "loss/%6": "f32"},
     }
+    if int8:
+        rz["quant"] = {p: {"bits": 8, "over": -2} for p in QUANTISED}
+    return rz
 
 
 def param_shapes(c):
@@ -106,7 +116,7 @@ class ClockSampler:
         return {"sm_mhz": int(statistics.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def cpu_prefill_tokens_per_s(consts, T, B, threads):
+def cpu_prefill_tokens_per_s(consts, T, B, threads, int8=False):
     """The CPU restatement on a bounded sample: one and two layers at a short sequence, one
     batch row; the per-layer time and the rest extrapolate to the whole depth."""
     sys.path.insert(0, os.path.join(ROOT, "tests"))
@@ -123,7 +133,7 @@ def cpu_prefill_tokens_per_s(consts, T, B, threads):
     for L in (1, 2):
         c = dict(consts, L=L)
         shapes = param_shapes(c)
-        rz = realization(shapes)
+        rz = realization(shapes, int8)
         rz["order"] = {"kind": "sequential"}
         h = Host(orc.vtable(), rz).prepare("llama", **c)
         for path, (shape, std) in shapes.items():
@@ -239,7 +249,7 @@ def main():
         vals = []
         sample = ""
         for _ in range(max(1, min(args.steps, 2))):
-            v, sample = cpu_prefill_tokens_per_s(consts, T, B, threads)
+            v, sample = cpu_prefill_tokens_per_s(consts, T, B, threads, w.get("int8", False))
             vals.append(v)
         v = statistics.median(vals)
         print(json.dumps({
@@ -260,7 +270,7 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     ex = Executor(local)
     shapes = param_shapes(consts)
-    host = Host(ex, realization(shapes)).prepare("llama", **consts)
+    host = Host(ex, realization(shapes, w.get("int8", False))).prepare("llama", **consts)
     for i, (path, (shape, std)) in enumerate(shapes.items()):
         host.init_param(path, 1000 + i, std, shape)
     ex.sync()
@@ -364,7 +374,7 @@ def main():
         }
         if world == 1 and not args.no_cpu_baseline:
             try:
-                v, sample = cpu_prefill_tokens_per_s(consts, T, B, threads)
+                v, sample = cpu_prefill_tokens_per_s(consts, T, B, threads, w.get("int8", False))
                 out["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample}
             except Exception as e:  # the baseline is reported, never the product's path
                 out["cpu_baseline"] = {"value": None, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": f"failed: {e}"}

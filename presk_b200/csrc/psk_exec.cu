@@ -43,6 +43,9 @@ struct psk_exec {
     std::unordered_map<void *, size_t> sizes;          // every live buffer and its bytes
     std::map<size_t, std::vector<void *>> pool;        // freed buffers by exact size
     std::unordered_map<void *, int64_t> causal;        // buffers a causal_mask launch wrote: its n
+    // int8 weights read by the tensor-core contraction: their integers as bf16, made once per buffer
+    // (weights are never written after they are stored), keyed by the codes' address and count
+    std::map<std::pair<const void *, int64_t>, void *> widened;
     uint32_t *flags = nullptr;                         // kFlagSlots words of the overflow guard
     uint32_t *status = nullptr;                        // one word: kernel-side trouble
     std::vector<int64_t> flag_serial;                  // the launch each slot was last given to
@@ -320,7 +323,7 @@ bool make_map(psk_exec *e, CUtensorMap *map, const void *base, int f16, uint64_t
     return r == CUDA_SUCCESS;
 }
 
-int launch_tc(psk_exec *e, const psk_gemm &g, const void *a, const void *b, void *c, uint32_t *flag)
+int launch_tc(psk_exec *e, const psk_gemm &g, const void *a, const void *b, void *c, uint32_t *flag, const float *col_scale = nullptr, int64_t cs_stride = 0, int64_t cs_lo = 0, int64_t cs_hi = 0)
 {
     if (!e->encode) return fail(e, PSK_E10001, "cuTensorMapEncodeTiled is not available from this driver");
     const bool f16 = g.in_dtype == PSK_F16;
@@ -344,6 +347,7 @@ int launch_tc(psk_exec *e, const psk_gemm &g, const void *a, const void *b, void
     const int64_t va = g.out_dtype == PSK_F32 ? 4 : 8; // elements in 16 bytes
     P.vec_ok = aligned16(c) && g.c_row_lo % va == 0 && g.c_row_hi % va == 0 && g.c_col_hi % va == 0 && g.c_lo % va == 0 && g.c_hi % va == 0 && g.c_col_lo_count % (g.out_dtype == PSK_F32 ? 32 : 64) == 0 && g.n % va == 0 && g.out_dtype != PSK_E8M15;
     P.scale = g.scale; P.scale_on = g.scale_on;
+    P.col_scale = col_scale; P.col_scale_stride = cs_stride; P.col_scale_lo = cs_lo; P.col_scale_hi = cs_hi;
     P.ovf = flag; P.status = e->status;
     if (!e->tc_attr_set) {
         CUDA_TRY(e, cudaFuncSetAttribute(tc::k_gemm_tc<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::Smem<256>::TOTAL));
@@ -419,6 +423,7 @@ void psk_exec_destroy(psk_exec *e)
     cudaSetDevice(e->device);
     cudaStreamSynchronize(e->stream);
     for (auto &kv : e->sizes) cudaFree(kv.first);
+    for (auto &kv : e->widened) cudaFree(kv.second);
     cudaFree(e->flags);
     cudaFree(e->status);
     cudaEventDestroy(e->ev0);
@@ -471,6 +476,12 @@ void psk_exec_free(psk_exec *e, void *p)
     if (it == e->sizes.end()) return;
     e->live -= it->second;
     e->causal.erase(p);
+    // widened copies of weights that lived in this buffer
+    for (auto w = e->widened.begin(); w != e->widened.end();) {
+        const uint8_t *q = (const uint8_t *)w->first.first;
+        if (q >= (const uint8_t *)p && q < (const uint8_t *)p + it->second) { cudaFree(w->second); w = e->widened.erase(w); }
+        else ++w;
+    }
     // The stream is in order and every kernel of this executor runs on it, so
     // a buffer handed out again is written only after its last reader ran.
     e->pool[it->second].push_back(p);
@@ -733,6 +744,44 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
         GemmMap g;
         bool mapped = map_gemm(L, g);
         const DevOperand &A = L.in[0], &B = L.in[1];
+        // int8 weights (operand 1) against bf16 activations under the device order: the weights' integers
+        // widened to bf16 once, the channel's scale applied to the sum
+        const bool w8 = mapped && device_order && e->encode && B.dtype == PSK_I8 && B.scales && !B.affine && A.dtype == PSK_BF16 && !l->int_accum
+            && (L.kdtype == PSK_BF16 || L.kdtype == PSK_F32) && g.a_k == 1 && (g.b_k == 1 || g.b_n == 1) && aligned16(A.p) && g.c_col_lo == 1 && g.n >= 8 && g.k >= 8;
+        if (w8) {
+            const int64_t count = l->in[1].numel;
+            auto key = std::make_pair(B.p, count);
+            auto it = e->widened.find(key);
+            if (it == e->widened.end()) {
+                void *wb = nullptr;
+                if (cudaMalloc(&wb, (size_t)count * 2) != cudaSuccess) { cudaGetLastError(); wb = nullptr; }
+                if (wb) {
+                    k_int8_to_bf16<<<grid_for(e, count, 256, 8), 256, 0, e->stream>>>((const int8_t *)B.p, (uint16_t *)wb, count);
+                    e->kernels += 1;
+                    it = e->widened.emplace(key, wb).first;
+                }
+            }
+            if (it != e->widened.end()) {
+                psk_gemm pg;
+                memset(&pg, 0, sizeof pg);
+                pg.in_dtype = PSK_BF16; pg.out_dtype = L.out.dtype; pg.b_n_major = g.b_k == 1 ? 0 : 1; pg.guarded = L.guarded;
+                pg.m = g.m; pg.n = g.n; pg.k = g.k; pg.batch = g.batch; pg.batch_lo = g.batch_lo;
+                pg.a_row = g.a_row; pg.a_lo = g.a_lo; pg.a_hi = g.a_hi;
+                pg.b_row = pg.b_n_major ? g.b_k : g.b_n; pg.b_lo = g.b_lo; pg.b_hi = g.b_hi;
+                pg.c_row_lo_count = g.c_row_lo_count; pg.c_row_lo = g.c_row_lo; pg.c_row_hi = g.c_row_hi;
+                pg.c_col_lo_count = g.c_col_lo_count; pg.c_col_hi = g.c_col_hi; pg.c_lo = g.c_lo; pg.c_hi = g.c_hi;
+                if (g.m == 1) pg.a_row = g.k;
+                std::string keep = e->error;
+                int r = launch_tc(e, pg, A.p, it->second, const_cast<void *>(L.out.p), L.ovf, B.scales, g.bs_n, g.bs_lo, g.bs_hi);
+                if (r == PSK_OK) {
+                    e->last_kernel = "k_gemm_tc";
+                    e->last_flops = 2.0 * (double)g.m * (double)g.n * (double)g.k * (double)g.batch;
+                    break;
+                }
+                if (r != PSK_E7001) { rc = r; break; }
+                e->error = keep; // strides no tensor map takes: the exact kernel below
+            }
+        }
         bool tc_ok = mapped && device_order && e->encode && A.dtype == B.dtype && (A.dtype == PSK_BF16 || A.dtype == PSK_F16)
             && (L.kdtype == A.dtype || L.kdtype == PSK_F32 || (L.kdtype == PSK_E8M15))
             && g.a_k == 1 && (g.b_k == 1 || g.b_n == 1) && aligned16(A.p) && aligned16(B.p) && g.c_col_lo == 1 && g.m >= 1 && g.n >= 8 && g.k >= 8;

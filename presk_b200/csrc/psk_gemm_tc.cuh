@@ -57,6 +57,11 @@ struct Params {
     int vec_ok; // 128-bit stores are aligned
     float scale;
     int scale_on;
+    // integer weights: operand 1 holds the weights' integers as bf16 numbers (exact), and the
+    // accumulator of column c is multiplied once by the channel's scale col_scale[c * col_scale_stride
+    // + batch terms] before it is rounded: (sum_k x·q)·s where the reference has sum_k x·(q·s)
+    const float *col_scale;
+    int64_t col_scale_stride, col_scale_lo, col_scale_hi;
     uint32_t *ovf;
     uint32_t *status;
 };
@@ -318,6 +323,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int64_t row0 = m0 + quad * 32;
             const int64_t boff = blo * P.c_lo + bhi * P.c_hi;
+            const float *cs_base = P.col_scale ? P.col_scale + blo * P.col_scale_lo + bhi * P.col_scale_hi : nullptr;
             const int64_t row = row0 + lane;
             const int64_t row_off = boff + (row / P.c_row_lo_count) * P.c_row_hi + (row % P.c_row_lo_count) * P.c_row_lo;
             const uint32_t tbase = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
@@ -335,6 +341,13 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
                         for (int q = 0; q < 8; ++q) {
                             float x0 = __uint_as_float(v[4 * q]), x1 = __uint_as_float(v[4 * q + 1]), x2 = __uint_as_float(v[4 * q + 2]), x3 = __uint_as_float(v[4 * q + 3]);
                             if (P.scale_on) { x0 = __fmul_rn(x0, P.scale); x1 = __fmul_rn(x1, P.scale); x2 = __fmul_rn(x2, P.scale); x3 = __fmul_rn(x3, P.scale); }
+                            if (P.col_scale) {
+                                const int64_t cc = col + 4 * q;
+                                if (cc + 3 < P.n) {
+                                    x0 = __fmul_rn(x0, cs_base[cc * P.col_scale_stride]); x1 = __fmul_rn(x1, cs_base[(cc + 1) * P.col_scale_stride]);
+                                    x2 = __fmul_rn(x2, cs_base[(cc + 2) * P.col_scale_stride]); x3 = __fmul_rn(x3, cs_base[(cc + 3) * P.col_scale_stride]);
+                                }
+                            }
                             stage_out[lane * 8 + (q ^ (lane & 7))] = make_uint4(__float_as_uint(x0), __float_as_uint(x1), __float_as_uint(x2), __float_as_uint(x3));
                         }
                     } else {
@@ -352,6 +365,15 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
                                     float x0 = __uint_as_float(half ? vb[q * 8 + 2 * i] : va[q * 8 + 2 * i]);
                                     float x1 = __uint_as_float(half ? vb[q * 8 + 2 * i + 1] : va[q * 8 + 2 * i + 1]);
                                     if (P.scale_on) { x0 = __fmul_rn(x0, P.scale); x1 = __fmul_rn(x1, P.scale); }
+                                    if (P.col_scale) {
+                                        const int64_t cc = col + half * 32 + q * 8 + 2 * i;
+                                        if (cc + 1 < P.n) {
+                                            x0 = __fmul_rn(x0, cs_base[cc * P.col_scale_stride]);
+                                            x1 = __fmul_rn(x1, cs_base[(cc + 1) * P.col_scale_stride]);
+                                        } else if (cc < P.n) {
+                                            x0 = __fmul_rn(x0, cs_base[cc * P.col_scale_stride]);
+                                        }
+                                    }
                                     // the hardware's rounding: the reference's for every number; a NaN
                                     // comes out canonical (its sign and payload are not kept on this path)
                                     if (P.out_dtype == PSK_BF16) {
@@ -398,6 +420,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
                                 const int64_t o = row_off + (cc / P.c_col_lo_count) * P.c_col_hi + (cc % P.c_col_lo_count);
                                 float x = __uint_as_float(v[i]);
                                 if (P.scale_on) x = __fmul_rn(x, P.scale);
+                                if (P.col_scale) x = __fmul_rn(x, cs_base[cc * P.col_scale_stride]);
                                 ovf |= store_real(P.c, P.out_dtype, o, x);
                             }
                     }

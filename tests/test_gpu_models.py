@@ -184,3 +184,25 @@ def test_w8a8_dense_is_exact_on_the_gpu(cuda, oracle):
         h.set_param("w", w)
         got = h.call("apply", [x], want.shape, np.float64)
         assert np.array_equal(got, want)
+
+
+def test_llama_int8_weights_on_tensor_cores(cuda, oracle):
+    """BASELINE config 5's shape of program at small constants: int8 projection and FFN weights with one
+    f32 scale a channel, bf16 activations, device order: the weights' integers go through the tensor
+    cores as bf16 numbers and the scale multiplies the sum. Against the oracle's sequential
+    sum of x·(q·s) the difference is a reassociation: a few bf16 ulps after two layers."""
+    c = dict(V=512, D=256, H=4, G=4, FF=512, L=2)
+    p = models.llama_params(c)
+    ids = np.random.default_rng(5).integers(0, c["V"], size=(2, 128), dtype=np.int64)
+    q = {k: {"bits": 8, "over": -2} for k in ("blocks.attn.wq", "blocks.attn.wk", "blocks.attn.wv", "blocks.attn.wo", "blocks.ff.gate.w", "blocks.ff.up.w", "blocks.ff.down.w")}
+    rz = {"default": "bf16", "order": {"kind": "device"}, "params": {"tok": "bf16", "head": "bf16", "norm.γ": "bf16", "blocks.n1.γ": "bf16", "blocks.n2.γ": "bf16"}, "quant": q, "storage": {"Llama.apply/%11": "f32"}}
+    ex_before = cuda.counts()
+    cuda.set_profiling(True)
+    h = models.give(Host(cuda, rz).prepare("llama", **c), p)
+    got = h.call("apply", [ids], (2, 128, c["V"]))
+    kinds = [r[0] for r in cuda.profile() if r[1] in ("dot", "ein[batch, seq, model]")]
+    cuda.set_profiling(False)
+    assert kinds and all(k == "k_gemm_tc" for k in kinds), kinds
+    ho = models.give(Host(oracle.vtable(), dict(rz, order={"kind": "sequential"})).prepare("llama", **c), p)
+    want = ho.call("apply", [ids], (2, 128, c["V"]))
+    assert np.abs(got - want).max() <= 2.0**-6 * np.abs(want).max()
