@@ -47,13 +47,13 @@ WORKLOADS = {
 QUANTISED = ("blocks.attn.wq", "blocks.attn.wk", "blocks.attn.wv", "blocks.attn.wo", "blocks.ff.gate.w", "blocks.ff.up.w", "blocks.ff.down.w")
 
 
-def realization(paths, int8=False):
+def realization(paths, int8=False, attention="unfused"):
     """A solved-style mixed bf16/f32 assignment: bf16 storage, f32 where a sum's result is reused
     widely (the norms' mean and root, the logits and the loss); with `int8`, the projection and
     FFN weights as integers with one scale a channel (`quant`, over the contracted axis)."""
     rz = {
         "default": "bf16",
-        "order": {"kind": "device"},
+        "order": {"kind": "device", "attention": attention},
         "params": {p: "bf16" for p in paths if not (int8 and p in QUANTISED)},
         "storage": {"RMSNorm.apply/%3": "f32", "RMSNorm.apply/%7": "f32", "Llama.apply/%11": "f32", "loss/%5": "f32", "loss/%6": "f32"},
     }
@@ -154,7 +154,8 @@ def cpu_prefill_tokens_per_s(consts, T, B, threads, int8=False):
 def microbench(args):
     """One kernel alone on synthetic operands, for tuning and for profiler captures:
     `--micro gemm --shape M,N,K[,batch[,b_n_major]]`, `--micro softmax --shape rows,n`,
-    `--micro ew --shape rows,cols`. Prints one JSON line (not the benchmark's)."""
+    `--micro ew --shape rows,cols`, `--micro attn --shape batch,heads,seq` (hd = 128, causal).
+    Prints one JSON line (not the benchmark's)."""
     import torch
     from presk_b200 import Executor, abi, launch_desc
 
@@ -195,6 +196,31 @@ def microbench(args):
         ms = timed(lambda: ex.gemm(g, a, b, c), args.steps)
         fl = 2.0 * m * n * k * batch
         print(json.dumps({"micro": "gemm", "shape": dims, "ms": ms, "TFLOP/s": fl / ms / 1e9, "GB/s": (batch * (m * k + n * k + m * n) * 2) / ms / 1e6}))
+    elif args.micro == "attn":
+        B, H, t = dims[:3]
+        hd = 128
+        q, k, v = ex.upload(bf16((B, H, t, hd))), ex.upload(bf16((B, H, t, hd))), ex.upload(bf16((B, t, H, hd)))
+        rt = ex.upload(np.array([0x4135], np.uint16))  # bf16(sqrt(128)) = 11.3125
+        out = ex.alloc(B * H * t * hd * 2)
+        lm = launch_desc(abi.OP_IOTA, abi.F32, [t, t])
+        lm.kind = abi.IOTA_CAUSAL
+        lm.out.dtype, lm.out.is_index, lm.out.stride[0], lm.out.stride[1] = abi.I64, 1, t, 1
+        mask = ex.alloc(t * t * 8)
+        ex.run(lm, [mask])
+        l = launch_desc(abi.OP_ATTENTION, abi.BF16, [B, H, t, hd], [t], order=abi.ORDER_DEVICE, name=b"attention[blockwise]")
+        l.n_inputs, l.masked = 5, 1
+        l.iparam[1] = l.iparam[2] = l.iparam[3] = abi.BF16
+        n = B * H * t * hd
+        for o, st in ((l.inputs[0], (H * t * hd, t * hd, hd, 1, 0)), (l.inputs[1], (H * t * hd, t * hd, 0, 1, hd)), (l.inputs[2], (t * H * hd, hd, 0, 1, H * hd)), (l.out, (t * H * hd, hd, H * hd, 1, 0))):
+            o.dtype, o.numel = abi.BF16, n
+            for a, x in enumerate(st):
+                o.stride[a] = x
+        l.inputs[3].dtype, l.inputs[3].numel = abi.BF16, 1
+        l.inputs[4].dtype, l.inputs[4].is_index, l.inputs[4].stride[2], l.inputs[4].stride[4], l.inputs[4].numel = abi.I64, 1, t, 1, t * t
+        ms = timed(lambda: ex.run(l, [q, k, v, rt, mask, out]), args.steps)
+        nqb = t // 128
+        fl = 4.0 * B * H * (nqb * (nqb + 1) / 2) * 128 * 128 * hd
+        print(json.dumps({"micro": "attn", "shape": dims, "ms": ms, "TFLOP/s (causal blocks, one pass)": fl / ms / 1e9}))
     elif args.micro in ("softmax", "ew"):
         rows, n = dims[:2]
         x = ex.upload(bf16((rows, n)))
@@ -225,13 +251,14 @@ def microbench(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--micro", default=None, choices=["gemm", "softmax", "ew"])
+    ap.add_argument("--micro", default=None, choices=["gemm", "softmax", "ew", "attn"])
     ap.add_argument("--shape", default="8192,8192,8192")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="llama7b_prefill_b8_t2048", choices=sorted(WORKLOADS))
+    ap.add_argument("--attention", default="blockwise", choices=["blockwise", "unfused"], help="the declared order of the attention launches: one blockwise kernel, or the reference's four launches")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--dump-profile", default=None, help="write the per-launch-name times of the timed steps to this file")
     args = ap.parse_args()
@@ -241,7 +268,7 @@ def main():
     consts, B, T = w["consts"], w["B"], w["T"]
     rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
     threads = os.cpu_count() or 1
-    config = {"workload": args.workload, **{k: v for k, v in consts.items()}, "batch_per_gpu": B, "seq_len": T, "global_batch": B * world, "parallelism": f"dp{world}", "realization": "bf16 storage, f32 norm statistics/logits/loss, order device", "l2": "inputs_larger_than_l2 (13.5 GB of weights stream through every step)"}
+    config = {"workload": args.workload, **{k: v for k, v in consts.items()}, "batch_per_gpu": B, "seq_len": T, "global_batch": B * world, "parallelism": f"dp{world}", "realization": "bf16 storage, f32 norm statistics/logits/loss, order device, attention " + args.attention, "l2": "inputs_larger_than_l2 (13.5 GB of weights stream through every step)"}
 
     if args.impl == "reference":
         if rank != 0:
@@ -270,7 +297,7 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     ex = Executor(local)
     shapes = param_shapes(consts)
-    host = Host(ex, realization(shapes, w.get("int8", False))).prepare("llama", **consts)
+    host = Host(ex, realization(shapes, w.get("int8", False), args.attention)).prepare("llama", **consts)
     for i, (path, (shape, std)) in enumerate(shapes.items()):
         host.init_param(path, 1000 + i, std, shape)
     ex.sync()

@@ -77,13 +77,22 @@ typedef enum {
     PSK_OP_COPY = 7,     /* lower.rs:1554-1667: slice, concat, split_heads, merge_heads, index, broadcast_like */
     PSK_OP_IOTA = 8,     /* lower.rs:1706-1750: positions, causal_mask, one_hot, fill */
     PSK_OP_CONVERT = 9,  /* host.rs:809-829: Buf::of(to, b.to_f64()) at a kernel's edge */
-    PSK_OP_MAGNITUDE = 10 /* presk-precision/src/envelope.rs:29-127: a site's max |x|, least non-zero |x|, least
+    PSK_OP_MAGNITUDE = 10, /* presk-precision/src/envelope.rs:29-127: a site's max |x|, least non-zero |x|, least
                              and greatest x. Output: four u32 words, merged into what they hold (so that one
                              slot collects several launches and several ranks): [0] bits of max |x|, start 0;
                              [1] bits of the least non-zero |x|, start 0x7f800000; [2], [3] least and greatest
                              x under the order-preserving map u = b ^ (b >> 31 ? 0xffffffff : 0x80000000) of
                              its bits b, start 0xff800000 and 0x007fffff. NaNs are passed over. No counterpart
                              among the reference's kernels: it measures envelopes on its exact interpreter. */
+    PSK_OP_ATTENTION = 11 /* four launches of an attention function as one (examples/coverage/llama.psk:100-102):
+                             scores = ein(q*k) over hd, scores / rt, softmax over seq2 where mask, ein(a*v) over
+                             seq2. Space: outer axes (..., seq, hd), one inner axis seq2. Inputs: q (stride 0 on
+                             seq2), k and v (stride 0 on seq; hd and seq2 both walked), rt (rank 0), and the mask
+                             over (seq, seq2) when n_inputs is 5. iparam[1..3]: the storage types of the three
+                             sites in between. The value is DEFINED as that of the four launches run one after
+                             the other; an executor may only fuse them under PSK_ORDER_DEVICE, and then agrees
+                             with them within a tolerance. No counterpart among the reference's kernels: its
+                             fusion (presk-core/src/fusion.rs) never crosses a contraction or a softmax. */
 } psk_op;
 
 /* Elementary operations of a fusion group's steps (lower.rs:184-226). */

@@ -454,8 +454,106 @@ static int psk_oracle_run_merged(const psk_launch *l, void *const *table, uint32
 /* Summed axes that every operand walks as one (stride[a] = stride[a+1]·dims[a+1]) are one axis:
  * the terms come in the same lexicographic order either way, so a contraction over several
  * contiguous axes (the output projection's groups, per, hd) is the nest over their product. */
+int psk_oracle_run(const psk_launch *l, void *const *table, uint32_t *overflow);
+
+/* PSK_OP_ATTENTION is by definition its four launches one after the other (examples/coverage/llama.psk:100-102:
+ * ein(q*k), / rt, softmax where mask, ein(a*v)), each of them the reference's own nest with its result stored in
+ * its site's type. The space (.., seq, hd | seq2) is re-read as (.., seq, seq2 | hd) for the first three. */
+static void attn_operand(psk_operand *d, const psk_operand *s, int no)
+{
+    *d = *s;
+    d->stride[no - 1] = s->stride[no];     /* seq2 becomes the last outer axis */
+    d->stride[no] = s->stride[no - 1];     /* hd the summed one */
+    d->scale_stride[no - 1] = s->scale_stride[no];
+    d->scale_stride[no] = s->scale_stride[no - 1];
+}
+
+static void attn_contiguous(psk_operand *d, int dtype, const int64_t *dims, int naxes, int skip)
+{
+    memset(d, 0, sizeof *d);
+    d->dtype = dtype;
+    int64_t acc = 1;
+    for (int a = naxes - 1; a >= 0; --a) {
+        if (a == skip) continue;
+        d->stride[a] = acc;
+        acc *= dims[a];
+    }
+    d->numel = acc;
+}
+
+static int attention_unfused(const psk_launch *l, void *const *table, uint32_t *overflow)
+{
+    const int no = l->n_outer;
+    if (no < 2 || no > PSK_MAX_RANK || l->n_inner != 1 || (l->n_inputs != 4 && l->n_inputs != 5)) return PSK_E7001;
+    const int64_t hd = l->dims[no - 1], t2 = l->dims[no];
+    int64_t rows = 1;
+    for (int a = 0; a < no - 1; ++a) rows *= l->dims[a];
+    const int d_scores = (int)l->iparam[1], d_scaled = (int)l->iparam[2], d_soft = (int)l->iparam[3];
+    const size_t n = (size_t)(rows * t2 ? rows * t2 : 1);
+    void *se = malloc(n * elem_bytes(d_scores)), *sc = malloc(n * elem_bytes(d_scaled)), *sm = malloc(n * elem_bytes(d_soft));
+    uint32_t ovf = 0, o1 = 0;
+    int rc = PSK_OK;
+    psk_launch m;
+    int64_t dims[PSK_MAX_AXES];
+    for (int a = 0; a < no - 1; ++a) dims[a] = l->dims[a];
+    dims[no - 1] = t2;
+    dims[no] = hd;
+    /* scores */
+    memset(&m, 0, sizeof m);
+    m.name = "attention: scores"; m.op = PSK_OP_CONTRACT; m.dtype = d_scores; m.order = l->order; m.guarded = l->guarded;
+    m.n_inputs = 2; m.n_outer = no; m.n_inner = 1;
+    memcpy(m.dims, dims, sizeof dims);
+    attn_operand(&m.in[0], &l->in[0], no);
+    attn_operand(&m.in[1], &l->in[1], no);
+    attn_contiguous(&m.out, d_scores, dims, no, -1);
+    { void *t[3] = {table[0], table[1], se}; rc = psk_oracle_run(&m, t, &o1); ovf |= o1; }
+    /* scores / rt */
+    if (rc == PSK_OK) {
+        memset(&m, 0, sizeof m);
+        m.name = "attention: div"; m.op = PSK_OP_FUSED; m.dtype = d_scaled; m.order = l->order; m.guarded = l->guarded;
+        m.n_inputs = 2; m.n_outer = no; m.n_inner = 0;
+        memcpy(m.dims, dims, sizeof dims);
+        attn_contiguous(&m.in[0], d_scores, dims, no, -1);
+        m.in[1] = l->in[3];
+        memset(m.in[1].stride, 0, sizeof m.in[1].stride);
+        attn_contiguous(&m.out, d_scaled, dims, no, -1);
+        m.n_steps = 1;
+        m.steps[0].prim = PSK_DIV; m.steps[0].nargs = 2; m.steps[0].src[0] = 0; m.steps[0].src[1] = 1;
+        void *t[3] = {se, table[3], sc};
+        rc = psk_oracle_run(&m, t, &o1); ovf |= o1;
+    }
+    /* softmax over seq2 */
+    if (rc == PSK_OK) {
+        memset(&m, 0, sizeof m);
+        m.name = "attention: softmax"; m.op = PSK_OP_SOFTMAX; m.dtype = d_soft; m.order = l->order; m.guarded = l->guarded;
+        m.n_inputs = l->n_inputs == 5 ? 2 : 1; m.masked = l->n_inputs == 5; m.n_outer = no - 1; m.n_inner = 1;
+        memcpy(m.dims, dims, sizeof dims);
+        attn_contiguous(&m.in[0], d_scaled, dims, no, -1);
+        attn_contiguous(&m.out, d_soft, dims, no, -1);
+        if (m.masked) attn_operand(&m.in[1], &l->in[4], no);
+        void *t[3] = {sc, m.masked ? table[4] : sm, sm};
+        if (!m.masked) t[1] = sm;
+        rc = psk_oracle_run(&m, t, &o1); ovf |= o1;
+    }
+    /* the weighted values */
+    if (rc == PSK_OK) {
+        m = *l;
+        m.name = "attention: values"; m.op = PSK_OP_CONTRACT; m.n_inputs = 2;
+        attn_contiguous(&m.in[0], d_soft, dims, no, -1);
+        m.in[0].stride[no] = m.in[0].stride[no - 1]; /* seq2 is the summed axis again, */
+        m.in[0].stride[no - 1] = 0;                  /* and hd is not an axis of the weights */
+        m.in[1] = l->in[2];
+        void *t[3] = {sm, table[2], table[l->n_inputs]};
+        rc = psk_oracle_run(&m, t, &o1); ovf |= o1;
+    }
+    free(se); free(sc); free(sm);
+    if (overflow) *overflow = ovf;
+    return rc;
+}
+
 int psk_oracle_run(const psk_launch *l, void *const *table, uint32_t *overflow)
 {
+    if (l->op == PSK_OP_ATTENTION) return attention_unfused(l, table, overflow);
     if (l->op == PSK_OP_CONTRACT && l->n_inner > 1) {
         psk_launch m = *l;
         int no = l->n_outer, w = 0;

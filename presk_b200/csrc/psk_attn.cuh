@@ -1,0 +1,288 @@
+// Blockwise causal attention for sm_100a: scores, scaling, masked softmax and
+// the product with the values in one kernel, the scores never in memory.
+//
+// What it replaces: the launches `ein[.., seq, seq2](q*k)`, `div` by sqrt(hd),
+// `softmax axis seq2 where mask`, `ein[.., seq, .., hd](a*v)` of an attention
+// function (examples/coverage/llama.psk:100-102), each of which the reference
+// runs as its own nest with its result stored in memory. It is used only under
+// the declared order "device" with `"attention": "blockwise"`, since it is a
+// different realization and not only a reordering of sums:
+//   - a score is rounded to bf16, divided by the root (the division's own
+//     result, by its correctly rounded reciprocal and one correction) and
+//     rounded to bf16 again, exactly as the two stored sites would hold it;
+//   - the row's maximum is taken over those values in a first pass over the
+//     key blocks, so the exponentials have the reference's arguments;
+//   - exp is the hardware's ex2 (relative error about 2^-22), the row's sum is
+//     accumulated block by block in f32, the unnormalised exponentials are
+//     rounded to bf16 for the second product and the quotient by the sum is
+//     taken once at the end, where the reference rounds exp/sum to bf16 first.
+// The result agrees with the unfused sequence to about a bf16 unit in the last
+// place of the output (tests state the tolerance).
+//
+// One CTA per (batch, head, block of 128 queries), 192 threads: warp 0 loads Q
+// once and K, V blocks through rings with TMA; warp 1 issues tcgen05.mma for
+// S = Q·K^T (into one of two 128-column accumulators) and O += P·V; warps 2-5
+// hold one query row a thread (its TMEM lane), so a row's maximum and sum need
+// no exchange between threads. Head dimension 128, bf16 in and out, sequence a
+// multiple of 128. Every wait is bounded as in psk_gemm_tc.cuh.
+#pragma once
+#include "psk_gemm_tc.cuh"
+#include "psk_hot.cuh"
+
+namespace psk {
+namespace attn {
+
+constexpr int BM = 128, BN = 128, HD = 128;
+constexpr int THREADS = 192;
+constexpr int TILE = 128 * 128 * 2;   // a 128 x 128 bf16 tile: two 16 KB halves of 64 columns
+constexpr int HALF = 128 * 64 * 2;
+constexpr int SMEM_TILES = 6 * TILE;  // Q, K x2, V x2, P
+constexpr int SMEM_TOTAL = SMEM_TILES + 256 + 1024;
+
+struct Params {
+    int64_t T;
+    int32_t causal;
+    int32_t per; // query heads to a key/value head
+    void *out;
+    int64_t o_b, o_g, o_t; // element strides of the output over batch, head, query (hd is contiguous)
+    const void *rt;        // the divisor, a rank-0 tensor
+    int32_t rt_dtype;
+    uint32_t *status;
+};
+
+PSK_DEV float bf16_round(float x) { return bits_f32(pack_bf16x2_hw(x, 0.0f) << 16); }
+
+PSK_DEV float fast_exp2(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__global__ void __launch_bounds__(THREADS, 1) k_attn_fwd(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const __grid_constant__ Params P)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t *sQ = smem, *sK = smem + TILE, *sV = smem + 3 * TILE, *sP = smem + 5 * TILE;
+    uint64_t *bars = (uint64_t *)(smem + SMEM_TILES);
+    // 0 q_full; 1,2 k_full; 3,4 k_empty; 5,6 v_full; 7,8 v_empty; 9,10 s_full; 11,12 s_free; 13 p_full; 14 p_free; 15 o_full
+    uint32_t *tmem_slot = (uint32_t *)(bars + 16);
+    volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
+    const uint32_t bar0 = tc::smem_u32(bars);
+    auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nqb = (int)(P.T / BM);
+    const int qb = nqb - 1 - (int)blockIdx.x; // the longest rows first
+    const int g = blockIdx.y, b = blockIdx.z;
+    const int gk = g / P.per; // the key/value head this query head reads
+    const int nkb = P.causal ? qb + 1 : nqb;
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int i = 0; i < 16; ++i) {
+            uint32_t count = 1;
+            if (i == 11 || i == 12 || i == 13) count = 4; // s_free, p_full: one arrival a softmax warp
+            tc::mbar_init(bar(i), count);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc::smem_u32(tmem_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t tS0 = tmem, tO = tmem + 256;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            bool ok = true;
+            tc::mbar_expect_tx(bar(0), TILE);
+            tc::tma_load_4d(tc::smem_u32(sQ), &map_q, bar(0), 0, qb * BM, g, b);
+            tc::tma_load_4d(tc::smem_u32(sQ + HALF), &map_q, bar(0), 64, qb * BM, g, b);
+            uint32_t ks = 0, kph = 0, vs = 0, vph = 0;
+            for (int pass = 0; pass < 2 && ok; ++pass)
+                for (int kb = 0; kb < nkb && ok; ++kb) {
+                    ok = tc::mbar_wait(bar(3 + ks), kph ^ 1u, abort_flag, P.status, 0x11u);
+                    if (!ok) break;
+                    tc::mbar_expect_tx(bar(1 + ks), TILE);
+                    tc::tma_load_4d(tc::smem_u32(sK + ks * TILE), &map_k, bar(1 + ks), 0, kb * BN, gk, b);
+                    tc::tma_load_4d(tc::smem_u32(sK + ks * TILE + HALF), &map_k, bar(1 + ks), 64, kb * BN, gk, b);
+                    if (++ks == 2) { ks = 0; kph ^= 1u; }
+                    if (pass == 1) {
+                        ok = tc::mbar_wait(bar(7 + vs), vph ^ 1u, abort_flag, P.status, 0x12u);
+                        if (!ok) break;
+                        tc::mbar_expect_tx(bar(5 + vs), TILE);
+                        tc::tma_load_4d(tc::smem_u32(sV + vs * TILE), &map_v, bar(5 + vs), 0, kb * BN, gk, b);
+                        tc::tma_load_4d(tc::smem_u32(sV + vs * TILE + HALF), &map_v, bar(5 + vs), 64, kb * BN, gk, b);
+                        if (++vs == 2) { vs = 0; vph ^= 1u; }
+                    }
+                }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc_qk = tc::instr_desc(0, 0, BN), idesc_pv = tc::instr_desc(0, 1, HD);
+            bool ok = tc::mbar_wait(bar(0), 0u, abort_flag, P.status, 0x21u);
+            uint32_t ks = 0, kph = 0, vs = 0, vph = 0, qk_count = 0;
+            auto issue_qk = [&]() -> bool {
+                const uint32_t sb = qk_count & 1u, sph = (qk_count >> 1) & 1u;
+                if (!tc::mbar_wait(bar(1 + ks), kph, abort_flag, P.status, 0x22u)) return false;
+                if (!tc::mbar_wait(bar(11 + sb), sph ^ 1u, abort_flag, P.status, 0x23u)) return false;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t qa = tc::smem_u32(sQ), ka = tc::smem_u32(sK + ks * TILE);
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk) {
+                    const uint32_t off = (uint32_t)(kk >> 2) * HALF + (uint32_t)(kk & 3) * 32u;
+                    tc::umma(tS0 + sb * 128u, tc::smem_desc(qa + off, 16, 1024), tc::smem_desc(ka + off, 16, 1024), idesc_qk, kk != 0 ? 1u : 0u);
+                }
+                tc::umma_commit(bar(3 + ks));  // the K block is free once these have read it
+                tc::umma_commit(bar(9 + sb));  // S is there
+                if (++ks == 2) { ks = 0; kph ^= 1u; }
+                ++qk_count;
+                return true;
+            };
+            // pass 1: the scores only, for the rows' maxima
+            for (int kb = 0; kb < nkb && ok; ++kb) ok = issue_qk();
+            // pass 2: scores of block kb+1 are issued before the product of block kb waits for P
+            if (ok) ok = issue_qk();
+            for (int kb = 0; kb < nkb && ok; ++kb) {
+                if (kb + 1 < nkb) ok = issue_qk();
+                if (!ok) break;
+                ok = tc::mbar_wait(bar(13), (uint32_t)(kb & 1), abort_flag, P.status, 0x24u);
+                if (!ok) break;
+                ok = tc::mbar_wait(bar(5 + vs), vph, abort_flag, P.status, 0x25u);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t pa = tc::smem_u32(sP), va = tc::smem_u32(sV + vs * TILE);
+#pragma unroll
+                for (int kk = 0; kk < BN / 16; ++kk) {
+                    const uint32_t aoff = (uint32_t)(kk >> 2) * HALF + (uint32_t)(kk & 3) * 32u;
+                    tc::umma(tO, tc::smem_desc(pa + aoff, 16, 1024), tc::smem_desc(va + (uint32_t)kk * 2048u, HALF, 1024), idesc_pv, (kb | kk) != 0 ? 1u : 0u);
+                }
+                tc::umma_commit(bar(7 + vs)); // the V block is free
+                tc::umma_commit(bar(14));     // and P may be overwritten
+                if (++vs == 2) { vs = 0; vph ^= 1u; }
+            }
+            if (ok) tc::umma_commit(bar(15));
+        }
+    } else {
+        const int quad = warp & 3;
+        const int row = quad * 32 + lane;              // this thread's query within the block
+        const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+        const float rtv = load_real(P.rt, P.rt_dtype, 0);
+        const float rr = __frcp_rn(rtv);
+        bool ok = true;
+        uint32_t qk_count = 0;
+        // a block's scores as the two stored sites would hold them: bf16(bf16(S) / rt), refused ones -inf
+        auto scores32 = [&](const uint32_t (&v)[32], int kb, int c0, float (&s)[32]) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                float x = bf16_round(__uint_as_float(v[i]));
+                x = bf16_round(div_by(x, rtv, rr));
+                if (P.causal && kb == qb && c0 + i > row) x = -INFINITY;
+                s[i] = x;
+            }
+        };
+        float m = -INFINITY;
+        for (int kb = 0; kb < nkb && ok; ++kb) {
+            const uint32_t sb = qk_count & 1u, sph = (qk_count >> 1) & 1u;
+            ok = tc::mbar_wait(bar(9 + sb), sph, abort_flag, P.status, 0x31u);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t v[32];
+                tc::tmem_ld32(tS0 + lane_base + sb * 128u + (uint32_t)c0, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                float s[32];
+                scores32(v, kb, c0, s);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) m = fmaxf(m, s[i]);
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(bar(11 + sb));
+            ++qk_count;
+        }
+        float z = 0.0f;
+        const float LOG2E = 1.44269504f;
+        for (int kb = 0; kb < nkb && ok; ++kb) {
+            const uint32_t sb = qk_count & 1u, sph = (qk_count >> 1) & 1u;
+            ok = tc::mbar_wait(bar(9 + sb), sph, abort_flag, P.status, 0x32u);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            // P of the block before must have been read by its product
+            ok = tc::mbar_wait(bar(14), (uint32_t)(kb & 1) ^ 1u, abort_flag, P.status, 0x33u);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t v[32];
+                tc::tmem_ld32(tS0 + lane_base + sb * 128u + (uint32_t)c0, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                float s[32];
+                scores32(v, kb, c0, s);
+                uint32_t packed[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float e0 = s[2 * i] == -INFINITY ? 0.0f : fast_exp2(__fmul_rn(__fsub_rn(s[2 * i], m), LOG2E));
+                    const float e1 = s[2 * i + 1] == -INFINITY ? 0.0f : fast_exp2(__fmul_rn(__fsub_rn(s[2 * i + 1], m), LOG2E));
+                    z += e0;
+                    z += e1;
+                    packed[i] = pack_bf16x2_hw(e0, e1);
+                }
+                // keys c0 .. c0+31 of this row: half (c0 / 64), 16-byte units (c0 % 64) / 8 .. +3, swizzled by the row
+                uint8_t *dst = sP + (c0 >> 6) * HALF + row * 128;
+                const int u0 = (c0 & 63) >> 3;
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    *reinterpret_cast<uint4 *>(dst + (((u0 + u) ^ (row & 7)) << 4)) = make_uint4(packed[4 * u], packed[4 * u + 1], packed[4 * u + 2], packed[4 * u + 3]);
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // the tensor core reads P through the async proxy
+            __syncwarp();
+            if (lane == 0) {
+                tc::mbar_arrive(bar(11 + sb));
+                tc::mbar_arrive(bar(13));
+            }
+            ++qk_count;
+        }
+        if (ok) {
+            ok = tc::mbar_wait(bar(15), 0u, abort_flag, P.status, 0x34u);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int64_t t = (int64_t)qb * BM + row;
+            uint16_t *orow = (uint16_t *)P.out + (int64_t)b * P.o_b + (int64_t)g * P.o_g + t * P.o_t;
+#pragma unroll 1
+            for (int c0 = 0; c0 < HD; c0 += 32) {
+                uint32_t v[32];
+                tc::tmem_ld32(tO + lane_base + (uint32_t)c0, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        w[i] = pack_bf16x2_hw(__fdiv_rn(__uint_as_float(v[u * 8 + 2 * i]), z), __fdiv_rn(__uint_as_float(v[u * 8 + 2 * i + 1]), z));
+                    *reinterpret_cast<uint4 *>(orow + c0 + u * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+    }
+}
+
+} // namespace attn
+} // namespace psk

@@ -21,6 +21,7 @@
 #include "psk_gemm_tc.cuh"
 #include "psk_kernels.cuh"
 #include "psk_hot.cuh"
+#include "psk_attn.cuh"
 
 using namespace psk;
 
@@ -65,6 +66,7 @@ struct psk_exec {
     EncodeTiledFn encode = nullptr;
     bool tc_attr_set = false;
     bool softmax_attr_set = false;
+    bool attn_attr_set = false;
 };
 
 namespace {
@@ -632,7 +634,7 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
     L.fparam = (float)l->fparam[0];
     L.status = e->status;
     L.ovf = L.guarded ? next_flag(e, l) : e->flags;
-    if (l->op != PSK_OP_EMBED && l->op != PSK_OP_IOTA && l->op != PSK_OP_MAGNITUDE) coalesce_outer(L);
+    if (l->op != PSK_OP_EMBED && l->op != PSK_OP_IOTA && l->op != PSK_OP_MAGNITUDE && l->op != PSK_OP_ATTENTION) coalesce_outer(L);
     L.total = 1;
     for (int a = 0; a < L.n_outer; ++a) L.total *= L.dims[a];
     L.inner = 1;
@@ -879,6 +881,59 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
         } else {
             k_softmax_seq<<<grid_for(e, L.total, 128, 16), 128, 0, e->stream>>>(L);
         }
+        e->kernels += 1;
+        break;
+    }
+    case PSK_OP_ATTENTION: {
+        // (batch, heads, seq, hd | seq2) or (batch, groups, per, seq, hd | seq2); see psk_attn.cuh
+        e->last_kernel = "k_attn_fwd";
+        const std::string nm = l->name ? l->name : "attention";
+        if (!device_order) { rc = fail(e, PSK_E7005, nm + ": blockwise attention is a declared order; under the sequential order the four launches run one by one"); break; }
+        const int no = L.n_outer;
+        if ((no != 4 && no != 5) || L.n_inner != 1 || (L.n_in != 4 && L.n_in != 5)) { rc = fail(e, PSK_E7001, nm + ": q, k, v, the divisor and at most a mask over (batch, [groups,] heads, seq, hd | seq2)"); break; }
+        const int ax_hd = no - 1, ax_seq = no - 2, ax_s2 = no, ax_b = 0, ax_g = 1, ax_p = no == 5 ? 2 : -1;
+        const int64_t B = L.dims[ax_b], G = L.dims[ax_g], Pn = ax_p >= 0 ? L.dims[ax_p] : 1, T = L.dims[ax_seq], HD = L.dims[ax_hd];
+        bool fits = HD == attn::HD && T == L.dims[ax_s2] && T % attn::BM == 0 && l->dtype == PSK_BF16 && l->out.dtype == PSK_BF16
+            && l->iparam[1] == PSK_BF16 && l->iparam[2] == PSK_BF16 && l->iparam[3] == PSK_BF16;
+        for (int i = 0; i < 3 && fits; ++i) fits = l->in[i].dtype == PSK_BF16 && L.in[i].stride[ax_hd] == 1 && aligned16(L.in[i].p);
+        const DevOperand &Q = L.in[0], &K = L.in[1], &V = L.in[2], &O = L.out;
+        fits = fits && O.stride[ax_hd] == 1 && aligned16(O.p) && O.stride[ax_seq] % 8 == 0 && O.stride[ax_b] % 8 == 0 && O.stride[ax_g] % 8 == 0;
+        fits = fits && Q.stride[ax_s2] == 0 && K.stride[ax_seq] == 0 && V.stride[ax_seq] == 0 && O.stride[ax_s2] == 0;
+        int64_t q_head = Q.stride[ax_g], o_head = O.stride[ax_g];
+        if (ax_p >= 0) {
+            fits = fits && K.stride[ax_p] == 0 && V.stride[ax_p] == 0 && (Pn == 1 || (Q.stride[ax_g] == Q.stride[ax_p] * Pn && O.stride[ax_g] == O.stride[ax_p] * Pn));
+            if (Pn > 1) { q_head = Q.stride[ax_p]; o_head = O.stride[ax_p]; }
+        }
+        bool causal = false;
+        if (fits && L.n_in == 5) {
+            auto it = e->causal.find(table[4]);
+            causal = it != e->causal.end() && it->second == T && l->in[4].offset == 0 && L.in[4].stride[ax_s2] == 1 && L.in[4].stride[ax_seq] == T && L.in[4].stride[ax_hd] == 0;
+            for (int a = 0; a < ax_seq && causal; ++a) causal = L.in[4].stride[a] == 0;
+            fits = causal;
+        }
+        if (!fits) { rc = fail(e, PSK_E7005, nm + ": blockwise attention runs bf16 sites, hd = 128, a sequence that is a multiple of 128 and no mask or the causal one"); break; }
+        if (!e->encode) { rc = fail(e, PSK_E10001, "cuTensorMapEncodeTiled is not available from this driver"); break; }
+        CUtensorMap mq, mk, mv;
+        bool ok = make_map(e, &mq, Q.p, 0, (uint64_t)HD, (uint64_t)T, (uint64_t)(G * Pn), (uint64_t)B, (uint64_t)Q.stride[ax_seq], (uint64_t)q_head, (uint64_t)Q.stride[ax_b], 64, attn::BM)
+            && make_map(e, &mk, K.p, 0, (uint64_t)HD, (uint64_t)T, (uint64_t)G, (uint64_t)B, (uint64_t)K.stride[ax_s2], (uint64_t)K.stride[ax_g], (uint64_t)K.stride[ax_b], 64, attn::BN)
+            && make_map(e, &mv, V.p, 0, (uint64_t)HD, (uint64_t)T, (uint64_t)G, (uint64_t)B, (uint64_t)V.stride[ax_s2], (uint64_t)V.stride[ax_g], (uint64_t)V.stride[ax_b], 64, attn::BN);
+        if (!ok) { rc = fail(e, PSK_E7001, nm + ": an operand's strides do not make a tensor map"); break; }
+        attn::Params A;
+        memset(&A, 0, sizeof A);
+        A.T = T; A.causal = causal ? 1 : 0; A.per = (int32_t)Pn;
+        A.out = const_cast<void *>(O.p); A.o_b = O.stride[ax_b]; A.o_g = o_head; A.o_t = O.stride[ax_seq];
+        A.rt = L.in[3].p; A.rt_dtype = L.in[3].dtype;
+        A.status = e->status;
+        if (!e->attn_attr_set) {
+            CUDA_TRY(e, cudaFuncSetAttribute(attn::k_attn_fwd, cudaFuncAttributeMaxDynamicSharedMemorySize, attn::SMEM_TOTAL));
+            e->attn_attr_set = true;
+        }
+        const int64_t nqb = T / attn::BM;
+        if (G * Pn > 65535 || B > 65535) { rc = fail(e, PSK_E7001, nm + ": more heads or batch entries than a grid holds"); break; }
+        dim3 grid((unsigned)nqb, (unsigned)(G * Pn), (unsigned)B);
+        attn::k_attn_fwd<<<grid, attn::THREADS, attn::SMEM_TOTAL, e->stream>>>(mq, mk, mv, A);
+        const double blocks = causal ? (double)nqb * (double)(nqb + 1) / 2.0 : (double)nqb * (double)nqb;
+        e->last_flops = 4.0 * (double)B * (double)(G * Pn) * blocks * 128.0 * 128.0 * (double)HD;
         e->kernels += 1;
         break;
     }

@@ -155,6 +155,7 @@ struct Realization {
     std::map<std::string, AffineSpec> scaled;  // sites stored in an affine format (presk-rt/src/lib.rs:287-360)
     std::map<std::string, int> int_sums;        // sites whose `product` and `accum` are i32: 1 product, 2 accum, 3 both
     int order = PSK_ORDER_SEQUENTIAL;
+    bool blockwise_attention = false; // "order": {"kind": "device", "attention": "blockwise"}
 
     static Realization parse(const char *text)
     {
@@ -197,6 +198,14 @@ struct Realization {
             if (kind == "sequential" || kind == "blocked") r.order = PSK_ORDER_SEQUENTIAL;
             else if (kind == "device") r.order = PSK_ORDER_DEVICE;
             else raise(PSK_E7005, "realization: the order `" + kind + "` is not one this executor has kernels for (sequential, device)");
+            if (const Json *at = o->get("attention")) {
+                if (at->str == "blockwise") {
+                    if (r.order != PSK_ORDER_DEVICE) raise(PSK_E7005, "realization: `attention: blockwise` is part of the order `device`");
+                    r.blockwise_attention = true;
+                } else if (at->str != "unfused") {
+                    raise(PSK_E7005, "realization: the attention order `" + at->str + "` is not one this executor has (unfused, blockwise)");
+                }
+            }
         }
         if (auto *m = j.get("arith"))
             if (!m->obj.empty()) raise(PSK_E7005, "realization: `arith` formats are the kernel interpreter's; this executor computes in f32 (E7005)");
@@ -771,6 +780,48 @@ struct psk_host {
         return out;
     }
 
+    // The four launches of an attention function as one (PSK_OP_ATTENTION), under the declared order
+    // `attention: blockwise`: q [batch, groups, per, seq, hd], k [batch, groups, seq2, hd],
+    // v [batch, seq2, groups, hd], result [batch, seq, groups, per, hd] as the last ein would lay it out.
+    // `sites`: scores, scaled scores, softmax, result. While magnitudes are being measured the launches
+    // stay apart, since the three sites in between are never stored by the fused one.
+    Tensor attention_blockwise(const std::vector<std::string> &sites, const Tensor &q, const Tensor &k, const Tensor &v, const Tensor &rt, const Tensor *mask)
+    {
+        const int64_t B = q.axes[0].len, G = q.axes[1].len, P = q.axes[2].len, T = q.axes[3].len, HD = q.axes[4].len, T2 = k.axes[2].len;
+        int d_mid[3];
+        for (int i = 0; i < 3; ++i) {
+            d_mid[i] = site_dtype(sites[i]);
+            if (rz.scaled.count(sites[i])) raise(PSK_E7005, "attention: blockwise: the site " + sites[i] + " is stored in an affine format, which the fused launch never stores");
+        }
+        int d = site_dtype(sites[3]);
+        Axes out_axes = {{"batch", B}, {"seq", T}, {"groups", G}, {"per", P}, {"hd", HD}};
+        Tensor out = fresh_at(sites[3], out_axes);
+        psk_launch l;
+        memset(&l, 0, sizeof l);
+        l.op = PSK_OP_ATTENTION;
+        l.dtype = d;
+        l.masked = mask ? 1 : 0;
+        l.iparam[1] = d_mid[0]; l.iparam[2] = d_mid[1]; l.iparam[3] = d_mid[2];
+        Axes outer = {{"batch", B}, {"groups", G}, {"per", P}, {"seq", T}, {"hd", HD}};
+        set_space(l, outer, {T2});
+        std::vector<int64_t> st, ss;
+        view(q, {0, 1, 2, 3, 4}, 6, st, ss); set_operand(l.in[0], q, st, ss);
+        view(k, {0, 1, 5, 4}, 6, st, ss);    set_operand(l.in[1], k, st, ss);
+        view(v, {0, 5, 1, 4}, 6, st, ss);    set_operand(l.in[2], v, st, ss);
+        set_operand(l.in[3], rt, {}, {});
+        std::vector<const Tensor *> ins = {&q, &k, &v, &rt};
+        if (mask) {
+            if (mask->axes.size() != 2 || mask->axes[0].len != T || mask->axes[1].len != T2) raise(PSK_E7001, "attention: the mask " + show(mask->axes) + " is not over (seq, seq2)");
+            view(*mask, {3, 5}, 6, st, ss);
+            set_operand(l.in[4], *mask, st, ss);
+            ins.push_back(mask);
+        }
+        view(out, {0, 3, 1, 2, 4}, 6, st, ss);
+        set_operand(l.out, out, st, {});
+        run(l, "attention[blockwise]", ins, out);
+        return out;
+    }
+
     Tensor cross_entropy(const std::string &site, const Tensor &logits, const Tensor &y)
     {
         Axes outer = y.axes;
@@ -1117,12 +1168,19 @@ struct psk_host {
         Tensor vd = dot(f + "/%14", x, wv);
         vd.axes.back().name = "kvout";
         Tensor v = split(vd, "kvout", {{"groups", G}, {"hd", HD}});
-        Tensor se = ein(f + "/%16", {"batch", "groups", "per", "seq", "seq2"}, {{"batch", "groups", "per", "seq", "hd"}, {"batch", "groups", "seq2", "hd"}}, {&q, &k});
-        Tensor hdr = scalar(f + "/%18", (double)HD);
-        Tensor rt = unary(f + "/%19", PSK_SQRT, hdr);
-        Tensor s = binary(f + "/%20", PSK_DIV, se, rt);
-        Tensor a = softmax(f + "/%21", "seq2", s, &mask);
-        Tensor o = ein(f + "/%22", {"batch", "seq", "groups", "per", "hd"}, {{"batch", "groups", "per", "seq", "seq2"}, {"batch", "seq2", "groups", "hd"}}, {&a, &v});
+        Tensor o;
+        if (rz.blockwise_attention && !calibrating) {
+            Tensor hdr = scalar(f + "/%18", (double)HD);
+            Tensor rt = unary(f + "/%19", PSK_SQRT, hdr);
+            o = attention_blockwise({f + "/%16", f + "/%20", f + "/%21", f + "/%22"}, q, k, v, rt, &mask);
+        } else {
+            Tensor se = ein(f + "/%16", {"batch", "groups", "per", "seq", "seq2"}, {{"batch", "groups", "per", "seq", "hd"}, {"batch", "groups", "seq2", "hd"}}, {&q, &k});
+            Tensor hdr = scalar(f + "/%18", (double)HD);
+            Tensor rt = unary(f + "/%19", PSK_SQRT, hdr);
+            Tensor s = binary(f + "/%20", PSK_DIV, se, rt);
+            Tensor a = softmax(f + "/%21", "seq2", s, &mask);
+            o = ein(f + "/%22", {"batch", "seq", "groups", "per", "hd"}, {{"batch", "groups", "per", "seq", "seq2"}, {"batch", "seq2", "groups", "hd"}}, {&a, &v});
+        }
         Tensor w2 = split(split(wo, "headhd", {{"groups", G}, {"rest", P * HD}}), "rest", {{"per", P}, {"hd", HD}});
         return ein(f + "/%26", {"batch", "seq", "model"}, {{"batch", "seq", "groups", "per", "hd"}, {"groups", "per", "hd", "model"}}, {&o, &w2});
     }

@@ -206,3 +206,23 @@ def test_llama_int8_weights_on_tensor_cores(cuda, oracle):
     ho = models.give(Host(oracle.vtable(), dict(rz, order={"kind": "sequential"})).prepare("llama", **c), p)
     want = ho.call("apply", [ids], (2, 128, c["V"]))
     assert np.abs(got - want).max() <= 2.0**-6 * np.abs(want).max()
+
+
+@pytest.mark.parametrize("G", [4, 2])
+def test_llama_blockwise_attention_within_tolerance(cuda, oracle, G):
+    """hd = 128, T = 256: the fused attention kernel inside the whole model (GQA when G < H), against the
+    oracle's unfused sequential run."""
+    c = dict(V=512, D=512, H=4, G=G, FF=512, L=2)
+    p = models.llama_params(c)
+    rng = np.random.default_rng(6)
+    ids = rng.integers(0, c["V"], size=(2, 256), dtype=np.int64)
+    rz = {"default": "bf16", "order": {"kind": "device", "attention": "blockwise"}, "params": {k: "bf16" for k in p}, "storage": {"Llama.apply/%11": "f32"}}
+    rs = dict(rz, order={"kind": "sequential"})
+    h = models.give(Host(cuda, rz).prepare("llama", **c), p)
+    h.set_logging(True)
+    lg = h.call("apply", [ids], (2, 256, c["V"]))
+    assert h.launch_log().count("attention[blockwise]") == c["L"]
+    lw = models.give(Host(oracle.vtable(), rs).prepare("llama", **c), p).call("apply", [ids], (2, 256, c["V"]))
+    assert np.abs(lg - lw).max() <= 2.0**-6 * np.abs(lw).max()
+    want = models.llama_numpy(p, c, ids)
+    assert np.abs(lg - want).max() <= 0.05 * np.abs(want).max()

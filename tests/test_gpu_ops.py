@@ -286,3 +286,90 @@ def test_integer_sums_over_scaled_values_are_exact(cuda, oracle):
         for p in dev + [pout, psw]:
             cuda.free(p)
         assert np.array_equal(got, want), f"trial {trial}"
+
+
+def bf16_of(oracle, x):
+    return np.frombuffer(oracle.convert(np.ascontiguousarray(x, np.float32), abi.BF16).tobytes(), dtype=np.uint16).reshape(x.shape)
+
+
+def bf16_value(u16):
+    return (u16.astype(np.uint32) << 16).view(np.float32)
+
+
+@pytest.mark.parametrize("B,G,P,T,causal", [(2, 2, 2, 384, True), (1, 3, 1, 256, True), (1, 1, 2, 128, False), (1, 2, 1, 1024, True)])
+def test_blockwise_attention_against_its_four_launches(cuda, oracle, B, G, P, T, causal):
+    """PSK_OP_ATTENTION under the device order (one tcgen05 kernel, scores never stored) against the
+    oracle's four launches with bf16 sites. Tolerance: the result is a bf16 number of magnitude up to
+    max|v|; the fused kernel rounds the unnormalised exponentials where the four launches round the
+    normalised ones, so an element may differ by a couple of bf16 units (2^-8 relative each)."""
+    HD = 128
+    rng = np.random.default_rng(B * 1000 + T)
+    q = bf16_of(oracle, rng.standard_normal((B, G, P, T, HD)) * 1.5)
+    k = bf16_of(oracle, rng.standard_normal((B, G, T, HD)) * 1.5)
+    v = bf16_of(oracle, rng.standard_normal((B, T, G, HD)))
+    rt = bf16_of(oracle, np.array(np.sqrt(np.float32(HD)), np.float32).reshape(()))
+    l = launch_desc(abi.OP_ATTENTION, abi.BF16, [B, G, P, T, HD], [T], order=abi.ORDER_DEVICE, name=b"attention[blockwise]")
+    l.n_inputs = 5 if causal else 4
+    l.masked = 1 if causal else 0
+    l.iparam[1] = l.iparam[2] = l.iparam[3] = abi.BF16
+    set_operand(l.inputs[0], abi.BF16, [B, G, P, T, HD], [0, 1, 2, 3, 4])
+    set_operand(l.inputs[1], abi.BF16, [B, G, T, HD], [0, 1, 5, 4])
+    set_operand(l.inputs[2], abi.BF16, [B, T, G, HD], [0, 5, 1, 4])
+    set_operand(l.inputs[3], abi.BF16, [], [])
+    set_operand(l.out, abi.BF16, [B, T, G, P, HD], [0, 3, 1, 2, 4])
+    host_in = [q, k, v, rt]
+    dev = [cuda.upload(a) for a in host_in]
+    if causal:
+        set_operand(l.inputs[4], abi.I64, [T, T], [3, 5], is_index=True)
+        mask_dev = cuda.alloc(T * T * 8)
+        m = launch_desc(abi.OP_IOTA, abi.BF16, [T, T], name=b"causal_mask seq")
+        m.kind = abi.IOTA_CAUSAL
+        set_operand(m.out, abi.I64, [T, T], [0, 1], is_index=True)
+        cuda.run(m, [mask_dev])
+        dev.append(mask_dev)
+        host_in.append(np.tril(np.ones((T, T), np.int64)))
+    out_bytes = B * T * G * P * HD * 2
+    pout = cuda.alloc(out_bytes)
+    cuda.run(l, dev + [pout])
+    cuda.sync()
+    got = bf16_value(cuda.download(pout, out_bytes).view(np.uint16))
+    for p in dev + [pout]:
+        cuda.free(p)
+    want_b = np.zeros(out_bytes, np.uint8)
+    oracle.run(l, [np.ascontiguousarray(a) for a in host_in] + [want_b])
+    want = bf16_value(want_b.view(np.uint16))
+    assert np.isfinite(got).all()
+    err = np.abs(got - want)
+    assert err.max() <= 2.0**-6 * np.abs(want).max(), (err.max(), np.abs(want).max())
+    assert err.mean() <= 2.0**-8 * np.abs(want).mean()  # on average well within one bf16 unit of an element
+    # against the exact statement in f64 over the same bf16 inputs
+    qf, kf, vf = bf16_value(q).astype(np.float64), bf16_value(k).astype(np.float64), bf16_value(v).astype(np.float64)
+    s = np.einsum("bgpsh,bgth->bgpst", qf, kf) / np.sqrt(HD)
+    if causal:
+        s = np.where(np.tril(np.ones((T, T), bool)), s, -np.inf)
+    a = np.exp(s - s.max(-1, keepdims=True))
+    a /= a.sum(-1, keepdims=True)
+    exact = np.einsum("bgpst,btgh->bsgph", a, vf).reshape(-1)
+    assert np.abs(got - exact).max() <= 0.03 * np.abs(exact).max()
+
+
+def test_blockwise_attention_is_refused_where_it_does_not_apply(cuda):
+    """Under the sequential order, or with a head dimension other than 128, the launch is refused with
+    E7005 and nothing runs: the host then keeps the four launches apart."""
+    from presk_b200 import PreskError
+    B, G, P, T, HD = 1, 1, 1, 128, 64
+    for order, hd in ((abi.ORDER_SEQUENTIAL, 128), (abi.ORDER_DEVICE, 64)):
+        l = launch_desc(abi.OP_ATTENTION, abi.BF16, [B, G, P, T, hd], [T], order=order, name=b"attention[blockwise]")
+        l.n_inputs = 4
+        l.iparam[1] = l.iparam[2] = l.iparam[3] = abi.BF16
+        set_operand(l.inputs[0], abi.BF16, [B, G, P, T, hd], [0, 1, 2, 3, 4])
+        set_operand(l.inputs[1], abi.BF16, [B, G, T, hd], [0, 1, 5, 4])
+        set_operand(l.inputs[2], abi.BF16, [B, T, G, hd], [0, 5, 1, 4])
+        set_operand(l.inputs[3], abi.BF16, [], [])
+        set_operand(l.out, abi.BF16, [B, T, G, P, hd], [0, 3, 1, 2, 4])
+        bufs = [cuda.alloc(T * hd * 2) for _ in range(3)] + [cuda.alloc(16), cuda.alloc(T * hd * 2)]
+        with pytest.raises(PreskError) as e:
+            cuda.run(l, bufs)
+        assert e.value.code == 7005
+        for p in bufs:
+            cuda.free(p)

@@ -160,3 +160,24 @@ def test_calibrate_envelope(oracle):
     # a second call folds into the same envelope
     h.call("apply", [(ids + 1) % c["V"]], (2, 16, c["V"]))
     assert h.envelope()["Llama.apply/%11"][0] >= mx
+
+
+def test_blockwise_attention_is_its_four_launches_on_the_oracle(oracle):
+    """`order: {kind: device, attention: blockwise}` makes one launch of scores, division, softmax and
+    weighted values; its value is defined as that of the four, so over the oracle the bits agree."""
+    c = models.LLAMA_TINY
+    p = models.llama_params(c)
+    ids = np.random.default_rng(8).integers(0, c["V"], size=(2, 16), dtype=np.int64)
+    outs, logs = [], []
+    for order in ({"kind": "device"}, {"kind": "device", "attention": "blockwise"}):
+        h = models.give(Host(oracle.vtable(), {"default": "bf16", "order": order}).prepare("llama", **c), p)
+        h.set_logging(True)
+        outs.append(h.call("apply", [ids], (2, 16, c["V"])))
+        logs.append(h.launch_log())
+    assert np.array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32))
+    assert logs[1].count("attention[blockwise]") == c["L"]
+    assert "softmax axis seq2 where" in logs[0] and "softmax axis seq2 where" not in logs[1]
+    assert len(logs[0]) - len(logs[1]) == 3 * c["L"]
+    with pytest.raises(PreskError) as e:
+        Host(oracle.vtable(), {"default": "bf16", "order": {"kind": "sequential", "attention": "blockwise"}})
+    assert e.value.code == 7005
