@@ -19,12 +19,17 @@
 // The result agrees with the unfused sequence to about a bf16 unit in the last
 // place of the output (tests state the tolerance).
 //
-// One CTA per (batch, head, block of 128 queries), 192 threads: warp 0 loads Q
+// One CTA per (batch, head, block of 128 queries), 576 threads: warp 0 loads Q
 // once and K, V blocks through rings with TMA; warp 1 issues tcgen05.mma for
-// S = Q·K^T (into one of two 128-column accumulators) and O += P·V; warps 2-5
-// hold one query row a thread (its TMEM lane), so a row's maximum and sum need
-// no exchange between threads. Head dimension 128, bf16 in and out, sequence a
-// multiple of 128. Every wait is bounded as in psk_gemm_tc.cuh.
+// S = Q·K^T (into one of two 128-column accumulators) and O += P·V; warps 2-17
+// do the softmax, four warps to a quadrant of tensor memory: a thread holds one
+// query row (its TMEM lane) and 32 of a block's 128 keys, so a row's maximum
+// and sum are exchanged between four threads once a pass, through shared
+// memory. P is double-buffered, so the exponentials of block i+1 are computed
+// while the tensor core multiplies block i. Head dimension 128, bf16 in and
+// out, sequence a multiple of 128. Every wait on an mbarrier is bounded as in
+// psk_gemm_tc.cuh; the two named barriers among the softmax warps are reached
+// by every one of them whether or not a wait has run out.
 #pragma once
 #include "psk_gemm_tc.cuh"
 #include "psk_hot.cuh"
@@ -33,10 +38,11 @@ namespace psk {
 namespace attn {
 
 constexpr int BM = 128, BN = 128, HD = 128;
-constexpr int THREADS = 192;
+constexpr int SOFTMAX_WARPS = 16;     // four to a quadrant of tensor memory, each 32 of a block's 128 keys
+constexpr int THREADS = (2 + SOFTMAX_WARPS) * 32;
 constexpr int TILE = 128 * 128 * 2;   // a 128 x 128 bf16 tile: two 16 KB halves of 64 columns
 constexpr int HALF = 128 * 64 * 2;
-constexpr int SMEM_TILES = 6 * TILE;  // Q, K x2, V x2, P
+constexpr int SMEM_TILES = 7 * TILE;  // Q, K x2, V x2, P x2
 constexpr int SMEM_TOTAL = SMEM_TILES + 256 + 1024;
 
 struct Params {
@@ -59,14 +65,20 @@ PSK_DEV float fast_exp2(float x)
     return y;
 }
 
+PSK_DEV void softmax_sync()
+{
+    asm volatile("bar.sync 1, %0;" ::"n"(SOFTMAX_WARPS * 32) : "memory");
+}
+
 __global__ void __launch_bounds__(THREADS, 1) k_attn_fwd(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const __grid_constant__ Params P)
 {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t *sQ = smem, *sK = smem + TILE, *sV = smem + 3 * TILE, *sP = smem + 5 * TILE;
     uint64_t *bars = (uint64_t *)(smem + SMEM_TILES);
-    // 0 q_full; 1,2 k_full; 3,4 k_empty; 5,6 v_full; 7,8 v_empty; 9,10 s_full; 11,12 s_free; 13 p_full; 14 p_free; 15 o_full
-    uint32_t *tmem_slot = (uint32_t *)(bars + 16);
+    // 0 q_full; 1,2 k_full; 3,4 k_empty; 5,6 v_full; 7,8 v_empty; 9,10 s_full; 11,12 s_free;
+    // 13,14 p_full; 15,16 p_free; 17 o_full
+    uint32_t *tmem_slot = (uint32_t *)(bars + 18);
     volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
     const uint32_t bar0 = tc::smem_u32(bars);
     auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
@@ -80,9 +92,9 @@ __global__ void __launch_bounds__(THREADS, 1) k_attn_fwd(const __grid_constant__
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
-        for (int i = 0; i < 16; ++i) {
+        for (int i = 0; i < 18; ++i) {
             uint32_t count = 1;
-            if (i == 11 || i == 12 || i == 13) count = 4; // s_free, p_full: one arrival a softmax warp
+            if (i >= 11 && i <= 14) count = SOFTMAX_WARPS; // s_free, p_full: one arrival a softmax warp
             tc::mbar_init(bar(i), count);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -151,128 +163,142 @@ __global__ void __launch_bounds__(THREADS, 1) k_attn_fwd(const __grid_constant__
             for (int kb = 0; kb < nkb && ok; ++kb) {
                 if (kb + 1 < nkb) ok = issue_qk();
                 if (!ok) break;
-                ok = tc::mbar_wait(bar(13), (uint32_t)(kb & 1), abort_flag, P.status, 0x24u);
+                const uint32_t pb = (uint32_t)kb & 1u, pph = ((uint32_t)kb >> 1) & 1u;
+                ok = tc::mbar_wait(bar(13 + pb), pph, abort_flag, P.status, 0x24u);
                 if (!ok) break;
                 ok = tc::mbar_wait(bar(5 + vs), vph, abort_flag, P.status, 0x25u);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t pa = tc::smem_u32(sP), va = tc::smem_u32(sV + vs * TILE);
+                const uint32_t pa = tc::smem_u32(sP + pb * TILE), va = tc::smem_u32(sV + vs * TILE);
 #pragma unroll
                 for (int kk = 0; kk < BN / 16; ++kk) {
                     const uint32_t aoff = (uint32_t)(kk >> 2) * HALF + (uint32_t)(kk & 3) * 32u;
                     tc::umma(tO, tc::smem_desc(pa + aoff, 16, 1024), tc::smem_desc(va + (uint32_t)kk * 2048u, HALF, 1024), idesc_pv, (kb | kk) != 0 ? 1u : 0u);
                 }
-                tc::umma_commit(bar(7 + vs)); // the V block is free
-                tc::umma_commit(bar(14));     // and P may be overwritten
+                tc::umma_commit(bar(7 + vs));  // the V block is free
+                tc::umma_commit(bar(15 + pb)); // and this P may be overwritten
                 if (++vs == 2) { vs = 0; vph ^= 1u; }
             }
-            if (ok) tc::umma_commit(bar(15));
+            if (ok) tc::umma_commit(bar(17));
         }
     } else {
-        const int quad = warp & 3;
-        const int row = quad * 32 + lane;              // this thread's query within the block
+        const int quad = warp & 3;            // the tensor-memory lanes this warp may read: 32·quad ..
+        const int cq = (warp - 2) >> 2;       // its quarter of a block's keys, and of the output's columns
+        const int row = quad * 32 + lane;     // this thread's query within the block
         const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
         const float rtv = load_real(P.rt, P.rt_dtype, 0);
         const float rr = __frcp_rn(rtv);
+        float *xch = reinterpret_cast<float *>(sP); // the P tiles are idle whenever the warps exchange a row's parts
         bool ok = true;
         uint32_t qk_count = 0;
-        // a block's scores as the two stored sites would hold them: bf16(bf16(S) / rt), refused ones -inf
-        auto scores32 = [&](const uint32_t (&v)[32], int kb, int c0, float (&s)[32]) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                float x = bf16_round(__uint_as_float(v[i]));
-                x = bf16_round(div_by(x, rtv, rr));
-                if (P.causal && kb == qb && c0 + i > row) x = -INFINITY;
-                s[i] = x;
-            }
-        };
-        float m = -INFINITY;
+        // ---- pass 1: the greatest and the least raw score of the row ------------------
+        // bf16(bf16(S) / rt) is monotone in S, so the row's maximum of the stored scaled scores is that
+        // function of the greatest raw score (of the least, if rt is negative).
+        float mx = -INFINITY, mn = INFINITY;
         for (int kb = 0; kb < nkb && ok; ++kb) {
             const uint32_t sb = qk_count & 1u, sph = (qk_count >> 1) & 1u;
             ok = tc::mbar_wait(bar(9 + sb), sph, abort_flag, P.status, 0x31u);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                uint32_t v[32];
-                tc::tmem_ld32(tS0 + lane_base + sb * 128u + (uint32_t)c0, v);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                float s[32];
-                scores32(v, kb, c0, s);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) m = fmaxf(m, s[i]);
-            }
+            uint32_t v[32];
+            tc::tmem_ld32(tS0 + lane_base + sb * 128u + (uint32_t)(cq * 32), v);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
-            if (lane == 0) tc::mbar_arrive(bar(11 + sb));
+            if (lane == 0) tc::mbar_arrive(bar(11 + sb)); // the scores are in registers
             ++qk_count;
+            if (P.causal && kb == qb) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    if (cq * 32 + i <= row) { mx = fmaxf(mx, __uint_as_float(v[i])); mn = fminf(mn, __uint_as_float(v[i])); }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) { mx = fmaxf(mx, __uint_as_float(v[i])); mn = fminf(mn, __uint_as_float(v[i])); }
+            }
         }
-        float z = 0.0f;
+        xch[cq * 128 + row] = mx;
+        xch[512 + cq * 128 + row] = mn;
+        softmax_sync();
+#pragma unroll
+        for (int c = 0; c < 4; ++c) { mx = fmaxf(mx, xch[c * 128 + row]); mn = fminf(mn, xch[512 + c * 128 + row]); }
+        softmax_sync(); // before the first P is written over the exchange
+        const float m = bf16_round(__fdiv_rn(bf16_round(rtv < 0.0f ? mn : mx), rtv));
+        // ---- pass 2: exponentials, the row's sum, P for the second product --------------
         const float LOG2E = 1.44269504f;
+        const float m2 = __fmul_rn(m, LOG2E);
+        float z = 0.0f;
         for (int kb = 0; kb < nkb && ok; ++kb) {
             const uint32_t sb = qk_count & 1u, sph = (qk_count >> 1) & 1u;
             ok = tc::mbar_wait(bar(9 + sb), sph, abort_flag, P.status, 0x32u);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            // P of the block before must have been read by its product
-            ok = tc::mbar_wait(bar(14), (uint32_t)(kb & 1) ^ 1u, abort_flag, P.status, 0x33u);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint32_t v[32];
+            tc::tmem_ld32(tS0 + lane_base + sb * 128u + (uint32_t)(cq * 32), v);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(bar(11 + sb));
+            ++qk_count;
+            const bool diag = P.causal && kb == qb;
+            uint32_t packed[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                // the two stored sites: bf16(S), then bf16(bf16(S) / rt); the quotient by the correctly
+                // rounded reciprocal and one correction (the division's own result for a normal numerator)
+                const uint32_t s1 = pack_bf16x2_hw(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+                const float a0 = bits_f32(s1 << 16), a1 = bits_f32(s1 & 0xffff0000u);
+                const float q0 = __fmul_rn(a0, rr), q1 = __fmul_rn(a1, rr);
+                const float d0 = __fmaf_rn(__fmaf_rn(-rtv, q0, a0), rr, q0), d1 = __fmaf_rn(__fmaf_rn(-rtv, q1, a1), rr, q1);
+                const uint32_t s2 = pack_bf16x2_hw(d0, d1);
+                float e0 = fast_exp2(__fmaf_rn(bits_f32(s2 << 16), LOG2E, -m2));
+                float e1 = fast_exp2(__fmaf_rn(bits_f32(s2 & 0xffff0000u), LOG2E, -m2));
+                if (diag) {
+                    if (cq * 32 + 2 * i > row) e0 = 0.0f;
+                    if (cq * 32 + 2 * i + 1 > row) e1 = 0.0f;
+                }
+                z += e0;
+                z += e1;
+                packed[i] = pack_bf16x2_hw(e0, e1);
+            }
+            // P of two blocks before must have been read by its product
+            const uint32_t pb = (uint32_t)kb & 1u, pph = ((uint32_t)kb >> 1) & 1u;
+            ok = tc::mbar_wait(bar(15 + pb), pph ^ 1u, abort_flag, P.status, 0x33u);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                uint32_t v[32];
-                tc::tmem_ld32(tS0 + lane_base + sb * 128u + (uint32_t)c0, v);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                float s[32];
-                scores32(v, kb, c0, s);
-                uint32_t packed[16];
+            // keys cq*32 .. +31 of this row: half (cq / 2), 16-byte units (cq % 2) * 4 .. +3, swizzled by the row
+            uint8_t *dst = sP + pb * TILE + (cq >> 1) * HALF + row * 128;
+            const int u0 = (cq & 1) * 4;
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const float e0 = s[2 * i] == -INFINITY ? 0.0f : fast_exp2(__fmul_rn(__fsub_rn(s[2 * i], m), LOG2E));
-                    const float e1 = s[2 * i + 1] == -INFINITY ? 0.0f : fast_exp2(__fmul_rn(__fsub_rn(s[2 * i + 1], m), LOG2E));
-                    z += e0;
-                    z += e1;
-                    packed[i] = pack_bf16x2_hw(e0, e1);
-                }
-                // keys c0 .. c0+31 of this row: half (c0 / 64), 16-byte units (c0 % 64) / 8 .. +3, swizzled by the row
-                uint8_t *dst = sP + (c0 >> 6) * HALF + row * 128;
-                const int u0 = (c0 & 63) >> 3;
-#pragma unroll
-                for (int u = 0; u < 4; ++u)
-                    *reinterpret_cast<uint4 *>(dst + (((u0 + u) ^ (row & 7)) << 4)) = make_uint4(packed[4 * u], packed[4 * u + 1], packed[4 * u + 2], packed[4 * u + 3]);
-            }
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            for (int u = 0; u < 4; ++u)
+                *reinterpret_cast<uint4 *>(dst + (((u0 + u) ^ (row & 7)) << 4)) = make_uint4(packed[4 * u], packed[4 * u + 1], packed[4 * u + 2], packed[4 * u + 3]);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // the tensor core reads P through the async proxy
             __syncwarp();
-            if (lane == 0) {
-                tc::mbar_arrive(bar(11 + sb));
-                tc::mbar_arrive(bar(13));
-            }
-            ++qk_count;
+            if (lane == 0) tc::mbar_arrive(bar(13 + pb));
         }
         if (ok) {
-            ok = tc::mbar_wait(bar(15), 0u, abort_flag, P.status, 0x34u);
+            ok = tc::mbar_wait(bar(17), 0u, abort_flag, P.status, 0x34u); // every product is done: P is idle again
             ok = __all_sync(0xffffffffu, ok);
         }
+        xch[cq * 128 + row] = z;
+        softmax_sync();
+        z = __fadd_rn(__fadd_rn(xch[row], xch[128 + row]), __fadd_rn(xch[256 + row], xch[384 + row]));
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int64_t t = (int64_t)qb * BM + row;
-            uint16_t *orow = (uint16_t *)P.out + (int64_t)b * P.o_b + (int64_t)g * P.o_g + t * P.o_t;
-#pragma unroll 1
-            for (int c0 = 0; c0 < HD; c0 += 32) {
-                uint32_t v[32];
-                tc::tmem_ld32(tO + lane_base + (uint32_t)c0, v);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            uint16_t *orow = (uint16_t *)P.out + (int64_t)b * P.o_b + (int64_t)g * P.o_g + t * P.o_t + cq * 32;
+            uint32_t v[32];
+            tc::tmem_ld32(tO + lane_base + (uint32_t)(cq * 32), v);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            const float rz = __frcp_rn(z);
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    uint32_t w[4];
+            for (int u = 0; u < 4; ++u) {
+                uint32_t w[4];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i)
-                        w[i] = pack_bf16x2_hw(__fdiv_rn(__uint_as_float(v[u * 8 + 2 * i]), z), __fdiv_rn(__uint_as_float(v[u * 8 + 2 * i + 1]), z));
-                    *reinterpret_cast<uint4 *>(orow + c0 + u * 8) = make_uint4(w[0], w[1], w[2], w[3]);
-                }
+                for (int i = 0; i < 4; ++i)
+                    w[i] = pack_bf16x2_hw(div_by(__uint_as_float(v[u * 8 + 2 * i]), z, rz), div_by(__uint_as_float(v[u * 8 + 2 * i + 1]), z, rz));
+                *reinterpret_cast<uint4 *>(orow + u * 8) = make_uint4(w[0], w[1], w[2], w[3]);
             }
         }
     }
