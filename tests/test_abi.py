@@ -52,3 +52,19 @@ def test_product_does_not_reach_into_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".cpp", ".h")):
                 text = open(os.path.join(d, f), errors="ignore").read()
                 assert "oracle/" not in text.replace("the CPU oracle's, loaded from oracle/", "") and "psk_oracle" not in text, f
+
+
+def test_the_target_description_is_in_the_reference_schema():
+    """presk_b200/targets/b200.json must parse under the reference's `Target` (deny_unknown_fields:
+    presk-precision/src/target.rs): only its keys, an order of its vocabulary, modes of two operands."""
+    import json
+    import pathlib
+
+    t = json.loads((pathlib.Path(__file__).resolve().parents[1] / "presk_b200" / "targets" / "b200.json").read_text())
+    assert set(t) <= {"name", "about", "storage", "scaled", "params", "quant", "arith", "contractions", "order"}
+    assert {"name", "storage", "arith"} <= set(t)
+    assert t["order"]["kind"] in ("sequential", "blocked", "interleaved", "chunked")
+    for m in t["contractions"]:
+        assert set(m) <= {"name", "operands", "product", "accum"} and len(m["operands"]) == 2
+    for s in t["scaled"]:
+        assert set(s) == {"int", "scheme"} and s["scheme"] in ("absmax", "pow2", "minmax")
