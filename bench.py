@@ -47,13 +47,13 @@ WORKLOADS = {
 QUANTISED = ("blocks.attn.wq", "blocks.attn.wk", "blocks.attn.wv", "blocks.attn.wo", "blocks.ff.gate.w", "blocks.ff.up.w", "blocks.ff.down.w")
 
 
-def realization(paths, int8=False, attention="unfused"):
+def realization(paths, int8=False, attention="unfused", launches="reference"):
     """A solved-style mixed bf16/f32 assignment: bf16 storage, f32 where a sum's result is reused
     widely (the norms' mean and root, the logits and the loss); with `int8`, the projection and
     FFN weights as integers with one scale a channel (`quant`, over the contracted axis)."""
     rz = {
         "default": "bf16",
-        "order": {"kind": "device", "attention": attention},
+        "order": {"kind": "device", "attention": attention, "launches": launches},
         "params": {p: "bf16" for p in paths if not (int8 and p in QUANTISED)},
         "storage": {"RMSNorm.apply/%3": "f32", "RMSNorm.apply/%7": "f32", "Llama.apply/%11": "f32", "loss/%5": "f32", "loss/%6": "f32"},
     }
@@ -259,6 +259,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="llama7b_prefill_b8_t2048", choices=sorted(WORKLOADS))
     ap.add_argument("--attention", default="blockwise", choices=["blockwise", "unfused"], help="the declared order of the attention launches: one blockwise kernel, or the reference's four launches")
+    ap.add_argument("--launches", default="merged", choices=["merged", "reference"], help="merged: bit-preserving rewrites of the launch list (views for slices, in-place concatenation, wider groups); reference: the reference's launch list")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--dump-profile", default=None, help="write the per-launch-name times of the timed steps to this file")
     args = ap.parse_args()
@@ -268,7 +269,7 @@ def main():
     consts, B, T = w["consts"], w["B"], w["T"]
     rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
     threads = os.cpu_count() or 1
-    config = {"workload": args.workload, **{k: v for k, v in consts.items()}, "batch_per_gpu": B, "seq_len": T, "global_batch": B * world, "parallelism": f"dp{world}", "realization": "bf16 storage, f32 norm statistics/logits/loss, order device, attention " + args.attention, "l2": "inputs_larger_than_l2 (13.5 GB of weights stream through every step)"}
+    config = {"workload": args.workload, **{k: v for k, v in consts.items()}, "batch_per_gpu": B, "seq_len": T, "global_batch": B * world, "parallelism": f"dp{world}", "realization": "bf16 storage, f32 norm statistics/logits/loss, order device, attention " + args.attention + ", launches " + args.launches, "l2": "inputs_larger_than_l2 (13.5 GB of weights stream through every step)"}
 
     if args.impl == "reference":
         if rank != 0:
@@ -297,7 +298,7 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     ex = Executor(local)
     shapes = param_shapes(consts)
-    host = Host(ex, realization(shapes, w.get("int8", False), args.attention)).prepare("llama", **consts)
+    host = Host(ex, realization(shapes, w.get("int8", False), args.attention, args.launches)).prepare("llama", **consts)
     for i, (path, (shape, std)) in enumerate(shapes.items()):
         host.init_param(path, 1000 + i, std, shape)
     ex.sync()

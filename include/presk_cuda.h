@@ -101,7 +101,10 @@ typedef enum {
     PSK_NEG, PSK_EXP, PSK_LOG, PSK_TANH, PSK_SQRT, PSK_SIN, PSK_COS, PSK_ABS,
     PSK_GELU, PSK_GELU_DERIV, PSK_RELU, PSK_HEAVISIDE, PSK_SIGN, PSK_SIGMOID,
     PSK_POW, /* by repeated multiplication, exponent in `imm` */
-    PSK_REAL /* identity on a real; an index read as a real */
+    PSK_REAL, /* identity on a real; an index read as a real */
+    PSK_ROUND /* the value as a store into the type `imm` (a psk_dtype without a guard: f32, bf16) and a load back
+                 would leave it. No primitive of the reference: it stands where two of its groups, each with its
+                 result stored in its site's type, run as one launch (realization `launches: merged`). */
 } psk_prim;
 
 /* One step of a group (presk-core/src/fusion.rs:19-59): an operation on one or

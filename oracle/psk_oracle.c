@@ -420,6 +420,8 @@ static float prim_unary(int prim, float x, int imm)
         for (int i = 1; i < imm; ++i) e = e * x;
         return e;
     }
+    case PSK_ROUND: /* a site inside a merged group: rounded as its own launch would have stored it */
+        return imm == PSK_BF16 ? psk_o_bf16_to_f32(psk_o_f32_to_bf16(x)) : imm == PSK_F16 ? psk_o_f16_to_f32(psk_o_f32_to_f16(x)) : imm == PSK_E8M15 ? psk_o_e8m15_to_f32(psk_o_f32_to_e8m15(x)) : x;
     default: return x;
     }
 }

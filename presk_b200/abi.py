@@ -24,7 +24,7 @@ OK, E7001, E7005, E7006, E7007, E10001 = 0, 7001, 7005, 7006, 7007, 10001
 OP_FUSED, OP_CONTRACT, OP_REDUCE, OP_SOFTMAX, OP_XENT, OP_ARGMAX, OP_EMBED, OP_COPY, OP_IOTA, OP_CONVERT, OP_MAGNITUDE, OP_ATTENTION = range(12)
 
 # psk_prim
-(ADD, SUB, MUL, DIV, MAX, MIN, NEG, EXP, LOG, TANH, SQRT, SIN, COS, ABS, GELU, GELU_DERIV, RELU, HEAVISIDE, SIGN, SIGMOID, POW, REAL) = range(22)
+(ADD, SUB, MUL, DIV, MAX, MIN, NEG, EXP, LOG, TANH, SQRT, SIN, COS, ABS, GELU, GELU_DERIV, RELU, HEAVISIDE, SIGN, SIGMOID, POW, REAL, ROUND) = range(23)
 
 ORDER_SEQUENTIAL, ORDER_DEVICE = 0, 1
 REDUCE_SUM, REDUCE_MEAN, REDUCE_SUMSQ = 0, 1, 2

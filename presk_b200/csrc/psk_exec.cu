@@ -67,6 +67,7 @@ struct psk_exec {
     bool tc_attr_set = false;
     bool softmax_attr_set = false;
     bool attn_attr_set = false;
+    uint16_t *silu_table = nullptr; // silu of every bf16 code, computed once by the device's own exact function
 };
 
 namespace {
@@ -177,6 +178,7 @@ int match_program(const psk_launch *l)
     }
     if (l->n_steps == 2 && l->n_inputs == 3 && is(0, PSK_DIV, 2, 0, 1) && is(1, PSK_MUL, 2, -1, 2)) return EW_DIV_MUL;
     if (l->n_steps == 2 && l->n_inputs == 1 && is(0, PSK_SIGMOID, 1, 0, 0) && is(1, PSK_MUL, 2, 0, -1)) return EW_SILU;
+    if (l->n_steps == 4 && l->n_inputs == 2 && is(0, PSK_SIGMOID, 1, 0, 0) && is(1, PSK_MUL, 2, 0, -1) && is(2, PSK_ROUND, 1, -2, 0) && l->steps[2].imm == PSK_BF16 && is(3, PSK_MUL, 2, -3, 1)) return EW_SILU_MUL;
     if (l->n_steps == 3 && l->n_inputs == 4 && is(0, PSK_MUL, 2, 0, 1) && is(1, PSK_MUL, 2, 2, 3)) {
         if (is(2, PSK_SUB, 2, -1, -2)) return EW_MUL_MUL_SUB;
         if (is(2, PSK_ADD, 2, -1, -2)) return EW_MUL_MUL_ADD;
@@ -426,6 +428,7 @@ void psk_exec_destroy(psk_exec *e)
     cudaStreamSynchronize(e->stream);
     for (auto &kv : e->sizes) cudaFree(kv.first);
     for (auto &kv : e->widened) cudaFree(kv.second);
+    if (e->silu_table) cudaFree(e->silu_table);
     cudaFree(e->flags);
     cudaFree(e->status);
     cudaEventDestroy(e->ev0);
@@ -664,19 +667,30 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
         if (l->n_steps < 1 || l->n_steps > PSK_MAX_STEPS) { rc = fail(e, PSK_E7001, "fused: a group of no step or of too many"); break; }
         bool vec = !any_affine && L.n_outer >= 1 && l->n_steps <= 8 && L.dims[L.n_outer - 1] % 8 == 0 && vec8_operand(L.out, L.dims, L.n_outer, true);
         for (int i = 0; vec && i < L.n_in; ++i) vec = vec8_operand(L.in[i], L.dims, L.n_outer, false);
-        bool hot = vec && L.n_outer <= 2 && L.n_in <= 4 && l->n_steps <= 4 && L.total / 8 < 0xffffffffll;
+        bool hot = vec && L.n_outer <= 3 && L.n_in <= 4 && l->n_steps <= 4 && L.total / 8 < 0xffffffffll;
         for (int i = 0; hot && i < L.n_in; ++i) hot = L.in[i].dtype != PSK_I8;
+        // three levels (rows in two, e.g. a view of every other run of a row) are taken by the compile-time
+        // programs only
+        const bool three = L.n_outer == 3;
+        if (hot && three) {
+            hot = L.out.dtype == PSK_BF16 && L.kdtype == PSK_BF16 && match_program(l) >= 0;
+            for (int i = 0; hot && i < L.n_in; ++i)
+                hot = L.in[i].dtype == PSK_BF16 || (L.in[i].stride[2] == 0 && (L.in[i].dtype == PSK_F32 || L.in[i].dtype == PSK_F16 || L.in[i].dtype == PSK_E8M15));
+        }
         if (hot) {
             EwParams E;
             memset(&E, 0, sizeof E);
             const int last = L.n_outer - 1;
             for (int i = 0; i < L.n_in; ++i) {
                 E.in[i] = L.in[i].p; E.dt[i] = L.in[i].dtype; E.cs[i] = (int32_t)L.in[i].stride[last];
-                E.rs[i] = L.n_outer == 2 ? L.in[i].stride[0] : 0;
+                E.rs[i] = L.n_outer >= 2 ? L.in[i].stride[last - 1] : 0;
+                E.rs0[i] = three ? L.in[i].stride[0] : 0;
             }
             E.out = const_cast<void *>(L.out.p); E.odt = L.out.dtype; E.kdt = L.kdtype;
-            E.ors = L.n_outer == 2 ? L.out.stride[0] : 0;
-            E.rows = L.n_outer == 2 ? (uint32_t)L.dims[0] : 1u;
+            E.ors = L.n_outer >= 2 ? L.out.stride[last - 1] : 0;
+            E.ors0 = three ? L.out.stride[0] : 0;
+            E.rows = L.n_outer == 2 ? (uint32_t)L.dims[0] : three ? (uint32_t)(L.dims[0] * L.dims[1]) : 1u;
+            E.rows1 = three ? (uint32_t)L.dims[1] : 0u;
             E.colv = (uint32_t)(L.dims[last] / 8);
             E.n_in = L.n_in; E.guarded = L.guarded; E.ovf = L.ovf; E.status = L.status;
             for (int k = 0; k < l->n_steps; ++k) E.steps[k] = l->steps[k];
@@ -688,7 +702,17 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
             for (int i = 0; i < L.n_in; ++i)
                 prog_ok = prog_ok && (L.in[i].dtype == PSK_BF16 || (E.cs[i] == 0 && (L.in[i].dtype == PSK_F32 || L.in[i].dtype == PSK_F16 || L.in[i].dtype == PSK_E8M15)));
             const int prog = prog_ok ? match_program(l) : -1;
-            if (prog >= 0) {
+            const bool lut = (prog == EW_SILU || prog == EW_SILU_MUL) && all_bf16 && !three && E.cs[0] == 1 && (prog == EW_SILU || E.cs[1] == 1) && work >= (int64_t)e->sms * 4096;
+            if (lut) {
+                if (!e->silu_table) {
+                    CUDA_TRY(e, cudaMalloc(&e->silu_table, 65536 * sizeof(uint16_t)));
+                    k_table_silu<<<64, 1024, 0, e->stream>>>(e->silu_table);
+                    CUDA_TRY(e, cudaFuncSetAttribute(k_ew_lut<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536 * 2));
+                    CUDA_TRY(e, cudaFuncSetAttribute(k_ew_lut<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536 * 2));
+                }
+                if (prog == EW_SILU) k_ew_lut<false><<<e->sms, 1024, 65536 * 2, e->stream>>>(E, e->silu_table);
+                else k_ew_lut<true><<<e->sms, 1024, 65536 * 2, e->stream>>>(E, e->silu_table);
+            } else if (prog >= 0) {
                 switch (prog) {
                 case EW_ADD: launch_prog<EW_ADD>(e, E); break;
                 case EW_SUB: launch_prog<EW_SUB>(e, E); break;
@@ -696,6 +720,7 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
                 case EW_DIV: launch_prog<EW_DIV>(e, E); break;
                 case EW_DIV_MUL: launch_prog<EW_DIV_MUL>(e, E); break;
                 case EW_SILU: launch_prog<EW_SILU>(e, E); break;
+                case EW_SILU_MUL: launch_prog<EW_SILU_MUL>(e, E); break;
                 case EW_MUL_MUL_SUB: launch_prog<EW_MUL_MUL_SUB>(e, E); break;
                 default: launch_prog<EW_MUL_MUL_ADD>(e, E); break;
                 }

@@ -156,6 +156,7 @@ struct Realization {
     std::map<std::string, int> int_sums;        // sites whose `product` and `accum` are i32: 1 product, 2 accum, 3 both
     int order = PSK_ORDER_SEQUENTIAL;
     bool blockwise_attention = false; // "order": {"kind": "device", "attention": "blockwise"}
+    bool merged_launches = false;     // "order": {..., "launches": "merged"}: bit-preserving rewrites of the launch list
 
     static Realization parse(const char *text)
     {
@@ -198,6 +199,10 @@ struct Realization {
             if (kind == "sequential" || kind == "blocked") r.order = PSK_ORDER_SEQUENTIAL;
             else if (kind == "device") r.order = PSK_ORDER_DEVICE;
             else raise(PSK_E7005, "realization: the order `" + kind + "` is not one this executor has kernels for (sequential, device)");
+            if (const Json *ml = o->get("launches")) {
+                if (ml->str == "merged") r.merged_launches = true;
+                else if (ml->str != "reference") raise(PSK_E7005, "realization: the launch list `" + ml->str + "` is not one this executor has (reference, merged)");
+            }
             if (const Json *at = o->get("attention")) {
                 if (at->str == "blockwise") {
                     if (r.order != PSK_ORDER_DEVICE) raise(PSK_E7005, "realization: `attention: blockwise` is part of the order `device`");
@@ -289,11 +294,13 @@ struct Tensor {
     int q_span = 1;
     bool borrowed = false;
     void *raw = nullptr; // a caller's device buffer (psk_host_call_device)
+    std::vector<int64_t> vstrides; // a view that is not row-major over its axes (merged launches only); empty: row-major
 
     int64_t numel() const { int64_t n = 1; for (auto &a : axes) n *= a.len; return n; }
     void *ptr() const { return raw ? raw : st->p; }
     std::vector<int64_t> strides() const
     {
+        if (!vstrides.empty()) return vstrides;
         std::vector<int64_t> s(axes.size());
         int64_t acc = 1;
         for (int i = (int)axes.size() - 1; i >= 0; --i) { s[i] = acc; acc *= axes[i].len; }
@@ -363,7 +370,7 @@ bool result_axes(const Axes &a, const Axes &b, Axes &out)
 
 const char *prim_name(int p)
 {
-    static const char *n[] = {"add", "sub", "mul", "div", "max", "min", "neg", "exp", "log", "tanh", "sqrt", "sin", "cos", "abs", "gelu", "gelu_deriv", "relu", "heaviside", "sign", "sigmoid", "pow", "real"};
+    static const char *n[] = {"add", "sub", "mul", "div", "max", "min", "neg", "exp", "log", "tanh", "sqrt", "sin", "cos", "abs", "gelu", "gelu_deriv", "relu", "heaviside", "sign", "sigmoid", "pow", "real", "round"};
     return n[p];
 }
 
@@ -575,7 +582,7 @@ struct psk_host {
     }
 
     // ---- elementwise (lower.rs:309-372) -------------------------------------------
-    Tensor fused(const std::string &site, const std::vector<StepSpec> &steps, const std::vector<const Tensor *> &ins, const std::string &name_override = "")
+    Tensor fused(const std::string &site, const std::vector<StepSpec> &steps, const std::vector<const Tensor *> &ins, const std::string &name_override = "", const Tensor *into = nullptr)
     {
         // the result's axes: the steps' broadcasts replayed (host.rs:1117-1137)
         std::vector<Axes> shapes;
@@ -590,7 +597,12 @@ struct psk_host {
         }
         Axes out_axes = shapes.back();
         int d = site_dtype(site);
-        Tensor out = fresh_at(site, out_axes);
+        if (into) {
+            bool same = into->axes.size() == out_axes.size() && into->dtype == d && !into->affine && !rz.scaled.count(site);
+            for (size_t a = 0; same && a < out_axes.size(); ++a) same = into->axes[a].len == out_axes[a].len;
+            if (!same) raise(PSK_E7001, "fused: the destination " + show(into->axes) + " is not the group's result " + show(out_axes));
+        }
+        Tensor out = into ? *into : fresh_at(site, out_axes);
         psk_launch l;
         memset(&l, 0, sizeof l);
         l.op = PSK_OP_FUSED;
@@ -603,7 +615,7 @@ struct psk_host {
             view(*ins[i], map, (int)out_axes.size(), st, ss);
             set_operand(l.in[i], *ins[i], st, ss);
         }
-        set_operand(l.out, out, contiguous(out_axes), {});
+        set_operand(l.out, out, out.strides(), {});
         l.n_steps = (int)steps.size();
         for (size_t k = 0; k < steps.size(); ++k) {
             l.steps[k].prim = steps[k].prim;
@@ -910,6 +922,20 @@ struct psk_host {
         return out;
     }
 
+    // The same elements without a copy: a view of x (merged launches; the reference's buffers have no strides,
+    // so its slice is a nest of its own, lower.rs:1554).
+    Tensor slice_view(const std::string &axis, int64_t lo, int64_t hi, const Tensor &x)
+    {
+        int p = -1;
+        for (size_t i = 0; i < x.axes.size(); ++i) if (x.axes[i].name == axis) { p = (int)i; break; }
+        if (p < 0 || lo > hi || hi > x.axes[p].len) raise(PSK_E7001, "slice of `" + axis + "` outside " + show(x.axes));
+        Tensor v = x;
+        v.vstrides = x.strides();
+        v.off += lo * v.vstrides[p];
+        v.axes[p].len = hi - lo;
+        return v;
+    }
+
     Tensor concat(const std::string &site, const std::string &axis, const Tensor &x, const Tensor &y)
     {
         int p = -1;
@@ -1005,6 +1031,13 @@ struct psk_host {
                     if ((int)i < t.q_over) t.q_over += (int)parts.size() - 1;
                     else if ((int)i < t.q_over + t.q_span) t.q_span += (int)parts.size() - 1;
                 }
+                if (!t.vstrides.empty()) {
+                    int64_t acc = t.vstrides[i];
+                    std::vector<int64_t> ps(parts.size());
+                    for (int k = (int)parts.size() - 1; k >= 0; --k) { ps[k] = acc; acc *= parts[k].len; }
+                    t.vstrides.erase(t.vstrides.begin() + i);
+                    t.vstrides.insert(t.vstrides.begin() + i, ps.begin(), ps.end());
+                }
                 t.axes.erase(t.axes.begin() + i);
                 t.axes.insert(t.axes.begin() + i, parts.begin(), parts.end());
                 return t;
@@ -1016,6 +1049,10 @@ struct psk_host {
         Tensor t = x;
         for (size_t i = 0; i + 1 < t.axes.size(); ++i)
             if (t.axes[i].name == a && t.axes[i + 1].name == b) {
+                if (!t.vstrides.empty()) {
+                    if (t.vstrides[i] != t.vstrides[i + 1] * t.axes[i + 1].len) raise(PSK_E7001, "merge: `" + a + "`, `" + b + "` of a view are not one run of elements");
+                    t.vstrides.erase(t.vstrides.begin() + i);
+                }
                 t.axes[i] = {"", t.axes[i].len * t.axes[i + 1].len};
                 t.axes.erase(t.axes.begin() + i + 1);
                 return t;
@@ -1137,6 +1174,28 @@ struct psk_host {
         const std::string f = "rope";
         int64_t hd = x.axes.back().len;
         Tensor p = split(x, "hd", {{"pair", 2}, {"rot", hd / 2}});
+        if (rz.merged_launches && !calibrating) {
+            // The same values from fewer launches: the two slices are views of x, cos and sin of the one angle table
+            // are computed once a call, and each half is written where the concatenation would copy it. Every
+            // site keeps its type's rounding, so this needs the copies' sites to be of the type they copy.
+            const int dx = x.dtype, d9 = rz.dtype_at(f + "/%9"), d12 = rz.dtype_at(f + "/%12");
+            bool plain = !x.affine && rz.dtype_at(f + "/%3") == dx && rz.dtype_at(f + "/%4") == dx && d9 == d12 && rz.dtype_at(f + "/%13") == d9;
+            for (auto site : {"/%3", "/%4", "/%9", "/%12", "/%13"}) plain = plain && !rz.scaled.count(f + site);
+            if (plain) {
+                Tensor x0 = slice_view("pair", 0, 1, p), x1 = slice_view("pair", 1, 2, p);
+                auto key = std::make_pair(phi.ptr(), phi.off);
+                auto hit = rope_tables.find(key);
+                if (hit == rope_tables.end()) hit = rope_tables.emplace(key, std::make_pair(unary(f + "/%5", PSK_COS, phi), unary(f + "/%6", PSK_SIN, phi))).first;
+                const Tensor &c = hit->second.first, &s = hit->second.second;
+                Tensor cat = fresh_at(f + "/%13", p.axes);
+                Tensor lo = slice_view("pair", 0, 1, cat), hi = slice_view("pair", 1, 2, cat);
+                fused(f + "/%9", {Bn(PSK_MUL, 0, 1), Bn(PSK_MUL, 2, 3), Bn(PSK_SUB, S(0), S(1))}, {&x0, &c, &x1, &s}, "", &lo);
+                fused(f + "/%12", {Bn(PSK_MUL, 0, 1), Bn(PSK_MUL, 2, 3), Bn(PSK_ADD, S(0), S(1))}, {&x1, &c, &x0, &s}, "", &hi);
+                Tensor m = merge(cat, "pair", "rot");
+                m.axes.back().name = "hd";
+                return m;
+            }
+        }
         Tensor x0 = slice(f + "/%3", "pair", 0, 1, p);
         Tensor x1 = slice(f + "/%4", "pair", 1, 2, p);
         Tensor c = unary(f + "/%5", PSK_COS, phi);
@@ -1191,6 +1250,19 @@ struct psk_host {
         const std::string f = "SwiGLU.apply";
         Tensor wg = layer(param("blocks.ff.gate.w"), l), wu = layer(param("blocks.ff.up.w"), l), wd = layer(param("blocks.ff.down.w"), l);
         Tensor g = dot("Dense.apply/%3", x, wg);
+        const int ds = rz.dtype_at("silu/%2"), dh = rz.dtype_at(f + "/%7");
+        if (rz.merged_launches && !calibrating && (ds == PSK_BF16 || ds == PSK_F32) && ds == dh && g.dtype == ds && !g.affine && !rz.scaled.count("silu/%2") && !rz.scaled.count(f + "/%7")) {
+            // silu's group and the product with `up` as one launch: silu's value is rounded to its site's type
+            // inside the group (PSK_ROUND), so the product reads what the separate launch would have stored
+            Tensor u = dot("Dense.apply/%3", x, wu);
+            if (u.dtype == ds && !u.affine) {
+                Tensor h = fused(f + "/%7", {U(PSK_SIGMOID, 0), Bn(PSK_MUL, 0, S(0)), U(PSK_ROUND, S(1), ds), Bn(PSK_MUL, S(2), 1)}, {&g, &u});
+                return dot("Dense.apply/%3", h, wd);
+            }
+            Tensor sg = fused("silu/%2", {U(PSK_SIGMOID, 0), Bn(PSK_MUL, 0, S(0))}, {&g});
+            Tensor h = binary(f + "/%7", PSK_MUL, sg, u);
+            return dot("Dense.apply/%3", h, wd);
+        }
         Tensor sg = fused("silu/%2", {U(PSK_SIGMOID, 0), Bn(PSK_MUL, 0, S(0))}, {&g});
         Tensor u = dot("Dense.apply/%3", x, wu);
         Tensor h = binary(f + "/%7", PSK_MUL, sg, u);
@@ -1410,8 +1482,13 @@ struct psk_host {
         return dot("Dense.apply/%4", a, param("w"));
     }
 
+    // values one call computes once where the source computes them again with the same arguments (merged launches)
+    std::map<std::pair<void *, int64_t>, std::pair<Tensor, Tensor>> rope_tables;
+
     Tensor call(const std::string &entry, const std::vector<Tensor> &in)
     {
+        struct Forget { psk_host *h; ~Forget() { h->rope_tables.clear(); } } forget{this};
+        rope_tables.clear();
         auto need = [&](size_t n) { if (in.size() != n) raise(PSK_E7001, model + "." + entry + " takes " + std::to_string(n) + " inputs"); };
         if (model == "llama") {
             if (entry == "apply") { need(1); return llama_apply(in[0]); }

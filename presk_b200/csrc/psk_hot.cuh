@@ -22,6 +22,9 @@ struct EwParams {
     int32_t cs[4];      // stride along the columns: 0 or 1
     int64_t rs[4], ors; // stride from row to row, in elements
     uint32_t rows, colv; // colv = cols / 8
+    // rows in two levels (k_ew_prog only): row r = r0 * rows1 + r1 lies at r0 * rs0 + r1 * rs; rows1 = 0: one level
+    uint32_t rows1, pad_;
+    int64_t rs0[4], ors0;
     int32_t n_in, guarded;
     psk_step steps[4];
     uint32_t *ovf, *status;
@@ -141,7 +144,7 @@ __global__ void __launch_bounds__(256, 2) k_ew(const __grid_constant__ EwParams 
                 switch (st.prim) {
                 case PSK_SIGMOID:
 #pragma unroll
-                    for (int t = 0; t < 8; ++t) sv[s][t] = __fdiv_rn(1.0f, __fadd_rn(1.0f, lm_expf(-a[0][t])));
+                    for (int t = 0; t < 8; ++t) sv[s][t] = __frcp_rn(__fadd_rn(1.0f, lm_expf(-a[0][t])));
                     break;
                 case PSK_SQRT:
 #pragma unroll
@@ -251,7 +254,7 @@ __global__ void __launch_bounds__(128, 3) k_ew_bf16(const __grid_constant__ EwPa
                     switch (st.prim) {
                     case PSK_SIGMOID:
 #pragma unroll
-                        for (int t = 0; t < 8; ++t) sv[s][t] = __fdiv_rn(1.0f, __fadd_rn(1.0f, lm_expf(-a[0][t])));
+                        for (int t = 0; t < 8; ++t) sv[s][t] = __frcp_rn(__fadd_rn(1.0f, lm_expf(-a[0][t])));
                         break;
                     case PSK_SQRT:
 #pragma unroll
@@ -272,7 +275,7 @@ __global__ void __launch_bounds__(128, 3) k_ew_bf16(const __grid_constant__ EwPa
 // compile time: no routing of step arguments at run time, a handful of
 // instructions an element. A launch whose steps are exactly one of these (the
 // executor compares them) and whose operands are all bf16 takes this kernel.
-enum EwProg { EW_ADD = 0, EW_SUB, EW_MUL, EW_DIV, EW_DIV_MUL, EW_SILU, EW_MUL_MUL_SUB, EW_MUL_MUL_ADD, EW_NPROG };
+enum EwProg { EW_ADD = 0, EW_SUB, EW_MUL, EW_DIV, EW_DIV_MUL, EW_SILU, EW_MUL_MUL_SUB, EW_MUL_MUL_ADD, EW_SILU_MUL, EW_NPROG };
 
 template <int PROG>
 PSK_DEV float ew_eval(float a, float b, float c, float d)
@@ -282,7 +285,9 @@ PSK_DEV float ew_eval(float a, float b, float c, float d)
     else if constexpr (PROG == EW_MUL) return __fmul_rn(a, b);
     else if constexpr (PROG == EW_DIV) return __fdiv_rn(a, b);
     else if constexpr (PROG == EW_DIV_MUL) return __fmul_rn(__fdiv_rn(a, b), c);                              // [div 0,1; mul s0,2]
-    else if constexpr (PROG == EW_SILU) return __fmul_rn(a, __fdiv_rn(1.0f, __fadd_rn(1.0f, lm_expf(-a))));    // [sigmoid 0; mul 0,s0]
+    else if constexpr (PROG == EW_SILU) return __fmul_rn(a, __frcp_rn(__fadd_rn(1.0f, lm_expf(-a))));    // [sigmoid 0; mul 0,s0]
+    else if constexpr (PROG == EW_SILU_MUL)                                                                   // [sigmoid 0; mul 0,s0; round s1 to bf16; mul s2,1]
+        return __fmul_rn(bf16_to_f32(f32_to_bf16(__fmul_rn(a, __frcp_rn(__fadd_rn(1.0f, lm_expf(-a)))))), b);
     else if constexpr (PROG == EW_MUL_MUL_SUB) return __fsub_rn(__fmul_rn(a, b), __fmul_rn(c, d));            // [mul 0,1; mul 2,3; sub s0,s1]
     else return __fadd_rn(__fmul_rn(a, b), __fmul_rn(c, d));                                                  // [mul 0,1; mul 2,3; add s0,s1]
 }
@@ -291,6 +296,13 @@ template <int PROG>
 struct EwArity {
     static constexpr int value = (PROG == EW_SILU) ? 1 : (PROG == EW_DIV_MUL) ? 3 : (PROG == EW_MUL_MUL_SUB || PROG == EW_MUL_MUL_ADD) ? 4 : 2;
 };
+
+PSK_DEV int64_t ew_row_offset(const EwParams &E, uint32_t r, int64_t s1, int64_t s0)
+{
+    if (E.rows1 == 0) return (int64_t)r * s1;
+    const uint32_t r0 = r / E.rows1;
+    return (int64_t)r0 * s0 + (int64_t)(r - r0 * E.rows1) * s1;
+}
 
 template <int PROG, int UNR>
 __global__ void __launch_bounds__(256, 2) k_ew_prog(const __grid_constant__ EwParams E)
@@ -303,7 +315,7 @@ __global__ void __launch_bounds__(256, 2) k_ew_prog(const __grid_constant__ EwPa
 #pragma unroll
     for (int i = 0; i < NIN; ++i) {
         whole[i] = 0;
-        if (E.cs[i] == 0 && E.rs[i] == 0) {
+        if (E.cs[i] == 0 && E.rs[i] == 0 && E.rs0[i] == 0) {
             uint32_t dummy = 0;
             const uint32_t h = f32_bits(edge_round(load_real(E.in[i], E.dt[i], 0), PSK_BF16, E.dt[i], &dummy)) >> 16;
             whole[i] = h | (h << 16);
@@ -320,14 +332,15 @@ __global__ void __launch_bounds__(256, 2) k_ew_prog(const __grid_constant__ EwPa
             if (idx < total) {
 #pragma unroll
                 for (int i = 0; i < NIN; ++i) {
-                    const uint16_t *p = (const uint16_t *)E.in[i] + (int64_t)rr[u] * E.rs[i];
+                    const int64_t ro = ew_row_offset(E, rr[u], E.rs[i], E.rs0[i]);
+                    const uint16_t *p = (const uint16_t *)E.in[i] + ro;
                     if (E.cs[i]) raw[u][i] = *reinterpret_cast<const uint4 *>(p + cc[u]);
-                    else if (E.rs[i] == 0) raw[u][i] = make_uint4(whole[i], whole[i], whole[i], whole[i]);
+                    else if (E.rs[i] == 0 && E.rs0[i] == 0) raw[u][i] = make_uint4(whole[i], whole[i], whole[i], whole[i]);
                     else {
                         // one value for the whole row, of any real type: the kernel's type is bf16, so the
                         // value it sees is the stored one rounded to bf16 at the kernel's edge
                         uint32_t dummy = 0;
-                        const float v = edge_round(load_real(E.in[i], E.dt[i], (int64_t)rr[u] * E.rs[i]), PSK_BF16, E.dt[i], &dummy);
+                        const float v = edge_round(load_real(E.in[i], E.dt[i], ro), PSK_BF16, E.dt[i], &dummy);
                         const uint32_t h = f32_bits(v) >> 16;
                         raw[u][i] = make_uint4(h | (h << 16), h | (h << 16), h | (h << 16), h | (h << 16));
                     }
@@ -353,7 +366,66 @@ __global__ void __launch_bounds__(256, 2) k_ew_prog(const __grid_constant__ EwPa
                 }
                 out[q] = pack_bf16x2(ew_eval<PROG>(lo[0], lo[1], lo[2], lo[3]), ew_eval<PROG>(hi[0], hi[1], hi[2], hi[3]));
             }
-            *reinterpret_cast<uint4 *>((uint16_t *)E.out + (int64_t)rr[u] * E.ors + cc[u]) = make_uint4(out[0], out[1], out[2], out[3]);
+            *reinterpret_cast<uint4 *>((uint16_t *)E.out + ew_row_offset(E, rr[u], E.ors, E.ors0) + cc[u]) = make_uint4(out[0], out[1], out[2], out[3]);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// A group of one bf16 input and a bf16 result is a function of 65 536 codes.
+// silu costs about fifty instructions an element when computed to the
+// reference's bits (its expf with a division inside, a reciprocal), which
+// makes a launch over [tokens, ff] instruction-bound at a quarter of the
+// memory rate. So the executor evaluates the very same device function once
+// over every code (k_table_silu), and launches read the result from a copy of
+// that table in shared memory: the same bits by construction, NaN payloads
+// included, at the memory's rate.
+// ---------------------------------------------------------------------------
+__global__ void k_table_silu(uint16_t *table)
+{
+    const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c < 65536u) table[c] = f32_to_bf16(ew_eval<EW_SILU>(bf16_to_f32((uint16_t)c), 0.0f, 0.0f, 0.0f));
+}
+
+// out = T[in0] (MUL = false), or bf16(T[in0] * in1) (MUL = true: the group [.., round to bf16, mul s2,1])
+template <bool MUL>
+__global__ void __launch_bounds__(1024, 1) k_ew_lut(const __grid_constant__ EwParams E, const uint16_t *__restrict__ table)
+{
+    extern __shared__ uint16_t s_table[];
+    for (uint32_t i = threadIdx.x; i < 65536u / 8u; i += blockDim.x)
+        reinterpret_cast<uint4 *>(s_table)[i] = reinterpret_cast<const uint4 *>(table)[i];
+    __syncthreads();
+    const uint32_t total = E.rows * E.colv;
+    const uint32_t stride = gridDim.x * blockDim.x;
+    constexpr int UNR = 2;
+    for (uint32_t idx0 = blockIdx.x * blockDim.x + threadIdx.x; idx0 < total; idx0 += stride * UNR) {
+        uint4 a[UNR], b[UNR];
+        int64_t oo[UNR];
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+            const uint32_t idx = idx0 + u * stride;
+            b[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (idx < total) {
+                uint32_t r = 0, c = idx * 8u;
+                if (E.rows != 1) { r = idx / E.colv; c = (idx - r * E.colv) * 8u; }
+                a[u] = *reinterpret_cast<const uint4 *>((const uint16_t *)E.in[0] + (int64_t)r * E.rs[0] + c);
+                if (MUL) b[u] = *reinterpret_cast<const uint4 *>((const uint16_t *)E.in[1] + (int64_t)r * E.rs[1] + c);
+                oo[u] = (int64_t)r * E.ors + c;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+            if (idx0 + u * stride >= total) break;
+            const uint32_t w[4] = {a[u].x, a[u].y, a[u].z, a[u].w};
+            const uint32_t v[4] = {b[u].x, b[u].y, b[u].z, b[u].w};
+            uint32_t o[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const uint32_t lo = s_table[w[q] & 0xffffu], hi = s_table[w[q] >> 16];
+                if (MUL) o[q] = pack_bf16x2(__fmul_rn(bits_f32(lo << 16), bits_f32(v[q] << 16)), __fmul_rn(bits_f32(hi << 16), bits_f32(v[q] & 0xffff0000u)));
+                else o[q] = lo | (hi << 16);
+            }
+            *reinterpret_cast<uint4 *>((uint16_t *)E.out + oo[u]) = make_uint4(o[0], o[1], o[2], o[3]);
         }
     }
 }

@@ -37,13 +37,14 @@ PSK_DEV float prim_unary(int prim, float x, int imm, uint32_t *status)
     case PSK_RELU: return x < 0.0f ? 0.0f : x;
     case PSK_HEAVISIDE: return x > 0.0f ? 1.0f : 0.0f;
     case PSK_SIGN: return x < 0.0f ? -1.0f : (x > 0.0f ? 1.0f : 0.0f);
-    case PSK_SIGMOID: return __fdiv_rn(1.0f, __fadd_rn(1.0f, lm_expf(-x)));
+    case PSK_SIGMOID: return __frcp_rn(__fadd_rn(1.0f, lm_expf(-x)));
     case PSK_POW: {
         if (imm == 0) return 1.0f;
         float e = x;
         for (int i = 1; i < imm; ++i) e = __fmul_rn(e, x);
         return e;
     }
+    case PSK_ROUND: return imm == PSK_BF16 ? bf16_to_f32(f32_to_bf16(x)) : imm == PSK_F16 ? f16_to_f32(f32_to_f16(x)) : imm == PSK_E8M15 ? e8m15_to_f32(f32_to_e8m15(x)) : x;
     default: return x; // PSK_REAL
     }
 }

@@ -226,3 +226,25 @@ def test_llama_blockwise_attention_within_tolerance(cuda, oracle, G):
     assert np.abs(lg - lw).max() <= 2.0**-6 * np.abs(lw).max()
     want = models.llama_numpy(p, c, ids)
     assert np.abs(lg - want).max() <= 0.05 * np.abs(want).max()
+
+
+@pytest.mark.parametrize("kind", ["sequential", "device"])
+def test_merged_launches_keep_every_bit_on_the_gpu(cuda, oracle, kind):
+    """`launches: merged` (slices as views, concatenation halves written in place, rotary tables once a call,
+    silu and the product with `up` as one group) changes which launches run, not one bit of any value."""
+    c = dict(V=512, D=256, H=4, G=2, FF=512, L=2)
+    p = models.llama_params(c)
+    ids = np.random.default_rng(10).integers(0, c["V"], size=(2, 128), dtype=np.int64)
+    outs = []
+    for extra in ({}, {"launches": "merged"}):
+        rz = {"default": "bf16", "order": dict(kind=kind, **extra), "params": {k: "bf16" for k in p}, "storage": {"Llama.apply/%11": "f32"}}
+        h = models.give(Host(cuda, rz).prepare("llama", **c), p)
+        h.set_logging(True)
+        outs.append(h.call("apply", [ids], (2, 128, c["V"])))
+        log = h.launch_log()
+    assert "fused 4 steps" in log and not any(n.startswith("slice") for n in log)
+    assert_same_bits(outs[1], outs[0])
+    if kind == "sequential":
+        rz = {"default": "bf16", "order": {"kind": "sequential"}, "params": {k: "bf16" for k in p}, "storage": {"Llama.apply/%11": "f32"}}
+        want = models.give(Host(oracle.vtable(), rz).prepare("llama", **c), p).call("apply", [ids], (2, 128, c["V"]))
+        assert_same_bits(outs[1], want)

@@ -373,3 +373,35 @@ def test_blockwise_attention_is_refused_where_it_does_not_apply(cuda):
         assert e.value.code == 7005
         for p in bufs:
             cuda.free(p)
+
+
+@pytest.mark.parametrize("with_mul", [False, True])
+def test_tabulated_silu_is_the_exact_one(cuda, oracle, with_mul):
+    """A bf16 silu group over enough elements is read from a table of all 65 536 codes that the device
+    computed with its exact function; with the product by a second operand it is the merged group
+    [sigmoid; mul; round to bf16; mul]. Every code occurs in the input, NaNs and infinities included:
+    the bits must be the oracle's."""
+    rows, cols = 2560, 2048  # 5.2 M elements: above the size from which the table is used
+    rng = np.random.default_rng(21)
+    g = rng.integers(0, 65536, size=(rows, cols), dtype=np.uint16)
+    g.ravel()[:65536] = np.arange(65536, dtype=np.uint16)
+    u = bf16_of(oracle, rng.standard_normal((rows, cols)) * 3.0)
+    l = launch_desc(abi.OP_FUSED, abi.BF16, [rows, cols])
+    if with_mul:
+        l.n_inputs, l.n_steps = 2, 4
+        steps = [(abi.SIGMOID, 1, 0, 0, 0), (abi.MUL, 2, 0, -1, 0), (abi.ROUND, 1, -2, 0, abi.BF16), (abi.MUL, 2, -3, 1, 0)]
+    else:
+        l.n_inputs, l.n_steps = 1, 2
+        steps = [(abi.SIGMOID, 1, 0, 0, 0), (abi.MUL, 2, 0, -1, 0)]
+    for k, (prim, nargs, a, b, imm) in enumerate(steps):
+        l.steps[k].prim, l.steps[k].nargs, l.steps[k].src[0], l.steps[k].src[1], l.steps[k].imm = prim, nargs, a, b, imm
+    set_operand(l.inputs[0], abi.BF16, [rows, cols], [0, 1])
+    if with_mul:
+        set_operand(l.inputs[1], abi.BF16, [rows, cols], [0, 1])
+    set_operand(l.out, abi.BF16, [rows, cols], [0, 1])
+    got, want, _, _ = run_both(cuda, oracle, l, [g, u] if with_mul else [g], rows * cols * 2)
+    a, b = got.view(np.uint16), want.view(np.uint16)
+    # a NaN is a NaN on both sides; which NaN the hardware's arithmetic makes of one is not the host's choice
+    nan = ((a & 0x7fff) > 0x7f80) & ((b & 0x7fff) > 0x7f80)
+    bad = np.nonzero((a != b) & ~nan)[0]
+    assert bad.size == 0, f"{bad.size} differ; first: code {g.ravel()[bad[0]]:#x}: {a[bad[0]]:#x} vs {b[bad[0]]:#x}"

@@ -181,3 +181,24 @@ def test_blockwise_attention_is_its_four_launches_on_the_oracle(oracle):
     with pytest.raises(PreskError) as e:
         Host(oracle.vtable(), {"default": "bf16", "order": {"kind": "sequential", "attention": "blockwise"}})
     assert e.value.code == 7005
+
+
+def test_merged_launches_keep_every_bit(oracle):
+    """`launches: merged` reads slices as views, writes a concatenation's halves in place and computes the
+    rotary cos/sin once a call: fewer launches, the same bits, under either order and with GQA."""
+    c = dict(models.LLAMA_TINY, G=1)
+    p = models.llama_params(c)
+    ids = np.random.default_rng(9).integers(0, c["V"], size=(2, 16), dtype=np.int64)
+    for default in ("f32", "bf16"):
+        outs, logs = [], []
+        for order in ({"kind": "sequential"}, {"kind": "sequential", "launches": "merged"}):
+            h = models.give(Host(oracle.vtable(), {"default": default, "order": order}).prepare("llama", **c), p)
+            h.set_logging(True)
+            outs.append(h.call("apply", [ids], (2, 16, c["V"])))
+            outs.append(h.call("apply", [ids], (2, 16, c["V"])))  # a second call: nothing kept from the first
+            logs.append(h.launch_log())
+        for o in outs[1:]:
+            assert np.array_equal(outs[0].view(np.uint32), o.view(np.uint32))
+        assert not any(n.startswith("slice") or n.startswith("concat") for n in logs[1])
+        assert logs[1].count("cos") == 1 and logs[0].count("cos") == 2 * c["L"]  # the log is that of the last call
+        assert len(logs[1]) < len(logs[0])
