@@ -154,7 +154,7 @@ def cpu_prefill_tokens_per_s(consts, T, B, threads, int8=False):
 def microbench(args):
     """One kernel alone on synthetic operands, for tuning and for profiler captures:
     `--micro gemm --shape M,N,K[,batch[,b_n_major]]`, `--micro softmax --shape rows,n`,
-    `--micro ew --shape rows,cols`, `--micro attn --shape batch,heads,seq` (hd = 128, causal).
+    `--micro ew --shape rows,cols`, `--micro attn --shape batch,heads,seq` (hd = 128, causal), `--micro norm --shape rows,cols`.
     Prints one JSON line (not the benchmark's)."""
     import torch
     from presk_b200 import Executor, abi, launch_desc
@@ -221,6 +221,22 @@ def microbench(args):
         nqb = t // 128
         fl = 4.0 * B * H * (nqb * (nqb + 1) / 2) * 128 * 128 * hd
         print(json.dumps({"micro": "attn", "shape": dims, "ms": ms, "TFLOP/s (causal blocks, one pass)": fl / ms / 1e9}))
+    elif args.micro == "norm":
+        # a norm's last group: x[rows, n] / root[rows] (f32) * gamma[n]
+        rows, n = dims[:2]
+        x, gam = ex.upload(bf16((rows, n))), ex.upload(bf16((n,)))
+        root = ex.upload((np.abs(rng.standard_normal(rows)) + 0.5).astype(np.float32))
+        out = ex.alloc(rows * n * 2)
+        l = launch_desc(abi.OP_FUSED, abi.BF16, [rows, n], order=abi.ORDER_DEVICE)
+        l.n_inputs, l.n_steps = 3, 2
+        l.steps[0].prim, l.steps[0].nargs, l.steps[0].src[0], l.steps[0].src[1] = abi.DIV, 2, 0, 1
+        l.steps[1].prim, l.steps[1].nargs, l.steps[1].src[0], l.steps[1].src[1] = abi.MUL, 2, -1, 2
+        for o in (l.inputs[0], l.out):
+            o.dtype, o.stride[0], o.stride[1], o.numel = abi.BF16, n, 1, rows * n
+        l.inputs[1].dtype, l.inputs[1].stride[0], l.inputs[1].numel = abi.F32, 1, rows
+        l.inputs[2].dtype, l.inputs[2].stride[1], l.inputs[2].numel = abi.BF16, 1, n
+        ms = timed(lambda: ex.run(l, [x, root, gam, out]), args.steps)
+        print(json.dumps({"micro": "norm", "shape": dims, "ms": ms, "GB/s": rows * n * 4 / ms / 1e6}))
     elif args.micro in ("softmax", "ew"):
         rows, n = dims[:2]
         x = ex.upload(bf16((rows, n)))
@@ -251,7 +267,7 @@ def microbench(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--micro", default=None, choices=["gemm", "softmax", "ew", "attn"])
+    ap.add_argument("--micro", default=None, choices=["gemm", "softmax", "ew", "attn", "norm"])
     ap.add_argument("--shape", default="8192,8192,8192")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
@@ -378,10 +394,11 @@ def main():
         if args.dump_profile:
             names = {}
             for k, name, kms, fl, bts in rows:
-                d = names.setdefault(k + " | " + name, [0, 0.0, 0.0, 0.0])
+                # launches of one name and different sizes (a norm's scalar root and its scaling of a whole tensor) apart
+                d = names.setdefault(k + " | " + name + f" | {bts / 1e6:.1f} MB", [0, 0.0, 0.0, 0.0])
                 d[0] += 1; d[1] += kms; d[2] += fl; d[3] += bts
             with open(args.dump_profile, "w") as f:
-                f.write("kernel | launch name\tlaunches\ttotal ms\tshare\tms/launch\tGB/s (algorithmic)\tTFLOP/s\n")
+                f.write("kernel | launch name | algorithmic bytes a launch\tlaunches\ttotal ms\tshare\tms/launch\tGB/s (algorithmic)\tTFLOP/s\n")
                 for key, d in sorted(names.items(), key=lambda kv: -kv[1][1]):
                     f.write(f"{key}\t{d[0]}\t{d[1]:.3f}\t{d[1] / total_kernel_ms:.4f}\t{d[1] / d[0]:.4f}\t{d[3] / (d[1] * 1e-3) / 1e9:.1f}\t{d[2] / (d[1] * 1e-3) / 1e12:.1f}\n")
         tc = by.get("k_gemm_tc", [0, 0.0, 0.0, 0.0])

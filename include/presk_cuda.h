@@ -84,7 +84,7 @@ typedef enum {
                              x under the order-preserving map u = b ^ (b >> 31 ? 0xffffffff : 0x80000000) of
                              its bits b, start 0xff800000 and 0x007fffff. NaNs are passed over. No counterpart
                              among the reference's kernels: it measures envelopes on its exact interpreter. */
-    PSK_OP_ATTENTION = 11 /* four launches of an attention function as one (examples/coverage/llama.psk:100-102):
+    PSK_OP_ATTENTION = 11, /* four launches of an attention function as one (examples/coverage/llama.psk:100-102):
                              scores = ein(q*k) over hd, scores / rt, softmax over seq2 where mask, ein(a*v) over
                              seq2. Space: outer axes (..., seq, hd), one inner axis seq2. Inputs: q (stride 0 on
                              seq2), k and v (stride 0 on seq; hd and seq2 both walked), rt (rank 0), and the mask
@@ -93,6 +93,21 @@ typedef enum {
                              the other; an executor may only fuse them under PSK_ORDER_DEVICE, and then agrees
                              with them within a tolerance. No counterpart among the reference's kernels: its
                              fusion (presk-core/src/fusion.rs) never crosses a contraction or a softmax. */
+    PSK_OP_RMSNORM = 12,  /* the four launches of RMSNorm.apply as one (examples/coverage/llama.psk:34-40): x*x, its
+                             mean over the last axis, sqrt(mean + eps), x / root * gamma. Space: the axes of x, no
+                             inner axis. Inputs: x, eps (rank 0), gamma (over the last axis). iparam[0]: the length
+                             of the last axis; iparam[1..3]: the storage types of the square's, the mean's and the
+                             root's sites; dtype: the result's. The value is DEFINED as that of the four launches run
+                             one after the other under the launch's order (the oracle runs exactly those); an
+                             executor that takes it must give their bits. No counterpart among the reference's
+                             kernels: its groups never cross a reduction. */
+    PSK_OP_ROPE = 13      /* the rotation of `rope` (examples/coverage/llama.psk:66-72) as one launch: with x read as
+                             (.., seq, pair = 2, rot) and c, s over (seq, rot),
+                               out[.., 0, r] = x[.., 0, r]*c - x[.., 1, r]*s,  out[.., 1, r] = x[.., 1, r]*c + x[.., 0, r]*s,
+                             every product rounded to f32 before the sum, the sums rounded once to the result's
+                             type: the reference's two slices, two groups of three steps and concatenation, for the
+                             case that all of their sites are stored in x's type (the host offers nothing else).
+                             Space: the axes of the result. Inputs: x, c, s. */
 } psk_op;
 
 /* Elementary operations of a fusion group's steps (lower.rs:184-226). */

@@ -553,9 +553,106 @@ static int attention_unfused(const psk_launch *l, void *const *table, uint32_t *
     return rc;
 }
 
+/* PSK_OP_RMSNORM is by definition RMSNorm.apply's four launches (examples/coverage/llama.psk:34-40): mul, mean over
+ * the last axis, [add eps; sqrt], [div; mul gamma], each the reference's own nest with its result in its site's type. */
+static int rmsnorm_unfused(const psk_launch *l, void *const *table, uint32_t *overflow)
+{
+    const int no = l->n_outer;
+    if (no < 1 || l->n_inner != 0 || l->n_inputs != 3) return PSK_E7001;
+    const int d2 = (int)l->iparam[1], d3 = (int)l->iparam[2], d7 = (int)l->iparam[3];
+    int64_t rows = 1;
+    for (int a = 0; a < no - 1; ++a) rows *= l->dims[a];
+    const int64_t n = l->dims[no - 1];
+    void *x2 = malloc((size_t)(rows * n ? rows * n : 1) * elem_bytes(d2)), *ms = malloc((size_t)(rows ? rows : 1) * elem_bytes(d3)), *rt = malloc((size_t)(rows ? rows : 1) * elem_bytes(d7));
+    uint32_t ovf = 0, o1 = 0;
+    int rc;
+    psk_launch m;
+    memset(&m, 0, sizeof m);
+    m.name = "rmsnorm: mul"; m.op = PSK_OP_FUSED; m.dtype = d2; m.order = l->order; m.guarded = l->guarded;
+    m.n_inputs = 2; m.n_outer = no;
+    memcpy(m.dims, l->dims, sizeof m.dims);
+    m.in[0] = l->in[0]; m.in[1] = l->in[0];
+    attn_contiguous(&m.out, d2, l->dims, no, -1);
+    m.n_steps = 1; m.steps[0].prim = PSK_MUL; m.steps[0].nargs = 2; m.steps[0].src[0] = 0; m.steps[0].src[1] = 1;
+    { void *t[3] = {table[0], table[0], x2}; rc = psk_oracle_run(&m, t, &o1); ovf |= o1; }
+    if (rc == PSK_OK) {
+        memset(&m, 0, sizeof m);
+        m.name = "rmsnorm: mean"; m.op = PSK_OP_REDUCE; m.kind = PSK_REDUCE_MEAN; m.dtype = d3; m.order = l->order; m.guarded = l->guarded;
+        m.n_inputs = 1; m.n_outer = no - 1; m.n_inner = 1; m.iparam[0] = n;
+        memcpy(m.dims, l->dims, sizeof m.dims);
+        attn_contiguous(&m.in[0], d2, l->dims, no, -1);
+        attn_contiguous(&m.out, d3, l->dims, no - 1, -1);
+        void *t[2] = {x2, ms};
+        rc = psk_oracle_run(&m, t, &o1); ovf |= o1;
+    }
+    if (rc == PSK_OK) {
+        memset(&m, 0, sizeof m);
+        m.name = "rmsnorm: root"; m.op = PSK_OP_FUSED; m.dtype = d7; m.order = l->order; m.guarded = l->guarded;
+        m.n_inputs = 2; m.n_outer = no - 1;
+        memcpy(m.dims, l->dims, sizeof m.dims);
+        attn_contiguous(&m.in[0], d3, l->dims, no - 1, -1);
+        m.in[1] = l->in[1];
+        memset(m.in[1].stride, 0, sizeof m.in[1].stride);
+        attn_contiguous(&m.out, d7, l->dims, no - 1, -1);
+        m.n_steps = 2;
+        m.steps[0].prim = PSK_ADD; m.steps[0].nargs = 2; m.steps[0].src[0] = 0; m.steps[0].src[1] = 1;
+        m.steps[1].prim = PSK_SQRT; m.steps[1].nargs = 1; m.steps[1].src[0] = -1;
+        void *t[3] = {ms, table[1], rt};
+        rc = psk_oracle_run(&m, t, &o1); ovf |= o1;
+    }
+    if (rc == PSK_OK) {
+        m = *l;
+        m.name = "rmsnorm: scale"; m.op = PSK_OP_FUSED; m.n_inputs = 3;
+        m.in[0] = l->in[0];
+        attn_contiguous(&m.in[1], d7, l->dims, no - 1, -1); /* one root a row: no stride on the last axis */
+        m.in[2] = l->in[2];
+        m.n_steps = 2;
+        m.steps[0].prim = PSK_DIV; m.steps[0].nargs = 2; m.steps[0].src[0] = 0; m.steps[0].src[1] = 1;
+        m.steps[1].prim = PSK_MUL; m.steps[1].nargs = 2; m.steps[1].src[0] = -1; m.steps[1].src[1] = 2;
+        void *t[4] = {table[0], rt, table[2], table[3]};
+        rc = psk_oracle_run(&m, t, &o1); ovf |= o1;
+    }
+    free(x2); free(ms); free(rt);
+    if (overflow) *overflow = ovf;
+    return rc;
+}
+
+/* PSK_OP_ROPE: the two groups of three steps of `rope` (examples/coverage/llama.psk:69-70), each reading the two
+ * halves of x through strides where the reference copies them out first, each writing its half of the result
+ * where the reference concatenates afterwards. Copies do not change a value, so these are the reference's values. */
+static int rope_unfused(const psk_launch *l, void *const *table, uint32_t *overflow)
+{
+    const int no = l->n_outer;
+    if (no < 3 || l->n_inner != 0 || l->n_inputs != 3 || l->dims[no - 2] != 2) return PSK_E7001;
+    uint32_t ovf = 0, o1 = 0;
+    int rc = PSK_OK;
+    for (int half = 0; half < 2 && rc == PSK_OK; ++half) {
+        psk_launch m = *l;
+        m.name = "rope: half"; m.op = PSK_OP_FUSED; m.n_inputs = 4;
+        m.dims[no - 2] = 1;
+        const int64_t xp = l->in[0].stride[no - 2];
+        m.in[0] = l->in[0]; m.in[0].offset += half * xp;        /* this half */
+        m.in[1] = l->in[1];
+        m.in[2] = l->in[0]; m.in[2].offset += (1 - half) * xp;  /* the other */
+        m.in[3] = l->in[2];
+        m.out.offset += half * l->out.stride[no - 2];
+        m.n_steps = 3;
+        m.steps[0].prim = PSK_MUL; m.steps[0].nargs = 2; m.steps[0].src[0] = 0; m.steps[0].src[1] = 1;
+        m.steps[1].prim = PSK_MUL; m.steps[1].nargs = 2; m.steps[1].src[0] = 2; m.steps[1].src[1] = 3;
+        m.steps[2].prim = half ? PSK_ADD : PSK_SUB; m.steps[2].nargs = 2; m.steps[2].src[0] = -1; m.steps[2].src[1] = -2;
+        void *t[5] = {table[0], table[1], table[0], table[2], table[3]};
+        rc = psk_oracle_run(&m, t, &o1);
+        ovf |= o1;
+    }
+    if (overflow) *overflow = ovf;
+    return rc;
+}
+
 int psk_oracle_run(const psk_launch *l, void *const *table, uint32_t *overflow)
 {
+    if (l->op == PSK_OP_ROPE) return rope_unfused(l, table, overflow);
     if (l->op == PSK_OP_ATTENTION) return attention_unfused(l, table, overflow);
+    if (l->op == PSK_OP_RMSNORM) return rmsnorm_unfused(l, table, overflow);
     if (l->op == PSK_OP_CONTRACT && l->n_inner > 1) {
         psk_launch m = *l;
         int no = l->n_outer, w = 0;

@@ -637,7 +637,7 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
     L.fparam = (float)l->fparam[0];
     L.status = e->status;
     L.ovf = L.guarded ? next_flag(e, l) : e->flags;
-    if (l->op != PSK_OP_EMBED && l->op != PSK_OP_IOTA && l->op != PSK_OP_MAGNITUDE && l->op != PSK_OP_ATTENTION) coalesce_outer(L);
+    if (l->op != PSK_OP_EMBED && l->op != PSK_OP_IOTA && l->op != PSK_OP_MAGNITUDE && l->op != PSK_OP_ATTENTION && l->op != PSK_OP_RMSNORM && l->op != PSK_OP_ROPE) coalesce_outer(L);
     L.total = 1;
     for (int a = 0; a < L.n_outer; ++a) L.total *= L.dims[a];
     L.inner = 1;
@@ -959,6 +959,67 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
         attn::k_attn_fwd<<<grid, attn::THREADS, attn::SMEM_TOTAL, e->stream>>>(mq, mk, mv, A);
         const double blocks = causal ? (double)nqb * (double)(nqb + 1) / 2.0 : (double)nqb * (double)nqb;
         e->last_flops = 4.0 * (double)B * (double)(G * Pn) * blocks * 128.0 * 128.0 * (double)HD;
+        e->kernels += 1;
+        break;
+    }
+    case PSK_OP_RMSNORM: {
+        e->last_kernel = "k_rmsnorm_rows";
+        const std::string nm = l->name ? l->name : "rmsnorm";
+        const int no = L.n_outer;
+        if (no < 1 || L.n_inner != 0 || L.n_in != 3) { rc = fail(e, PSK_E7001, nm + ": x, eps and gamma over the axes of x"); break; }
+        const int64_t n = L.dims[no - 1];
+        // rows: every leading axis of x and of the result must walk whole rows one after the other
+        bool fits = device_order && l->dtype == PSK_BF16 && l->in[0].dtype == PSK_BF16 && l->in[2].dtype == PSK_BF16 && l->out.dtype == PSK_BF16
+            && l->iparam[0] == n && l->iparam[1] == PSK_BF16 && l->iparam[2] == PSK_F32 && l->iparam[3] == PSK_F32
+            && n % 256 == 0 && (n / 256 == 1 || n / 256 == 2 || n / 256 == 4 || n / 256 == 8 || n / 256 == 16)
+            && L.in[0].stride[no - 1] == 1 && L.out.stride[no - 1] == 1 && L.in[2].stride[no - 1] == 1
+            && aligned16(L.in[0].p) && aligned16(L.out.p) && aligned16(L.in[2].p) && !l->in[1].is_index && l->in[1].dtype != PSK_F64 && l->in[1].dtype != PSK_I8;
+        int64_t rows = 1, x_row = n, o_row = n;
+        for (int a = no - 2; a >= 0 && fits; --a) {
+            if (a == no - 2) { x_row = L.in[0].stride[a]; o_row = L.out.stride[a]; }
+            else fits = L.in[0].stride[a] == x_row * rows && L.out.stride[a] == o_row * rows;
+            fits = fits && L.in[2].stride[a] == 0;
+            rows *= L.dims[a];
+        }
+        fits = fits && x_row % 8 == 0 && o_row % 8 == 0;
+        if (!fits) { rc = fail(e, PSK_E7005, nm + ": the merged norm runs under the device order on bf16 rows of 256, 512, 1024, 2048 or 4096 elements with f32 statistics"); break; }
+        RmsParams R;
+        R.x = (const uint16_t *)L.in[0].p; R.gamma = (const uint16_t *)L.in[2].p; R.eps = L.in[1].p; R.eps_dtype = L.in[1].dtype;
+        R.out = (uint16_t *)const_cast<void *>(L.out.p); R.x_row = x_row; R.out_row = o_row; R.rows = rows; R.n = (int32_t)n;
+        const int g = grid_for(e, rows * 32, 256, 8);
+        switch (n / 256) {
+        case 1: k_rmsnorm_rows<1><<<g, 256, 0, e->stream>>>(R); break;
+        case 2: k_rmsnorm_rows<2><<<g, 256, 0, e->stream>>>(R); break;
+        case 4: k_rmsnorm_rows<4><<<g, 256, 0, e->stream>>>(R); break;
+        case 8: k_rmsnorm_rows<8><<<g, 256, 0, e->stream>>>(R); break;
+        default: k_rmsnorm_rows<16><<<g, 256, 0, e->stream>>>(R); break;
+        }
+        e->kernels += 1;
+        break;
+    }
+    case PSK_OP_ROPE: {
+        e->last_kernel = "k_rope_bf16";
+        const std::string nm = l->name ? l->name : "rope";
+        const int no = L.n_outer;
+        if (no < 3 || L.n_inner != 0 || L.n_in != 3 || L.dims[no - 2] != 2) { rc = fail(e, PSK_E7001, nm + ": x over (.., seq, pair = 2, rot), cos and sin over (seq, rot)"); break; }
+        const int64_t rot = L.dims[no - 1], T = L.dims[no - 3];
+        bool fits = l->dtype == PSK_BF16 && l->out.dtype == PSK_BF16 && rot % 8 == 0 && rot <= (1 << 20) && T <= 0x7fffffff;
+        for (int i = 0; i < 3 && fits; ++i) fits = l->in[i].dtype == PSK_BF16 && aligned16(L.in[i].p) && L.in[i].stride[no - 1] == 1;
+        fits = fits && aligned16(L.out.p) && L.out.stride[no - 1] == 1;
+        // x and the result: whole rows of 2·rot one after the other; the tables: [seq, rot], broadcast elsewhere
+        int64_t expect = 1, rows = 1;
+        for (int a = no - 1; a >= 0 && fits; --a) {
+            fits = L.in[0].stride[a] == expect && L.out.stride[a] == expect;
+            const int64_t tab = a == no - 1 ? 1 : a == no - 3 ? rot : 0;
+            fits = fits && L.in[1].stride[a] == tab && L.in[2].stride[a] == tab;
+            expect *= L.dims[a];
+            if (a <= no - 3) rows *= L.dims[a];
+        }
+        if (!fits) { rc = fail(e, PSK_E7005, nm + ": the merged rotation runs on contiguous bf16 rows with bf16 tables over (seq, rot)"); break; }
+        RopeParams R;
+        R.x = (const uint16_t *)L.in[0].p; R.c = (const uint16_t *)L.in[1].p; R.s = (const uint16_t *)L.in[2].p;
+        R.out = (uint16_t *)const_cast<void *>(L.out.p); R.rows = rows; R.seq = (int32_t)T; R.rotv = (int32_t)(rot / 8);
+        k_rope_bf16<<<grid_for(e, rows * (rot / 8), 256, 8), 256, 0, e->stream>>>(R);
         e->kernels += 1;
         break;
     }

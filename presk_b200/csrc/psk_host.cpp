@@ -465,7 +465,9 @@ struct psk_host {
         for (size_t a = 0; a < sstride.size(); ++a) o.scale_stride[a] = sstride[a];
     }
 
-    void run(psk_launch &l, const std::string &name, const std::vector<const Tensor *> &ins, const Tensor &out)
+    // `may_refuse`: a merged launch the executor may decline (E7005) before doing anything; the caller
+    // then issues the launches it stands for. Returns whether it ran.
+    bool run(psk_launch &l, const std::string &name, const std::vector<const Tensor *> &ins, const Tensor &out, bool may_refuse = false)
     {
         l.name = name.c_str();
         l.order = rz.order;
@@ -476,10 +478,13 @@ struct psk_host {
         table.push_back(out.ptr());
         for (auto *t : ins)
             if (t->dtype == PSK_I8 && !t->affine) table.push_back((uint8_t *)t->scales->p + t->soff * 4);
-        check(vt->run(vt->self, &l, table.data()), name.c_str());
+        int rc = vt->run(vt->self, &l, table.data());
+        if (rc == PSK_E7005 && may_refuse) return false;
+        check(rc, name.c_str());
         launches += 1;
         if (logging) { log += name; log += '\n'; }
         if (calibrating && !out.is_index && out.numel() > 0 && !current_site.empty()) observe(out);
+        return true;
     }
 
     // Folds a launch's output into its site's magnitudes.
@@ -797,7 +802,7 @@ struct psk_host {
     // v [batch, seq2, groups, hd], result [batch, seq, groups, per, hd] as the last ein would lay it out.
     // `sites`: scores, scaled scores, softmax, result. While magnitudes are being measured the launches
     // stay apart, since the three sites in between are never stored by the fused one.
-    Tensor attention_blockwise(const std::vector<std::string> &sites, const Tensor &q, const Tensor &k, const Tensor &v, const Tensor &rt, const Tensor *mask)
+    Tensor attention_blockwise(const std::vector<std::string> &sites, const Tensor &q, const Tensor &k, const Tensor &v, const Tensor &rt, const Tensor *mask, bool *ran)
     {
         const int64_t B = q.axes[0].len, G = q.axes[1].len, P = q.axes[2].len, T = q.axes[3].len, HD = q.axes[4].len, T2 = k.axes[2].len;
         int d_mid[3];
@@ -830,7 +835,7 @@ struct psk_host {
         }
         view(out, {0, 3, 1, 2, 4}, 6, st, ss);
         set_operand(l.out, out, st, {});
-        run(l, "attention[blockwise]", ins, out);
+        *ran = run(l, "attention[blockwise]", ins, out, true);
         return out;
     }
 
@@ -1136,6 +1141,33 @@ struct psk_host {
     Tensor llama_rmsnorm(const Tensor &gamma, const Tensor &x)
     {
         const std::string f = "RMSNorm.apply";
+        if (rz.merged_launches && rz.order == PSK_ORDER_DEVICE && !calibrating && !x.affine) {
+            bool plain = true;
+            for (auto site : {"/%2", "/%3", "/%5", "/%7", "/%10"}) plain = plain && !rz.scaled.count(f + site);
+            if (plain) {
+                // the four launches below as one, when the executor takes it (PSK_OP_RMSNORM: their bits)
+                Tensor eps = scalar(f + "/%5", 1e-5);
+                const int d10 = site_dtype(f + "/%10");
+                Tensor out = fresh(x.axes, d10);
+                psk_launch l;
+                memset(&l, 0, sizeof l);
+                l.op = PSK_OP_RMSNORM;
+                l.dtype = d10;
+                l.iparam[0] = x.axes.back().len;
+                l.iparam[1] = rz.dtype_at(f + "/%2"); l.iparam[2] = rz.dtype_at(f + "/%3"); l.iparam[3] = rz.dtype_at(f + "/%7");
+                set_space(l, x.axes, {});
+                set_operand(l.in[0], x, x.strides(), {});
+                set_operand(l.in[1], eps, {}, {});
+                std::vector<int> map;
+                if (align(gamma.axes, x.axes, map)) {
+                    std::vector<int64_t> st, ss;
+                    view(gamma, map, (int)x.axes.size(), st, ss);
+                    set_operand(l.in[2], gamma, st, ss);
+                    set_operand(l.out, out, out.strides(), {});
+                    if (run(l, "rmsnorm[merged]", {&x, &eps, &gamma}, out, true)) return out;
+                }
+            }
+        }
         Tensor x2 = binary(f + "/%2", PSK_MUL, x, x);
         Tensor ms = reduce_axis(f + "/%3", PSK_REDUCE_MEAN, "model", x2);
         Tensor eps = scalar(f + "/%5", 1e-5);
@@ -1188,9 +1220,29 @@ struct psk_host {
                 if (hit == rope_tables.end()) hit = rope_tables.emplace(key, std::make_pair(unary(f + "/%5", PSK_COS, phi), unary(f + "/%6", PSK_SIN, phi))).first;
                 const Tensor &c = hit->second.first, &s = hit->second.second;
                 Tensor cat = fresh_at(f + "/%13", p.axes);
-                Tensor lo = slice_view("pair", 0, 1, cat), hi = slice_view("pair", 1, 2, cat);
-                fused(f + "/%9", {Bn(PSK_MUL, 0, 1), Bn(PSK_MUL, 2, 3), Bn(PSK_SUB, S(0), S(1))}, {&x0, &c, &x1, &s}, "", &lo);
-                fused(f + "/%12", {Bn(PSK_MUL, 0, 1), Bn(PSK_MUL, 2, 3), Bn(PSK_ADD, S(0), S(1))}, {&x1, &c, &x0, &s}, "", &hi);
+                bool one = false;
+                if (d9 == dx && c.dtype == dx && s.dtype == dx && !c.affine && !s.affine && p.vstrides.empty()) {
+                    // both halves in one launch (PSK_OP_ROPE), when the executor takes it
+                    psk_launch l;
+                    memset(&l, 0, sizeof l);
+                    l.op = PSK_OP_ROPE;
+                    l.dtype = site_dtype(f + "/%13");
+                    set_space(l, p.axes, {});
+                    const int na = (int)p.axes.size();
+                    set_operand(l.in[0], p, p.strides(), {});
+                    std::vector<int64_t> st(na, 0), ss;
+                    st[na - 3] = c.axes[1].len; st[na - 1] = 1;
+                    set_operand(l.in[1], c, st, {});
+                    set_operand(l.in[2], s, st, {});
+                    set_operand(l.out, cat, cat.strides(), {});
+                    one = c.axes.size() == 2 && c.axes[0].len == p.axes[na - 3].len && c.axes[1].len == p.axes[na - 1].len
+                        && run(l, "rope[merged]", {&p, &c, &s}, cat, true);
+                }
+                if (!one) {
+                    Tensor lo = slice_view("pair", 0, 1, cat), hi = slice_view("pair", 1, 2, cat);
+                    fused(f + "/%9", {Bn(PSK_MUL, 0, 1), Bn(PSK_MUL, 2, 3), Bn(PSK_SUB, S(0), S(1))}, {&x0, &c, &x1, &s}, "", &lo);
+                    fused(f + "/%12", {Bn(PSK_MUL, 0, 1), Bn(PSK_MUL, 2, 3), Bn(PSK_ADD, S(0), S(1))}, {&x1, &c, &x0, &s}, "", &hi);
+                }
                 Tensor m = merge(cat, "pair", "rot");
                 m.axes.back().name = "hd";
                 return m;
@@ -1228,14 +1280,20 @@ struct psk_host {
         vd.axes.back().name = "kvout";
         Tensor v = split(vd, "kvout", {{"groups", G}, {"hd", HD}});
         Tensor o;
+        bool fused_attention = false;
+        Tensor hdr, rt;
         if (rz.blockwise_attention && !calibrating) {
-            Tensor hdr = scalar(f + "/%18", (double)HD);
-            Tensor rt = unary(f + "/%19", PSK_SQRT, hdr);
-            o = attention_blockwise({f + "/%16", f + "/%20", f + "/%21", f + "/%22"}, q, k, v, rt, &mask);
-        } else {
+            // the root is computed before the scores here and after them below; neither reads the other
+            hdr = scalar(f + "/%18", (double)HD);
+            rt = unary(f + "/%19", PSK_SQRT, hdr);
+            o = attention_blockwise({f + "/%16", f + "/%20", f + "/%21", f + "/%22"}, q, k, v, rt, &mask, &fused_attention);
+        }
+        if (!fused_attention) {
             Tensor se = ein(f + "/%16", {"batch", "groups", "per", "seq", "seq2"}, {{"batch", "groups", "per", "seq", "hd"}, {"batch", "groups", "seq2", "hd"}}, {&q, &k});
-            Tensor hdr = scalar(f + "/%18", (double)HD);
-            Tensor rt = unary(f + "/%19", PSK_SQRT, hdr);
+            if (!rt.st) {
+                hdr = scalar(f + "/%18", (double)HD);
+                rt = unary(f + "/%19", PSK_SQRT, hdr);
+            }
             Tensor s = binary(f + "/%20", PSK_DIV, se, rt);
             Tensor a = softmax(f + "/%21", "seq2", s, &mask);
             o = ein(f + "/%22", {"batch", "seq", "groups", "per", "hd"}, {{"batch", "groups", "per", "seq", "seq2"}, {"batch", "seq2", "groups", "hd"}}, {&a, &v});

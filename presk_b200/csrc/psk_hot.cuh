@@ -277,6 +277,29 @@ __global__ void __launch_bounds__(128, 3) k_ew_bf16(const __grid_constant__ EwPa
 // executor compares them) and whose operands are all bf16 takes this kernel.
 enum EwProg { EW_ADD = 0, EW_SUB, EW_MUL, EW_DIV, EW_DIV_MUL, EW_SILU, EW_MUL_MUL_SUB, EW_MUL_MUL_ADD, EW_SILU_MUL, EW_NPROG };
 
+// a / b given r = the correctly rounded 1 / b (Markstein's correction): the quotient to nearest by one
+// multiplication and two fused operations. That is the division's own result whenever no intermediate leaves
+// the normal range, which holds when both exponents lie in [2^-55, 2^55]: the quotient is then within 2^+-111,
+// the remainder is exact and nothing overflows. Outside (zero, tiny, huge, infinite or NaN), the division.
+PSK_DEV bool div_by_in_range(float x) { return ((f32_bits(x) >> 23) & 0xffu) - 72u <= 110u; }
+
+PSK_DEV float div_by(float a, float b, float r)
+{
+    if (!div_by_in_range(a) || !div_by_in_range(b)) return __fdiv_rn(a, b);
+    const float q = __fmul_rn(a, r);
+    const float rem = __fmaf_rn(-b, q, a);
+    return __fmaf_rn(rem, r, q);
+}
+
+// The same with the divisor's test made once by the caller (one divisor, many numerators).
+PSK_DEV float div_by_checked(float a, float b, float r, bool b_in_range)
+{
+    if (!b_in_range || !div_by_in_range(a)) return __fdiv_rn(a, b);
+    const float q = __fmul_rn(a, r);
+    const float rem = __fmaf_rn(-b, q, a);
+    return __fmaf_rn(rem, r, q);
+}
+
 template <int PROG>
 PSK_DEV float ew_eval(float a, float b, float c, float d)
 {
@@ -305,7 +328,7 @@ PSK_DEV int64_t ew_row_offset(const EwParams &E, uint32_t r, int64_t s1, int64_t
 }
 
 template <int PROG, int UNR>
-__global__ void __launch_bounds__(256, 2) k_ew_prog(const __grid_constant__ EwParams E)
+__global__ void __launch_bounds__(256, EwArity<PROG>::value >= 4 ? 2 : 3) k_ew_prog(const __grid_constant__ EwParams E)
 {
     constexpr int NIN = EwArity<PROG>::value;
     const uint32_t total = E.rows * E.colv;
@@ -351,6 +374,13 @@ __global__ void __launch_bounds__(256, 2) k_ew_prog(const __grid_constant__ EwPa
         for (int u = 0; u < UNR; ++u) {
             if (idx0 + u * stride >= total) break;
             uint32_t out[4];
+            // a divisor that is one value for the vector (a row's root): its reciprocal once, then a
+            // multiplication and a correction an element instead of a division
+            constexpr bool DIVIDES = PROG == EW_DIV || PROG == EW_DIV_MUL;
+            const bool by_scalar = DIVIDES && E.cs[1] == 0;
+            float sdiv = 0.0f, srcp = 0.0f;
+            bool sdiv_ok = false;
+            if (DIVIDES && by_scalar) { sdiv = bits_f32(raw[u][1].x << 16); srcp = __frcp_rn(sdiv); sdiv_ok = div_by_in_range(sdiv); }
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 float lo[4], hi[4];
@@ -364,7 +394,15 @@ __global__ void __launch_bounds__(256, 2) k_ew_prog(const __grid_constant__ EwPa
                         lo[i] = hi[i] = 0.0f;
                     }
                 }
-                out[q] = pack_bf16x2(ew_eval<PROG>(lo[0], lo[1], lo[2], lo[3]), ew_eval<PROG>(hi[0], hi[1], hi[2], hi[3]));
+                if (DIVIDES && by_scalar) {
+                    float ql = div_by_checked(lo[0], sdiv, srcp, sdiv_ok), qh = div_by_checked(hi[0], sdiv, srcp, sdiv_ok);
+                    if (PROG == EW_DIV_MUL) { ql = __fmul_rn(ql, lo[2]); qh = __fmul_rn(qh, hi[2]); }
+                    out[q] = pack_bf16x2_hw(ql, qh);
+                } else {
+                    // every program ends in an arithmetic operation, whose NaN is the device's canonical one:
+                    // the hardware's conversion and the reference's formula make the same bf16 of it
+                    out[q] = pack_bf16x2_hw(ew_eval<PROG>(lo[0], lo[1], lo[2], lo[3]), ew_eval<PROG>(hi[0], hi[1], hi[2], hi[3]));
+                }
             }
             *reinterpret_cast<uint4 *>((uint16_t *)E.out + ew_row_offset(E, rr[u], E.ors, E.ors0) + cc[u]) = make_uint4(out[0], out[1], out[2], out[3]);
         }
@@ -431,6 +469,129 @@ __global__ void __launch_bounds__(1024, 1) k_ew_lut(const __grid_constant__ EwPa
 }
 
 // ---------------------------------------------------------------------------
+// PSK_OP_ROPE for bf16: a thread takes eight rotary positions of one row and
+// writes both halves, so x is read once and the result written once, both as
+// whole contiguous rows. Products are rounded to f32 before they are added
+// (no fused multiply-add), the sums rounded once to bf16.
+// ---------------------------------------------------------------------------
+struct RopeParams {
+    const uint16_t *x, *c, *s;
+    uint16_t *out;
+    int64_t rows;      // every leading axis and seq
+    int32_t seq, rotv; // rotv = rot / 8
+};
+
+__global__ void __launch_bounds__(256, 4) k_rope_bf16(const __grid_constant__ RopeParams P)
+{
+    const int64_t total = P.rows * P.rotv;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    const int rot = P.rotv * 8;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+        const int64_t row = idx / P.rotv;
+        const int cv = (int)(idx - row * P.rotv) * 8;
+        const int t = (int)(row % P.seq);
+        const uint16_t *xr = P.x + row * 2 * rot + cv;
+        const uint4 a = *reinterpret_cast<const uint4 *>(xr), b = *reinterpret_cast<const uint4 *>(xr + rot);
+        const uint4 c = *reinterpret_cast<const uint4 *>(P.c + (int64_t)t * rot + cv), s = *reinterpret_cast<const uint4 *>(P.s + (int64_t)t * rot + cv);
+        const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w}, cw[4] = {c.x, c.y, c.z, c.w}, sw[4] = {s.x, s.y, s.z, s.w};
+        uint32_t o0[4], o1[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float a0 = bits_f32(aw[q] << 16), a1 = bits_f32(aw[q] & 0xffff0000u), b0 = bits_f32(bw[q] << 16), b1 = bits_f32(bw[q] & 0xffff0000u);
+            const float c0 = bits_f32(cw[q] << 16), c1 = bits_f32(cw[q] & 0xffff0000u), s0 = bits_f32(sw[q] << 16), s1 = bits_f32(sw[q] & 0xffff0000u);
+            o0[q] = pack_bf16x2_hw(__fsub_rn(__fmul_rn(a0, c0), __fmul_rn(b0, s0)), __fsub_rn(__fmul_rn(a1, c1), __fmul_rn(b1, s1)));
+            o1[q] = pack_bf16x2_hw(__fadd_rn(__fmul_rn(b0, c0), __fmul_rn(a0, s0)), __fadd_rn(__fmul_rn(b1, c1), __fmul_rn(a1, s1)));
+        }
+        uint16_t *orow = P.out + row * 2 * rot + cv;
+        *reinterpret_cast<uint4 *>(orow) = make_uint4(o0[0], o0[1], o0[2], o0[3]);
+        *reinterpret_cast<uint4 *>(orow + rot) = make_uint4(o1[0], o1[1], o1[2], o1[3]);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// PSK_OP_RMSNORM under PSK_ORDER_DEVICE, bf16 rows: a warp a row, the row read
+// once into registers. The bits are those of the four launches it stands for,
+// as this executor runs them under the same order:
+//   x*x rounded to bf16 (the square's site);
+//   their f32 sum in k_reduce_rows_tree's grouping (lane l adds the elements of
+//   vectors l, l+32, .. in index order, then the xor tree), divided by n;
+//   sqrt(mean + eps) in f32, rounded to bf16 at the last group's edge;
+//   x / root * gamma, the division by the root's correctly rounded reciprocal
+//   with one correction (k_ew_prog's), rounded to bf16.
+// NV = vectors of eight a lane = n / 256.
+// ---------------------------------------------------------------------------
+struct RmsParams {
+    const uint16_t *x, *gamma;
+    const void *eps;
+    uint16_t *out;
+    int64_t x_row, out_row; // element strides from row to row
+    int64_t rows;
+    int32_t n, eps_dtype;
+};
+
+template <int NV>
+__global__ void __launch_bounds__(256, 4) k_rmsnorm_rows(const __grid_constant__ RmsParams P)
+{
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    const float eps = load_real(P.eps, P.eps_dtype, 0); // widened exactly: the root's group computes in f32
+    const float nf = (float)(double)P.n;
+    constexpr int G = NV < 4 ? NV : 4; // vectors loaded before any is used
+    for (int64_t row = warp; row < P.rows; row += nwarps) {
+        const uint16_t *xr = P.x + row * P.x_row + lane * 8;
+        // pass 1: the sum of the rounded squares, vector by vector in index order. The row is not kept in
+        // registers (that would leave one block an SM); the second pass finds it in the L1 or the L2.
+        float acc = 0.0f;
+#pragma unroll 1
+        for (int j0 = 0; j0 < NV; j0 += G) {
+            uint4 v[G];
+#pragma unroll
+            for (int j = 0; j < G; ++j) v[j] = *reinterpret_cast<const uint4 *>(xr + (j0 + j) * 256);
+#pragma unroll
+            for (int j = 0; j < G; ++j) {
+                const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float lo = bits_f32(w[q] << 16), hi = bits_f32(w[q] & 0xffff0000u);
+                    const uint32_t sq = pack_bf16x2_hw(__fmul_rn(lo, lo), __fmul_rn(hi, hi));
+                    acc = __fadd_rn(acc, bits_f32(sq << 16));
+                    acc = __fadd_rn(acc, bits_f32(sq & 0xffff0000u));
+                }
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, o));
+        const float ms = __fdiv_rn(acc, nf);
+        const float root = bits_f32(pack_bf16x2_hw(__fsqrt_rn(__fadd_rn(ms, eps)), 0.0f) << 16);
+        const float rr = __frcp_rn(root);
+        const bool ok = div_by_in_range(root);
+        uint16_t *orow = P.out + row * P.out_row + lane * 8;
+        const uint16_t *gr = P.gamma + lane * 8;
+#pragma unroll 1
+        for (int j0 = 0; j0 < NV; j0 += G) {
+            uint4 v[G], g[G];
+#pragma unroll
+            for (int j = 0; j < G; ++j) {
+                v[j] = *reinterpret_cast<const uint4 *>(xr + (j0 + j) * 256);
+                g[j] = *reinterpret_cast<const uint4 *>(gr + (j0 + j) * 256);
+            }
+#pragma unroll
+            for (int j = 0; j < G; ++j) {
+                const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+                const uint32_t gw[4] = {g[j].x, g[j].y, g[j].z, g[j].w};
+                uint32_t o[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float lo = div_by_checked(bits_f32(w[q] << 16), root, rr, ok), hi = div_by_checked(bits_f32(w[q] & 0xffff0000u), root, rr, ok);
+                    o[q] = pack_bf16x2_hw(__fmul_rn(lo, bits_f32(gw[q] << 16)), __fmul_rn(hi, bits_f32(gw[q] & 0xffff0000u)));
+                }
+                *reinterpret_cast<uint4 *>(orow + (j0 + j) * 256) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
 // Softmax over a contiguous axis under PSK_ORDER_DEVICE: a warp a row, the
 // row held in shared memory between the passes, the exponentials computed
 // once (the bits of computing them twice), the maximum and the sum shuffle
@@ -438,19 +599,7 @@ __global__ void __launch_bounds__(1024, 1) k_ew_lut(const __grid_constant__ EwPa
 // exponentiated; the refused tail is written as zeros, which is what the
 // reference's selections give it (lower.rs:1368-1419).
 // ---------------------------------------------------------------------------
-// a / b for positive finite b, given r = the correctly rounded 1 / b: the
-// quotient to nearest by one multiplication and two fused operations
-// (Markstein's correction), which is the division's own result whenever no
-// intermediate leaves the normal range; outside it, the division itself.
-PSK_DEV float div_by(float a, float b, float r)
-{
-    const uint32_t ea = (f32_bits(a) >> 23) & 0xffu;
-    if (ea < 40u || ea > 210u) return __fdiv_rn(a, b); // zero, tiny, huge, infinite or NaN numerator
-    const float q = __fmul_rn(a, r);
-    const float rem = __fmaf_rn(-b, q, a);
-    return __fmaf_rn(rem, r, q);
-}
-
+// The division by the row's sum is `div_by` above.
 template <int WARPS>
 __global__ void __launch_bounds__(WARPS * 32, 6) k_softmax_rows_smem(const __grid_constant__ DevLaunch L)
 {

@@ -405,3 +405,32 @@ def test_tabulated_silu_is_the_exact_one(cuda, oracle, with_mul):
     nan = ((a & 0x7fff) > 0x7f80) & ((b & 0x7fff) > 0x7f80)
     bad = np.nonzero((a != b) & ~nan)[0]
     assert bad.size == 0, f"{bad.size} differ; first: code {g.ravel()[bad[0]]:#x}: {a[bad[0]]:#x} vs {b[bad[0]]:#x}"
+
+
+@pytest.mark.parametrize("with_mul", [False, True])
+def test_division_by_a_row_scalar_is_the_ieee_division(cuda, oracle, with_mul):
+    """bf16 rows divided by one f32 value a row (a norm's root, rounded to bf16 at the kernel's edge), then
+    optionally scaled by a bf16 vector: the program kernel divides by the reciprocal with one correction.
+    Every bf16 code as a numerator against 4 096 divisors of every magnitude: the oracle's bits."""
+    rows, cols = 4096, 65536 // 16
+    rng = np.random.default_rng(31)
+    codes = np.arange(65536, dtype=np.uint16)
+    a = np.stack([np.roll(codes, int(s))[:cols] for s in rng.integers(0, 65536, rows)])
+    a[:16] = codes.reshape(16, cols)
+    div = (rng.standard_normal(rows) * 10.0 ** rng.integers(-30, 30, rows)).astype(np.float32)
+    div[:8] = [1.0, -3.0, 11.3125, 2.0**-100, 2.0**100, 1e-38, 3e38, 0.1]
+    gamma = bf16_of(oracle, rng.standard_normal(cols) + 1.0)
+    l = launch_desc(abi.OP_FUSED, abi.BF16, [rows, cols])
+    l.n_inputs, l.n_steps = (3, 2) if with_mul else (2, 1)
+    l.steps[0].prim, l.steps[0].nargs, l.steps[0].src[0], l.steps[0].src[1] = abi.DIV, 2, 0, 1
+    if with_mul:
+        l.steps[1].prim, l.steps[1].nargs, l.steps[1].src[0], l.steps[1].src[1] = abi.MUL, 2, -1, 2
+        set_operand(l.inputs[2], abi.BF16, [cols], [1])
+    set_operand(l.inputs[0], abi.BF16, [rows, cols], [0, 1])
+    set_operand(l.inputs[1], abi.F32, [rows], [0])
+    set_operand(l.out, abi.BF16, [rows, cols], [0, 1])
+    got, want, _, _ = run_both(cuda, oracle, l, [a, div, gamma] if with_mul else [a, div], rows * cols * 2)
+    x, y = got.view(np.uint16), want.view(np.uint16)
+    nan = ((x & 0x7fff) > 0x7f80) & ((y & 0x7fff) > 0x7f80)
+    bad = np.nonzero((x != y) & ~nan)[0]
+    assert bad.size == 0, f"{bad.size} differ; first: {a.ravel()[bad[0]]:#x} / {div[bad[0] // cols]!r}: {x[bad[0]]:#x} vs {y[bad[0]]:#x}"

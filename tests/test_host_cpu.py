@@ -191,12 +191,14 @@ def test_merged_launches_keep_every_bit(oracle):
     ids = np.random.default_rng(9).integers(0, c["V"], size=(2, 16), dtype=np.int64)
     for default in ("f32", "bf16"):
         outs, logs = [], []
-        for order in ({"kind": "sequential"}, {"kind": "sequential", "launches": "merged"}):
+        for order in ({"kind": "sequential"}, {"kind": "sequential", "launches": "merged"}, {"kind": "device", "launches": "merged"}):
             h = models.give(Host(oracle.vtable(), {"default": default, "order": order}).prepare("llama", **c), p)
             h.set_logging(True)
             outs.append(h.call("apply", [ids], (2, 16, c["V"])))
             outs.append(h.call("apply", [ids], (2, 16, c["V"])))  # a second call: nothing kept from the first
             logs.append(h.launch_log())
+        # under the device order the norm's four launches are offered as one too (the oracle runs the four)
+        assert logs[2].count("rmsnorm[merged]") == 2 * c["L"] + 1 and "mean axis model" not in logs[2]
         for o in outs[1:]:
             assert np.array_equal(outs[0].view(np.uint32), o.view(np.uint32))
         assert not any(n.startswith("slice") or n.startswith("concat") for n in logs[1])
