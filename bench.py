@@ -47,6 +47,12 @@ WORKLOADS = {
 QUANTISED = ("blocks.attn.wq", "blocks.attn.wk", "blocks.attn.wv", "blocks.attn.wo", "blocks.ff.gate.w", "blocks.ff.up.w", "blocks.ff.down.w")
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel's heaviest frequent shape, from the
+# ncu capture summarised in profiles/k_gemm_tc_ffn_16384x11008x4096.md (bytes a launch; algorithmic bytes: 585 MB)
+GEMM_TRAFFIC = {"llama7b_prefill_b8_t2048": 907765248 + 347590144}
+GEMM_TRAFFIC_OF = "k_gemm_tc<256>, dot [16384, 4096] x [4096, 11008] (gate/up projections: 64 of a step's 225 contractions), one launch under ncu"
+
+
 def realization(paths, int8=False, attention="unfused", launches="reference"):
     """A solved-style mixed bf16/f32 assignment: bf16 storage, f32 where a sum's result is reused
     widely (the norms' mean and root, the logits and the loss); with `int8`, the projection and
@@ -411,7 +417,7 @@ def main():
             "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": int(ids_np.nbytes + y_np.nbytes), "d2h_bytes_per_step": 4},
             "gpu_launches": int(kernels_after - kernels_before),
             "clocks": clocks,
-            "roofline": {"bound": "tensor", "kernel": "k_gemm_tc", "achieved": achieved, "peak": tf_peak, "unit": "TFLOP/s", "frac": achieved / tf_peak, "traffic": None, "peak_source": peak_kind,
+            "roofline": {"bound": "tensor", "kernel": "k_gemm_tc", "achieved": achieved, "peak": tf_peak, "unit": "TFLOP/s", "frac": achieved / tf_peak, "traffic": GEMM_TRAFFIC.get(args.workload), "traffic_of": GEMM_TRAFFIC_OF if args.workload in GEMM_TRAFFIC else None, "peak_source": peak_kind,
                          "model_tflops": flops_per_token(consts, T) * B * T * args.steps / (ms * 1e-3) / 1e12, "hbm_peak_gbs": hbm_peak},
             "kernel_shares": shares,
             "loss": loss_all,

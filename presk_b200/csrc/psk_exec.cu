@@ -11,6 +11,7 @@
 #include <cuda_runtime.h>
 #include <algorithm>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <string>
@@ -344,6 +345,15 @@ int launch_tc(psk_exec *e, const psk_gemm &g, const void *a, const void *b, void
     P.m = g.m; P.n = g.n; P.k = g.k; P.batch = g.batch; P.batch_lo = g.batch_lo;
     P.tiles_m = (g.m + tc::BM - 1) / tc::BM;
     P.tiles_n = (g.n + bn - 1) / bn;
+    {
+        // a panel's columns of B (bn·k elements each) should stay in the L2 while A streams past them: a
+        // quarter of the L2 for them; at least 8 columns, all of them when that fits
+        static const long forced = getenv("PSK_GEMM_PANEL") ? atol(getenv("PSK_GEMM_PANEL")) : 0;
+        const int64_t col_bytes = (int64_t)bn * g.k * 2;
+        int64_t panel = std::max<int64_t>(8, (32ll << 20) / std::max<int64_t>(col_bytes, 1));
+        if (forced > 0) panel = forced;
+        P.panel = std::min<int64_t>(panel, P.tiles_n);
+    }
     P.c_row_lo_count = g.c_row_lo_count; P.c_row_lo = g.c_row_lo; P.c_row_hi = g.c_row_hi;
     P.c_col_lo_count = g.c_col_lo_count; P.c_col_hi = g.c_col_hi;
     P.c_lo = g.c_lo; P.c_hi = g.c_hi;

@@ -46,6 +46,7 @@ struct Params {
     int64_t m, n, k;
     int64_t batch, batch_lo;
     int64_t tiles_m, tiles_n;
+    int64_t panel; // tile-columns handed out together (tile_of)
     int64_t c_row_lo_count, c_row_lo, c_row_hi;
     int64_t c_col_lo_count, c_col_hi;
     int64_t c_lo, c_hi;
@@ -175,10 +176,11 @@ PSK_DEV void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
 // tile-columns, down every tile-row of a panel before the next panel: the
 // CTAs running at one time then share a few columns of B and a band of rows of
 // A that together fit the L2, instead of sweeping all of B for a few rows of A.
-constexpr int PANEL = 8;
-PSK_DEV void tile_of(int64_t r, int64_t tiles_m, int64_t tiles_n, int64_t &mt, int64_t &nt)
+// The panel's width is the host's choice (Params::panel): wide enough that A is not streamed from memory once a
+// panel more often than needed, narrow enough that the panel's columns of B stay in the L2.
+PSK_DEV void tile_of(int64_t r, int64_t tiles_m, int64_t tiles_n, int64_t PANEL, int64_t &mt, int64_t &nt)
 {
-    const int64_t per_panel = (int64_t)PANEL * tiles_m;
+    const int64_t per_panel = PANEL * tiles_m;
     const int64_t panel = r / per_panel, in_panel = r - panel * per_panel;
     const int64_t width = tiles_n - panel * PANEL < PANEL ? tiles_n - panel * PANEL : PANEL;
     mt = in_panel / width;
@@ -251,7 +253,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
             for (int64_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 const int64_t b = t / tiles_per_batch, r = t % tiles_per_batch;
                 int64_t mt, nt;
-                tile_of(r, P.tiles_m, P.tiles_n, mt, nt);
+                tile_of(r, P.tiles_m, P.tiles_n, P.panel, mt, nt);
                 const int m0 = (int)mt * BM, n0 = (int)nt * BN;
                 const int blo = (int)(b % P.batch_lo), bhi = (int)(b / P.batch_lo);
                 for (int kb = 0; kb < num_kb; ++kb) {
@@ -314,7 +316,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
         for (int64_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
             const int64_t b = t / tiles_per_batch, r = t % tiles_per_batch;
             int64_t mt, nt;
-            tile_of(r, P.tiles_m, P.tiles_n, mt, nt);
+            tile_of(r, P.tiles_m, P.tiles_n, P.panel, mt, nt);
             const int64_t m0 = mt * BM, n0 = nt * BN;
             const int64_t blo = b % P.batch_lo, bhi = b / P.batch_lo;
             ok = mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, P.status, 4u);

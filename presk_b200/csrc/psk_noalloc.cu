@@ -122,6 +122,7 @@ extern "C" int psk_gemm_noalloc(const psk_gemm *g, const void *a, const void *b,
     P.m = g->m; P.n = g->n; P.k = g->k; P.batch = g->batch; P.batch_lo = g->batch_lo;
     P.tiles_m = (g->m + tc::BM - 1) / tc::BM;
     P.tiles_n = (g->n + bn - 1) / bn;
+    P.panel = P.tiles_n < 8 ? P.tiles_n : 8;
     P.c_row_lo_count = g->c_row_lo_count; P.c_row_lo = g->c_row_lo; P.c_row_hi = g->c_row_hi;
     P.c_col_lo_count = g->c_col_lo_count; P.c_col_hi = g->c_col_hi;
     P.c_lo = g->c_lo; P.c_hi = g->c_hi;
