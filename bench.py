@@ -227,6 +227,19 @@ def microbench(args):
         nqb = t // 128
         fl = 4.0 * B * H * (nqb * (nqb + 1) / 2) * 128 * 128 * hd
         print(json.dumps({"micro": "attn", "shape": dims, "ms": ms, "TFLOP/s (causal blocks, one pass)": fl / ms / 1e9}))
+    elif args.micro == "e8m15":
+        # config 3's contraction: x[m, k] · w[k, n], every site e8m15, under the device order
+        m, n, k = dims[:3]
+        a = ex.upload(rng.integers(0, 256, size=m * k * 3, dtype=np.uint8) & np.tile(np.array([255, 255, 0x3f], np.uint8), m * k))
+        b = ex.upload(rng.integers(0, 256, size=n * k * 3, dtype=np.uint8) & np.tile(np.array([255, 255, 0x3f], np.uint8), n * k))
+        c = ex.alloc(m * n * 3)
+        l = launch_desc(abi.OP_CONTRACT, abi.E8M15, [m, n], [k], order=abi.ORDER_DEVICE)
+        l.n_inputs = 2
+        l.inputs[0].dtype, l.inputs[0].numel, l.inputs[0].stride[0], l.inputs[0].stride[2] = abi.E8M15, m * k, k, 1
+        l.inputs[1].dtype, l.inputs[1].numel, l.inputs[1].stride[1], l.inputs[1].stride[2] = abi.E8M15, n * k, 1, n
+        l.out.dtype, l.out.numel, l.out.stride[0], l.out.stride[1] = abi.E8M15, m * n, n, 1
+        ms = timed(lambda: ex.run(l, [a, b, c]), args.steps)
+        print(json.dumps({"micro": "e8m15", "shape": dims, "ms": ms, "TFLOP/s (2mnk)": 2.0 * m * n * k / ms / 1e9}))
     elif args.micro == "norm":
         # a norm's last group: x[rows, n] / root[rows] (f32) * gamma[n]
         rows, n = dims[:2]
@@ -273,7 +286,7 @@ def microbench(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--micro", default=None, choices=["gemm", "softmax", "ew", "attn", "norm"])
+    ap.add_argument("--micro", default=None, choices=["gemm", "softmax", "ew", "attn", "norm", "e8m15"])
     ap.add_argument("--shape", default="8192,8192,8192")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)

@@ -47,6 +47,11 @@ struct Params {
     int64_t batch, batch_lo;
     int64_t tiles_m, tiles_n;
     int64_t panel; // tile-columns handed out together (tile_of)
+    // e8m15 operands as two bf16 planes each (x = hi + lo exactly): the operands hold [hi | lo] along the summed
+    // axis, 2·split_k long, and the kernel's k runs over 4·split_k: quarter q reads A's plane q >> 1 and B's
+    // plane q & 1, so the four exact partial products hi·hi', hi·lo', lo·hi', lo·lo' add up in one accumulator.
+    // 0: the operands are what they are.
+    int64_t split_k;
     int64_t c_row_lo_count, c_row_lo, c_row_hi;
     int64_t c_col_lo_count, c_col_hi;
     int64_t c_lo, c_hi;
@@ -261,13 +266,19 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
                     if (!ok) break;
                     const uint32_t fb = full0 + 8 * stage;
                     mbar_expect_tx(fb, S::A_BYTES + S::B_BYTES);
-                    tma_load_4d(smem_u32(smem_a + stage * S::A_BYTES), &map_a, fb, kb * BK, m0, blo, bhi);
+                    int ka = kb * BK, kbb = kb * BK;
+                    if (P.split_k) {
+                        const int q = (int)(ka / P.split_k), r = (int)(ka - q * P.split_k);
+                        ka = (q >> 1) * (int)P.split_k + r;
+                        kbb = (q & 1) * (int)P.split_k + r;
+                    }
+                    tma_load_4d(smem_u32(smem_a + stage * S::A_BYTES), &map_a, fb, ka, m0, blo, bhi);
                     if (!P.b_n_major) {
-                        tma_load_4d(smem_u32(smem_b + stage * S::B_BYTES), &map_b, fb, kb * BK, n0, blo, bhi);
+                        tma_load_4d(smem_u32(smem_b + stage * S::B_BYTES), &map_b, fb, kbb, n0, blo, bhi);
                     } else {
 #pragma unroll
                         for (int c = 0; c < BN / 64; ++c)
-                            tma_load_4d(smem_u32(smem_b + stage * S::B_BYTES + c * 8192), &map_b, fb, n0 + c * 64, kb * BK, blo, bhi);
+                            tma_load_4d(smem_u32(smem_b + stage * S::B_BYTES + c * 8192), &map_b, fb, n0 + c * 64, kbb, blo, bhi);
                     }
                     if (++stage == S::STAGES) { stage = 0; phase ^= 1u; }
                 }

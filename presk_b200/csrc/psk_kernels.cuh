@@ -1120,3 +1120,24 @@ __global__ void __launch_bounds__(256) k_init_normal(void *dst, int to, int64_t 
 }
 
 } // namespace psk
+
+namespace psk {
+// An e8m15 matrix as two bf16 planes, x = hi + lo exactly: hi is x cut to bf16's eight significant bits, lo the
+// eight that remain (an infinity or a NaN goes to hi whole, lo zero; a remainder below bf16's least subnormal,
+// which only a value near 2^-126 has, is dropped). Element (r, c) of plane p is written at
+// p * plane_stride + r * row_stride + c, so the planes lie side by side along whichever axis is summed.
+__global__ void k_split_e8m15(const uint8_t *src, int64_t rows, int64_t cols, int64_t src_row, uint16_t *dst, int64_t row_stride, int64_t plane_stride)
+{
+    const int64_t total = rows * cols, step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step) {
+        const int64_t r = i / cols, c = i - r * cols;
+        const uint32_t code = load_e8m15(src, r * src_row + c);
+        const uint32_t hi = code >> 8;
+        uint32_t lo = 0;
+        if ((code & 0x7f8000u) != 0x7f8000u) lo = f32_bits(__fsub_rn(bits_f32(code << 8), bits_f32(hi << 16))) >> 16;
+        uint16_t *d = dst + r * row_stride + c;
+        d[0] = (uint16_t)hi;
+        d[plane_stride] = (uint16_t)lo;
+    }
+}
+} // namespace psk

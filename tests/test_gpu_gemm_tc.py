@@ -68,3 +68,55 @@ def test_gemm_output_types_round_once(cuda, oracle, in_dtype, out_dtype, tol):
     raw = oracle.convert(want.astype(np.float32), out_dtype)
     rounded = oracle.widen(raw, out_dtype, want.size).reshape(want.shape)
     assert np.mean(got != rounded) < 0.02
+
+
+@pytest.mark.parametrize("m,n,k,b_n_major", [(256, 256, 128, True), (384, 1000 // 8 * 8, 512, False), (1024, 1024, 1024, True)])
+def test_e8m15_contraction_on_tensor_cores(cuda, oracle, m, n, k, b_n_major):
+    """e8m15 operands under the device order: two bf16 planes each (x = hi + lo exactly), four partial products
+    summed in one f32 accumulator. The products are exact, so the result differs from the oracle's sequential
+    f32 sum only by the order of the additions: the f32 tolerance of the bf16 contractions, then one rounding
+    to e8m15 (2^-16 relative)."""
+    from presk_b200 import abi, launch_desc
+    rng = np.random.default_rng(m + n + k)
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    b = rng.standard_normal((k, n) if b_n_major else (n, k)).astype(np.float32)
+    a.ravel()[:4] = [0.0, -0.0, 1.0 + 2.0**-15, 3.0e-30]
+    a8, b8 = oracle.convert(a, abi.E8M15), oracle.convert(b, abi.E8M15)
+    l = launch_desc(abi.OP_CONTRACT, abi.E8M15, [m, n], [k], order=abi.ORDER_DEVICE)
+    l.n_inputs = 2
+    l.inputs[0].dtype, l.inputs[0].numel = abi.E8M15, m * k
+    l.inputs[0].stride[0], l.inputs[0].stride[2] = k, 1
+    l.inputs[1].dtype, l.inputs[1].numel = abi.E8M15, n * k
+    if b_n_major:
+        l.inputs[1].stride[1], l.inputs[1].stride[2] = 1, n
+    else:
+        l.inputs[1].stride[1], l.inputs[1].stride[2] = k, 1
+    l.out.dtype, l.out.numel = abi.E8M15, m * n
+    l.out.stride[0], l.out.stride[1] = n, 1
+    pa, pb, pc = cuda.upload(a8), cuda.upload(b8), cuda.alloc(m * n * 3)
+    cuda.set_profiling(True)
+    cuda.run(l, [pa, pb, pc])
+    cuda.sync()
+    assert any(rec[0] == "k_gemm_tc" for rec in cuda.profile()), "the launch did not reach the tensor-core kernel"
+    cuda.set_profiling(False)
+    got8 = cuda.download(pc, m * n * 3)
+    for p in (pa, pb, pc):
+        cuda.free(p)
+    want8 = np.zeros(m * n * 3, np.uint8)
+    ls = launch_desc(abi.OP_CONTRACT, abi.E8M15, [m, n], [k])
+    ls.n_inputs = 2
+    for i in range(2):
+        ls.inputs[i] = l.inputs[i]
+    ls.out = l.out
+    oracle.run(ls, [np.ascontiguousarray(a8), np.ascontiguousarray(b8), want8])
+
+    def widen(u8):
+        t = np.ascontiguousarray(u8).view(np.uint8).reshape(-1, 3).astype(np.uint32)
+        return ((t[:, 0] | (t[:, 1] << 8) | (t[:, 2] << 16)) << 8).view(np.float32)
+
+    got, want = widen(got8), widen(want8)
+    assert np.abs(got - want).max() <= 4e-6 * k + 1e-5 + 2.0**-15 * np.abs(want).max()
+    # and against the exact sum of the same e8m15 inputs in f64
+    af, bf = widen(a8).reshape(m, k).astype(np.float64), widen(b8).reshape(b.shape).astype(np.float64)
+    exact = (af @ bf if b_n_major else af @ bf.T).ravel()
+    assert np.abs(got - exact).max() <= 4e-6 * k + 1e-5 + 2.0**-15 * np.abs(exact).max()
