@@ -117,6 +117,8 @@ typedef enum {
     PSK_GELU, PSK_GELU_DERIV, PSK_RELU, PSK_HEAVISIDE, PSK_SIGN, PSK_SIGMOID,
     PSK_POW, /* by repeated multiplication, exponent in `imm` */
     PSK_REAL, /* identity on a real; an index read as a real */
+    PSK_DIV_N, /* x / n with n = `imm` a constant of the kernel in its arithmetic type (lower.rs:1257-1270 `mean_vjp`:
+                  the cotangent of a mean, broadcast, divided by the count) */
     PSK_ROUND /* the value as a store into the type `imm` (a psk_dtype without a guard: f32, bf16) and a load back
                  would leave it. No primitive of the reference: it stands where two of its groups, each with its
                  result stored in its site's type, run as one launch (realization `launches: merged`). */
@@ -140,7 +142,10 @@ typedef struct {
 typedef enum { PSK_ORDER_SEQUENTIAL = 0, PSK_ORDER_DEVICE = 1 } psk_order;
 
 typedef enum {
-    PSK_REDUCE_SUM = 0, PSK_REDUCE_MEAN = 1, PSK_REDUCE_SUMSQ = 2
+    PSK_REDUCE_SUM = 0, PSK_REDUCE_MEAN = 1, PSK_REDUCE_SUMSQ = 2,
+    PSK_REDUCE_SUM_STORED = 3 /* lower.rs:1670-1680 `sum_to`: the sum is kept in the output buffer, so every partial sum
+                                 is rounded to the output's type (and tested by the guard) before the next term is
+                                 added; terms in row-major order of the summed axes; never reassociated */
 } psk_reduce_kind;
 
 typedef enum {
@@ -390,6 +395,9 @@ typedef struct {
     int64_t dims[PSK_MAX_RANK];
 } psk_value;
 int psk_host_call(psk_host *h, const char *entry, const psk_value *inputs, int32_t n_inputs, void *out_host, int32_t out_dtype, int64_t out_capacity, int64_t *out_numel);
+/* A leaf of the last call's result when the entry returns a tree of the parameters' shape (a gradient,
+ * `grad(..)(θ)`: presk-rt/src/lib.rs `Value::Record`): `path` is the parameter's, as in psk_host_set_param. */
+int psk_host_result(psk_host *h, const char *path, void *out_host, int32_t out_dtype, int64_t out_capacity, int64_t *out_numel);
 
 /* The same with the inputs already on the executor (`inputs[i].data` is a
  * device pointer of the host's executor) and the result left there: what a

@@ -420,6 +420,7 @@ static float prim_unary(int prim, float x, int imm)
         for (int i = 1; i < imm; ++i) e = e * x;
         return e;
     }
+    case PSK_DIV_N: return x / (float)(double)imm; /* lower.rs:1266 `mean_vjp` */
     case PSK_ROUND: /* a site inside a merged group: rounded as its own launch would have stored it */
         return imm == PSK_BF16 ? psk_o_bf16_to_f32(psk_o_f32_to_bf16(x)) : imm == PSK_F16 ? psk_o_f16_to_f32(psk_o_f32_to_f16(x)) : imm == PSK_E8M15 ? psk_o_e8m15_to_f32(psk_o_f32_to_e8m15(x)) : x;
     default: return x;
@@ -871,6 +872,10 @@ static int psk_oracle_run_merged(const psk_launch *l, void *const *table, uint32
             for (int64_t c = 0; c < inner; ++c) {
                 float x = load_operand(&in[0], base + offset_of(l->in[0].stride, l->dims, no, ni, c), 0, kd, &ovf);
                 acc = acc + (l->kind == PSK_REDUCE_SUMSQ ? x * x : x);
+                if (l->kind == PSK_REDUCE_SUM_STORED) { /* lower.rs:1677 `sum_to`: the sum lives in the output buffer */
+                    ovf |= psk_o_overflows(l->out.dtype, acc);
+                    acc = prim_unary(PSK_ROUND, acc, l->out.dtype);
+                }
             }
             if (l->kind == PSK_REDUCE_MEAN) acc = acc / (float)(double)l->iparam[0];
             ovf |= store_real(outp, l->out.dtype, offset_of(l->out.stride, l->dims, 0, no, lin), acc);

@@ -52,3 +52,42 @@ void ref_indices(uint64_t seed, int split_of, int split_index, uint64_t bound, i
     presk_rng_from_seed(&r, key.b);
     for (size_t i = 0; i < n; ++i) out[i] = (int64_t)(presk_uniform01(&r) * (double)bound);
 }
+
+/* A key by its path from the master key of a seed: path[0] is the child among the entry's arguments
+ * (crates/presk-interp/src/run.rs:78 `master.split(n)`), the rest the children `split_key` takes inside
+ * the initializers (crates/presk-core/src/lower/init.rs). */
+static void key_at(uint64_t seed, const int *path, int npath, presk_key *out)
+{
+    presk_key k, c;
+    presk_key_from_seed(&k, seed);
+    for (int i = 0; i < npath; ++i) {
+        presk_key_split(&k, (uint64_t)path[i], &c);
+        k = c;
+    }
+    *out = k;
+}
+
+/* n uniform draws in [0, 1) of that key (key.rs:53-55), as `xavier_uniform` takes them (host.rs:1641-1657). */
+void ref_uniforms_at(uint64_t seed, const int *path, int npath, double *out, size_t n)
+{
+    presk_key k;
+    presk_rng r;
+    key_at(seed, path, npath, &k);
+    presk_rng_from_seed(&r, k.b);
+    for (size_t i = 0; i < n; ++i) out[i] = presk_uniform01(&r);
+}
+
+/* n standard normal draws of that key (key.rs:63-73). */
+void ref_normals_at(uint64_t seed, const int *path, int npath, double *out, size_t n)
+{
+    presk_key k;
+    presk_rng r;
+    key_at(seed, path, npath, &k);
+    presk_rng_from_seed(&r, k.b);
+    for (size_t i = 0; i < n; ++i) {
+        double u1;
+        do { u1 = presk_uniform01(&r); } while (!(u1 > 0.0));
+        double u2 = presk_uniform01(&r);
+        out[i] = sqrt(-2.0 * presk_log(u1)) * presk_cos(2.0 * 3.14159265358979323846 * u2);
+    }
+}

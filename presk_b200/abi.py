@@ -24,10 +24,10 @@ OK, E7001, E7005, E7006, E7007, E10001 = 0, 7001, 7005, 7006, 7007, 10001
 OP_FUSED, OP_CONTRACT, OP_REDUCE, OP_SOFTMAX, OP_XENT, OP_ARGMAX, OP_EMBED, OP_COPY, OP_IOTA, OP_CONVERT, OP_MAGNITUDE, OP_ATTENTION, OP_RMSNORM, OP_ROPE = range(14)
 
 # psk_prim
-(ADD, SUB, MUL, DIV, MAX, MIN, NEG, EXP, LOG, TANH, SQRT, SIN, COS, ABS, GELU, GELU_DERIV, RELU, HEAVISIDE, SIGN, SIGMOID, POW, REAL, ROUND) = range(23)
+(ADD, SUB, MUL, DIV, MAX, MIN, NEG, EXP, LOG, TANH, SQRT, SIN, COS, ABS, GELU, GELU_DERIV, RELU, HEAVISIDE, SIGN, SIGMOID, POW, REAL, DIV_N, ROUND) = range(24)
 
 ORDER_SEQUENTIAL, ORDER_DEVICE = 0, 1
-REDUCE_SUM, REDUCE_MEAN, REDUCE_SUMSQ = 0, 1, 2
+REDUCE_SUM, REDUCE_MEAN, REDUCE_SUMSQ, REDUCE_SUM_STORED = 0, 1, 2, 3
 IOTA_POSITIONS, IOTA_CAUSAL, IOTA_ONE_HOT, IOTA_FILL = 0, 1, 2, 3
 
 
@@ -110,6 +110,7 @@ PROTOTYPES = {
     "psk_host_set_param": (C.c_int, [C.c_void_p, C.c_char_p, C.c_void_p, C.c_int32, C.POINTER(C.c_int64), C.c_int32]),
     "psk_host_init_param": (C.c_int, [C.c_void_p, C.c_char_p, C.c_uint64, C.c_double, C.POINTER(C.c_int64), C.c_int32]),
     "psk_host_call": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(Value), C.c_int32, C.c_void_p, C.c_int32, C.c_int64, C.POINTER(C.c_int64)]),
+    "psk_host_result": (C.c_int, [C.c_void_p, C.c_char_p, C.c_void_p, C.c_int32, C.c_int64, C.POINTER(C.c_int64)]),
     "psk_host_call_device": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(Value), C.c_int32, C.POINTER(C.c_void_p), C.POINTER(C.c_int32), C.POINTER(C.c_int64)]),
     "psk_host_set_calibrating": (None, [C.c_void_p, C.c_int]),
     "psk_host_envelope": (C.c_char_p, [C.c_void_p]),

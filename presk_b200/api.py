@@ -197,6 +197,16 @@ class Host:
             raise PreskError(abi.E7001, f"the result has {n.value} elements, not {out.size}")
         return out
 
+    def result(self, path, shape, out_dtype=np.float32):
+        """A leaf of the last call's result when that is a tree (a gradient), by the parameter's path."""
+        out = np.empty(shape, dtype=out_dtype)
+        n = C.c_int64()
+        code = {np.dtype(np.float32): abi.F32, np.dtype(np.float64): abi.F64}[np.dtype(out_dtype)]
+        self._check(self.lib.psk_host_result(self.handle, path.encode(), out.ctypes.data, code, out.size, C.byref(n)))
+        if n.value != out.size:
+            raise PreskError(abi.E7001, f"the result `{path}` has {n.value} elements, not {out.size}")
+        return out
+
     def call_device(self, entry, inputs):
         """Backend::call with device inputs [(ptr, dtype, shape)]; returns (ptr, dtype, numel), queued."""
         vals, _ = self._values(inputs, device_ptrs=True)

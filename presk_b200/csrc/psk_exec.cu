@@ -904,8 +904,9 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
     }
     case PSK_OP_REDUCE: {
         e->last_kernel = "k_reduce";
-        if (device_order && L.n_outer == 0) k_reduce_all_tree<<<1, 1024, 0, e->stream>>>(L);
-        else if (device_order && L.n_inner == 1 && L.in[0].stride[L.n_outer] == 1 && L.inner >= 64 && (L.inner % 8 != 0 || vec8_operand(L.in[0], L.dims, L.n_outer + 1, false) ))
+        const bool may_regroup = device_order && L.kind != PSK_REDUCE_SUM_STORED; // sum_to rounds every partial sum
+        if (may_regroup && L.n_outer == 0) k_reduce_all_tree<<<1, 1024, 0, e->stream>>>(L);
+        else if (may_regroup && L.n_inner == 1 && L.in[0].stride[L.n_outer] == 1 && L.inner >= 64 && (L.inner % 8 != 0 || vec8_operand(L.in[0], L.dims, L.n_outer + 1, false) ))
             k_reduce_rows_tree<<<grid_for(e, L.total * 32, 256, 8), 256, 0, e->stream>>>(L);
         else k_reduce_seq<<<grid_for(e, L.total, 128, 16), 128, 0, e->stream>>>(L);
         e->kernels += 1;

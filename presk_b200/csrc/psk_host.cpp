@@ -370,7 +370,7 @@ bool result_axes(const Axes &a, const Axes &b, Axes &out)
 
 const char *prim_name(int p)
 {
-    static const char *n[] = {"add", "sub", "mul", "div", "max", "min", "neg", "exp", "log", "tanh", "sqrt", "sin", "cos", "abs", "gelu", "gelu_deriv", "relu", "heaviside", "sign", "sigmoid", "pow", "real", "round"};
+    static const char *n[] = {"add", "sub", "mul", "div", "max", "min", "neg", "exp", "log", "tanh", "sqrt", "sin", "cos", "abs", "gelu", "gelu_deriv", "relu", "heaviside", "sign", "sigmoid", "pow", "real", "div_n", "round"};
     return n[p];
 }
 
@@ -587,7 +587,9 @@ struct psk_host {
     }
 
     // ---- elementwise (lower.rs:309-372) -------------------------------------------
-    Tensor fused(const std::string &site, const std::vector<StepSpec> &steps, const std::vector<const Tensor *> &ins, const std::string &name_override = "", const Tensor *into = nullptr)
+    // `shape`: the result's axes when they are a template's and not the operands' own (mean_vjp broadcasts a
+    // cotangent into its template, lower.rs:1257-1270)
+    Tensor fused(const std::string &site, const std::vector<StepSpec> &steps, const std::vector<const Tensor *> &ins, const std::string &name_override = "", const Tensor *into = nullptr, const Axes *shape = nullptr)
     {
         // the result's axes: the steps' broadcasts replayed (host.rs:1117-1137)
         std::vector<Axes> shapes;
@@ -600,7 +602,7 @@ struct psk_host {
                 shapes.push_back(r);
             }
         }
-        Axes out_axes = shapes.back();
+        Axes out_axes = shape ? *shape : shapes.back();
         int d = site_dtype(site);
         if (into) {
             bool same = into->axes.size() == out_axes.size() && into->dtype == d && !into->affine && !rz.scaled.count(site);
@@ -1409,6 +1411,131 @@ struct psk_host {
         return reduce_all("loss/%6", PSK_REDUCE_MEAN, ce);
     }
 
+
+    // ===========================================================================
+    // examples/spec/mlp/mlp.psk: `mse` and `mse_grad`, the reverse-mode program that the reference's
+    // transformation makes of it (crates/presk-core/tests/snapshots/ad__ad_mlp.snap gives every function
+    // and let number below). hidden = 4·D. A gradient is a tree of the parameters' shape: its leaves
+    // are left in `results` under the parameters' paths.
+    // ===========================================================================
+    std::map<std::string, Tensor> results;
+
+    // zeros_like (host.rs:1506): a buffer of zeros of the leaf's shape, made by the host, no launch
+    Tensor zeros(const std::string &site, const Axes &axes)
+    {
+        int d = site_dtype(site);
+        Tensor out = fresh(axes, d);
+        std::vector<uint8_t> z((size_t)std::max<int64_t>(1, out.numel()) * elem_bytes(d), 0);
+        check(vt->upload(vt->self, out.ptr(), z.data(), z.size()), "zeros_like");
+        return out;
+    }
+
+    // lower.rs:1670-1680: x summed into the shape of `tmpl` (whose axes align into x's), the sum kept in the
+    // output buffer; the summed axes in x's order
+    Tensor sum_to(const std::string &site, const Tensor &x, const Tensor &tmpl)
+    {
+        std::vector<int> map;
+        if (!align(tmpl.axes, x.axes, map)) raise(PSK_E7001, "sum_to: cannot reduce " + show(x.axes) + " to " + show(tmpl.axes));
+        std::vector<int> pos(x.axes.size(), -1); // where each axis of x sits in the launch's space
+        for (size_t i = 0; i < map.size(); ++i) pos[map[i]] = (int)i;
+        std::vector<int64_t> inner;
+        int next = (int)map.size();
+        for (size_t a = 0; a < x.axes.size(); ++a)
+            if (pos[a] < 0) { pos[a] = next++; inner.push_back(x.axes[a].len); }
+        int d = site_dtype(site);
+        Tensor out = fresh(tmpl.axes, d);
+        psk_launch l;
+        memset(&l, 0, sizeof l);
+        l.op = PSK_OP_REDUCE;
+        l.dtype = d;
+        l.kind = PSK_REDUCE_SUM_STORED;
+        set_space(l, tmpl.axes, inner);
+        std::vector<int64_t> st, ss;
+        view(x, pos, next, st, ss);
+        set_operand(l.in[0], x, st, ss);
+        set_operand(l.out, out, contiguous(tmpl.axes), {});
+        run(l, "sum_to", {&x}, out);
+        return out;
+    }
+
+    struct LinearGrad { Tensor w, b, x; };
+
+    // Linear.apply.bwd: %0 θ, %1 x, %2 ct; %8 sum_to ct, b; %9 zeros_like θ; %11 dot_vjp_l ct, w; %12 dot_vjp_r x, ct;
+    // %13 zeros_like θ; %15 add of the two trees, leaf by leaf (w, then b).
+    LinearGrad spec_linear_bwd(const std::string &prefix, const Tensor &x, const Tensor &ct)
+    {
+        const std::string f = "Linear.apply.bwd";
+        const Tensor &w = param(prefix + ".w"), &b = param(prefix + ".b");
+        Tensor gb = sum_to(f + "/%8", ct, b);
+        Tensor zw = zeros(f + "/%9", w.axes);
+        // the names of the leading axes of ct, then the two of w
+        std::vector<std::string> lead, cts, xs;
+        for (size_t i = 0; i + 1 < ct.axes.size(); ++i) lead.push_back("x" + std::to_string(i));
+        cts = lead; cts.push_back("out");
+        xs = lead; xs.push_back("in");
+        std::vector<std::string> gx_axes = lead; gx_axes.push_back("in");
+        Tensor gx = ein(f + "/%11", gx_axes, {cts, {"in", "out"}}, {&ct, &w}, "dot_vjp_l");
+        for (size_t i = 0; i + 1 < x.axes.size(); ++i) gx.axes[i] = x.axes[i];
+        gx.axes.back() = x.axes.back();
+        Tensor gw = ein(f + "/%12", {"in", "out"}, {xs, cts}, {&x, &ct}, "dot_vjp_r");
+        gw.axes = w.axes;
+        Tensor zb = zeros(f + "/%13", b.axes);
+        LinearGrad g;
+        g.w = binary(f + "/%15", PSK_ADD, zw, gw);
+        g.b = binary(f + "/%15", PSK_ADD, gb, zb);
+        g.x = gx;
+        return g;
+    }
+
+    // MLP.apply.fwd: the result and the residuals (%3 before gelu, %4 after)
+    Tensor spec_mlp_fwd(const Tensor &x, Tensor *pre, Tensor *post, const std::string &fn)
+    {
+        Tensor h = linear("l1", x);
+        Tensor a = unary(fn + "/%4", PSK_GELU, h);
+        if (pre) *pre = h;
+        if (post) *post = a;
+        return linear("l2", a);
+    }
+
+    // mse: %3 ŷ, [%4 sub; %5 pow 2] one group, %6 mean
+    Tensor spec_mse(const Tensor &x, const Tensor &y)
+    {
+        Tensor yh = spec_mlp_fwd(x, nullptr, nullptr, "MLP.apply");
+        Tensor sq = fused("mse/%5", {Bn(PSK_SUB, 0, 1), U(PSK_POW, S(0), 2)}, {&yh, &y});
+        return reduce_all("mse/%6", PSK_REDUCE_MEAN, sq);
+    }
+
+    Tensor spec_mse_grad(const Tensor &x, const Tensor &y)
+    {
+        // mse_grad.lambda0.grad: %3 nat 1, %4 real: the cotangent of the loss
+        Tensor ct = scalar("mse_grad.lambda0.grad/%4", 1.0);
+        // mse.fwd: %7 MLP.apply.fwd, %9 sub
+        Tensor pre, post;
+        Tensor yh = spec_mlp_fwd(x, &pre, &post, "MLP.apply.fwd");
+        Tensor diff = binary("mse.fwd/%9", PSK_SUB, yh, y);
+        // mse.bwd: %8 mean_vjp ct, x; %10 real 2; [%11 pow 1 %5; %12 mul %10, %11; %13 mul %8, %12]; %15 sum_to %13, %4
+        const std::string f = "mse.bwd";
+        Tensor shaped = fresh(x.axes, site_dtype(f + "/%8")); // the template's shape only
+        Tensor g8 = fused(f + "/%8", {U(PSK_DIV_N, 0, (int)x.numel())}, {&ct}, "mean_vjp", nullptr, &shaped.axes);
+        Tensor two = scalar(f + "/%10", 2.0);
+        Tensor g13 = fused(f + "/%13", {U(PSK_POW, 0, 1), Bn(PSK_MUL, 1, S(0)), Bn(PSK_MUL, 2, S(1))}, {&diff, &two, &g8});
+        Tensor g15 = sum_to(f + "/%15", g13, yh);
+        // MLP.apply.bwd: %4, %5 residuals; %8 Linear.apply.bwd(l2, %5, ct); %11 zeros_like θ; [%13 gelu' %4; %14 mul %10, %13];
+        // %15 Linear.apply.bwd(l1, x, %14); %18 zeros_like θ; %20 add of the trees (l1.w, l1.b, l2.w, l2.b)
+        const std::string m = "MLP.apply.bwd";
+        LinearGrad g2 = spec_linear_bwd("l2", post, g15);
+        Tensor z1w = zeros(m + "/%11", param("l1.w").axes), z1b = zeros(m + "/%11", param("l1.b").axes);
+        Tensor g14 = fused(m + "/%14", {U(PSK_GELU_DERIV, 0), Bn(PSK_MUL, 1, S(0))}, {&pre, &g2.x});
+        LinearGrad g1 = spec_linear_bwd("l1", x, g14);
+        Tensor z2w = zeros(m + "/%18", param("l2.w").axes), z2b = zeros(m + "/%18", param("l2.b").axes);
+        results.clear();
+        results["l1.w"] = binary(m + "/%20", PSK_ADD, z1w, g1.w);
+        results["l1.b"] = binary(m + "/%20", PSK_ADD, z1b, g1.b);
+        results["l2.w"] = binary(m + "/%20", PSK_ADD, g2.w, z2w);
+        results["l2.b"] = binary(m + "/%20", PSK_ADD, g2.b, z2b);
+        return results["l1.w"];
+    }
+
     // x·w then a row LayerNorm: %0 θ, %1 x, %2 w; %3 dot; LayerNorm.apply on it.
     Tensor contract_ln(const Tensor &x, const Tensor &w)
     {
@@ -1563,6 +1690,9 @@ struct psk_host {
         } else if (model == "rmsnorm") {
             need(1);
             return rmsnorm_spec(param("γ"), in[0], 1e-6);
+        } else if (model == "mlp_spec") {
+            if (entry == "mse") { need(2); return spec_mse(in[0], in[1]); }
+            if (entry == "mse_grad") { need(2); return spec_mse_grad(in[0], in[1]); }
         } else if (model == "contract_ln") {
             need(2);
             return contract_ln(in[0], in[1]);
@@ -1579,6 +1709,7 @@ struct psk_host {
         std::vector<std::string> names;
         if (model == "llama" || model == "gpt") names = {"batch", "seq"};
         else if (model == "mlp") names = i == 0 ? std::vector<std::string>{"batch", "model"} : std::vector<std::string>{"batch"};
+        else if (model == "mlp_spec") names = {"batch", "model"};
         else if (model == "layernorm" || model == "rmsnorm") {
             // ℝ[..., model: D] with a prefix of named axes
             static const char *prefix[] = {"batch", "seq", "a2", "a3", "a4", "a5", "a6"};
@@ -1642,7 +1773,7 @@ int psk_host_prepare(psk_host *h, const char *model, const char *consts)
 {
     HOST_TRY(h, {
         h->model = model ? model : "";
-        static const char *known[] = {"llama", "gpt", "mlp", "layernorm", "rmsnorm", "contract_ln", "dense"};
+        static const char *known[] = {"llama", "gpt", "mlp", "mlp_spec", "layernorm", "rmsnorm", "contract_ln", "dense"};
         bool ok = false;
         for (auto k : known) ok |= h->model == k;
         if (!ok) raise(PSK_E7001, "no model `" + h->model + "`");
@@ -1771,6 +1902,28 @@ int psk_host_call_device(psk_host *h, const char *entry, const psk_value *inputs
         if (out) *out = (uint8_t *)h->last_result.ptr() + h->last_result.off * (int64_t)elem_bytes(h->last_result.dtype);
         if (out_dtype) *out_dtype = h->last_result.dtype;
         if (out_numel) *out_numel = h->last_result.numel();
+    });
+    return PSK_OK;
+}
+
+// A leaf of the last call's result when that is a tree (a gradient: one leaf a parameter, by the parameter's
+// path), read as f32 or f64 reals.
+int psk_host_result(psk_host *h, const char *path, void *out_host, int32_t out_dtype, int64_t out_capacity, int64_t *out_numel)
+{
+    HOST_TRY(h, {
+        auto it = h->results.find(path ? path : "");
+        if (it == h->results.end()) raise(PSK_E7001, std::string("the last call left no result `") + (path ? path : "") + "`");
+        const Tensor &r = it->second;
+        if (out_numel) *out_numel = r.numel();
+        if (r.numel() > out_capacity) raise(PSK_E7001, "the result has " + std::to_string(r.numel()) + " elements and the buffer holds " + std::to_string(out_capacity));
+        if (out_dtype != PSK_F32 && out_dtype != PSK_F64) raise(PSK_E7001, "a result is read as f32 or f64");
+        Tensor o = r;
+        if (r.dtype != out_dtype || r.off != 0 || r.affine) {
+            o = h->fresh(r.axes, out_dtype);
+            h->convert_into(r, o);
+        }
+        h->check(h->vt->download(h->vt->self, out_host, o.ptr(), (size_t)o.numel() * elem_bytes(out_dtype)), "download");
+        h->check(h->vt->sync(h->vt->self), "result");
     });
     return PSK_OK;
 }

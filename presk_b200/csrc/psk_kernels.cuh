@@ -44,6 +44,7 @@ PSK_DEV float prim_unary(int prim, float x, int imm, uint32_t *status)
         for (int i = 1; i < imm; ++i) e = __fmul_rn(e, x);
         return e;
     }
+    case PSK_DIV_N: return __fdiv_rn(x, (float)(double)imm);
     case PSK_ROUND: return imm == PSK_BF16 ? bf16_to_f32(f32_to_bf16(x)) : imm == PSK_F16 ? f16_to_f32(f32_to_f16(x)) : imm == PSK_E8M15 ? e8m15_to_f32(f32_to_e8m15(x)) : x;
     default: return x; // PSK_REAL
     }
@@ -544,11 +545,13 @@ __global__ void __launch_bounds__(128) k_reduce_seq(const __grid_constant__ DevL
             for (int64_t c = 0; c < L.inner; ++c) {
                 float x = load_operand(L.in[0], base + c * s, 0, L.kdtype, &ovf);
                 acc = __fadd_rn(acc, L.kind == PSK_REDUCE_SUMSQ ? __fmul_rn(x, x) : x);
+                if (L.kind == PSK_REDUCE_SUM_STORED) { ovf |= store_overflows(L.out.dtype, acc); acc = prim_unary(PSK_ROUND, acc, L.out.dtype, L.status); }
             }
         } else {
             for (int64_t c = 0; c < L.inner; ++c) {
                 float x = load_operand(L.in[0], base + operand_offset(L.in[0], L.dims, L.n_outer, L.n_inner, c), 0, L.kdtype, &ovf);
                 acc = __fadd_rn(acc, L.kind == PSK_REDUCE_SUMSQ ? __fmul_rn(x, x) : x);
+                if (L.kind == PSK_REDUCE_SUM_STORED) { ovf |= store_overflows(L.out.dtype, acc); acc = prim_unary(PSK_ROUND, acc, L.out.dtype, L.status); }
             }
         }
         ovf |= store_real(const_cast<void *>(L.out.p), L.out.dtype, ooff, reduce_finish(L, acc));

@@ -3,6 +3,7 @@ fixtures, so that the suite can run where the reference tree is not mounted.
 
 Sources (paths within presk-lang/presk, read as text):
   tests/run/layernorm_apply.snap, rmsnorm_apply.snap   seed-0 outputs of the exact interpreter, 12 digits
+  tests/run/mlp_mse.snap, mlp_mse_grad.snap             seed-0 loss and gradient of examples/spec/mlp/mlp.psk at D = 4, B = 2
   crates/presk-interp/src/key.rs:86-93                  the first four normal draws of the key seed 0 names
 Run:  python tests/golden/make_golden.py [/root/reference]
 """
@@ -18,6 +19,19 @@ for name in ("layernorm_apply", "rmsnorm_apply"):
     body = text.split("---")[-1]
     m = re.search(r"\[batch: (\d+), model: (\d+)\] (\[\[.*\]\])", body)
     out[name] = {"shape": [int(m.group(1)), int(m.group(2))], "values": json.loads(m.group(3))}
+text = open(os.path.join(ref, "tests", "run", "mlp_mse.snap")).read().split("---")[-1]
+out["mlp_mse"] = float(re.search(r"= ([-0-9.e]+)", text).group(1))
+text = open(os.path.join(ref, "tests", "run", "mlp_mse_grad.snap")).read().split("---")[-1]
+grad = {}
+layer = None
+for line in text.splitlines():
+    m = re.match(r"\s*(l\d) = \{", line)
+    if m:
+        layer = m.group(1)
+    m = re.match(r"\s*(w|b) = \[([0-9, ]+)\] (\[.*\])\s*$", line)
+    if m:
+        grad[layer + "." + m.group(1)] = {"shape": [int(x) for x in m.group(2).split(",")], "values": json.loads(m.group(3))}
+out["mlp_mse_grad"] = grad
 key_rs = open(os.path.join(ref, "crates", "presk-interp", "src", "key.rs")).read()
 m = re.search(r"assert_eq!\(first, \[([^\]]+)\]\)", key_rs)
 out["seed0_first_normals_bits"] = [int(x.strip(), 16) for x in m.group(1).split(",")]

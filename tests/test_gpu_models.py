@@ -248,3 +248,25 @@ def test_merged_launches_keep_every_bit_on_the_gpu(cuda, oracle, kind):
         rz = {"default": "bf16", "order": {"kind": "sequential"}, "params": {k: "bf16" for k in p}, "storage": {"Llama.apply/%11": "f32"}}
         want = models.give(Host(oracle.vtable(), rz).prepare("llama", **c), p).call("apply", [ids], (2, 128, c["V"]))
         assert_same_bits(outs[1], want)
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16", "f16"])
+@pytest.mark.parametrize("d,b", [(4, 2), (64, 48)])
+def test_mlp_gradient_bit_exact(cuda, oracle, dtype, d, b):
+    """The reverse-mode program of examples/spec/mlp/mlp.psk (`mse_grad`: sum_to, dot_vjp_l, dot_vjp_r,
+    mean_vjp, gelu', tree additions): every leaf of the gradient, the oracle's bits."""
+    rng = np.random.default_rng(d)
+    bound = np.sqrt(6.0 / (5 * d))
+    params = {"l1.w": rng.uniform(-bound, bound, (d, 4 * d)), "l1.b": rng.standard_normal(4 * d) * 0.1,
+              "l2.w": rng.uniform(-bound, bound, (4 * d, d)), "l2.b": rng.standard_normal(d) * 0.1}
+    x, y = rng.standard_normal((b, d)), rng.standard_normal((b, d))
+    leaves = []
+    for ex in (cuda, oracle.vtable()):
+        h = Host(ex, dtype).prepare("mlp_spec", D=d)
+        for k, v in params.items():
+            h.set_param(k, v)
+        loss = h.call("mse", [x, y], (), np.float32)
+        h.call("mse_grad", [x, y], (d, 4 * d), np.float32)
+        leaves.append([loss] + [h.result(k, np.shape(v), np.float32) for k, v in params.items()])
+    for got, want in zip(*leaves):
+        assert_same_bits(np.atleast_1d(got), np.atleast_1d(want))

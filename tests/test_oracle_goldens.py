@@ -69,3 +69,49 @@ def test_bf16_storage_rounds_every_site(oracle, ref):
     assert np.all(bits & 0xFFFF == 0)
     want = np.array(GOLD["rmsnorm_apply"]["values"])
     np.testing.assert_allclose(got, want, rtol=2e-2, atol=2e-2)
+
+
+def draws_at(ref, kind, seed, path, n):
+    out = np.empty(n, dtype=np.float64)
+    p = (C.c_int * len(path))(*path)
+    fn = ref.ref_uniforms_at if kind == "uniform" else ref.ref_normals_at
+    fn.argtypes = [C.c_uint64, C.POINTER(C.c_int), C.c_int, C.c_void_p, C.c_size_t]
+    fn(seed, p, len(path), out.ctypes.data, n)
+    return out
+
+
+def spec_mlp_seed0(ref, d=4, b=2):
+    """The arguments `presk run examples/spec/mlp/mlp.psk --entry mse --const D=4 --const B=2` synthesizes from
+    seed 0 (crates/presk-interp/src/run.rs:73-101, 315-366): the entry's three arguments θ, x, y take the three
+    children of the master key; θ is MLP.init of its key (split in two for l1, l2; each Linear.init splits its key
+    in two and draws w from the first by xavier_uniform, host.rs:1641-1657; b is zeros); x and y are normal draws."""
+    bound = np.sqrt(6.0 / (d + 4 * d))
+    params = {
+        "l1.w": ((2.0 * draws_at(ref, "uniform", 0, [0, 0, 0], d * 4 * d) - 1.0) * bound).reshape(d, 4 * d),
+        "l1.b": np.zeros(4 * d),
+        "l2.w": ((2.0 * draws_at(ref, "uniform", 0, [0, 1, 0], d * 4 * d) - 1.0) * bound).reshape(4 * d, d),
+        "l2.b": np.zeros(d),
+    }
+    x = draws_at(ref, "normal", 0, [1], b * d).reshape(b, d)
+    y = draws_at(ref, "normal", 0, [2], b * d).reshape(b, d)
+    return params, x, y
+
+
+def test_mlp_loss_and_gradient_goldens_on_the_oracle(oracle, ref):
+    """tests/run/mlp_mse.snap and mlp_mse_grad.snap (exact interpreter, 12 digits): the forward pass and the
+    reverse-mode program of crates/presk-core/tests/snapshots/ad__ad_mlp.snap, launch by launch, in f32."""
+    params, x, y = spec_mlp_seed0(ref)
+    h = Host(oracle.vtable(), "f32").prepare("mlp_spec", D=4)
+    for k, v in params.items():
+        h.set_param(k, v)
+    h.set_logging(True)
+    loss = h.call("mse", [x, y], (), np.float32)
+    assert abs(float(loss) - GOLD["mlp_mse"]) <= 2e-6
+    assert h.launch_log() == ["dot", "add", "gelu", "dot", "add", "fused 2 steps", "mean"]
+    h.call("mse_grad", [x, y], (4, 16), np.float32)
+    linear_bwd = ["sum_to", "dot_vjp_l", "dot_vjp_r", "add", "add"]
+    assert h.launch_log() == (["dot", "add", "gelu", "dot", "add", "sub", "mean_vjp", "fused 3 steps", "sum_to"]
+                              + linear_bwd + ["fused 2 steps"] + linear_bwd + ["add"] * 4)
+    for path, g in GOLD["mlp_mse_grad"].items():
+        got = h.result(path, tuple(g["shape"]), np.float32)
+        np.testing.assert_allclose(got, np.array(g["values"]), rtol=0, atol=2e-6, err_msg=path)
