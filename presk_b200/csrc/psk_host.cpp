@@ -1678,6 +1678,15 @@ struct psk_host {
         if (model == "llama") {
             if (entry == "apply") { need(1); return llama_apply(in[0]); }
             if (entry == "loss") { need(2); return llama_loss(in[0], in[1]); }
+            if (entry == "attention") {
+                // one attention function on given activations [batch, seq, model], with the causal mask and the
+                // angles of its sequence length: examples/spec/rope/rope.psk `attention2` is this with G = H
+                need(1);
+                const int64_t T = in[0].axes[1].len;
+                Tensor mask = causal_mask("Llama.apply/%2", "seq", T);
+                Tensor phi = llama_angles(T);
+                return llama_attention(0, in[0], mask, phi);
+            }
         } else if (model == "gpt") {
             if (entry == "apply") { need(1); return gpt_apply(in[0]); }
             if (entry == "loss") { need(2); return gpt_loss(in[0], in[1]); }
@@ -1707,7 +1716,8 @@ struct psk_host {
     Axes input_axes(const std::string &entry, int i, const psk_value &v)
     {
         std::vector<std::string> names;
-        if (model == "llama" || model == "gpt") names = {"batch", "seq"};
+        if (model == "llama" && entry == "attention") names = {"batch", "seq", "model"};
+        else if (model == "llama" || model == "gpt") names = {"batch", "seq"};
         else if (model == "mlp") names = i == 0 ? std::vector<std::string>{"batch", "model"} : std::vector<std::string>{"batch"};
         else if (model == "mlp_spec") names = {"batch", "model"};
         else if (model == "layernorm" || model == "rmsnorm") {

@@ -270,3 +270,19 @@ def test_mlp_gradient_bit_exact(cuda, oracle, dtype, d, b):
         leaves.append([loss] + [h.result(k, np.shape(v), np.float32) for k, v in params.items()])
     for got, want in zip(*leaves):
         assert_same_bits(np.atleast_1d(got), np.atleast_1d(want))
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_attention_entry_bit_exact(cuda, oracle, dtype):
+    """The attention function alone on given activations (the entry the rope golden is checked through)."""
+    c = dict(V=8, D=64, H=4, G=2, FF=8, L=1)
+    rng = np.random.default_rng(12)
+    params = {"blocks.attn." + n: rng.standard_normal((1, 64, 64 if n in ("wq", "wo") else 32)) * 0.05 for n in ("wq", "wk", "wv", "wo")}
+    x = rng.standard_normal((3, 24, 64))
+    outs = []
+    for ex in (cuda, oracle.vtable()):
+        h = Host(ex, dtype).prepare("llama", **c)
+        for k, v in params.items():
+            h.set_param(k, v)
+        outs.append(h.call("attention", [x], (3, 24, 64), np.float32))
+    assert_same_bits(*outs)
