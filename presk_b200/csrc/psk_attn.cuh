@@ -7,9 +7,10 @@
 // runs as its own nest with its result stored in memory. It is used only under
 // the declared order "device" with `"attention": "blockwise"`, since it is a
 // different realization and not only a reordering of sums:
-//   - a score is rounded to bf16, divided by the root (the division's own
-//     result, by its correctly rounded reciprocal and one correction) and
-//     rounded to bf16 again, exactly as the two stored sites would hold it;
+//   - a score is rounded to bf16, divided by the root and rounded to bf16
+//     again, exactly as the two stored sites would hold it (the quotient of
+//     two bf16 numbers rounds to the same bf16 number whether it is computed by
+//     a division or by the correctly rounded reciprocal; see the kernel);
 //   - the row's maximum is taken over those values in a first pass over the
 //     key blocks, so the exponentials have the reference's arguments;
 //   - exp is the hardware's ex2 (relative error about 2^-22), the row's sum is
@@ -186,7 +187,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_attn_fwd(const __grid_constant__
         const int cq = (warp - 2) >> 2;       // its quarter of a block's keys, and of the output's columns
         const int row = quad * 32 + lane;     // this thread's query within the block
         const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
-        const float rtv = load_real(P.rt, P.rt_dtype, 0);
+        const float rtv = bf16_round(load_real(P.rt, P.rt_dtype, 0)); // the division's kernel is bf16: it reads rt rounded to bf16 at its edge
         const float rr = __frcp_rn(rtv);
         float *xch = reinterpret_cast<float *>(sP); // the P tiles are idle whenever the warps exchange a row's parts
         bool ok = true;
@@ -194,7 +195,9 @@ __global__ void __launch_bounds__(THREADS, 1) k_attn_fwd(const __grid_constant__
         // ---- pass 1: the greatest and the least raw score of the row ------------------
         // bf16(bf16(S) / rt) is monotone in S, so the row's maximum of the stored scaled scores is that
         // function of the greatest raw score (of the least, if rt is negative).
-        float mx = -INFINITY, mn = INFINITY;
+        // rt > 0 (a root): only the greatest raw score matters; otherwise only the least. One comparison an element.
+        const bool want_max = !(rtv < 0.0f);
+        float ext = want_max ? -INFINITY : INFINITY;
         for (int kb = 0; kb < nkb && ok; ++kb) {
             const uint32_t sb = qk_count & 1u, sph = (qk_count >> 1) & 1u;
             ok = tc::mbar_wait(bar(9 + sb), sph, abort_flag, P.status, 0x31u);
@@ -208,22 +211,23 @@ __global__ void __launch_bounds__(THREADS, 1) k_attn_fwd(const __grid_constant__
             __syncwarp();
             if (lane == 0) tc::mbar_arrive(bar(11 + sb)); // the scores are in registers
             ++qk_count;
-            if (P.causal && kb == qb) {
+            const int allowed = (P.causal && kb == qb) ? row - cq * 32 : 31; // the last allowed key of these 32
+            if (want_max) {
 #pragma unroll
                 for (int i = 0; i < 32; ++i)
-                    if (cq * 32 + i <= row) { mx = fmaxf(mx, __uint_as_float(v[i])); mn = fminf(mn, __uint_as_float(v[i])); }
+                    if (i <= allowed) ext = fmaxf(ext, __uint_as_float(v[i]));
             } else {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) { mx = fmaxf(mx, __uint_as_float(v[i])); mn = fminf(mn, __uint_as_float(v[i])); }
+                for (int i = 0; i < 32; ++i)
+                    if (i <= allowed) ext = fminf(ext, __uint_as_float(v[i]));
             }
         }
-        xch[cq * 128 + row] = mx;
-        xch[512 + cq * 128 + row] = mn;
+        xch[cq * 128 + row] = ext;
         softmax_sync();
 #pragma unroll
-        for (int c = 0; c < 4; ++c) { mx = fmaxf(mx, xch[c * 128 + row]); mn = fminf(mn, xch[512 + c * 128 + row]); }
+        for (int c = 0; c < 4; ++c) ext = want_max ? fmaxf(ext, xch[c * 128 + row]) : fminf(ext, xch[c * 128 + row]);
         softmax_sync(); // before the first P is written over the exchange
-        const float m = bf16_round(__fdiv_rn(bf16_round(rtv < 0.0f ? mn : mx), rtv));
+        const float m = bf16_round(__fdiv_rn(bf16_round(ext), rtv));
         // ---- pass 2: exponentials, the row's sum, P for the second product --------------
         const float LOG2E = 1.44269504f;
         const float m2 = __fmul_rn(m, LOG2E);
@@ -245,12 +249,12 @@ __global__ void __launch_bounds__(THREADS, 1) k_attn_fwd(const __grid_constant__
             uint32_t packed[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-                // the two stored sites: bf16(S), then bf16(bf16(S) / rt); the quotient by the correctly
-                // rounded reciprocal and one correction (the division's own result for a normal numerator)
+                // the two stored sites: bf16(S), then bf16(bf16(S) / rt). With a and rt both bf16 numbers the
+                // quotient is never within 2^-17 (relative) of the midpoint of two bf16 numbers without being one of
+                // them, and it cannot be such a midpoint (an odd 9-bit significand times rt's has more than a's 8
+                // bits), so a·RN(1/rt), which is within 2^-23 of a/rt, rounds to the same bf16 number as a/rt.
                 const uint32_t s1 = pack_bf16x2_hw(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
-                const float a0 = bits_f32(s1 << 16), a1 = bits_f32(s1 & 0xffff0000u);
-                const float q0 = __fmul_rn(a0, rr), q1 = __fmul_rn(a1, rr);
-                const float d0 = __fmaf_rn(__fmaf_rn(-rtv, q0, a0), rr, q0), d1 = __fmaf_rn(__fmaf_rn(-rtv, q1, a1), rr, q1);
+                const float d0 = __fmul_rn(bits_f32(s1 << 16), rr), d1 = __fmul_rn(bits_f32(s1 & 0xffff0000u), rr);
                 const uint32_t s2 = pack_bf16x2_hw(d0, d1);
                 float e0 = fast_exp2(__fmaf_rn(bits_f32(s2 << 16), LOG2E, -m2));
                 float e1 = fast_exp2(__fmaf_rn(bits_f32(s2 & 0xffff0000u), LOG2E, -m2));
