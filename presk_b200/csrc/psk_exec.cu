@@ -507,6 +507,7 @@ void psk_exec_free(psk_exec *e, void *p)
 int psk_exec_upload(psk_exec *e, void *dst, const void *src_host, size_t bytes)
 {
     cudaSetDevice(e->device);
+    e->causal.erase(dst);
     CUDA_TRY(e, cudaMemcpyAsync(dst, src_host, bytes, cudaMemcpyHostToDevice, e->stream));
     CUDA_TRY(e, cudaStreamSynchronize(e->stream)); // the host buffer is the caller's again
     return PSK_OK;
@@ -631,6 +632,7 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
     if (l->dtype == PSK_F64 && l->op != PSK_OP_CONVERT)
         return fail(e, PSK_E7005, std::string(l->name ? l->name : "?") + ": this executor computes in f32; a site realised f64 is not runnable by it");
     const int naxes = l->n_outer + l->n_inner;
+    if (!e->causal.empty() && l->op != PSK_OP_MAGNITUDE) e->causal.erase(table[l->n_inputs]); // whatever this launch writes is no longer known to be a causal mask
     DevLaunch L;
     memset(&L, 0, sizeof L);
     L.n_in = l->n_inputs; L.n_outer = l->n_outer; L.n_inner = l->n_inner; L.kdtype = l->dtype;
