@@ -34,9 +34,9 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 WORKLOADS = {
-    # BASELINE.json configs[3]: 32 layers, d 4096, 32 heads of 128, SwiGLU 11008, vocab 32000, seq 2048, batch 8 a GPU
+    # the Llama-7B-shaped prefill: 32 layers, d 4096, 32 heads of 128, SwiGLU 11008, vocab 32000, seq 2048, batch 8 a GPU
     "llama7b_prefill_b8_t2048": dict(consts=dict(V=32000, D=4096, H=32, G=32, FF=11008, L=32), B=8, T=2048),
-    # BASELINE.json configs[4], int8 half: the same architecture, projection and FFN weights int8 with one f32 scale a
+    # its int8 variant: the same architecture, projection and FFN weights int8 with one f32 scale a
     # channel, bf16 activations, seq 1024, batch 16 a GPU
     "llama7b_int8_prefill_b16_t1024": dict(consts=dict(V=32000, D=4096, H=32, G=32, FF=11008, L=32), B=16, T=1024, int8=True),
     # a small shape of the same program, for trying the script out
@@ -228,7 +228,7 @@ def microbench(args):
         fl = 4.0 * B * H * (nqb * (nqb + 1) / 2) * 128 * 128 * hd
         print(json.dumps({"micro": "attn", "shape": dims, "ms": ms, "TFLOP/s (causal blocks, one pass)": fl / ms / 1e9}))
     elif args.micro == "e8m15":
-        # config 3's contraction: x[m, k] · w[k, n], every site e8m15, under the device order
+        # the contraction-plus-LayerNorm workload's contraction: x[m, k] · w[k, n], every site e8m15, under the device order
         m, n, k = dims[:3]
         a = ex.upload(rng.integers(0, 256, size=m * k * 3, dtype=np.uint8) & np.tile(np.array([255, 255, 0x3f], np.uint8), m * k))
         b = ex.upload(rng.integers(0, 256, size=n * k * 3, dtype=np.uint8) & np.tile(np.array([255, 255, 0x3f], np.uint8), n * k))

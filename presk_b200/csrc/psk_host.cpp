@@ -1546,7 +1546,7 @@ struct psk_host {
 
 
     // ===========================================================================
-    // examples/corpus/nlp/05_gpt.psk (BASELINE config 2). Outside training a dropout is
+    // examples/corpus/nlp/05_gpt.psk (the GPT workload). Outside training a dropout is
     // a mask of ones, made by the host, and the product with it is still a launch
     // (host.rs:1626).
     // ===========================================================================

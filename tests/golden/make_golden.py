@@ -6,7 +6,7 @@ Sources (paths within presk-lang/presk, read as text):
   tests/run/mlp_mse.snap, mlp_mse_grad.snap             seed-0 loss and gradient of examples/spec/mlp/mlp.psk at D = 4, B = 2
   tests/run/rope_attention2.snap                        seed-0 output of examples/spec/rope/rope.psk `attention2` at B = 2, T = 8
   crates/presk-interp/src/key.rs:86-93                  the first four normal draws of the key seed 0 names
-Run:  python tests/golden/make_golden.py [/root/reference]
+Run:  python tests/golden/make_golden.py [path of the reference's tree]
 """
 import json
 import os

@@ -61,7 +61,7 @@ def llama_numpy(p, c, ids, y=None):
 
 
 def mlp_params(seed=0, d_in=784, d_h=256, d_out=10):
-    """xavier_uniform weights, zero biases (BASELINE config 1)."""
+    """xavier_uniform weights, zero biases (the MLP classifier workload)."""
     rng = np.random.default_rng(seed)
     xav = lambda i, o: rng.uniform(-np.sqrt(6.0 / (i + o)), np.sqrt(6.0 / (i + o)), size=(i, o)).astype(np.float32)
     return {"l1.w": xav(d_in, d_h), "l1.b": np.zeros(d_h, np.float32), "l2.w": xav(d_h, d_out), "l2.b": np.zeros(d_out, np.float32)}
@@ -83,7 +83,7 @@ GPT_TINY = dict(V=65, D=32, H=4, L=2)
 
 def gpt_params(c, T, seed=0):
     """examples/corpus/nlp/05_gpt.psk's parameters: normal(0.02) tables, xavier linear maps, zero biases;
-    the head drawn normal(0.02) too so that the logits are not all zero (BASELINE config 2)."""
+    the head drawn normal(0.02) too so that the logits are not all zero (the GPT workload)."""
     rng = np.random.default_rng(seed)
     V, D, L = c["V"], c["D"], c["L"]
     n = lambda *s: (rng.standard_normal(s) * 0.02).astype(np.float32)

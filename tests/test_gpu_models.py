@@ -41,7 +41,7 @@ def test_norms_bit_exact(cuda, oracle, model, dtype):
 
 
 def test_mlp_config1_bit_exact(cuda, oracle):
-    """BASELINE config 1 at full size: Linear{784,256} · ReLU · Linear{256,10} + cross-entropy, B = 4096, all f32."""
+    """The MLP classifier workload at full size: Linear{784,256} · ReLU · Linear{256,10} + cross-entropy, B = 4096, all f32."""
     p = models.mlp_params()
     x, y = models.mlp_inputs(4096)
     got, want = both(cuda, oracle, "f32", "mlp", {}, p, "apply", [x], (4096, 10))
@@ -100,7 +100,7 @@ def test_llama_device_order_within_tolerance(cuda, oracle):
 @pytest.mark.parametrize("dtype,scale,overflows", [("f16", 1.0, False), ("f16", 2.0**20, True), ("e8m15", 2.0**20, False)])
 @pytest.mark.parametrize("order", ["sequential", "device"])
 def test_contract_ln_config3_and_overflow_guard(cuda, oracle, dtype, scale, overflows, order):
-    """BASELINE config 3 at N = 1024: x·w stored in f16 / e8m15 then a row LayerNorm; inputs scaled
+    """The contraction-plus-LayerNorm workload at N = 1024: x·w stored in f16 / e8m15 then a row LayerNorm; inputs scaled
     by 2^20 overflow the f16 store of the `dot` and stop the run with E7007."""
     n = 1024 if order == "device" else 256
     rng = np.random.default_rng(6)
@@ -127,7 +127,7 @@ def test_contract_ln_config3_and_overflow_guard(cuda, oracle, dtype, scale, over
 
 @pytest.mark.parametrize("dtype", ["f32", "bf16"])
 def test_gpt_config2_bit_exact_under_sequential_order(cuda, oracle, dtype):
-    """BASELINE config 2's program (05_gpt.psk) at reduced constants; its full shape runs under device order below."""
+    """The GPT workload's program (05_gpt.psk) at reduced constants; its full shape runs under device order below."""
     c = models.GPT_TINY
     T = 16
     p = models.gpt_params(c, T)
@@ -187,7 +187,7 @@ def test_w8a8_dense_is_exact_on_the_gpu(cuda, oracle):
 
 
 def test_llama_int8_weights_on_tensor_cores(cuda, oracle):
-    """BASELINE config 5's shape of program at small constants: int8 projection and FFN weights with one
+    """The int8 workload's shape of program at small constants: int8 projection and FFN weights with one
     f32 scale a channel, bf16 activations, device order: the weights' integers go through the tensor
     cores as bf16 numbers and the scale multiplies the sum. Against the oracle's sequential
     sum of x·(q·s) the difference is a reassociation: a few bf16 ulps after two layers."""

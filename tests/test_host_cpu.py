@@ -88,7 +88,7 @@ def test_realization_errors(oracle):
 
 
 def test_overflow_guard_stops_the_run(oracle):
-    """Inputs scaled by 2^20 overflow the binary16 store of the `dot` (BASELINE config 3): E7007."""
+    """Inputs scaled by 2^20 overflow the binary16 store of the `dot` (the contraction-plus-LayerNorm workload): E7007."""
     rng = np.random.default_rng(5)
     n = 64
     x, w = rng.standard_normal((n, n)).astype(np.float32), rng.standard_normal((n, n)).astype(np.float32)
