@@ -314,6 +314,28 @@ int psk_exec_gemm(psk_exec *e, const psk_gemm *g, const void *a, const void *b, 
 #define PSK_NOALLOC_MAX_BATCH 1023
 int psk_gemm_noalloc(const psk_gemm *g, const void *a, const void *b, void *c, void *stream, int64_t *overflowed_batch, char *err, size_t err_cap);
 
+/* ---- the exchange step of a sharded call -------------------------------------------------------------------
+ * The path shards by the batch axis: every rank (one process a GPU) runs the same launches on its rows, and
+ * nothing crosses between GPUs until the end of a call, where the loss (and, under `presk calibrate`, each
+ * site's magnitudes) is combined. No counterpart in the reference, whose executors are single-process: these
+ * stand where its `Backend` reads a scalar back (presk-kernel/src/host.rs:1584, 1844). NCCL over NVLink;
+ * looked up at run time (libnccl.so.2), so that the library loads where NCCL is absent. */
+#define PSK_COMM_ID_BYTES 128
+#define PSK_COMM_U32 100 /* raw 32-bit words, compared as unsigned integers (dtype argument) */
+typedef enum { PSK_COMM_SUM = 0, PSK_COMM_MAX = 1, PSK_COMM_MIN = 2 } psk_comm_op;
+typedef struct psk_comm psk_comm;
+/* Rank 0 makes an id and gives it to the others by whatever route started them (a file, a socket, MPI). */
+int psk_comm_unique_id(uint8_t id[PSK_COMM_ID_BYTES]);
+/* Collective: every rank calls it with the same id. NULL on failure; psk_comm_error(NULL) says why. */
+psk_comm *psk_comm_create(psk_exec *e, int32_t nranks, int32_t rank, const uint8_t id[PSK_COMM_ID_BYTES]);
+void psk_comm_destroy(psk_comm *c);
+const char *psk_comm_error(const psk_comm *c);
+int32_t psk_comm_rank(const psk_comm *c);
+int32_t psk_comm_size(const psk_comm *c);
+/* In place, on the executor's stream, ordered after the launches queued before it; `dtype` is PSK_F32, PSK_F64,
+ * PSK_I64 or PSK_COMM_U32. */
+int psk_comm_allreduce(psk_comm *c, void *device_buf, int64_t count, int32_t dtype, int32_t op);
+
 /* ---------------------------------------------------------------------------
  * The executor as a table of functions, so that the host program can run
  * over another one (KernelBackend::with_exec, host.rs:466). The library's
@@ -421,6 +443,13 @@ const char *psk_host_envelope(psk_host *h);
 int64_t psk_host_launches(const psk_host *h);
 const char *psk_host_launch_log(const psk_host *h);
 void psk_host_set_logging(psk_host *h, int on);
+
+/* The mean over all ranks' rows of a per-rank mean that stays on the executor (a loss from psk_host_call_device):
+ * sum over ranks, divided by the number of ranks (equal rows a rank), read back as f64. */
+int psk_host_mean_over_ranks(psk_host *h, psk_comm *c, const void *device_scalar, int32_t dtype, double *out);
+/* Merges the magnitudes psk_host_envelope reports over the ranks: one max-reduction (the minima travel
+ * complemented). After it every rank's envelope is that of the whole batch. */
+int psk_host_envelope_allreduce(psk_host *h, psk_comm *c);
 
 #ifdef __cplusplus
 }

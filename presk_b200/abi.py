@@ -28,6 +28,9 @@ OP_FUSED, OP_CONTRACT, OP_REDUCE, OP_SOFTMAX, OP_XENT, OP_ARGMAX, OP_EMBED, OP_C
 
 ORDER_SEQUENTIAL, ORDER_DEVICE = 0, 1
 REDUCE_SUM, REDUCE_MEAN, REDUCE_SUMSQ, REDUCE_SUM_STORED = 0, 1, 2, 3
+COMM_U32 = 100
+COMM_SUM, COMM_MAX, COMM_MIN = 0, 1, 2
+COMM_ID_BYTES = 128
 IOTA_POSITIONS, IOTA_CAUSAL, IOTA_ONE_HOT, IOTA_FILL = 0, 1, 2, 3
 
 
@@ -110,6 +113,15 @@ PROTOTYPES = {
     "psk_host_set_param": (C.c_int, [C.c_void_p, C.c_char_p, C.c_void_p, C.c_int32, C.POINTER(C.c_int64), C.c_int32]),
     "psk_host_init_param": (C.c_int, [C.c_void_p, C.c_char_p, C.c_uint64, C.c_double, C.POINTER(C.c_int64), C.c_int32]),
     "psk_host_call": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(Value), C.c_int32, C.c_void_p, C.c_int32, C.c_int64, C.POINTER(C.c_int64)]),
+    "psk_comm_unique_id": (C.c_int, [C.c_void_p]),
+    "psk_comm_create": (C.c_void_p, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]),
+    "psk_comm_destroy": (None, [C.c_void_p]),
+    "psk_comm_error": (C.c_char_p, [C.c_void_p]),
+    "psk_comm_rank": (C.c_int32, [C.c_void_p]),
+    "psk_comm_size": (C.c_int32, [C.c_void_p]),
+    "psk_comm_allreduce": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32]),
+    "psk_host_mean_over_ranks": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.POINTER(C.c_double)]),
+    "psk_host_envelope_allreduce": (C.c_int, [C.c_void_p, C.c_void_p]),
     "psk_host_result": (C.c_int, [C.c_void_p, C.c_char_p, C.c_void_p, C.c_int32, C.c_int64, C.POINTER(C.c_int64)]),
     "psk_host_call_device": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(Value), C.c_int32, C.POINTER(C.c_void_p), C.POINTER(C.c_int32), C.POINTER(C.c_int64)]),
     "psk_host_set_calibrating": (None, [C.c_void_p, C.c_int]),

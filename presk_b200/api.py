@@ -117,6 +117,39 @@ class Executor:
         return vt
 
 
+class Comm:
+    """The exchange step of a sharded call (`psk_comm_*`): one communicator a rank, over the executor's stream."""
+
+    @staticmethod
+    def unique_id():
+        lib = abi.load()
+        buf = C.create_string_buffer(abi.COMM_ID_BYTES)
+        rc = lib.psk_comm_unique_id(buf)
+        if rc != abi.OK:
+            raise PreskError(rc, lib.psk_comm_error(None).decode())
+        return buf.raw
+
+    def __init__(self, executor, nranks, rank, unique_id):
+        self.lib = executor.lib
+        self.executor = executor
+        self.handle = self.lib.psk_comm_create(executor.handle, nranks, rank, C.create_string_buffer(unique_id, abi.COMM_ID_BYTES))
+        if not self.handle:
+            raise PreskError(abi.E10001, self.lib.psk_comm_error(None).decode())
+
+    def allreduce(self, device_ptr, count, dtype, op):
+        rc = self.lib.psk_comm_allreduce(self.handle, device_ptr, count, dtype, op)
+        if rc != abi.OK:
+            raise PreskError(rc, self.lib.psk_comm_error(self.handle).decode())
+
+    def size(self):
+        return self.lib.psk_comm_size(self.handle)
+
+    def close(self):
+        if self.handle:
+            self.lib.psk_comm_destroy(self.handle)
+            self.handle = None
+
+
 class Host:
     """`Backend`: prepare a model under a realization, give it parameters, call an entry.
 
@@ -196,6 +229,16 @@ class Host:
         if n.value != out.size:
             raise PreskError(abi.E7001, f"the result has {n.value} elements, not {out.size}")
         return out
+
+    def mean_over_ranks(self, comm, device_scalar, dtype):
+        """The mean over all ranks of a per-rank mean left on the executor by `call_device`."""
+        out = C.c_double()
+        self._check(self.lib.psk_host_mean_over_ranks(self.handle, comm.handle, device_scalar, dtype, C.byref(out)))
+        return out.value
+
+    def envelope_allreduce(self, comm):
+        """Merges the calibrated magnitudes over the ranks."""
+        self._check(self.lib.psk_host_envelope_allreduce(self.handle, comm.handle))
 
     def result(self, path, shape, out_dtype=np.float32):
         """A leaf of the last call's result when that is a tree (a gradient), by the parameter's path."""

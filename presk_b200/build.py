@@ -32,7 +32,7 @@ def _nvcc():
 
 
 def sources():
-    return [os.path.join(CSRC, f) for f in ("psk_exec.cu", "psk_host.cpp", "psk_noalloc.cu") if os.path.exists(os.path.join(CSRC, f))]
+    return [os.path.join(CSRC, f) for f in ("psk_exec.cu", "psk_host.cpp", "psk_noalloc.cu", "psk_comm.cpp") if os.path.exists(os.path.join(CSRC, f))]
 
 
 def stale():
@@ -54,7 +54,7 @@ def build(force=False, verbose=False):
         cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-x", "cu" if src.endswith(".cu") else "c++", "-c", src, "-o", obj]
         subprocess.run(cmd, check=True)
         objs.append(obj)
-    subprocess.run([_nvcc(), "-shared", "-o", LIB] + objs + ["-lcudart"], check=True)
+    subprocess.run([_nvcc(), "-shared", "-o", LIB] + objs + ["-lcudart", "-ldl"], check=True)
     return LIB
 
 

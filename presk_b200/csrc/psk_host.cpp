@@ -1938,6 +1938,48 @@ int psk_host_result(psk_host *h, const char *path, void *out_host, int32_t out_d
     return PSK_OK;
 }
 
+int psk_host_mean_over_ranks(psk_host *h, psk_comm *c, const void *device_scalar, int32_t dtype, double *out)
+{
+    HOST_TRY(h, {
+        if (!c || !device_scalar || !out) raise(PSK_E7001, "psk_host_mean_over_ranks: a communicator, a scalar and somewhere to put the mean");
+        // the scalar as a double on the host, summed over the ranks as doubles, divided by their number
+        uint8_t raw[8] = {0};
+        h->check(h->vt->download(h->vt->self, raw, device_scalar, elem_bytes(dtype)), "download");
+        double x;
+        switch (dtype) {
+        case PSK_F64: memcpy(&x, raw, 8); break;
+        case PSK_F32: { float f; memcpy(&f, raw, 4); x = f; break; }
+        case PSK_BF16: { uint32_t w = (uint32_t)(raw[0] | (raw[1] << 8)) << 16; float f; memcpy(&f, &w, 4); x = f; break; }
+        default: raise(PSK_E7001, "psk_host_mean_over_ranks: a loss is f64, f32 or bf16");
+        }
+        Storage tmp(h->vt, 8);
+        h->check(h->vt->upload(h->vt->self, tmp.p, &x, 8), "upload");
+        if (psk_comm_allreduce(c, tmp.p, 1, PSK_F64, PSK_COMM_SUM) != PSK_OK) raise(PSK_E10001, std::string("all-reduce: ") + psk_comm_error(c));
+        h->check(h->vt->download(h->vt->self, &x, tmp.p, 8), "download");
+        *out = x / (double)psk_comm_size(c);
+    });
+    return PSK_OK;
+}
+
+int psk_host_envelope_allreduce(psk_host *h, psk_comm *c)
+{
+    HOST_TRY(h, {
+        if (!c) raise(PSK_E7001, "psk_host_envelope_allreduce: a communicator");
+        if (!h->slots || h->slot_of.empty()) return PSK_OK;
+        // words 0 and 3 of a site merge by maximum, words 1 and 2 by minimum: complemented, one maximum does all four
+        std::vector<uint32_t> words(h->slot_of.size() * 4);
+        h->check(h->vt->sync(h->vt->self), "calibrate");
+        h->check(h->vt->download(h->vt->self, words.data(), h->slots->p, words.size() * 4), "calibrate");
+        for (size_t i = 0; i < words.size(); i += 4) { words[i + 1] = ~words[i + 1]; words[i + 2] = ~words[i + 2]; }
+        h->check(h->vt->upload(h->vt->self, h->slots->p, words.data(), words.size() * 4), "calibrate");
+        if (psk_comm_allreduce(c, h->slots->p, (int64_t)words.size(), PSK_COMM_U32, PSK_COMM_MAX) != PSK_OK) raise(PSK_E10001, std::string("all-reduce: ") + psk_comm_error(c));
+        h->check(h->vt->download(h->vt->self, words.data(), h->slots->p, words.size() * 4), "calibrate");
+        for (size_t i = 0; i < words.size(); i += 4) { words[i + 1] = ~words[i + 1]; words[i + 2] = ~words[i + 2]; }
+        h->check(h->vt->upload(h->vt->self, h->slots->p, words.data(), words.size() * 4), "calibrate");
+    });
+    return PSK_OK;
+}
+
 void psk_host_set_calibrating(psk_host *h, int on)
 {
     h->calibrating = on != 0;
