@@ -227,6 +227,18 @@ def microbench(args):
         nqb = t // 128
         fl = 4.0 * B * H * (nqb * (nqb + 1) / 2) * 128 * 128 * hd
         print(json.dumps({"micro": "attn", "shape": dims, "ms": ms, "TFLOP/s (causal blocks, one pass)": fl / ms / 1e9}))
+    elif args.micro == "f32c":
+        # x[m, k] · w[k, n], every site f32, under the device order (three bf16 planes an operand)
+        m, n, k = dims[:3]
+        a, b = ex.upload(rng.standard_normal((m, k)).astype(np.float32)), ex.upload(rng.standard_normal((k, n)).astype(np.float32))
+        c = ex.alloc(m * n * 4)
+        l = launch_desc(abi.OP_CONTRACT, abi.F32, [m, n], [k], order=abi.ORDER_DEVICE if len(dims) < 4 or dims[3] else abi.ORDER_SEQUENTIAL)
+        l.n_inputs = 2
+        l.inputs[0].dtype, l.inputs[0].numel, l.inputs[0].stride[0], l.inputs[0].stride[2] = abi.F32, m * k, k, 1
+        l.inputs[1].dtype, l.inputs[1].numel, l.inputs[1].stride[1], l.inputs[1].stride[2] = abi.F32, n * k, 1, n
+        l.out.dtype, l.out.numel, l.out.stride[0], l.out.stride[1] = abi.F32, m * n, n, 1
+        ms = timed(lambda: ex.run(l, [a, b, c]), args.steps)
+        print(json.dumps({"micro": "f32c", "shape": dims, "ms": ms, "TFLOP/s (2mnk)": 2.0 * m * n * k / ms / 1e9}))
     elif args.micro == "e8m15":
         # the contraction-plus-LayerNorm workload's contraction: x[m, k] · w[k, n], every site e8m15, under the device order
         m, n, k = dims[:3]
@@ -286,7 +298,7 @@ def microbench(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--micro", default=None, choices=["gemm", "softmax", "ew", "attn", "norm", "e8m15"])
+    ap.add_argument("--micro", default=None, choices=["gemm", "softmax", "ew", "attn", "norm", "e8m15", "f32c"])
     ap.add_argument("--shape", default="8192,8192,8192")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)

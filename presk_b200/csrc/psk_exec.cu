@@ -328,14 +328,14 @@ bool make_map(psk_exec *e, CUtensorMap *map, const void *base, int f16, uint64_t
     return r == CUDA_SUCCESS;
 }
 
-int launch_tc(psk_exec *e, const psk_gemm &g, const void *a, const void *b, void *c, uint32_t *flag, const float *col_scale = nullptr, int64_t cs_stride = 0, int64_t cs_lo = 0, int64_t cs_hi = 0, int64_t split_k = 0)
+int launch_tc(psk_exec *e, const psk_gemm &g, const void *a, const void *b, void *c, uint32_t *flag, const float *col_scale = nullptr, int64_t cs_stride = 0, int64_t cs_lo = 0, int64_t cs_hi = 0, int64_t split_k = 0, int planes = 2)
 {
     if (!e->encode) return fail(e, PSK_E10001, "cuTensorMapEncodeTiled is not available from this driver");
     const bool f16 = g.in_dtype == PSK_F16;
     const int bn = g.n >= 256 || g.n % 128 != 0 ? 256 : 128;
     const int64_t batch_hi = g.batch / g.batch_lo;
     CUtensorMap ma, mb;
-    const uint64_t kphys = split_k ? (uint64_t)(2 * split_k) : (uint64_t)g.k; // what the operands hold along the summed axis
+    const uint64_t kphys = split_k ? (uint64_t)(planes * split_k) : (uint64_t)g.k; // what the operands hold along the summed axis
     if (!make_map(e, &ma, a, f16, kphys, (uint64_t)g.m, (uint64_t)g.batch_lo, (uint64_t)batch_hi, (uint64_t)g.a_row, (uint64_t)g.a_lo, (uint64_t)g.a_hi, tc::BK, tc::BM))
         return fail(e, PSK_E7001, "tensor-core contraction: operand 0's strides do not make a tensor map");
     bool okb = g.b_n_major
@@ -346,7 +346,7 @@ int launch_tc(psk_exec *e, const psk_gemm &g, const void *a, const void *b, void
     P.m = g.m; P.n = g.n; P.k = g.k; P.batch = g.batch; P.batch_lo = g.batch_lo;
     P.tiles_m = (g.m + tc::BM - 1) / tc::BM;
     P.tiles_n = (g.n + bn - 1) / bn;
-    P.split_k = split_k;
+    P.split_k = split_k; P.planes = planes; P.pad_ = 0;
     {
         // a panel's columns of B (bn·k elements each) should stay in the L2 while A streams past them: a
         // quarter of the L2 for them; at least 8 columns, all of them when that fits
@@ -823,27 +823,36 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
                 e->error = keep; // strides no tensor map takes: the exact kernel below
             }
         }
-        // e8m15 operands under the device order: each as two bf16 planes (exact), four partial products in one
-        // tensor-memory accumulator: exact products, f32 sums in the unit's order, as for bf16
-        if (mapped && device_order && e->encode && A.dtype == PSK_E8M15 && B.dtype == PSK_E8M15 && (L.kdtype == PSK_E8M15 || L.kdtype == PSK_F32)
+        // e8m15 or f32 operands under the device order: each as two or three bf16 planes (exact), every partial
+        // product in one tensor-memory accumulator: exact products, f32 sums in the unit's order, as for bf16
+        const bool wide_e = A.dtype == PSK_E8M15 && B.dtype == PSK_E8M15 && (L.kdtype == PSK_E8M15 || L.kdtype == PSK_F32);
+        const bool wide_f = A.dtype == PSK_F32 && B.dtype == PSK_F32 && L.kdtype == PSK_F32 && 2.0 * (double)g.m * (double)g.n * (double)g.k >= 1e8;
+        if (mapped && device_order && e->encode && (wide_e || wide_f)
             && g.batch == 1 && g.a_k == 1 && (g.b_k == 1 || g.b_n == 1) && g.c_col_lo == 1 && g.k % 64 == 0 && g.n % 8 == 0 && g.m >= 1 && g.n >= 8) {
             const bool bnm = g.b_k != 1;
-            uint16_t *pa = (uint16_t *)psk_exec_alloc(e, (size_t)g.m * 2 * g.k * 2), *pb = (uint16_t *)psk_exec_alloc(e, (size_t)g.n * 2 * g.k * 2);
+            const int planes = wide_f ? 3 : 2;
+            uint16_t *pa = (uint16_t *)psk_exec_alloc(e, (size_t)g.m * planes * g.k * 2), *pb = (uint16_t *)psk_exec_alloc(e, (size_t)g.n * planes * g.k * 2);
             if (pa && pb) {
-                k_split_e8m15<<<grid_for(e, g.m * g.k, 256, 8), 256, 0, e->stream>>>((const uint8_t *)A.p, g.m, g.k, g.a_row, pa, 2 * g.k, g.k);
-                if (bnm) k_split_e8m15<<<grid_for(e, g.n * g.k, 256, 8), 256, 0, e->stream>>>((const uint8_t *)B.p, g.k, g.n, g.b_k, pb, g.n, g.k * g.n);
-                else k_split_e8m15<<<grid_for(e, g.n * g.k, 256, 8), 256, 0, e->stream>>>((const uint8_t *)B.p, g.n, g.k, g.b_n, pb, 2 * g.k, g.k);
+                if (wide_f) {
+                    k_split_f32<<<grid_for(e, g.m * g.k, 256, 8), 256, 0, e->stream>>>((const float *)A.p, g.m, g.k, g.a_row, pa, planes * g.k, g.k);
+                    if (bnm) k_split_f32<<<grid_for(e, g.n * g.k, 256, 8), 256, 0, e->stream>>>((const float *)B.p, g.k, g.n, g.b_k, pb, g.n, g.k * g.n);
+                    else k_split_f32<<<grid_for(e, g.n * g.k, 256, 8), 256, 0, e->stream>>>((const float *)B.p, g.n, g.k, g.b_n, pb, planes * g.k, g.k);
+                } else {
+                    k_split_e8m15<<<grid_for(e, g.m * g.k, 256, 8), 256, 0, e->stream>>>((const uint8_t *)A.p, g.m, g.k, g.a_row, pa, planes * g.k, g.k);
+                    if (bnm) k_split_e8m15<<<grid_for(e, g.n * g.k, 256, 8), 256, 0, e->stream>>>((const uint8_t *)B.p, g.k, g.n, g.b_k, pb, g.n, g.k * g.n);
+                    else k_split_e8m15<<<grid_for(e, g.n * g.k, 256, 8), 256, 0, e->stream>>>((const uint8_t *)B.p, g.n, g.k, g.b_n, pb, planes * g.k, g.k);
+                }
                 e->kernels += 2;
                 psk_gemm pg;
                 memset(&pg, 0, sizeof pg);
                 pg.in_dtype = PSK_BF16; pg.out_dtype = L.out.dtype; pg.b_n_major = bnm ? 1 : 0; pg.guarded = L.guarded;
-                pg.m = g.m; pg.n = g.n; pg.k = 4 * g.k; pg.batch = 1; pg.batch_lo = 1;
-                pg.a_row = 2 * g.k; pg.a_lo = pg.a_hi = 0;
-                pg.b_row = bnm ? g.n : 2 * g.k; pg.b_lo = pg.b_hi = 0;
+                pg.m = g.m; pg.n = g.n; pg.k = (int64_t)planes * planes * g.k; pg.batch = 1; pg.batch_lo = 1;
+                pg.a_row = planes * g.k; pg.a_lo = pg.a_hi = 0;
+                pg.b_row = bnm ? g.n : planes * g.k; pg.b_lo = pg.b_hi = 0;
                 pg.c_row_lo_count = g.c_row_lo_count; pg.c_row_lo = g.c_row_lo; pg.c_row_hi = g.c_row_hi;
                 pg.c_col_lo_count = g.c_col_lo_count; pg.c_col_hi = g.c_col_hi; pg.c_lo = g.c_lo; pg.c_hi = g.c_hi;
                 std::string keep = e->error;
-                int r = launch_tc(e, pg, pa, pb, const_cast<void *>(L.out.p), L.ovf, nullptr, 0, 0, 0, g.k);
+                int r = launch_tc(e, pg, pa, pb, const_cast<void *>(L.out.p), L.ovf, nullptr, 0, 0, 0, g.k, planes);
                 psk_exec_free(e, pa); // the pool hands a buffer out again only to later work of the same stream
                 psk_exec_free(e, pb);
                 if (r == PSK_OK) {

@@ -47,11 +47,12 @@ struct Params {
     int64_t batch, batch_lo;
     int64_t tiles_m, tiles_n;
     int64_t panel; // tile-columns handed out together (tile_of)
-    // e8m15 operands as two bf16 planes each (x = hi + lo exactly): the operands hold [hi | lo] along the summed
-    // axis, 2·split_k long, and the kernel's k runs over 4·split_k: quarter q reads A's plane q >> 1 and B's
-    // plane q & 1, so the four exact partial products hi·hi', hi·lo', lo·hi', lo·lo' add up in one accumulator.
-    // 0: the operands are what they are.
+    // Wider operands as `planes` bf16 planes each (an e8m15 number is the exact sum of two bf16 numbers, an f32
+    // of three): the operands hold their planes side by side along the summed axis, planes·split_k long, and the
+    // kernel's k runs over planes²·split_k: part t reads A's plane t / planes and B's plane t % planes, so all
+    // the exact partial products add up in one accumulator. split_k = 0: the operands are what they are.
     int64_t split_k;
+    int32_t planes, pad_;
     int64_t c_row_lo_count, c_row_lo, c_row_hi;
     int64_t c_col_lo_count, c_col_hi;
     int64_t c_lo, c_hi;
@@ -269,8 +270,8 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
                     int ka = kb * BK, kbb = kb * BK;
                     if (P.split_k) {
                         const int q = (int)(ka / P.split_k), r = (int)(ka - q * P.split_k);
-                        ka = (q >> 1) * (int)P.split_k + r;
-                        kbb = (q & 1) * (int)P.split_k + r;
+                        ka = (q / P.planes) * (int)P.split_k + r;
+                        kbb = (q % P.planes) * (int)P.split_k + r;
                     }
                     tma_load_4d(smem_u32(smem_a + stage * S::A_BYTES), &map_a, fb, ka, m0, blo, bhi);
                     if (!P.b_n_major) {

@@ -1122,6 +1122,29 @@ __global__ void __launch_bounds__(256) k_init_normal(void *dst, int to, int64_t 
     }
 }
 
+
+// An f32 matrix as three bf16 planes, hi + mid + lo = x exactly (24 significant bits in three runs of eight; an
+// infinity or a NaN goes to hi whole). Element (r, c) of plane p is written at p * plane_stride + r * row_stride + c.
+__global__ void k_split_f32(const float *src, int64_t rows, int64_t cols, int64_t src_row, uint16_t *dst, int64_t row_stride, int64_t plane_stride)
+{
+    const int64_t total = rows * cols, step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step) {
+        const int64_t r = i / cols, c = i - r * cols;
+        const float x = src[r * src_row + c];
+        const uint32_t b = f32_bits(x);
+        const uint32_t hi = b >> 16;
+        uint32_t mid = 0, lo = 0;
+        if ((b & 0x7f800000u) != 0x7f800000u) {
+            const float r1 = __fsub_rn(x, bits_f32(hi << 16));
+            mid = f32_bits(r1) >> 16;
+            lo = f32_bits(__fsub_rn(r1, bits_f32(mid << 16))) >> 16;
+        }
+        uint16_t *d = dst + r * row_stride + c;
+        d[0] = (uint16_t)hi;
+        d[plane_stride] = (uint16_t)mid;
+        d[2 * plane_stride] = (uint16_t)lo;
+    }
+}
 } // namespace psk
 
 namespace psk {

@@ -120,3 +120,39 @@ def test_e8m15_contraction_on_tensor_cores(cuda, oracle, m, n, k, b_n_major):
     af, bf = widen(a8).reshape(m, k).astype(np.float64), widen(b8).reshape(b.shape).astype(np.float64)
     exact = (af @ bf if b_n_major else af @ bf.T).ravel()
     assert np.abs(got - exact).max() <= 4e-6 * k + 1e-5 + 2.0**-15 * np.abs(exact).max()
+
+
+@pytest.mark.parametrize("m,n,k,b_n_major", [(512, 512, 256, True), (384, 1000 // 8 * 8, 512, False), (1024, 1024, 1024, True)])
+def test_f32_contraction_on_tensor_cores(cuda, oracle, m, n, k, b_n_major):
+    """f32 operands under the device order: three bf16 planes each (x = hi + mid + lo exactly), nine partial products
+    in one f32 accumulator. Exact products; the result differs from the sequential f32 sum by the order of the
+    additions only."""
+    from presk_b200 import abi, launch_desc
+    rng = np.random.default_rng(m * 3 + n + k)
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    b = rng.standard_normal((k, n) if b_n_major else (n, k)).astype(np.float32)
+    a.ravel()[:5] = [0.0, -0.0, 1.0 + 2.0**-23, 3.0e-30, -1.7e10]
+    l = launch_desc(abi.OP_CONTRACT, abi.F32, [m, n], [k], order=abi.ORDER_DEVICE)
+    l.n_inputs = 2
+    l.inputs[0].dtype, l.inputs[0].numel, l.inputs[0].stride[0], l.inputs[0].stride[2] = abi.F32, m * k, k, 1
+    l.inputs[1].dtype, l.inputs[1].numel = abi.F32, n * k
+    if b_n_major:
+        l.inputs[1].stride[1], l.inputs[1].stride[2] = 1, n
+    else:
+        l.inputs[1].stride[1], l.inputs[1].stride[2] = k, 1
+    l.out.dtype, l.out.numel, l.out.stride[0], l.out.stride[1] = abi.F32, m * n, n, 1
+    pa, pb, pc = cuda.upload(a), cuda.upload(b), cuda.alloc(m * n * 4)
+    cuda.set_profiling(True)
+    cuda.run(l, [pa, pb, pc])
+    cuda.sync()
+    assert any(rec[0] == "k_gemm_tc" for rec in cuda.profile()), "the launch did not reach the tensor-core kernel"
+    cuda.set_profiling(False)
+    got = cuda.download(pc, m * n * 4).view(np.float32)
+    for p in (pa, pb, pc):
+        cuda.free(p)
+    exact = (a.astype(np.float64) @ b.astype(np.float64) if b_n_major else a.astype(np.float64) @ b.astype(np.float64).T).ravel()
+    scale = np.abs(a).max() * np.abs(b).max()
+    assert np.abs(got - exact).max() <= (4e-6 * k + 1e-5) * max(1.0, scale / 16)
+    # the nine partial products must all be there: an f32-accurate result, far below a bf16-plane's 2^-8
+    row = slice(5 * n, 6 * n)
+    assert np.abs(got[row] - exact[row]).max() <= 1e-4 * np.abs(exact[row]).max() + 1e-4
