@@ -1536,6 +1536,41 @@ struct psk_host {
         return results["l1.w"];
     }
 
+
+    // ===========================================================================
+    // examples/spec/concat/concat.psk `loss`: slices of an index window, the weights of three projections
+    // concatenated for one product, its result cut back into three slices, min, max and clamp element by
+    // element, a head, the mean cross-entropy. The sites' numbers are not pinned by a snapshot of the reference
+    // (they name where a realization file would put a type, nothing else); the value is (tests/run/concat_loss.snap).
+    // ===========================================================================
+    Tensor toy_loss(const Tensor &w)
+    {
+        const int64_t T = w.axes[1].len - 1, D = C("D");
+        Tensor ids = slice("inputs/%1", "seq", 0, T, w);
+        Tensor tgt = slice("targets/%1", "seq", 1, T + 1, w);
+        Tensor x = embed("Toy.apply/%3", param("tok"), ids);
+        x.axes.back().name = "model";
+        Tensor wq = param("qkv.wq"), wk = param("qkv.wk"), wv = param("qkv.wv");
+        for (Tensor *t : {&wq, &wk, &wv}) t->axes = {{"model", D}, {"out", D}};
+        Tensor w2 = concat("QKV.apply/%5", "out", wq, wk);
+        Tensor w3 = concat("QKV.apply/%7", "out", w2, wv);
+        Tensor y = dot("QKV.apply/%8", x, w3);
+        y.axes.back().name = "out";
+        Tensor q = slice("QKV.apply/%9", "out", 0, D, y), k = slice("QKV.apply/%10", "out", D, 2 * D, y), v = slice("QKV.apply/%11", "out", 2 * D, 3 * D, y);
+        // hardtanh(q) = min(max(q, -1), 1); leaky(k) = max(k, k * 0.01); g = hardtanh(q) * leaky(k) + min(v, q)
+        Tensor one = scalar("hardtanh/%2", 1.0);
+        Tensor neg = unary("hardtanh/%3", PSK_NEG, one);
+        Tensor c = scalar("leaky/%2", 0.01);
+        Tensor g = fused("Toy.apply/%12", {Bn(PSK_MAX, 0, 3), Bn(PSK_MIN, S(0), 4), Bn(PSK_MUL, 1, 5), Bn(PSK_MAX, 1, S(2)), Bn(PSK_MUL, S(1), S(3)), Bn(PSK_MIN, 2, 0), Bn(PSK_ADD, S(4), S(5))},
+                         {&q, &k, &v, &neg, &one, &c});
+        Tensor head = param("head");
+        head.axes = {{"out", D}, {"vocab", C("V")}};
+        Tensor logits = dot("Toy.apply/%14", g, head);
+        logits.axes.back().name = "vocab";
+        Tensor ce = cross_entropy("loss/%5", logits, tgt);
+        return reduce_all("loss/%6", PSK_REDUCE_MEAN, ce);
+    }
+
     // x·w then a row LayerNorm: %0 θ, %1 x, %2 w; %3 dot; LayerNorm.apply on it.
     Tensor contract_ln(const Tensor &x, const Tensor &w)
     {
@@ -1699,6 +1734,8 @@ struct psk_host {
         } else if (model == "rmsnorm") {
             need(1);
             return rmsnorm_spec(param("γ"), in[0], 1e-6);
+        } else if (model == "toy") {
+            if (entry == "loss") { need(1); return toy_loss(in[0]); }
         } else if (model == "mlp_spec") {
             if (entry == "mse") { need(2); return spec_mse(in[0], in[1]); }
             if (entry == "mse_grad") { need(2); return spec_mse_grad(in[0], in[1]); }
@@ -1720,6 +1757,7 @@ struct psk_host {
         else if (model == "llama" || model == "gpt") names = {"batch", "seq"};
         else if (model == "mlp") names = i == 0 ? std::vector<std::string>{"batch", "model"} : std::vector<std::string>{"batch"};
         else if (model == "mlp_spec") names = {"batch", "model"};
+        else if (model == "toy") names = {"batch", "seq"};
         else if (model == "layernorm" || model == "rmsnorm") {
             // ℝ[..., model: D] with a prefix of named axes
             static const char *prefix[] = {"batch", "seq", "a2", "a3", "a4", "a5", "a6"};
@@ -1783,7 +1821,7 @@ int psk_host_prepare(psk_host *h, const char *model, const char *consts)
 {
     HOST_TRY(h, {
         h->model = model ? model : "";
-        static const char *known[] = {"llama", "gpt", "mlp", "mlp_spec", "layernorm", "rmsnorm", "contract_ln", "dense"};
+        static const char *known[] = {"llama", "gpt", "mlp", "mlp_spec", "toy", "layernorm", "rmsnorm", "contract_ln", "dense"};
         bool ok = false;
         for (auto k : known) ok |= h->model == k;
         if (!ok) raise(PSK_E7001, "no model `" + h->model + "`");

@@ -5,6 +5,7 @@ Sources (paths within presk-lang/presk, read as text):
   tests/run/layernorm_apply.snap, rmsnorm_apply.snap   seed-0 outputs of the exact interpreter, 12 digits
   tests/run/mlp_mse.snap, mlp_mse_grad.snap             seed-0 loss and gradient of examples/spec/mlp/mlp.psk at D = 4, B = 2
   tests/run/rope_attention2.snap                        seed-0 output of examples/spec/rope/rope.psk `attention2` at B = 2, T = 8
+  tests/run/concat_loss.snap                            seed-0 loss of examples/spec/concat/concat.psk at B = 2, T = 8
   crates/presk-interp/src/key.rs:86-93                  the first four normal draws of the key seed 0 names
 Run:  python tests/golden/make_golden.py [path of the reference's tree]
 """
@@ -36,6 +37,8 @@ out["mlp_mse_grad"] = grad
 text = open(os.path.join(ref, "tests", "run", "rope_attention2.snap")).read().split("---")[-1]
 m = re.search(r"\[batch: (\d+), seq: (\d+), model: (\d+)\] (\[\[\[.*\]\]\])", text)
 out["rope_attention2"] = {"shape": [int(m.group(1)), int(m.group(2)), int(m.group(3))], "values": json.loads(m.group(4))}
+text = open(os.path.join(ref, "tests", "run", "concat_loss.snap")).read().split("---")[-1]
+out["concat_loss"] = float(re.search(r"= ([-0-9.e]+)", text).group(1))
 key_rs = open(os.path.join(ref, "crates", "presk-interp", "src", "key.rs")).read()
 m = re.search(r"assert_eq!\(first, \[([^\]]+)\]\)", key_rs)
 out["seed0_first_normals_bits"] = [int(x.strip(), 16) for x in m.group(1).split(",")]

@@ -286,3 +286,20 @@ def test_attention_entry_bit_exact(cuda, oracle, dtype):
             h.set_param(k, v)
         outs.append(h.call("attention", [x], (3, 24, 64), np.float32))
     assert_same_bits(*outs)
+
+
+def test_toy_loss_bit_exact(cuda, oracle):
+    """examples/spec/concat/concat.psk `loss` (index slices, concatenated weights, min/max/clamp, cross-entropy)."""
+    v, d = 64, 16
+    rng = np.random.default_rng(14)
+    params = {"tok": rng.standard_normal((v, d)) * 0.5, "qkv.wq": rng.standard_normal((d, d)), "qkv.wk": rng.standard_normal((d, d)),
+              "qkv.wv": rng.standard_normal((d, d)), "head": rng.standard_normal((d, v)) * 0.3}
+    w = rng.integers(0, v, size=(5, 33), dtype=np.int64)
+    for dtype in ("f32", "bf16"):
+        outs = []
+        for ex in (cuda, oracle.vtable()):
+            h = Host(ex, dtype).prepare("toy", V=v, D=d)
+            for k, p in params.items():
+                h.set_param(k, p)
+            outs.append(h.call("loss", [w], (), np.float32))
+        assert_same_bits(np.atleast_1d(outs[0]), np.atleast_1d(outs[1]))

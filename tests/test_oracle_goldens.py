@@ -131,3 +131,24 @@ def test_rope_attention_golden_on_the_oracle(oracle, ref):
     got = h.call("attention", [x], (b, t, d), np.float32)
     want = np.array(g["values"])
     np.testing.assert_allclose(got, want, rtol=0, atol=2e-8)  # outputs are of magnitude 8e-3: f32 accuracy
+
+
+def indices_at(ref, seed, path, bound, n):
+    """Indices below `bound` as an idx input is synthesized (run.rs:327-333): floor(uniform · bound)."""
+    return (draws_at(ref, "uniform", seed, path, n) * bound).astype(np.int64)
+
+
+def test_concat_loss_golden_on_the_oracle(oracle, ref):
+    """tests/run/concat_loss.snap: examples/spec/concat/concat.psk `loss` at B = 2, T = 8, seed 0 (slices of an index
+    window, concatenated weights, min/max/clamp groups, embed, cross-entropy, mean). θ is the first argument's key
+    through Toy.init (its own parameters tok and head first, then the module it uses, whose init draws wq, wk, wv),
+    the window the second's."""
+    v, d, b, t = 64, 16, 2, 8
+    h = Host(oracle.vtable(), "f32").prepare("toy", V=v, D=d)
+    h.set_param("tok", (draws_at(ref, "normal", 0, [0, 0], v * d) * 0.02).reshape(v, d))
+    for i, name in enumerate(("wq", "wk", "wv")):
+        h.set_param("qkv." + name, (draws_at(ref, "normal", 0, [0, 2, i], d * d) * 0.02).reshape(d, d))
+    h.set_param("head", (draws_at(ref, "normal", 0, [0, 1], d * v) * 0.02).reshape(d, v))
+    w = indices_at(ref, 0, [1], v, b * (t + 1)).reshape(b, t + 1)
+    got = float(h.call("loss", [w], (), np.float32))
+    assert abs(got - GOLD["concat_loss"]) <= 2e-6 * GOLD["concat_loss"], (got, GOLD["concat_loss"])
