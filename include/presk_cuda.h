@@ -101,13 +101,19 @@ typedef enum {
                              one after the other under the launch's order (the oracle runs exactly those); an
                              executor that takes it must give their bits. No counterpart among the reference's
                              kernels: its groups never cross a reduction. */
-    PSK_OP_ROPE = 13      /* the rotation of `rope` (examples/coverage/llama.psk:66-72) as one launch: with x read as
+    PSK_OP_ROPE = 13,     /* the rotation of `rope` (examples/coverage/llama.psk:66-72) as one launch: with x read as
                              (.., seq, pair = 2, rot) and c, s over (seq, rot),
                                out[.., 0, r] = x[.., 0, r]*c - x[.., 1, r]*s,  out[.., 1, r] = x[.., 1, r]*c + x[.., 0, r]*s,
                              every product rounded to f32 before the sum, the sums rounded once to the result's
                              type: the reference's two slices, two groups of three steps and concatenation, for the
                              case that all of their sites are stored in x's type (the host offers nothing else).
                              Space: the axes of the result. Inputs: x, c, s. */
+    PSK_OP_CONTRACT_ADD = 14 /* a contraction and the addition of a third operand to its result as one launch: the
+                             reference's `ein`/`dot` followed by a residual `add` (examples/coverage/llama.psk:117-118).
+                             Inputs 0 and 1 as in PSK_OP_CONTRACT, input 2 over the outer axes. iparam[1]: the storage
+                             type of the contraction's own site; dtype: the sum's. The value is DEFINED as that of the
+                             two launches (contraction stored in its type, then in[2] + it); an executor that takes
+                             it must give their bits under the launch's order. */
 } psk_op;
 
 /* Elementary operations of a fusion group's steps (lower.rs:184-226). */

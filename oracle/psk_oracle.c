@@ -649,8 +649,49 @@ static int rope_unfused(const psk_launch *l, void *const *table, uint32_t *overf
     return rc;
 }
 
+/* PSK_OP_CONTRACT_ADD: the contraction into a buffer of its own site's type, then the addition, two launches. */
+static int contract_add_unfused(const psk_launch *l, void *const *table, uint32_t *overflow)
+{
+    if (l->n_inputs != 3) return PSK_E7001;
+    const int no = l->n_outer, dc = (int)l->iparam[1];
+    int64_t total = 1;
+    for (int a = 0; a < no; ++a) total *= l->dims[a];
+    void *tmp = malloc((size_t)(total ? total : 1) * elem_bytes(dc));
+    uint32_t ovf = 0, o1 = 0;
+    psk_launch m = *l;
+    m.op = PSK_OP_CONTRACT; m.n_inputs = 2; m.dtype = dc;
+    attn_contiguous(&m.out, dc, l->dims, no, -1);
+    int scale_slot = 4;
+    void *t1[5] = {table[0], table[1], tmp, NULL, NULL};
+    int extra = 3;
+    for (int i = 0; i < 2; ++i)
+        if (l->in[i].dtype == PSK_I8 && !l->in[i].affine) t1[extra++] = table[scale_slot++];
+    int rc = psk_oracle_run(&m, t1, &o1);
+    ovf |= o1;
+    if (rc == PSK_OK) {
+        psk_launch a;
+        memset(&a, 0, sizeof a);
+        a.name = "contract_add: add"; a.op = PSK_OP_FUSED; a.dtype = l->dtype; a.order = l->order; a.guarded = l->guarded;
+        a.n_inputs = 2; a.n_outer = no;
+        memcpy(a.dims, l->dims, sizeof a.dims);
+        a.in[0] = l->in[2];
+        for (int k = no; k < PSK_MAX_AXES; ++k) a.in[0].stride[k] = 0;
+        attn_contiguous(&a.in[1], dc, l->dims, no, -1);
+        a.out = l->out;
+        a.n_steps = 1;
+        a.steps[0].prim = PSK_ADD; a.steps[0].nargs = 2; a.steps[0].src[0] = 0; a.steps[0].src[1] = 1;
+        void *t2[3] = {table[2], tmp, table[3]};
+        rc = psk_oracle_run(&a, t2, &o1);
+        ovf |= o1;
+    }
+    free(tmp);
+    if (overflow) *overflow = ovf;
+    return rc;
+}
+
 int psk_oracle_run(const psk_launch *l, void *const *table, uint32_t *overflow)
 {
+    if (l->op == PSK_OP_CONTRACT_ADD) return contract_add_unfused(l, table, overflow);
     if (l->op == PSK_OP_ROPE) return rope_unfused(l, table, overflow);
     if (l->op == PSK_OP_ATTENTION) return attention_unfused(l, table, overflow);
     if (l->op == PSK_OP_RMSNORM) return rmsnorm_unfused(l, table, overflow);

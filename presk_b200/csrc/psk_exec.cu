@@ -328,7 +328,7 @@ bool make_map(psk_exec *e, CUtensorMap *map, const void *base, int f16, uint64_t
     return r == CUDA_SUCCESS;
 }
 
-int launch_tc(psk_exec *e, const psk_gemm &g, const void *a, const void *b, void *c, uint32_t *flag, const float *col_scale = nullptr, int64_t cs_stride = 0, int64_t cs_lo = 0, int64_t cs_hi = 0, int64_t split_k = 0, int planes = 2)
+int launch_tc(psk_exec *e, const psk_gemm &g, const void *a, const void *b, void *c, uint32_t *flag, const float *col_scale = nullptr, int64_t cs_stride = 0, int64_t cs_lo = 0, int64_t cs_hi = 0, int64_t split_k = 0, int planes = 2, const void *addend = nullptr)
 {
     if (!e->encode) return fail(e, PSK_E10001, "cuTensorMapEncodeTiled is not available from this driver");
     const bool f16 = g.in_dtype == PSK_F16;
@@ -347,6 +347,7 @@ int launch_tc(psk_exec *e, const psk_gemm &g, const void *a, const void *b, void
     P.tiles_m = (g.m + tc::BM - 1) / tc::BM;
     P.tiles_n = (g.n + bn - 1) / bn;
     P.split_k = split_k; P.planes = planes; P.pad_ = 0;
+    P.addend = addend;
     {
         // a panel's columns of B (bn·k elements each) should stay in the L2 while A streams past them: a
         // quarter of the L2 for them; at least 8 columns, all of them when that fits
@@ -365,6 +366,7 @@ int launch_tc(psk_exec *e, const psk_gemm &g, const void *a, const void *b, void
     P.scale = g.scale; P.scale_on = g.scale_on;
     P.col_scale = col_scale; P.col_scale_stride = cs_stride; P.col_scale_lo = cs_lo; P.col_scale_hi = cs_hi;
     P.ovf = flag; P.status = e->status;
+    if (addend && !(P.vec_ok && g.out_dtype == PSK_BF16)) return fail(e, PSK_E7001, "tensor-core contraction: an addend needs the staged bf16 epilogue");
     if (!e->tc_attr_set) {
         CUDA_TRY(e, cudaFuncSetAttribute(tc::k_gemm_tc<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::Smem<256>::TOTAL));
         CUDA_TRY(e, cudaFuncSetAttribute(tc::k_gemm_tc<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::Smem<128>::TOTAL));
@@ -659,7 +661,7 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
     const bool device_order = l->order == PSK_ORDER_DEVICE;
     bool any_affine = l->out.affine != 0;
     for (int i = 0; i < l->n_inputs; ++i) any_affine = any_affine || l->in[i].affine != 0;
-    if (any_affine && l->op != PSK_OP_FUSED && l->op != PSK_OP_CONTRACT && l->op != PSK_OP_CONVERT)
+    if (any_affine && l->op != PSK_OP_FUSED && l->op != PSK_OP_CONTRACT && l->op != PSK_OP_CONVERT && l->op != PSK_OP_CONTRACT_ADD)
         return fail(e, PSK_E7005, std::string(l->name ? l->name : "?") + ": values in an affine format are read and written by elementwise groups, contractions and conversions only");
     if (any_affine && l->op == PSK_OP_CONTRACT && !l->int_accum)
         return fail(e, PSK_E7005, std::string(l->name ? l->name : "?") + ": a contraction over affine values counts its sums in integers (product and accum i32) on this executor");
@@ -1080,6 +1082,35 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
         R.out = (uint16_t *)const_cast<void *>(L.out.p); R.rows = rows; R.seq = (int32_t)T; R.rotv = (int32_t)(rot / 8);
         k_rope_bf16<<<grid_for(e, rows * (rot / 8), 256, 8), 256, 0, e->stream>>>(R);
         e->kernels += 1;
+        break;
+    }
+    case PSK_OP_CONTRACT_ADD: {
+        const std::string nm = l->name ? l->name : "contract+add";
+        if (L.n_in != 3 || l->int_accum) { rc = fail(e, PSK_E7001, nm + ": two operands of a contraction and an addend"); break; }
+        DevLaunch L2 = L;
+        L2.n_in = 2;
+        GemmMap g;
+        const bool mapped = map_gemm(L2, g);
+        const DevOperand &A = L.in[0], &B = L.in[1], &X = L.in[2];
+        bool fits = mapped && device_order && e->encode && A.dtype == PSK_BF16 && B.dtype == PSK_BF16 && X.dtype == PSK_BF16 && !any_affine
+            && l->dtype == PSK_BF16 && l->out.dtype == PSK_BF16 && l->iparam[1] == PSK_BF16
+            && g.a_k == 1 && (g.b_k == 1 || g.b_n == 1) && aligned16(A.p) && aligned16(B.p) && aligned16(X.p) && g.c_col_lo == 1 && g.m >= 1 && g.n >= 8 && g.k >= 8;
+        for (int a = 0; a < L.n_outer && fits; ++a) fits = L.dims[a] == 1 || X.stride[a] == L.out.stride[a]; // the addend walks the space as the result does
+        if (!fits) { rc = fail(e, PSK_E7005, nm + ": the merged contraction and addition run on the tensor cores, bf16 throughout, the addend laid out as the result"); break; }
+        psk_gemm pg;
+        memset(&pg, 0, sizeof pg);
+        pg.in_dtype = PSK_BF16; pg.out_dtype = PSK_BF16; pg.b_n_major = g.b_k == 1 ? 0 : 1; pg.guarded = 0;
+        pg.m = g.m; pg.n = g.n; pg.k = g.k; pg.batch = g.batch; pg.batch_lo = g.batch_lo;
+        pg.a_row = g.a_row; pg.a_lo = g.a_lo; pg.a_hi = g.a_hi;
+        pg.b_row = pg.b_n_major ? g.b_k : g.b_n; pg.b_lo = g.b_lo; pg.b_hi = g.b_hi;
+        pg.c_row_lo_count = g.c_row_lo_count; pg.c_row_lo = g.c_row_lo; pg.c_row_hi = g.c_row_hi;
+        pg.c_col_lo_count = g.c_col_lo_count; pg.c_col_hi = g.c_col_hi; pg.c_lo = g.c_lo; pg.c_hi = g.c_hi;
+        if (g.m == 1) pg.a_row = g.k;
+        int r = launch_tc(e, pg, A.p, B.p, const_cast<void *>(L.out.p), L.ovf, nullptr, 0, 0, 0, 0, 2, X.p);
+        if (r == PSK_E7001) { rc = fail(e, PSK_E7005, nm + ": " + e->error); break; } // strides no tensor map or staged epilogue takes: the caller's two launches
+        rc = r;
+        e->last_kernel = "k_gemm_tc";
+        e->last_flops = 2.0 * (double)g.m * (double)g.n * (double)g.k * (double)g.batch;
         break;
     }
     case PSK_OP_XENT: {

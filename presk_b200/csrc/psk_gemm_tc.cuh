@@ -53,6 +53,9 @@ struct Params {
     // the exact partial products add up in one accumulator. split_k = 0: the operands are what they are.
     int64_t split_k;
     int32_t planes, pad_;
+    // PSK_OP_CONTRACT_ADD: bf16 values laid out exactly as C, added to the result after it has been rounded to
+    // bf16 as its own site would store it; the sum is rounded to bf16 again. Staged bf16 epilogue only.
+    const void *addend;
     int64_t c_row_lo_count, c_row_lo, c_row_hi;
     int64_t c_col_lo_count, c_col_hi;
     int64_t c_lo, c_hi;
@@ -374,6 +377,11 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
 #pragma unroll
                             for (int q = 0; q < 4; ++q) {
                                 uint32_t u[4];
+                                uint4 add8 = make_uint4(0u, 0u, 0u, 0u);
+                                if (P.addend && row < P.m && col + half * 32 + q * 8 < P.n) {
+                                    const int64_t cc = col + half * 32 + q * 8;
+                                    add8 = *reinterpret_cast<const uint4 *>((const uint16_t *)P.addend + row_off + (cc / P.c_col_lo_count) * P.c_col_hi + (cc % P.c_col_lo_count));
+                                }
 #pragma unroll
                                 for (int i = 0; i < 4; ++i) {
                                     float x0 = __uint_as_float(half ? vb[q * 8 + 2 * i] : va[q * 8 + 2 * i]);
@@ -392,6 +400,11 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
                                     // comes out canonical (its sign and payload are not kept on this path)
                                     if (P.out_dtype == PSK_BF16) {
                                         u[i] = pack_bf16x2_hw(x0, x1);
+                                        if (P.addend) {
+                                            // this thread's row, the eight columns of (half, q): 16 bytes of the addend
+                                            const uint32_t aw = i == 0 ? add8.x : i == 1 ? add8.y : i == 2 ? add8.z : add8.w;
+                                            u[i] = pack_bf16x2_hw(__fadd_rn(bits_f32(aw << 16), bits_f32(u[i] << 16)), __fadd_rn(bits_f32(aw & 0xffff0000u), bits_f32(u[i] & 0xffff0000u)));
+                                        }
                                     } else {
                                         ovf |= overflows(x0, kF16Overflow) | overflows(x1, kF16Overflow);
                                         u[i] = pack_f16x2_hw(x0, x1);

@@ -642,7 +642,9 @@ struct psk_host {
     // ---- contractions ---------------------------------------------------------------
     // lower.rs:586-636: the iteration space is the output's axes, then the summed
     // ones in the order the operands first name them.
-    Tensor ein(const std::string &site, const std::vector<std::string> &output, const std::vector<std::vector<std::string>> &operands, const std::vector<const Tensor *> &ins, const std::string &name_override = "")
+    // `addend`, `add_site`: the residual addition that follows the contraction in the source (`x + f(..)`), issued
+    // with it as one launch under merged launches when the executor takes it, else as the `add` it is.
+    Tensor ein(const std::string &site, const std::vector<std::string> &output, const std::vector<std::vector<std::string>> &operands, const std::vector<const Tensor *> &ins, const std::string &name_override = "", const Tensor *addend = nullptr, const std::string &add_site = "")
     {
         std::vector<std::pair<std::string, int64_t>> names;
         for (size_t t = 0; t < ins.size(); ++t) {
@@ -695,12 +697,31 @@ struct psk_host {
             for (size_t i = 0; i < output.size(); ++i) name += (i ? ", " : "") + output[i];
             name += "]";
         }
+        if (addend && rz.merged_launches && !calibrating && !out.affine && !addend->affine && !rz.scaled.count(add_site) && !l.int_accum) {
+            std::vector<int> amap;
+            if (align(addend->axes, out_axes, amap) && addend->axes.size() == out_axes.size()) {
+                psk_launch m = l;
+                m.op = PSK_OP_CONTRACT_ADD;
+                m.iparam[1] = d;
+                m.dtype = site_dtype(add_site);
+                Tensor sum = fresh(out_axes, m.dtype);
+                std::vector<int64_t> st, ss;
+                view(*addend, amap, (int)all.size(), st, ss);
+                set_operand(m.in[2], *addend, st, ss);
+                set_operand(m.out, sum, contiguous(out_axes), {});
+                std::vector<const Tensor *> ins3 = ins;
+                ins3.push_back(addend);
+                if (run(m, name + "+add", ins3, sum, true)) return sum;
+                site_dtype(site);
+            }
+        }
         run(l, name, ins, out);
+        if (addend) return binary(add_site, PSK_ADD, *addend, out);
         return out;
     }
 
     // lower.rs:481-513: x[..., K] · w[K, rest...]
-    Tensor dot(const std::string &site, const Tensor &x, const Tensor &w)
+    Tensor dot(const std::string &site, const Tensor &x, const Tensor &w, const Tensor *addend = nullptr, const std::string &add_site = "")
     {
         if (x.axes.empty() || w.axes.empty()) raise(PSK_E7001, "dot: both operands need at least one axis");
         if (x.axes.back().len != w.axes[0].len) raise(PSK_E7001, "dot: contracted axes differ (" + std::to_string(x.axes.back().len) + " vs " + std::to_string(w.axes[0].len) + ")");
@@ -711,8 +732,10 @@ struct psk_host {
         xs.push_back("k");
         ws.push_back("k");
         for (size_t i = 1; i < w.axes.size(); ++i) { ws.push_back("w" + std::to_string(i)); os.push_back(ws.back()); out_axes.push_back(w.axes[i]); }
-        Tensor out = ein(site, os, {xs, ws}, {&x, &w}, "dot");
-        out.axes = out_axes;
+        Tensor plain;
+        if (addend) { plain = *addend; for (auto &a : plain.axes) a.name.clear(); } // aligned by position, as `add` aligns equal shapes
+        Tensor out = ein(site, os, {xs, ws}, {&x, &w}, "dot", addend ? &plain : nullptr, add_site);
+        out.axes = addend ? addend->axes : out_axes;
         return out;
     }
 
@@ -1263,7 +1286,7 @@ struct psk_host {
     }
 
     // llama.psk:86-110. %0 θ, %1 x, %2 mask, %3 φ.
-    Tensor llama_attention(int64_t l, const Tensor &x, const Tensor &mask, const Tensor &phi)
+    Tensor llama_attention(int64_t l, const Tensor &x, const Tensor &mask, const Tensor &phi, const Tensor *residual = nullptr, const std::string &add_site = "")
     {
         const std::string f = "Attention.apply";
         const int64_t D = C("D"), H = C("H"), G = C("G", H), HD = D / H, P = H / G;
@@ -1301,11 +1324,11 @@ struct psk_host {
             o = ein(f + "/%22", {"batch", "seq", "groups", "per", "hd"}, {{"batch", "groups", "per", "seq", "seq2"}, {"batch", "seq2", "groups", "hd"}}, {&a, &v});
         }
         Tensor w2 = split(split(wo, "headhd", {{"groups", G}, {"rest", P * HD}}), "rest", {{"per", P}, {"hd", HD}});
-        return ein(f + "/%26", {"batch", "seq", "model"}, {{"batch", "seq", "groups", "per", "hd"}, {"groups", "per", "hd", "model"}}, {&o, &w2});
+        return ein(f + "/%26", {"batch", "seq", "model"}, {{"batch", "seq", "groups", "per", "hd"}, {"groups", "per", "hd", "model"}}, {&o, &w2}, "", residual, add_site);
     }
 
     // llama.psk:43,45-50. silu: %0 x, %1 sigmoid, %2 mul.
-    Tensor llama_swiglu(int64_t l, const Tensor &x)
+    Tensor llama_swiglu(int64_t l, const Tensor &x, const Tensor *residual = nullptr, const std::string &add_site = "")
     {
         const std::string f = "SwiGLU.apply";
         Tensor wg = layer(param("blocks.ff.gate.w"), l), wu = layer(param("blocks.ff.up.w"), l), wd = layer(param("blocks.ff.down.w"), l);
@@ -1317,16 +1340,16 @@ struct psk_host {
             Tensor u = dot("Dense.apply/%3", x, wu);
             if (u.dtype == ds && !u.affine) {
                 Tensor h = fused(f + "/%7", {U(PSK_SIGMOID, 0), Bn(PSK_MUL, 0, S(0)), U(PSK_ROUND, S(1), ds), Bn(PSK_MUL, S(2), 1)}, {&g, &u});
-                return dot("Dense.apply/%3", h, wd);
+                return dot("Dense.apply/%3", h, wd, residual, add_site);
             }
             Tensor sg = fused("silu/%2", {U(PSK_SIGMOID, 0), Bn(PSK_MUL, 0, S(0))}, {&g});
             Tensor h = binary(f + "/%7", PSK_MUL, sg, u);
-            return dot("Dense.apply/%3", h, wd);
+            return dot("Dense.apply/%3", h, wd, residual, add_site);
         }
         Tensor sg = fused("silu/%2", {U(PSK_SIGMOID, 0), Bn(PSK_MUL, 0, S(0))}, {&g});
         Tensor u = dot("Dense.apply/%3", x, wu);
         Tensor h = binary(f + "/%7", PSK_MUL, sg, u);
-        return dot("Dense.apply/%3", h, wd);
+        return dot("Dense.apply/%3", h, wd, residual, add_site);
     }
 
     // llama.psk:112-119. %0 θ, %1 x, %2 mask, %3 φ.
@@ -1334,11 +1357,10 @@ struct psk_host {
     {
         const std::string f = "Block.apply";
         Tensor n1 = llama_rmsnorm(layer(param("blocks.n1.γ"), l), x);
-        Tensor at = llama_attention(l, n1, mask, phi);
-        Tensor x1 = binary(f + "/%8", PSK_ADD, x, at);
+        // the two residual additions follow a contraction each; the contraction takes them along (see `ein`)
+        Tensor x1 = llama_attention(l, n1, mask, phi, &x, f + "/%8");
         Tensor n2 = llama_rmsnorm(layer(param("blocks.n2.γ"), l), x1);
-        Tensor ff = llama_swiglu(l, n2);
-        return binary(f + "/%13", PSK_ADD, x1, ff);
+        return llama_swiglu(l, n2, &x1, f + "/%13");
     }
 
     // llama.psk:121-134. %0 θ, %1 ids.
