@@ -314,5 +314,253 @@ __global__ void __launch_bounds__(THREADS, 1) k_attn_fwd(const __grid_constant__
     }
 }
 
+
+// ---------------------------------------------------------------------------
+// The same computation with key blocks of 64 and half the threads, sized so that two CTAs share an SM (96 KB of
+// shared memory, 256 tensor-memory columns, 320 threads each): while one CTA waits (for its first tiles, for a
+// product, at its end), the other computes. K and V blocks travel through one ring of three 16 KB stages in the
+// order the products use them; P is single-buffered; a row is held by two threads (32 of a block's 64 keys each).
+// ---------------------------------------------------------------------------
+namespace v2 {
+constexpr int BN2 = 64;
+constexpr int SOFTMAX_WARPS2 = 8;
+constexpr int THREADS2 = (2 + SOFTMAX_WARPS2) * 32;
+constexpr int KV_STAGE = BN2 * HD * 2;        // 16 KB: two halves of [64 keys x 64 hd]
+constexpr int KV_HALF = BN2 * 64 * 2;         // 8 KB
+constexpr int RING = 3;
+constexpr int P_BYTES = BM * BN2 * 2;         // 16 KB: [128 rows x 64 keys]
+constexpr int SMEM_TILES2 = TILE + RING * KV_STAGE + P_BYTES;
+constexpr int SMEM_TOTAL2 = SMEM_TILES2 + 256 + 1024;
+
+PSK_DEV void softmax_sync2()
+{
+    asm volatile("bar.sync 1, %0;" ::"n"(SOFTMAX_WARPS2 * 32) : "memory");
+}
+
+__global__ void __launch_bounds__(THREADS2, 2) k_attn_fwd2(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const __grid_constant__ Params P)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t *sQ = smem, *sR = smem + TILE, *sP = smem + TILE + RING * KV_STAGE;
+    uint64_t *bars = (uint64_t *)(smem + SMEM_TILES2);
+    // 0 q_full; 1..3 ring full; 4..6 ring empty; 7,8 s_full; 9,10 s_free; 11 p_full; 12 p_free; 13 o_full
+    uint32_t *tmem_slot = (uint32_t *)(bars + 14);
+    volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
+    const uint32_t bar0 = tc::smem_u32(bars);
+    auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nqb = (int)(P.T / BM);
+    const int qb = nqb - 1 - (int)blockIdx.x; // the longest rows first
+    const int g = blockIdx.y, b = blockIdx.z;
+    const int gk = g / P.per;
+    const int nkb = P.causal ? 2 * (qb + 1) : (int)(P.T / BN2);
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int i = 0; i < 14; ++i) tc::mbar_init(bar(i), (i == 9 || i == 10 || i == 11) ? SOFTMAX_WARPS2 : 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc::smem_u32(tmem_slot)), "r"(256) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t tS0 = tmem, tO = tmem + 128;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            bool ok = true;
+            tc::mbar_expect_tx(bar(0), TILE);
+            tc::tma_load_4d(tc::smem_u32(sQ), &map_q, bar(0), 0, qb * BM, g, b);
+            tc::tma_load_4d(tc::smem_u32(sQ + HALF), &map_q, bar(0), 64, qb * BM, g, b);
+            uint32_t ps = 0, pph = 0;
+            auto load = [&](const CUtensorMap *map, int kb) -> bool {
+                if (!tc::mbar_wait(bar(4 + ps), pph ^ 1u, abort_flag, P.status, 0x41u)) return false;
+                tc::mbar_expect_tx(bar(1 + ps), KV_STAGE);
+                tc::tma_load_4d(tc::smem_u32(sR + ps * KV_STAGE), map, bar(1 + ps), 0, kb * BN2, gk, b);
+                tc::tma_load_4d(tc::smem_u32(sR + ps * KV_STAGE + KV_HALF), map, bar(1 + ps), 64, kb * BN2, gk, b);
+                if (++ps == RING) { ps = 0; pph ^= 1u; }
+                return true;
+            };
+            for (int kb = 0; kb < nkb && ok; ++kb) ok = load(&map_k, kb);
+            if (ok) ok = load(&map_k, 0);
+            for (int kb = 0; kb < nkb && ok; ++kb) {
+                if (kb + 1 < nkb) ok = load(&map_k, kb + 1);
+                if (ok) ok = load(&map_v, kb);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc_qk = tc::instr_desc(0, 0, BN2), idesc_pv = tc::instr_desc(0, 1, HD);
+            bool ok = tc::mbar_wait(bar(0), 0u, abort_flag, P.status, 0x51u);
+            uint32_t rs = 0, rph = 0, qk_count = 0;
+            auto issue_qk = [&]() -> bool {
+                const uint32_t sb = qk_count & 1u, sph = (qk_count >> 1) & 1u;
+                if (!tc::mbar_wait(bar(1 + rs), rph, abort_flag, P.status, 0x52u)) return false;
+                if (!tc::mbar_wait(bar(9 + sb), sph ^ 1u, abort_flag, P.status, 0x53u)) return false;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t qa = tc::smem_u32(sQ), ka = tc::smem_u32(sR + rs * KV_STAGE);
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk) {
+                    const uint32_t qoff = (uint32_t)(kk >> 2) * HALF + (uint32_t)(kk & 3) * 32u;
+                    const uint32_t koff = (uint32_t)(kk >> 2) * KV_HALF + (uint32_t)(kk & 3) * 32u;
+                    tc::umma(tS0 + sb * 64u, tc::smem_desc(qa + qoff, 16, 1024), tc::smem_desc(ka + koff, 16, 1024), idesc_qk, kk != 0 ? 1u : 0u);
+                }
+                tc::umma_commit(bar(4 + rs));
+                tc::umma_commit(bar(7 + sb));
+                if (++rs == RING) { rs = 0; rph ^= 1u; }
+                ++qk_count;
+                return true;
+            };
+            for (int kb = 0; kb < nkb && ok; ++kb) ok = issue_qk();
+            if (ok) ok = issue_qk();
+            for (int kb = 0; kb < nkb && ok; ++kb) {
+                if (kb + 1 < nkb) ok = issue_qk();
+                if (!ok) break;
+                ok = tc::mbar_wait(bar(11), (uint32_t)(kb & 1), abort_flag, P.status, 0x54u);
+                if (!ok) break;
+                ok = tc::mbar_wait(bar(1 + rs), rph, abort_flag, P.status, 0x55u);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t pa = tc::smem_u32(sP), va = tc::smem_u32(sR + rs * KV_STAGE);
+#pragma unroll
+                for (int kk = 0; kk < BN2 / 16; ++kk)
+                    tc::umma(tO, tc::smem_desc(pa + (uint32_t)kk * 32u, 16, 1024), tc::smem_desc(va + (uint32_t)kk * 2048u, KV_HALF, 1024), idesc_pv, (kb | kk) != 0 ? 1u : 0u);
+                tc::umma_commit(bar(4 + rs)); // the V block is free
+                tc::umma_commit(bar(12));     // and P may be overwritten
+                if (++rs == RING) { rs = 0; rph ^= 1u; }
+            }
+            if (ok) tc::umma_commit(bar(13));
+        }
+    } else {
+        const int quad = warp & 3;
+        const int ch = (warp - 2) >> 2;      // which 32 of a block's 64 keys, and which half of the output's columns
+        const int row = quad * 32 + lane;
+        const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+        const float rtv = bf16_round(load_real(P.rt, P.rt_dtype, 0));
+        const float rr = __frcp_rn(rtv);
+        float *xch = reinterpret_cast<float *>(sP);
+        bool ok = true;
+        uint32_t qk_count = 0;
+        const bool want_max = !(rtv < 0.0f);
+        float ext = want_max ? -INFINITY : INFINITY;
+        // the last allowed key among this thread's 32 of block kb (31 or more: all of them; negative: none)
+        auto limit = [&](int kb) { return P.causal ? (qb * BM + row) - (kb * BN2 + ch * 32) : 31; };
+        for (int kb = 0; kb < nkb && ok; ++kb) {
+            const uint32_t sb = qk_count & 1u, sph = (qk_count >> 1) & 1u;
+            ok = tc::mbar_wait(bar(7 + sb), sph, abort_flag, P.status, 0x61u);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint32_t v[32];
+            tc::tmem_ld32(tS0 + lane_base + sb * 64u + (uint32_t)(ch * 32), v);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(bar(9 + sb));
+            ++qk_count;
+            const int lim = limit(kb);
+            if (want_max) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    if (i <= lim) ext = fmaxf(ext, __uint_as_float(v[i]));
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    if (i <= lim) ext = fminf(ext, __uint_as_float(v[i]));
+            }
+        }
+        xch[ch * 128 + row] = ext;
+        softmax_sync2();
+        ext = want_max ? fmaxf(xch[row], xch[128 + row]) : fminf(xch[row], xch[128 + row]);
+        softmax_sync2();
+        const float m = bf16_round(__fdiv_rn(bf16_round(ext), rtv));
+        const float LOG2E = 1.44269504f;
+        const float m2 = __fmul_rn(m, LOG2E);
+        float z = 0.0f;
+        for (int kb = 0; kb < nkb && ok; ++kb) {
+            const uint32_t sb = qk_count & 1u, sph = (qk_count >> 1) & 1u;
+            ok = tc::mbar_wait(bar(7 + sb), sph, abort_flag, P.status, 0x62u);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint32_t v[32];
+            tc::tmem_ld32(tS0 + lane_base + sb * 64u + (uint32_t)(ch * 32), v);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(bar(9 + sb));
+            ++qk_count;
+            const int lim = limit(kb);
+            uint32_t packed[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                // bf16(S), then bf16(bf16(S) / rt) by the reciprocal (exact for bf16 operands: see k_attn_fwd)
+                const uint32_t s1 = pack_bf16x2_hw(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+                const float d0 = __fmul_rn(bits_f32(s1 << 16), rr), d1 = __fmul_rn(bits_f32(s1 & 0xffff0000u), rr);
+                const uint32_t s2 = pack_bf16x2_hw(d0, d1);
+                float e0 = fast_exp2(__fmaf_rn(bits_f32(s2 << 16), LOG2E, -m2));
+                float e1 = fast_exp2(__fmaf_rn(bits_f32(s2 & 0xffff0000u), LOG2E, -m2));
+                if (lim < 31) {
+                    if (2 * i > lim) e0 = 0.0f;
+                    if (2 * i + 1 > lim) e1 = 0.0f;
+                }
+                z += e0;
+                z += e1;
+                packed[i] = pack_bf16x2_hw(e0, e1);
+            }
+            ok = tc::mbar_wait(bar(12), (uint32_t)(kb & 1) ^ 1u, abort_flag, P.status, 0x63u); // P of the block before was read
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            uint8_t *dst = sP + row * 128;
+            const int u0 = ch * 4;
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                *reinterpret_cast<uint4 *>(dst + (((u0 + u) ^ (row & 7)) << 4)) = make_uint4(packed[4 * u], packed[4 * u + 1], packed[4 * u + 2], packed[4 * u + 3]);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(bar(11));
+        }
+        if (ok) {
+            ok = tc::mbar_wait(bar(13), 0u, abort_flag, P.status, 0x64u);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        xch[ch * 128 + row] = z;
+        softmax_sync2();
+        z = __fadd_rn(xch[row], xch[128 + row]);
+        if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int64_t t = (int64_t)qb * BM + row;
+            uint16_t *orow = (uint16_t *)P.out + (int64_t)b * P.o_b + (int64_t)g * P.o_g + t * P.o_t + ch * 64;
+            const float rz = __frcp_rn(z);
+#pragma unroll 1
+            for (int c0 = 0; c0 < 64; c0 += 32) {
+                uint32_t v[32];
+                tc::tmem_ld32(tO + lane_base + (uint32_t)(ch * 64 + c0), v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        w[i] = pack_bf16x2_hw(div_by(__uint_as_float(v[u * 8 + 2 * i]), z, rz), div_by(__uint_as_float(v[u * 8 + 2 * i + 1]), z, rz));
+                    *reinterpret_cast<uint4 *>(orow + c0 + u * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256) : "memory");
+    }
+}
+} // namespace v2
+
 } // namespace attn
 } // namespace psk
