@@ -251,6 +251,11 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table);
 /* The overflow guard's flag since the last call, cleared by it: 0, or
  * 1 + the serial number of the first guarded launch that overflowed. */
 int64_t psk_exec_overflow(psk_exec *e);
+/* Every wait of a kernel of this library on a barrier is limited (about two seconds); when one runs out the kernel
+ * records where, leaves its loops, frees what it holds and returns, and the next psk_exec_sync reports PSK_E10001.
+ * This runs a kernel whose only wait cannot be satisfied, limited to `cycles` SM cycles (at most 4e8), and returns
+ * what the host reports for it: PSK_E10001 with the message in psk_last_error. The executor stays usable. */
+int psk_exec_wait_selftest(psk_exec *e, int64_t cycles);
 
 /* Launches queued, and how many kernels of this library they started. */
 void psk_exec_counts(const psk_exec *e, int64_t *launches, int64_t *kernels);

@@ -113,6 +113,7 @@ PROTOTYPES = {
     "psk_host_set_param": (C.c_int, [C.c_void_p, C.c_char_p, C.c_void_p, C.c_int32, C.POINTER(C.c_int64), C.c_int32]),
     "psk_host_init_param": (C.c_int, [C.c_void_p, C.c_char_p, C.c_uint64, C.c_double, C.POINTER(C.c_int64), C.c_int32]),
     "psk_host_call": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(Value), C.c_int32, C.c_void_p, C.c_int32, C.c_int64, C.POINTER(C.c_int64)]),
+    "psk_exec_wait_selftest": (C.c_int, [C.c_void_p, C.c_int64]),
     "psk_comm_unique_id": (C.c_int, [C.c_void_p]),
     "psk_comm_create": (C.c_void_p, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]),
     "psk_comm_destroy": (None, [C.c_void_p]),

@@ -523,12 +523,31 @@ static int check_status(psk_exec *e)
     if (st) {
         cudaMemsetAsync(e->status, 0, sizeof st, e->stream);
         char buf[256];
-        if (st & 0x100u) snprintf(buf, sizeof buf, "a bounded wait ran out in the tensor-core contraction (role %u); its results are not valid", st & 0xffu);
+        if (st & 0x100u) snprintf(buf, sizeof buf, "a bounded wait ran out in a tensor-core kernel (role 0x%x); its results are not valid", st & 0xffu);
         else if (st & 2u) snprintf(buf, sizeof buf, "an index outside its bound reached a gather");
         else snprintf(buf, sizeof buf, "sin or cos of an argument at or beyond 2^28*pi/2 is not supported by this executor");
         return fail(e, (st & 0x100u) ? PSK_E10001 : PSK_E7001, buf);
     }
     return PSK_OK;
+}
+
+// A kernel whose only wait can never be satisfied and is limited to `cycles`: returns what the next sync reports
+// (PSK_E10001, "a bounded wait ran out ..."), and leaves the executor usable. For tests of that report.
+int psk_exec_wait_selftest(psk_exec *e, int64_t cycles)
+{
+    cudaSetDevice(e->device);
+    if (cycles < 1 || cycles > 400000000ll) return fail(e, PSK_E7001, "psk_exec_wait_selftest: between 1 and 4e8 cycles (a fraction of a second)");
+    int *flag = (int *)psk_exec_alloc(e, sizeof(int));
+    if (!flag) return PSK_E10001;
+    tc::k_wait_runs_out<<<1, 32, 0, e->stream>>>(e->status, (long long)cycles, flag);
+    int gave_up = -1;
+    cudaError_t err = cudaMemcpyAsync(&gave_up, flag, sizeof gave_up, cudaMemcpyDeviceToHost, e->stream);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(e->stream);
+    psk_exec_free(e, flag);
+    if (err != cudaSuccess) return fail(e, PSK_E10001, std::string("psk_exec_wait_selftest: ") + cudaGetErrorString(err));
+    e->kernels += 1;
+    if (gave_up != 1) return fail(e, PSK_E10001, "psk_exec_wait_selftest: the wait did not run out");
+    return check_status(e);
 }
 
 int64_t psk_exec_overflow(psk_exec *e)

@@ -94,7 +94,7 @@ PSK_DEV void mbar_arrive(uint32_t bar)
 }
 
 // A bounded wait: false when it gave up or another role already had.
-PSK_DEV bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, uint32_t *status, uint32_t where)
+PSK_DEV bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, uint32_t *status, uint32_t where, long long limit = WAIT_CYCLES)
 {
     const long long t0 = clock64();
     for (uint32_t it = 0;; ++it) {
@@ -108,7 +108,7 @@ PSK_DEV bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, 
             : "memory");
         if (ok) return true;
         if (*abort_flag) return false;
-        if ((it & 255u) == 255u && clock64() - t0 > WAIT_CYCLES) {
+        if ((it & 255u) == 255u && clock64() - t0 > limit) {
             *abort_flag = 1;
             atomicOr(status, 0x100u | where);
             return false;
@@ -194,6 +194,21 @@ PSK_DEV void tile_of(int64_t r, int64_t tiles_m, int64_t tiles_n, int64_t PANEL,
     const int64_t width = tiles_n - panel * PANEL < PANEL ? tiles_n - panel * PANEL : PANEL;
     mt = in_panel / width;
     nt = panel * PANEL + (in_panel - mt * width);
+}
+
+// The bounded wait by itself, for a test of the host's reporting: one thread waits on a barrier that nothing
+// arrives at, gives up after `limit` cycles, records where (role 0x7f) and returns. Nothing else happens.
+static __global__ void k_wait_runs_out(uint32_t *status, long long limit, int *gave_up)
+{
+    __shared__ uint64_t bar_word;
+    __shared__ int abort_word;
+    if (threadIdx.x == 0) {
+        abort_word = 0;
+        mbar_init(smem_u32(&bar_word), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        const bool ok = mbar_wait(smem_u32(&bar_word), 0u, &abort_word, status, 0x7fu, limit);
+        *gave_up = ok ? 0 : 1;
+    }
 }
 
 template <int BN>

@@ -434,3 +434,24 @@ def test_division_by_a_row_scalar_is_the_ieee_division(cuda, oracle, with_mul):
     nan = ((x & 0x7fff) > 0x7f80) & ((y & 0x7fff) > 0x7f80)
     bad = np.nonzero((x != y) & ~nan)[0]
     assert bad.size == 0, f"{bad.size} differ; first: {a.ravel()[bad[0]]:#x} / {div[bad[0] // cols]!r}: {x[bad[0]]:#x} vs {y[bad[0]]:#x}"
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_executor_lives_on(cuda):
+    """Every barrier wait in the tensor-core kernels is bounded. A kernel whose only wait cannot be satisfied
+    (limited to 2e7 cycles, about 10 ms) gives up, records where, and the host reports E10001; the next launch on the
+    same executor runs normally."""
+    rc = cuda.lib.psk_exec_wait_selftest(cuda.handle, 20_000_000)
+    assert rc == abi.E10001
+    assert b"bounded wait ran out" in cuda.lib.psk_last_error(cuda.handle)
+    x = np.arange(64, dtype=np.float32)
+    l = launch_desc(abi.OP_FUSED, abi.F32, [64])
+    l.n_inputs, l.n_steps = 1, 1
+    l.steps[0].prim, l.steps[0].nargs, l.steps[0].src[0] = abi.NEG, 1, 0
+    set_operand(l.inputs[0], abi.F32, [64], [0])
+    set_operand(l.out, abi.F32, [64], [0])
+    p, q = cuda.upload(x), cuda.alloc(256)
+    cuda.run(l, [p, q])
+    cuda.sync()
+    assert np.array_equal(cuda.download(q, 256).view(np.float32), -x)
+    cuda.free(p)
+    cuda.free(q)
