@@ -1201,6 +1201,19 @@ struct psk_host {
     }
 
     // llama.psk:55-59
+    // examples/spec/rope/rope.psk:33-37, Llama 3's scaling of the frequencies with its defaults:
+    // s = clamp((context·ω / 2π − lo) / (hi − lo), 0, 1), ω' = ω · ((1 − s) / k + s); clamp is min(max(x, lo), hi).
+    Tensor llama3_scaling(const Tensor &w)
+    {
+        const std::string f = "llama3_scaling";
+        Tensor ctx = scalar(f + "/%6", 8192.0), two_pi = scalar(f + "/%8", 6.283185307179586), lo = scalar(f + "/%10", 1.0), span = scalar(f + "/%12", 4.0 - 1.0);
+        Tensor zero = scalar(f + "/%14", 0.0), one = scalar(f + "/%15", 1.0), k = scalar(f + "/%19", 32.0);
+        Tensor sc = fused(f + "/%17", {Bn(PSK_MUL, 0, 1), Bn(PSK_DIV, S(0), 2), Bn(PSK_SUB, S(1), 3), Bn(PSK_DIV, S(2), 4), Bn(PSK_MAX, S(3), 5), Bn(PSK_MIN, S(4), 6)},
+                          {&ctx, &w, &two_pi, &lo, &span, &zero, &one});
+        return fused(f + "/%24", {Bn(PSK_SUB, 0, 1), Bn(PSK_DIV, S(0), 2), Bn(PSK_ADD, S(1), 1), Bn(PSK_MUL, 3, S(2))}, {&one, &sc, &k, &w});
+    }
+
+    double rope_base = 1e4; // the base of the frequencies: 10 000 in llama.psk; an entry may set another
     Tensor llama_frequencies()
     {
         const std::string f = "frequencies";
@@ -1210,18 +1223,20 @@ struct psk_host {
         Tensor pos = positions(f + "/%3", "rot", hd / 2);
         Tensor rp = unary(f + "/%4", PSK_REAL, pos);
         Tensor hdr = scalar(f + "/%7", (double)hd);
-        Tensor base = scalar(f + "/%10", 1e4);
+        Tensor base = scalar(f + "/%10", rope_base);
         Tensor lg = unary(f + "/%11", PSK_LOG, base);
         return fused(f + "/%13", {Bn(PSK_MUL, 0, 1), Bn(PSK_DIV, S(0), 2), Bn(PSK_MUL, S(1), 3), U(PSK_EXP, S(2))}, {&neg, &rp, &hdr, &lg});
     }
 
     // llama.psk:61-62
+    bool rope_llama3 = false;
     Tensor llama_angles(int64_t T)
     {
         const std::string f = "angles";
         Tensor pos = positions(f + "/%0", "seq", T);
         Tensor rp = unary(f + "/%1", PSK_REAL, pos);
         Tensor fr = llama_frequencies();
+        if (rope_llama3) fr = llama3_scaling(fr);
         return ein(f + "/%3", {"seq", "rot"}, {{"seq"}, {"rot"}}, {&rp, &fr});
     }
 
@@ -1735,13 +1750,17 @@ struct psk_host {
         if (model == "llama") {
             if (entry == "apply") { need(1); return llama_apply(in[0]); }
             if (entry == "loss") { need(2); return llama_loss(in[0], in[1]); }
-            if (entry == "attention") {
+            if (entry == "attention" || entry == "attention3") {
                 // one attention function on given activations [batch, seq, model], with the causal mask and the
                 // angles of its sequence length: examples/spec/rope/rope.psk `attention2` is this with G = H
                 need(1);
+                // `attention3` (rope.psk:96-97): the base 500 000 and Llama 3's scaling of the frequencies
                 const int64_t T = in[0].axes[1].len;
                 Tensor mask = causal_mask("Llama.apply/%2", "seq", T);
+                const double keep = rope_base;
+                if (entry == "attention3") { rope_base = 5e5; rope_llama3 = true; }
                 Tensor phi = llama_angles(T);
+                rope_base = keep; rope_llama3 = false;
                 return llama_attention(0, in[0], mask, phi);
             }
         } else if (model == "gpt") {
@@ -1775,7 +1794,7 @@ struct psk_host {
     Axes input_axes(const std::string &entry, int i, const psk_value &v)
     {
         std::vector<std::string> names;
-        if (model == "llama" && entry == "attention") names = {"batch", "seq", "model"};
+        if (model == "llama" && (entry == "attention" || entry == "attention3")) names = {"batch", "seq", "model"};
         else if (model == "llama" || model == "gpt") names = {"batch", "seq"};
         else if (model == "mlp") names = i == 0 ? std::vector<std::string>{"batch", "model"} : std::vector<std::string>{"batch"};
         else if (model == "mlp_spec") names = {"batch", "model"};

@@ -4,7 +4,7 @@ fixtures, so that the suite can run where the reference tree is not mounted.
 Sources (paths within presk-lang/presk, read as text):
   tests/run/layernorm_apply.snap, rmsnorm_apply.snap   seed-0 outputs of the exact interpreter, 12 digits
   tests/run/mlp_mse.snap, mlp_mse_grad.snap             seed-0 loss and gradient of examples/spec/mlp/mlp.psk at D = 4, B = 2
-  tests/run/rope_attention2.snap                        seed-0 output of examples/spec/rope/rope.psk `attention2` at B = 2, T = 8
+  tests/run/rope_attention2.snap, rope_attention3.snap   seed-0 outputs of examples/spec/rope/rope.psk `attention2`, `attention3` at B = 2, T = 8
   tests/run/concat_loss.snap                            seed-0 loss of examples/spec/concat/concat.psk at B = 2, T = 8
   crates/presk-interp/src/key.rs:86-93                  the first four normal draws of the key seed 0 names
 Run:  python tests/golden/make_golden.py [path of the reference's tree]
@@ -34,9 +34,10 @@ for line in text.splitlines():
     if m:
         grad[layer + "." + m.group(1)] = {"shape": [int(x) for x in m.group(2).split(",")], "values": json.loads(m.group(3))}
 out["mlp_mse_grad"] = grad
-text = open(os.path.join(ref, "tests", "run", "rope_attention2.snap")).read().split("---")[-1]
-m = re.search(r"\[batch: (\d+), seq: (\d+), model: (\d+)\] (\[\[\[.*\]\]\])", text)
-out["rope_attention2"] = {"shape": [int(m.group(1)), int(m.group(2)), int(m.group(3))], "values": json.loads(m.group(4))}
+for name in ("rope_attention2", "rope_attention3"):
+    text = open(os.path.join(ref, "tests", "run", name + ".snap")).read().split("---")[-1]
+    m = re.search(r"\[batch: (\d+), seq: (\d+), model: (\d+)\] (\[\[\[.*\]\]\])", text)
+    out[name] = {"shape": [int(m.group(1)), int(m.group(2)), int(m.group(3))], "values": json.loads(m.group(4))}
 text = open(os.path.join(ref, "tests", "run", "concat_loss.snap")).read().split("---")[-1]
 out["concat_loss"] = float(re.search(r"= ([-0-9.e]+)", text).group(1))
 key_rs = open(os.path.join(ref, "crates", "presk-interp", "src", "key.rs")).read()

@@ -117,18 +117,19 @@ def test_mlp_loss_and_gradient_goldens_on_the_oracle(oracle, ref):
         np.testing.assert_allclose(got, np.array(g["values"]), rtol=0, atol=2e-6, err_msg=path)
 
 
-def test_rope_attention_golden_on_the_oracle(oracle, ref):
-    """tests/run/rope_attention2.snap: causal attention with rotary embeddings (examples/spec/rope/rope.psk
+@pytest.mark.parametrize("entry,key", [("attention", "rope_attention2"), ("attention3", "rope_attention3")])
+def test_rope_attention_golden_on_the_oracle(oracle, ref, entry, key):
+    """tests/run/rope_attention2.snap (and rope_attention3.snap: the base 500 000 with Llama 3's frequency scaling): causal attention with rotary embeddings (examples/spec/rope/rope.psk
     `attention2`, H = 2, HD = 8, B = 2, T = 8, seed 0) from the exact interpreter. The host's Llama attention
     with G = H is the same function (llama.psk's `per` axis has length 1); its parameters are the four children of
     θ's key drawn normal(std = 0.02) in declaration order, x the second argument's key."""
-    g = GOLD["rope_attention2"]
+    g = GOLD[key]
     b, t, d = g["shape"]
     h = Host(oracle.vtable(), "f32").prepare("llama", V=8, D=d, H=2, G=2, FF=8, L=1)
     for i, name in enumerate(("wq", "wk", "wv", "wo")):
         h.set_param("blocks.attn." + name, (draws_at(ref, "normal", 0, [0, i], d * d) * 0.02).reshape(1, d, d))
     x = draws_at(ref, "normal", 0, [1], b * t * d).reshape(b, t, d)
-    got = h.call("attention", [x], (b, t, d), np.float32)
+    got = h.call(entry, [x], (b, t, d), np.float32)
     want = np.array(g["values"])
     np.testing.assert_allclose(got, want, rtol=0, atol=2e-8)  # outputs are of magnitude 8e-3: f32 accuracy
 
