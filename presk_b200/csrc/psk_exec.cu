@@ -925,6 +925,14 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
                 dim3 grid((unsigned)((g.n + 63) / 64), (unsigned)((g.m + 63) / 64), (unsigned)g.batch);
                 e->last_flops = 2.0 * (double)g.m * (double)g.n * (double)g.k * (double)g.batch;
                 if (grid.y > 65535 || grid.z > 65535) { k_contract_generic<<<grid_for(e, L.total, 256, 8), 256, 0, e->stream>>>(L); e->last_kernel = "k_contract_generic"; }
+                else if (g.m >= 128 && g.n >= 128 && (A.dtype == PSK_F32 || A.dtype == PSK_BF16) && (B.dtype == PSK_F32 || B.dtype == PSK_BF16) && (g.m + 127) / 128 <= 65535) {
+                    dim3 big((unsigned)((g.n + 127) / 128), (unsigned)((g.m + 127) / 128), (unsigned)g.batch);
+                    if (A.dtype == PSK_F32 && B.dtype == PSK_F32) k_gemm_exact_big<PSK_F32, PSK_F32><<<big, 256, 0, e->stream>>>(G);
+                    else if (A.dtype == PSK_BF16 && B.dtype == PSK_BF16) k_gemm_exact_big<PSK_BF16, PSK_BF16><<<big, 256, 0, e->stream>>>(G);
+                    else if (A.dtype == PSK_F32) k_gemm_exact_big<PSK_F32, PSK_BF16><<<big, 256, 0, e->stream>>>(G);
+                    else k_gemm_exact_big<PSK_BF16, PSK_F32><<<big, 256, 0, e->stream>>>(G);
+                    e->last_kernel = "k_gemm_exact";
+                }
                 else { k_gemm_exact<<<grid, 256, 0, e->stream>>>(G); e->last_kernel = "k_gemm_exact"; }
             } else {
                 k_contract_generic<<<grid_for(e, L.total, 256, 8), 256, 0, e->stream>>>(L);

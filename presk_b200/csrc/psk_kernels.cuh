@@ -523,6 +523,78 @@ __global__ void __launch_bounds__(256) k_gemm_exact(const __grid_constant__ DevG
     if (G.guarded && ovf) atomicOr(G.ovf, 1u);
 }
 
+// The same contraction for large operands: 128 x 128 tiles, 16 k a step, 8 x 8 results a thread, the next tile
+// fetched while the current one is multiplied. Every result still adds its products one by one in increasing k
+// (a multiplication, then an addition: no fused operation), so the bits are k_gemm_exact's. f32 and bf16 operands.
+template <int ADT, int BDT>
+__global__ void __launch_bounds__(256, 2) k_gemm_exact_big(const __grid_constant__ DevGemmExact G)
+{
+    __shared__ float As[2][16][128 + 4];
+    __shared__ float Bs[2][16][128 + 4];
+    const int tid = threadIdx.x, tx = tid % 16, ty = tid / 16;
+    const int64_t i0 = (int64_t)blockIdx.y * 128, j0 = (int64_t)blockIdx.x * 128;
+    const int64_t bz = blockIdx.z, blo = bz % G.batch_lo, bhi = bz / G.batch_lo;
+    const int64_t aoff = blo * G.a_lo + bhi * G.a_hi, boff = blo * G.b_lo + bhi * G.b_hi, coff = blo * G.c_lo + bhi * G.c_hi;
+    uint32_t ovf = 0;
+    float acc[8][8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+#pragma unroll
+        for (int c = 0; c < 8; ++c) acc[r][c] = 0.0f;
+    // which elements of a 128 x 16 tile this thread fetches, eight of each operand: element e = tid + 256 t of the
+    // tile, walked along k when k is the operand's contiguous axis, else along the rows (or columns)
+    const bool ak = G.a_k == 1, bk = G.b_k == 1;
+    const int a_kk0 = ak ? tid % 16 : tid / 128, a_ii0 = ak ? tid / 16 : tid % 128, a_dkk = ak ? 0 : 2, a_dii = ak ? 16 : 0;
+    const int b_kk0 = bk ? tid % 16 : tid / 128, b_jj0 = bk ? tid / 16 : tid % 128, b_dkk = bk ? 0 : 2, b_djj = bk ? 16 : 0;
+    float ra[8], rb[8];
+    auto fetch = [&](int64_t k0) {
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+            const int64_t i = i0 + a_ii0 + t * a_dii, ka = k0 + a_kk0 + t * a_dkk, j = j0 + b_jj0 + t * b_djj, kb = k0 + b_kk0 + t * b_dkk;
+            ra[t] = (i < G.m && ka < G.k) ? edge_round(load_real(G.a, ADT, aoff + i * G.a_i + ka * G.a_k), G.kdtype, ADT, &ovf) : 0.0f;
+            rb[t] = (j < G.n && kb < G.k) ? edge_round(load_real(G.b, BDT, boff + kb * G.b_k + j * G.b_j), G.kdtype, BDT, &ovf) : 0.0f;
+        }
+    };
+    auto stash = [&](int buf) {
+#pragma unroll
+        for (int t = 0; t < 8; ++t) { As[buf][a_kk0 + t * a_dkk][a_ii0 + t * a_dii] = ra[t]; Bs[buf][b_kk0 + t * b_dkk][b_jj0 + t * b_djj] = rb[t]; }
+    };
+    fetch(0);
+    stash(0);
+    __syncthreads();
+    int buf = 0;
+    for (int64_t k0 = 0; k0 < G.k; k0 += 16) {
+        const bool more = k0 + 16 < G.k;
+        if (more) fetch(k0 + 16);
+        const int kmax = (int)((G.k - k0) < 16 ? (G.k - k0) : 16);
+#pragma unroll 4
+        for (int kk = 0; kk < kmax; ++kk) {
+            const float4 a0 = *reinterpret_cast<const float4 *>(&As[buf][kk][ty * 4]), a1 = *reinterpret_cast<const float4 *>(&As[buf][kk][64 + ty * 4]);
+            const float4 b0 = *reinterpret_cast<const float4 *>(&Bs[buf][kk][tx * 4]), b1 = *reinterpret_cast<const float4 *>(&Bs[buf][kk][64 + tx * 4]);
+            const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+            const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+            for (int r = 0; r < 8; ++r)
+#pragma unroll
+                for (int c = 0; c < 8; ++c) acc[r][c] = __fadd_rn(acc[r][c], __fmul_rn(a[r], b[c]));
+        }
+        if (more) stash(buf ^ 1);
+        __syncthreads();
+        buf ^= 1;
+    }
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            const int64_t i = i0 + (r < 4 ? ty * 4 + r : 64 + ty * 4 + r - 4), j = j0 + (c < 4 ? tx * 4 + c : 64 + tx * 4 + c - 4);
+            if (i < G.m && j < G.n) {
+                const int64_t o = coff + (i / G.c_row_lo_count) * G.c_row_hi + (i % G.c_row_lo_count) * G.c_row_lo + (j / G.c_col_lo_count) * G.c_col_hi + (j % G.c_col_lo_count) * G.c_col_lo;
+                ovf |= store_real(G.c, G.c_dtype, o, acc[r][c]);
+            }
+        }
+    if (G.guarded && ovf) atomicOr(G.ovf, 1u);
+}
+
 // ---------------------------------------------------------------------------
 // PSK_OP_REDUCE (lower.rs:1221-1255, 1693): sum, mean (sum / n), sum of
 // squares; exact: one thread per output, the terms in lexicographic order.

@@ -156,3 +156,39 @@ def test_f32_contraction_on_tensor_cores(cuda, oracle, m, n, k, b_n_major):
     # the nine partial products must all be there: an f32-accurate result, far below a bf16-plane's 2^-8
     row = slice(5 * n, 6 * n)
     assert np.abs(got[row] - exact[row]).max() <= 1e-4 * np.abs(exact[row]).max() + 1e-4
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16", "mixed"])
+@pytest.mark.parametrize("m,n,k,b_n_major", [(300, 260, 70, True), (257, 384, 200, False), (128, 128, 16, True), (513, 129, 33, False)])
+def test_exact_contraction_of_large_operands_is_the_oracle_s_bits(cuda, oracle, dt, m, n, k, b_n_major):
+    """Sequential order, operands of 128 rows and columns or more: the 128 x 128 tile kernel (`k_gemm_exact_big`), ragged
+    edges and both layouts of the second operand. Every result adds its products in increasing k: the oracle's bits."""
+    from presk_b200 import abi, launch_desc
+    rng = np.random.default_rng(m + 7 * n + k)
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    b = rng.standard_normal((k, n) if b_n_major else (n, k)).astype(np.float32)
+    a.ravel()[:3] = [-0.0, 0.0, 1e-30]
+    da = abi.F32 if dt == "f32" else abi.BF16
+    db = abi.BF16 if dt == "bf16" else abi.F32
+    kd = abi.F32 if dt != "bf16" else abi.BF16
+    ab = a if da == abi.F32 else oracle.convert(a, abi.BF16)
+    bb = b if db == abi.F32 else oracle.convert(b, abi.BF16)
+    l = launch_desc(abi.OP_CONTRACT, kd, [m, n], [k])
+    l.n_inputs = 2
+    l.inputs[0].dtype, l.inputs[0].numel, l.inputs[0].stride[0], l.inputs[0].stride[2] = da, m * k, k, 1
+    l.inputs[1].dtype, l.inputs[1].numel = db, n * k
+    if b_n_major:
+        l.inputs[1].stride[1], l.inputs[1].stride[2] = 1, n
+    else:
+        l.inputs[1].stride[1], l.inputs[1].stride[2] = k, 1
+    l.out.dtype, l.out.numel, l.out.stride[0], l.out.stride[1] = kd, m * n, n, 1
+    nbytes = m * n * abi.DTYPE_BYTES[kd]
+    pa, pb, pc = cuda.upload(np.ascontiguousarray(ab)), cuda.upload(np.ascontiguousarray(bb)), cuda.alloc(nbytes)
+    cuda.run(l, [pa, pb, pc])
+    cuda.sync()
+    got = cuda.download(pc, nbytes)
+    for p in (pa, pb, pc):
+        cuda.free(p)
+    want = np.zeros(nbytes, np.uint8)
+    oracle.run(l, [np.ascontiguousarray(ab), np.ascontiguousarray(bb), want])
+    assert np.array_equal(got, want)
