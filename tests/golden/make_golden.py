@@ -7,14 +7,16 @@ Sources (paths within presk-lang/presk, read as text):
   tests/run/rope_attention2.snap, rope_attention3.snap   seed-0 outputs of examples/spec/rope/rope.psk `attention2`, `attention3` at B = 2, T = 8
   tests/run/concat_loss.snap                            seed-0 loss of examples/spec/concat/concat.psk at B = 2, T = 8
   crates/presk-interp/src/key.rs:86-93                  the first four normal draws of the key seed 0 names
-Run:  python tests/golden/make_golden.py [path of the reference's tree]
+Run:  python tests/golden/make_golden.py <path of the reference's tree>
 """
 import json
 import os
 import re
 import sys
 
-ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    sys.exit(__doc__)
+ref = sys.argv[1]
 out = {}
 for name in ("layernorm_apply", "rmsnorm_apply"):
     text = open(os.path.join(ref, "tests", "run", name + ".snap")).read()
