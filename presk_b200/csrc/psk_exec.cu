@@ -335,9 +335,14 @@ int launch_tc(psk_exec *e, const psk_gemm &g, const void *a, const void *b, void
     const bool f16 = g.in_dtype == PSK_F16;
     const int bn = g.n >= 256 || g.n % 128 != 0 ? 256 : 128;
     const int64_t batch_hi = g.batch / g.batch_lo;
+    // tiles of 256 rows (two accumulators sharing B's tile): a third less traffic a product, but the accumulators
+    // fill tensor memory and a tile's epilogue is no longer hidden behind the next tile's products. Sustained, on
+    // one box: +11 % at K = 11008, +6 % at K = 8192, -3 to -5 % at K = 4096. So only where the summed axis is long.
+    static const bool m256_on = getenv("PSK_GEMM_M256") ? atoi(getenv("PSK_GEMM_M256")) != 0 : true;
+    const int mt_rows = (m256_on && bn == 256 && g.m >= 512 && g.k >= 8192) ? 2 : 1;
     CUtensorMap ma, mb;
     const uint64_t kphys = split_k ? (uint64_t)(planes * split_k) : (uint64_t)g.k; // what the operands hold along the summed axis
-    if (!make_map(e, &ma, a, f16, kphys, (uint64_t)g.m, (uint64_t)g.batch_lo, (uint64_t)batch_hi, (uint64_t)g.a_row, (uint64_t)g.a_lo, (uint64_t)g.a_hi, tc::BK, tc::BM))
+    if (!make_map(e, &ma, a, f16, kphys, (uint64_t)g.m, (uint64_t)g.batch_lo, (uint64_t)batch_hi, (uint64_t)g.a_row, (uint64_t)g.a_lo, (uint64_t)g.a_hi, tc::BK, (uint32_t)(tc::BM * mt_rows)))
         return fail(e, PSK_E7001, "tensor-core contraction: operand 0's strides do not make a tensor map");
     bool okb = g.b_n_major
         ? make_map(e, &mb, b, f16, (uint64_t)g.n, kphys, (uint64_t)g.batch_lo, (uint64_t)batch_hi, (uint64_t)g.b_row, (uint64_t)g.b_lo, (uint64_t)g.b_hi, 64, tc::BK)
@@ -345,7 +350,7 @@ int launch_tc(psk_exec *e, const psk_gemm &g, const void *a, const void *b, void
     if (!okb) return fail(e, PSK_E7001, "tensor-core contraction: operand 1's strides do not make a tensor map");
     tc::Params P;
     P.m = g.m; P.n = g.n; P.k = g.k; P.batch = g.batch; P.batch_lo = g.batch_lo;
-    P.tiles_m = (g.m + tc::BM - 1) / tc::BM;
+    P.tiles_m = (g.m + tc::BM * mt_rows - 1) / (tc::BM * mt_rows);
     P.tiles_n = (g.n + bn - 1) / bn;
     P.split_k = split_k; P.planes = planes; P.pad_ = 0;
     P.addend = addend;
@@ -371,11 +376,13 @@ int launch_tc(psk_exec *e, const psk_gemm &g, const void *a, const void *b, void
     if (!e->tc_attr_set) {
         CUDA_TRY(e, cudaFuncSetAttribute(tc::k_gemm_tc<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::Smem<256>::TOTAL));
         CUDA_TRY(e, cudaFuncSetAttribute(tc::k_gemm_tc<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::Smem<128>::TOTAL));
+        CUDA_TRY(e, cudaFuncSetAttribute(tc::k_gemm_tc<256, false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::Smem<256, 2>::TOTAL));
         e->tc_attr_set = true;
     }
     const int64_t tiles = P.tiles_m * P.tiles_n * g.batch;
     const int grid = (int)std::min<int64_t>(tiles, e->sms);
-    if (bn == 256) tc::k_gemm_tc<256><<<grid, tc::THREADS, tc::Smem<256>::TOTAL, e->stream>>>(ma, mb, P);
+    if (mt_rows == 2) tc::k_gemm_tc<256, false, 2><<<grid, tc::THREADS, tc::Smem<256, 2>::TOTAL, e->stream>>>(ma, mb, P);
+    else if (bn == 256) tc::k_gemm_tc<256><<<grid, tc::THREADS, tc::Smem<256>::TOTAL, e->stream>>>(ma, mb, P);
     else tc::k_gemm_tc<128><<<grid, tc::THREADS, tc::Smem<128>::TOTAL, e->stream>>>(ma, mb, P);
     CUDA_TRY(e, cudaGetLastError());
     e->kernels += 1;

@@ -211,11 +211,15 @@ static __global__ void k_wait_runs_out(uint32_t *status, long long limit, int *g
     }
 }
 
-template <int BN>
+// MT: 128-row halves of a CTA's tile. With MT = 2 a CTA computes 256 x BN, both halves multiplying the same tile of B:
+// a third fewer bytes from the L2 into shared memory a product, which is what the kernel's sustained rate under the
+// power cap depends on (measured: with B's loads left out it holds cuBLAS's rate, 14 % above its own). The two
+// accumulators then fill tensor memory, so the epilogue of a tile is overlapped with the next tile's loads only.
+template <int BN, int MT = 1>
 struct Smem {
-    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int A_BYTES = MT * BM * BK * 2;
     static constexpr int B_BYTES = BN * BK * 2;
-    static constexpr int STAGES = (BN == 256) ? 4 : 6;
+    static constexpr int STAGES = MT == 2 ? 3 : (BN == 256) ? 4 : 6;
     static constexpr int TILE_BYTES = STAGES * (A_BYTES + B_BYTES);
     static constexpr int BAR_BYTES = 256;
     static constexpr int STAGE_OUT = 8 * 32 * 128; // the epilogue's staging: 32 rows of 128 bytes a warp
@@ -228,10 +232,11 @@ struct Smem {
 // only when that is exact), then the store's rounding.
 // PER_BATCH: the guard's flag is one word a batch entry (P.ovf[b]) instead of
 // one word a launch, for a caller that wants to know which entry overflowed.
-template <int BN, bool PER_BATCH = false>
+template <int BN, bool PER_BATCH = false, int MT = 1>
 __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ Params P)
 {
-    using S = Smem<BN>;
+    static_assert(MT == 1 || (MT == 2 && BN == 256), "two halves fill tensor memory with 256 columns each");
+    using S = Smem<BN, MT>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t *smem_a = smem;
@@ -278,7 +283,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
                 const int64_t b = t / tiles_per_batch, r = t % tiles_per_batch;
                 int64_t mt, nt;
                 tile_of(r, P.tiles_m, P.tiles_n, P.panel, mt, nt);
-                const int m0 = (int)mt * BM, n0 = (int)nt * BN;
+                const int m0 = (int)mt * BM * MT, n0 = (int)nt * BN; // the map of A has a box of BM * MT rows
                 const int blo = (int)(b % P.batch_lo), bhi = (int)(b / P.batch_lo);
                 for (int kb = 0; kb < num_kb; ++kb) {
                     ok = mbar_wait(empty0 + 8 * stage, phase ^ 1u, abort_flag, P.status, 1u);
@@ -309,10 +314,12 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
             for (int64_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-                ok = mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1u, abort_flag, P.status, 2u);
-                if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t tacc = tmem_base + acc * BN;
+                if constexpr (MT == 1) {
+                    ok = mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1u, abort_flag, P.status, 2u);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                }
+                const uint32_t tacc = MT == 1 ? tmem_base + acc * BN : tmem_base;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     ok = mbar_wait(full0 + 8 * stage, phase, abort_flag, P.status, 3u);
                     if (!ok) break;
@@ -320,17 +327,32 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
                     const uint32_t a_addr = smem_u32(smem_a + stage * S::A_BYTES);
                     const uint32_t b_addr = smem_u32(smem_b + stage * S::B_BYTES);
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k) {
-                        const uint64_t ad = smem_desc(a_addr + k * 32, 16, 1024);
-                        const uint64_t bd = P.b_n_major ? smem_desc(b_addr + k * 2048, 8192, 1024) : smem_desc(b_addr + k * 32, 16, 1024);
-                        umma(tacc, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+                    for (int h = 0; h < MT; ++h) {
+                        if (MT == 2 && kb == 0) {
+                            // this half's accumulator must have been drained by the epilogue of the tile before
+                            ok = mbar_wait(tempty0 + 8 * h, acc_phase ^ 1u, abort_flag, P.status, 2u);
+                            if (!ok) break;
+                            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        }
+#pragma unroll
+                        for (int k = 0; k < BK / UMMA_K; ++k) {
+                            const uint64_t ad = smem_desc(a_addr + h * (BM * BK * 2) + k * 32, 16, 1024);
+                            const uint64_t bd = P.b_n_major ? smem_desc(b_addr + k * 2048, 8192, 1024) : smem_desc(b_addr + k * 32, 16, 1024);
+                            umma(tacc + h * BN, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+                        }
                     }
+                    if (!ok) break;
                     umma_commit(empty0 + 8 * stage); // the stage is free once these have read it
                     if (++stage == S::STAGES) { stage = 0; phase ^= 1u; }
                 }
                 if (!ok) break;
-                umma_commit(tfull0 + 8 * acc);
-                if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+                if constexpr (MT == 1) {
+                    umma_commit(tfull0 + 8 * acc);
+                    if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+                } else {
+                    umma_commit(tfull0);
+                    acc_phase ^= 1u;
+                }
             }
         }
     } else {
@@ -347,18 +369,20 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
             const int64_t b = t / tiles_per_batch, r = t % tiles_per_batch;
             int64_t mt, nt;
             tile_of(r, P.tiles_m, P.tiles_n, P.panel, mt, nt);
-            const int64_t m0 = mt * BM, n0 = nt * BN;
+            const int64_t m0 = mt * BM * MT, n0 = nt * BN;
             const int64_t blo = b % P.batch_lo, bhi = b / P.batch_lo;
-            ok = mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, P.status, 4u);
+            ok = mbar_wait(MT == 1 ? tfull0 + 8 * acc : tfull0, acc_phase, abort_flag, P.status, 4u);
             ok = __all_sync(0xffffffffu, ok); // the loads below want the whole warp
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int64_t row0 = m0 + quad * 32;
+#pragma unroll 1
+            for (int mh = 0; mh < MT; ++mh) { // the tile's 128-row halves, each with its own accumulator
+            const int64_t row0 = m0 + mh * BM + quad * 32;
             const int64_t boff = blo * P.c_lo + bhi * P.c_hi;
             const float *cs_base = P.col_scale ? P.col_scale + blo * P.col_scale_lo + bhi * P.col_scale_hi : nullptr;
             const int64_t row = row0 + lane;
             const int64_t row_off = boff + (row / P.c_row_lo_count) * P.c_row_hi + (row % P.c_row_lo_count) * P.c_row_lo;
-            const uint32_t tbase = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
+            const uint32_t tbase = tmem_base + ((uint32_t)(quad * 32) << 16) + (MT == 1 ? acc : (uint32_t)mh) * BN;
             if (staged) {
                 // 128 bytes of every row at a time: through shared memory, so that a store
                 // instruction writes whole 128-byte lines (8 lanes a row, 4 rows an instruction)
@@ -474,8 +498,10 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
-            if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+            if (lane == 0) mbar_arrive(tempty0 + 8 * (MT == 1 ? acc : (uint32_t)mh));
+            } // mh
+            if (MT == 2) acc_phase ^= 1u;
+            else if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
         }
         if (P.guarded && ovf) atomicOr(P.ovf, 1u);
     }
