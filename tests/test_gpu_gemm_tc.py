@@ -192,3 +192,69 @@ def test_exact_contraction_of_large_operands_is_the_oracle_s_bits(cuda, oracle, 
     want = np.zeros(nbytes, np.uint8)
     oracle.run(l, [np.ascontiguousarray(ab), np.ascontiguousarray(bb), want])
     assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("b_n_major", [0, 1])
+@pytest.mark.parametrize("out_dtype", [abi.BF16, abi.F32])
+def test_gemm_long_summed_axis_takes_the_256_row_tiles(cuda, oracle, b_n_major, out_dtype):
+    """K >= 8192: tiles of 256 rows, two accumulators multiplying one tile of B; 640 rows leave the last tile half
+    empty, 520 columns the last column tile ragged."""
+    got, want = run_gemm(cuda, oracle, 640, 520, 8192, 1, b_n_major, abi.BF16, out_dtype, seed=9)
+    tol = 4e-6 * 8192 + 1e-5 if out_dtype == abi.F32 else 2.0**-8 * np.abs(want).max() + 1e-3
+    assert np.abs(got - want).max() <= tol
+
+
+def test_contract_add_and_integer_weights_on_the_256_row_tiles(cuda, oracle):
+    """The epilogue's extras on the long-K form of the kernel: a residual addend (the same bits as the contraction
+    followed by the addition on this executor) and integer weights with one scale a column (within the bf16
+    tolerance of the oracle's sequential result)."""
+    from presk_b200 import launch_desc
+    m, n, k = 512, 256, 8192
+    rng = np.random.default_rng(17)
+    a = oracle.convert((rng.standard_normal((m, k)) * 0.1).astype(np.float32), abi.BF16)
+    w = oracle.convert((rng.standard_normal((k, n)) * 0.1).astype(np.float32), abi.BF16)
+    x = oracle.convert(rng.standard_normal((m, n)).astype(np.float32), abi.BF16)
+
+    def contract(op, n_inputs):
+        l = launch_desc(op, abi.BF16, [m, n], [k], order=abi.ORDER_DEVICE)
+        l.n_inputs = n_inputs
+        l.inputs[0].dtype, l.inputs[0].numel, l.inputs[0].stride[0], l.inputs[0].stride[2] = abi.BF16, m * k, k, 1
+        l.inputs[1].dtype, l.inputs[1].numel, l.inputs[1].stride[1], l.inputs[1].stride[2] = abi.BF16, n * k, 1, n
+        l.out.dtype, l.out.numel, l.out.stride[0], l.out.stride[1] = abi.BF16, m * n, n, 1
+        return l
+
+    pa, pw, px = cuda.upload(a), cuda.upload(w), cuda.upload(x)
+    pc, ps, pf = cuda.alloc(m * n * 2), cuda.alloc(m * n * 2), cuda.alloc(m * n * 2)
+    cuda.run(contract(abi.OP_CONTRACT, 2), [pa, pw, pc])
+    add = launch_desc(abi.OP_FUSED, abi.BF16, [m, n], order=abi.ORDER_DEVICE)
+    add.n_inputs, add.n_steps = 2, 1
+    add.steps[0].prim, add.steps[0].nargs, add.steps[0].src[0], add.steps[0].src[1] = abi.ADD, 2, 0, 1
+    for o in (add.inputs[0], add.inputs[1], add.out):
+        o.dtype, o.numel, o.stride[0], o.stride[1] = abi.BF16, m * n, n, 1
+    cuda.run(add, [px, pc, ps])
+    fused = contract(abi.OP_CONTRACT_ADD, 3)
+    fused.iparam[1] = abi.BF16
+    fused.inputs[2].dtype, fused.inputs[2].numel, fused.inputs[2].stride[0], fused.inputs[2].stride[1] = abi.BF16, m * n, n, 1
+    cuda.run(fused, [pa, pw, px, pf])
+    cuda.sync()
+    assert np.array_equal(cuda.download(pf, m * n * 2), cuda.download(ps, m * n * 2))
+    # integer weights: codes and one f32 scale a column
+    q = rng.integers(-127, 128, size=(k, n), dtype=np.int8)
+    sc = (rng.uniform(0.5, 2.0, n) * 1e-3).astype(np.float32)
+    lq = contract(abi.OP_CONTRACT, 2)
+    lq.inputs[1].dtype = abi.I8
+    lq.inputs[1].scale_stride[1] = 1
+    pq, psc = cuda.upload(q), cuda.upload(sc)
+    cuda.run(lq, [pa, pq, pc, psc])
+    cuda.sync()
+    got = (cuda.download(pc, m * n * 2).view(np.uint16).astype(np.uint32) << 16).view(np.float32)
+    want_b = np.zeros(m * n * 2, np.uint8)
+    ls = contract(abi.OP_CONTRACT, 2)
+    ls.order = abi.ORDER_SEQUENTIAL
+    ls.inputs[1].dtype = abi.I8
+    ls.inputs[1].scale_stride[1] = 1
+    oracle.run(ls, [np.ascontiguousarray(a), np.ascontiguousarray(q), want_b, np.ascontiguousarray(sc)])
+    want = (want_b.view(np.uint16).astype(np.uint32) << 16).view(np.float32)
+    assert np.abs(got - want).max() <= 2.0**-7 * np.abs(want).max()
+    for p in (pa, pw, px, pc, ps, pf, pq, psc):
+        cuda.free(p)
