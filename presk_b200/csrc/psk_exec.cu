@@ -337,9 +337,9 @@ int launch_tc(psk_exec *e, const psk_gemm &g, const void *a, const void *b, void
     const int64_t batch_hi = g.batch / g.batch_lo;
     // tiles of 256 rows (two accumulators sharing B's tile): a third less traffic a product, but the accumulators
     // fill tensor memory and a tile's epilogue is no longer hidden behind the next tile's products. Sustained, on
-    // one box: +11 % at K = 11008, +6 % at K = 8192, -3 to -5 % at K = 4096. So only where the summed axis is long.
+    // one box, against 128-row tiles: +12 % at K = 11008, +3 % at K = 4096 (N = 4096, 11008), +2 % for the f32 head.
     static const bool m256_on = getenv("PSK_GEMM_M256") ? atoi(getenv("PSK_GEMM_M256")) != 0 : true;
-    const int mt_rows = (m256_on && bn == 256 && g.m >= 512 && g.k >= 8192) ? 2 : 1;
+    const int mt_rows = (m256_on && bn == 256 && g.m >= 512) ? 2 : 1;
     CUtensorMap ma, mb;
     const uint64_t kphys = split_k ? (uint64_t)(planes * split_k) : (uint64_t)g.k; // what the operands hold along the summed axis
     if (!make_map(e, &ma, a, f16, kphys, (uint64_t)g.m, (uint64_t)g.batch_lo, (uint64_t)batch_hi, (uint64_t)g.a_row, (uint64_t)g.a_lo, (uint64_t)g.a_hi, tc::BK, (uint32_t)(tc::BM * mt_rows)))

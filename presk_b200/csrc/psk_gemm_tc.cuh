@@ -365,6 +365,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
         uint4 *stage_out = reinterpret_cast<uint4 *>(smem + S::TILE_BYTES + S::BAR_BYTES) + (warp - 2) * 32 * 8;
         const bool staged = P.vec_ok && (P.out_dtype == PSK_BF16 || P.out_dtype == PSK_F16 || P.out_dtype == PSK_F32);
         const int group_cols = P.out_dtype == PSK_F32 ? 32 : 64; // columns in 128 bytes
+        const bool plain_bf16 = P.out_dtype == PSK_BF16 && !P.scale_on && !P.col_scale && !P.addend;
         for (int64_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
             const int64_t b = t / tiles_per_batch, r = t % tiles_per_batch;
             int64_t mt, nt;
@@ -381,8 +382,33 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
             const int64_t boff = blo * P.c_lo + bhi * P.c_hi;
             const float *cs_base = P.col_scale ? P.col_scale + blo * P.col_scale_lo + bhi * P.col_scale_hi : nullptr;
             const int64_t row = row0 + lane;
-            const int64_t row_off = boff + (row / P.c_row_lo_count) * P.c_row_hi + (row % P.c_row_lo_count) * P.c_row_lo;
+            int64_t row_off;
+            {
+                const uint32_t cnt = (uint32_t)(P.c_row_lo_count < 0x7fffffffll ? P.c_row_lo_count : 0x7fffffffll);
+                const uint32_t rq = (uint32_t)row / cnt;
+                row_off = boff + (int64_t)rq * P.c_row_hi + (int64_t)((uint32_t)row - rq * cnt) * P.c_row_lo;
+            }
             const uint32_t tbase = tmem_base + ((uint32_t)(quad * 32) << 16) + (MT == 1 ? acc : (uint32_t)mh) * BN;
+            // Where the rows this lane stores lie (rows 4·it + lane / 8 of the warp's 32), once a half-tile and in 32-bit
+            // arithmetic: a 64-bit division for every store was most of this epilogue's instructions.
+            int64_t row_offs[8];
+            bool rows_ok[8];
+            {
+                const uint32_t cnt = (uint32_t)(P.c_row_lo_count < 0x7fffffffll ? P.c_row_lo_count : 0x7fffffffll);
+                const uint32_t first = (uint32_t)row0;
+                const uint32_t q0 = first / cnt, r0 = first - q0 * cnt;
+#pragma unroll
+                for (int it = 0; it < 8; ++it) {
+                    const uint32_t rr = (uint32_t)(it * 4 + (lane >> 3));
+                    uint32_t rq = q0, rm = r0 + rr;
+                    if (rm >= cnt) {
+                        if (cnt >= 32u) { rm -= cnt; rq += 1u; }
+                        else { rq += rm / cnt; rm = rm % cnt; }
+                    }
+                    row_offs[it] = boff + (int64_t)rq * P.c_row_hi + (int64_t)rm * P.c_row_lo;
+                    rows_ok[it] = row0 + rr < P.m;
+                }
+            }
             if (staged) {
                 // 128 bytes of every row at a time: through shared memory, so that a store
                 // instruction writes whole 128-byte lines (8 lanes a row, 4 rows an instruction)
@@ -407,20 +433,36 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
                             stage_out[lane * 8 + (q ^ (lane & 7))] = make_uint4(__float_as_uint(x0), __float_as_uint(x1), __float_as_uint(x2), __float_as_uint(x3));
                         }
                     } else {
+                        int64_t add_col_off = 0;
+                        if (P.addend) {
+                            const uint32_t ccnt = (uint32_t)(P.c_col_lo_count < 0x7fffffffll ? P.c_col_lo_count : 0x7fffffffll);
+                            const uint32_t cq = (uint32_t)col / ccnt;
+                            add_col_off = (int64_t)cq * P.c_col_hi + (int64_t)((uint32_t)col - cq * ccnt);
+                        }
                         uint32_t va[32], vb[32];
                         tmem_ld32(tbase + c0, va);
                         tmem_ld32(tbase + c0 + 32, vb);
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        if (plain_bf16) {
+                            // nothing but the rounding: the common case, kept free of the tests below
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                stage_out[lane * 8 + (q ^ (lane & 7))] = make_uint4(
+                                    pack_bf16x2_hw(__uint_as_float(va[q * 8]), __uint_as_float(va[q * 8 + 1])), pack_bf16x2_hw(__uint_as_float(va[q * 8 + 2]), __uint_as_float(va[q * 8 + 3])),
+                                    pack_bf16x2_hw(__uint_as_float(va[q * 8 + 4]), __uint_as_float(va[q * 8 + 5])), pack_bf16x2_hw(__uint_as_float(va[q * 8 + 6]), __uint_as_float(va[q * 8 + 7])));
+                                stage_out[lane * 8 + ((4 + q) ^ (lane & 7))] = make_uint4(
+                                    pack_bf16x2_hw(__uint_as_float(vb[q * 8]), __uint_as_float(vb[q * 8 + 1])), pack_bf16x2_hw(__uint_as_float(vb[q * 8 + 2]), __uint_as_float(vb[q * 8 + 3])),
+                                    pack_bf16x2_hw(__uint_as_float(vb[q * 8 + 4]), __uint_as_float(vb[q * 8 + 5])), pack_bf16x2_hw(__uint_as_float(vb[q * 8 + 6]), __uint_as_float(vb[q * 8 + 7])));
+                            }
+                        } else
 #pragma unroll
                         for (int half = 0; half < 2; ++half) {
 #pragma unroll
                             for (int q = 0; q < 4; ++q) {
                                 uint32_t u[4];
                                 uint4 add8 = make_uint4(0u, 0u, 0u, 0u);
-                                if (P.addend && row < P.m && col + half * 32 + q * 8 < P.n) {
-                                    const int64_t cc = col + half * 32 + q * 8;
-                                    add8 = *reinterpret_cast<const uint4 *>((const uint16_t *)P.addend + row_off + (cc / P.c_col_lo_count) * P.c_col_hi + (cc % P.c_col_lo_count));
-                                }
+                                if (P.addend && row < P.m && col + half * 32 + q * 8 < P.n) // the group's 64 columns lie in one column level (vec_ok)
+                                    add8 = *reinterpret_cast<const uint4 *>((const uint16_t *)P.addend + row_off + add_col_off + half * 32 + q * 8);
 #pragma unroll
                                 for (int i = 0; i < 4; ++i) {
                                     float x0 = __uint_as_float(half ? vb[q * 8 + 2 * i] : va[q * 8 + 2 * i]);
@@ -455,15 +497,16 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
                     }
                     __syncwarp();
                     if (col < P.n) {
-                        const int64_t col_off = (col / P.c_col_lo_count) * P.c_col_hi + (col % P.c_col_lo_count);
+                        const uint32_t ccnt = (uint32_t)(P.c_col_lo_count < 0x7fffffffll ? P.c_col_lo_count : 0x7fffffffll);
+                        const uint32_t cq = (uint32_t)col / ccnt;
+                        const int64_t col_off = (int64_t)cq * P.c_col_hi + (int64_t)((uint32_t)col - cq * ccnt);
                         const int unit = lane & 7;
                         const int units_live = (int)((P.n - col) >= group_cols ? 8 : ((P.n - col) * (P.out_dtype == PSK_F32 ? 4 : 2)) / 16);
 #pragma unroll
                         for (int it = 0; it < 8; ++it) {
                             const int rr = it * 4 + (lane >> 3);
-                            const int64_t grow = row0 + rr;
-                            if (grow < P.m && unit < units_live) {
-                                const int64_t off = boff + (grow / P.c_row_lo_count) * P.c_row_hi + (grow % P.c_row_lo_count) * P.c_row_lo + col_off;
+                            if (rows_ok[it] && unit < units_live) {
+                                const int64_t off = row_offs[it] + col_off;
                                 const uint4 w = stage_out[rr * 8 + (unit ^ (rr & 7))];
                                 uint8_t *dst = (uint8_t *)P.c + off * (P.out_dtype == PSK_F32 ? 4 : 2) + unit * 16;
                                 *reinterpret_cast<uint4 *>(dst) = w;
