@@ -367,6 +367,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
         const int group_cols = P.out_dtype == PSK_F32 ? 32 : 64; // columns in 128 bytes
         const bool plain_bf16 = P.out_dtype == PSK_BF16 && !P.scale_on && !P.col_scale && !P.addend;
         const bool plain_add = P.out_dtype == PSK_BF16 && !P.scale_on && !P.col_scale && P.addend;
+        const bool plain_f32 = P.out_dtype == PSK_F32 && !P.scale_on && !P.col_scale;
         for (int64_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
             const int64_t b = t / tiles_per_batch, r = t % tiles_per_batch;
             int64_t mt, nt;
@@ -420,6 +421,10 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
                         uint32_t v[32];
                         tmem_ld32(tbase + c0, v);
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        if (plain_f32) {
+#pragma unroll
+                            for (int q = 0; q < 8; ++q) stage_out[lane * 8 + (q ^ (lane & 7))] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                        } else
 #pragma unroll
                         for (int q = 0; q < 8; ++q) {
                             float x0 = __uint_as_float(v[4 * q]), x1 = __uint_as_float(v[4 * q + 1]), x2 = __uint_as_float(v[4 * q + 2]), x3 = __uint_as_float(v[4 * q + 3]);
