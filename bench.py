@@ -49,8 +49,8 @@ QUANTISED = ("blocks.attn.wq", "blocks.attn.wk", "blocks.attn.wv", "blocks.attn.
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel's heaviest frequent shape, from the
 # ncu capture summarised in profiles/k_gemm_tc_ffn_16384x11008x4096.md (bytes a launch; algorithmic bytes: 585 MB)
-GEMM_TRAFFIC = {"llama7b_prefill_b8_t2048": 907765248 + 347590144}
-GEMM_TRAFFIC_OF = "k_gemm_tc<256>, dot [16384, 4096] x [4096, 11008] (gate/up projections: 64 of a step's 225 contractions), one launch under ncu"
+GEMM_TRAFFIC = {"llama7b_prefill_b8_t2048": 796489216 + 334924800}
+GEMM_TRAFFIC_OF = "k_gemm_tc<256, false, 2>, dot [16384, 4096] x [4096, 11008] (gate/up projections: 64 of a step's 225 contractions), one launch under ncu"
 
 
 def realization(paths, int8=False, attention="unfused", launches="reference"):
