@@ -39,6 +39,9 @@ WORKLOADS = {
     # its int8 variant: the same architecture, projection and FFN weights int8 with one f32 scale a
     # channel, bf16 activations, seq 1024, batch 16 a GPU
     "llama7b_int8_prefill_b16_t1024": dict(consts=dict(V=32000, D=4096, H=32, G=32, FF=11008, L=32), B=16, T=1024, int8=True),
+    # and with those weights stored e4m3fn (a `params` entry; the reference has no scale for such weights, so N(0, 0.02)
+    # keeps about three significant bits): the same launches, the weights widened exactly
+    "llama7b_e4m3w_prefill_b16_t1024": dict(consts=dict(V=32000, D=4096, H=32, G=32, FF=11008, L=32), B=16, T=1024, int8="e4m3fn"),
     # a small shape of the same program, for trying the script out
     "llama_small": dict(consts=dict(V=4096, D=1024, H=8, G=8, FF=2816, L=4), B=4, T=512),
 }
@@ -56,14 +59,15 @@ GEMM_TRAFFIC_OF = "k_gemm_tc<256, false, 2>, dot [16384, 4096] x [4096, 11008] (
 def realization(paths, int8=False, attention="unfused", launches="reference"):
     """A solved-style mixed bf16/f32 assignment: bf16 storage, f32 where a sum's result is reused
     widely (the norms' mean and root, the logits and the loss); with `int8`, the projection and
-    FFN weights as integers with one scale a channel (`quant`, over the contracted axis)."""
+    FFN weights as integers with one scale a channel (`quant`, over the contracted axis); with `int8` the
+    string "e4m3fn", those weights stored e4m3fn instead (`params`)."""
     rz = {
         "default": "bf16",
         "order": {"kind": "device", "attention": attention, "launches": launches},
-        "params": {p: "bf16" for p in paths if not (int8 and p in QUANTISED)},
+        "params": {p: ("e4m3fn" if int8 == "e4m3fn" and p in QUANTISED else "bf16") for p in paths if not (int8 is True and p in QUANTISED)},
         "storage": {"RMSNorm.apply/%3": "f32", "RMSNorm.apply/%7": "f32", "Llama.apply/%11": "f32", "loss/%5": "f32", "loss/%6": "f32"},
     }
-    if int8:
+    if int8 is True:
         rz["quant"] = {p: {"bits": 8, "over": -2} for p in QUANTISED}
     return rz
 

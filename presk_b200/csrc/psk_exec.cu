@@ -377,11 +377,15 @@ int launch_tc(psk_exec *e, const psk_gemm &g, const void *a, const void *b, void
         CUDA_TRY(e, cudaFuncSetAttribute(tc::k_gemm_tc<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::Smem<256>::TOTAL));
         CUDA_TRY(e, cudaFuncSetAttribute(tc::k_gemm_tc<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::Smem<128>::TOTAL));
         CUDA_TRY(e, cudaFuncSetAttribute(tc::k_gemm_tc<256, false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::Smem<256, 2>::TOTAL));
+        CUDA_TRY(e, cudaFuncSetAttribute(tc::k_gemm_tc<256, false, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::Smem<256, 2>::TOTAL));
+        CUDA_TRY(e, cudaFuncSetAttribute(tc::k_gemm_tc<256, false, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::Smem<256>::TOTAL));
         e->tc_attr_set = true;
     }
     const int64_t tiles = P.tiles_m * P.tiles_n * g.batch;
     const int grid = (int)std::min<int64_t>(tiles, e->sms);
-    if (mt_rows == 2) tc::k_gemm_tc<256, false, 2><<<grid, tc::THREADS, tc::Smem<256, 2>::TOTAL, e->stream>>>(ma, mb, P);
+    if (mt_rows == 2 && col_scale) tc::k_gemm_tc<256, false, 2, true><<<grid, tc::THREADS, tc::Smem<256, 2>::TOTAL, e->stream>>>(ma, mb, P);
+    else if (bn == 256 && col_scale) tc::k_gemm_tc<256, false, 1, true><<<grid, tc::THREADS, tc::Smem<256>::TOTAL, e->stream>>>(ma, mb, P);
+    else if (mt_rows == 2) tc::k_gemm_tc<256, false, 2><<<grid, tc::THREADS, tc::Smem<256, 2>::TOTAL, e->stream>>>(ma, mb, P);
     else if (bn == 256) tc::k_gemm_tc<256><<<grid, tc::THREADS, tc::Smem<256>::TOTAL, e->stream>>>(ma, mb, P);
     else tc::k_gemm_tc<128><<<grid, tc::THREADS, tc::Smem<128>::TOTAL, e->stream>>>(ma, mb, P);
     CUDA_TRY(e, cudaGetLastError());
@@ -496,6 +500,23 @@ void *psk_exec_alloc(psk_exec *e, size_t bytes)
     return p;
 }
 
+// A widened copy of weights is valid while the codes it was made from are: anything that writes into the
+// buffer holding them (an upload, a launch's output) drops it.
+static void forget_widened(psk_exec *e, const void *written)
+{
+    if (e->widened.empty()) return;
+    const uint8_t *lo = (const uint8_t *)written, *hi = lo + 1;
+    for (auto &kv : e->sizes) {
+        const uint8_t *b = (const uint8_t *)kv.first;
+        if (lo >= b && lo < b + kv.second) { lo = b; hi = b + kv.second; break; }
+    }
+    for (auto w = e->widened.begin(); w != e->widened.end();) {
+        const uint8_t *q = (const uint8_t *)w->first.first;
+        if (q >= lo && q < hi) { cudaFree(w->second); w = e->widened.erase(w); }
+        else ++w;
+    }
+}
+
 void psk_exec_free(psk_exec *e, void *p)
 {
     if (!p) return;
@@ -518,6 +539,7 @@ int psk_exec_upload(psk_exec *e, void *dst, const void *src_host, size_t bytes)
 {
     cudaSetDevice(e->device);
     e->causal.erase(dst);
+    forget_widened(e, dst);
     CUDA_TRY(e, cudaMemcpyAsync(dst, src_host, bytes, cudaMemcpyHostToDevice, e->stream));
     CUDA_TRY(e, cudaStreamSynchronize(e->stream)); // the host buffer is the caller's again
     return PSK_OK;
@@ -653,6 +675,22 @@ int psk_exec_gemm(psk_exec *e, const psk_gemm *g, const void *a, const void *b, 
     return r;
 }
 
+// Integer or e4m3fn weights as the bf16 numbers they are: a copy made at the weights' first contraction on the
+// tensor cores and kept until the codes are written again or freed.
+static const void *widened_weights(psk_exec *e, const void *codes, int64_t count, bool int8)
+{
+    auto key = std::make_pair(codes, count);
+    auto it = e->widened.find(key);
+    if (it != e->widened.end()) return it->second;
+    void *wb = nullptr;
+    if (cudaMalloc(&wb, (size_t)count * 2) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    if (int8) k_int8_to_bf16<<<grid_for(e, count, 256, 8), 256, 0, e->stream>>>((const int8_t *)codes, (uint16_t *)wb, count);
+    else k_e4m3_to_bf16<<<grid_for(e, count, 256, 8), 256, 0, e->stream>>>((const uint8_t *)codes, (uint16_t *)wb, count);
+    e->kernels += 1;
+    e->widened.emplace(key, wb);
+    return wb;
+}
+
 int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
 {
     cudaSetDevice(e->device);
@@ -662,6 +700,7 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
         return fail(e, PSK_E7005, std::string(l->name ? l->name : "?") + ": this executor computes in f32; a site realised f64 is not runnable by it");
     const int naxes = l->n_outer + l->n_inner;
     if (!e->causal.empty() && l->op != PSK_OP_MAGNITUDE) e->causal.erase(table[l->n_inputs]); // whatever this launch writes is no longer known to be a causal mask
+    if (!e->widened.empty() && l->op != PSK_OP_MAGNITUDE && (l->out.dtype == PSK_I8 || l->out.dtype == PSK_E4M3)) forget_widened(e, table[l->n_inputs]);
     DevLaunch L;
     memset(&L, 0, sizeof L);
     L.n_in = l->n_inputs; L.n_outer = l->n_outer; L.n_inner = l->n_inner; L.kdtype = l->dtype;
@@ -818,20 +857,14 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
         // widened to bf16 once, the channel's scale applied to the sum
         const bool w8 = mapped && device_order && e->encode && B.dtype == PSK_I8 && B.scales && !B.affine && A.dtype == PSK_BF16 && !l->int_accum
             && (L.kdtype == PSK_BF16 || L.kdtype == PSK_F32) && g.a_k == 1 && (g.b_k == 1 || g.b_n == 1) && aligned16(A.p) && g.c_col_lo == 1 && g.n >= 8 && g.k >= 8;
-        if (w8) {
-            const int64_t count = l->in[1].numel;
-            auto key = std::make_pair(B.p, count);
-            auto it = e->widened.find(key);
-            if (it == e->widened.end()) {
-                void *wb = nullptr;
-                if (cudaMalloc(&wb, (size_t)count * 2) != cudaSuccess) { cudaGetLastError(); wb = nullptr; }
-                if (wb) {
-                    k_int8_to_bf16<<<grid_for(e, count, 256, 8), 256, 0, e->stream>>>((const int8_t *)B.p, (uint16_t *)wb, count);
-                    e->kernels += 1;
-                    it = e->widened.emplace(key, wb).first;
-                }
-            }
-            if (it != e->widened.end()) {
+        // e4m3fn weights (a `params` entry narrower than the site: the kernel's loads widen them exactly,
+        // presk-kernel/src/ir.rs:47-49) against bf16 activations: every e4m3fn number is a bf16 number, so the
+        // same widened copy, without a scale
+        const bool wf8 = mapped && device_order && e->encode && B.dtype == PSK_E4M3 && !B.affine && A.dtype == PSK_BF16 && !l->int_accum
+            && (L.kdtype == PSK_BF16 || L.kdtype == PSK_F32) && g.a_k == 1 && (g.b_k == 1 || g.b_n == 1) && aligned16(A.p) && g.c_col_lo == 1 && g.n >= 8 && g.k >= 8;
+        if (w8 || wf8) {
+            const void *wide = widened_weights(e, B.p, l->in[1].numel, w8);
+            if (wide) {
                 psk_gemm pg;
                 memset(&pg, 0, sizeof pg);
                 pg.in_dtype = PSK_BF16; pg.out_dtype = L.out.dtype; pg.b_n_major = g.b_k == 1 ? 0 : 1; pg.guarded = L.guarded;
@@ -842,7 +875,7 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
                 pg.c_col_lo_count = g.c_col_lo_count; pg.c_col_hi = g.c_col_hi; pg.c_lo = g.c_lo; pg.c_hi = g.c_hi;
                 if (g.m == 1) pg.a_row = g.k;
                 std::string keep = e->error;
-                int r = launch_tc(e, pg, A.p, it->second, const_cast<void *>(L.out.p), L.ovf, B.scales, g.bs_n, g.bs_lo, g.bs_hi);
+                int r = launch_tc(e, pg, A.p, wide, const_cast<void *>(L.out.p), L.ovf, w8 ? B.scales : nullptr, w8 ? g.bs_n : 0, w8 ? g.bs_lo : 0, w8 ? g.bs_hi : 0);
                 if (r == PSK_OK) {
                     e->last_kernel = "k_gemm_tc";
                     e->last_flops = 2.0 * (double)g.m * (double)g.n * (double)g.k * (double)g.batch;
@@ -1131,7 +1164,8 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
         GemmMap g;
         const bool mapped = map_gemm(L2, g);
         const DevOperand &A = L.in[0], &B = L.in[1], &X = L.in[2];
-        bool fits = mapped && device_order && e->encode && A.dtype == PSK_BF16 && B.dtype == PSK_BF16 && X.dtype == PSK_BF16 && !any_affine
+        const bool b_int8 = B.dtype == PSK_I8 && B.scales, b_e4m3 = B.dtype == PSK_E4M3; // as in a plain contraction: read through a widened copy
+        bool fits = mapped && device_order && e->encode && A.dtype == PSK_BF16 && (B.dtype == PSK_BF16 || b_int8 || b_e4m3) && X.dtype == PSK_BF16 && !any_affine
             && l->dtype == PSK_BF16 && l->out.dtype == PSK_BF16 && l->iparam[1] == PSK_BF16
             && g.a_k == 1 && (g.b_k == 1 || g.b_n == 1) && aligned16(A.p) && aligned16(B.p) && aligned16(X.p) && g.c_col_lo == 1 && g.m >= 1 && g.n >= 8 && g.k >= 8;
         for (int a = 0; a < L.n_outer && fits; ++a) fits = L.dims[a] == 1 || X.stride[a] == L.out.stride[a]; // the addend walks the space as the result does
@@ -1145,7 +1179,12 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
         pg.c_row_lo_count = g.c_row_lo_count; pg.c_row_lo = g.c_row_lo; pg.c_row_hi = g.c_row_hi;
         pg.c_col_lo_count = g.c_col_lo_count; pg.c_col_hi = g.c_col_hi; pg.c_lo = g.c_lo; pg.c_hi = g.c_hi;
         if (g.m == 1) pg.a_row = g.k;
-        int r = launch_tc(e, pg, A.p, B.p, const_cast<void *>(L.out.p), L.ovf, nullptr, 0, 0, 0, 0, 2, X.p);
+        const void *bp = B.p;
+        if (b_int8 || b_e4m3) {
+            bp = widened_weights(e, B.p, l->in[1].numel, b_int8);
+            if (!bp) { rc = fail(e, PSK_E7005, nm + ": no memory for the weights' bf16 copy"); break; }
+        }
+        int r = launch_tc(e, pg, A.p, bp, const_cast<void *>(L.out.p), L.ovf, b_int8 ? B.scales : nullptr, b_int8 ? g.bs_n : 0, b_int8 ? g.bs_lo : 0, b_int8 ? g.bs_hi : 0, 0, 2, X.p);
         if (r == PSK_E7001) { rc = fail(e, PSK_E7005, nm + ": " + e->error); break; } // strides no tensor map or staged epilogue takes: the caller's two launches
         rc = r;
         e->last_kernel = "k_gemm_tc";

@@ -28,6 +28,7 @@
 // where in `status`, raises a flag in shared memory that ends every other
 // loop, frees its tensor memory and returns.
 #pragma once
+#include <type_traits>
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -232,7 +233,9 @@ struct Smem {
 // only when that is exact), then the store's rounding.
 // PER_BATCH: the guard's flag is one word a batch entry (P.ovf[b]) instead of
 // one word a launch, for a caller that wants to know which entry overflowed.
-template <int BN, bool PER_BATCH = false, int MT = 1>
+// CS: the instantiation launched when columns carry a scale (integer weights); it alone holds the epilogue's
+// vector paths for scales, so that the plain instantiation keeps its registers.
+template <int BN, bool PER_BATCH = false, int MT = 1, bool CS = false>
 __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ Params P)
 {
     static_assert(MT == 1 || (MT == 2 && BN == 256), "two halves fill tensor memory with 256 columns each");
@@ -368,6 +371,8 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
         const bool plain_bf16 = P.out_dtype == PSK_BF16 && !P.scale_on && !P.col_scale && !P.addend;
         const bool plain_add = P.out_dtype == PSK_BF16 && !P.scale_on && !P.col_scale && P.addend;
         const bool plain_f32 = P.out_dtype == PSK_F32 && !P.scale_on && !P.col_scale;
+        const bool plain_cs = CS && P.out_dtype == PSK_BF16 && !P.scale_on && P.col_scale && P.col_scale_stride == 1 && !P.addend;
+        const bool plain_cs_add = CS && P.out_dtype == PSK_BF16 && !P.scale_on && P.col_scale && P.col_scale_stride == 1 && P.addend;
         for (int64_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
             const int64_t b = t / tiles_per_batch, r = t % tiles_per_batch;
             int64_t mt, nt;
@@ -448,6 +453,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
                         uint32_t va[32], vb[32];
                         tmem_ld32(tbase + c0, va);
                         tmem_ld32(tbase + c0 + 32, vb);
+                        const bool cs_add = plain_cs_add && col + 64 <= P.n && (reinterpret_cast<uintptr_t>(cs_base + col) & 15) == 0;
                         if (plain_add) {
                             // the residual of this lane's row, 128 bytes, fetched while tensor memory is being read (taking it
                             // through the staging tile in whole lines was tried and is slower: 0.58 ms against 0.48 ms)
@@ -469,6 +475,29 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
                                 }
                                 stage_out[lane * 8 + (j ^ (lane & 7))] = make_uint4(u[0], u[1], u[2], u[3]);
                             }
+                        } else if (cs_add) {
+                            // integer weights and a residual: each column's sum times its channel's scale, rounded, then the
+                            // addition, rounded; eight columns at a time (their scales and this row's addend fetched together)
+                            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                            const float4 *sc = reinterpret_cast<const float4 *>(cs_base + col);
+                            const uint4 *ap = reinterpret_cast<const uint4 *>((const uint16_t *)P.addend + row_off + add_col_off);
+                            const bool live = row < P.m;
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                const uint4 ad = live ? ap[j] : make_uint4(0u, 0u, 0u, 0u);
+                                const float4 s0 = __ldg(sc + 2 * j), s1 = __ldg(sc + 2 * j + 1);
+                                const uint32_t aw[4] = {ad.x, ad.y, ad.z, ad.w};
+                                const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+                                uint32_t u[4];
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    const int e = (j & 3) * 8 + 2 * i;
+                                    const float x0 = __fmul_rn(__uint_as_float(j < 4 ? va[e] : vb[e]), sv[2 * i]), x1 = __fmul_rn(__uint_as_float(j < 4 ? va[e + 1] : vb[e + 1]), sv[2 * i + 1]);
+                                    const uint32_t p = pack_bf16x2_hw(x0, x1);
+                                    u[i] = pack_bf16x2_hw(__fadd_rn(bits_f32(aw[i] << 16), bits_f32(p << 16)), __fadd_rn(bits_f32(aw[i] & 0xffff0000u), bits_f32(p & 0xffff0000u)));
+                                }
+                                stage_out[lane * 8 + (j ^ (lane & 7))] = make_uint4(u[0], u[1], u[2], u[3]);
+                            }
                         } else {
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                         if (plain_bf16) {
@@ -481,6 +510,24 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
                                 stage_out[lane * 8 + ((4 + q) ^ (lane & 7))] = make_uint4(
                                     pack_bf16x2_hw(__uint_as_float(vb[q * 8]), __uint_as_float(vb[q * 8 + 1])), pack_bf16x2_hw(__uint_as_float(vb[q * 8 + 2]), __uint_as_float(vb[q * 8 + 3])),
                                     pack_bf16x2_hw(__uint_as_float(vb[q * 8 + 4]), __uint_as_float(vb[q * 8 + 5])), pack_bf16x2_hw(__uint_as_float(vb[q * 8 + 6]), __uint_as_float(vb[q * 8 + 7])));
+                            }
+                        } else if (plain_cs && col + 64 <= P.n && (reinterpret_cast<uintptr_t>(cs_base + col) & 15) == 0) {
+                            // integer weights: each column's sum times its channel's scale (one f32 multiplication), then the
+                            // rounding; the 64 scales of the group are the same for every lane (one line of the L1 a load)
+                            const float4 *sc = reinterpret_cast<const float4 *>(cs_base + col);
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                const float4 s0 = __ldg(sc + 2 * q), s1 = __ldg(sc + 2 * q + 1), s2 = __ldg(sc + 8 + 2 * q), s3 = __ldg(sc + 8 + 2 * q + 1);
+                                stage_out[lane * 8 + (q ^ (lane & 7))] = make_uint4(
+                                    pack_bf16x2_hw(__fmul_rn(__uint_as_float(va[q * 8]), s0.x), __fmul_rn(__uint_as_float(va[q * 8 + 1]), s0.y)),
+                                    pack_bf16x2_hw(__fmul_rn(__uint_as_float(va[q * 8 + 2]), s0.z), __fmul_rn(__uint_as_float(va[q * 8 + 3]), s0.w)),
+                                    pack_bf16x2_hw(__fmul_rn(__uint_as_float(va[q * 8 + 4]), s1.x), __fmul_rn(__uint_as_float(va[q * 8 + 5]), s1.y)),
+                                    pack_bf16x2_hw(__fmul_rn(__uint_as_float(va[q * 8 + 6]), s1.z), __fmul_rn(__uint_as_float(va[q * 8 + 7]), s1.w)));
+                                stage_out[lane * 8 + ((4 + q) ^ (lane & 7))] = make_uint4(
+                                    pack_bf16x2_hw(__fmul_rn(__uint_as_float(vb[q * 8]), s2.x), __fmul_rn(__uint_as_float(vb[q * 8 + 1]), s2.y)),
+                                    pack_bf16x2_hw(__fmul_rn(__uint_as_float(vb[q * 8 + 2]), s2.z), __fmul_rn(__uint_as_float(vb[q * 8 + 3]), s2.w)),
+                                    pack_bf16x2_hw(__fmul_rn(__uint_as_float(vb[q * 8 + 4]), s3.x), __fmul_rn(__uint_as_float(vb[q * 8 + 5]), s3.y)),
+                                    pack_bf16x2_hw(__fmul_rn(__uint_as_float(vb[q * 8 + 6]), s3.z), __fmul_rn(__uint_as_float(vb[q * 8 + 7]), s3.w)));
                             }
                         } else
 #pragma unroll

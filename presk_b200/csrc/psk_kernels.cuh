@@ -1166,6 +1166,14 @@ __global__ void __launch_bounds__(256) k_int8_to_bf16(const int8_t *q, uint16_t 
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) out[i] = (uint16_t)(f32_bits((float)q[i]) >> 16);
 }
 
+// e4m3fn weights as bf16 numbers (4 exponent and 3 fraction bits fit bf16's 8 and 7; the subnormals are
+// normal bf16 numbers; the NaN stays a NaN).
+__global__ void __launch_bounds__(256) k_e4m3_to_bf16(const uint8_t *q, uint16_t *out, int64_t n)
+{
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) out[i] = (uint16_t)(f32_bits(e4m3_to_f32(q[i])) >> 16);
+}
+
 // Normal draws for parameters made on the device: a counter-based hash
 // (splitmix64) and Box-Muller in f32 with CUDA's own logf/cosf. These are not
 // the reference's keys; they only have to be the same on every run.

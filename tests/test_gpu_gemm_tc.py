@@ -258,3 +258,75 @@ def test_contract_add_and_integer_weights_on_the_256_row_tiles(cuda, oracle):
     assert np.abs(got - want).max() <= 2.0**-7 * np.abs(want).max()
     for p in (pa, pw, px, pc, ps, pf, pq, psc):
         cuda.free(p)
+
+
+def _narrow_weight_launch(m, n, k, wdtype, order):
+    from presk_b200 import launch_desc
+    l = launch_desc(abi.OP_CONTRACT, abi.BF16, [m, n], [k], order=order)
+    l.n_inputs = 2
+    l.inputs[0].dtype, l.inputs[0].numel, l.inputs[0].stride[0], l.inputs[0].stride[2] = abi.BF16, m * k, k, 1
+    l.inputs[1].dtype, l.inputs[1].numel, l.inputs[1].stride[1], l.inputs[1].stride[2] = wdtype, n * k, 1, n
+    l.out.dtype, l.out.numel, l.out.stride[0], l.out.stride[1] = abi.BF16, m * n, n, 1
+    if wdtype == abi.I8:
+        l.inputs[1].scale_stride[1] = 1
+    return l
+
+
+def _bf16_values(raw):
+    return (np.frombuffer(raw, np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def test_integer_weights_widened_once_follow_their_codes(cuda, oracle):
+    """Integer weights reach the tensor-core kernel as a bf16 copy made once and kept; the copy is dropped when
+    the codes are written again. 328 columns: five whole groups of 64 (the epilogue's path with the scales of
+    a group loaded as vectors) and a ragged one of 8."""
+    m, n, k = 512, 328, 256
+    rng = np.random.default_rng(23)
+    a = oracle.convert((rng.standard_normal((m, k)) * 0.1).astype(np.float32), abi.BF16)
+    sc = (rng.uniform(0.5, 2.0, n) * 1e-3).astype(np.float32)
+    pa, psc, pc = cuda.upload(a), cuda.upload(sc), cuda.alloc(m * n * 2)
+    pq = cuda.alloc(k * n)
+    for seed in (1, 2):
+        q = np.random.default_rng(seed).integers(-127, 128, size=(k, n), dtype=np.int8)
+        cuda._check(cuda.lib.psk_exec_upload(cuda.handle, pq, q.ctypes.data_as(C.c_void_p), q.nbytes))
+        cuda.set_profiling(True)
+        cuda.run(_narrow_weight_launch(m, n, k, abi.I8, abi.ORDER_DEVICE), [pa, pq, pc, psc])
+        cuda.sync()
+        assert any(rec[0] == "k_gemm_tc" for rec in cuda.profile()), "the launch did not reach the tensor-core kernel"
+        cuda.set_profiling(False)
+        got = _bf16_values(cuda.download(pc, m * n * 2))
+        want_b = np.zeros(m * n * 2, np.uint8)
+        oracle.run(_narrow_weight_launch(m, n, k, abi.I8, abi.ORDER_SEQUENTIAL), [np.ascontiguousarray(a), np.ascontiguousarray(q), want_b, sc])
+        want = _bf16_values(want_b)
+        assert np.abs(got - want).max() <= 2.0**-7 * np.abs(want).max(), seed
+    for p in (pa, psc, pc, pq):
+        cuda.free(p)
+
+
+@pytest.mark.parametrize("m,n,k", [(512, 256, 512), (130, 264, 72)])
+def test_e4m3_weights_on_tensor_cores(cuda, oracle, m, n, k):
+    """Weights stored e4m3fn under a bf16 site (a `params` entry narrower than the site): widened exactly, once,
+    to the bf16 numbers they are; products exact, sums in the unit's order, within the bf16 tolerance of the
+    oracle's sequential result."""
+    rng = np.random.default_rng(29)
+    a = oracle.convert((rng.standard_normal((m, k)) * 0.1).astype(np.float32), abi.BF16)
+    w = oracle.convert(rng.standard_normal((k, n)).astype(np.float32), abi.E4M3)
+    assert w.dtype == np.uint8 and w.size == k * n
+    pa, pw, pc = cuda.upload(a), cuda.upload(w), cuda.alloc(m * n * 2)
+    cuda.set_profiling(True)
+    cuda.run(_narrow_weight_launch(m, n, k, abi.E4M3, abi.ORDER_DEVICE), [pa, pw, pc])
+    cuda.sync()
+    assert any(rec[0] == "k_gemm_tc" for rec in cuda.profile()), "the launch did not reach the tensor-core kernel"
+    cuda.set_profiling(False)
+    got = _bf16_values(cuda.download(pc, m * n * 2))
+    want_b = np.zeros(m * n * 2, np.uint8)
+    oracle.run(_narrow_weight_launch(m, n, k, abi.E4M3, abi.ORDER_SEQUENTIAL), [np.ascontiguousarray(a), np.ascontiguousarray(w), want_b])
+    want = _bf16_values(want_b)
+    assert np.isfinite(want).all() and np.abs(want).max() > 0.1
+    assert np.abs(got - want).max() <= 2.0**-7 * np.abs(want).max()
+    # and the sequential order on the device is the oracle's bits
+    cuda.run(_narrow_weight_launch(m, n, k, abi.E4M3, abi.ORDER_SEQUENTIAL), [pa, pw, pc])
+    cuda.sync()
+    assert np.array_equal(np.frombuffer(cuda.download(pc, m * n * 2), np.uint8), want_b)
+    for p in (pa, pw, pc):
+        cuda.free(p)

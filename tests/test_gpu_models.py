@@ -250,6 +250,46 @@ def test_merged_launches_keep_every_bit_on_the_gpu(cuda, oracle, kind):
         assert_same_bits(outs[1], want)
 
 
+NARROW = ("blocks.attn.wq", "blocks.attn.wk", "blocks.attn.wv", "blocks.attn.wo", "blocks.ff.gate.w", "blocks.ff.up.w", "blocks.ff.down.w")
+
+
+@pytest.mark.parametrize("weights", ["int8", "e4m3fn"])
+def test_narrow_weights_through_the_model(cuda, oracle, weights):
+    """Projection and FFN weights as int8 codes with a scale a channel (`quant`) or stored e4m3fn (`params`), bf16
+    activations. Sequential order: the oracle's bits. Device order: the contractions run on the tensor cores from a
+    bf16 copy of the codes, merged launches (the residual additions in the contractions' epilogues among them) keep
+    the bits of the unmerged list, and the logits stay within the bf16 tolerance of the sequential result."""
+    c = dict(V=512, D=256, H=4, G=2, FF=512, L=2)
+    p = models.llama_params(c)
+    ids = np.random.default_rng(12).integers(0, c["V"], size=(2, 128), dtype=np.int64)
+
+    def rz(order):
+        r = {"default": "bf16", "order": order, "storage": {"Llama.apply/%11": "f32"}}
+        if weights == "int8":
+            r["params"] = {k: "bf16" for k in p if k not in NARROW}
+            r["quant"] = {k: {"bits": 8, "over": -2} for k in NARROW}
+        else:
+            r["params"] = {k: ("e4m3fn" if k in NARROW else "bf16") for k in p}
+        return r
+
+    want = models.give(Host(oracle.vtable(), rz({"kind": "sequential"})).prepare("llama", **c), p).call("apply", [ids], (2, 128, c["V"]))
+    got = models.give(Host(cuda, rz({"kind": "sequential"})).prepare("llama", **c), p).call("apply", [ids], (2, 128, c["V"]))
+    assert_same_bits(got, want)
+    outs = []
+    for extra in ({}, {"launches": "merged"}):
+        h = models.give(Host(cuda, rz(dict(kind="device", **extra))).prepare("llama", **c), p)
+        h.set_logging(True)
+        cuda.set_profiling(True)
+        outs.append(h.call("apply", [ids], (2, 128, c["V"])))
+        prof = cuda.profile()
+        cuda.set_profiling(False)
+        log = h.launch_log()
+        assert sum(1 for rec in prof if rec[0] == "k_gemm_tc") >= 7 * c["L"], "the narrow weights did not reach the tensor-core kernel"
+    assert any(n.endswith("+add") for n in log), log
+    assert_same_bits(outs[1], outs[0])
+    assert np.abs(outs[1] - want).max() <= 2.0**-5 * np.abs(want).max()
+
+
 @pytest.mark.parametrize("dtype", ["f32", "bf16", "f16"])
 @pytest.mark.parametrize("d,b", [(4, 2), (64, 48)])
 def test_mlp_gradient_bit_exact(cuda, oracle, dtype, d, b):

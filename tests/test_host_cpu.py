@@ -204,3 +204,22 @@ def test_merged_launches_keep_every_bit(oracle):
         assert not any(n.startswith("slice") or n.startswith("concat") for n in logs[1])
         assert logs[1].count("cos") == 1 and logs[0].count("cos") == 2 * c["L"]  # the log is that of the last call
         assert len(logs[1]) < len(logs[0])
+
+
+def test_e4m3_weights_are_the_bf16_model_on_rounded_weights(oracle):
+    """`params: e4m3fn` under bf16 sites: the kernels' loads widen the codes exactly, so the call is, bit for bit,
+    the bf16 model run on weights rounded to e4m3fn beforehand."""
+    c = models.LLAMA_TINY
+    p = models.llama_params(c)
+    narrow = ("blocks.attn.wq", "blocks.attn.wk", "blocks.attn.wv", "blocks.attn.wo", "blocks.ff.gate.w", "blocks.ff.up.w", "blocks.ff.down.w")
+    ids = np.random.default_rng(3).integers(0, c["V"], size=(2, 16), dtype=np.int64)
+    h = models.give(Host(oracle.vtable(), {"default": "bf16", "params": {k: "e4m3fn" for k in narrow}}).prepare("llama", **c), p)
+    got = h.call("apply", [ids], (2, 16, c["V"]))
+    rounded = dict(p)
+    for k in narrow:
+        w = np.asarray(p[k], np.float32)
+        rounded[k] = oracle.widen(oracle.convert(w, abi.E4M3), abi.E4M3, w.size).reshape(w.shape)
+    want = models.give(Host(oracle.vtable(), {"default": "bf16"}).prepare("llama", **c), rounded).call("apply", [ids], (2, 16, c["V"]))
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    plain = models.give(Host(oracle.vtable(), {"default": "bf16"}).prepare("llama", **c), p).call("apply", [ids], (2, 16, c["V"]))
+    assert not np.array_equal(plain, want)
