@@ -108,12 +108,21 @@ typedef enum {
                              type: the reference's two slices, two groups of three steps and concatenation, for the
                              case that all of their sites are stored in x's type (the host offers nothing else).
                              Space: the axes of the result. Inputs: x, c, s. */
-    PSK_OP_CONTRACT_ADD = 14 /* a contraction and the addition of a third operand to its result as one launch: the
+    PSK_OP_CONTRACT_ADD = 14, /* a contraction and the addition of a third operand to its result as one launch: the
                              reference's `ein`/`dot` followed by a residual `add` (examples/coverage/llama.psk:117-118).
                              Inputs 0 and 1 as in PSK_OP_CONTRACT, input 2 over the outer axes. iparam[1]: the storage
                              type of the contraction's own site; dtype: the sum's. The value is DEFINED as that of the
                              two launches (contraction stored in its type, then in[2] + it); an executor that takes
                              it must give their bits under the launch's order. */
+    PSK_OP_XENT_VJP = 15, /* lower.rs:1472-1488: cross_entropy_vjp. Space as PSK_OP_XENT (outer axes, one inner axis:
+                             the classes). Inputs: logits, labels, the cotangent over the outer axes. Output over the
+                             whole space: (exp(x - m) / z - [k == y]) * ct, m and z as in PSK_OP_XENT (the maximum from
+                             the row's first element, z summed in index order), each operation rounded. */
+    PSK_OP_EMBED_VJP = 16 /* lower.rs:1444-1457: embed_vjp. Space as PSK_OP_EMBED: (the indices' axes..., d). Inputs: the
+                             table (its shape only: never read), the indices, the cotangent over the space. Output: a
+                             table of iparam[0] rows (strides in out.stride[0], out.stride[1]), zero-filled, then
+                             row idx[iv] += ct[iv, :] for every iv in index order, each sum kept in the output's
+                             storage type (rounded there after every addition). */
 } psk_op;
 
 /* Elementary operations of a fusion group's steps (lower.rs:184-226). */

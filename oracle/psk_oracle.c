@@ -980,6 +980,53 @@ static int psk_oracle_run_merged(const psk_launch *l, void *const *table, uint32
         if (bad) return PSK_E7001;
         break;
     }
+    case PSK_OP_XENT_VJP: { /* lower.rs:1472-1488: (softmax(x) - onehot(y)) * ct, row by row */
+        const int64_t n = inner, s = l->in[0].stride[no], os = l->out.stride[no];
+#pragma omp parallel for schedule(static) reduction(| : ovf_all)
+        for (int64_t row = 0; row < total; ++row) {
+            uint32_t ovf = 0;
+            int64_t base = offset_of(l->in[0].stride, l->dims, 0, no, row);
+            float m = load_operand(&in[0], base, 0, kd, &ovf);
+            for (int64_t k = 0; k < n; ++k) {
+                float x = load_operand(&in[0], base + k * s, 0, kd, &ovf);
+                if (x > m) m = x;
+            }
+            float z = 0.0f;
+            for (int64_t k = 0; k < n; ++k) z = z + presk_expf(load_operand(&in[0], base + k * s, 0, kd, &ovf) - m);
+            int64_t y = ((const int64_t *)in[1].p)[offset_of(l->in[1].stride, l->dims, 0, no, row)];
+            float ct = load_operand(&in[2], offset_of(l->in[2].stride, l->dims, 0, no, row), 0, kd, &ovf);
+            int64_t obase = offset_of(l->out.stride, l->dims, 0, no, row);
+            for (int64_t k = 0; k < n; ++k) {
+                /* the reference compares the two integers as reals of the kernel's type */
+                float hot = (float)k == (float)y ? 1.0f : 0.0f;
+                float sm = presk_expf(load_operand(&in[0], base + k * s, 0, kd, &ovf) - m) / z;
+                ovf |= store_real(outp, l->out.dtype, obase + k * os, (sm - hot) * ct);
+            }
+            ovf_all |= ovf;
+        }
+        break;
+    }
+    case PSK_OP_EMBED_VJP: { /* lower.rs:1444-1457: zero fill, then one row added per index, in index order */
+        const int last = no - 1;
+        const int64_t d = l->dims[last], rows = total / (d ? d : 1), vocab = l->iparam[0];
+        uint32_t ovf = 0;
+        int bad = 0;
+        for (int64_t v = 0; v < vocab; ++v)
+            for (int64_t j = 0; j < d; ++j) store_real(outp, l->out.dtype, v * l->out.stride[0] + j * l->out.stride[1], 0.0f);
+        for (int64_t row = 0; row < rows; ++row) {
+            int64_t id = ((const int64_t *)in[1].p)[offset_of(l->in[1].stride, l->dims, 0, last, row)];
+            if (id < 0 || id >= vocab) { bad = 1; continue; }
+            int64_t cbase = offset_of(l->in[2].stride, l->dims, 0, last, row);
+            for (int64_t j = 0; j < d; ++j) {
+                int64_t o = id * l->out.stride[0] + j * l->out.stride[1];
+                float acc = load_real(outp, l->out.dtype, o) + load_operand(&in[2], cbase + j * l->in[2].stride[last], 0, kd, &ovf);
+                ovf |= store_real(outp, l->out.dtype, o, acc);
+            }
+        }
+        ovf_all |= ovf;
+        if (bad) return PSK_E7001;
+        break;
+    }
     case PSK_OP_ARGMAX: { /* lower.rs:1490: the last of equal maxima */
         const int64_t n = inner, s = l->in[0].stride[no];
         for (int64_t row = 0; row < total; ++row) {

@@ -21,7 +21,7 @@ DTYPE_BYTES = {F64: 8, F32: 4, BF16: 2, I64: 8, F16: 2, E8M15: 3, I8: 1, E4M3: 1
 OK, E7001, E7005, E7006, E7007, E10001 = 0, 7001, 7005, 7006, 7007, 10001
 
 # psk_op
-OP_FUSED, OP_CONTRACT, OP_REDUCE, OP_SOFTMAX, OP_XENT, OP_ARGMAX, OP_EMBED, OP_COPY, OP_IOTA, OP_CONVERT, OP_MAGNITUDE, OP_ATTENTION, OP_RMSNORM, OP_ROPE, OP_CONTRACT_ADD = range(15)
+OP_FUSED, OP_CONTRACT, OP_REDUCE, OP_SOFTMAX, OP_XENT, OP_ARGMAX, OP_EMBED, OP_COPY, OP_IOTA, OP_CONVERT, OP_MAGNITUDE, OP_ATTENTION, OP_RMSNORM, OP_ROPE, OP_CONTRACT_ADD, OP_XENT_VJP, OP_EMBED_VJP = range(17)
 
 # psk_prim
 (ADD, SUB, MUL, DIV, MAX, MIN, NEG, EXP, LOG, TANH, SQRT, SIN, COS, ABS, GELU, GELU_DERIV, RELU, HEAVISIDE, SIGN, SIGMOID, POW, REAL, DIV_N, ROUND) = range(24)

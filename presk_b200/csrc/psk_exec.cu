@@ -719,7 +719,7 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
     L.fparam = (float)l->fparam[0];
     L.status = e->status;
     L.ovf = L.guarded ? next_flag(e, l) : e->flags;
-    if (l->op != PSK_OP_EMBED && l->op != PSK_OP_IOTA && l->op != PSK_OP_MAGNITUDE && l->op != PSK_OP_ATTENTION && l->op != PSK_OP_RMSNORM && l->op != PSK_OP_ROPE) coalesce_outer(L);
+    if (l->op != PSK_OP_EMBED && l->op != PSK_OP_EMBED_VJP && l->op != PSK_OP_IOTA && l->op != PSK_OP_MAGNITUDE && l->op != PSK_OP_ATTENTION && l->op != PSK_OP_RMSNORM && l->op != PSK_OP_ROPE) coalesce_outer(L);
     L.total = 1;
     for (int a = 0; a < L.n_outer; ++a) L.total *= L.dims[a];
     L.inner = 1;
@@ -741,8 +741,8 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
     e->last_kernel = "other";
     e->last_flops = 0;
     int rc = PSK_OK;
-    if (L.total == 0 && l->op != PSK_OP_MAGNITUDE) {
-        // an empty result: nothing to store
+    if (L.total == 0 && l->op != PSK_OP_MAGNITUDE && l->op != PSK_OP_EMBED_VJP) {
+        // an empty result: nothing to store (embed_vjp still zero-fills its table)
     } else switch (l->op) {
     case PSK_OP_FUSED: {
         e->last_kernel = "k_fused";
@@ -1198,6 +1198,22 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
         if (device_order && L.inner >= 256 && vec_ok) k_xent_rows_tree<<<(int)std::min<int64_t>(L.total, (int64_t)e->sms * 8), 256, 0, e->stream>>>(L);
         else k_xent_seq<<<grid_for(e, L.total, 128, 16), 128, 0, e->stream>>>(L);
         e->kernels += 1;
+        break;
+    }
+    case PSK_OP_XENT_VJP: {
+        e->last_kernel = "k_xent_vjp";
+        if (L.n_inner != 1 || L.n_in != 3) { rc = fail(e, PSK_E7001, "cross_entropy_vjp: logits, labels and a cotangent"); break; }
+        k_xent_vjp_rows<<<(int)std::min<int64_t>((L.total + 3) / 4, (int64_t)e->sms * 16), 128, 0, e->stream>>>(L);
+        e->kernels += 1;
+        break;
+    }
+    case PSK_OP_EMBED_VJP: {
+        e->last_kernel = "k_embed_vjp";
+        if (L.n_inner != 0 || L.n_in != 3 || L.n_outer < 2 || l->iparam[0] < 0) { rc = fail(e, PSK_E7001, "embed_vjp: a table, indices with an axis and a cotangent"); break; }
+        if (l->iparam[0] > 0) {
+            k_embed_vjp<<<(int)std::min<int64_t>(l->iparam[0], (int64_t)e->sms * 8), 256, 0, e->stream>>>(L);
+            e->kernels += 1;
+        }
         break;
     }
     case PSK_OP_ARGMAX:

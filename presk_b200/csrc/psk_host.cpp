@@ -918,6 +918,64 @@ struct psk_host {
         return out;
     }
 
+    // lower.rs:1472-1488: the cotangent of the logits, (softmax - onehot(y)) * ct row by row
+    Tensor cross_entropy_vjp(const std::string &site, const Tensor &logits, const Tensor &y, const Tensor &ct)
+    {
+        if (logits.axes.size() != y.axes.size() + 1 || ct.axes.size() != y.axes.size()) raise(PSK_E7001, "cross_entropy_vjp: " + show(logits.axes) + ", labels " + show(y.axes) + ", cotangent " + show(ct.axes));
+        const int64_t v = logits.axes.back().len;
+        const int no = (int)y.axes.size();
+        int d = site_dtype(site);
+        Tensor out = fresh(logits.axes, d);
+        psk_launch l;
+        memset(&l, 0, sizeof l);
+        l.op = PSK_OP_XENT_VJP;
+        l.dtype = d;
+        set_space(l, y.axes, {v});
+        std::vector<int> full, outer;
+        for (int i = 0; i <= no; ++i) full.push_back(i);
+        for (int i = 0; i < no; ++i) outer.push_back(i);
+        std::vector<int64_t> st, ss;
+        view(logits, full, no + 1, st, ss);
+        set_operand(l.in[0], logits, st, ss);
+        view(y, outer, no + 1, st, ss);
+        set_operand(l.in[1], y, st, ss);
+        view(ct, outer, no + 1, st, ss);
+        set_operand(l.in[2], ct, st, ss);
+        set_operand(l.out, out, contiguous(logits.axes), {});
+        run(l, "cross_entropy_vjp", {&logits, &y, &ct}, out);
+        return out;
+    }
+
+    // lower.rs:1444-1457: the cotangent of the table: zeros, then one row of ct added per index, in index order
+    Tensor embed_vjp(const std::string &site, const Tensor &table, const Tensor &ids, const Tensor &ct)
+    {
+        if (table.axes.size() != 2 || ct.axes.size() != ids.axes.size() + 1 || ids.axes.empty()) raise(PSK_E7001, "embed_vjp: " + show(table.axes) + ", indices " + show(ids.axes) + ", cotangent " + show(ct.axes));
+        int d = site_dtype(site);
+        Tensor out = fresh(table.axes, d);
+        psk_launch l;
+        memset(&l, 0, sizeof l);
+        l.op = PSK_OP_EMBED_VJP;
+        l.dtype = d;
+        l.iparam[0] = table.axes[0].len;
+        set_space(l, ct.axes, {});
+        const int rank = (int)ct.axes.size();
+        std::vector<int64_t> ts(rank, 0);
+        ts[0] = table.axes[1].len;
+        ts[1] = 1;
+        set_operand(l.in[0], table, ts, {});
+        std::vector<int> im, cm;
+        for (int i = 0; i + 1 < rank; ++i) im.push_back(i);
+        for (int i = 0; i < rank; ++i) cm.push_back(i);
+        std::vector<int64_t> st, ss;
+        view(ids, im, rank, st, ss);
+        set_operand(l.in[1], ids, st, ss);
+        view(ct, cm, rank, st, ss);
+        set_operand(l.in[2], ct, st, ss);
+        set_operand(l.out, out, ts, {});
+        run(l, "embed_vjp", {&table, &ids, &ct}, out);
+        return out;
+    }
+
     // A strided copy of `src` read through `stride`/`off` into `dst` at `dst_off`
     // with `dst_stride`, over `space`.
     void copy_part(const std::string &name, int d, const Axes &space, const Tensor &src, const std::vector<int64_t> &stride, int64_t extra_off, const Tensor &dst, const std::vector<int64_t> &dst_stride, int64_t dst_off, bool count)
@@ -964,6 +1022,23 @@ struct psk_host {
         v.off += lo * v.vstrides[p];
         v.axes[p].len = hi - lo;
         return v;
+    }
+
+    // lower.rs:1574-1588: zeros of the template's shape with ct at lo..hi of the axis. One nest in the reference
+    // (a zero fill, then the stores); here the host's zeros and one copy, counted as the one launch it is.
+    Tensor slice_vjp(const std::string &site, const std::string &axis, int64_t lo, int64_t hi, const Tensor &tmpl, const Tensor &ct)
+    {
+        int p = -1;
+        for (size_t i = 0; i < tmpl.axes.size(); ++i) if (tmpl.axes[i].name == axis) { p = (int)i; break; }
+        if (p < 0 || ct.axes.size() != tmpl.axes.size() || ct.axes[p].len != hi - lo || hi > tmpl.axes[p].len)
+            raise(PSK_E7001, "slice_vjp " + axis + ": " + std::to_string(lo) + ".." + std::to_string(hi) + ": a cotangent of " + show(ct.axes) + " into " + show(tmpl.axes));
+        int d = site_dtype(site);
+        const int64_t before = launches;
+        Tensor out = zeros(site, tmpl.axes);
+        launches = before;
+        auto os = contiguous(tmpl.axes);
+        copy_part("slice_vjp " + axis + ": " + std::to_string(lo) + ".." + std::to_string(hi), d, ct.axes, ct, ct.strides(), 0, out, os, lo * os[p], true);
+        return out;
     }
 
     Tensor concat(const std::string &site, const std::string &axis, const Tensor &x, const Tensor &y)
@@ -1608,6 +1683,94 @@ struct psk_host {
         return reduce_all("loss/%6", PSK_REDUCE_MEAN, ce);
     }
 
+    // The first operand's and the second's share of a cotangent through max(a, b) (min(a, b): called with the
+    // operands exchanged), presk-core/src/ad/rules.rs:115-124: diff = a - b, u = heaviside(diff) (1 where diff > 0),
+    // ca = ct * u, cb = ct * (1 - u). diff and u have two readers and are launches of their own; 1 - u has one
+    // and joins its product.
+    void max_vjp(const std::string &f, const Tensor &a, const Tensor &b, const Tensor &ct, const Tensor &one, Tensor *ca, Tensor *cb)
+    {
+        Tensor diff = binary(f + "/diff", PSK_SUB, a, b);
+        Tensor u = unary(f + "/u", PSK_HEAVISIDE, diff);
+        if (ca) *ca = binary(f + "/ca", PSK_MUL, ct, u);
+        if (cb) *cb = fused(f + "/cb", {Bn(PSK_SUB, 0, 1), Bn(PSK_MUL, 2, S(0))}, {&one, &u, &ct});
+    }
+
+    // examples/spec/concat/concat.psk `loss_grad`: the reverse-mode program of `loss`, built by the rules of
+    // presk-core/src/ad/rules.rs (cross_entropy_vjp, dot_vjp_l/r, the max/min rule above, slice_vjp, a concat's
+    // cotangent cut into two slices, embed_vjp, mean_vjp), cotangents of a value with several readers added in
+    // the reverse of the readers' order. The reference's own list of launches for this program is not pinned
+    // by a snapshot (neither the sites' numbers, written here as names, nor its additions of zero trees, left
+    // out: x + 0 changes no value but a -0); the gradient's values are (tests/run/concat_loss_grad.snap).
+    // Leaves in `results`: tok, head, qkv.wq, qkv.wk, qkv.wv.
+    Tensor toy_loss_grad(const Tensor &w)
+    {
+        const int64_t T = w.axes[1].len - 1, D = C("D");
+        const std::string f = "loss_grad";
+        // the forward pass, every value the reverse pass reads kept
+        Tensor ids = slice("inputs/%1", "seq", 0, T, w);
+        Tensor tgt = slice("targets/%1", "seq", 1, T + 1, w);
+        Tensor tok = param("tok");
+        Tensor x = embed("Toy.apply/%3", tok, ids);
+        x.axes.back().name = "model";
+        Tensor wq = param("qkv.wq"), wk = param("qkv.wk"), wv = param("qkv.wv");
+        for (Tensor *t : {&wq, &wk, &wv}) t->axes = {{"model", D}, {"out", D}};
+        Tensor w2 = concat("QKV.apply/%5", "out", wq, wk);
+        Tensor w3 = concat("QKV.apply/%7", "out", w2, wv);
+        Tensor y = dot("QKV.apply/%8", x, w3);
+        y.axes.back().name = "out";
+        Tensor q = slice("QKV.apply/%9", "out", 0, D, y), k = slice("QKV.apply/%10", "out", D, 2 * D, y), v = slice("QKV.apply/%11", "out", 2 * D, 3 * D, y);
+        Tensor one = scalar("hardtanh/%2", 1.0);
+        Tensor neg = unary("hardtanh/%3", PSK_NEG, one);
+        Tensor c = scalar("leaky/%2", 0.01);
+        Tensor m1 = binary(f + "/hardtanh.max", PSK_MAX, q, neg);
+        Tensor ht = binary(f + "/hardtanh.min", PSK_MIN, m1, one);
+        Tensor kc = binary(f + "/leaky.mul", PSK_MUL, k, c);
+        Tensor lk = binary(f + "/leaky.max", PSK_MAX, k, kc);
+        Tensor g = fused(f + "/g", {Bn(PSK_MUL, 0, 1), Bn(PSK_MIN, 2, 3), Bn(PSK_ADD, S(0), S(1))}, {&ht, &lk, &v, &q});
+        Tensor head = param("head");
+        head.axes = {{"out", D}, {"vocab", C("V")}};
+        Tensor logits = dot("Toy.apply/%14", g, head);
+        logits.axes.back().name = "vocab";
+        Tensor ce = cross_entropy("loss/%5", logits, tgt);
+        // the reverse pass
+        Tensor ct = scalar(f + "/ct", 1.0);
+        Tensor c_ce = fused(f + "/mean_vjp", {U(PSK_DIV_N, 0, (int)ce.numel())}, {&ct}, "mean_vjp", nullptr, &ce.axes);
+        Tensor c_logits = cross_entropy_vjp(f + "/cross_entropy_vjp", logits, tgt, c_ce);
+        Tensor c_g = ein(f + "/head.dot_vjp_l", {"batch", "seq", "out"}, {{"batch", "seq", "vocab"}, {"out", "vocab"}}, {&c_logits, &head}, "dot_vjp_l");
+        Tensor c_head = ein(f + "/head.dot_vjp_r", {"out", "vocab"}, {{"batch", "seq", "out"}, {"batch", "seq", "vocab"}}, {&g, &c_logits}, "dot_vjp_r");
+        // g = hardtanh(q) * leaky(k) + min(v, q): the sum hands its cotangent to both terms
+        Tensor c_v, c_q2;
+        max_vjp(f + "/min", q, v, c_g, one, &c_v, &c_q2); // min(v, q): (a, b) = (q, v); the first operand v takes ct * u
+        Tensor c_ht = binary(f + "/mul.l", PSK_MUL, c_g, lk);
+        Tensor c_lk = binary(f + "/mul.r", PSK_MUL, c_g, ht);
+        Tensor c_k1, c_kc;
+        max_vjp(f + "/leaky.max", k, kc, c_lk, one, &c_k1, &c_kc);
+        Tensor c_k2 = binary(f + "/leaky.mul", PSK_MUL, c_kc, c);
+        Tensor c_k = binary(f + "/k.add", PSK_ADD, c_k1, c_k2);
+        Tensor c_m1;
+        max_vjp(f + "/hardtanh.min", one, m1, c_ht, one, &c_m1, nullptr); // min(m1, 1): (a, b) = (1, m1); the first operand m1 takes ct * u
+        Tensor c_q1;
+        max_vjp(f + "/hardtanh.max", q, neg, c_m1, one, &c_q1, nullptr);
+        Tensor c_q = binary(f + "/q.add", PSK_ADD, c_q2, c_q1);
+        // y's three slices, the last reader first
+        Tensor yv = slice_vjp(f + "/slice_vjp.v", "out", 2 * D, 3 * D, y, c_v);
+        Tensor yk = slice_vjp(f + "/slice_vjp.k", "out", D, 2 * D, y, c_k);
+        Tensor yq = slice_vjp(f + "/slice_vjp.q", "out", 0, D, y, c_q);
+        Tensor c_y1 = binary(f + "/y.add", PSK_ADD, yv, yk);
+        Tensor c_y = binary(f + "/y.add", PSK_ADD, c_y1, yq);
+        Tensor c_x = ein(f + "/qkv.dot_vjp_l", {"batch", "seq", "model"}, {{"batch", "seq", "out"}, {"model", "out"}}, {&c_y, &w3}, "dot_vjp_l");
+        Tensor c_w3 = ein(f + "/qkv.dot_vjp_r", {"model", "out"}, {{"batch", "seq", "model"}, {"batch", "seq", "out"}}, {&x, &c_y}, "dot_vjp_r");
+        c_w3.axes = {{"model", D}, {"out", 3 * D}};
+        Tensor c_w2 = slice(f + "/concat.l", "out", 0, 2 * D, c_w3);
+        results.clear();
+        results["qkv.wv"] = slice(f + "/concat.r", "out", 2 * D, 3 * D, c_w3);
+        results["qkv.wq"] = slice(f + "/concat.l", "out", 0, D, c_w2);
+        results["qkv.wk"] = slice(f + "/concat.r", "out", D, 2 * D, c_w2);
+        results["head"] = c_head;
+        results["tok"] = embed_vjp(f + "/embed_vjp", tok, ids, c_x);
+        return results["tok"];
+    }
+
     // x·w then a row LayerNorm: %0 θ, %1 x, %2 w; %3 dot; LayerNorm.apply on it.
     Tensor contract_ln(const Tensor &x, const Tensor &w)
     {
@@ -1777,6 +1940,7 @@ struct psk_host {
             return rmsnorm_spec(param("γ"), in[0], 1e-6);
         } else if (model == "toy") {
             if (entry == "loss") { need(1); return toy_loss(in[0]); }
+            if (entry == "loss_grad") { need(1); return toy_loss_grad(in[0]); }
         } else if (model == "mlp_spec") {
             if (entry == "mse") { need(2); return spec_mse(in[0], in[1]); }
             if (entry == "mse_grad") { need(2); return spec_mse_grad(in[0], in[1]); }

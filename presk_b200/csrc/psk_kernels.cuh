@@ -867,6 +867,88 @@ __global__ void __launch_bounds__(128) k_xent_seq(const __grid_constant__ DevLau
     if (L.guarded && ovf) atomicOr(L.ovf, 1u);
 }
 
+// ---------------------------------------------------------------------------
+// PSK_OP_XENT_VJP (lower.rs:1472): (exp(x - m) / z - [k == y]) * ct over the last axis. A warp a row: lane 0
+// takes the maximum and z in index order (the sum's order is the value), every lane then writes its share
+// of the row.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) k_xent_vjp_rows(const __grid_constant__ DevLaunch L)
+{
+    uint32_t ovf = 0;
+    const int lane = threadIdx.x & 31;
+    const int64_t n = L.inner, s = L.in[0].stride[L.n_outer], os = L.out.stride[L.n_outer];
+    const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+    for (int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < L.total; row += warps) {
+        const int64_t base = operand_offset(L.in[0], L.dims, 0, L.n_outer, row);
+        float m = 0.0f, z = 0.0f;
+        if (lane == 0) {
+            m = load_operand(L.in[0], base, 0, L.kdtype, &ovf);
+            for (int64_t k = 0; k < n; ++k) {
+                float x = load_operand(L.in[0], base + k * s, 0, L.kdtype, &ovf);
+                if (x > m) m = x;
+            }
+            for (int64_t k = 0; k < n; ++k) z = __fadd_rn(z, lm_expf(__fsub_rn(load_operand(L.in[0], base + k * s, 0, L.kdtype, &ovf), m)));
+        }
+        m = __shfl_sync(0xffffffffu, m, 0);
+        z = __shfl_sync(0xffffffffu, z, 0);
+        const int64_t y = ((const int64_t *)L.in[1].p)[operand_offset(L.in[1], L.dims, 0, L.n_outer, row)];
+        const float ct = load_operand(L.in[2], operand_offset(L.in[2], L.dims, 0, L.n_outer, row), 0, L.kdtype, &ovf);
+        const int64_t obase = operand_offset(L.out, L.dims, 0, L.n_outer, row);
+        for (int64_t k = lane; k < n; k += 32) {
+            const float hot = (float)k == (float)y ? 1.0f : 0.0f; // the reference compares them as reals of the kernel's type
+            const float sm = __fdiv_rn(lm_expf(__fsub_rn(load_operand(L.in[0], base + k * s, 0, L.kdtype, &ovf), m)), z);
+            ovf |= store_real(const_cast<void *>(L.out.p), L.out.dtype, obase + k * os, __fmul_rn(__fsub_rn(sm, hot), ct));
+        }
+    }
+    if (L.guarded && ovf) atomicOr(L.ovf, 1u);
+}
+
+// ---------------------------------------------------------------------------
+// PSK_OP_EMBED_VJP (lower.rs:1444): the table's gradient. The reference zero-fills the table and adds one row of
+// the cotangent per index, in index order, the sum kept in the output's storage. Here a block owns a row of
+// the table: it walks the indices in order, 256 at a time, keeps the positions that name its row (in order),
+// and each thread adds those rows of the cotangent into its columns: the same additions in the same order.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) k_embed_vjp(const __grid_constant__ DevLaunch L)
+{
+    __shared__ int64_t hits[256];
+    __shared__ int warp_hits[8];
+    uint32_t ovf = 0;
+    const int last = L.n_outer - 1;
+    const int64_t d = L.dims[last], rows = d ? L.total / d : 0, vocab = L.iparam[0];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int64_t v = blockIdx.x; v < vocab; v += gridDim.x) {
+        // this thread's columns: tid, tid + 256, ...; the running sums live in the output, as the reference's do
+        for (int64_t j = tid; j < d; j += 256) store_real(const_cast<void *>(L.out.p), L.out.dtype, v * L.out.stride[0] + j * L.out.stride[1], 0.0f);
+        for (int64_t r0 = 0; r0 < rows; r0 += 256) {
+            const int64_t row = r0 + tid;
+            bool hit = false;
+            if (row < rows) {
+                const int64_t id = ((const int64_t *)L.in[1].p)[operand_offset(L.in[1], L.dims, 0, last, row)];
+                hit = id == v;
+                if (v == 0 && (id < 0 || id >= vocab)) atomicOr(L.status, 2u);
+            }
+            const uint32_t ballot = __ballot_sync(0xffffffffu, hit);
+            if (lane == 0) warp_hits[warp] = __popc(ballot);
+            __syncthreads();
+            int before = 0, all = 0;
+            for (int w = 0; w < 8; ++w) { if (w < warp) before += warp_hits[w]; all += warp_hits[w]; }
+            if (hit) hits[before + __popc(ballot & ((1u << lane) - 1u))] = row;
+            __syncthreads();
+            for (int h = 0; h < all; ++h) {
+                const int64_t cbase = operand_offset(L.in[2], L.dims, 0, last, hits[h]);
+                for (int64_t j = tid; j < d; j += 256) {
+                    const int64_t o = v * L.out.stride[0] + j * L.out.stride[1];
+                    const float acc = __fadd_rn(load_real(L.out.p, L.out.dtype, o), load_operand(L.in[2], cbase + j * L.in[2].stride[last], 0, L.kdtype, &ovf));
+                    ovf |= store_real(const_cast<void *>(L.out.p), L.out.dtype, o, acc);
+                }
+            }
+            __syncthreads();
+        }
+    }
+    if (L.guarded && ovf) atomicOr(L.ovf, 1u);
+}
+
 // Under PSK_ORDER_DEVICE: a block a row, z a tree sum.
 __global__ void __launch_bounds__(256) k_xent_rows_tree(const __grid_constant__ DevLaunch L)
 {

@@ -343,3 +343,25 @@ def test_toy_loss_bit_exact(cuda, oracle):
                 h.set_param(k, p)
             outs.append(h.call("loss", [w], (), np.float32))
         assert_same_bits(np.atleast_1d(outs[0]), np.atleast_1d(outs[1]))
+
+
+@pytest.mark.parametrize("v,d,b,t", [(64, 16, 5, 33), (300, 96, 4, 64)])
+def test_toy_loss_gradient_bit_exact(cuda, oracle, v, d, b, t):
+    """examples/spec/concat/concat.psk `loss_grad`: cross_entropy_vjp, dot_vjp_l/r, the max/min rule (ties go to the
+    second operand: weights of 1 make q hit the clamp's bounds exactly), slice_vjp, embed_vjp with repeated tokens:
+    every leaf of the gradient, the oracle's bits, in f32, bf16 and f16."""
+    rng = np.random.default_rng(v)
+    params = {"tok": np.round(rng.standard_normal((v, d)) * 2) / 4, "qkv.wq": np.eye(d), "qkv.wk": rng.standard_normal((d, d)) * 0.3,
+              "qkv.wv": np.diag(np.where(np.arange(d) % 2, 0.5, 1.0)), "head": rng.standard_normal((d, v)) * 0.3}  # v == q in every other column
+    w = rng.integers(0, v // 2, size=(b, t + 1), dtype=np.int64)
+    for dtype in ("f32", "bf16", "f16"):
+        leaves = []
+        for ex in (cuda, oracle.vtable()):
+            h = Host(ex, dtype).prepare("toy", V=v, D=d)
+            for k, p in params.items():
+                h.set_param(k, p)
+            h.call("loss_grad", [w], (v, d), np.float32)
+            leaves.append([h.result(k, np.shape(p), np.float32) for k, p in params.items()])
+        for k, got, want in zip(params, *leaves):
+            assert_same_bits(got, want)
+            assert np.isfinite(want).all() and (np.abs(want).max() > 0), k

@@ -455,3 +455,62 @@ def test_a_wait_that_runs_out_is_reported_and_the_executor_lives_on(cuda):
     assert np.array_equal(cuda.download(q, 256).view(np.float32), -x)
     cuda.free(p)
     cuda.free(q)
+
+
+@pytest.mark.parametrize("dtype", [abi.F32, abi.BF16])
+@pytest.mark.parametrize("rows,v", [(64, 10), (16, 1000), (5, 4099), (3, 65)])
+def test_cross_entropy_vjp_bit_exact(cuda, oracle, rows, v, dtype):
+    """(softmax(x) - onehot(y)) * ct a row: the maximum and z in index order, every operation rounded; one label
+    outside the classes (no class is hot: the comparison of the two integers simply fails)."""
+    rng = np.random.default_rng(v + rows)
+    x = oracle.convert((rng.standard_normal((rows, v)) * 3).astype(np.float32), dtype)
+    ct = oracle.convert(rng.standard_normal(rows).astype(np.float32), dtype)
+    y = rng.integers(0, v, size=(rows,), dtype=np.int64)
+    y[0] = v + 3
+    l = launch_desc(abi.OP_XENT_VJP, dtype, [rows], [v])
+    l.n_inputs = 3
+    set_operand(l.inputs[0], dtype, [rows, v], [0, 1])
+    set_operand(l.inputs[1], abi.I64, [rows], [0], is_index=True)
+    set_operand(l.inputs[2], dtype, [rows], [0])
+    set_operand(l.out, dtype, [rows, v], [0, 1])
+    nbytes = rows * v * abi.DTYPE_BYTES[dtype]
+    got, want, _, _ = run_both(cuda, oracle, l, [x, y, ct], nbytes)
+    assert np.array_equal(got, want)
+    g = oracle.widen(got, dtype, rows * v).reshape(rows, v).astype(np.float64)
+    xv = oracle.widen(x, dtype, rows * v).reshape(rows, v).astype(np.float64)
+    sm = np.exp(xv - xv.max(1, keepdims=True))
+    sm /= sm.sum(1, keepdims=True)
+    hot = np.zeros_like(sm)
+    hot[np.arange(1, rows), y[1:]] = 1.0
+    ref = (sm - hot) * oracle.widen(ct, dtype, rows).astype(np.float64)[:, None]
+    assert np.abs(g - ref).max() <= (1e-5 if dtype == abi.F32 else 2.0**-7) * max(1.0, np.abs(ref).max())
+
+
+@pytest.mark.parametrize("dtype", [abi.F32, abi.BF16])
+@pytest.mark.parametrize("shape,vocab,d", [((3, 7), 50, 24), ((2, 300), 17, 30), ((1, 1), 5, 8), ((0, 4), 6, 8)])
+def test_embed_vjp_bit_exact(cuda, oracle, shape, vocab, d, dtype):
+    """The table's gradient: zeros, then one row of the cotangent added per index in index order, the running sum
+    kept in the output's type (bf16: rounded after every addition; 600 indices into 17 rows make long chains).
+    No index at all still leaves a table of zeros."""
+    rng = np.random.default_rng(vocab)
+    n = int(np.prod(shape))
+    ids = rng.integers(0, vocab, size=shape, dtype=np.int64)
+    ct = oracle.convert(rng.standard_normal(shape + (d,)).astype(np.float32), dtype)
+    table = np.zeros(vocab * d * abi.DTYPE_BYTES[dtype], np.uint8)
+    l = launch_desc(abi.OP_EMBED_VJP, dtype, list(shape) + [d])
+    l.n_inputs = 3
+    l.iparam[0] = vocab
+    l.inputs[0].dtype, l.inputs[0].numel = dtype, vocab * d
+    l.inputs[0].stride[0], l.inputs[0].stride[1] = d, 1
+    set_operand(l.inputs[1], abi.I64, list(shape), [0, 1], is_index=True)
+    set_operand(l.inputs[2], dtype, list(shape) + [d], [0, 1, 2])
+    l.out.dtype, l.out.numel = dtype, vocab * d
+    l.out.stride[0], l.out.stride[1] = d, 1
+    nbytes = vocab * d * abi.DTYPE_BYTES[dtype]
+    got, want, _, _ = run_both(cuda, oracle, l, [table, ids, ct if n else np.zeros(1, np.uint8)], nbytes)
+    assert np.array_equal(got, want)
+    g = oracle.widen(got, dtype, vocab * d).reshape(vocab, d).astype(np.float64)
+    ref = np.zeros((vocab, d))
+    if n:
+        np.add.at(ref, ids.reshape(-1), oracle.widen(ct, dtype, n * d).reshape(n, d).astype(np.float64))
+    assert np.abs(g - ref).max() <= (1e-5 if dtype == abi.F32 else 0.1) * max(1.0, np.abs(ref).max())

@@ -153,3 +153,30 @@ def test_concat_loss_golden_on_the_oracle(oracle, ref):
     w = indices_at(ref, 0, [1], v, b * (t + 1)).reshape(b, t + 1)
     got = float(h.call("loss", [w], (), np.float32))
     assert abs(got - GOLD["concat_loss"]) <= 2e-6 * GOLD["concat_loss"], (got, GOLD["concat_loss"])
+
+
+def test_concat_loss_grad_golden_on_the_oracle(oracle, ref):
+    """tests/run/concat_loss_grad.snap: the gradient of the same loss, every leaf (tok, head, qkv.wq, qkv.wk, qkv.wv):
+    cross_entropy_vjp, dot_vjp_l/r, the max/min rule at q, k and v, slice_vjp, the concatenation's cotangent cut
+    in two, embed_vjp. wk's leaf is of magnitude 4e-7 (it flows through leaky's 0.01 and k's small values): an
+    absolute tolerance scaled to each leaf."""
+    v, d, b, t = 64, 16, 2, 8
+    h = Host(oracle.vtable(), "f32").prepare("toy", V=v, D=d)
+    h.set_param("tok", (draws_at(ref, "normal", 0, [0, 0], v * d) * 0.02).reshape(v, d))
+    for i, name in enumerate(("wq", "wk", "wv")):
+        h.set_param("qkv." + name, (draws_at(ref, "normal", 0, [0, 2, i], d * d) * 0.02).reshape(d, d))
+    h.set_param("head", (draws_at(ref, "normal", 0, [0, 1], d * v) * 0.02).reshape(d, v))
+    w = indices_at(ref, 0, [1], v, b * (t + 1)).reshape(b, t + 1)
+    h.set_logging(True)
+    h.call("loss_grad", [w], (v, d), np.float32)
+    log = h.launch_log()
+    assert log.count("cross_entropy_vjp") == 1 and log.count("embed_vjp") == 1 and log.count("dot_vjp_l") == 2 and log.count("dot_vjp_r") == 2
+    assert sum(1 for n in log if n.startswith("slice_vjp out")) == 3 and log.count("heaviside") == 4
+    for path, g in GOLD["concat_loss_grad"].items():
+        want = np.array(g["values"])
+        got = h.result(path, tuple(g["shape"]), np.float32)
+        np.testing.assert_allclose(got, want, rtol=0, atol=3e-6 * np.abs(want).max(), err_msg=path)
+    # rows of tokens the window does not hold stay zero
+    tok = h.result("tok", (v, d), np.float32)
+    absent = np.setdiff1d(np.arange(v), w[:, :t])
+    assert absent.size and not tok[absent].any()
