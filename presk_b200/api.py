@@ -212,10 +212,11 @@ class Host:
                 for k, d in enumerate(shape):
                     vals[i].dims[k] = d
             else:
+                shape = np.shape(x)  # a rank-0 value stays rank 0 (ascontiguousarray would make it [1])
                 a = np.ascontiguousarray(x)
                 keep.append(a)
-                vals[i].data, vals[i].dtype, vals[i].rank = a.ctypes.data, _dtype_of_array(a), a.ndim
-                for k, d in enumerate(a.shape):
+                vals[i].data, vals[i].dtype, vals[i].rank = a.ctypes.data, _dtype_of_array(a), len(shape)
+                for k, d in enumerate(shape):
                     vals[i].dims[k] = d
         return vals, keep
 

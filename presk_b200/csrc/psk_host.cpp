@@ -1771,6 +1771,75 @@ struct psk_host {
         return results["tok"];
     }
 
+    // ===========================================================================
+    // examples/tests/data/stack_grad.psk: a tower of L blocks x + tanh(x·w + b) * scale over a stacked parameter
+    // tree (blocks.w [L, D, D], blocks.b [L, D]: the fold reads layer l as a view), the loss mean(y^2), and its
+    // gradient through the fold: per block, last first, the rules of presk-core/src/ad/rules.rs (add, mul, tanh:
+    // ct * (1 - y*y), sum_to for the bias, dot_vjp_l/r), each layer's leaves placed at l of the stacked gradient.
+    // As for `toy`, the reference's list of launches is not pinned by a snapshot; the values are
+    // (tests/run/stack_grad.snap).
+    // ===========================================================================
+    Tensor tower_block(int64_t l, const Tensor &x, const Tensor &scale, Tensor *tanh_out)
+    {
+        const int64_t D = C("D");
+        const std::string f = tanh_out ? "Block.apply.fwd" : "Block.apply";
+        Tensor w = layer(param("blocks.w"), l), b = layer(param("blocks.b"), l);
+        w.axes = {{"model", D}, {"out", D}};
+        b.axes = {{"model", D}};
+        Tensor h = dot(f + "/%4", x, w);
+        h.axes.back().name = "model";
+        if (!tanh_out) return fused(f + "/%8", {Bn(PSK_ADD, 0, 1), U(PSK_TANH, S(0)), Bn(PSK_MUL, S(1), 2), Bn(PSK_ADD, 3, S(2))}, {&h, &b, &scale, &x});
+        *tanh_out = fused(f + "/%6", {Bn(PSK_ADD, 0, 1), U(PSK_TANH, S(0))}, {&h, &b}); // read again by the reverse pass
+        return fused(f + "/%8", {Bn(PSK_MUL, 0, 1), Bn(PSK_ADD, 2, S(0))}, {tanh_out, &scale, &x});
+    }
+
+    Tensor tower_loss(const Tensor &x0, const Tensor &scale)
+    {
+        Tensor x = x0;
+        for (int64_t l = 0; l < C("L"); ++l) x = tower_block(l, x, scale, nullptr);
+        Tensor sq = unary("loss/%4", PSK_POW, x, 2);
+        return reduce_all("loss/%5", PSK_REDUCE_MEAN, sq);
+    }
+
+    Tensor tower_loss_grad(const Tensor &x0, const Tensor &scale)
+    {
+        const int64_t L = C("L"), D = C("D");
+        const std::string f = "loss_grad";
+        std::vector<Tensor> xs, ts(L);
+        Tensor x = x0;
+        for (int64_t l = 0; l < L; ++l) {
+            xs.push_back(x);
+            x = tower_block(l, x, scale, &ts[l]);
+        }
+        Tensor ct1 = scalar(f + "/ct", 1.0);
+        Tensor c_sq = fused(f + "/mean_vjp", {U(PSK_DIV_N, 0, (int)x.numel())}, {&ct1}, "mean_vjp", nullptr, &x.axes);
+        Tensor two = scalar(f + "/two", 2.0), one = scalar(f + "/one", 1.0);
+        Tensor ct = fused(f + "/pow", {U(PSK_POW, 0, 1), Bn(PSK_MUL, 1, S(0)), Bn(PSK_MUL, 2, S(1))}, {&x, &two, &c_sq});
+        const Tensor &pw = param("blocks.w"), &pb = param("blocks.b");
+        Tensor gw = zeros(f + "/blocks.w", pw.axes), gb = zeros(f + "/blocks.b", pb.axes);
+        for (int64_t l = L - 1; l >= 0; --l) {
+            Tensor w = layer(pw, l), b = layer(pb, l);
+            w.axes = {{"model", D}, {"out", D}};
+            b.axes = {{"model", D}};
+            // through x + t * scale, then tanh: ct * scale * (1 - t * t)
+            Tensor c_a = fused(f + "/tanh", {Bn(PSK_MUL, 0, 1), Bn(PSK_MUL, 2, 2), Bn(PSK_SUB, 3, S(1)), Bn(PSK_MUL, S(0), S(2))}, {&ct, &scale, &ts[l], &one});
+            Tensor c_b = sum_to(f + "/b", c_a, b);
+            Tensor ca = c_a;
+            ca.axes.back().name = "out";
+            Tensor xin = xs[l];
+            xin.axes.back().name = "model";
+            Tensor c_x = ein(f + "/dot_vjp_l", {"batch", "model"}, {{"batch", "out"}, {"model", "out"}}, {&ca, &w}, "dot_vjp_l");
+            Tensor c_w = ein(f + "/dot_vjp_r", {"model", "out"}, {{"batch", "model"}, {"batch", "out"}}, {&xin, &ca}, "dot_vjp_r");
+            ct = binary(f + "/x.add", PSK_ADD, ct, c_x);
+            copy_part("scatter_params", c_w.dtype, c_w.axes, c_w, c_w.strides(), 0, gw, contiguous(c_w.axes), l * D * D, true);
+            copy_part("scatter_params", c_b.dtype, c_b.axes, c_b, c_b.strides(), 0, gb, contiguous(c_b.axes), l * D, true);
+        }
+        results.clear();
+        results["blocks.w"] = gw;
+        results["blocks.b"] = gb;
+        return gw;
+    }
+
     // x·w then a row LayerNorm: %0 θ, %1 x, %2 w; %3 dot; LayerNorm.apply on it.
     Tensor contract_ln(const Tensor &x, const Tensor &w)
     {
@@ -1941,6 +2010,9 @@ struct psk_host {
         } else if (model == "toy") {
             if (entry == "loss") { need(1); return toy_loss(in[0]); }
             if (entry == "loss_grad") { need(1); return toy_loss_grad(in[0]); }
+        } else if (model == "tower") {
+            if (entry == "loss") { need(2); return tower_loss(in[0], in[1]); }
+            if (entry == "loss_grad") { need(2); return tower_loss_grad(in[0], in[1]); }
         } else if (model == "mlp_spec") {
             if (entry == "mse") { need(2); return spec_mse(in[0], in[1]); }
             if (entry == "mse_grad") { need(2); return spec_mse_grad(in[0], in[1]); }
@@ -1963,6 +2035,7 @@ struct psk_host {
         else if (model == "mlp") names = i == 0 ? std::vector<std::string>{"batch", "model"} : std::vector<std::string>{"batch"};
         else if (model == "mlp_spec") names = {"batch", "model"};
         else if (model == "toy") names = {"batch", "seq"};
+        else if (model == "tower") names = {"batch", "model"};
         else if (model == "layernorm" || model == "rmsnorm") {
             // ℝ[..., model: D] with a prefix of named axes
             static const char *prefix[] = {"batch", "seq", "a2", "a3", "a4", "a5", "a6"};
@@ -2026,7 +2099,7 @@ int psk_host_prepare(psk_host *h, const char *model, const char *consts)
 {
     HOST_TRY(h, {
         h->model = model ? model : "";
-        static const char *known[] = {"llama", "gpt", "mlp", "mlp_spec", "toy", "layernorm", "rmsnorm", "contract_ln", "dense"};
+        static const char *known[] = {"llama", "gpt", "mlp", "mlp_spec", "toy", "tower", "layernorm", "rmsnorm", "contract_ln", "dense"};
         bool ok = false;
         for (auto k : known) ok |= h->model == k;
         if (!ok) raise(PSK_E7001, "no model `" + h->model + "`");

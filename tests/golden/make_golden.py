@@ -5,6 +5,7 @@ Sources (paths within presk-lang/presk, read as text):
   tests/run/layernorm_apply.snap, rmsnorm_apply.snap   seed-0 outputs of the exact interpreter, 12 digits
   tests/run/mlp_mse.snap, mlp_mse_grad.snap             seed-0 loss and gradient of examples/spec/mlp/mlp.psk at D = 4, B = 2
   tests/run/rope_attention2.snap, rope_attention3.snap   seed-0 outputs of examples/spec/rope/rope.psk `attention2`, `attention3` at B = 2, T = 8
+  tests/run/stack_grad.snap                             seed-0 gradient of examples/tests/data/stack_grad.psk `loss_grad` at B = 2
   tests/run/concat_loss.snap, concat_loss_grad.snap     seed-0 loss and gradient of examples/spec/concat/concat.psk at B = 2, T = 8
   crates/presk-interp/src/key.rs:86-93                  the first four normal draws of the key seed 0 names
 Run:  python tests/golden/make_golden.py <path of the reference's tree>
@@ -51,6 +52,14 @@ for line in text.splitlines():
         grad[path] = {"shape": [int(m.group(2)), int(m.group(3))], "values": json.loads(m.group(4))}
 assert sorted(grad) == ["head", "qkv.wk", "qkv.wq", "qkv.wv", "tok"], sorted(grad)
 out["concat_loss_grad"] = grad
+text = open(os.path.join(ref, "tests", "run", "stack_grad.snap")).read().split("---")[-1]
+grad = {}
+for line in text.splitlines():
+    m = re.match(r"\s*(w|b) = \[([0-9, ]+)\] (\[\[.*\]\])\s*$", line)
+    if m:
+        grad["blocks." + m.group(1)] = {"shape": [int(x) for x in m.group(2).split(",")], "values": json.loads(m.group(3))}
+assert sorted(grad) == ["blocks.b", "blocks.w"], sorted(grad)
+out["stack_grad"] = grad
 key_rs = open(os.path.join(ref, "crates", "presk-interp", "src", "key.rs")).read()
 m = re.search(r"assert_eq!\(first, \[([^\]]+)\]\)", key_rs)
 out["seed0_first_normals_bits"] = [int(x.strip(), 16) for x in m.group(1).split(",")]

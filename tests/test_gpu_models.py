@@ -365,3 +365,25 @@ def test_toy_loss_gradient_bit_exact(cuda, oracle, v, d, b, t):
         for k, got, want in zip(params, *leaves):
             assert_same_bits(got, want)
             assert np.isfinite(want).all() and (np.abs(want).max() > 0), k
+
+
+@pytest.mark.parametrize("d,L,b", [(3, 3, 2), (64, 4, 40)])
+def test_tower_gradient_through_the_fold_bit_exact(cuda, oracle, d, L, b):
+    """examples/tests/data/stack_grad.psk `loss` and `loss_grad`: a fold over a stacked parameter tree and its
+    reverse pass (layers read as views of [L, D, D] and [L, D], each layer's leaves placed at l of the stacked
+    gradient): the oracle's bits in f32, bf16 and f16."""
+    rng = np.random.default_rng(d)
+    params = {"blocks.w": rng.uniform(-1, 1, (L, d, d)) * np.sqrt(3.0 / d), "blocks.b": rng.standard_normal((L, d)) * 0.5}
+    x, scale = rng.standard_normal((b, d)), np.float64(0.7)
+    for dtype in ("f32", "bf16", "f16"):
+        leaves = []
+        for ex in (cuda, oracle.vtable()):
+            h = Host(ex, dtype).prepare("tower", D=d, L=L)
+            for k, p in params.items():
+                h.set_param(k, p)
+            loss = h.call("loss", [x, scale], (), np.float32)
+            h.call("loss_grad", [x, scale], (L, d, d), np.float32)
+            leaves.append([np.atleast_1d(loss)] + [h.result(k, np.shape(p), np.float32) for k, p in params.items()])
+        for got, want in zip(*leaves):
+            assert_same_bits(got, want)
+            assert np.isfinite(want).all() and np.abs(want).max() > 0

@@ -180,3 +180,35 @@ def test_concat_loss_grad_golden_on_the_oracle(oracle, ref):
     tok = h.result("tok", (v, d), np.float32)
     absent = np.setdiff1d(np.arange(v), w[:, :t])
     assert absent.size and not tok[absent].any()
+
+
+def test_stack_grad_golden_on_the_oracle(oracle, ref):
+    """tests/run/stack_grad.snap: examples/tests/data/stack_grad.psk `loss_grad` at B = 2, seed 0: the gradient through
+    a fold over a stacked parameter tree (three blocks x + tanh(x·w + b) * scale, the loss mean(y^2)). Tower.init
+    splits θ's key once (its one `use`), the stack splits that in L, each block's init in two: w xavier_uniform
+    (fan_in = fan_out = 3: bound 1), b normal(std = 0.5); x and the rank-0 scale are the second and third
+    arguments' keys."""
+    L, d, b = 3, 3, 2
+    h = Host(oracle.vtable(), "f32").prepare("tower", D=d, L=L)
+    w = np.stack([(2.0 * draws_at(ref, "uniform", 0, [0, 0, l, 0], d * d) - 1.0).reshape(d, d) for l in range(L)])
+    bias = np.stack([draws_at(ref, "normal", 0, [0, 0, l, 1], d) * 0.5 for l in range(L)])
+    h.set_param("blocks.w", w)
+    h.set_param("blocks.b", bias)
+    x = draws_at(ref, "normal", 0, [1], b * d).reshape(b, d)
+    scale = draws_at(ref, "normal", 0, [2], 1).reshape(())
+    h.set_logging(True)
+    h.call("loss_grad", [x, scale], (L, d, d), np.float32)
+    log = h.launch_log()
+    assert log.count("dot_vjp_l") == L and log.count("dot_vjp_r") == L and log.count("sum_to") == L and log.count("scatter_params") == 2 * L
+    for path, g in GOLD["stack_grad"].items():
+        want = np.array(g["values"])
+        got = h.result(path, tuple(g["shape"]), np.float32)
+        np.testing.assert_allclose(got, want, rtol=0, atol=3e-6 * np.abs(want).max(), err_msg=path)
+    # and the loss the gradient belongs to, against a central difference in f64 of the same function
+    def loss_at(wv):
+        y = x.astype(np.float64)
+        for l in range(L):
+            y = y + np.tanh(y @ wv[l] + bias[l]) * float(scale)
+        return np.mean(y * y)
+    got_loss = float(h.call("loss", [x, scale], (), np.float32))
+    assert abs(got_loss - loss_at(w)) <= 2e-6 * abs(loss_at(w))
