@@ -440,6 +440,21 @@ int psk_host_call(psk_host *h, const char *entry, const psk_value *inputs, int32
 /* A leaf of the last call's result when the entry returns a tree of the parameters' shape (a gradient,
  * `grad(..)(θ)`: presk-rt/src/lib.rs `Value::Record`): `path` is the parameter's, as in psk_host_set_param. */
 int psk_host_result(psk_host *h, const char *path, void *out_host, int32_t out_dtype, int64_t out_capacity, int64_t *out_numel);
+/* Gives the host a leaf of a gradient in place of one a call computed: `adamw.step` takes its `g` as an argument
+ * (presk-core/src/lower/optim.rs:8). f32 or f64 reals of the parameter's size; stored at the default type. */
+int psk_host_set_result(psk_host *h, const char *path, const void *data, int32_t dtype, const int64_t *dims, int32_t rank);
+
+/* The optimizer of a training run: the functions presk-core/src/lower/optim.rs:118-330 builds from an
+ * `optimizer adamw { … }` block. `hyperparameters` is NAME=VALUE words: lr (1e-3), beta1 (0.9), beta2 (0.999),
+ * eps (1e-8), weight_decay (0), schedule (constant | linear | cosine), warmup (steps); the block's defaults in
+ * brackets. grad_clip is refused (E7005). Setting them forgets the moments (`adamw.init`: zeros). */
+int psk_host_adamw(psk_host *h, const char *hyperparameters);
+/* `adamw.step(θ, (m, v), g, t, total)`: g = the leaves the last gradient call (or psk_host_set_result) left, one a
+ * parameter; t counts from 1. The parameters and moments are replaced; psk_host_result then reads θ' under a
+ * parameter's path and the moments under "m:" + path and "v:" + path. */
+int psk_host_adamw_step(psk_host *h, int64_t t, int64_t total);
+/* `adamw.lr(t, total)`: the schedule's learning rate, computed by the executor in the `adamw.lr` sites' type. */
+int psk_host_adamw_lr(psk_host *h, int64_t t, int64_t total, double *out);
 
 /* The same with the inputs already on the executor (`inputs[i].data` is a
  * device pointer of the host's executor) and the result left there: what a

@@ -251,6 +251,26 @@ class Host:
             raise PreskError(abi.E7001, f"the result `{path}` has {n.value} elements, not {out.size}")
         return out
 
+    def set_result(self, path, array):
+        """Gives a leaf of a gradient (what `adamw.step` takes as `g`) in place of a computed one."""
+        a = np.ascontiguousarray(array, dtype=np.float64)
+        dims = (C.c_int64 * max(a.ndim, 1))(*a.shape)
+        self._check(self.lib.psk_host_set_result(self.handle, path.encode(), a.ctypes.data, abi.F64, dims, a.ndim))
+
+    def adamw(self, **hyperparameters):
+        """`optimizer adamw { … }`: lr, beta1, beta2, eps, weight_decay, schedule, warmup; forgets the moments."""
+        self._check(self.lib.psk_host_adamw(self.handle, " ".join(f"{k}={v!r}" if isinstance(v, float) else f"{k}={v}" for k, v in hyperparameters.items()).encode()))
+        return self
+
+    def adamw_step(self, t, total):
+        """`adamw.step` on the last gradient's leaves; the parameters and moments are replaced."""
+        self._check(self.lib.psk_host_adamw_step(self.handle, t, total))
+
+    def adamw_lr(self, t, total):
+        out = C.c_double()
+        self._check(self.lib.psk_host_adamw_lr(self.handle, t, total, C.byref(out)))
+        return out.value
+
     def call_device(self, entry, inputs):
         """Backend::call with device inputs [(ptr, dtype, shape)]; returns (ptr, dtype, numel), queued."""
         vals, _ = self._values(inputs, device_ptrs=True)

@@ -1840,6 +1840,142 @@ struct psk_host {
         return gw;
     }
 
+    // ===========================================================================
+    // The optimizer of a training run: `adamw.init`, `adamw.lr`, `adamw.step` as presk-core/src/lower/optim.rs:118-330
+    // builds them (AdamW with decoupled decay; schedules constant, linear(warmup), cosine(warmup) written with relu
+    // so that they are ordinary primitives). Lets of a parameter tree's type run leaf by leaf; the groups are those
+    // fusion.rs forms over the builder's lets: per step two scalar `sub`s (1 - β), the two bias corrections as
+    // groups of four scalar steps (1 - exp(t · ln β)), the schedule as one scalar group, and per leaf three groups:
+    // m' (3 steps), v' (4 steps), θ' (9 steps). Sites: `adamw.step/%N`, N the root let's number in the builder's
+    // order (parameters %0-%4, then every let), `adamw.lr/%N` likewise. `grad_clip` is not built (refused).
+    // ===========================================================================
+    struct AdamW { double lr = 1e-3, beta1 = 0.9, beta2 = 0.999, eps = 1e-8, weight_decay = 0.0; int schedule = 0; int64_t warmup = 0; } adamw;
+    std::map<std::string, Tensor> moment_m, moment_v;
+
+    void adamw_configure(const std::string &text)
+    {
+        adamw = AdamW();
+        moment_m.clear();
+        moment_v.clear();
+        std::istringstream ss(text);
+        std::string tok;
+        while (ss >> tok) {
+            size_t eq = tok.find('=');
+            if (eq == std::string::npos) raise(PSK_E7001, "a hyperparameter is NAME=VALUE, not `" + tok + "`");
+            const std::string k = tok.substr(0, eq), v = tok.substr(eq + 1);
+            if (k == "lr") adamw.lr = strtod(v.c_str(), nullptr);
+            else if (k == "beta1") adamw.beta1 = strtod(v.c_str(), nullptr);
+            else if (k == "beta2") adamw.beta2 = strtod(v.c_str(), nullptr);
+            else if (k == "eps") adamw.eps = strtod(v.c_str(), nullptr);
+            else if (k == "weight_decay") adamw.weight_decay = strtod(v.c_str(), nullptr);
+            else if (k == "warmup") adamw.warmup = strtoll(v.c_str(), nullptr, 10);
+            else if (k == "schedule") {
+                if (v == "constant") adamw.schedule = 0;
+                else if (v == "linear") adamw.schedule = 1;
+                else if (v == "cosine") adamw.schedule = 2;
+                else raise(PSK_E7001, "schedule is constant, linear or cosine, not `" + v + "`");
+            } else if (k == "grad_clip") raise(PSK_E7005, "adamw: grad_clip is not built");
+            else raise(PSK_E7001, "adamw has no hyperparameter `" + k + "`");
+        }
+    }
+
+    // adamw.lr(t, total), optim.rs:279-328
+    Tensor adamw_lr(int64_t t, int64_t total)
+    {
+        const std::string f = "adamw.lr";
+        Tensor base = scalar(f + "/base", adamw.lr);
+        if (adamw.schedule == 0) return base;
+        Tensor tr = scalar(f + "/t", (double)t), totr = scalar(f + "/total", (double)total), w = scalar(f + "/warmup", (double)adamw.warmup);
+        Tensor one = scalar(f + "/one", 1.0), half = scalar(f + "/half", 0.5), pi = scalar(f + "/pi", 3.14159265358979323846);
+        std::vector<StepSpec> st;
+        int warm;
+        if (adamw.warmup == 0) warm = 3; // the input `one`
+        else {
+            st.push_back(Bn(PSK_DIV, 1, 2));                          // t / w
+            st.push_back(Bn(PSK_SUB, 3, S(0)));                       // min(1, x) = 1 - relu(1 - x)
+            st.push_back(U(PSK_RELU, S(1)));
+            st.push_back(Bn(PSK_SUB, 3, S(2)));
+            warm = S(3);
+        }
+        const int o = (int)st.size();
+        st.push_back(Bn(PSK_SUB, 1, 2));                              // o+0: t - w
+        st.push_back(Bn(PSK_SUB, 4, 2));                              // o+1: total - w
+        st.push_back(Bn(PSK_SUB, S(o + 1), 3));                       // o+2: ... - 1
+        st.push_back(U(PSK_RELU, S(o + 2)));                          // o+3
+        st.push_back(Bn(PSK_ADD, S(o + 3), 3));                       // o+4: max(total - w, 1)
+        st.push_back(Bn(PSK_DIV, S(o), S(o + 4)));                    // o+5
+        st.push_back(U(PSK_RELU, S(o + 5)));                          // o+6
+        st.push_back(Bn(PSK_SUB, 3, S(o + 6)));                       // o+7: min(1, .)
+        st.push_back(U(PSK_RELU, S(o + 7)));                          // o+8
+        st.push_back(Bn(PSK_SUB, 3, S(o + 8)));                       // o+9: the progress p
+        int decay;
+        if (adamw.schedule == 2) {
+            st.push_back(Bn(PSK_MUL, 5, S(o + 9)));                   // o+10: π p
+            st.push_back(U(PSK_COS, S(o + 10)));                      // o+11
+            st.push_back(Bn(PSK_ADD, 3, S(o + 11)));                  // o+12: 1 + cos
+            st.push_back(Bn(PSK_MUL, S(o + 12), 6));                  // o+13: half of it
+            decay = S(o + 13);
+        } else {
+            st.push_back(Bn(PSK_SUB, 3, S(o + 9)));                   // o+10: 1 - p
+            decay = S(o + 10);
+        }
+        st.push_back(Bn(PSK_MUL, warm, decay));
+        st.push_back(Bn(PSK_MUL, 0, S((int)st.size() - 1)));
+        return fused(f + "/lr", st, {&base, &tr, &w, &one, &totr, &pi, &half});
+    }
+
+    // adamw.step(θ, (m, v), g, t, total), optim.rs:156-219; g = the leaves of the last gradient (`results`).
+    // θ', m', v' replace the host's parameters and moments; `results` then holds θ' under the parameters'
+    // paths and the moments under "m:" + path, "v:" + path.
+    void adamw_step(int64_t t, int64_t total)
+    {
+        const std::string f = "adamw.step";
+        if (t < 1) raise(PSK_E7001, "adamw.step: steps count from 1");
+        for (auto &kv : params) {
+            if (!results.count(kv.first)) raise(PSK_E7001, "adamw.step: the gradient has no leaf `" + kv.first + "`");
+            if (kv.second.dtype == PSK_I8 || kv.second.scales) raise(PSK_E7005, "adamw.step: `" + kv.first + "` is quantised");
+        }
+        Tensor one = scalar(f + "/%8", 1.0), b1 = scalar(f + "/%10", adamw.beta1), b2 = scalar(f + "/%12", adamw.beta2);
+        Tensor omb1 = binary(f + "/%13", PSK_SUB, one, b1), omb2 = binary(f + "/%14", PSK_SUB, one, b2);
+        Tensor tr = scalar(f + "/%22", (double)t);
+        // 1 - exp(t · ln β)
+        auto bias_correction = [&](const std::string &site, const Tensor &beta) {
+            return fused(site, {U(PSK_LOG, 0), Bn(PSK_MUL, 1, S(0)), U(PSK_EXP, S(1)), Bn(PSK_SUB, 2, S(2))}, {&beta, &tr, &one});
+        };
+        Tensor bc1 = bias_correction(f + "/%26", b1), bc2 = bias_correction(f + "/%30", b2);
+        Tensor eps = scalar(f + "/%35", adamw.eps), lambda = scalar(f + "/%39", adamw.weight_decay);
+        Tensor lr = adamw_lr(t, total);
+        std::map<std::string, Tensor> grads = results, next;
+        results.clear();
+        for (auto &kv : params) {
+            const std::string &path = kv.first;
+            Tensor theta = kv.second, g = grads[path];
+            g.axes = theta.axes;
+            if (!moment_m.count(path)) { // adamw.init: zeros_like θ
+                moment_m[path] = zeros(f + "/%17", theta.axes);
+                moment_v[path] = zeros(f + "/%21", theta.axes);
+            }
+            const Tensor &m = moment_m[path], &v = moment_v[path];
+            Tensor m2 = fused(f + "/%17", {Bn(PSK_MUL, 0, 1), Bn(PSK_MUL, 2, 3), Bn(PSK_ADD, S(0), S(1))}, {&m, &b1, &g, &omb1});
+            Tensor v2 = fused(f + "/%21", {Bn(PSK_MUL, 0, 1), Bn(PSK_MUL, 2, 2), Bn(PSK_MUL, S(1), 3), Bn(PSK_ADD, S(0), S(2))}, {&v, &b2, &g, &omb2});
+            // m̂ = m'/bc1, v̂ = v'/bc2, √v̂, + ε, m̂ / that, θ·λ, their sum, × lr, θ - that
+            Tensor theta2 = fused(f + "/%44", {Bn(PSK_DIV, 0, 1), Bn(PSK_DIV, 2, 3), U(PSK_SQRT, S(1)), Bn(PSK_ADD, S(2), 4), Bn(PSK_DIV, S(0), S(3)), Bn(PSK_MUL, 5, 6), Bn(PSK_ADD, S(4), S(5)), Bn(PSK_MUL, S(6), 7), Bn(PSK_SUB, 5, S(7))},
+                                  {&m2, &bc1, &v2, &bc2, &eps, &theta, &lambda, &lr});
+            if (theta2.dtype != theta.dtype) { // a parameter stays in its own storage type
+                Tensor back = fresh(theta.axes, theta.dtype);
+                convert_into(theta2, back);
+                theta2 = back;
+            }
+            next[path] = theta2;
+            moment_m[path] = m2;
+            moment_v[path] = v2;
+            results[path] = theta2;
+            results["m:" + path] = m2;
+            results["v:" + path] = v2;
+        }
+        for (auto &kv : next) params[kv.first] = kv.second;
+    }
+
     // x·w then a row LayerNorm: %0 θ, %1 x, %2 w; %3 dot; LayerNorm.apply on it.
     Tensor contract_ln(const Tensor &x, const Tensor &w)
     {
@@ -2250,6 +2386,56 @@ int psk_host_result(psk_host *h, const char *path, void *out_host, int32_t out_d
         }
         h->check(h->vt->download(h->vt->self, out_host, o.ptr(), (size_t)o.numel() * elem_bytes(out_dtype)), "download");
         h->check(h->vt->sync(h->vt->self), "result");
+    });
+    return PSK_OK;
+}
+
+int psk_host_set_result(psk_host *h, const char *path, const void *data, int32_t dtype, const int64_t *dims, int32_t rank)
+{
+    HOST_TRY(h, {
+        if (!path || !data || (dtype != PSK_F32 && dtype != PSK_F64) || rank < 0 || rank > PSK_MAX_RANK) raise(PSK_E7001, "psk_host_set_result: a path and f32 or f64 reals");
+        auto p = h->params.find(path);
+        if (p == h->params.end()) raise(PSK_E7001, std::string("no parameter `") + path + "`");
+        Axes axes;
+        for (int i = 0; i < rank; ++i) axes.push_back({"", dims[i]});
+        Tensor raw = h->fresh(axes, dtype);
+        if (raw.numel() != p->second.numel()) raise(PSK_E7001, std::string("the leaf `") + path + "` has " + std::to_string(p->second.numel()) + " elements");
+        h->check(h->vt->upload(h->vt->self, raw.ptr(), data, (size_t)raw.numel() * elem_bytes(dtype)), "upload");
+        Tensor leaf = raw;
+        if (dtype != h->rz.dflt) {
+            leaf = h->fresh(axes, h->rz.dflt);
+            h->convert_into(raw, leaf);
+        }
+        h->results[path] = leaf;
+    });
+    return PSK_OK;
+}
+
+int psk_host_adamw(psk_host *h, const char *hyperparameters)
+{
+    HOST_TRY(h, { h->adamw_configure(hyperparameters ? hyperparameters : ""); });
+    return PSK_OK;
+}
+
+int psk_host_adamw_step(psk_host *h, int64_t t, int64_t total)
+{
+    HOST_TRY(h, {
+        h->launches = 0;
+        h->log.clear();
+        h->adamw_step(t, total);
+        h->check(h->vt->sync(h->vt->self), "adamw.step");
+    });
+    return PSK_OK;
+}
+
+int psk_host_adamw_lr(psk_host *h, int64_t t, int64_t total, double *out)
+{
+    HOST_TRY(h, {
+        Tensor lr = h->adamw_lr(t, total);
+        Tensor o = h->fresh({}, PSK_F64);
+        h->convert_into(lr, o);
+        h->check(h->vt->download(h->vt->self, out, o.ptr(), 8), "download");
+        h->check(h->vt->sync(h->vt->self), "adamw.lr");
     });
     return PSK_OK;
 }

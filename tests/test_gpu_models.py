@@ -387,3 +387,32 @@ def test_tower_gradient_through_the_fold_bit_exact(cuda, oracle, d, L, b):
         for got, want in zip(*leaves):
             assert_same_bits(got, want)
             assert np.isfinite(want).all() and np.abs(want).max() > 0
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_training_steps_bit_exact(cuda, oracle, dtype):
+    """Five steps of `loss_grad` + `adamw.step` (decay, cosine schedule with warm-up) on the tower and on the concat
+    toy: parameters, both moments and the loss after the last step, the oracle's bits."""
+    rng = np.random.default_rng(21)
+    d, L, b = 32, 3, 24
+    tower = ("tower", dict(D=d, L=L), {"blocks.w": rng.uniform(-1, 1, (L, d, d)) * np.sqrt(3.0 / d), "blocks.b": rng.standard_normal((L, d)) * 0.5},
+             [rng.standard_normal((b, d)), np.float64(0.7)], (L, d, d))
+    v, dt = 64, 16
+    toy = ("toy", dict(V=v, D=dt), {"tok": rng.standard_normal((v, dt)) * 0.5, "qkv.wq": rng.standard_normal((dt, dt)) * 0.3, "qkv.wk": rng.standard_normal((dt, dt)) * 0.3,
+                                    "qkv.wv": rng.standard_normal((dt, dt)) * 0.3, "head": rng.standard_normal((dt, v)) * 0.3},
+           [rng.integers(0, v, size=(4, 17), dtype=np.int64)], (v, dt))
+    for model, consts, params, inputs, first_shape in (tower, toy):
+        runs = []
+        for ex in (cuda, oracle.vtable()):
+            h = Host(ex, dtype).prepare(model, **consts).adamw(lr=1e-2, beta2=0.95, weight_decay=0.1, schedule="cosine", warmup=2)
+            for k, p in params.items():
+                h.set_param(k, p)
+            for t in range(1, 6):
+                h.call("loss_grad", inputs, first_shape)
+                h.adamw_step(t, 5)
+            leaves = [h.result(pre + k, np.shape(p)) for k, p in params.items() for pre in ("", "m:", "v:")]
+            leaves.append(np.atleast_1d(h.call("loss", inputs, ())))
+            runs.append(leaves)
+        for got, want in zip(*runs):
+            assert_same_bits(got, want)
+            assert np.isfinite(want).all()
