@@ -446,8 +446,8 @@ int psk_host_set_result(psk_host *h, const char *path, const void *data, int32_t
 
 /* The optimizer of a training run: the functions presk-core/src/lower/optim.rs:118-330 builds from an
  * `optimizer adamw { … }` block. `hyperparameters` is NAME=VALUE words: lr (1e-3), beta1 (0.9), beta2 (0.999),
- * eps (1e-8), weight_decay (0), schedule (constant | linear | cosine), warmup (steps); the block's defaults in
- * brackets. grad_clip is refused (E7005). Setting them forgets the moments (`adamw.init`: zeros). */
+ * eps (1e-8), weight_decay (0), grad_clip (none), schedule (constant | linear | cosine), warmup (steps); the
+ * block's defaults in brackets. Setting them forgets the moments (`adamw.init`: zeros). */
 int psk_host_adamw(psk_host *h, const char *hyperparameters);
 /* `adamw.step(θ, (m, v), g, t, total)`: g = the leaves the last gradient call (or psk_host_set_result) left, one a
  * parameter; t counts from 1. The parameters and moments are replaced; psk_host_result then reads θ' under a

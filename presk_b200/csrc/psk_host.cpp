@@ -1847,9 +1847,12 @@ struct psk_host {
     // fusion.rs forms over the builder's lets: per step two scalar `sub`s (1 - β), the two bias corrections as
     // groups of four scalar steps (1 - exp(t · ln β)), the schedule as one scalar group, and per leaf three groups:
     // m' (3 steps), v' (4 steps), θ' (9 steps). Sites: `adamw.step/%N`, N the root let's number in the builder's
-    // order (parameters %0-%4, then every let), `adamw.lr/%N` likewise. `grad_clip` is not built (refused).
+    // order (parameters %0-%4, then every let; a `grad_clip` puts 14 lets before the rest). With `grad_clip = c` the
+    // gradient is scaled by min(1, c / (‖g‖₂ + 1e-6)) first: `sum_squares` a leaf, the leaves' sums added by the host
+    // in f64 (presk-kernel/src/host.rs:1571-1587; here in the order of the parameters' paths), one scalar group of
+    // six steps for the factor, one `mul` a leaf.
     // ===========================================================================
-    struct AdamW { double lr = 1e-3, beta1 = 0.9, beta2 = 0.999, eps = 1e-8, weight_decay = 0.0; int schedule = 0; int64_t warmup = 0; } adamw;
+    struct AdamW { double lr = 1e-3, beta1 = 0.9, beta2 = 0.999, eps = 1e-8, weight_decay = 0.0, grad_clip = 0.0; bool clip = false; int schedule = 0; int64_t warmup = 0; } adamw;
     std::map<std::string, Tensor> moment_m, moment_v;
 
     void adamw_configure(const std::string &text)
@@ -1874,7 +1877,7 @@ struct psk_host {
                 else if (v == "linear") adamw.schedule = 1;
                 else if (v == "cosine") adamw.schedule = 2;
                 else raise(PSK_E7001, "schedule is constant, linear or cosine, not `" + v + "`");
-            } else if (k == "grad_clip") raise(PSK_E7005, "adamw: grad_clip is not built");
+            } else if (k == "grad_clip") { adamw.grad_clip = strtod(v.c_str(), nullptr); adamw.clip = true; }
             else raise(PSK_E7001, "adamw has no hyperparameter `" + k + "`");
         }
     }
@@ -1935,31 +1938,51 @@ struct psk_host {
             if (!results.count(kv.first)) raise(PSK_E7001, "adamw.step: the gradient has no leaf `" + kv.first + "`");
             if (kv.second.dtype == PSK_I8 || kv.second.scales) raise(PSK_E7005, "adamw.step: `" + kv.first + "` is quantised");
         }
-        Tensor one = scalar(f + "/%8", 1.0), b1 = scalar(f + "/%10", adamw.beta1), b2 = scalar(f + "/%12", adamw.beta2);
-        Tensor omb1 = binary(f + "/%13", PSK_SUB, one, b1), omb2 = binary(f + "/%14", PSK_SUB, one, b2);
-        Tensor tr = scalar(f + "/%22", (double)t);
+        std::map<std::string, Tensor> grads = results;
+        const int shift = adamw.clip ? 14 : 0;
+        auto at = [&](int n) { return f + "/%" + std::to_string(n + shift); };
+        if (adamw.clip) {
+            // %7 sum_squares g (a launch a leaf, the sums added on the host), then [%8 sqrt; %11 + 1e-6; %14 c / it;
+            // %17 1 - it; %18 relu; %19 1 - it] as one scalar group, %20 g * factor leaf by leaf
+            double acc = 0.0;
+            for (auto &kv : params) {
+                Tensor n2 = reduce_all(f + "/%7", PSK_REDUCE_SUMSQ, grads[kv.first]);
+                Tensor wide = fresh({}, PSK_F64);
+                convert_into(n2, wide);
+                double v = 0.0;
+                check(vt->download(vt->self, &v, wide.ptr(), 8), "download");
+                check(vt->sync(vt->self), "sum_squares");
+                acc += v;
+            }
+            Tensor n2 = scalar(f + "/%7", acc), tiny = scalar(f + "/%10", 1e-6), c = scalar(f + "/%13", adamw.grad_clip), one1 = scalar(f + "/%16", 1.0);
+            Tensor factor = fused(f + "/%19", {U(PSK_SQRT, 0), Bn(PSK_ADD, S(0), 1), Bn(PSK_DIV, 2, S(1)), Bn(PSK_SUB, 3, S(2)), U(PSK_RELU, S(3)), Bn(PSK_SUB, 3, S(4))}, {&n2, &tiny, &c, &one1});
+            for (auto &kv : params) grads[kv.first] = binary(f + "/%20", PSK_MUL, grads[kv.first], factor);
+        }
+        Tensor one = scalar(at(8), 1.0), b1 = scalar(at(10), adamw.beta1), b2 = scalar(at(12), adamw.beta2);
+        Tensor omb1 = binary(at(13), PSK_SUB, one, b1), omb2 = binary(at(14), PSK_SUB, one, b2);
+        Tensor tr = scalar(at(22), (double)t);
         // 1 - exp(t · ln β)
         auto bias_correction = [&](const std::string &site, const Tensor &beta) {
             return fused(site, {U(PSK_LOG, 0), Bn(PSK_MUL, 1, S(0)), U(PSK_EXP, S(1)), Bn(PSK_SUB, 2, S(2))}, {&beta, &tr, &one});
         };
-        Tensor bc1 = bias_correction(f + "/%26", b1), bc2 = bias_correction(f + "/%30", b2);
-        Tensor eps = scalar(f + "/%35", adamw.eps), lambda = scalar(f + "/%39", adamw.weight_decay);
+        Tensor bc1 = bias_correction(at(26), b1), bc2 = bias_correction(at(30), b2);
+        Tensor eps = scalar(at(35), adamw.eps), lambda = scalar(at(39), adamw.weight_decay);
         Tensor lr = adamw_lr(t, total);
-        std::map<std::string, Tensor> grads = results, next;
+        std::map<std::string, Tensor> next;
         results.clear();
         for (auto &kv : params) {
             const std::string &path = kv.first;
             Tensor theta = kv.second, g = grads[path];
             g.axes = theta.axes;
             if (!moment_m.count(path)) { // adamw.init: zeros_like θ
-                moment_m[path] = zeros(f + "/%17", theta.axes);
-                moment_v[path] = zeros(f + "/%21", theta.axes);
+                moment_m[path] = zeros(at(17), theta.axes);
+                moment_v[path] = zeros(at(21), theta.axes);
             }
             const Tensor &m = moment_m[path], &v = moment_v[path];
-            Tensor m2 = fused(f + "/%17", {Bn(PSK_MUL, 0, 1), Bn(PSK_MUL, 2, 3), Bn(PSK_ADD, S(0), S(1))}, {&m, &b1, &g, &omb1});
-            Tensor v2 = fused(f + "/%21", {Bn(PSK_MUL, 0, 1), Bn(PSK_MUL, 2, 2), Bn(PSK_MUL, S(1), 3), Bn(PSK_ADD, S(0), S(2))}, {&v, &b2, &g, &omb2});
+            Tensor m2 = fused(at(17), {Bn(PSK_MUL, 0, 1), Bn(PSK_MUL, 2, 3), Bn(PSK_ADD, S(0), S(1))}, {&m, &b1, &g, &omb1});
+            Tensor v2 = fused(at(21), {Bn(PSK_MUL, 0, 1), Bn(PSK_MUL, 2, 2), Bn(PSK_MUL, S(1), 3), Bn(PSK_ADD, S(0), S(2))}, {&v, &b2, &g, &omb2});
             // m̂ = m'/bc1, v̂ = v'/bc2, √v̂, + ε, m̂ / that, θ·λ, their sum, × lr, θ - that
-            Tensor theta2 = fused(f + "/%44", {Bn(PSK_DIV, 0, 1), Bn(PSK_DIV, 2, 3), U(PSK_SQRT, S(1)), Bn(PSK_ADD, S(2), 4), Bn(PSK_DIV, S(0), S(3)), Bn(PSK_MUL, 5, 6), Bn(PSK_ADD, S(4), S(5)), Bn(PSK_MUL, S(6), 7), Bn(PSK_SUB, 5, S(7))},
+            Tensor theta2 = fused(at(44), {Bn(PSK_DIV, 0, 1), Bn(PSK_DIV, 2, 3), U(PSK_SQRT, S(1)), Bn(PSK_ADD, S(2), 4), Bn(PSK_DIV, S(0), S(3)), Bn(PSK_MUL, 5, 6), Bn(PSK_ADD, S(4), S(5)), Bn(PSK_MUL, S(6), 7), Bn(PSK_SUB, 5, S(7))},
                                   {&m2, &bc1, &v2, &bc2, &eps, &theta, &lambda, &lr});
             if (theta2.dtype != theta.dtype) { // a parameter stays in its own storage type
                 Tensor back = fresh(theta.axes, theta.dtype);

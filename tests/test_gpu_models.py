@@ -404,7 +404,7 @@ def test_training_steps_bit_exact(cuda, oracle, dtype):
     for model, consts, params, inputs, first_shape in (tower, toy):
         runs = []
         for ex in (cuda, oracle.vtable()):
-            h = Host(ex, dtype).prepare(model, **consts).adamw(lr=1e-2, beta2=0.95, weight_decay=0.1, schedule="cosine", warmup=2)
+            h = Host(ex, dtype).prepare(model, **consts).adamw(lr=1e-2, beta2=0.95, weight_decay=0.1, grad_clip=0.5, schedule="cosine", warmup=2)
             for k, p in params.items():
                 h.set_param(k, p)
             for t in range(1, 6):

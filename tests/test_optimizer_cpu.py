@@ -73,8 +73,6 @@ def test_training_steps_follow_float64_adamw_and_lower_the_loss(oracle):
 
 def test_optimizer_errors(oracle):
     h = Host(oracle.vtable(), "f32").prepare("tower", D=3, L=1)
-    with pytest.raises(PreskError, match="E7005"):
-        h.adamw(grad_clip=1.0)
     with pytest.raises(PreskError, match="E7001"):
         h.adamw(momentum=0.9)
     h.adamw()
@@ -82,3 +80,28 @@ def test_optimizer_errors(oracle):
     h.set_param("blocks.b", np.ones((1, 3)))
     with pytest.raises(PreskError, match="no leaf"):
         h.adamw_step(1, 10)
+
+
+@pytest.mark.parametrize("clip", [0.05, 100.0])
+def test_gradient_clipping_to_the_global_norm(oracle, clip):
+    """`grad_clip = c`: g · min(1, c / (‖g‖₂ + 1e-6)) over all leaves before the moments (optim.rs:166-178); a bound
+    below the norm scales the step, one far above leaves it alone."""
+    rng = np.random.default_rng(8)
+    g = {"blocks.w": rng.standard_normal((2, 4, 4)), "blocks.b": rng.standard_normal((2, 4))}
+    norm = np.sqrt(sum((v.astype(np.float32).astype(np.float64) ** 2).sum() for v in g.values()))
+    factor = min(1.0, clip / (norm + 1e-6))
+    outs = []
+    for hp, scale in ((dict(grad_clip=clip), 1.0), (dict(), factor)):
+        h = Host(oracle.vtable(), "f32").prepare("tower", D=4, L=2).adamw(lr=1e-2, **hp)
+        h.set_param("blocks.w", np.ones((2, 4, 4)))
+        h.set_param("blocks.b", np.ones((2, 4)))
+        for k, v in g.items():
+            h.set_result(k, v.astype(np.float32).astype(np.float64) * scale)
+        h.set_logging(True)
+        h.adamw_step(1, 10)
+        if hp:
+            assert h.launch_log()[:5] == ["sum_squares", "sum_squares", "fused 6 steps", "mul", "mul"]
+        outs.append({k: h.result("m:" + k, v.shape) for k, v in g.items()})
+    for k in g:
+        np.testing.assert_allclose(outs[0][k], outs[1][k], rtol=2e-5, atol=1e-9)  # min(1, x) = 1 - relu(1 - x) keeps x to 2^-24 absolute
+    assert (factor < 1.0) == (clip < norm)
