@@ -1841,6 +1841,242 @@ struct psk_host {
     }
 
     // ===========================================================================
+    // examples/coverage/llama.psk `loss` in reverse mode (`grad(λ θ. loss(θ, batch))(θ)`): the forward pass with
+    // every value the reverse pass reads kept (so no merged launch and no blockwise attention here), then the
+    // rules of presk-core/src/ad/rules.rs function by function, last let first: mul, div (∂b = -ct·y/b), sqrt,
+    // sigmoid (ct·y·(1 - y)), mean_vjp, sum_to for broadcast operands, the `ein` rule (the cotangent contracted with
+    // the other operand), softmax (y·(ct - Σ ct·y)), slice_vjp and the concatenation's two slices in `rope`,
+    // dot_vjp_l/r, embed_vjp, cross_entropy_vjp. Cotangents of a value with several readers are added in the
+    // reverse of the readers' order. The reference keeps no snapshot of this transformed program: the sites are
+    // written as names and the list of launches is this derivation; the values are held against an independent
+    // float64 reverse-mode statement of the model in the tests. Leaves in `results` under the parameters' paths
+    // (stacked leaves as [L, ...]).
+    // ===========================================================================
+    struct NormKept { Tensor x, rt, d; };
+    Tensor train_norm(const Tensor &gamma, const Tensor &x, NormKept &k)
+    {
+        const std::string f = "RMSNorm.apply.fwd";
+        Tensor x2 = binary(f + "/x2", PSK_MUL, x, x);
+        Tensor ms = reduce_axis(f + "/ms", PSK_REDUCE_MEAN, "model", x2);
+        Tensor eps = scalar(f + "/eps", 1e-5);
+        k.x = x;
+        k.rt = fused(f + "/rt", {Bn(PSK_ADD, 0, 1), U(PSK_SQRT, S(0))}, {&ms, &eps});
+        k.d = binary(f + "/d", PSK_DIV, x, k.rt);
+        return binary(f + "/y", PSK_MUL, k.d, gamma);
+    }
+    Tensor train_norm_bwd(const Tensor &gamma, const NormKept &k, const Tensor &ct, Tensor *c_gamma)
+    {
+        const std::string f = "RMSNorm.apply.bwd";
+        Tensor c_d = binary(f + "/c_d", PSK_MUL, ct, gamma);
+        Tensor t = binary(f + "/ct_d", PSK_MUL, ct, k.d);
+        *c_gamma = sum_to(f + "/c_gamma", t, gamma);
+        Tensor c_x1 = binary(f + "/c_x.div", PSK_DIV, c_d, k.rt);
+        Tensor t2 = fused(f + "/c_rt.full", {Bn(PSK_MUL, 0, 1), Bn(PSK_DIV, S(0), 2), U(PSK_NEG, S(1))}, {&c_d, &k.d, &k.rt});
+        Tensor c_rt = sum_to(f + "/c_rt", t2, k.rt);
+        Tensor two = scalar(f + "/two", 2.0);
+        Tensor c_ms = fused(f + "/c_ms", {Bn(PSK_MUL, 0, 1), Bn(PSK_DIV, 2, S(0))}, {&two, &k.rt, &c_rt});
+        Tensor c_xx = fused(f + "/mean_vjp", {U(PSK_DIV_N, 0, (int)k.x.axes.back().len)}, {&c_ms}, "mean_vjp", nullptr, &k.x.axes);
+        return fused(f + "/c_x", {Bn(PSK_MUL, 0, 1), Bn(PSK_ADD, 2, S(0)), Bn(PSK_ADD, S(1), S(0))}, {&c_xx, &k.x, &c_x1});
+    }
+
+    struct RopeKept { Tensor c, s; };
+    Tensor train_rope(const Tensor &phi, const Tensor &x, RopeKept &k)
+    {
+        const std::string f = "rope.fwd";
+        const int64_t hd = x.axes.back().len;
+        Tensor p = split(x, "hd", {{"pair", 2}, {"rot", hd / 2}});
+        Tensor x0 = slice(f + "/x0", "pair", 0, 1, p), x1 = slice(f + "/x1", "pair", 1, 2, p);
+        if (!k.c.st) { k.c = unary(f + "/cos", PSK_COS, phi); k.s = unary(f + "/sin", PSK_SIN, phi); }
+        Tensor a = fused(f + "/a", {Bn(PSK_MUL, 0, 1), Bn(PSK_MUL, 2, 3), Bn(PSK_SUB, S(0), S(1))}, {&x0, &k.c, &x1, &k.s});
+        Tensor b = fused(f + "/b", {Bn(PSK_MUL, 0, 1), Bn(PSK_MUL, 2, 3), Bn(PSK_ADD, S(0), S(1))}, {&x1, &k.c, &x0, &k.s});
+        Tensor m = merge(concat(f + "/cat", "pair", a, b), "pair", "rot");
+        m.axes.back().name = "hd";
+        return m;
+    }
+    // The rotation is linear in x: the cotangent goes back through the transposed rotation.
+    Tensor train_rope_bwd(const RopeKept &k, const Tensor &ct)
+    {
+        const std::string f = "rope.bwd";
+        const int64_t hd = ct.axes.back().len;
+        Tensor cp = split(ct, "hd", {{"pair", 2}, {"rot", hd / 2}});
+        Tensor c_a = slice(f + "/c_a", "pair", 0, 1, cp), c_b = slice(f + "/c_b", "pair", 1, 2, cp);
+        Tensor c_x0 = fused(f + "/c_x0", {Bn(PSK_MUL, 0, 1), Bn(PSK_MUL, 2, 3), Bn(PSK_ADD, S(0), S(1))}, {&c_b, &k.s, &c_a, &k.c});
+        Tensor c_x1 = fused(f + "/c_x1", {Bn(PSK_MUL, 0, 1), U(PSK_NEG, 2), Bn(PSK_MUL, S(1), 3), Bn(PSK_ADD, S(0), S(2))}, {&c_b, &k.c, &c_a, &k.s});
+        Tensor p1 = slice_vjp(f + "/slice_vjp.x1", "pair", 1, 2, cp, c_x1), p0 = slice_vjp(f + "/slice_vjp.x0", "pair", 0, 1, cp, c_x0);
+        Tensor m = merge(binary(f + "/c_p", PSK_ADD, p1, p0), "pair", "rot");
+        m.axes.back().name = "hd";
+        return m;
+    }
+
+    struct AttnKept { Tensor x, q, k, v, a, o; };
+    struct AttnGrad { Tensor x, wq, wk, wv, wo; };
+    Tensor train_attention(int64_t l, const Tensor &x, const Tensor &mask, const Tensor &phi, RopeKept &rk, AttnKept &kept)
+    {
+        const std::string f = "Attention.apply.fwd";
+        const int64_t D = C("D"), H = C("H"), G = C("G", H), HD = D / H, P = H / G;
+        Tensor wq = layer(param("blocks.attn.wq"), l), wk = layer(param("blocks.attn.wk"), l), wv = layer(param("blocks.attn.wv"), l), wo = layer(param("blocks.attn.wo"), l);
+        wq.axes = {{"model", D}, {"groups", G}, {"per", P}, {"hd", HD}};
+        wk.axes = {{"model", D}, {"groups", G}, {"hd", HD}};
+        wv.axes = {{"model", D}, {"kvout", G * HD}};
+        wo.axes = {{"groups", G}, {"per", P}, {"hd", HD}, {"model", D}};
+        kept.x = x;
+        kept.q = train_rope(phi, ein(f + "/q", {"batch", "groups", "per", "seq", "hd"}, {{"batch", "seq", "model"}, {"model", "groups", "per", "hd"}}, {&x, &wq}), rk);
+        kept.k = train_rope(phi, ein(f + "/k", {"batch", "groups", "seq", "hd"}, {{"batch", "seq", "model"}, {"model", "groups", "hd"}}, {&x, &wk}), rk);
+        Tensor vd = dot(f + "/v", x, wv);
+        vd.axes.back().name = "kvout";
+        kept.v = split(vd, "kvout", {{"groups", G}, {"hd", HD}});
+        Tensor se = ein(f + "/scores", {"batch", "groups", "per", "seq", "seq2"}, {{"batch", "groups", "per", "seq", "hd"}, {"batch", "groups", "seq2", "hd"}}, {&kept.q, &kept.k});
+        Tensor rt = unary(f + "/rt", PSK_SQRT, scalar(f + "/hd", (double)HD));
+        Tensor sc = binary(f + "/scaled", PSK_DIV, se, rt);
+        kept.a = softmax(f + "/softmax", "seq2", sc, &mask);
+        kept.o = ein(f + "/o", {"batch", "seq", "groups", "per", "hd"}, {{"batch", "groups", "per", "seq", "seq2"}, {"batch", "seq2", "groups", "hd"}}, {&kept.a, &kept.v});
+        return ein(f + "/out", {"batch", "seq", "model"}, {{"batch", "seq", "groups", "per", "hd"}, {"groups", "per", "hd", "model"}}, {&kept.o, &wo});
+    }
+    AttnGrad train_attention_bwd(int64_t l, const AttnKept &kept, const RopeKept &rk, const Tensor &ct)
+    {
+        const std::string f = "Attention.apply.bwd";
+        const int64_t D = C("D"), H = C("H"), G = C("G", H), HD = D / H, P = H / G;
+        Tensor wq = layer(param("blocks.attn.wq"), l), wk = layer(param("blocks.attn.wk"), l), wv = layer(param("blocks.attn.wv"), l), wo = layer(param("blocks.attn.wo"), l);
+        wq.axes = {{"model", D}, {"groups", G}, {"per", P}, {"hd", HD}};
+        wk.axes = {{"model", D}, {"groups", G}, {"hd", HD}};
+        wv.axes = {{"model", D}, {"kvout", G * HD}};
+        wo.axes = {{"groups", G}, {"per", P}, {"hd", HD}, {"model", D}};
+        AttnGrad g;
+        // the output projection, an `ein` of o and wo: each operand's cotangent is ct contracted with the other
+        Tensor c_o = ein(f + "/c_o", {"batch", "seq", "groups", "per", "hd"}, {{"batch", "seq", "model"}, {"groups", "per", "hd", "model"}}, {&ct, &wo});
+        g.wo = ein(f + "/c_wo", {"groups", "per", "hd", "model"}, {{"batch", "seq", "model"}, {"batch", "seq", "groups", "per", "hd"}}, {&ct, &kept.o});
+        Tensor c_a = ein(f + "/c_a", {"batch", "groups", "per", "seq", "seq2"}, {{"batch", "seq", "groups", "per", "hd"}, {"batch", "seq2", "groups", "hd"}}, {&c_o, &kept.v});
+        Tensor c_v = ein(f + "/c_v", {"batch", "seq2", "groups", "hd"}, {{"batch", "seq", "groups", "per", "hd"}, {"batch", "groups", "per", "seq", "seq2"}}, {&c_o, &kept.a});
+        // softmax: y · (ct - Σ_seq2 ct · y); refused positions have y = 0
+        Tensor t = binary(f + "/ct_y", PSK_MUL, c_a, kept.a);
+        Tensor sum = reduce_axis(f + "/sum", PSK_REDUCE_SUM, "seq2", t);
+        Tensor c_sc = fused(f + "/c_scaled", {Bn(PSK_SUB, 0, 1), Bn(PSK_MUL, 2, S(0))}, {&c_a, &sum, &kept.a});
+        Tensor rt = unary(f + "/rt", PSK_SQRT, scalar(f + "/hd", (double)HD));
+        Tensor c_se = binary(f + "/c_scores", PSK_DIV, c_sc, rt);
+        Tensor c_q = ein(f + "/c_q", {"batch", "groups", "per", "seq", "hd"}, {{"batch", "groups", "per", "seq", "seq2"}, {"batch", "groups", "seq2", "hd"}}, {&c_se, &kept.k});
+        Tensor c_k = ein(f + "/c_k", {"batch", "groups", "seq2", "hd"}, {{"batch", "groups", "per", "seq", "seq2"}, {"batch", "groups", "per", "seq", "hd"}}, {&c_se, &kept.q});
+        c_k.axes[2].name = "seq";
+        Tensor c_qe = train_rope_bwd(rk, c_q), c_ke = train_rope_bwd(rk, c_k);
+        // v = split(x · wv)
+        Tensor c_vd = merge(c_v, "groups", "hd");
+        c_vd.axes[1].name = "seq";
+        c_vd.axes.back().name = "kvout";
+        Tensor cx_v = ein(f + "/v.dot_vjp_l", {"batch", "seq", "model"}, {{"batch", "seq", "kvout"}, {"model", "kvout"}}, {&c_vd, &wv}, "dot_vjp_l");
+        g.wv = ein(f + "/v.dot_vjp_r", {"model", "kvout"}, {{"batch", "seq", "model"}, {"batch", "seq", "kvout"}}, {&kept.x, &c_vd}, "dot_vjp_r");
+        Tensor cx_k = ein(f + "/cx_k", {"batch", "seq", "model"}, {{"batch", "groups", "seq", "hd"}, {"model", "groups", "hd"}}, {&c_ke, &wk});
+        g.wk = ein(f + "/c_wk", {"model", "groups", "hd"}, {{"batch", "groups", "seq", "hd"}, {"batch", "seq", "model"}}, {&c_ke, &kept.x});
+        Tensor cx_q = ein(f + "/cx_q", {"batch", "seq", "model"}, {{"batch", "groups", "per", "seq", "hd"}, {"model", "groups", "per", "hd"}}, {&c_qe, &wq});
+        g.wq = ein(f + "/c_wq", {"model", "groups", "per", "hd"}, {{"batch", "groups", "per", "seq", "hd"}, {"batch", "seq", "model"}}, {&c_qe, &kept.x});
+        // x is read by q, k, v in that order: the last reader's share first
+        g.x = fused(f + "/c_x", {Bn(PSK_ADD, 0, 1), Bn(PSK_ADD, S(0), 2)}, {&cx_v, &cx_k, &cx_q});
+        return g;
+    }
+
+    struct FfKept { Tensor x, g, sig, sg, u, h; };
+    struct FfGrad { Tensor x, gate, up, down; };
+    Tensor train_swiglu(int64_t l, const Tensor &x, FfKept &k)
+    {
+        const std::string f = "SwiGLU.apply.fwd";
+        Tensor wg = layer(param("blocks.ff.gate.w"), l), wu = layer(param("blocks.ff.up.w"), l), wd = layer(param("blocks.ff.down.w"), l);
+        k.x = x;
+        k.g = dot(f + "/gate", x, wg);
+        k.sig = unary(f + "/sigmoid", PSK_SIGMOID, k.g);
+        k.sg = binary(f + "/silu", PSK_MUL, k.g, k.sig);
+        k.u = dot(f + "/up", x, wu);
+        k.h = binary(f + "/h", PSK_MUL, k.sg, k.u);
+        Tensor y = dot(f + "/down", k.h, wd);
+        y.axes.back().name = "model";
+        return y;
+    }
+    FfGrad train_swiglu_bwd(int64_t l, const FfKept &k, const Tensor &ct)
+    {
+        const std::string f = "SwiGLU.apply.bwd";
+        const int64_t D = C("D"), FF = C("FF");
+        Tensor wg = layer(param("blocks.ff.gate.w"), l), wu = layer(param("blocks.ff.up.w"), l), wd = layer(param("blocks.ff.down.w"), l);
+        wg.axes = {{"model", D}, {"ff", FF}};
+        wu.axes = {{"model", D}, {"ff", FF}};
+        wd.axes = {{"ff", FF}, {"model", D}};
+        const std::vector<std::string> xm = {"batch", "seq", "model"}, xf = {"batch", "seq", "ff"};
+        FfGrad g;
+        Tensor c_h = ein(f + "/down.dot_vjp_l", xf, {xm, {"ff", "model"}}, {&ct, &wd}, "dot_vjp_l");
+        g.down = ein(f + "/down.dot_vjp_r", {"ff", "model"}, {xf, xm}, {&k.h, &ct}, "dot_vjp_r");
+        Tensor c_sg = binary(f + "/c_silu", PSK_MUL, c_h, k.u);
+        Tensor c_u = binary(f + "/c_up", PSK_MUL, c_h, k.sg);
+        // silu(g) = g · σ(g): ct · σ + (ct · g) · σ · (1 - σ)
+        Tensor one = scalar(f + "/one", 1.0);
+        Tensor c_g = fused(f + "/c_gate", {Bn(PSK_MUL, 0, 1), Bn(PSK_MUL, 0, 2), Bn(PSK_SUB, 3, 1), Bn(PSK_MUL, 1, S(2)), Bn(PSK_MUL, S(1), S(3)), Bn(PSK_ADD, S(0), S(4))}, {&c_sg, &k.sig, &k.g, &one});
+        Tensor cx_u = ein(f + "/up.dot_vjp_l", xm, {xf, {"model", "ff"}}, {&c_u, &wu}, "dot_vjp_l");
+        g.up = ein(f + "/up.dot_vjp_r", {"model", "ff"}, {xm, xf}, {&k.x, &c_u}, "dot_vjp_r");
+        Tensor cx_g = ein(f + "/gate.dot_vjp_l", xm, {xf, {"model", "ff"}}, {&c_g, &wg}, "dot_vjp_l");
+        g.gate = ein(f + "/gate.dot_vjp_r", {"model", "ff"}, {xm, xf}, {&k.x, &c_g}, "dot_vjp_r");
+        g.x = binary(f + "/c_x", PSK_ADD, cx_u, cx_g);
+        return g;
+    }
+
+    Tensor llama_loss_grad(const Tensor &ids, const Tensor &y)
+    {
+        const std::string f = "loss_grad";
+        const int64_t T = ids.axes[1].len, L = C("L");
+        Tensor mask = causal_mask("Llama.apply/%2", "seq", T);
+        Tensor tok = param("tok");
+        Tensor x = embed("Llama.apply/%4", tok, ids);
+        x.axes.back().name = "model";
+        Tensor phi = llama_angles(T);
+        struct BlockKept { Tensor x, x1; NormKept n1, n2; AttnKept at; FfKept ff; };
+        std::vector<BlockKept> kept(L);
+        RopeKept rk;
+        for (int64_t l = 0; l < L; ++l) {
+            BlockKept &b = kept[l];
+            b.x = x;
+            Tensor h1 = train_norm(layer(param("blocks.n1.γ"), l), x, b.n1);
+            b.x1 = binary("Block.apply.fwd/x1", PSK_ADD, x, train_attention(l, h1, mask, phi, rk, b.at));
+            Tensor h2 = train_norm(layer(param("blocks.n2.γ"), l), b.x1, b.n2);
+            x = binary("Block.apply.fwd/x2", PSK_ADD, b.x1, train_swiglu(l, h2, b.ff));
+        }
+        NormKept nf;
+        Tensor hn = train_norm(param("norm.γ"), x, nf);
+        Tensor head = param("head");
+        head.axes = {{"model", C("D")}, {"vocab", C("V")}};
+        Tensor logits = dot("Llama.apply/%11", hn, head);
+        logits.axes.back().name = "vocab";
+        Tensor ce = cross_entropy("loss/%5", logits, y);
+        // the reverse pass
+        Tensor ct1 = scalar(f + "/ct", 1.0);
+        Tensor c_ce = fused(f + "/mean_vjp", {U(PSK_DIV_N, 0, (int)ce.numel())}, {&ct1}, "mean_vjp", nullptr, &ce.axes);
+        Tensor c_logits = cross_entropy_vjp(f + "/cross_entropy_vjp", logits, y, c_ce);
+        const std::vector<std::string> xm = {"batch", "seq", "model"}, xv = {"batch", "seq", "vocab"};
+        Tensor c_hn = ein(f + "/head.dot_vjp_l", xm, {xv, {"model", "vocab"}}, {&c_logits, &head}, "dot_vjp_l");
+        std::map<std::string, Tensor> out;
+        out["head"] = ein(f + "/head.dot_vjp_r", {"model", "vocab"}, {xm, xv}, {&hn, &c_logits}, "dot_vjp_r");
+        Tensor ct = train_norm_bwd(param("norm.γ"), nf, c_hn, &out["norm.γ"]);
+        static const char *stacked[] = {"blocks.n1.γ", "blocks.n2.γ", "blocks.attn.wq", "blocks.attn.wk", "blocks.attn.wv", "blocks.attn.wo", "blocks.ff.gate.w", "blocks.ff.up.w", "blocks.ff.down.w"};
+        for (auto path : stacked) out[path] = zeros(f + "/" + path, param(path).axes);
+        auto place = [&](const char *path, int64_t l, const Tensor &leaf) {
+            Tensor &dst = out[path];
+            const int64_t chunk = dst.numel() / dst.axes[0].len;
+            if (leaf.numel() != chunk) raise(PSK_E10001, std::string("loss_grad: the leaf of `") + path + "` has " + std::to_string(leaf.numel()) + " elements");
+            copy_part("scatter_params", leaf.dtype, leaf.axes, leaf, leaf.strides(), 0, dst, contiguous(leaf.axes), l * chunk, true);
+        };
+        for (int64_t l = L - 1; l >= 0; --l) {
+            BlockKept &b = kept[l];
+            // x2 = x1 + ff(n2(x1)); x1 = x + attn(n1(x))
+            FfGrad fg = train_swiglu_bwd(l, b.ff, ct);
+            Tensor c_n2;
+            Tensor c_x1 = binary("Block.apply.bwd/c_x1", PSK_ADD, ct, train_norm_bwd(layer(param("blocks.n2.γ"), l), b.n2, fg.x, &c_n2));
+            AttnGrad ag = train_attention_bwd(l, b.at, rk, c_x1);
+            Tensor c_n1;
+            ct = binary("Block.apply.bwd/c_x", PSK_ADD, c_x1, train_norm_bwd(layer(param("blocks.n1.γ"), l), b.n1, ag.x, &c_n1));
+            place("blocks.ff.gate.w", l, fg.gate); place("blocks.ff.up.w", l, fg.up); place("blocks.ff.down.w", l, fg.down);
+            place("blocks.n2.γ", l, c_n2); place("blocks.n1.γ", l, c_n1);
+            place("blocks.attn.wq", l, ag.wq); place("blocks.attn.wk", l, ag.wk); place("blocks.attn.wv", l, ag.wv); place("blocks.attn.wo", l, ag.wo);
+            b = BlockKept(); // this block's kept values are no longer read
+        }
+        out["tok"] = embed_vjp(f + "/embed_vjp", tok, ids, ct);
+        results = out;
+        return results["tok"];
+    }
+
+    // ===========================================================================
     // The optimizer of a training run: `adamw.init`, `adamw.lr`, `adamw.step` as presk-core/src/lower/optim.rs:118-330
     // builds them (AdamW with decoupled decay; schedules constant, linear(warmup), cosine(warmup) written with relu
     // so that they are ordinary primitives). Lets of a parameter tree's type run leaf by leaf; the groups are those
@@ -2141,6 +2377,7 @@ struct psk_host {
         if (model == "llama") {
             if (entry == "apply") { need(1); return llama_apply(in[0]); }
             if (entry == "loss") { need(2); return llama_loss(in[0], in[1]); }
+            if (entry == "loss_grad") { need(2); return llama_loss_grad(in[0], in[1]); }
             if (entry == "attention" || entry == "attention3") {
                 // one attention function on given activations [batch, seq, model], with the causal mask and the
                 // angles of its sequence length: examples/spec/rope/rope.psk `attention2` is this with G = H

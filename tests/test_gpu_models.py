@@ -416,3 +416,50 @@ def test_training_steps_bit_exact(cuda, oracle, dtype):
         for got, want in zip(*runs):
             assert_same_bits(got, want)
             assert np.isfinite(want).all()
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_llama_gradient_bit_exact(cuda, oracle, dtype):
+    """examples/coverage/llama.psk `loss_grad` (grouped-query attention, three blocks): every leaf of the gradient,
+    the oracle's bits under the sequential order; then two training steps with AdamW, parameters still bit-equal."""
+    c = dict(V=50, D=32, H=4, G=2, FF=48, L=3)
+    p = models.llama_params(c, seed=4, std=0.2)
+    rng = np.random.default_rng(6)
+    ids = rng.integers(0, c["V"] // 2, size=(2, 12), dtype=np.int64)
+    y = rng.integers(0, c["V"], size=(2, 12), dtype=np.int64)
+    runs = []
+    for ex in (cuda, oracle.vtable()):
+        h = models.give(Host(ex, dtype).prepare("llama", **c), p).adamw(lr=1e-2, weight_decay=0.1, grad_clip=1.0)
+        h.call("loss_grad", [ids, y], p["tok"].shape)
+        leaves = [h.result(k, np.shape(v)) for k, v in p.items()]
+        for t in (1, 2):
+            h.adamw_step(t, 2)
+            h.call("loss_grad", [ids, y], p["tok"].shape)
+        leaves += [h.result(k, np.shape(v)) for k, v in p.items()]
+        runs.append(leaves)
+    for got, want in zip(*runs):
+        assert_same_bits(got, want)
+        assert np.isfinite(want).all() and np.abs(want).max() > 0
+
+
+def test_llama_gradient_device_order_within_tolerance(cuda, oracle):
+    """The same program under the device order at a size whose contractions reach the tensor cores (bf16 storage):
+    every leaf within a bf16 tolerance of the oracle's f32 sequential gradient, relative to the leaf's largest entry."""
+    c = dict(V=512, D=256, H=4, G=2, FF=512, L=2)
+    p = models.llama_params(c, seed=5, std=0.05)
+    rng = np.random.default_rng(9)
+    ids = rng.integers(0, c["V"], size=(2, 128), dtype=np.int64)
+    y = rng.integers(0, c["V"], size=(2, 128), dtype=np.int64)
+    want_h = models.give(Host(oracle.vtable(), "f32").prepare("llama", **c), p)
+    want_h.call("loss_grad", [ids, y], p["tok"].shape)
+    rz = {"default": "bf16", "order": {"kind": "device"}, "params": {k: "bf16" for k in p}, "storage": {"Llama.apply/%11": "f32", "loss/%5": "f32"}}
+    h = models.give(Host(cuda, rz).prepare("llama", **c), p)
+    cuda.set_profiling(True)
+    h.call("loss_grad", [ids, y], p["tok"].shape)
+    prof = cuda.profile()
+    cuda.set_profiling(False)
+    assert sum(1 for rec in prof if rec[0] == "k_gemm_tc") >= 10 * c["L"], "the reverse pass's contractions did not reach the tensor-core kernel"
+    for k, v in p.items():
+        want, got = want_h.result(k, np.shape(v)), h.result(k, np.shape(v))
+        assert np.isfinite(got).all(), k
+        assert np.abs(got - want).max() <= 0.06 * np.abs(want).max(), (k, np.abs(got - want).max(), np.abs(want).max())
