@@ -190,6 +190,40 @@ def microbench(args):
         ex.sync()
         return e0.elapsed_time(e1) / reps
 
+    if args.micro == "train":
+        # one training step (loss_grad + adamw.step) of a Llama-shaped model under the device order, bf16 storage:
+        # --shape V,D,H,FF,L,B,T. Not the benchmark's metric: the reverse pass is not tuned.
+        from presk_b200 import Host
+        V, D, H, FF, L, B, T = dims[:7]
+        consts = dict(V=V, D=D, H=H, G=H, FF=FF, L=L)
+        shapes = param_shapes(consts)
+        rz = realization(shapes, False, "unfused", "reference")
+        host = Host(ex, rz).prepare("llama", **consts).adamw(lr=1e-4, weight_decay=0.1, grad_clip=1.0)
+        for i, (path, (shape, std)) in enumerate(shapes.items()):
+            if std < 0:
+                host.set_param(path, np.ones(shape, np.float32))
+            else:
+                host.init_param(path, 1000 + i, std, shape)
+        ids = rng.integers(0, V, size=(B, T), dtype=np.int64)
+        y = rng.integers(0, V, size=(B, T), dtype=np.int64)
+        step = [0]
+
+        def one():
+            step[0] += 1
+            host.call("loss_grad", [ids, y], shapes["tok"][0])
+            host.adamw_step(step[0], 1000)
+
+        for _ in range(2):
+            one()
+        ex.sync()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            one()
+        ex.sync()
+        ms = (time.perf_counter() - t0) * 1e3 / args.steps
+        flops = 3.0 * flops_per_token(consts, T) * B * T
+        print(json.dumps({"micro": "train", "shape": dims, "ms_per_step": ms, "tokens/s": B * T / ms * 1e3, "model TFLOP/s (3x forward)": flops / ms / 1e9, "loss": float(host.call("loss", [ids, y], ()))}))
+        return
     if args.micro == "gemm":
         m, n, k = dims[:3]
         batch = dims[3] if len(dims) > 3 else 1
@@ -302,7 +336,7 @@ def microbench(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--micro", default=None, choices=["gemm", "softmax", "ew", "attn", "norm", "e8m15", "f32c"])
+    ap.add_argument("--micro", default=None, choices=["gemm", "softmax", "ew", "attn", "norm", "e8m15", "f32c", "train"])
     ap.add_argument("--shape", default="8192,8192,8192")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
