@@ -198,6 +198,7 @@ def microbench(args):
         consts = dict(V=V, D=D, H=H, G=H, FF=FF, L=L)
         shapes = param_shapes(consts)
         rz = realization(shapes, False, "unfused", "reference")
+        rz["functions"] = {"adamw.step": "f32", "adamw.lr": "f32"}  # moments and the schedule in f32; parameters stay bf16
         host = Host(ex, rz).prepare("llama", **consts).adamw(lr=1e-4, weight_decay=0.1, grad_clip=1.0)
         for i, (path, (shape, std)) in enumerate(shapes.items()):
             if std < 0:

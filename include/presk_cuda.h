@@ -292,7 +292,9 @@ void *psk_exec_stream(psk_exec *e);
 typedef struct {
     int32_t in_dtype;  /* PSK_BF16 or PSK_F16, both operands */
     int32_t out_dtype; /* PSK_F32, PSK_BF16, PSK_F16 or PSK_E8M15 */
-    int32_t b_n_major; /* 0: B[batch][n][k], k contiguous; 1: B[batch][k][n], n contiguous */
+    int32_t b_n_major; /* bit 0: 0 B[batch][n][k], k contiguous; 1 B[batch][k][n], n contiguous.
+                          bit 1: 0 A[batch][m][k], k contiguous (a_row: a row's stride); 1 A[batch][k][m], m contiguous
+                          (a_row: the stride between two k) */
     int32_t guarded;
     int64_t m, n, k;
     int64_t batch, batch_lo;                 /* batch index = hi * batch_lo + lo */

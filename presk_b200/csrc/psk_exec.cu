@@ -342,9 +342,13 @@ int launch_tc(psk_exec *e, const psk_gemm &g, const void *a, const void *b, void
     const int mt_rows = (m256_on && bn == 256 && g.m >= 512) ? 2 : 1;
     CUtensorMap ma, mb;
     const uint64_t kphys = split_k ? (uint64_t)(planes * split_k) : (uint64_t)g.k; // what the operands hold along the summed axis
-    if (!make_map(e, &ma, a, f16, kphys, (uint64_t)g.m, (uint64_t)g.batch_lo, (uint64_t)batch_hi, (uint64_t)g.a_row, (uint64_t)g.a_lo, (uint64_t)g.a_hi, tc::BK, (uint32_t)(tc::BM * mt_rows)))
-        return fail(e, PSK_E7001, "tensor-core contraction: operand 0's strides do not make a tensor map");
-    bool okb = g.b_n_major
+    const bool a_m_major = (g.b_n_major & 2) != 0, b_n_major = (g.b_n_major & 1) != 0;
+    if (a_m_major && split_k) return fail(e, PSK_E7001, "tensor-core contraction: planes of a transposed operand");
+    const bool oka = a_m_major
+        ? make_map(e, &ma, a, f16, (uint64_t)g.m, kphys, (uint64_t)g.batch_lo, (uint64_t)batch_hi, (uint64_t)g.a_row, (uint64_t)g.a_lo, (uint64_t)g.a_hi, 64, tc::BK)
+        : make_map(e, &ma, a, f16, kphys, (uint64_t)g.m, (uint64_t)g.batch_lo, (uint64_t)batch_hi, (uint64_t)g.a_row, (uint64_t)g.a_lo, (uint64_t)g.a_hi, tc::BK, (uint32_t)(tc::BM * mt_rows));
+    if (!oka) return fail(e, PSK_E7001, "tensor-core contraction: operand 0's strides do not make a tensor map");
+    bool okb = b_n_major
         ? make_map(e, &mb, b, f16, (uint64_t)g.n, kphys, (uint64_t)g.batch_lo, (uint64_t)batch_hi, (uint64_t)g.b_row, (uint64_t)g.b_lo, (uint64_t)g.b_hi, 64, tc::BK)
         : make_map(e, &mb, b, f16, kphys, (uint64_t)g.n, (uint64_t)g.batch_lo, (uint64_t)batch_hi, (uint64_t)g.b_row, (uint64_t)g.b_lo, (uint64_t)g.b_hi, tc::BK, (uint32_t)bn);
     if (!okb) return fail(e, PSK_E7001, "tensor-core contraction: operand 1's strides do not make a tensor map");
@@ -352,7 +356,7 @@ int launch_tc(psk_exec *e, const psk_gemm &g, const void *a, const void *b, void
     P.m = g.m; P.n = g.n; P.k = g.k; P.batch = g.batch; P.batch_lo = g.batch_lo;
     P.tiles_m = (g.m + tc::BM * mt_rows - 1) / (tc::BM * mt_rows);
     P.tiles_n = (g.n + bn - 1) / bn;
-    P.split_k = split_k; P.planes = planes; P.pad_ = 0;
+    P.split_k = split_k; P.planes = planes; P.a_m_major = a_m_major ? 1 : 0;
     P.addend = addend;
     {
         // a panel's columns of B (bn·k elements each) should stay in the L2 while A streams past them: a
@@ -366,7 +370,7 @@ int launch_tc(psk_exec *e, const psk_gemm &g, const void *a, const void *b, void
     P.c_row_lo_count = g.c_row_lo_count; P.c_row_lo = g.c_row_lo; P.c_row_hi = g.c_row_hi;
     P.c_col_lo_count = g.c_col_lo_count; P.c_col_hi = g.c_col_hi;
     P.c_lo = g.c_lo; P.c_hi = g.c_hi;
-    P.c = c; P.out_dtype = g.out_dtype; P.in_f16 = f16; P.b_n_major = g.b_n_major; P.guarded = g.guarded;
+    P.c = c; P.out_dtype = g.out_dtype; P.in_f16 = f16; P.b_n_major = b_n_major ? 1 : 0; P.guarded = g.guarded;
     const int64_t va = g.out_dtype == PSK_F32 ? 4 : 8; // elements in 16 bytes
     P.vec_ok = aligned16(c) && g.c_row_lo % va == 0 && g.c_row_hi % va == 0 && g.c_col_hi % va == 0 && g.c_lo % va == 0 && g.c_hi % va == 0 && g.c_col_lo_count % (g.out_dtype == PSK_F32 ? 32 : 64) == 0 && g.n % va == 0 && g.out_dtype != PSK_E8M15;
     P.scale = g.scale; P.scale_on = g.scale_on;
@@ -931,17 +935,19 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
         }
         bool tc_ok = mapped && device_order && e->encode && A.dtype == B.dtype && (A.dtype == PSK_BF16 || A.dtype == PSK_F16)
             && (L.kdtype == A.dtype || L.kdtype == PSK_F32 || (L.kdtype == PSK_E8M15))
-            && g.a_k == 1 && (g.b_k == 1 || g.b_n == 1) && aligned16(A.p) && aligned16(B.p) && g.c_col_lo == 1 && g.m >= 1 && g.n >= 8 && g.k >= 8;
+            && (g.a_k == 1 || (g.a_row == 1 && g.m >= 8)) && (g.b_k == 1 || g.b_n == 1) && aligned16(A.p) && aligned16(B.p) && g.c_col_lo == 1 && g.m >= 1 && g.n >= 8 && g.k >= 8;
         if (tc_ok) {
             psk_gemm pg;
             memset(&pg, 0, sizeof pg);
-            pg.in_dtype = A.dtype; pg.out_dtype = L.out.dtype; pg.b_n_major = g.b_k == 1 ? 0 : 1; pg.guarded = L.guarded;
+            // a first operand whose rows are contiguous along m (x read as xᵀ in dot_vjp_r): the kernel's M-major form
+            const bool a_m_major = g.a_k != 1;
+            pg.in_dtype = A.dtype; pg.out_dtype = L.out.dtype; pg.b_n_major = (g.b_k == 1 ? 0 : 1) | (a_m_major ? 2 : 0); pg.guarded = L.guarded;
             pg.m = g.m; pg.n = g.n; pg.k = g.k; pg.batch = g.batch; pg.batch_lo = g.batch_lo;
-            pg.a_row = g.a_row; pg.a_lo = g.a_lo; pg.a_hi = g.a_hi;
-            pg.b_row = pg.b_n_major ? g.b_k : g.b_n; pg.b_lo = g.b_lo; pg.b_hi = g.b_hi;
+            pg.a_row = a_m_major ? g.a_k : g.a_row; pg.a_lo = g.a_lo; pg.a_hi = g.a_hi;
+            pg.b_row = (pg.b_n_major & 1) ? g.b_k : g.b_n; pg.b_lo = g.b_lo; pg.b_hi = g.b_hi;
             pg.c_row_lo_count = g.c_row_lo_count; pg.c_row_lo = g.c_row_lo; pg.c_row_hi = g.c_row_hi;
             pg.c_col_lo_count = g.c_col_lo_count; pg.c_col_hi = g.c_col_hi; pg.c_lo = g.c_lo; pg.c_hi = g.c_hi;
-            if (g.m == 1) pg.a_row = g.k; // a single row: any stride of 16 bytes will do
+            if (g.m == 1 && !a_m_major) pg.a_row = g.k; // a single row: any stride of 16 bytes will do
             if (g.n == 1) pg.b_row = g.k;
             std::string keep = e->error;
             rc = launch_tc(e, pg, A.p, B.p, const_cast<void *>(L.out.p), L.ovf);

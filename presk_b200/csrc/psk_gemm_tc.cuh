@@ -53,7 +53,7 @@ struct Params {
     // kernel's k runs over planes²·split_k: part t reads A's plane t / planes and B's plane t % planes, so all
     // the exact partial products add up in one accumulator. split_k = 0: the operands are what they are.
     int64_t split_k;
-    int32_t planes, pad_;
+    int32_t planes, a_m_major; // a_m_major: A[batch][k][m], m contiguous (a transposed operand: dot_vjp_r's first)
     // PSK_OP_CONTRACT_ADD: bf16 values laid out exactly as C, added to the result after it has been rounded to
     // bf16 as its own site would store it; the sum is rounded to bf16 again. Staged bf16 epilogue only.
     const void *addend;
@@ -141,12 +141,13 @@ PSK_DEV uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes
 
 // The instruction descriptor of kind::f16: f32 accumulator, both operands
 // bf16 or both binary16, A K-major, B K-major or N-major, M = 128, N = bn.
-PSK_DEV uint32_t instr_desc(int in_f16, int b_n_major, int bn)
+PSK_DEV uint32_t instr_desc(int in_f16, int b_n_major, int bn, int a_m_major = 0)
 {
     uint32_t d = 0;
     d |= 1u << 4;                        // accumulator f32
     d |= (in_f16 ? 0u : 1u) << 7;        // A: 0 binary16, 1 bf16
     d |= (in_f16 ? 0u : 1u) << 10;       // B
+    d |= (a_m_major ? 1u : 0u) << 15;    // A major: 0 K, 1 MN
     d |= (b_n_major ? 1u : 0u) << 16;    // B major: 0 K, 1 MN
     d |= (uint32_t)(bn >> 3) << 17;
     d |= (uint32_t)(BM >> 4) << 24;
@@ -299,7 +300,14 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
                         ka = (q / P.planes) * (int)P.split_k + r;
                         kbb = (q % P.planes) * (int)P.split_k + r;
                     }
-                    tma_load_4d(smem_u32(smem_a + stage * S::A_BYTES), &map_a, fb, ka, m0, blo, bhi);
+                    if (!P.a_m_major) {
+                        tma_load_4d(smem_u32(smem_a + stage * S::A_BYTES), &map_a, fb, ka, m0, blo, bhi);
+                    } else {
+                        // 64 rows of the summed axis by 64 contiguous m a box, as B's N-major form below
+#pragma unroll
+                        for (int c = 0; c < BM * MT / 64; ++c)
+                            tma_load_4d(smem_u32(smem_a + stage * S::A_BYTES + c * 8192), &map_a, fb, m0 + c * 64, ka, blo, bhi);
+                    }
                     if (!P.b_n_major) {
                         tma_load_4d(smem_u32(smem_b + stage * S::B_BYTES), &map_b, fb, kbb, n0, blo, bhi);
                     } else {
@@ -313,7 +321,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            const uint32_t idesc = instr_desc(P.in_f16, P.b_n_major, BN);
+            const uint32_t idesc = instr_desc(P.in_f16, P.b_n_major, BN, P.a_m_major);
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
             for (int64_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
@@ -339,7 +347,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
                         }
 #pragma unroll
                         for (int k = 0; k < BK / UMMA_K; ++k) {
-                            const uint64_t ad = smem_desc(a_addr + h * (BM * BK * 2) + k * 32, 16, 1024);
+                            const uint64_t ad = P.a_m_major ? smem_desc(a_addr + h * (BM * BK * 2) + k * 2048, 8192, 1024) : smem_desc(a_addr + h * (BM * BK * 2) + k * 32, 16, 1024);
                             const uint64_t bd = P.b_n_major ? smem_desc(b_addr + k * 2048, 8192, 1024) : smem_desc(b_addr + k * 32, 16, 1024);
                             umma(tacc + h * BN, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
                         }

@@ -1944,9 +1944,9 @@ struct psk_host {
         AttnGrad g;
         // the output projection, an `ein` of o and wo: each operand's cotangent is ct contracted with the other
         Tensor c_o = ein(f + "/c_o", {"batch", "seq", "groups", "per", "hd"}, {{"batch", "seq", "model"}, {"groups", "per", "hd", "model"}}, {&ct, &wo});
-        g.wo = ein(f + "/c_wo", {"groups", "per", "hd", "model"}, {{"batch", "seq", "model"}, {"batch", "seq", "groups", "per", "hd"}}, {&ct, &kept.o});
+        g.wo = ein(f + "/c_wo", {"groups", "per", "hd", "model"}, {{"batch", "seq", "groups", "per", "hd"}, {"batch", "seq", "model"}}, {&kept.o, &ct});
         Tensor c_a = ein(f + "/c_a", {"batch", "groups", "per", "seq", "seq2"}, {{"batch", "seq", "groups", "per", "hd"}, {"batch", "seq2", "groups", "hd"}}, {&c_o, &kept.v});
-        Tensor c_v = ein(f + "/c_v", {"batch", "seq2", "groups", "hd"}, {{"batch", "seq", "groups", "per", "hd"}, {"batch", "groups", "per", "seq", "seq2"}}, {&c_o, &kept.a});
+        Tensor c_v = ein(f + "/c_v", {"batch", "seq2", "groups", "hd"}, {{"batch", "groups", "per", "seq", "seq2"}, {"batch", "seq", "groups", "per", "hd"}}, {&kept.a, &c_o});
         // softmax: y · (ct - Σ_seq2 ct · y); refused positions have y = 0
         Tensor t = binary(f + "/ct_y", PSK_MUL, c_a, kept.a);
         Tensor sum = reduce_axis(f + "/sum", PSK_REDUCE_SUM, "seq2", t);
@@ -1956,17 +1956,38 @@ struct psk_host {
         Tensor c_q = ein(f + "/c_q", {"batch", "groups", "per", "seq", "hd"}, {{"batch", "groups", "per", "seq", "seq2"}, {"batch", "groups", "seq2", "hd"}}, {&c_se, &kept.k});
         Tensor c_k = ein(f + "/c_k", {"batch", "groups", "seq2", "hd"}, {{"batch", "groups", "per", "seq", "seq2"}, {"batch", "groups", "per", "seq", "hd"}}, {&c_se, &kept.q});
         c_k.axes[2].name = "seq";
-        Tensor c_qe = train_rope_bwd(rk, c_q), c_ke = train_rope_bwd(rk, c_k);
+        // The projections' cotangents with the positions before the heads again ([batch, seq, out]: a copy, no value
+        // changes), so that both of a projection's gradients are plain matrix products over rows of (batch, seq).
+        auto rows_of = [&](const std::string &site, const Tensor &t, const std::string &out_name) {
+            const int r = (int)t.axes.size(); // [batch, heads.., seq, hd]
+            Axes oa;
+            std::vector<int64_t> st;
+            auto ts = t.strides();
+            oa.push_back(t.axes[0]); st.push_back(ts[0]);
+            oa.push_back(t.axes[r - 2]); st.push_back(ts[r - 2]);
+            for (int i = 1; i < r - 2; ++i) { oa.push_back(t.axes[i]); st.push_back(ts[i]); }
+            oa.push_back(t.axes[r - 1]); st.push_back(ts[r - 1]);
+            Tensor out = fresh(oa, site_dtype(site));
+            copy_part("seq_before_heads", out.dtype, oa, t, st, 0, out, contiguous(oa), 0, true);
+            int64_t width = 1;
+            for (int i = 2; i < r; ++i) width *= oa[i].len;
+            out.axes = {oa[0], oa[1], {out_name, width}};
+            return out;
+        };
+        Tensor c_qh = rows_of(f + "/c_q.rows", train_rope_bwd(rk, c_q), "qout"), c_kh = rows_of(f + "/c_k.rows", train_rope_bwd(rk, c_k), "kvout");
+        Tensor wq2 = wq, wk2 = wk;
+        wq2.axes = {{"model", D}, {"qout", D}};
+        wk2.axes = {{"model", D}, {"kvout", G * HD}};
         // v = split(x · wv)
         Tensor c_vd = merge(c_v, "groups", "hd");
         c_vd.axes[1].name = "seq";
         c_vd.axes.back().name = "kvout";
         Tensor cx_v = ein(f + "/v.dot_vjp_l", {"batch", "seq", "model"}, {{"batch", "seq", "kvout"}, {"model", "kvout"}}, {&c_vd, &wv}, "dot_vjp_l");
         g.wv = ein(f + "/v.dot_vjp_r", {"model", "kvout"}, {{"batch", "seq", "model"}, {"batch", "seq", "kvout"}}, {&kept.x, &c_vd}, "dot_vjp_r");
-        Tensor cx_k = ein(f + "/cx_k", {"batch", "seq", "model"}, {{"batch", "groups", "seq", "hd"}, {"model", "groups", "hd"}}, {&c_ke, &wk});
-        g.wk = ein(f + "/c_wk", {"model", "groups", "hd"}, {{"batch", "groups", "seq", "hd"}, {"batch", "seq", "model"}}, {&c_ke, &kept.x});
-        Tensor cx_q = ein(f + "/cx_q", {"batch", "seq", "model"}, {{"batch", "groups", "per", "seq", "hd"}, {"model", "groups", "per", "hd"}}, {&c_qe, &wq});
-        g.wq = ein(f + "/c_wq", {"model", "groups", "per", "hd"}, {{"batch", "groups", "per", "seq", "hd"}, {"batch", "seq", "model"}}, {&c_qe, &kept.x});
+        Tensor cx_k = ein(f + "/cx_k", {"batch", "seq", "model"}, {{"batch", "seq", "kvout"}, {"model", "kvout"}}, {&c_kh, &wk2});
+        g.wk = ein(f + "/c_wk", {"model", "kvout"}, {{"batch", "seq", "model"}, {"batch", "seq", "kvout"}}, {&kept.x, &c_kh});
+        Tensor cx_q = ein(f + "/cx_q", {"batch", "seq", "model"}, {{"batch", "seq", "qout"}, {"model", "qout"}}, {&c_qh, &wq2});
+        g.wq = ein(f + "/c_wq", {"model", "qout"}, {{"batch", "seq", "model"}, {"batch", "seq", "qout"}}, {&kept.x, &c_qh});
         // x is read by q, k, v in that order: the last reader's share first
         g.x = fused(f + "/c_x", {Bn(PSK_ADD, 0, 1), Bn(PSK_ADD, S(0), 2)}, {&cx_v, &cx_k, &cx_q});
         return g;

@@ -106,6 +106,7 @@ extern "C" int psk_gemm_noalloc(const psk_gemm *g, const void *a, const void *b,
         S.done = true;
     }
 
+    if (g->b_n_major & ~1) return say(err, err_cap, PSK_E7001, "psk_gemm_noalloc: the first operand is read k-contiguous here");
     const bool f16 = g->in_dtype == PSK_F16;
     const int bn = g->n >= 256 || g->n % 128 != 0 ? 256 : 128;
     const int64_t batch_hi = g->batch / g->batch_lo;

@@ -330,3 +330,66 @@ def test_e4m3_weights_on_tensor_cores(cuda, oracle, m, n, k):
     assert np.array_equal(np.frombuffer(cuda.download(pc, m * n * 2), np.uint8), want_b)
     for p in (pa, pw, pc):
         cuda.free(p)
+
+
+@pytest.mark.parametrize("b_n_major", [0, 1])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (256, 512, 256), (640, 520, 1024), (136, 264, 72), (4096, 1024, 2048)])
+def test_gemm_first_operand_m_major(cuda, oracle, m, n, k, b_n_major):
+    """The first operand stored [k][m], m contiguous (x read as its transpose: a weight's gradient xᵀ·ct), through
+    both tile forms (640 and 4096 rows take the 256-row one), ragged edges included."""
+    rng = np.random.default_rng(m + n)
+    a = rng.standard_normal((k, m)).astype(np.float32)
+    b = rng.standard_normal((k, n) if b_n_major else (n, k)).astype(np.float32)
+    ab, bb = to_bits(oracle, a, abi.BF16), to_bits(oracle, b, abi.BF16)
+    av = oracle.widen(ab, abi.BF16, a.size).reshape(a.shape).astype(np.float64)
+    bv = oracle.widen(bb, abi.BF16, b.size).reshape(b.shape).astype(np.float64)
+    want = av.T @ (bv if b_n_major else bv.T)
+    pa, pb, pc = cuda.upload(ab), cuda.upload(bb), cuda.alloc(m * n * 4)
+    g = abi.Gemm()
+    g.in_dtype, g.out_dtype, g.b_n_major, g.guarded = abi.BF16, abi.F32, b_n_major | 2, 1
+    g.m, g.n, g.k, g.batch, g.batch_lo = m, n, k, 1, 1
+    g.a_row, g.a_lo, g.a_hi = m, m * k, m * k
+    g.b_row, g.b_lo, g.b_hi = (n if b_n_major else k), n * k, n * k
+    g.c_row_lo_count, g.c_row_lo, g.c_row_hi = m, n, 0
+    g.c_col_lo_count, g.c_col_hi = n, 0
+    g.c_lo, g.c_hi = m * n, m * n
+    cuda.gemm(g, pa, pb, pc)
+    cuda.sync()
+    got = np.frombuffer(cuda.download(pc, m * n * 4), np.float32).reshape(m, n)
+    for p in (pa, pb, pc):
+        cuda.free(p)
+    assert np.abs(got - want).max() <= 4e-6 * k + 1e-5
+
+
+def test_weight_gradient_contraction_reaches_the_tensor_cores(cuda, oracle):
+    """dot_vjp_r as a launch: out[model, ff] = Σ over (batch, seq) of x[batch, seq, model] · ct[batch, seq, ff] under the
+    device order: the transposed first operand goes to the tensor-core kernel's M-major form."""
+    from presk_b200 import launch_desc
+    bsz, t, d, ff = 2, 256, 192, 320
+    rng = np.random.default_rng(31)
+    x = oracle.convert((rng.standard_normal((bsz, t, d)) * 0.5).astype(np.float32), abi.BF16)
+    ct = oracle.convert((rng.standard_normal((bsz, t, ff)) * 0.5).astype(np.float32), abi.BF16)
+
+    def launch(order):
+        l = launch_desc(abi.OP_CONTRACT, abi.BF16, [d, ff], [bsz, t], order=order)
+        l.n_inputs = 2
+        l.inputs[0].dtype, l.inputs[0].numel = abi.BF16, x.size // 2
+        l.inputs[0].stride[0], l.inputs[0].stride[2], l.inputs[0].stride[3] = 1, t * d, d
+        l.inputs[1].dtype, l.inputs[1].numel = abi.BF16, ct.size // 2
+        l.inputs[1].stride[1], l.inputs[1].stride[2], l.inputs[1].stride[3] = 1, t * ff, ff
+        l.out.dtype, l.out.numel, l.out.stride[0], l.out.stride[1] = abi.BF16, d * ff, ff, 1
+        return l
+
+    px, pct, pc = cuda.upload(x), cuda.upload(ct), cuda.alloc(d * ff * 2)
+    cuda.set_profiling(True)
+    cuda.run(launch(abi.ORDER_DEVICE), [px, pct, pc])
+    cuda.sync()
+    assert any(rec[0] == "k_gemm_tc" for rec in cuda.profile()), "the launch did not reach the tensor-core kernel"
+    cuda.set_profiling(False)
+    got = _bf16_values(cuda.download(pc, d * ff * 2))
+    want_b = np.zeros(d * ff * 2, np.uint8)
+    oracle.run(launch(abi.ORDER_SEQUENTIAL), [x, ct, want_b])
+    want = _bf16_values(want_b)
+    assert np.abs(got - want).max() <= 2.0**-7 * np.abs(want).max()
+    for p in (px, pct, pc):
+        cuda.free(p)
