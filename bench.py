@@ -223,6 +223,16 @@ def microbench(args):
         ex.sync()
         ms = (time.perf_counter() - t0) * 1e3 / args.steps
         flops = 3.0 * flops_per_token(consts, T) * B * T
+        ex.set_profiling(True)
+        one()
+        agg = {}
+        for kern, name, kms, _, _ in ex.profile():
+            a = agg.setdefault(kern + " | " + name, [0, 0.0])
+            a[0] += 1
+            a[1] += kms
+        ex.set_profiling(False)
+        top = sorted(agg.items(), key=lambda kv: -kv[1][1])[:14]
+        print(json.dumps({"top_launches_ms": {k: [v[0], round(v[1], 3)] for k, v in top}, "profiled_total_ms": round(sum(v[1] for v in agg.values()), 2)}))
         print(json.dumps({"micro": "train", "shape": dims, "ms_per_step": ms, "tokens/s": B * T / ms * 1e3, "model TFLOP/s (3x forward)": flops / ms / 1e9, "loss": float(host.call("loss", [ids, y], ()))}))
         return
     if args.micro == "gemm":

@@ -992,7 +992,16 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
     case PSK_OP_REDUCE: {
         e->last_kernel = "k_reduce";
         const bool may_regroup = device_order && L.kind != PSK_REDUCE_SUM_STORED; // sum_to rounds every partial sum
-        if (may_regroup && L.n_outer == 0) k_reduce_all_tree<<<1, 1024, 0, e->stream>>>(L);
+        if (may_regroup && L.n_outer == 0 && L.inner >= (1ll << 20)) {
+            const int blocks = std::min(e->sms * 2, 1024);
+            float *partials = (float *)psk_exec_alloc(e, (size_t)blocks * 4);
+            if (!partials) { rc = fail(e, PSK_E10001, "reduce: no memory for the partial sums"); break; }
+            k_reduce_all_partials<<<blocks, 1024, 0, e->stream>>>(L, partials);
+            k_reduce_all_finish<<<1, 1024, 0, e->stream>>>(L, partials, blocks);
+            psk_exec_free(e, partials); // handed out again only to later work of the same stream
+            e->kernels += 1;
+        }
+        else if (may_regroup && L.n_outer == 0) k_reduce_all_tree<<<1, 1024, 0, e->stream>>>(L);
         else if (may_regroup && L.n_inner == 1 && L.in[0].stride[L.n_outer] == 1 && L.inner >= 64 && (L.inner % 8 != 0 || vec8_operand(L.in[0], L.dims, L.n_outer + 1, false) ))
             k_reduce_rows_tree<<<grid_for(e, L.total * 32, 256, 8), 256, 0, e->stream>>>(L);
         else k_reduce_seq<<<grid_for(e, L.total, 128, 16), 128, 0, e->stream>>>(L);
@@ -1209,7 +1218,8 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
     case PSK_OP_XENT_VJP: {
         e->last_kernel = "k_xent_vjp";
         if (L.n_inner != 1 || L.n_in != 3) { rc = fail(e, PSK_E7001, "cross_entropy_vjp: logits, labels and a cotangent"); break; }
-        k_xent_vjp_rows<<<(int)std::min<int64_t>((L.total + 3) / 4, (int64_t)e->sms * 16), 128, 0, e->stream>>>(L);
+        if (device_order && L.inner >= 256) k_xent_vjp_rows_tree<<<(int)std::min<int64_t>(L.total, (int64_t)e->sms * 8), 256, 0, e->stream>>>(L);
+        else k_xent_vjp_rows<<<(int)std::min<int64_t>((L.total + 3) / 4, (int64_t)e->sms * 16), 128, 0, e->stream>>>(L);
         e->kernels += 1;
         break;
     }

@@ -1537,8 +1537,26 @@ struct psk_host {
     {
         int d = site_dtype(site);
         Tensor out = fresh(axes, d);
-        std::vector<uint8_t> z((size_t)std::max<int64_t>(1, out.numel()) * elem_bytes(d), 0);
-        check(vt->upload(vt->self, out.ptr(), z.data(), z.size()), "zeros_like");
+        if (out.numel() <= 4096) {
+            std::vector<uint8_t> z((size_t)std::max<int64_t>(1, out.numel()) * elem_bytes(d), 0);
+            check(vt->upload(vt->self, out.ptr(), z.data(), z.size()), "zeros_like");
+            return out;
+        }
+        // a large leaf: filled on the executor, not sent from the host (still no launch of the program's)
+        psk_launch l;
+        memset(&l, 0, sizeof l);
+        l.op = PSK_OP_IOTA;
+        l.kind = PSK_IOTA_FILL;
+        l.dtype = d;
+        l.fparam[0] = 0.0;
+        Axes flat = {{"", out.numel()}};
+        set_space(l, flat, {});
+        set_operand(l.out, out, {1}, {});
+        const int64_t before = launches;
+        const std::string keep = log;
+        run(l, "zeros_like", {}, out);
+        launches = before;
+        log = keep;
         return out;
     }
 

@@ -709,6 +709,33 @@ __global__ void __launch_bounds__(1024) k_reduce_all_tree(const __grid_constant_
     if (L.guarded && ovf) atomicOr(L.ovf, 1u);
 }
 
+// The same for a large tensor (a parameter tree's leaf under `sum_squares`): every block sums its share into
+// `partials`, a second launch of one block sums those. The grid's size is fixed, so the sum's order is too.
+__global__ void __launch_bounds__(1024) k_reduce_all_partials(const __grid_constant__ DevLaunch L, float *partials)
+{
+    __shared__ float red[32];
+    uint32_t ovf = 0;
+    float acc = 0.0f;
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < L.inner; c += step) {
+        float x = load_operand(L.in[0], operand_offset(L.in[0], L.dims, L.n_outer, L.n_inner, c), 0, L.kdtype, &ovf);
+        acc += L.kind == PSK_REDUCE_SUMSQ ? __fmul_rn(x, x) : x;
+    }
+    acc = block_reduce<false>(acc, red);
+    if (threadIdx.x == 0) partials[blockIdx.x] = acc;
+    if (L.guarded && ovf) atomicOr(L.ovf, 1u);
+}
+__global__ void __launch_bounds__(1024) k_reduce_all_finish(const __grid_constant__ DevLaunch L, const float *partials, int n)
+{
+    __shared__ float red[32];
+    float acc = 0.0f;
+    for (int c = threadIdx.x; c < n; c += blockDim.x) acc += partials[c];
+    acc = block_reduce<false>(acc, red);
+    uint32_t ovf = 0;
+    if (threadIdx.x == 0) ovf |= store_real(const_cast<void *>(L.out.p), L.out.dtype, 0, reduce_finish(L, acc));
+    if (L.guarded && ovf) atomicOr(L.ovf, 1u);
+}
+
 // ---------------------------------------------------------------------------
 // PSK_OP_SOFTMAX (lower.rs:1274-1419), three passes, exact: a thread a row.
 // Input 1, when masked, is indices 0 or 1 broadcast into the scores; iparam[0]
@@ -990,6 +1017,32 @@ __global__ void __launch_bounds__(256) k_xent_rows_tree(const __grid_constant__ 
             if (y >= 0 && y < n) xy = load_operand(L.in[0], base + y * L.in[0].stride[L.n_outer], 0, L.kdtype, &ovf);
             else atomicOr(L.status, 2u);
             ovf |= store_real(const_cast<void *>(L.out.p), L.out.dtype, obase, __fsub_rn(__fadd_rn(lm_logf(z), m), xy));
+        }
+    }
+    if (L.guarded && ovf) atomicOr(L.ovf, 1u);
+}
+
+// PSK_OP_XENT_VJP under PSK_ORDER_DEVICE: a block a row, the maximum and z as trees, then every thread its share.
+__global__ void __launch_bounds__(256) k_xent_vjp_rows_tree(const __grid_constant__ DevLaunch L)
+{
+    __shared__ float red[32];
+    uint32_t ovf = 0;
+    const int64_t n = L.inner, s = L.in[0].stride[L.n_outer], os = L.out.stride[L.n_outer];
+    for (int64_t row = blockIdx.x; row < L.total; row += gridDim.x) {
+        const int64_t base = operand_offset(L.in[0], L.dims, 0, L.n_outer, row);
+        float m = -INFINITY;
+        for (int64_t c = threadIdx.x; c < n; c += blockDim.x) m = fmaxf(m, load_operand(L.in[0], base + c * s, 0, L.kdtype, &ovf));
+        m = block_reduce<true>(m, red);
+        float z = 0.0f;
+        for (int64_t c = threadIdx.x; c < n; c += blockDim.x) z += lm_expf(__fsub_rn(load_operand(L.in[0], base + c * s, 0, L.kdtype, &ovf), m));
+        z = block_reduce<false>(z, red);
+        const int64_t y = ((const int64_t *)L.in[1].p)[operand_offset(L.in[1], L.dims, 0, L.n_outer, row)];
+        const float ct = load_operand(L.in[2], operand_offset(L.in[2], L.dims, 0, L.n_outer, row), 0, L.kdtype, &ovf);
+        const int64_t obase = operand_offset(L.out, L.dims, 0, L.n_outer, row);
+        for (int64_t k = threadIdx.x; k < n; k += blockDim.x) {
+            const float hot = (float)k == (float)y ? 1.0f : 0.0f;
+            const float sm = __fdiv_rn(lm_expf(__fsub_rn(load_operand(L.in[0], base + k * s, 0, L.kdtype, &ovf), m)), z);
+            ovf |= store_real(const_cast<void *>(L.out.p), L.out.dtype, obase + k * os, __fmul_rn(__fsub_rn(sm, hot), ct));
         }
     }
     if (L.guarded && ovf) atomicOr(L.ovf, 1u);
