@@ -751,7 +751,7 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
     case PSK_OP_FUSED: {
         e->last_kernel = "k_fused";
         if (l->n_steps < 1 || l->n_steps > PSK_MAX_STEPS) { rc = fail(e, PSK_E7001, "fused: a group of no step or of too many"); break; }
-        bool vec = !any_affine && L.n_outer >= 1 && l->n_steps <= 8 && L.dims[L.n_outer - 1] % 8 == 0 && vec8_operand(L.out, L.dims, L.n_outer, true);
+        bool vec = !any_affine && L.n_outer >= 1 && l->n_steps <= 12 && L.dims[L.n_outer - 1] % 8 == 0 && vec8_operand(L.out, L.dims, L.n_outer, true);
         for (int i = 0; vec && i < L.n_in; ++i) vec = vec8_operand(L.in[i], L.dims, L.n_outer, false);
         bool hot = vec && L.n_outer <= 3 && L.n_in <= 4 && l->n_steps <= 4 && L.total / 8 < 0xffffffffll;
         for (int i = 0; hot && i < L.n_in; ++i) hot = L.in[i].dtype != PSK_I8;
@@ -828,7 +828,8 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
                 }
             }
         }
-        else if (vec) k_fused_vec8<<<grid_for(e, L.total / 8, 256, 8), 256, 0, e->stream>>>(L);
+        else if (vec && l->n_steps > 8) k_fused_vec8<12><<<grid_for(e, L.total / 8, 256, 8), 256, 0, e->stream>>>(L);
+        else if (vec) k_fused_vec8<8><<<grid_for(e, L.total / 8, 256, 8), 256, 0, e->stream>>>(L);
         else k_fused<<<grid_for(e, L.total, 256, 8), 256, 0, e->stream>>>(L);
         e->kernels += 1;
         break;
@@ -991,7 +992,10 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
     }
     case PSK_OP_REDUCE: {
         e->last_kernel = "k_reduce";
-        const bool may_regroup = device_order && L.kind != PSK_REDUCE_SUM_STORED; // sum_to rounds every partial sum
+        // Under the device order a sum's terms may be regrouped; `sum_to`, whose running sum the reference keeps in the
+        // output's storage, is then summed in f32 and rounded once like any other (a declared difference in order).
+        const bool may_regroup = device_order;
+        const bool cols = may_regroup && L.n_outer >= 1 && L.n_inner >= 1 && L.inner >= 64 && L.in[0].stride[L.n_outer - 1] == 1 && L.in[0].stride[L.n_outer + L.n_inner - 1] != 1;
         if (may_regroup && L.n_outer == 0 && L.inner >= (1ll << 20)) {
             const int blocks = std::min(e->sms * 2, 1024);
             float *partials = (float *)psk_exec_alloc(e, (size_t)blocks * 4);
@@ -1004,6 +1008,7 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
         else if (may_regroup && L.n_outer == 0) k_reduce_all_tree<<<1, 1024, 0, e->stream>>>(L);
         else if (may_regroup && L.n_inner == 1 && L.in[0].stride[L.n_outer] == 1 && L.inner >= 64 && (L.inner % 8 != 0 || vec8_operand(L.in[0], L.dims, L.n_outer + 1, false) ))
             k_reduce_rows_tree<<<grid_for(e, L.total * 32, 256, 8), 256, 0, e->stream>>>(L);
+        else if (cols) k_reduce_cols_tree<<<(int)std::min<int64_t>((L.total + 31) / 32, (int64_t)e->sms * 2), 1024, 0, e->stream>>>(L);
         else k_reduce_seq<<<grid_for(e, L.total, 128, 16), 128, 0, e->stream>>>(L);
         e->kernels += 1;
         break;

@@ -2220,15 +2220,19 @@ struct psk_host {
             // %7 sum_squares g (a launch a leaf, the sums added on the host), then [%8 sqrt; %11 + 1e-6; %14 c / it;
             // %17 1 - it; %18 relu; %19 1 - it] as one scalar group, %20 g * factor leaf by leaf
             double acc = 0.0;
+            std::vector<Tensor> sums; // every leaf's launch first, then one wait for all of them
             for (auto &kv : params) {
                 Tensor n2 = reduce_all(f + "/%7", PSK_REDUCE_SUMSQ, grads[kv.first]);
                 Tensor wide = fresh({}, PSK_F64);
                 convert_into(n2, wide);
+                sums.push_back(wide);
+            }
+            for (auto &wide : sums) {
                 double v = 0.0;
                 check(vt->download(vt->self, &v, wide.ptr(), 8), "download");
-                check(vt->sync(vt->self), "sum_squares");
                 acc += v;
             }
+            check(vt->sync(vt->self), "sum_squares");
             Tensor n2 = scalar(f + "/%7", acc), tiny = scalar(f + "/%10", 1e-6), c = scalar(f + "/%13", adamw.grad_clip), one1 = scalar(f + "/%16", 1.0);
             Tensor factor = fused(f + "/%19", {U(PSK_SQRT, 0), Bn(PSK_ADD, S(0), 1), Bn(PSK_DIV, 2, S(1)), Bn(PSK_SUB, 3, S(2)), U(PSK_RELU, S(3)), Bn(PSK_SUB, 3, S(4))}, {&n2, &tiny, &c, &one1});
             for (auto &kv : params) grads[kv.first] = binary(f + "/%20", PSK_MUL, grads[kv.first], factor);

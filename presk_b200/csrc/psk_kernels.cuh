@@ -333,6 +333,8 @@ PSK_DEV uint32_t store_vec(const DevOperand &o, int64_t off, const float (&x)[V]
 // PSK_OP_FUSED, vectorised: the last axis is contiguous (stride 1) or
 // broadcast (stride 0) in every operand, a multiple of 8 long, and every
 // base and outer stride is a multiple of 8 elements; at most 8 steps.
+// MAXS: the most steps a group may have here (8 for the forward groups; 12 for the optimizer's 9-step update)
+template <int MAXS = 8>
 __global__ void __launch_bounds__(256) k_fused_vec8(const __grid_constant__ DevLaunch L)
 {
     uint32_t ovf = 0;
@@ -356,9 +358,9 @@ __global__ void __launch_bounds__(256) k_fused_vec8(const __grid_constant__ DevL
                 soff[i] += ix * L.in[i].sstride[a];
             }
         }
-        float vals[8][8];
+        float vals[MAXS][8];
 #pragma unroll
-        for (int s = 0; s < 8; ++s) {
+        for (int s = 0; s < MAXS; ++s) {
             if (s < L.n_steps) {
                 const psk_step st = L.steps[s];
                 float a[2][8];
@@ -371,10 +373,10 @@ __global__ void __launch_bounds__(256) k_fused_vec8(const __grid_constant__ DevL
                         } else {
 #pragma unroll
                             for (int t = 0; t < 8; ++t) {
-                                // a step reads an earlier one: s' < s <= 7
+                                // a step reads an earlier one: s' < s <= MAXS - 1
                                 float v = 0.0f;
 #pragma unroll
-                                for (int q = 0; q < 7; ++q)
+                                for (int q = 0; q < MAXS - 1; ++q)
                                     if (q == -1 - src) v = vals[q][t];
                                 a[j][t] = v;
                             }
@@ -391,7 +393,7 @@ __global__ void __launch_bounds__(256) k_fused_vec8(const __grid_constant__ DevL
         for (int t = 0; t < 8; ++t) {
             float v = 0.0f;
 #pragma unroll
-            for (int q = 0; q < 8; ++q)
+            for (int q = 0; q < MAXS; ++q)
                 if (q == L.n_steps - 1) v = vals[q][t];
             res[t] = v;
         }
@@ -690,6 +692,37 @@ __global__ void __launch_bounds__(256) k_reduce_rows_tree(const __grid_constant_
             int64_t ooff = operand_offset(L.out, L.dims, 0, L.n_outer, row);
             ovf |= store_real(const_cast<void *>(L.out.p), L.out.dtype, ooff, reduce_finish(L, acc));
         }
+    }
+    if (L.guarded && ovf) atomicOr(L.ovf, 1u);
+}
+
+// Sums over leading rows for every element of a contiguous last outer axis (a bias's or a gain's gradient: `sum_to`
+// of [rows, n] into [n]) under PSK_ORDER_DEVICE: a block of 32 x 32 threads takes 32 neighbouring outputs, its 32
+// thread rows stride through the summed index, and their partial sums meet in shared memory.
+__global__ void __launch_bounds__(1024) k_reduce_cols_tree(const __grid_constant__ DevLaunch L)
+{
+    __shared__ float part[32][33];
+    uint32_t ovf = 0;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    for (int64_t o0 = (int64_t)blockIdx.x * 32; o0 < L.total; o0 += (int64_t)gridDim.x * 32) {
+        const int64_t o = o0 + tx;
+        float acc = 0.0f;
+        if (o < L.total) {
+            const int64_t base = operand_offset(L.in[0], L.dims, 0, L.n_outer, o);
+            for (int64_t c = ty; c < L.inner; c += 32) {
+                float x = load_operand(L.in[0], base + operand_offset(L.in[0], L.dims, L.n_outer, L.n_inner, c), 0, L.kdtype, &ovf);
+                acc += L.kind == PSK_REDUCE_SUMSQ ? __fmul_rn(x, x) : x;
+            }
+        }
+        part[ty][tx] = acc;
+        __syncthreads();
+        if (ty == 0 && o < L.total) {
+            float sum = 0.0f;
+#pragma unroll
+            for (int r = 0; r < 32; ++r) sum += part[r][tx];
+            ovf |= store_real(const_cast<void *>(L.out.p), L.out.dtype, operand_offset(L.out, L.dims, 0, L.n_outer, o), reduce_finish(L, sum));
+        }
+        __syncthreads();
     }
     if (L.guarded && ovf) atomicOr(L.ovf, 1u);
 }
