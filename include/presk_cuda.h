@@ -487,6 +487,11 @@ int psk_host_mean_over_ranks(psk_host *h, psk_comm *c, const void *device_scalar
 /* Merges the magnitudes psk_host_envelope reports over the ranks: one max-reduction (the minima travel
  * complemented). After it every rank's envelope is that of the whole batch. */
 int psk_host_envelope_allreduce(psk_host *h, psk_comm *c);
+/* A training step over a sharded batch: every rank holds the gradient of the mean loss over its own rows (as many
+ * rows on every rank); this sums each leaf of the last gradient over the ranks (NCCL, in the leaf's storage type, on
+ * the executor's stream) and divides by their number, so that psk_host_adamw_step takes the same step everywhere:
+ * the gradient all-reduce a data-parallel `presk train` needs. */
+int psk_host_grads_allreduce(psk_host *h, psk_comm *c);
 
 #ifdef __cplusplus
 }

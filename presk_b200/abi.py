@@ -123,6 +123,7 @@ PROTOTYPES = {
     "psk_comm_allreduce": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32]),
     "psk_host_mean_over_ranks": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.POINTER(C.c_double)]),
     "psk_host_envelope_allreduce": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "psk_host_grads_allreduce": (C.c_int, [C.c_void_p, C.c_void_p]),
     "psk_host_result": (C.c_int, [C.c_void_p, C.c_char_p, C.c_void_p, C.c_int32, C.c_int64, C.POINTER(C.c_int64)]),
     "psk_host_set_result": (C.c_int, [C.c_void_p, C.c_char_p, C.c_void_p, C.c_int32, C.POINTER(C.c_int64), C.c_int32]),
     "psk_host_adamw": (C.c_int, [C.c_void_p, C.c_char_p]),

@@ -237,6 +237,10 @@ class Host:
         self._check(self.lib.psk_host_mean_over_ranks(self.handle, comm.handle, device_scalar, dtype, C.byref(out)))
         return out.value
 
+    def grads_allreduce(self, comm):
+        """The last gradient's leaves averaged over the ranks of `comm` (a data-parallel training step)."""
+        self._check(self.lib.psk_host_grads_allreduce(self.handle, comm.handle))
+
     def envelope_allreduce(self, comm):
         """Merges the calibrated magnitudes over the ranks."""
         self._check(self.lib.psk_host_envelope_allreduce(self.handle, comm.handle))

@@ -111,14 +111,16 @@ const char *psk_comm_error(const psk_comm *c) { return c ? c->error.c_str() : g_
 int psk_comm_allreduce(psk_comm *c, void *device_buf, int64_t count, int32_t dtype, int32_t op)
 {
     if (!c || !c->comm) return PSK_E10001;
-    // NCCL's ncclDataType_t and ncclRedOp_t: uint32 3, int64 4, float32 7, float64 8; sum 0, max 2, min 3
+    // NCCL's ncclDataType_t and ncclRedOp_t: uint32 3, int64 4, float16 6, float32 7, float64 8, bfloat16 9; sum 0, max 2, min 3
     int nd;
     switch (dtype) {
     case PSK_F32: nd = 7; break;
     case PSK_F64: nd = 8; break;
+    case PSK_F16: nd = 6; break;
+    case PSK_BF16: nd = 9; break;
     case PSK_I64: nd = 4; break;
     case PSK_COMM_U32: nd = 3; break;
-    default: c->error = "psk_comm_allreduce: f32, f64, i64 or raw 32-bit words"; return PSK_E7001;
+    default: c->error = "psk_comm_allreduce: f32, f64, bf16, f16, i64 or raw 32-bit words"; return PSK_E7001;
     }
     int no;
     switch (op) {

@@ -2785,6 +2785,30 @@ int psk_host_envelope_allreduce(psk_host *h, psk_comm *c)
     return PSK_OK;
 }
 
+int psk_host_grads_allreduce(psk_host *h, psk_comm *c)
+{
+    HOST_TRY(h, {
+        if (!c) raise(PSK_E7001, "psk_host_grads_allreduce: a communicator");
+        const int n = psk_comm_size(c);
+        for (auto &kv : h->results) {
+            Tensor leaf = kv.second;
+            if (leaf.dtype != PSK_F32 && leaf.dtype != PSK_BF16 && leaf.dtype != PSK_F16 && leaf.dtype != PSK_F64) raise(PSK_E7005, "psk_host_grads_allreduce: the leaf `" + kv.first + "` is not stored as a float NCCL sums");
+            if (!leaf.vstrides.empty() || leaf.affine) {
+                // a view: summed through a contiguous copy
+                Tensor flat = h->fresh(leaf.axes, leaf.dtype);
+                h->convert_into(leaf, flat);
+                leaf = flat;
+            }
+            void *p = (uint8_t *)leaf.ptr() + leaf.off * (int64_t)elem_bytes(leaf.dtype);
+            if (psk_comm_allreduce(c, p, leaf.numel(), leaf.dtype, PSK_COMM_SUM) != PSK_OK) raise(PSK_E10001, std::string("all-reduce of `") + kv.first + "`: " + psk_comm_error(c));
+            // every rank's loss is the mean over its own rows (as many on every rank): the whole batch's gradient is the ranks' mean
+            kv.second = n > 1 ? h->fused("grads_allreduce/mean", {U(PSK_DIV_N, 0, n)}, {&leaf}) : leaf;
+        }
+        h->check(h->vt->sync(h->vt->self), "grads_allreduce");
+    });
+    return PSK_OK;
+}
+
 void psk_host_set_calibrating(psk_host *h, int on)
 {
     h->calibrating = on != 0;

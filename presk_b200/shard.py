@@ -1,5 +1,5 @@
-"""Sharding of the batch axis over ranks (one process a GPU) and the one exchange the
-forward pass needs: the final loss.
+"""Sharding of the batch axis over ranks (one process a GPU) and the exchanges of a sharded run: the final
+loss of a forward pass, calibration's magnitudes, and a training step's gradient.
 
 Every launch of a forward pass carries `batch` as an outer parallel axis with disjoint
 outputs (presk-kernel/src/ir.rs:345-375), so a rank runs the whole model on its own rows
@@ -45,3 +45,21 @@ def combine_envelopes(envelope, device="cpu", group=None):
         dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
     t = t.cpu()
     return {s: (float(t[i, 0]), float(-t[i, 1]), float(-t[i, 2]), float(t[i, 3])) for i, s in enumerate(sites)}
+
+
+def combine_gradients(leaves, local_count, device="cpu", group=None):
+    """A training step over a sharded batch: each rank holds the gradient of the mean loss over its own rows; the
+    gradient of the mean over all rows is the row-weighted mean of those, one all-reduce a leaf. `leaves` maps a
+    parameter's path to a float array; every rank passes the same paths. Returns the combined leaves, which the
+    caller hands back to the host (`Host.set_result`) before `adamw_step`: every rank then takes the same step."""
+    world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+    n = torch.tensor([float(local_count)], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(n, op=dist.ReduceOp.SUM, group=group)
+    out = {}
+    for path in sorted(leaves):
+        t = torch.as_tensor(leaves[path], dtype=torch.float64, device=device) * float(local_count)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group)
+        out[path] = (t / n).cpu().numpy()
+    return out

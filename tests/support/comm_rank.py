@@ -56,6 +56,13 @@ out["loss"] = h.mean_over_ranks(comm, ptr, dt)
 h.envelope_allreduce(comm)
 env = h.envelope()
 out["envelope"] = {k: list(v) for k, v in sorted(env.items())[:40]}
+# a data-parallel training step: each rank's gradient on its rows, averaged over the ranks, the same AdamW step
+ht = models.give(Host(ex, "f32").prepare("llama", **c), params).adamw(lr=1e-2, weight_decay=0.1)
+ht.call("loss_grad", [ids[mine], y[mine]], params["tok"].shape)
+ht.grads_allreduce(comm)
+out["grad_head"] = ht.result("head", params["head"].shape).astype(np.float64).tolist()
+ht.adamw_step(1, 2)
+out["head_after"] = ht.result("head", params["head"].shape).astype(np.float64).tolist()
 comm.close()
 with open(out_file, "w") as f:
     json.dump(out, f)

@@ -48,3 +48,13 @@ def test_two_ranks_exchange_loss_and_envelope(tmp_path, oracle):
         if site.startswith("loss/"):
             continue  # the loss's own sites are per-rank means; they are what mean_over_ranks combines
         np.testing.assert_allclose(got, whole[site], rtol=1e-6, err_msg=site)
+    # the data-parallel training step: both ranks hold the whole batch's gradient and take its AdamW step
+    ht = models.give(Host(oracle.vtable(), "f32").prepare("llama", **c), params).adamw(lr=1e-2, weight_decay=0.1)
+    ht.call("loss_grad", [ids, y], params["tok"].shape)
+    want_g = ht.result("head", params["head"].shape).astype(np.float64)
+    assert outs[0]["grad_head"] == outs[1]["grad_head"]
+    assert np.abs(np.array(outs[0]["grad_head"]) - want_g).max() <= 1e-5 * np.abs(want_g).max()
+    ht.adamw_step(1, 2)
+    want_p = ht.result("head", params["head"].shape).astype(np.float64)
+    assert outs[0]["head_after"] == outs[1]["head_after"]
+    assert np.abs(np.array(outs[0]["head_after"]) - want_p).max() <= 2e-3 * np.abs(want_p).max()

@@ -77,3 +77,62 @@ def test_two_ranks_give_the_whole_batch_loss(oracle, tmp_path):
             continue
         assert tuple(got["envelope"][site]) == v, site
     assert got["slowest"] == 2.0
+
+
+TRAIN_WORKER = textwrap.dedent("""
+    import os, sys, json
+    import numpy as np
+    sys.path.insert(0, {root!r}); sys.path.insert(0, os.path.join({root!r}, "tests"))
+    import torch.distributed as dist
+    import models, oracle_lib
+    from presk_b200 import Host, shard
+    dist.init_process_group("gloo", init_method="tcp://127.0.0.1:{port}", rank=int(sys.argv[1]), world_size=2)
+    rank, world = dist.get_rank(), dist.get_world_size()
+    c = models.LLAMA_TINY
+    p = models.llama_params(c, seed=4, std=0.1)
+    rng = np.random.default_rng(11)
+    ids = rng.integers(0, c["V"], size=(4, 12), dtype=np.int64)
+    y = rng.integers(0, c["V"], size=(4, 12), dtype=np.int64)
+    lo, hi = shard.shard_rows(4, rank, world)
+    h = models.give(Host(oracle_lib.load().vtable(), "f32").prepare("llama", **c), p).adamw(lr=1e-2, weight_decay=0.1, grad_clip=1.0)
+    for t in (1, 2):
+        h.call("loss_grad", [ids[lo:hi], y[lo:hi]], p["tok"].shape)
+        mine = {{k: h.result(k, np.shape(v), np.float64) for k, v in p.items()}}
+        for k, g in shard.combine_gradients(mine, (hi - lo) * 12).items():
+            h.set_result(k, g)
+        h.adamw_step(t, 2)
+    after = {{k: h.result(k, np.shape(v), np.float64).tolist() for k, v in p.items()}}
+    with open(sys.argv[2], "w") as f:  # not through a pipe: the parent reads the ranks one after the other
+        json.dump(after, f)
+    dist.barrier()
+    dist.destroy_process_group()
+""")
+
+
+def test_two_ranks_take_the_whole_batch_s_training_steps(oracle, tmp_path):
+    """Two data-parallel ranks, each with half the rows: gradients combined by `shard.combine_gradients`, the same
+    AdamW step on both. After two steps both ranks hold the same parameters, and they are the parameters one
+    process reaches on the whole batch (to the accuracy of f32 gradients summed in another order)."""
+    port = 31500 + os.getpid() % 2000
+    script = tmp_path / "train_worker.py"
+    script.write_text(TRAIN_WORKER.format(root=ROOT, port=port))
+    procs = [subprocess.Popen([sys.executable, str(script), str(r), str(tmp_path / f"rank{r}.json")], stdout=subprocess.DEVNULL, stderr=subprocess.PIPE, text=True) for r in range(2)]
+    outs = [p.communicate(timeout=240) for p in procs]
+    assert all(p.returncode == 0 for p in procs), outs
+    import json
+    ranks = [json.load(open(tmp_path / f"rank{r}.json")) for r in range(2)]
+    c = models.LLAMA_TINY
+    p = models.llama_params(c, seed=4, std=0.1)
+    rng = np.random.default_rng(11)
+    ids = rng.integers(0, c["V"], size=(4, 12), dtype=np.int64)
+    y = rng.integers(0, c["V"], size=(4, 12), dtype=np.int64)
+    h = models.give(Host(oracle.vtable(), "f32").prepare("llama", **c), p).adamw(lr=1e-2, weight_decay=0.1, grad_clip=1.0)
+    for t in (1, 2):
+        h.call("loss_grad", [ids, y], p["tok"].shape)
+        h.adamw_step(t, 2)
+    for k, v in p.items():
+        a, b = np.array(ranks[0][k]), np.array(ranks[1][k])
+        assert np.array_equal(a, b), k
+        whole = h.result(k, np.shape(v), np.float64)
+        assert np.abs(a - whole).max() <= 2e-3 * max(np.abs(whole).max(), 1e-3), (k, np.abs(a - whole).max())
+        assert np.abs(whole - np.asarray(v, np.float64)).max() > 0, k
