@@ -160,7 +160,9 @@ typedef enum {
     PSK_REDUCE_SUM = 0, PSK_REDUCE_MEAN = 1, PSK_REDUCE_SUMSQ = 2,
     PSK_REDUCE_SUM_STORED = 3 /* lower.rs:1670-1680 `sum_to`: the sum is kept in the output buffer, so every partial sum
                                  is rounded to the output's type (and tested by the guard) before the next term is
-                                 added; terms in row-major order of the summed axes; never reassociated */
+                                 added; terms in row-major order of the summed axes. Under PSK_ORDER_DEVICE an
+                                 executor may sum it like PSK_REDUCE_SUM (f32 partial sums in its own order, one
+                                 rounding): the declared difference of that order */
 } psk_reduce_kind;
 
 typedef enum {
