@@ -334,7 +334,14 @@ int psk_exec_gemm(psk_exec *e, const psk_gemm *g, const void *a, const void *b, 
  * contents: two calls that overlap on one GPU (two host threads, or a second
  * route to the same kernel) race on it. The first call on a device looks the
  * array's device address up and sets the kernel's attributes; make that first
- * call before any stream capture begins. */
+ * call before any stream capture begins. Every call, the first included, waits
+ * for `stream` and copies the flags back to the host before it returns, so the
+ * entry point is not callable while the stream is capturing.
+ *
+ * The descriptor is checked before anything is launched: out_dtype one of
+ * PSK_F32, PSK_BF16, PSK_F16, PSK_E8M15; c_row_lo_count and c_col_lo_count at
+ * least 1 (the kernel divides by them); no negative stride. Anything else is
+ * PSK_E7001 (PSK_E7005 for a type the kernel does not store). */
 #define PSK_NOALLOC_MAX_BATCH 1023
 int psk_gemm_noalloc(const psk_gemm *g, const void *a, const void *b, void *c, void *stream, int64_t *overflowed_batch, char *err, size_t err_cap);
 

@@ -52,6 +52,7 @@ struct psk_exec {
     uint32_t *status = nullptr;                        // one word: kernel-side trouble
     std::vector<int64_t> flag_serial;                  // the launch each slot was last given to
     int64_t guarded_since = 0;
+    int64_t latched_overflow = 0;                      // 1 + serial of an overflow found when the slots were recycled
     int64_t launches = 0, kernels = 0;
     std::string overflow_name;
     bool profiling = false;
@@ -397,11 +398,35 @@ int launch_tc(psk_exec *e, const psk_gemm &g, const void *a, const void *b, void
     return PSK_OK;
 }
 
+// The guard's flags since the last drain: 0, or 1 + the serial number of the first guarded launch whose flag is set.
+// Waits for the stream, clears the flags and starts the slots over.
+int64_t drain_flags(psk_exec *e)
+{
+    if (e->guarded_since == 0) return 0;
+    cudaSetDevice(e->device);
+    std::vector<uint32_t> host(kFlagSlots);
+    if (cudaMemcpyAsync(host.data(), e->flags, kFlagSlots * sizeof(uint32_t), cudaMemcpyDeviceToHost, e->stream) != cudaSuccess) return 0;
+    cudaStreamSynchronize(e->stream);
+    int64_t first = -1;
+    const int64_t used = std::min<int64_t>(e->guarded_since, kFlagSlots);
+    for (int64_t s = 0; s < used; ++s)
+        if (host[s] && (first < 0 || e->flag_serial[s] < first)) first = e->flag_serial[s];
+    cudaMemsetAsync(e->flags, 0, kFlagSlots * sizeof(uint32_t), e->stream);
+    e->guarded_since = 0;
+    return first < 0 ? 0 : first + 1;
+}
+
+// A slot of the guard's flags for one guarded launch. A slot is never shared by two launches between two drains:
+// when every slot has been handed out the flags are drained first, and an overflow found then is kept
+// (`latched_overflow`) for the next psk_exec_overflow, so that the launch it names is the one that overflowed.
 uint32_t *next_flag(psk_exec *e, const psk_launch *l)
 {
-    int slot = (int)(e->guarded_since % kFlagSlots);
+    if (e->guarded_since >= kFlagSlots) {
+        const int64_t o = drain_flags(e);
+        if (o && !e->latched_overflow) e->latched_overflow = o;
+    }
+    const int slot = (int)e->guarded_since;
     e->flag_serial[slot] = e->launches;
-    if (e->guarded_since < kFlagSlots) { /* first use since the last check: still zero */ }
     e->guarded_since += 1;
     (void)l;
     return e->flags + slot;
@@ -463,6 +488,8 @@ void psk_exec_destroy(psk_exec *e)
     cudaFree(e->status);
     cudaEventDestroy(e->ev0);
     cudaEventDestroy(e->ev1);
+    for (auto &r : e->prof) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
+    for (cudaEvent_t ev : e->event_pool) cudaEventDestroy(ev);
     cudaStreamDestroy(e->stream);
     delete e;
 }
@@ -516,7 +543,7 @@ static void forget_widened(psk_exec *e, const void *written)
     }
     for (auto w = e->widened.begin(); w != e->widened.end();) {
         const uint8_t *q = (const uint8_t *)w->first.first;
-        if (q >= lo && q < hi) { cudaFree(w->second); w = e->widened.erase(w); }
+        if (q >= lo && q < hi) { cudaFree(w->second); e->live -= (size_t)w->first.second * 2; w = e->widened.erase(w); }
         else ++w;
     }
 }
@@ -531,7 +558,7 @@ void psk_exec_free(psk_exec *e, void *p)
     // widened copies of weights that lived in this buffer
     for (auto w = e->widened.begin(); w != e->widened.end();) {
         const uint8_t *q = (const uint8_t *)w->first.first;
-        if (q >= (const uint8_t *)p && q < (const uint8_t *)p + it->second) { cudaFree(w->second); w = e->widened.erase(w); }
+        if (q >= (const uint8_t *)p && q < (const uint8_t *)p + it->second) { cudaFree(w->second); e->live -= (size_t)w->first.second * 2; w = e->widened.erase(w); }
         else ++w;
     }
     // The stream is in order and every kernel of this executor runs on it, so
@@ -586,18 +613,13 @@ int psk_exec_wait_selftest(psk_exec *e, int64_t cycles)
 
 int64_t psk_exec_overflow(psk_exec *e)
 {
-    if (e->guarded_since == 0) return 0;
-    cudaSetDevice(e->device);
-    std::vector<uint32_t> host(kFlagSlots);
-    if (cudaMemcpyAsync(host.data(), e->flags, kFlagSlots * sizeof(uint32_t), cudaMemcpyDeviceToHost, e->stream) != cudaSuccess) return 0;
-    cudaStreamSynchronize(e->stream);
-    int64_t first = -1;
-    int64_t used = std::min<int64_t>(e->guarded_since, kFlagSlots);
-    for (int64_t s = 0; s < used; ++s)
-        if (host[s] && (first < 0 || e->flag_serial[s] < first)) first = e->flag_serial[s];
-    cudaMemsetAsync(e->flags, 0, kFlagSlots * sizeof(uint32_t), e->stream);
-    e->guarded_since = 0;
-    return first < 0 ? 0 : first + 1;
+    const int64_t now = drain_flags(e);
+    if (e->latched_overflow) { // found when the slots ran out: earlier than anything still in the flags
+        const int64_t o = e->latched_overflow;
+        e->latched_overflow = 0;
+        return o;
+    }
+    return now;
 }
 
 int psk_exec_sync(psk_exec *e)
@@ -667,6 +689,13 @@ int psk_exec_gemm(psk_exec *e, const psk_gemm *g, const void *a, const void *b, 
     cudaSetDevice(e->device);
     if (g->in_dtype != PSK_BF16 && g->in_dtype != PSK_F16) return fail(e, PSK_E7005, "tensor-core contraction: operands are bf16 or f16");
     if (!aligned16(a) || !aligned16(b)) return fail(e, PSK_E7001, "tensor-core contraction: operands must be 16-byte aligned");
+    if (g->out_dtype != PSK_F32 && g->out_dtype != PSK_BF16 && g->out_dtype != PSK_F16 && g->out_dtype != PSK_E8M15)
+        return fail(e, PSK_E7005, "tensor-core contraction: the result is stored as f32, bf16, f16 or e8m15");
+    if (g->m < 1 || g->n < 1 || g->k < 1 || g->batch < 1 || g->batch_lo < 1 || g->batch % g->batch_lo != 0)
+        return fail(e, PSK_E7001, "tensor-core contraction: sizes must be positive and batch a multiple of batch_lo");
+    if (g->c_row_lo_count < 1 || g->c_col_lo_count < 1) return fail(e, PSK_E7001, "tensor-core contraction: c_row_lo_count and c_col_lo_count are at least 1");
+    if (g->a_row < 0 || g->a_lo < 0 || g->a_hi < 0 || g->b_row < 0 || g->b_lo < 0 || g->b_hi < 0 || g->c_row_lo < 0 || g->c_row_hi < 0 || g->c_col_hi < 0 || g->c_lo < 0 || g->c_hi < 0)
+        return fail(e, PSK_E7001, "tensor-core contraction: a negative stride");
     uint32_t *flag = e->flags;
     if (g->guarded) {
         psk_launch dummy;
@@ -692,6 +721,8 @@ static const void *widened_weights(psk_exec *e, const void *codes, int64_t count
     else k_e4m3_to_bf16<<<grid_for(e, count, 256, 8), 256, 0, e->stream>>>((const uint8_t *)codes, (uint16_t *)wb, count);
     e->kernels += 1;
     e->widened.emplace(key, wb);
+    e->live += (size_t)count * 2; // the copy is device memory of this executor like any buffer of its pool
+    e->peak = std::max(e->peak, e->live);
     return wb;
 }
 
@@ -1290,6 +1321,7 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
 int psk_exec_quantize(psk_exec *e, const void *w, int from, int8_t *q, float *s, int64_t outer, int64_t k, int64_t inner)
 {
     cudaSetDevice(e->device);
+    forget_widened(e, q); // codes written anew: a bf16 copy of what the buffer held before is stale
     k_quant_scales<<<grid_for(e, outer * inner, 256, 8), 256, 0, e->stream>>>(w, from, s, outer, k, inner);
     k_quant_codes<<<grid_for(e, outer * k * inner, 256, 8), 256, 0, e->stream>>>(w, from, s, q, outer, k, inner);
     CUDA_TRY(e, cudaGetLastError());

@@ -189,8 +189,17 @@ struct Realization {
             for (auto &kv : q->obj) {
                 QuantSpec s;
                 if (auto *b = kv.second.get("bits")) s.bits = (int)b->num;
-                if (auto *o = kv.second.get("over")) s.over = (int)o->num;
+                // `over` is an AxisRef: a position or a name (presk-rt/src/quant.rs:46-49). Parameters reach this
+                // host without axis names (psk_host_set_param takes lengths only), so a name cannot be resolved here.
+                const Json *o = kv.second.get("over");
+                if (!o) raise(PSK_E7001, "realization: quant[" + kv.first + "] names no axis (`over`)");
+                if (o->kind != Json::Num) raise(PSK_E7005, "realization: quant[" + kv.first + "]: `over` is given by position on this executor (its parameters carry no axis names)");
+                s.over = (int)o->num;
                 if (s.bits != 8) raise(PSK_E7005, "realization: quant[" + kv.first + "]: this executor stores int8 weights only");
+                // the scales are absmax ones (quant.rs:299-323 `scale_of`); a power-of-two scheme gives other codes
+                if (const Json *sc = kv.second.get("scheme"))
+                    if (sc->kind != Json::Str || sc->str != "absmax")
+                        raise(PSK_E7005, "realization: quant[" + kv.first + "]: the scheme `" + (sc->kind == Json::Str ? sc->str : "?") + "` is not one this executor quantises with (absmax)");
                 r.quant[kv.first] = s;
             }
         if (auto *o = j.get("order")) {

@@ -81,6 +81,12 @@ extern "C" int psk_gemm_noalloc(const psk_gemm *g, const void *a, const void *b,
     }
     if (g->m < 1 || g->n < 1 || g->k < 1 || g->batch_lo < 1 || g->batch % g->batch_lo != 0) return say(err, err_cap, PSK_E7001, "psk_gemm_noalloc: sizes must be positive and batch a multiple of batch_lo");
     if (((uintptr_t)a & 15u) || ((uintptr_t)b & 15u)) return say(err, err_cap, PSK_E7001, "psk_gemm_noalloc: operands must be 16-byte aligned");
+    // the result's side of the descriptor: the kernel divides by the two counts and adds the strides to `c`
+    if (g->out_dtype != PSK_F32 && g->out_dtype != PSK_BF16 && g->out_dtype != PSK_F16 && g->out_dtype != PSK_E8M15)
+        return say(err, err_cap, PSK_E7005, "psk_gemm_noalloc: the result is stored as f32, bf16, f16 or e8m15");
+    if (g->c_row_lo_count < 1 || g->c_col_lo_count < 1) return say(err, err_cap, PSK_E7001, "psk_gemm_noalloc: c_row_lo_count and c_col_lo_count are at least 1");
+    if (g->a_row < 0 || g->a_lo < 0 || g->a_hi < 0 || g->b_row < 0 || g->b_lo < 0 || g->b_hi < 0 || g->c_row_lo < 0 || g->c_row_hi < 0 || g->c_col_hi < 0 || g->c_lo < 0 || g->c_hi < 0)
+        return say(err, err_cap, PSK_E7001, "psk_gemm_noalloc: a negative stride");
 
     int device = -1;
     if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return say(err, err_cap, PSK_E10001, "psk_gemm_noalloc: no current CUDA device");

@@ -4,6 +4,7 @@ and runs a small sharded loss and calibration through the host program, then wri
 import json
 import os
 import sys
+import threading
 import time
 
 import numpy as np
@@ -16,6 +17,21 @@ import models  # noqa: E402
 from presk_b200 import Comm, Executor, Host, abi  # noqa: E402
 
 rank, nranks, id_file, out_file = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], sys.argv[4]
+
+# The rank's own deadline: if the exchange has not finished by then (a peer died before its all-reduce), the
+# process ends itself, and with it whatever of its work still waits on the GPU for that peer.
+DEADLINE_S = 240
+
+
+def _give_up():
+    sys.stderr.write(f"comm_rank {rank}: not finished after {DEADLINE_S} s; exiting\n")
+    sys.stderr.flush()
+    os._exit(3)
+
+
+_watchdog = threading.Timer(DEADLINE_S, _give_up)
+_watchdog.daemon = True
+_watchdog.start()
 ex = Executor(rank)
 if rank == 0:
     uid = Comm.unique_id()
@@ -66,3 +82,4 @@ out["head_after"] = ht.result("head", params["head"].shape).astype(np.float64).t
 comm.close()
 with open(out_file, "w") as f:
     json.dump(out, f)
+_watchdog.cancel()

@@ -79,6 +79,13 @@ def test_realization_errors(oracle):
         Host(oracle.vtable(), {"default": "f32", "order": {"kind": "interleaved", "partials": 4}})
     with pytest.raises(PreskError, match="E7005"):
         Host(oracle.vtable(), {"default": "f32", "accum": {"Dense.apply/%3": "i32"}})
+    # quant entries the reference accepts and this host does not run: a power-of-two scheme (quant.rs:30-38) and an
+    # axis given by name (quant.rs:46-49); both refused, neither read as something else
+    with pytest.raises(PreskError, match="E7005.*pow2"):
+        Host(oracle.vtable(), {"default": "f32", "quant": {"blocks.attn.wq": {"bits": 8, "over": -2, "scheme": "pow2"}}})
+    with pytest.raises(PreskError, match="E7005.*by position"):
+        Host(oracle.vtable(), {"default": "f32", "quant": {"blocks.attn.wq": {"bits": 8, "over": "model"}}})
+    Host(oracle.vtable(), {"default": "f32", "quant": {"blocks.attn.wq": {"bits": 8, "over": -2, "scheme": "absmax"}}}).close()
     h = Host(oracle.vtable(), {"default": "f32", "params": {"blocks.attn.wz": "bf16"}})
     with pytest.raises(PreskError, match="no parameter of Llama"):
         h.prepare("llama", **models.LLAMA_TINY)

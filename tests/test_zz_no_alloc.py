@@ -84,3 +84,13 @@ def test_sizes_beyond_the_static_scratch_are_refused(cuda):
     g = gemm_desc(128, 128, 64, 1024, abi.BF16, abi.BF16)
     rc, where, msg = call_noalloc(cuda, g, 16, 16, 16)  # refused before any pointer is touched
     assert rc == abi.E7001 and "beyond" in msg and "1023" in msg
+
+
+def test_a_descriptor_the_kernel_cannot_index_with_is_refused(cuda):
+    """The result's side of the descriptor is checked before any launch: the kernel divides by the two
+    counts and adds the strides to the caller's pointer, so a zero count or a negative stride never reaches it."""
+    for field, value, code in (("c_row_lo_count", 0, abi.E7001), ("c_col_lo_count", 0, abi.E7001), ("c_row_lo", -256, abi.E7001), ("out_dtype", 77, abi.E7005)):
+        g = gemm_desc(128, 256, 64, 1, abi.BF16, abi.BF16)
+        setattr(g, field, value)
+        rc, where, msg = call_noalloc(cuda, g, 16, 16, 16)
+        assert rc == code and msg, (field, rc, msg)
