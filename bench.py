@@ -5,19 +5,28 @@ batch of synthetic token ids, through the host program of libpresk_cuda.so.
 
   value   tokens/s over all ranks with the ids already on the device, timed with
           CUDA events on the executor's stream, the maximum over ranks
-  e2e     the same through psk_host_call with pinned HOST buffers: the host-to-device
-          copy of the ids and labels and the device-to-host read of the loss are
-          inside the timed region of every step
+  e2e     the same through the C ABI with pinned HOST buffers: the host-to-device
+          copy of the ids and labels, the gather of the loss over the ranks (one
+          all-reduce) and its device-to-host read are inside the timed region of
+          every step
   roofline  the tensor-core contraction kernel: its floating-point operations over its
           own time (events around every launch of the timed steps), against the
           measured cuBLAS bf16 rate of MEASURED_PEAKS.json
+  parity  a pre-flight outside the timed region: one layer of the workload's width
+          over the CUDA executor (the benchmark's realization) and over the CPU oracle
+          (sequential order), logits and loss compared; rank 0 only
   cpu_baseline  the CPU restatement of the same launches (oracle/, OpenMP over the
           host's cores) on a bounded sample, rank 0 and N = 1 only
 
-`--impl reference` times that CPU path alone, on the same metric.
+`--impl reference` times that CPU path alone, on the same metric, with one layer at
+the workload's own sequence length among its samples.
+
+`--workload` also takes the smaller configurations (the MLP classifier, the small
+GPT, the contraction-plus-LayerNorm sweep); each prints the same JSON shape.
 
 The batch axis is sharded over the ranks with no collective on the data path; the
-per-rank losses are summed with one NCCL all-reduce after the timed region.
+per-rank losses are combined with one all-reduce a step (`--comm psk`: the library's
+own psk_comm_* over NCCL on the executor's stream; `--comm torch`: torch.distributed).
 """
 import argparse
 import json
@@ -44,7 +53,15 @@ WORKLOADS = {
     "llama7b_e4m3w_prefill_b16_t1024": dict(consts=dict(V=32000, D=4096, H=32, G=32, FF=11008, L=32), B=16, T=1024, int8="e4m3fn"),
     # a small shape of the same program, for trying the script out
     "llama_small": dict(consts=dict(V=4096, D=1024, H=8, G=8, FF=2816, L=4), B=4, T=512),
+    # the 2-layer ReLU MLP classifier: Linear{784,256}, ReLU, Linear{256,10}, cross-entropy; batch 4096; all f32 (sequential order: the reference's bits)
+    "mlp_b4096": dict(kind="mlp", B=4096),
+    # the small GPT decoder: 4 layers, d 128, 4 heads, context 64, vocabulary 65, batch 256; a mixed bf16/f32 assignment
+    "gpt_l4_d128_b256_t64": dict(kind="gpt", consts=dict(V=65, D=128, H=4, L=4), B=256, T=64),
 }
+# x[N, N]·w[N, N] then a row LayerNorm, every site stored f16 or e8m15, computed in f32
+for _n in (1024, 4096, 8192):
+    for _dt in ("f16", "e8m15"):
+        WORKLOADS[f"contract_ln_{_n}_{_dt}"] = dict(kind="contract_ln", N=_n, dtype=_dt)
 
 
 QUANTISED = ("blocks.attn.wq", "blocks.attn.wk", "blocks.attn.wv", "blocks.attn.wo", "blocks.ff.gate.w", "blocks.ff.up.w", "blocks.ff.down.w")
@@ -126,10 +143,34 @@ class ClockSampler:
         return {"sm_mhz": int(statistics.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def cpu_prefill_tokens_per_s(consts, T, B, threads, int8=False):
-    """The CPU restatement on a bounded sample: one and two layers at a short sequence, one
-    batch row; the per-layer time and the rest extrapolate to the whole depth."""
+def time_call(fn, warmup=1, reps=3):
+    """The reference's timing protocol (presk-driver/src/bench.rs:28-48): untimed warm-up calls, then the
+    median of `reps` timed ones. Returns (median seconds, every timing)."""
+    for _ in range(warmup):
+        fn()
+    ts = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        fn()
+        ts.append(time.perf_counter() - t0)
+    return statistics.median(ts), ts
+
+
+def cpu_prefill_tokens_per_s(consts, T, B, threads, int8=False, direct=False, direct_budget_s=240.0):
+    """The CPU restatement of the prefill on a bounded sample of the workload, every timing a median of three
+    after a warm-up call:
+
+      * one and two layers of the full width at B = 1, T = 128: the per-layer time and the rest (embedding, final
+        norm, head, loss), both proportional to the number of tokens;
+      * the attention function at the workload's own T and at 128 on 16 heads of 128 (32 on a host of more than
+        16 threads): the part of a layer that grows with T squared, per head (every head does the same work on
+        its own [T, 128] operands);
+      * with `direct` (the reference arm): one layer of the full width at B = 1 and the workload's T, the whole
+        thing, so that attention's share at that length is measured and not modelled.
+
+    tokens/s of the whole depth = B·T / (B · (rest + L · layer)), every term scaled to T tokens."""
     sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import headline
     import oracle_lib
     from presk_b200 import Host
 
@@ -137,28 +178,74 @@ def cpu_prefill_tokens_per_s(consts, T, B, threads, int8=False):
     # set before the OpenMP runtime of the oracle's library is loaded
     os.environ["OMP_NUM_THREADS"] = str(threads)
     orc = oracle_lib.load()
-    times = {}
-    Ts, Bs = min(T, 128), 1
     rng = np.random.default_rng(0)
+    Ts = min(T, 128)
+    weights = "int8" if int8 is True else ("e4m3fn" if int8 == "e4m3fn" else "bf16")
+    fmt = lambda ts: "[" + ", ".join(f"{t:.2f}" for t in ts) + "]"
+
+    c2 = dict(consts, L=2)
+    p2 = headline.llama_params_f32(c2, seed=0)
+    ids = rng.integers(0, consts["V"], size=(1, Ts), dtype=np.int64)
+    y = rng.integers(0, consts["V"], size=(1, Ts), dtype=np.int64)
+    med, raw = {}, {}
+    hosts = {}
     for L in (1, 2):
         c = dict(consts, L=L)
-        shapes = param_shapes(c)
-        rz = realization(shapes, int8)
-        rz["order"] = {"kind": "sequential"}
-        h = Host(orc.vtable(), rz).prepare("llama", **c)
-        for path, (shape, std) in shapes.items():
-            h.set_param(path, np.ones(shape, np.float32) if std < 0 else (rng.standard_normal(shape, dtype=np.float32) * np.float32(std)))
-        ids = rng.integers(0, c["V"], size=(Bs, Ts), dtype=np.int64)
-        y = rng.integers(0, c["V"], size=(Bs, Ts), dtype=np.int64)
+        p = {k: (np.ascontiguousarray(v[:L]) if k.startswith("blocks.") else v) for k, v in p2.items()}
+        h = headline.give(Host(orc.vtable(), headline.realization(p, headline.ORACLE_ORDER, weights)).prepare("llama", **c), p)
+        med[L], raw[L] = time_call(lambda: h.call("loss", [ids, y], ()))
+        if L == 1 and direct:
+            hosts[1] = h
+        else:
+            h.close()
+    # the part of a layer that grows with T squared, per head: a few heads of 128 at T and at 128
+    # (as many heads as keep every thread busy: the oracle divides the (batch, head) loop over the threads)
+    hs = min(consts["H"], 32 if threads > 16 else 16)
+    ca = dict(V=64, D=128 * hs, H=hs, G=hs, FF=256, L=1)
+    pa = headline.llama_params_f32(ca, seed=1)
+    ha = headline.give(Host(orc.vtable(), headline.realization(pa, headline.ORACLE_ORDER)).prepare("llama", **ca), pa)
+    xa = {t: rng.standard_normal((1, t, ca["D"])).astype(np.float32) for t in {Ts, T}}
+    att = {t: time_call(lambda t=t: ha.call("attention", [xa[t]], (1, t, ca["D"]))) for t in sorted(xa)}
+    ha.close()
+    if T > Ts:
+        quad_head = max((att[T][0] - att[Ts][0] * (T / Ts)) / ((T * T - T * Ts) * ca["H"]), 0.0)  # seconds a head a (token pair)
+    else:
+        quad_head = 0.0
+    heads = consts["H"]
+    layer_s = max(med[2] - med[1], 1e-9)
+    rest_s = max(med[1] - layer_s, 0.0)
+    lin_layer_s = max(layer_s - heads * quad_head * Ts * Ts, 0.0)
+    up = T / Ts
+    layer_T_model = lin_layer_s * up + heads * quad_head * T * T
+    rest_T = rest_s * up
+    sample = (f"oracle (C restatement, OpenMP, {threads} threads), warm-up 1 + median of 3 each; B=1, T={Ts}: L=1 {fmt(raw[1])} s, L=2 {fmt(raw[2])} s"
+              f" => layer {layer_s:.2f} s, rest {rest_s:.2f} s; attention function on {hs} heads of 128: T={Ts} {fmt(att[Ts][1])} s"
+              + (f", T={T} {fmt(att[T][1])} s => {heads * quad_head * T * T:.1f} s a layer of {heads} heads at T={T}" if T > Ts else "")
+              + f"; modelled layer at T={T}: {layer_T_model:.1f} s")
+    layer_T = layer_T_model
+    if direct:
+        # one whole layer of the full width at the workload's own sequence length
+        idsT = rng.integers(0, consts["V"], size=(1, T), dtype=np.int64)
+        yT = rng.integers(0, consts["V"], size=(1, T), dtype=np.int64)
+        h1 = hosts[1]
+        t_start = time.perf_counter()
         t0 = time.perf_counter()
-        h.call("loss", [ids, y], ())
-        times[L] = time.perf_counter() - t0
-        h.close()
-    per_layer = max(times[2] - times[1], 1e-9)
-    rest = max(times[1] - per_layer, 0.0)
-    full = rest + consts["L"] * per_layer
-    sample = f"L=1 and L=2 at B={Bs}, T={Ts} ({times[1]:.2f} s, {times[2]:.2f} s); per layer {per_layer:.2f} s, extrapolated to L={consts['L']}; attention's T-dependent share is that of T={Ts}"
-    return Bs * Ts / full, sample
+        h1.call("loss", [idsT, yT], ())
+        warm = time.perf_counter() - t0
+        ts = []
+        while len(ts) < 3 and (time.perf_counter() - t_start) + warm <= direct_budget_s:
+            t0 = time.perf_counter()
+            h1.call("loss", [idsT, yT], ())
+            ts.append(time.perf_counter() - t0)
+        h1.close()
+        whole = statistics.median(ts) if ts else warm
+        layer_T = max(whole - rest_T, 1e-9)
+        sample += (f"; measured whole L=1, B=1, T={T}: warm-up {warm:.1f} s, timed {fmt(ts)} s"
+                   + ("" if ts else " (no timed call fitted the time limit: the warm-up call is used)")
+                   + f" => layer {layer_T:.1f} s (used)")
+    full = rest_T + consts["L"] * layer_T
+    sample += f"; extrapolated to L={consts['L']}: {full:.0f} s a sequence"
+    return T / full, sample
 
 
 def microbench(args):
@@ -317,6 +404,49 @@ def microbench(args):
         l.inputs[2].dtype, l.inputs[2].stride[1], l.inputs[2].numel = abi.BF16, 1, n
         ms = timed(lambda: ex.run(l, [x, root, gam, out]), args.steps)
         print(json.dumps({"micro": "norm", "shape": dims, "ms": ms, "GB/s": rows * n * 4 / ms / 1e6}))
+    elif args.micro == "rmsnorm":
+        # the merged RMSNorm launch: x[rows, n] bf16, f32 statistics, gamma[n]; --shape rows,n
+        rows, n = dims[:2]
+        x, gam = ex.upload(bf16((rows, n))), ex.upload(bf16((n,)))
+        eps = ex.upload(np.array([1e-5], np.float32))
+        out = ex.alloc(rows * n * 2)
+        l = launch_desc(abi.OP_RMSNORM, abi.BF16, [rows, n], order=abi.ORDER_DEVICE, name=b"rmsnorm[merged]")
+        l.n_inputs = 3
+        l.iparam[0], l.iparam[1], l.iparam[2], l.iparam[3] = n, abi.BF16, abi.F32, abi.F32
+        for o in (l.inputs[0], l.out):
+            o.dtype, o.stride[0], o.stride[1], o.numel = abi.BF16, n, 1, rows * n
+        l.inputs[1].dtype, l.inputs[1].numel = abi.F32, 1
+        l.inputs[2].dtype, l.inputs[2].stride[1], l.inputs[2].numel = abi.BF16, 1, n
+        ms = timed(lambda: ex.run(l, [x, eps, gam, out]), args.steps)
+        print(json.dumps({"micro": "rmsnorm", "shape": dims, "ms": ms, "GB/s": rows * n * 4 / ms / 1e6}))
+    elif args.micro == "rope":
+        # the merged rotation: x[rows, seq, 2, rot] bf16 with cos and sin over [seq, rot]; --shape rows,seq,rot
+        rows, seq, rot = dims[:3]
+        x, c, sn = ex.upload(bf16((rows, seq, 2, rot))), ex.upload(bf16((seq, rot))), ex.upload(bf16((seq, rot)))
+        n = rows * seq * 2 * rot
+        out = ex.alloc(n * 2)
+        l = launch_desc(abi.OP_ROPE, abi.BF16, [rows, seq, 2, rot], order=abi.ORDER_DEVICE, name=b"rope[merged]")
+        l.n_inputs = 3
+        for o in (l.inputs[0], l.out):
+            o.dtype, o.numel = abi.BF16, n
+            o.stride[0], o.stride[1], o.stride[2], o.stride[3] = seq * 2 * rot, 2 * rot, rot, 1
+        for o in (l.inputs[1], l.inputs[2]):
+            o.dtype, o.numel, o.stride[1], o.stride[3] = abi.BF16, seq * rot, rot, 1
+        ms = timed(lambda: ex.run(l, [x, c, sn, out]), args.steps)
+        print(json.dumps({"micro": "rope", "shape": dims, "ms": ms, "GB/s": n * 4 / ms / 1e6}))
+    elif args.micro == "xent":
+        # cross-entropy of f32 logits [rows, v] against labels, under the device order; --shape rows,v
+        rows, v = dims[:2]
+        x = ex.upload(rng.standard_normal((rows, v)).astype(np.float32))
+        y = ex.upload(rng.integers(0, v, size=(rows,), dtype=np.int64))
+        out = ex.alloc(rows * 4)
+        l = launch_desc(abi.OP_XENT, abi.F32, [rows], [v], order=abi.ORDER_DEVICE, name=b"cross_entropy")
+        l.n_inputs = 2
+        l.inputs[0].dtype, l.inputs[0].numel, l.inputs[0].stride[0], l.inputs[0].stride[1] = abi.F32, rows * v, v, 1
+        l.inputs[1].dtype, l.inputs[1].is_index, l.inputs[1].numel, l.inputs[1].stride[0] = abi.I64, 1, rows, 1
+        l.out.dtype, l.out.numel, l.out.stride[0] = abi.F32, rows, 1
+        ms = timed(lambda: ex.run(l, [x, y, out]), args.steps)
+        print(json.dumps({"micro": "xent", "shape": dims, "ms": ms, "GB/s": rows * v * 4 / ms / 1e6}))
     elif args.micro in ("softmax", "ew"):
         rows, n = dims[:2]
         x = ex.upload(bf16((rows, n)))
@@ -345,9 +475,168 @@ def microbench(args):
         print(json.dumps({"micro": args.micro, "shape": dims, "ms": ms, "GB/s": traffic / ms / 1e6}))
 
 
+def load_peaks():
+    try:
+        return json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except OSError:
+        return {}
+
+
+def profile_table(rows):
+    """{kernel family: [launches, ms, flops, algorithmic bytes]} of psk_exec_profile's rows."""
+    by = {}
+    for k, name, kms, fl, bts in rows:
+        d = by.setdefault(k, [0, 0.0, 0.0, 0.0])
+        d[0] += 1; d[1] += kms; d[2] += fl; d[3] += bts
+    return by
+
+
+def shares_of(by):
+    total = sum(d[1] for d in by.values()) or 1.0
+    return {k: {"launches": d[0], "ms": round(d[1], 3), "share": round(d[1] / total, 4), "GB/s": round(d[3] / (d[1] * 1e-3) / 1e9, 1) if d[1] > 0 else None} for k, d in sorted(by.items(), key=lambda kv: -kv[1][1])}
+
+
+# ---- the smaller configurations --------------------------------------------------------------------------------
+def small_case(name, w):
+    """(model, consts, realization, params, inputs of `entry`, entry, units a step, unit, flops a step) of a small workload."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import models
+    if w["kind"] == "mlp":
+        B = w["B"]
+        x, y = models.mlp_inputs(B)
+        return dict(model="mlp", consts={}, rz="f32", params=models.mlp_params(), inputs=[x, y], entry="loss", units=B, unit="samples/s",
+                    metric="samples/sec 2-layer ReLU MLP forward+loss", flops=2.0 * B * (784 * 256 + 256 * 10), dtype="f32", order="sequential")
+    if w["kind"] == "gpt":
+        c, B, T = w["consts"], w["B"], w["T"]
+        rng = np.random.default_rng(2)
+        ids = rng.integers(0, c["V"], size=(B, T), dtype=np.int64)
+        y = rng.integers(0, c["V"], size=(B, T), dtype=np.int64)
+        rz = {"default": "bf16", "order": {"kind": "device"}, "storage": {"LayerNorm.apply/%2": "f32", "LayerNorm.apply/%5": "f32", "LayerNorm.apply/%10": "f32", "GPT.apply/%24": "f32", "loss/%6": "f32", "loss/%7": "f32"}}
+        D, L, V = c["D"], c["L"], c["V"]
+        return dict(model="gpt", consts=c, rz=rz, params=models.gpt_params(c, T), inputs=[ids, y], entry="loss", units=B * T, unit="tokens/s",
+                    metric="tokens/sec small GPT forward+loss", flops=float(B * T) * (L * (24 * D * D + 4 * T * D) + 2 * D * V), dtype="bf16 storage, f32 accumulation", order="device")
+    n, dt = w["N"], w["dtype"]
+    rng = np.random.default_rng(n)
+    x = rng.standard_normal((n, n), dtype=np.float32)
+    wt = rng.standard_normal((n, n), dtype=np.float32)
+    return dict(model="contract_ln", consts={}, rz={"default": dt, "order": {"kind": "device"}}, params={"ln.γ": np.ones(n, np.float32), "ln.β": np.zeros(n, np.float32)}, inputs=[x, wt], entry="apply",
+                units=2.0 * n * n * n / 1e12, unit="TFLOP/s", metric=f"TFLOP/s (2·N^3) of x·w + row LayerNorm, N={n}, stored {dt}", flops=2.0 * n * n * n, dtype=f"{dt} storage, f32 accumulation", order="device", out_shape=(n, n))
+
+
+def small_cpu(case, w, threads):
+    """The CPU restatement on the same inputs at full size (a bounded part of the rows for the largest contraction)."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import models
+    import oracle_lib
+    from presk_b200 import Host
+    os.environ["OMP_NUM_THREADS"] = str(threads)
+    orc = oracle_lib.load()
+    rz = case["rz"] if isinstance(case["rz"], str) else dict(case["rz"], order={"kind": "sequential"})
+    h = models.give(Host(orc.vtable(), rz).prepare(case["model"], **case["consts"]), case["params"])
+    inputs, frac, note = case["inputs"], 1.0, "full size"
+    if w["kind"] == "contract_ln" and w["N"] > 4096:
+        rows = 1024  # every row of x is an independent 1/N of the work (its row of the product, its LayerNorm)
+        inputs = [np.ascontiguousarray(inputs[0][:rows]), inputs[1]]
+        frac, note = rows / w["N"], f"{rows} of the {w['N']} rows of x (rows are independent; time scaled by {w['N'] // rows})"
+    out_shape = case.get("out_shape", ())
+    if out_shape and frac < 1.0:
+        out_shape = (inputs[0].shape[0], out_shape[1])
+    med, raw = time_call(lambda: h.call(case["entry"], inputs, out_shape), warmup=1, reps=3)
+    h.close()
+    value = case["units"] / (med / frac)
+    return value, f"oracle (C restatement, OpenMP, {threads} threads), {note}; warm-up 1 + median of 3: [" + ", ".join(f"{t:.3f}" for t in raw) + "] s"
+
+
+def run_small(args, name, w):
+    threads = os.cpu_count() or 1
+    rank = int(os.environ.get("RANK", 0))
+    case = small_case(name, w)
+    config = {"workload": name, **{k: v for k, v in w.items() if k != "kind"}, "realization": case["rz"] if isinstance(case["rz"], str) else json.dumps(case["rz"], ensure_ascii=False), "l2": "flushed between timed steps (a 256 MB buffer is overwritten)", "parallelism": "replicas (one GPU holds the whole problem)"}
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        v, sample = small_cpu(case, w, threads)
+        print(json.dumps({"impl": "reference", "metric": case["metric"], "value": v, "unit": case["unit"], "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * case["units"] / v,
+                          "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": case["dtype"], "data": "synthetic", "config": config,
+                          "cpu_baseline": {"value": v, "unit": case["unit"], "cores": threads, "kind": "port", "sample": sample}, "e2e": {"value": v, "unit": case["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        return
+    import torch
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import models
+    from presk_b200 import Executor, Host, abi
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    ex = Executor(local)
+    host = models.give(Host(ex, case["rz"]).prepare(case["model"], **case["consts"]), case["params"])
+    stream = torch.cuda.ExternalStream(ex.stream(), device=torch.device("cuda", local))
+    dev_inputs = []
+    for a in case["inputs"]:
+        dev_inputs.append((ex.upload(a), abi.I64 if a.dtype == np.int64 else abi.F32, a.shape))
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=f"cuda:{local}")
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
+        host.call_device(case["entry"], dev_inputs)
+    ex.sync()
+    _, k0 = ex.counts()
+    sampler = ClockSampler(local)
+    sampler.start()
+    ex.set_profiling(True)
+    ms = 0.0
+    evs = []
+    for _ in range(args.steps):
+        with torch.cuda.stream(stream):
+            flush.zero_()  # L2 holds nothing of the step before
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        host.call_device(case["entry"], dev_inputs)
+        e1.record(stream)
+        evs.append((e0, e1))
+    ex.sync()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = sum(a.elapsed_time(b) for a, b in evs)
+    rows = ex.profile()
+    ex.set_profiling(False)
+    _, k1 = ex.counts()
+    # end to end: host arrays in, the result read back, every step
+    out_shape = case.get("out_shape", ())
+    for _ in range(2):
+        host.call(case["entry"], case["inputs"], out_shape)
+    ex.sync()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        res = host.call(case["entry"], case["inputs"], out_shape)
+    ex.sync()
+    e2e_s = time.perf_counter() - t0
+    by = profile_table(rows)
+    peaks = load_peaks()
+    hbm_peak = peaks.get("hbm_gbs") or 6650.0
+    tf_peak = peaks.get("bf16_tflops") or 1590.0
+    top = max(by.items(), key=lambda kv: kv[1][1]) if by else ("none", [0, 0.0, 0.0, 0.0])
+    if top[0] == "k_gemm_tc":
+        ach = top[1][2] / (top[1][1] * 1e-3) / 1e12
+        roof = {"bound": "tensor", "kernel": top[0], "achieved": ach, "peak": tf_peak, "unit": "TFLOP/s", "frac": ach / tf_peak, "traffic": None}
+    else:
+        ach = top[1][3] / (top[1][1] * 1e-3) / 1e9 if top[1][1] > 0 else 0.0
+        roof = {"bound": "hbm", "kernel": top[0], "achieved": ach, "peak": hbm_peak, "unit": "GB/s", "frac": ach / hbm_peak, "traffic": None}
+    roof["peak_source"] = "measured (MEASURED_PEAKS.json: copy bandwidth, burst cuBLAS bf16)" if peaks else "fallback"
+    roof["note"] = "algorithmic work of the kernel family with the largest share of the step, over its event-timed launches"
+    out = {"metric": case["metric"], "value": case["units"] * args.steps / (ms * 1e-3), "unit": case["unit"], "n_gpus": 1, "steps": args.steps, "warmup": warm, "ms_per_step": ms / args.steps,
+           "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": case["dtype"], "data": "synthetic", "config": config,
+           "e2e": {"value": case["units"] * args.steps / e2e_s, "unit": case["unit"], "h2d_bytes_per_step": int(sum(a.nbytes for a in case["inputs"])), "d2h_bytes_per_step": int(np.asarray(res).nbytes)},
+           "gpu_launches": int(k1 - k0), "clocks": clocks, "roofline": roof, "kernel_shares": shares_of(by), "model_tflops": case["flops"] * args.steps / (ms * 1e-3) / 1e12}
+    if not args.no_cpu_baseline:
+        try:
+            v, sample = small_cpu(case, w, threads)
+            out["cpu_baseline"] = {"value": v, "unit": case["unit"], "cores": threads, "kind": "port", "sample": sample}
+        except Exception as e:  # the baseline is reported, never the product's path
+            out["cpu_baseline"] = {"value": None, "unit": case["unit"], "cores": threads, "kind": "port", "sample": f"failed: {e}"}
+    print(json.dumps(out, ensure_ascii=False))
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--micro", default=None, choices=["gemm", "softmax", "ew", "attn", "norm", "e8m15", "f32c", "train"])
+    ap.add_argument("--micro", default=None, choices=["gemm", "softmax", "ew", "attn", "norm", "e8m15", "f32c", "train", "rmsnorm", "rope", "xent"])
     ap.add_argument("--shape", default="8192,8192,8192")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
@@ -356,12 +645,16 @@ def main():
     ap.add_argument("--workload", default="llama7b_prefill_b8_t2048", choices=sorted(WORKLOADS))
     ap.add_argument("--attention", default="blockwise", choices=["blockwise", "unfused"], help="the declared order of the attention launches: one blockwise kernel, or the reference's four launches")
     ap.add_argument("--launches", default="merged", choices=["merged", "reference"], help="merged: bit-preserving rewrites of the launch list (views for slices, in-place concatenation, wider groups); reference: the reference's launch list")
+    ap.add_argument("--comm", default="psk", choices=["psk", "torch"], help="what carries the loss gather of a sharded run: the library's psk_comm_* (NCCL on the executor's stream) or torch.distributed")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-parity", action="store_true", help="skip the parity pre-flight against the CPU oracle")
     ap.add_argument("--dump-profile", default=None, help="write the per-launch-name times of the timed steps to this file")
     args = ap.parse_args()
     if args.micro:
         return microbench(args)
     w = WORKLOADS[args.workload]
+    if w.get("kind", "llama") != "llama":
+        return run_small(args, args.workload, w)
     consts, B, T = w["consts"], w["B"], w["T"]
     rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
     threads = os.cpu_count() or 1
@@ -370,29 +663,43 @@ def main():
     if args.impl == "reference":
         if rank != 0:
             return
-        vals = []
-        sample = ""
-        for _ in range(max(1, min(args.steps, 2))):
-            v, sample = cpu_prefill_tokens_per_s(consts, T, B, threads, w.get("int8", False))
-            vals.append(v)
-        v = statistics.median(vals)
+        v, sample = cpu_prefill_tokens_per_s(consts, T, B, threads, w.get("int8", False), direct=True)
         print(json.dumps({
             "impl": "reference", "metric": "tokens/sec Llama-7B-shape prefill", "value": v, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": 1e3 * B * T / v, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 storage, f32 arithmetic", "data": "synthetic",
             "config": config, "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
             "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-            "note": "the reference's Rust executors cannot be built on this box (no cargo/rustc); this is the C restatement of the same loop nests (oracle/), OpenMP over the host's cores",
+            "note": "the reference's Rust executors cannot be built on this box (no cargo/rustc); this is the C restatement of the same loop nests (oracle/), OpenMP over the host's cores; a step is a bounded sample (one layer of the full width at the workload's sequence length, one sequence) and ms_per_step is the extrapolation to the whole depth and batch",
         }))
         return
 
     import torch
     import torch.distributed as dist
-    from presk_b200 import Executor, Host, abi
+    from presk_b200 import Comm, Executor, Host, abi, shard
 
     torch.cuda.set_device(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     ex = Executor(local)
+    comm, comm_kind = None, "none (one rank)"
+    if world > 1:
+        comm_kind = "torch.distributed (NCCL)"
+        if args.comm == "psk":
+            # rank 0 makes the communicator's id; the others get it over the process group that started them
+            box = [Comm.unique_id() if rank == 0 else None]
+            dist.broadcast_object_list(box, src=0)
+            try:
+                comm = Comm(ex, world, rank, box[0])
+                comm_kind = "psk_comm (NCCL on the executor's stream)"
+            except Exception as e:  # reported in the line; the gather then goes through torch.distributed
+                comm_kind = f"torch.distributed (psk_comm could not be made: {e})"
+            # every rank must take the same route
+            flags = torch.tensor([1.0 if comm is not None else 0.0], device="cuda")
+            dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+            if float(flags[0]) == 0.0 and comm is not None:
+                comm.close()
+                comm = None
+                comm_kind = "torch.distributed (psk_comm failed on another rank)"
     shapes = param_shapes(consts)
     host = Host(ex, realization(shapes, w.get("int8", False), args.attention, args.launches)).prepare("llama", **consts)
     for i, (path, (shape, std)) in enumerate(shapes.items()):
@@ -437,76 +744,101 @@ def main():
     rows = ex.profile()
     ex.set_profiling(False)
     launches_after, kernels_after = ex.counts()
-    loss = float(np.frombuffer(ex.download(out_ptr, 4).tobytes(), dtype=np.float32)[0])
 
-    # ---- e2e: host buffers in, loss out, every step ----
+    # ---- e2e: host buffers in, the loss of the whole batch out, every step ----
+    def step_e2e():
+        if comm is not None:
+            # all through the C ABI: two copies from pinned host memory, the launches, one all-reduce of the
+            # per-rank mean on the executor's stream, the result read back
+            ex._check(ex.lib.psk_exec_upload(ex.handle, ids_dev, ids_np.ctypes.data, ids_np.nbytes))
+            ex._check(ex.lib.psk_exec_upload(ex.handle, y_dev, y_np.ctypes.data, y_np.nbytes))
+            ptr, dt, _ = host.call_device("loss", dev_inputs)
+            return host.mean_over_ranks(comm, ptr, dt)
+        mine = float(host.call("loss", [ids_np, y_np], ()))
+        return shard.combine_mean(mine, B * T, device="cuda") if world > 1 else mine
+
     for _ in range(2):
-        host.call("loss", [ids_np, y_np], ())
+        step_e2e()
     barrier()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        host.call("loss", [ids_np, y_np], ())
+        loss_all = step_e2e()
     barrier()
     e2e_s = time.perf_counter() - t0
 
-    from presk_b200 import shard
     ms = shard.max_over_ranks(ms, device="cuda")
     e2e_ms = shard.max_over_ranks(e2e_s * 1e3, device="cuda")
-    loss_all = shard.combine_mean(loss, B * T, device="cuda")  # the final loss gather: one all-reduce
     tokens = B * T * world * args.steps
     value = tokens / (ms * 1e-3)
     e2e = tokens / (e2e_ms * 1e-3)
-
-    if rank == 0:
-        peaks = {}
-        try:
-            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-        except OSError:
-            pass
-        tf_peak = peaks.get("bf16_tflops_sustained") or 1400.0
-        hbm_peak = peaks.get("hbm_gbs") or 6650.0
-        peak_kind = "measured (MEASURED_PEAKS.json, sustained cuBLAS bf16)" if peaks else "fallback"
-        by = {}
-        for k, name, kms, fl, bts in rows:
-            d = by.setdefault(k, [0, 0.0, 0.0, 0.0])
-            d[0] += 1; d[1] += kms; d[2] += fl; d[3] += bts
-        total_kernel_ms = sum(d[1] for d in by.values()) or 1.0
-        if args.dump_profile:
-            names = {}
-            for k, name, kms, fl, bts in rows:
-                # launches of one name and different sizes (a norm's scalar root and its scaling of a whole tensor) apart
-                d = names.setdefault(k + " | " + name + f" | {bts / 1e6:.1f} MB", [0, 0.0, 0.0, 0.0])
-                d[0] += 1; d[1] += kms; d[2] += fl; d[3] += bts
-            with open(args.dump_profile, "w") as f:
-                f.write("kernel | launch name | algorithmic bytes a launch\tlaunches\ttotal ms\tshare\tms/launch\tGB/s (algorithmic)\tTFLOP/s\n")
-                for key, d in sorted(names.items(), key=lambda kv: -kv[1][1]):
-                    f.write(f"{key}\t{d[0]}\t{d[1]:.3f}\t{d[1] / total_kernel_ms:.4f}\t{d[1] / d[0]:.4f}\t{d[3] / (d[1] * 1e-3) / 1e9:.1f}\t{d[2] / (d[1] * 1e-3) / 1e12:.1f}\n")
-        tc = by.get("k_gemm_tc", [0, 0.0, 0.0, 0.0])
-        achieved = tc[2] / (tc[1] * 1e-3) / 1e12 if tc[1] > 0 else 0.0
-        shares = {k: {"launches": d[0], "ms": round(d[1], 3), "share": round(d[1] / total_kernel_ms, 4), "GB/s": round(d[3] / (d[1] * 1e-3) / 1e9, 1) if d[1] > 0 else None} for k, d in sorted(by.items(), key=lambda kv: -kv[1][1])}
-        out = {
-            "metric": "tokens/sec Llama-7B-shape prefill", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 storage, f32 accumulation", "data": "synthetic",
-            "config": config,
-            "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": int(ids_np.nbytes + y_np.nbytes), "d2h_bytes_per_step": 4},
-            "gpu_launches": int(kernels_after - kernels_before),
-            "clocks": clocks,
-            "roofline": {"bound": "tensor", "kernel": "k_gemm_tc", "achieved": achieved, "peak": tf_peak, "unit": "TFLOP/s", "frac": achieved / tf_peak, "traffic": GEMM_TRAFFIC.get(args.workload), "traffic_of": GEMM_TRAFFIC_OF if args.workload in GEMM_TRAFFIC else None, "peak_source": peak_kind,
-                         "model_tflops": flops_per_token(consts, T) * B * T * args.steps / (ms * 1e-3) / 1e12, "hbm_peak_gbs": hbm_peak},
-            "kernel_shares": shares,
-            "loss": loss_all,
-            "launches_per_step": int((launches_after - launches_before) / args.steps),
-        }
-        if world == 1 and not args.no_cpu_baseline:
-            try:
-                v, sample = cpu_prefill_tokens_per_s(consts, T, B, threads, w.get("int8", False))
-                out["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample}
-            except Exception as e:  # the baseline is reported, never the product's path
-                out["cpu_baseline"] = {"value": None, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": f"failed: {e}"}
-        print(json.dumps(out))
+    if comm is not None:
+        comm.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if rank != 0:
+        return
+
+    peaks = load_peaks()
+    tf_peak = peaks.get("bf16_tflops_sustained") or 1400.0
+    hbm_peak = peaks.get("hbm_gbs") or 6650.0
+    peak_kind = "measured (MEASURED_PEAKS.json, sustained cuBLAS bf16)" if peaks else "fallback"
+    by = profile_table(rows)
+    total_kernel_ms = sum(d[1] for d in by.values()) or 1.0
+    if args.dump_profile:
+        names = {}
+        for k, name, kms, fl, bts in rows:
+            # launches of one name and different sizes (a norm's scalar root and its scaling of a whole tensor) apart
+            d = names.setdefault(k + " | " + name + f" | {bts / 1e6:.1f} MB", [0, 0.0, 0.0, 0.0])
+            d[0] += 1; d[1] += kms; d[2] += fl; d[3] += bts
+        with open(args.dump_profile, "w") as f:
+            f.write("kernel | launch name | algorithmic bytes a launch\tlaunches\ttotal ms\tshare\tms/launch\tGB/s (algorithmic)\tTFLOP/s\n")
+            for key, d in sorted(names.items(), key=lambda kv: -kv[1][1]):
+                f.write(f"{key}\t{d[0]}\t{d[1]:.3f}\t{d[1] / total_kernel_ms:.4f}\t{d[1] / d[0]:.4f}\t{d[3] / (d[1] * 1e-3) / 1e9:.1f}\t{d[2] / (d[1] * 1e-3) / 1e12:.1f}\n")
+    tc = by.get("k_gemm_tc", [0, 0.0, 0.0, 0.0])
+    achieved = tc[2] / (tc[1] * 1e-3) / 1e12 if tc[1] > 0 else 0.0
+    out = {
+        "metric": "tokens/sec Llama-7B-shape prefill", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 storage, f32 accumulation", "data": "synthetic",
+        "config": config,
+        "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": int(ids_np.nbytes + y_np.nbytes), "d2h_bytes_per_step": 8 if comm is not None else 4, "loss_gather": comm_kind},
+        "gpu_launches": int(kernels_after - kernels_before),
+        "clocks": clocks,
+        "roofline": {"bound": "tensor", "kernel": "k_gemm_tc", "achieved": achieved, "peak": tf_peak, "unit": "TFLOP/s", "frac": achieved / tf_peak, "traffic": GEMM_TRAFFIC.get(args.workload), "traffic_of": GEMM_TRAFFIC_OF if args.workload in GEMM_TRAFFIC else None, "peak_source": peak_kind,
+                     "model_tflops": flops_per_token(consts, T) * B * T * args.steps / (ms * 1e-3) / 1e12, "hbm_peak_gbs": hbm_peak},
+        "kernel_shares": shares_of(by),
+        "loss": loss_all,
+        "launches_per_step": int((launches_after - launches_before) / args.steps),
+    }
+    if not args.no_parity:
+        out["parity"] = parity_preflight(ex, consts, w.get("int8", False))
+    if world == 1 and not args.no_cpu_baseline:
+        try:
+            v, sample = cpu_prefill_tokens_per_s(consts, T, B, threads, w.get("int8", False))
+            out["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample}
+        except Exception as e:  # the baseline is reported, never the product's path
+            out["cpu_baseline"] = {"value": None, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": f"failed: {e}"}
+    print(json.dumps(out, ensure_ascii=False))
+
+
+def parity_preflight(ex, consts, int8):
+    """Outside every timed region: one layer of the workload's own width (and its vocabulary) at B = 1, T = 256
+    over the CUDA executor under the benchmark's realization and over the CPU oracle under the sequential order
+    with the reference's launch list; the oracle is the checker. The largest difference of the logits against
+    their scale, and both losses."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    try:
+        import headline
+        import oracle_lib
+        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
+        weights = "int8" if int8 is True else ("e4m3fn" if int8 == "e4m3fn" else "bf16")
+        r = headline.llama_width_parity(ex, oracle_lib.load(), B=1, T=256, weights=weights, consts={k: v for k, v in consts.items() if k != "L"})
+        tol = headline.LOGITS_TOL * (2.0 if weights != "bf16" else 1.0) * r["logits_scale"]
+        ok = r["finite"] and r["logits_max_err"] <= tol and abs(r["loss_gpu"] - r["loss_oracle"]) <= headline.LOSS_RTOL * abs(r["loss_oracle"])
+        return {"ok": bool(ok), "max_err": r["logits_max_err"], "tol": tol, "mean_err": r["logits_mean_err"], "logits_scale": r["logits_scale"], "loss_gpu": r["loss_gpu"], "loss_oracle": r["loss_oracle"], "loss_rtol": headline.LOSS_RTOL,
+                "shape": r["shape"], "against": "CPU oracle, order sequential, the reference's launch list; the GPU side runs the benchmark's realization (device order, blockwise attention, merged launches)"}
+    except Exception as e:
+        return {"ok": False, "error": str(e)}
 
 
 if __name__ == "__main__":

@@ -1,0 +1,97 @@
+"""The benchmark's own widths, at sizes the CPU oracle finishes in seconds.
+
+The throughput number is quoted on a Llama-7B-shaped prefill (d 4096, 32 heads of 128, SwiGLU 11008,
+vocabulary 32000, 32 layers, sequence 2048). The oracle cannot run that whole, but it runs one layer of that
+width on a short sequence; the functions here build such a case once and run it over both executors, for
+tests/test_gpu_headline.py and for bench.py's parity pre-flight (outside its timed region; the oracle is the
+checker there, never the thing measured).
+
+TEST INFRASTRUCTURE: nothing under presk_b200/ imports this module.
+"""
+import numpy as np
+
+WIDTH_7B = dict(V=32000, D=4096, H=32, G=32, FF=11008)
+QUANTISED = ("blocks.attn.wq", "blocks.attn.wk", "blocks.attn.wv", "blocks.attn.wo", "blocks.ff.gate.w", "blocks.ff.up.w", "blocks.ff.down.w")
+F32_SITES = {"RMSNorm.apply/%3": "f32", "RMSNorm.apply/%7": "f32", "Llama.apply/%11": "f32", "loss/%5": "f32", "loss/%6": "f32"}
+
+
+def llama_params_f32(c, seed=0, std=0.02):
+    """normal(0, std) weights and unit norms, drawn in float32 (a 7B-wide layer is half a billion numbers)."""
+    rng = np.random.default_rng(seed)
+    V, D, FF, L, H = c["V"], c["D"], c["FF"], c["L"], c["H"]
+    G = c.get("G", H)
+    HD = D // H
+
+    def n(*s):
+        a = rng.standard_normal(s, dtype=np.float32)
+        a *= np.float32(std)
+        return a
+
+    return {
+        "tok": n(V, D), "head": n(D, V), "norm.γ": np.ones(D, np.float32),
+        "blocks.n1.γ": np.ones((L, D), np.float32), "blocks.n2.γ": np.ones((L, D), np.float32),
+        "blocks.attn.wq": n(L, D, D), "blocks.attn.wk": n(L, D, G * HD), "blocks.attn.wv": n(L, D, G * HD), "blocks.attn.wo": n(L, D, D),
+        "blocks.ff.gate.w": n(L, D, FF), "blocks.ff.up.w": n(L, D, FF), "blocks.ff.down.w": n(L, FF, D),
+    }
+
+
+def realization(paths, order, weights="bf16"):
+    """The benchmark's realization (bf16 sites, f32 norm statistics, logits and loss) under `order`;
+    `weights`: "bf16", "int8" (a `quant` entry a projection) or "e4m3fn" (a `params` entry)."""
+    rz = {"default": "bf16", "order": order, "storage": dict(F32_SITES)}
+    rz["params"] = {p: ("e4m3fn" if weights == "e4m3fn" and p in QUANTISED else "bf16") for p in paths if not (weights == "int8" and p in QUANTISED)}
+    if weights == "int8":
+        rz["quant"] = {p: {"bits": 8, "over": -2} for p in QUANTISED}
+    return rz
+
+
+BENCH_ORDER = {"kind": "device", "attention": "blockwise", "launches": "merged"}
+ORACLE_ORDER = {"kind": "sequential"}
+
+
+def give(host, params):
+    for k, v in params.items():
+        host.set_param(k, v)
+    return host
+
+
+def llama_width_parity(cuda_executor, oracle, B=1, T=256, weights="bf16", consts=None, seed=0, want_loss=True, params=None):
+    """One layer of the 7B width over both executors: the CUDA one under the benchmark's order (tensor-core
+    contractions, the blockwise attention kernel, merged launches), the oracle under the sequential order with
+    the reference's launch list. Returns a dict with the logits' largest difference, their scale, and both losses."""
+    from presk_b200 import Host
+    c = dict(consts or WIDTH_7B, L=1)
+    p = params if params is not None else llama_params_f32(c, seed)
+    rng = np.random.default_rng(seed + 1)
+    ids = rng.integers(0, c["V"], size=(B, T), dtype=np.int64)
+    y = rng.integers(0, c["V"], size=(B, T), dtype=np.int64)
+    out = {"shape": f"llama L=1 V={c['V']} D={c['D']} H={c['H']} G={c['G']} FF={c['FF']} B={B} T={T}, weights {weights}"}
+    res = {}
+    for name, ex, order in (("gpu", cuda_executor, BENCH_ORDER), ("oracle", oracle.vtable(), ORACLE_ORDER)):
+        h = give(Host(ex, realization(p, order, weights)).prepare("llama", **c), p)
+        if name == "gpu":
+            h.set_logging(True)
+        logits = h.call("apply", [ids], (B, T, c["V"]))
+        loss = float(h.call("loss", [ids, y], ())) if want_loss else None
+        if name == "gpu":
+            out["gpu_launch_log"] = h.launch_log()
+        res[name] = (logits, loss)
+        h.close()
+    (lg, ls), (lw, lsw) = res["gpu"], res["oracle"]
+    out["logits_max_err"] = float(np.abs(lg - lw).max())
+    out["logits_scale"] = float(np.abs(lw).max())
+    out["logits_mean_err"] = float(np.abs(lg - lw).mean())
+    out["finite"] = bool(np.isfinite(lg).all())
+    out["loss_gpu"], out["loss_oracle"] = ls, lsw
+    return out
+
+
+# What the comparison above may differ by, and why it is stated against the tensor's scale and not entry by entry:
+# a logit is a sum of 4096 products of mixed sign, so an entry near zero carries the same absolute error as the
+# largest one (cancellation), and a per-entry relative bound would be violated by design. Every bf16 site rounds to
+# 2^-9 relative; sums reordered on the tensor cores move an element of a site to the neighbouring bf16 number now and
+# then, and one layer plus the head passes about ten such sites: 2^-6 of the logits' scale bounds the largest entry,
+# and the mean error stays below 2^-9 of it.
+LOGITS_TOL = 2.0**-6
+LOGITS_MEAN_TOL = 2.0**-9
+LOSS_RTOL = 2e-3
