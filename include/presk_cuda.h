@@ -368,6 +368,23 @@ int32_t psk_comm_size(const psk_comm *c);
 int psk_comm_allreduce(psk_comm *c, void *device_buf, int64_t count, int32_t dtype, int32_t op);
 
 /* ---------------------------------------------------------------------------
+ * From the reference's kernel to a launch. `KernelExec::run` receives `(idx, &Kernel, inputs, out)`
+ * (crates/presk-kernel/src/host.rs:30), and a `Kernel` prints itself as text (its `Display`,
+ * crates/presk-kernel/src/ir.rs:495-596): `kernel NAME (%0 : T[..], ..) -> %N : T[..] { loop nest }`. This reads
+ * the first kernel of `kernel_text` and fills `*out` with the launch that computes it: the iteration space, each
+ * buffer's element strides in it, the steps of an elementwise group. The pointer table of psk_exec_run is then
+ * the kernel's inputs in order, its output, and the scales of each `intB/OVER` input.
+ *
+ * Recognised by structure: a perfect nest around one store (PSK_OP_FUSED, PSK_OP_COPY); sums kept in a scalar or
+ * in the output over the loops that do not index the output (PSK_OP_CONTRACT, PSK_OP_REDUCE). Recognised by name
+ * and buffers, the body's layout being free: `dot` in any tiling, `softmax axis A [where]`, `cross_entropy`,
+ * `argmax`, `embed`. Anything else is refused with PSK_E7005 and a message in `err`; text that is not the
+ * grammar, with PSK_E7001. `order` is the psk_order to run it under (the nest itself states the sequential one).
+ * `name` (may be NULL) receives the kernel's name, which `out->name` then points at; `*rest` (may be NULL) is
+ * left after the kernel read, for a listing of several. */
+int psk_describe(const char *kernel_text, int32_t order, psk_launch *out, char *name, size_t name_cap, const char **rest, char *err, size_t err_cap);
+
+/* ---------------------------------------------------------------------------
  * The executor as a table of functions, so that the host program can run
  * over another one (KernelBackend::with_exec, host.rs:466). The library's
  * own is the CUDA executor; tests hand the host a CPU one.

@@ -304,6 +304,26 @@ class Host:
         return self.lib.psk_host_launch_log(self.handle).decode().splitlines()
 
 
+def describe(kernel_text, order=abi.ORDER_SEQUENTIAL):
+    """`psk_describe` on every kernel of a listing in the reference's text form: [(name, psk_launch)].
+    The launches keep their names alive (each holds a pointer into its own buffer)."""
+    lib = abi.load()
+    out = []
+    text = kernel_text.encode() if isinstance(kernel_text, str) else kernel_text
+    while b"kernel " in text:
+        l = abi.Launch()
+        name = C.create_string_buffer(256)
+        err = C.create_string_buffer(512)
+        rest = C.c_char_p()
+        rc = lib.psk_describe(text, order, C.byref(l), name, 256, C.byref(rest), err, 512)
+        if rc != abi.OK:
+            raise PreskError(rc, err.value.decode())
+        l._name_keep = name
+        out.append((name.value.decode(), l))
+        text = rest.value or b""
+    return out
+
+
 def launch_desc(op, dtype, dims_outer, dims_inner=(), order=abi.ORDER_SEQUENTIAL, name=b"launch"):
     """An empty `psk_launch` over an iteration space; the caller fills the operands."""
     l = abi.Launch()

@@ -8,6 +8,9 @@ Sources (paths within presk-lang/presk, read as text):
   tests/run/stack_grad.snap                             seed-0 gradient of examples/tests/data/stack_grad.psk `loss_grad` at B = 2
   tests/run/concat_loss.snap, concat_loss_grad.snap     seed-0 loss and gradient of examples/spec/concat/concat.psk at B = 2, T = 8
   crates/presk-interp/src/key.rs:86-93                  the first four normal draws of the key seed 0 names
+  crates/presk-kernel/tests/snapshots/conformance__linear_kernels.snap
+                                                        the kernel text of a row-wise `dot` and an `add` (what an executor is handed)
+  tests/run/minigpt_forward.snap, minigpt_loss.snap      seed-0 logits (all zero: the head is initialised to zeros) and loss of MiniGPT
 Run:  python tests/golden/make_golden.py <path of the reference's tree>
 """
 import json
@@ -65,6 +68,15 @@ m = re.search(r"assert_eq!\(first, \[([^\]]+)\]\)", key_rs)
 out["seed0_first_normals_bits"] = [int(x.strip(), 16) for x in m.group(1).split(",")]
 m = re.search(r"assert_eq!\(fold, (0x[0-9a-f]+)\)", key_rs)
 out["seed0_next_100000_fnv"] = int(m.group(1), 16)
+text = open(os.path.join(ref, "crates", "presk-kernel", "tests", "snapshots", "conformance__linear_kernels.snap")).read()
+out["linear_kernels_text"] = text.split("---")[-1].lstrip("\n")
+text = open(os.path.join(ref, "tests", "run", "minigpt_forward.snap")).read().split("---")[-1]
+m = re.search(r"\[batch: (\d+), seq: (\d+), (\d+)\] (\[\[\[.*\]\]\])", text)
+vals = json.loads(m.group(4))
+flat = [x for b in vals for t in b for x in t]
+out["minigpt_forward"] = {"shape": [int(m.group(1)), int(m.group(2)), int(m.group(3))], "all_equal_to": flat[0], "distinct": len(set(flat))}
+text = open(os.path.join(ref, "tests", "run", "minigpt_loss.snap")).read().split("---")[-1]
+out["minigpt_loss"] = float(re.search(r"= ([-0-9.e]+)", text).group(1))
 with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_vectors.json"), "w") as f:
     json.dump(out, f, indent=1)
 print("wrote", list(out))
