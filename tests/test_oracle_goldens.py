@@ -15,6 +15,7 @@ import os
 import numpy as np
 import pytest
 
+import models
 from presk_b200 import Host, abi
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -212,3 +213,25 @@ def test_stack_grad_golden_on_the_oracle(oracle, ref):
         return np.mean(y * y)
     got_loss = float(h.call("loss", [x, scale], (), np.float32))
     assert abs(got_loss - loss_at(w)) <= 2e-6 * abs(loss_at(w))
+
+
+def test_minigpt_zero_head_goldens_on_the_oracle(oracle):
+    """tests/run/minigpt_forward.snap and minigpt_loss.snap (examples/spec/minigpt, V = 64, D = 16, H = 2, L = 2,
+    B = 2, T = 8, seed 0): MiniGPT's head is initialised to zeros, so every logit is exactly 0 and the loss is ln 64
+    whatever the other parameters are. The host's GPT (examples/corpus/nlp/05_gpt.psk, the same decoder with learned
+    positions) under the same constants and a zero head must give the same two values: what this pins is the head
+    contraction on exact zeros, cross_entropy's `ln z + m - x[y]` and the mean, not the key derivation."""
+    g = GOLD["minigpt_forward"]
+    assert g["all_equal_to"] == 0 and g["distinct"] == 1
+    c = dict(V=64, D=16, H=2, L=2)
+    b, t, v = g["shape"]
+    p = models.gpt_params(c, t)
+    p["head"] = np.zeros_like(p["head"])
+    rng = np.random.default_rng(0)
+    ids = rng.integers(0, c["V"], size=(b, t), dtype=np.int64)
+    y = rng.integers(0, c["V"], size=(b, t), dtype=np.int64)
+    h = models.give(Host(oracle.vtable(), "f32").prepare("gpt", **c), p)
+    logits = h.call("apply", [ids], (b, t, v))
+    assert np.all(logits == 0.0)
+    loss = float(h.call("loss", [ids, y], ()))
+    assert abs(loss - GOLD["minigpt_loss"]) <= 1e-6
