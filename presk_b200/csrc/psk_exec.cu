@@ -23,6 +23,7 @@
 #include "psk_kernels.cuh"
 #include "psk_hot.cuh"
 #include "psk_attn.cuh"
+#include "psk_gemm_i8.cuh"
 
 using namespace psk;
 
@@ -69,6 +70,7 @@ struct psk_exec {
     bool tc_attr_set = false;
     bool softmax_attr_set = false;
     bool attn_attr_set = false;
+    bool i8_attr_set = false;
     uint16_t *silu_table = nullptr; // silu of every bf16 code, computed once by the device's own exact function
 };
 
@@ -393,6 +395,77 @@ int launch_tc(psk_exec *e, const psk_gemm &g, const void *a, const void *b, void
     else if (mt_rows == 2) tc::k_gemm_tc<256, false, 2><<<grid, tc::THREADS, tc::Smem<256, 2>::TOTAL, e->stream>>>(ma, mb, P);
     else if (bn == 256) tc::k_gemm_tc<256><<<grid, tc::THREADS, tc::Smem<256>::TOTAL, e->stream>>>(ma, mb, P);
     else tc::k_gemm_tc<128><<<grid, tc::THREADS, tc::Smem<128>::TOTAL, e->stream>>>(ma, mb, P);
+    CUDA_TRY(e, cudaGetLastError());
+    e->kernels += 1;
+    return PSK_OK;
+}
+
+// A tensor map over 8-bit codes: dimensions and strides in elements (= bytes).
+bool make_map_u8(psk_exec *e, CUtensorMap *map, const void *base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t d3, uint64_t s1, uint64_t s2, uint64_t s3, uint32_t box0, uint32_t box1)
+{
+    cuuint64_t dims[4] = {d0, d1, d2, d3};
+    cuuint64_t strides[3] = {s1, s2, s3};
+    for (int i = 0; i < 3; ++i) {
+        if (dims[i + 1] == 1 && strides[i] == 0) strides[i] = (i == 0 ? (d0 + 15) / 16 * 16 : strides[i - 1] * dims[i]);
+        if (strides[i] % 16 != 0 || strides[i] == 0) return false;
+    }
+    cuuint32_t box[4] = {box0, box1, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = e->encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+// The integer-sum contraction on the tensor cores (psk_gemm_i8.cuh). PSK_E7001: strides no tensor map takes
+// (the caller then runs the scalar kernel).
+int launch_i8(psk_exec *e, const GemmMap &g, const DevOperand &A, const DevOperand &B, const DevOperand &O, const psk_operand &out_desc, uint32_t *flag, bool guarded)
+{
+    if (!e->encode) return fail(e, PSK_E10001, "cuTensorMapEncodeTiled is not available from this driver");
+    const bool b_n_major = g.b_k != 1;
+    const int64_t batch_hi = g.batch / g.batch_lo;
+    CUtensorMap ma, mb;
+    if (!make_map_u8(e, &ma, A.p, (uint64_t)g.k, (uint64_t)g.m, (uint64_t)g.batch_lo, (uint64_t)batch_hi, (uint64_t)g.a_row, (uint64_t)g.a_lo, (uint64_t)g.a_hi, tci8::BKB, tci8::BM * tci8::MT))
+        return fail(e, PSK_E7001, "integer contraction: operand 0's strides do not make a tensor map");
+    const bool okb = b_n_major
+        ? make_map_u8(e, &mb, B.p, (uint64_t)g.n, (uint64_t)g.k, (uint64_t)g.batch_lo, (uint64_t)batch_hi, (uint64_t)g.b_k, (uint64_t)g.b_lo, (uint64_t)g.b_hi, 128, tci8::BKB)
+        : make_map_u8(e, &mb, B.p, (uint64_t)g.k, (uint64_t)g.n, (uint64_t)g.batch_lo, (uint64_t)batch_hi, (uint64_t)g.b_n, (uint64_t)g.b_lo, (uint64_t)g.b_hi, tci8::BKB, tci8::BN);
+    if (!okb) return fail(e, PSK_E7001, "integer contraction: operand 1's strides do not make a tensor map");
+    tci8::Params P;
+    memset(&P, 0, sizeof P);
+    P.m = g.m; P.n = g.n; P.k = g.k; P.batch = g.batch; P.batch_lo = g.batch_lo;
+    P.tiles_m = (g.m + tci8::BM * tci8::MT - 1) / (tci8::BM * tci8::MT);
+    P.tiles_n = (g.n + tci8::BN - 1) / tci8::BN;
+    {
+        const int64_t col_bytes = (int64_t)tci8::BN * g.k;
+        P.panel = std::min<int64_t>(std::max<int64_t>(8, (32ll << 20) / std::max<int64_t>(col_bytes, 1)), P.tiles_n);
+    }
+    P.c_row_lo_count = g.c_row_lo_count; P.c_row_lo = g.c_row_lo; P.c_row_hi = g.c_row_hi;
+    P.c_col_lo_count = g.c_col_lo_count; P.c_col_hi = g.c_col_hi;
+    P.c_lo = g.c_lo; P.c_hi = g.c_hi;
+    P.c = const_cast<void *>(O.p); P.out_dtype = O.dtype;
+    P.out_affine = out_desc.affine; P.out_zero = out_desc.affine_zero; P.out_scale = out_desc.affine_scale;
+    P.a_unsigned = A.affine == 2 ? 1 : 0; P.a_zero = A.affine_zero; P.a_scale = A.affine_scale;
+    P.b_n_major = b_n_major ? 1 : 0;
+    P.col_scale = B.scales; P.col_scale_stride = g.bs_n; P.col_scale_lo = g.bs_lo; P.col_scale_hi = g.bs_hi;
+    P.guarded = guarded ? 1 : 0;
+    const int64_t va = O.dtype == PSK_F32 ? 4 : 8;
+    P.vec_ok = aligned16(O.p) && g.c_row_lo % va == 0 && g.c_row_hi % va == 0 && g.c_col_hi % va == 0 && g.c_lo % va == 0 && g.c_hi % va == 0 && g.c_col_lo_count % 32 == 0 && g.n % va == 0;
+    P.ovf = flag; P.status = e->status;
+    int32_t *colsum = nullptr;
+    if (A.affine_zero != 0) {
+        colsum = (int32_t *)psk_exec_alloc(e, (size_t)g.n * g.batch * 4);
+        if (!colsum) return fail(e, PSK_E10001, "integer contraction: no memory for the weights' column sums");
+        tci8::k_colsum_i8<<<grid_for(e, g.n * g.batch, 256, 8), 256, 0, e->stream>>>((const int8_t *)B.p, g.n, g.k, g.batch, g.batch_lo, g.b_n, g.b_k, g.b_lo, g.b_hi, colsum);
+        e->kernels += 1;
+        P.colsum = colsum;
+    }
+    if (!e->i8_attr_set) {
+        CUDA_TRY(e, cudaFuncSetAttribute(tci8::k_gemm_i8, cudaFuncAttributeMaxDynamicSharedMemorySize, tci8::SMEM_TOTAL));
+        e->i8_attr_set = true;
+    }
+    const int64_t tiles = P.tiles_m * P.tiles_n * g.batch;
+    const int grid = (int)std::min<int64_t>(tiles, e->sms);
+    tci8::k_gemm_i8<<<grid, tci8::THREADS, tci8::SMEM_TOTAL, e->stream>>>(ma, mb, P);
+    if (colsum) psk_exec_free(e, colsum); // handed out again only to later work of the same stream
     CUDA_TRY(e, cudaGetLastError());
     e->kernels += 1;
     return PSK_OK;
@@ -880,6 +953,32 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
             bool ok = L.n_in == 2;
             for (int i = 0; ok && i < 2; ++i) ok = L.in[i].affine != 0 || (L.in[i].dtype == PSK_I8 && L.in[i].scales != nullptr);
             if (!ok) { rc = fail(e, PSK_E7005, std::string(l->name ? l->name : "?") + ": integer sums need two operands that are affine values or integer weights"); break; }
+            {
+                // On the tensor cores (tcgen05 kind::i8) when the operands are an affine activation with its summed
+                // axis contiguous and integer weights with a scale a column: 32-bit sums that wrap are
+                // associative, so the result is the scalar kernel's under every order. The raw sum of codes must
+                // stay inside 32 bits (k <= 65536); 16-byte rows for the tensor maps.
+                GemmMap g;
+                static const bool i8_tc = getenv("PSK_I8_TC") ? atoi(getenv("PSK_I8_TC")) != 0 : true;
+                const DevOperand &A = L.in[0], &B = L.in[1];
+                bool fits = i8_tc && e->encode && map_gemm(L, g) && A.affine != 0 && !B.affine && B.dtype == PSK_I8 && B.scales
+                    && g.a_k == 1 && (g.b_k == 1 || g.b_n == 1) && g.k >= 16 && g.k <= 65536 && g.c_col_lo == 1 && g.m >= 1 && g.n >= 16
+                    && aligned16(A.p) && aligned16(B.p)
+                    && (L.out.affine != 0 || L.out.dtype == PSK_F32 || L.out.dtype == PSK_BF16 || L.out.dtype == PSK_F16 || L.out.dtype == PSK_E8M15);
+                for (int a = L.n_outer; fits && a < L.n_outer + L.n_inner; ++a) fits = B.sstride[a] == 0;
+                if (fits) {
+                    if (g.m == 1) g.a_row = (g.k + 15) / 16 * 16;
+                    std::string keep = e->error;
+                    const int r = launch_i8(e, g, A, B, L.out, l->out, L.ovf, L.guarded);
+                    if (r == PSK_OK) {
+                        e->last_kernel = "k_gemm_i8";
+                        e->last_flops = 2.0 * (double)g.m * (double)g.n * (double)g.k * (double)g.batch;
+                        break;
+                    }
+                    if (r != PSK_E7001) { rc = r; break; }
+                    e->error = keep; // strides no tensor map takes: the scalar kernel
+                }
+            }
             k_contract_int<<<grid_for(e, L.total, 128, 16), 128, 0, e->stream>>>(L);
             e->last_kernel = "k_contract_int";
             e->last_flops = 2.0 * (double)L.total * (double)L.inner;

@@ -393,3 +393,64 @@ def test_weight_gradient_contraction_reaches_the_tensor_cores(cuda, oracle):
     assert np.abs(got - want).max() <= 2.0**-7 * np.abs(want).max()
     for p in (px, pct, pc):
         cuda.free(p)
+
+
+@pytest.mark.parametrize("m,k,n,b_n_major", [(300, 576, 272, True), (300, 576, 272, False), (512, 4096, 256, True), (129, 160, 48, True), (1, 1024, 512, True), (64, 65536, 32, False)])
+def test_integer_sums_on_the_tensor_cores_are_exact(cuda, oracle, m, k, n, b_n_major):
+    """`product: i32, accum: i32` at contraction scale: affine activations (u8 with a zero point, i8 without and
+    with one) times int8 weights with a scale a column, on tcgen05's 8-bit integer kind. Sums modulo 2^32 are
+    associative and the store rounds the exact value once, so every output is the oracle's, bit for bit, for every
+    result type (bf16, f32, f16, e8m15, affine i8): ragged edges, a summed axis that is no multiple of the tile,
+    the longest sum the kernel takes (65536 terms of the largest codes, which stays inside 32 bits)."""
+    from presk_b200 import abi, launch_desc
+    rng = np.random.default_rng(m * 7 + k + n)
+    cases = [(2, 37, abi.BF16), (1, 0, abi.F32), (1, -5, abi.BF16), (2, 255, abi.F16), (1, 0, abi.E8M15), (2, 128, "affine")]
+    for kind, zero, store in cases:
+        lo, hi = (0, 255) if kind == 2 else (-128, 127)
+        codes = rng.integers(lo, hi + 1, size=(m, k)).astype(np.uint8 if kind == 2 else np.int8)
+        qw = rng.integers(-127, 128, size=(k, n) if b_n_major else (n, k)).astype(np.int8)
+        if k == 65536:  # the extreme: every product the largest there is
+            codes[:] = hi
+            qw[:] = 127 if kind == 2 else -127
+        s_a = np.float32(rng.uniform(1.0, 2.0) * 2.0 ** int(rng.integers(-10, -2)))
+        sw = (rng.uniform(1.0, 2.0, size=n) * 2.0 ** rng.integers(-12, -4, size=n)).astype(np.float32)
+        l = launch_desc(abi.OP_CONTRACT, abi.F32, [m, n], [k], name=b"dot")
+        l.n_inputs, l.int_accum = 2, 1
+        l.inputs[0].dtype = abi.U8 if kind == 2 else abi.I8
+        l.inputs[0].affine, l.inputs[0].affine_zero, l.inputs[0].affine_scale = kind, zero, float(s_a)
+        l.inputs[0].stride[0], l.inputs[0].stride[2], l.inputs[0].numel = k, 1, m * k
+        l.inputs[1].dtype, l.inputs[1].numel = abi.I8, k * n
+        if b_n_major:
+            l.inputs[1].stride[1], l.inputs[1].stride[2] = 1, n
+        else:
+            l.inputs[1].stride[1], l.inputs[1].stride[2] = k, 1
+        l.inputs[1].scale_stride[1] = 1
+        l.out.stride[0], l.out.stride[1], l.out.numel = n, 1, m * n
+        if store == "affine":
+            l.out.dtype, l.out.affine, l.out.affine_zero = abi.I8, 1, 3
+            l.out.affine_scale = float(np.float32(float(s_a) * float(sw.mean()) * np.sqrt(k) * 40.0))
+            out_bytes = m * n
+        else:
+            l.dtype = l.out.dtype = store
+            out_bytes = m * n * abi.DTYPE_BYTES[store]
+        dev = [cuda.upload(codes), cuda.upload(qw)]
+        pout, psw = cuda.alloc(out_bytes), cuda.upload(sw)
+        cuda.set_profiling(True)
+        cuda.run(l, dev + [pout, psw])
+        cuda.overflow()
+        cuda.sync()
+        kinds = [rec[0] for rec in cuda.profile()]
+        cuda.set_profiling(False)
+        assert kinds == ["k_gemm_i8"], kinds  # the tensor-core kernel took it
+        got = cuda.download(pout, out_bytes)
+        for p in dev + [pout, psw]:
+            cuda.free(p)
+        want = np.zeros(out_bytes, np.uint8)
+        oracle.run(l, [codes, qw, want, sw])
+        bad = np.nonzero(got != want)[0]
+        assert bad.size == 0, (kind, zero, store, bad.size, bad[:4], got[bad[:4]], want[bad[:4]])
+        if store == abi.F32:  # and the oracle's integer is the one numpy's 64-bit sum wraps to
+            acc = (codes.astype(np.int64) - zero) @ (qw.astype(np.int64) if b_n_major else qw.astype(np.int64).T)
+            acc = ((acc + 2**31) % 2**32) - 2**31
+            ref = acc.astype(np.float64) * float(s_a) * sw.astype(np.float64)[None, :]
+            np.testing.assert_allclose(got.view(np.float32).reshape(m, n), ref, rtol=1e-6)
