@@ -338,6 +338,22 @@ def microbench(args):
         ms = timed(lambda: ex.gemm(g, a, b, c), args.steps)
         fl = 2.0 * m * n * k * batch
         print(json.dumps({"micro": "gemm", "shape": dims, "ms": ms, "TFLOP/s": fl / ms / 1e9, "GB/s": (batch * (m * k + n * k + m * n) * 2) / ms / 1e6}))
+    elif args.micro == "gemm_i8":
+        # the integer-sum contraction: i8 activation codes [m, k] (one scale) times int8 weights [k, n] (a scale a column), bf16 result
+        m, n, k = dims[:3]
+        a = ex.upload(rng.integers(-128, 128, size=(m, k), dtype=np.int8))
+        b = ex.upload(rng.integers(-127, 128, size=(k, n), dtype=np.int8))
+        sw = ex.upload((rng.uniform(1.0, 2.0, size=n) * 2.0 ** -8).astype(np.float32))
+        c = ex.alloc(m * n * 2)
+        l = launch_desc(abi.OP_CONTRACT, abi.BF16, [m, n], [k], order=abi.ORDER_DEVICE, name=b"dot")
+        l.n_inputs, l.int_accum = 2, 1
+        l.inputs[0].dtype, l.inputs[0].affine, l.inputs[0].affine_zero, l.inputs[0].affine_scale = abi.I8, 1, int(dims[3]) if len(dims) > 3 else 0, 0.03125
+        l.inputs[0].stride[0], l.inputs[0].stride[2], l.inputs[0].numel = k, 1, m * k
+        l.inputs[1].dtype, l.inputs[1].stride[1], l.inputs[1].stride[2], l.inputs[1].numel = abi.I8, 1, n, k * n
+        l.inputs[1].scale_stride[1] = 1
+        l.out.dtype, l.out.stride[0], l.out.stride[1], l.out.numel = abi.BF16, n, 1, m * n
+        ms = timed(lambda: ex.run(l, [a, b, c, sw]), args.steps)
+        print(json.dumps({"micro": "gemm_i8", "shape": dims, "ms": ms, "TOP/s": 2.0 * m * n * k / ms / 1e9}))
     elif args.micro == "attn":
         B, H, t = dims[:3]
         hd = 128
@@ -351,6 +367,7 @@ def microbench(args):
         ex.run(lm, [mask])
         l = launch_desc(abi.OP_ATTENTION, abi.BF16, [B, H, t, hd], [t], order=abi.ORDER_DEVICE, name=b"attention[blockwise]")
         l.n_inputs, l.masked = 5, 1
+        l.iparam[0] = dims[3] if len(dims) > 3 else 0  # 1: the one-pass kernel (`attention: online`)
         l.iparam[1] = l.iparam[2] = l.iparam[3] = abi.BF16
         n = B * H * t * hd
         for o, st in ((l.inputs[0], (H * t * hd, t * hd, hd, 1, 0)), (l.inputs[1], (H * t * hd, t * hd, 0, 1, hd)), (l.inputs[2], (t * H * hd, hd, 0, 1, H * hd)), (l.out, (t * H * hd, hd, H * hd, 1, 0))):
@@ -636,14 +653,14 @@ def run_small(args, name, w):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--micro", default=None, choices=["gemm", "softmax", "ew", "attn", "norm", "e8m15", "f32c", "train", "rmsnorm", "rope", "xent"])
+    ap.add_argument("--micro", default=None, choices=["gemm", "gemm_i8", "softmax", "ew", "attn", "norm", "e8m15", "f32c", "train", "rmsnorm", "rope", "xent"])
     ap.add_argument("--shape", default="8192,8192,8192")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="llama7b_prefill_b8_t2048", choices=sorted(WORKLOADS))
-    ap.add_argument("--attention", default="blockwise", choices=["blockwise", "unfused"], help="the declared order of the attention launches: one blockwise kernel, or the reference's four launches")
+    ap.add_argument("--attention", default="blockwise", choices=["blockwise", "online", "unfused"], help="the declared order of the attention launches: one kernel in two passes over the keys (blockwise) or in one (online), or the reference's four launches")
     ap.add_argument("--launches", default="merged", choices=["merged", "reference"], help="merged: bit-preserving rewrites of the launch list (views for slices, in-place concatenation, wider groups); reference: the reference's launch list")
     ap.add_argument("--comm", default="psk", choices=["psk", "torch"], help="what carries the loss gather of a sharded run: the library's psk_comm_* (NCCL on the executor's stream) or torch.distributed")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -811,7 +828,7 @@ def main():
         "launches_per_step": int((launches_after - launches_before) / args.steps),
     }
     if not args.no_parity:
-        out["parity"] = parity_preflight(ex, consts, w.get("int8", False))
+        out["parity"] = parity_preflight(ex, consts, w.get("int8", False), args.attention, args.launches)
     if world == 1 and not args.no_cpu_baseline:
         try:
             v, sample = cpu_prefill_tokens_per_s(consts, T, B, threads, w.get("int8", False))
@@ -821,7 +838,7 @@ def main():
     print(json.dumps(out, ensure_ascii=False))
 
 
-def parity_preflight(ex, consts, int8):
+def parity_preflight(ex, consts, int8, attention="blockwise", launches="merged"):
     """Outside every timed region: one layer of the workload's own width (and its vocabulary) at B = 1, T = 256
     over the CUDA executor under the benchmark's realization and over the CPU oracle under the sequential order
     with the reference's launch list; the oracle is the checker. The largest difference of the logits against
@@ -832,11 +849,11 @@ def parity_preflight(ex, consts, int8):
         import oracle_lib
         os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
         weights = "int8" if int8 is True else ("e4m3fn" if int8 == "e4m3fn" else "bf16")
-        r = headline.llama_width_parity(ex, oracle_lib.load(), B=1, T=256, weights=weights, consts={k: v for k, v in consts.items() if k != "L"})
+        r = headline.llama_width_parity(ex, oracle_lib.load(), B=1, T=256, weights=weights, consts={k: v for k, v in consts.items() if k != "L"}, order={"kind": "device", "attention": attention, "launches": launches})
         tol = headline.LOGITS_TOL * (2.0 if weights != "bf16" else 1.0) * r["logits_scale"]
         ok = r["finite"] and r["logits_max_err"] <= tol and abs(r["loss_gpu"] - r["loss_oracle"]) <= headline.LOSS_RTOL * abs(r["loss_oracle"])
         return {"ok": bool(ok), "max_err": r["logits_max_err"], "tol": tol, "mean_err": r["logits_mean_err"], "logits_scale": r["logits_scale"], "loss_gpu": r["loss_gpu"], "loss_oracle": r["loss_oracle"], "loss_rtol": headline.LOSS_RTOL,
-                "shape": r["shape"], "against": "CPU oracle, order sequential, the reference's launch list; the GPU side runs the benchmark's realization (device order, blockwise attention, merged launches)"}
+                "shape": r["shape"], "against": f"CPU oracle, order sequential, the reference's launch list; the GPU side runs the benchmark's realization (device order, attention {attention}, launches {launches})"}
     except Exception as e:
         return {"ok": False, "error": str(e)}
 

@@ -89,7 +89,9 @@ typedef enum {
                              seq2. Space: outer axes (..., seq, hd), one inner axis seq2. Inputs: q (stride 0 on
                              seq2), k and v (stride 0 on seq; hd and seq2 both walked), rt (rank 0), and the mask
                              over (seq, seq2) when n_inputs is 5. iparam[1..3]: the storage types of the three
-                             sites in between. The value is DEFINED as that of the four launches run one after
+                             sites in between. iparam[0]: how an executor may fuse them: 0 blockwise (two passes
+                             over the keys, each stored site's rounding kept in registers), 1 online (one pass
+                             against a running reference maximum, the sites in between not rounded). The value is DEFINED as that of the four launches run one after
                              the other; an executor may only fuse them under PSK_ORDER_DEVICE, and then agrees
                              with them within a tolerance. No counterpart among the reference's kernels: its
                              fusion (presk-core/src/fusion.rs) never crosses a contraction or a softmax. */

@@ -562,5 +562,287 @@ __global__ void __launch_bounds__(THREADS2, 2) k_attn_fwd2(const __grid_constant
 }
 } // namespace v2
 
+
+// ---------------------------------------------------------------------------
+// One pass over the key blocks (the declared order `attention: online`): the exponentials are taken against a
+// running reference maximum instead of the row's final one, so the scores are multiplied once, not twice.
+//
+//   * A thread owns a query row (its tensor-memory lane) and all 64 keys of a block: no exchange between threads,
+//     ever. Four softmax warps a CTA, two CTAs an SM.
+//   * The reference m of a row (in units of log2: score · log2(e) / rt) starts as the first block's maximum. A later
+//     block whose maximum exceeds m by more than RESCALE_AT moves it: the row's sum and its accumulator in tensor
+//     memory are multiplied by 2^(m_old - m_new) (tcgen05.ld, multiply, tcgen05.st), between the product that last
+//     added to the accumulator and the next one. Until then exponentials may reach 2^RESCALE_AT, which bf16 and the
+//     f32 accumulator hold exactly as well as numbers below one. Rows whose maximum settles early never pay.
+//   * Unlike the two-pass kernels, the raw and the scaled scores are not rounded to bf16 in between (no memory ever
+//     holds them here): exp2(s · c - m) straight from the f32 score, c = log2(e) / rt. The result is nearer the exact
+//     attention than the four launches' and differs from theirs by their own roundings; the tests state by how much.
+// K and V blocks travel through one ring of three stages in the order the products use them, P is single-buffered,
+// every mbarrier wait is bounded, as in k_attn_fwd2.
+// ---------------------------------------------------------------------------
+namespace v3 {
+constexpr int BN3 = 64;
+constexpr int SOFTMAX_WARPS3 = 4;
+constexpr int THREADS3 = (2 + SOFTMAX_WARPS3) * 32;
+constexpr int KV_STAGE3 = BN3 * HD * 2;       // 16 KB: two halves of [64 keys x 64 hd]
+constexpr int KV_HALF3 = BN3 * 64 * 2;
+constexpr int RING3 = 3;
+constexpr int P_BYTES3 = BM * BN3 * 2;        // 16 KB: [128 rows x 64 keys]
+constexpr int SMEM_TILES3 = TILE + RING3 * KV_STAGE3 + P_BYTES3;
+constexpr int SMEM_TOTAL3 = SMEM_TILES3 + 256 + 1024;
+constexpr float RESCALE_AT = 8.0f;
+
+PSK_DEV void tmem_st32(uint32_t taddr, const uint32_t (&r)[32])
+{
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr),
+          "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+
+__global__ void __launch_bounds__(THREADS3, 2) k_attn_fwd3(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const __grid_constant__ Params P)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t *sQ = smem, *sR = smem + TILE, *sP = smem + TILE + RING3 * KV_STAGE3;
+    uint64_t *bars = (uint64_t *)(smem + SMEM_TILES3);
+    // 0 q_full; 1..3 ring full; 4..6 ring empty; 7,8 s_full; 9,10 s_free; 11 p_full; 12 p_free; 13 o_full
+    uint32_t *tmem_slot = (uint32_t *)(bars + 14);
+    volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
+    const uint32_t bar0 = tc::smem_u32(bars);
+    auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nqb = (int)(P.T / BM);
+    const int qb = nqb - 1 - (int)blockIdx.x; // the longest rows first
+    const int g = blockIdx.y, b = blockIdx.z;
+    const int gk = g / P.per;
+    const int nkb = P.causal ? 2 * (qb + 1) : (int)(P.T / BN3);
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int i = 0; i < 14; ++i) tc::mbar_init(bar(i), (i == 9 || i == 10 || i == 11) ? SOFTMAX_WARPS3 : 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc::smem_u32(tmem_slot)), "r"(256) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t tS0 = tmem, tO = tmem + 128;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            bool ok = true;
+            tc::mbar_expect_tx(bar(0), TILE);
+            tc::tma_load_4d(tc::smem_u32(sQ), &map_q, bar(0), 0, qb * BM, g, b);
+            tc::tma_load_4d(tc::smem_u32(sQ + HALF), &map_q, bar(0), 64, qb * BM, g, b);
+            uint32_t ps = 0, pph = 0;
+            auto load = [&](const CUtensorMap *map, int kb) -> bool {
+                if (!tc::mbar_wait(bar(4 + ps), pph ^ 1u, abort_flag, P.status, 0x81u)) return false;
+                tc::mbar_expect_tx(bar(1 + ps), KV_STAGE3);
+                tc::tma_load_4d(tc::smem_u32(sR + ps * KV_STAGE3), map, bar(1 + ps), 0, kb * BN3, gk, b);
+                tc::tma_load_4d(tc::smem_u32(sR + ps * KV_STAGE3 + KV_HALF3), map, bar(1 + ps), 64, kb * BN3, gk, b);
+                if (++ps == RING3) { ps = 0; pph ^= 1u; }
+                return true;
+            };
+            // in the order the products read them: K0, then (K of the next block, V of this one) a block
+            ok = load(&map_k, 0);
+            for (int kb = 0; kb < nkb && ok; ++kb) {
+                if (kb + 1 < nkb) ok = load(&map_k, kb + 1);
+                if (ok) ok = load(&map_v, kb);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc_qk = tc::instr_desc(0, 0, BN3), idesc_pv = tc::instr_desc(0, 1, HD);
+            bool ok = tc::mbar_wait(bar(0), 0u, abort_flag, P.status, 0x91u);
+            uint32_t rs = 0, rph = 0, qk_count = 0;
+            auto issue_qk = [&]() -> bool {
+                const uint32_t sb = qk_count & 1u, sph = (qk_count >> 1) & 1u;
+                if (!tc::mbar_wait(bar(1 + rs), rph, abort_flag, P.status, 0x92u)) return false;
+                if (!tc::mbar_wait(bar(9 + sb), sph ^ 1u, abort_flag, P.status, 0x93u)) return false;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t qa = tc::smem_u32(sQ), ka = tc::smem_u32(sR + rs * KV_STAGE3);
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk) {
+                    const uint32_t qoff = (uint32_t)(kk >> 2) * HALF + (uint32_t)(kk & 3) * 32u;
+                    const uint32_t koff = (uint32_t)(kk >> 2) * KV_HALF3 + (uint32_t)(kk & 3) * 32u;
+                    tc::umma(tS0 + sb * 64u, tc::smem_desc(qa + qoff, 16, 1024), tc::smem_desc(ka + koff, 16, 1024), idesc_qk, kk != 0 ? 1u : 0u);
+                }
+                tc::umma_commit(bar(4 + rs));
+                tc::umma_commit(bar(7 + sb));
+                if (++rs == RING3) { rs = 0; rph ^= 1u; }
+                ++qk_count;
+                return true;
+            };
+            if (ok) ok = issue_qk();
+            for (int kb = 0; kb < nkb && ok; ++kb) {
+                if (kb + 1 < nkb) ok = issue_qk();
+                if (!ok) break;
+                ok = tc::mbar_wait(bar(11), (uint32_t)(kb & 1), abort_flag, P.status, 0x94u);
+                if (!ok) break;
+                ok = tc::mbar_wait(bar(1 + rs), rph, abort_flag, P.status, 0x95u);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t pa = tc::smem_u32(sP), va = tc::smem_u32(sR + rs * KV_STAGE3);
+#pragma unroll
+                for (int kk = 0; kk < BN3 / 16; ++kk)
+                    tc::umma(tO, tc::smem_desc(pa + (uint32_t)kk * 32u, 16, 1024), tc::smem_desc(va + (uint32_t)kk * 2048u, KV_HALF3, 1024), idesc_pv, (kb | kk) != 0 ? 1u : 0u);
+                tc::umma_commit(bar(4 + rs)); // the V block is free
+                tc::umma_commit(bar(12));     // and P may be overwritten, the accumulator rescaled
+                if (++rs == RING3) { rs = 0; rph ^= 1u; }
+            }
+            if (ok) tc::umma_commit(bar(13));
+        }
+    } else {
+        const int quad = warp & 3;
+        const int row = quad * 32 + lane;
+        const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+        const float rtv = bf16_round(load_real(P.rt, P.rt_dtype, 0)); // the division's kernel is bf16: it reads rt rounded to bf16 at its edge
+        const float c = __fdiv_rn(1.44269504f, rtv);                  // log2(e) / rt
+        const bool want_max = !(c < 0.0f);
+        bool ok = true;
+        float m = 0.0f, z = 0.0f;
+        for (int kb = 0; kb < nkb && ok; ++kb) {
+            const uint32_t sb = (uint32_t)kb & 1u, sph = ((uint32_t)kb >> 1) & 1u;
+            ok = tc::mbar_wait(bar(7 + sb), sph, abort_flag, P.status, 0xa1u);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint32_t va[32], vb[32];
+            tc::tmem_ld32(tS0 + lane_base + sb * 64u, va);
+            tc::tmem_ld32(tS0 + lane_base + sb * 64u + 32u, vb);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(bar(9 + sb)); // the scores are in registers
+            // the last allowed key of this row in this block (63 or more: all; negative: none)
+            const int lim = P.causal ? (qb * BM + row) - kb * BN3 : 63;
+            // the block's greatest scaled score over the allowed keys: c times the greatest raw score (the least, if c < 0)
+            float blk = want_max ? -INFINITY : INFINITY;
+            if (want_max) {
+                if (lim >= 63) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) blk = fmaxf(blk, fmaxf(__uint_as_float(va[i]), __uint_as_float(vb[i])));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        if (i <= lim) blk = fmaxf(blk, __uint_as_float(va[i]));
+                        if (i + 32 <= lim) blk = fmaxf(blk, __uint_as_float(vb[i]));
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    if (i <= lim) blk = fminf(blk, __uint_as_float(va[i]));
+                    if (i + 32 <= lim) blk = fminf(blk, __uint_as_float(vb[i]));
+                }
+            }
+            const float blk2 = __fmul_rn(blk, c); // -inf when the row sees nothing of this block
+            float factor = 1.0f;
+            if (kb == 0) {
+                m = blk2; // every row sees the first key of the first block
+            } else if (blk2 > m + RESCALE_AT) {
+                factor = fast_exp2(m - blk2);
+                z *= factor;
+                m = blk2;
+            }
+            uint32_t packed[32];
+            if (lim >= 63) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float e0 = fast_exp2(__fmaf_rn(__uint_as_float(va[2 * i]), c, -m)), e1 = fast_exp2(__fmaf_rn(__uint_as_float(va[2 * i + 1]), c, -m));
+                    const float f0 = fast_exp2(__fmaf_rn(__uint_as_float(vb[2 * i]), c, -m)), f1 = fast_exp2(__fmaf_rn(__uint_as_float(vb[2 * i + 1]), c, -m));
+                    z += e0 + e1;
+                    z += f0 + f1;
+                    packed[i] = pack_bf16x2_hw(e0, e1);
+                    packed[16 + i] = pack_bf16x2_hw(f0, f1);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    float e0 = fast_exp2(__fmaf_rn(__uint_as_float(va[2 * i]), c, -m)), e1 = fast_exp2(__fmaf_rn(__uint_as_float(va[2 * i + 1]), c, -m));
+                    float f0 = fast_exp2(__fmaf_rn(__uint_as_float(vb[2 * i]), c, -m)), f1 = fast_exp2(__fmaf_rn(__uint_as_float(vb[2 * i + 1]), c, -m));
+                    if (2 * i > lim) e0 = 0.0f;
+                    if (2 * i + 1 > lim) e1 = 0.0f;
+                    if (32 + 2 * i > lim) f0 = 0.0f;
+                    if (33 + 2 * i > lim) f1 = 0.0f;
+                    z += e0 + e1;
+                    z += f0 + f1;
+                    packed[i] = pack_bf16x2_hw(e0, e1);
+                    packed[16 + i] = pack_bf16x2_hw(f0, f1);
+                }
+            }
+            // the product of the block before has read P and added to the accumulator
+            ok = tc::mbar_wait(bar(12), (uint32_t)(kb & 1) ^ 1u, abort_flag, P.status, 0xa2u);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            if (__any_sync(0xffffffffu, factor != 1.0f)) {
+                // this warp's 32 rows of the accumulator times their factors (1 for the rows that did not move)
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+                for (int c0 = 0; c0 < HD; c0 += 32) {
+                    uint32_t o[32];
+                    tc::tmem_ld32(tO + lane_base + (uint32_t)c0, o);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+                    tmem_st32(tO + lane_base + (uint32_t)c0, o);
+                }
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            }
+            uint8_t *dst = sP + row * 128;
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                *reinterpret_cast<uint4 *>(dst + ((u ^ (row & 7)) << 4)) = make_uint4(packed[4 * u], packed[4 * u + 1], packed[4 * u + 2], packed[4 * u + 3]);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // the tensor core reads P through the async proxy
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(bar(11));
+        }
+        if (ok) {
+            ok = tc::mbar_wait(bar(13), 0u, abort_flag, P.status, 0xa3u);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int64_t t = (int64_t)qb * BM + row;
+            uint16_t *orow = (uint16_t *)P.out + (int64_t)b * P.o_b + (int64_t)g * P.o_g + t * P.o_t;
+            const float rz = __frcp_rn(z);
+#pragma unroll 1
+            for (int c0 = 0; c0 < HD; c0 += 32) {
+                uint32_t v[32];
+                tc::tmem_ld32(tO + lane_base + (uint32_t)c0, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        w[i] = pack_bf16x2_hw(div_by(__uint_as_float(v[u * 8 + 2 * i]), z, rz), div_by(__uint_as_float(v[u * 8 + 2 * i + 1]), z, rz));
+                    *reinterpret_cast<uint4 *>(orow + c0 + u * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256) : "memory");
+    }
+}
+} // namespace v3
+
 } // namespace attn
 } // namespace psk

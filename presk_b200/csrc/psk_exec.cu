@@ -1190,7 +1190,7 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
     }
     case PSK_OP_ATTENTION: {
         // (batch, heads, seq, hd | seq2) or (batch, groups, per, seq, hd | seq2); see psk_attn.cuh
-        e->last_kernel = "k_attn_fwd";
+        e->last_kernel = l->iparam[0] == 1 ? "k_attn_fwd3" : "k_attn_fwd";
         const std::string nm = l->name ? l->name : "attention";
         if (!device_order) { rc = fail(e, PSK_E7005, nm + ": blockwise attention is a declared order; under the sequential order the four launches run one by one"); break; }
         const int no = L.n_outer;
@@ -1219,10 +1219,11 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
         if (!e->encode) { rc = fail(e, PSK_E10001, "cuTensorMapEncodeTiled is not available from this driver"); break; }
         // two kernels of the same computation: key blocks of 128 and one CTA an SM, or of 64 and two (see psk_attn.cuh)
         static const bool two_a_sm = getenv("PSK_ATTN_KERNEL") ? atoi(getenv("PSK_ATTN_KERNEL")) != 1 : true; // measured: 0.63 ms against 0.74 ms at B = 8, H = 32, T = 2048
+        const bool online = l->iparam[0] == 1; // the declared order `attention: online`: one pass, a running reference maximum
         CUtensorMap mq, mk, mv;
         bool ok = make_map(e, &mq, Q.p, 0, (uint64_t)HD, (uint64_t)T, (uint64_t)(G * Pn), (uint64_t)B, (uint64_t)Q.stride[ax_seq], (uint64_t)q_head, (uint64_t)Q.stride[ax_b], 64, attn::BM)
-            && make_map(e, &mk, K.p, 0, (uint64_t)HD, (uint64_t)T, (uint64_t)G, (uint64_t)B, (uint64_t)K.stride[ax_s2], (uint64_t)K.stride[ax_g], (uint64_t)K.stride[ax_b], 64, two_a_sm ? attn::v2::BN2 : attn::BN)
-            && make_map(e, &mv, V.p, 0, (uint64_t)HD, (uint64_t)T, (uint64_t)G, (uint64_t)B, (uint64_t)V.stride[ax_s2], (uint64_t)V.stride[ax_g], (uint64_t)V.stride[ax_b], 64, two_a_sm ? attn::v2::BN2 : attn::BN);
+            && make_map(e, &mk, K.p, 0, (uint64_t)HD, (uint64_t)T, (uint64_t)G, (uint64_t)B, (uint64_t)K.stride[ax_s2], (uint64_t)K.stride[ax_g], (uint64_t)K.stride[ax_b], 64, (two_a_sm || online) ? attn::v2::BN2 : attn::BN)
+            && make_map(e, &mv, V.p, 0, (uint64_t)HD, (uint64_t)T, (uint64_t)G, (uint64_t)B, (uint64_t)V.stride[ax_s2], (uint64_t)V.stride[ax_g], (uint64_t)V.stride[ax_b], 64, (two_a_sm || online) ? attn::v2::BN2 : attn::BN);
         if (!ok) { rc = fail(e, PSK_E7001, nm + ": an operand's strides do not make a tensor map"); break; }
         attn::Params A;
         memset(&A, 0, sizeof A);
@@ -1233,12 +1234,14 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
         if (!e->attn_attr_set) {
             CUDA_TRY(e, cudaFuncSetAttribute(attn::k_attn_fwd, cudaFuncAttributeMaxDynamicSharedMemorySize, attn::SMEM_TOTAL));
             CUDA_TRY(e, cudaFuncSetAttribute(attn::v2::k_attn_fwd2, cudaFuncAttributeMaxDynamicSharedMemorySize, attn::v2::SMEM_TOTAL2));
+            CUDA_TRY(e, cudaFuncSetAttribute(attn::v3::k_attn_fwd3, cudaFuncAttributeMaxDynamicSharedMemorySize, attn::v3::SMEM_TOTAL3));
             e->attn_attr_set = true;
         }
         const int64_t nqb = T / attn::BM;
         if (G * Pn > 65535 || B > 65535) { rc = fail(e, PSK_E7001, nm + ": more heads or batch entries than a grid holds"); break; }
         dim3 grid((unsigned)nqb, (unsigned)(G * Pn), (unsigned)B);
-        if (two_a_sm) attn::v2::k_attn_fwd2<<<grid, attn::v2::THREADS2, attn::v2::SMEM_TOTAL2, e->stream>>>(mq, mk, mv, A);
+        if (online) attn::v3::k_attn_fwd3<<<grid, attn::v3::THREADS3, attn::v3::SMEM_TOTAL3, e->stream>>>(mq, mk, mv, A);
+        else if (two_a_sm) attn::v2::k_attn_fwd2<<<grid, attn::v2::THREADS2, attn::v2::SMEM_TOTAL2, e->stream>>>(mq, mk, mv, A);
         else attn::k_attn_fwd<<<grid, attn::THREADS, attn::SMEM_TOTAL, e->stream>>>(mq, mk, mv, A);
         const double blocks = causal ? (double)nqb * (double)(nqb + 1) / 2.0 : (double)nqb * (double)nqb;
         e->last_flops = 4.0 * (double)B * (double)(G * Pn) * blocks * 128.0 * 128.0 * (double)HD;

@@ -155,7 +155,8 @@ struct Realization {
     std::map<std::string, AffineSpec> scaled;  // sites stored in an affine format (presk-rt/src/lib.rs:287-360)
     std::map<std::string, int> int_sums;        // sites whose `product` and `accum` are i32: 1 product, 2 accum, 3 both
     int order = PSK_ORDER_SEQUENTIAL;
-    bool blockwise_attention = false; // "order": {"kind": "device", "attention": "blockwise"}
+    bool blockwise_attention = false; // "order": {"kind": "device", "attention": "blockwise"} or "online"
+    bool online_attention = false;    // "attention": "online": the one-pass form of the same launch
     bool merged_launches = false;     // "order": {..., "launches": "merged"}: bit-preserving rewrites of the launch list
 
     static Realization parse(const char *text)
@@ -216,8 +217,12 @@ struct Realization {
                 if (at->str == "blockwise") {
                     if (r.order != PSK_ORDER_DEVICE) raise(PSK_E7005, "realization: `attention: blockwise` is part of the order `device`");
                     r.blockwise_attention = true;
+                } else if (at->str == "online") {
+                    if (r.order != PSK_ORDER_DEVICE) raise(PSK_E7005, "realization: `attention: online` is part of the order `device`");
+                    r.blockwise_attention = true;
+                    r.online_attention = true;
                 } else if (at->str != "unfused") {
-                    raise(PSK_E7005, "realization: the attention order `" + at->str + "` is not one this executor has (unfused, blockwise)");
+                    raise(PSK_E7005, "realization: the attention order `" + at->str + "` is not one this executor has (unfused, blockwise, online)");
                 }
             }
         }
@@ -852,6 +857,7 @@ struct psk_host {
         l.op = PSK_OP_ATTENTION;
         l.dtype = d;
         l.masked = mask ? 1 : 0;
+        l.iparam[0] = rz.online_attention ? 1 : 0;
         l.iparam[1] = d_mid[0]; l.iparam[2] = d_mid[1]; l.iparam[3] = d_mid[2];
         Axes outer = {{"batch", B}, {"groups", G}, {"per", P}, {"seq", T}, {"hd", HD}};
         set_space(l, outer, {T2});
@@ -869,7 +875,7 @@ struct psk_host {
         }
         view(out, {0, 3, 1, 2, 4}, 6, st, ss);
         set_operand(l.out, out, st, {});
-        *ran = run(l, "attention[blockwise]", ins, out, true);
+        *ran = run(l, rz.online_attention ? "attention[online]" : "attention[blockwise]", ins, out, true);
         return out;
     }
 

@@ -55,7 +55,7 @@ def give(host, params):
     return host
 
 
-def llama_width_parity(cuda_executor, oracle, B=1, T=256, weights="bf16", consts=None, seed=0, want_loss=True, params=None):
+def llama_width_parity(cuda_executor, oracle, B=1, T=256, weights="bf16", consts=None, seed=0, want_loss=True, params=None, order=None):
     """One layer of the 7B width over both executors: the CUDA one under the benchmark's order (tensor-core
     contractions, the blockwise attention kernel, merged launches), the oracle under the sequential order with
     the reference's launch list. Returns a dict with the logits' largest difference, their scale, and both losses."""
@@ -67,8 +67,8 @@ def llama_width_parity(cuda_executor, oracle, B=1, T=256, weights="bf16", consts
     y = rng.integers(0, c["V"], size=(B, T), dtype=np.int64)
     out = {"shape": f"llama L=1 V={c['V']} D={c['D']} H={c['H']} G={c['G']} FF={c['FF']} B={B} T={T}, weights {weights}"}
     res = {}
-    for name, ex, order in (("gpu", cuda_executor, BENCH_ORDER), ("oracle", oracle.vtable(), ORACLE_ORDER)):
-        h = give(Host(ex, realization(p, order, weights)).prepare("llama", **c), p)
+    for name, ex, how in (("gpu", cuda_executor, order or BENCH_ORDER), ("oracle", oracle.vtable(), ORACLE_ORDER)):
+        h = give(Host(ex, realization(p, how, weights)).prepare("llama", **c), p)
         if name == "gpu":
             h.set_logging(True)
         logits = h.call("apply", [ids], (B, T, c["V"]))

@@ -296,21 +296,32 @@ def bf16_value(u16):
     return (u16.astype(np.uint32) << 16).view(np.float32)
 
 
-@pytest.mark.parametrize("B,G,P,T,causal", [(2, 2, 2, 384, True), (1, 3, 1, 256, True), (1, 1, 2, 128, False), (1, 2, 1, 1024, True)])
-def test_blockwise_attention_against_its_four_launches(cuda, oracle, B, G, P, T, causal):
+@pytest.mark.parametrize("online", [0, 1, 2])
+@pytest.mark.parametrize("B,G,P,T,causal", [(2, 2, 2, 384, True), (1, 3, 1, 256, True), (1, 1, 2, 128, False), (1, 2, 1, 1024, True), (1, 2, 1, 512, False)])
+def test_blockwise_attention_against_its_four_launches(cuda, oracle, B, G, P, T, causal, online):
     """PSK_OP_ATTENTION under the device order (one tcgen05 kernel, scores never stored) against the
     oracle's four launches with bf16 sites. Tolerance: the result is a bf16 number of magnitude up to
     max|v|; the fused kernel rounds the unnormalised exponentials where the four launches round the
-    normalised ones, so an element may differ by a couple of bf16 units (2^-8 relative each)."""
+    normalised ones, so an element may differ by a couple of bf16 units (2^-8 relative each).
+    `online` = 1, 2: the one-pass kernel (`attention: online`, iparam[0] = 1), which takes the exponentials against
+    a running reference maximum and does not round the scores in between; 2 makes the keys grow along the
+    sequence so that rows' maxima keep rising and the accumulator in tensor memory is rescaled many times.
+    The same tolerances hold: what it leaves out are roundings of the four launches, each of 2^-9 relative on a
+    score of a few units, which moves an exponential by about a percent and the weighted mean of the values by
+    far less."""
     HD = 128
     rng = np.random.default_rng(B * 1000 + T)
     q = bf16_of(oracle, rng.standard_normal((B, G, P, T, HD)) * 1.5)
-    k = bf16_of(oracle, rng.standard_normal((B, G, T, HD)) * 1.5)
+    kf = rng.standard_normal((B, G, T, HD)) * 1.5
+    if online == 2:
+        kf = kf * (0.25 + 3.0 * np.arange(T)[None, None, :, None] / T)
+    k = bf16_of(oracle, kf)
     v = bf16_of(oracle, rng.standard_normal((B, T, G, HD)))
     rt = bf16_of(oracle, np.array(np.sqrt(np.float32(HD)), np.float32).reshape(()))
     l = launch_desc(abi.OP_ATTENTION, abi.BF16, [B, G, P, T, HD], [T], order=abi.ORDER_DEVICE, name=b"attention[blockwise]")
     l.n_inputs = 5 if causal else 4
     l.masked = 1 if causal else 0
+    l.iparam[0] = 1 if online else 0
     l.iparam[1] = l.iparam[2] = l.iparam[3] = abi.BF16
     set_operand(l.inputs[0], abi.BF16, [B, G, P, T, HD], [0, 1, 2, 3, 4])
     set_operand(l.inputs[1], abi.BF16, [B, G, T, HD], [0, 1, 5, 4])
@@ -330,8 +341,11 @@ def test_blockwise_attention_against_its_four_launches(cuda, oracle, B, G, P, T,
         host_in.append(np.tril(np.ones((T, T), np.int64)))
     out_bytes = B * T * G * P * HD * 2
     pout = cuda.alloc(out_bytes)
+    cuda.set_profiling(True)
     cuda.run(l, dev + [pout])
     cuda.sync()
+    assert [rec[0] for rec in cuda.profile()] == ["k_attn_fwd3" if online else "k_attn_fwd"]
+    cuda.set_profiling(False)
     got = bf16_value(cuda.download(pout, out_bytes).view(np.uint16))
     for p in dev + [pout]:
         cuda.free(p)
@@ -341,7 +355,7 @@ def test_blockwise_attention_against_its_four_launches(cuda, oracle, B, G, P, T,
     assert np.isfinite(got).all()
     err = np.abs(got - want)
     assert err.max() <= 2.0**-6 * np.abs(want).max(), (err.max(), np.abs(want).max())
-    assert err.mean() <= 2.0**-8 * np.abs(want).mean()  # on average well within one bf16 unit of an element
+    assert err.mean() <= 2.0**-8 * np.abs(want).mean(), (err.mean(), np.abs(want).mean())  # on average well within one bf16 unit of an element
     # against the exact statement in f64 over the same bf16 inputs
     qf, kf, vf = bf16_value(q).astype(np.float64), bf16_value(k).astype(np.float64), bf16_value(v).astype(np.float64)
     s = np.einsum("bgpsh,bgth->bgpst", qf, kf) / np.sqrt(HD)

@@ -176,7 +176,7 @@ def test_blockwise_attention_is_its_four_launches_on_the_oracle(oracle):
     p = models.llama_params(c)
     ids = np.random.default_rng(8).integers(0, c["V"], size=(2, 16), dtype=np.int64)
     outs, logs = [], []
-    for order in ({"kind": "device"}, {"kind": "device", "attention": "blockwise"}):
+    for order in ({"kind": "device"}, {"kind": "device", "attention": "blockwise"}, {"kind": "device", "attention": "online"}):
         h = models.give(Host(oracle.vtable(), {"default": "bf16", "order": order}).prepare("llama", **c), p)
         h.set_logging(True)
         outs.append(h.call("apply", [ids], (2, 16, c["V"])))
@@ -185,6 +185,9 @@ def test_blockwise_attention_is_its_four_launches_on_the_oracle(oracle):
     assert logs[1].count("attention[blockwise]") == c["L"]
     assert "softmax axis seq2 where" in logs[0] and "softmax axis seq2 where" not in logs[1]
     assert len(logs[0]) - len(logs[1]) == 3 * c["L"]
+    # `attention: online` is the same launch with another way of fusing it allowed: the same definition, the same bits here
+    assert np.array_equal(outs[0].view(np.uint32), outs[2].view(np.uint32))
+    assert logs[2].count("attention[online]") == c["L"] and len(logs[2]) == len(logs[1])
     with pytest.raises(PreskError) as e:
         Host(oracle.vtable(), {"default": "bf16", "order": {"kind": "sequential", "attention": "blockwise"}})
     assert e.value.code == 7005
