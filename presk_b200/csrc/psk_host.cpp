@@ -1390,6 +1390,49 @@ struct psk_host {
         return m;
     }
 
+    // ---- generation with a cache of keys and values -------------------------------------------------------
+    // The reference's serve loop calls the generation function on the whole window for every new token
+    // (crates/presk-serve/src/lib.rs:241: every position's keys and values are computed again). Every launch of
+    // the decoder treats the rows of (batch, seq) independently except the attention, which reads the keys and
+    // values of the positions before; so the last position's logits need only that position's row through every
+    // launch, plus the earlier positions' keys (after `rope`) and values, which do not change. `prefill` runs a
+    // window as `apply` does and keeps them, a layer each, in the layouts the attention's contractions read:
+    // k [batch, groups, TMAX, hd], v [batch, TMAX, groups, hd]; `step` runs one new position a sequence against
+    // them. Under the sequential order `step`'s logits are the bits of the last row of `apply` on the whole
+    // window: the same launches on the same numbers in the same order, fewer rows of them.
+    enum KvMode { KV_OFF, KV_PREFILL, KV_STEP };
+    struct KvCache {
+        int64_t batch = 0, tmax = 0, len = 0;
+        std::vector<Tensor> k, v;
+    } kv;
+    KvMode kv_mode = KV_OFF;
+
+    void kv_store(int64_t l, const Tensor &k, const Tensor &v, int64_t at)
+    {
+        const int64_t B = k.axes[0].len, G = k.axes[1].len, T = k.axes[2].len, HD = k.axes[3].len;
+        if (k.affine || v.affine) raise(PSK_E7005, "prefill: keys or values stored in an affine format are not kept");
+        if ((int64_t)kv.k.size() <= l) { kv.k.resize(l + 1); kv.v.resize(l + 1); }
+        if (!kv.k[l].st) {
+            kv.k[l] = fresh({{"batch", B}, {"groups", G}, {"seq2", kv.tmax}, {"hd", HD}}, k.dtype);
+            kv.v[l] = fresh({{"batch", B}, {"seq2", kv.tmax}, {"groups", G}, {"hd", HD}}, v.dtype);
+        }
+        if (kv.k[l].dtype != k.dtype || kv.v[l].dtype != v.dtype || kv.k[l].axes[0].len != B) raise(PSK_E7001, "step: the cache was filled under another batch or another type");
+        if (at + T > kv.tmax) raise(PSK_E7001, "the cache holds TMAX = " + std::to_string(kv.tmax) + " positions; position " + std::to_string(at + T - 1) + " does not fit");
+        // copies, not launches of the program: the positions' keys and values to their rows of the cache
+        copy_part("cache k", k.dtype, k.axes, k, k.strides(), 0, kv.k[l], kv.k[l].strides(), at * HD, false);
+        copy_part("cache v", v.dtype, v.axes, v, v.strides(), 0, kv.v[l], kv.v[l].strides(), at * G * HD, false);
+    }
+
+    // The first n positions of a layer's cache, as the attention's operands: views, nothing copied.
+    Tensor kv_view(const Tensor &c, int64_t n)
+    {
+        Tensor v = c;
+        v.vstrides = c.strides();
+        for (auto &a : v.axes)
+            if (a.name == "seq2") a.len = n;
+        return v;
+    }
+
     // llama.psk:86-110. %0 θ, %1 x, %2 mask, %3 φ.
     Tensor llama_attention(int64_t l, const Tensor &x, const Tensor &mask, const Tensor &phi, const Tensor *residual = nullptr, const std::string &add_site = "")
     {
@@ -1409,10 +1452,21 @@ struct psk_host {
         Tensor vd = dot(f + "/%14", x, wv);
         vd.axes.back().name = "kvout";
         Tensor v = split(vd, "kvout", {{"groups", G}, {"hd", HD}});
+        const Tensor *use_mask = &mask;
+        if (kv_mode == KV_PREFILL) kv_store(l, k, v, 0);
+        if (kv_mode == KV_STEP) {
+            // the new position's keys and values join the cache; the attention reads every position so far, all
+            // of them allowed to the new one (the causal mask's last row), so the softmax needs no mask:
+            // with every position allowed the masked nest computes the unmasked one's bits (lower.rs:1368-1419)
+            kv_store(l, k, v, kv.len);
+            k = kv_view(kv.k[l], kv.len + 1);
+            v = kv_view(kv.v[l], kv.len + 1);
+            use_mask = nullptr;
+        }
         Tensor o;
         bool fused_attention = false;
         Tensor hdr, rt;
-        if (rz.blockwise_attention && !calibrating) {
+        if (rz.blockwise_attention && !calibrating && kv_mode != KV_STEP) {
             // the root is computed before the scores here and after them below; neither reads the other
             hdr = scalar(f + "/%18", (double)HD);
             rt = unary(f + "/%19", PSK_SQRT, hdr);
@@ -1425,7 +1479,7 @@ struct psk_host {
                 rt = unary(f + "/%19", PSK_SQRT, hdr);
             }
             Tensor s = binary(f + "/%20", PSK_DIV, se, rt);
-            Tensor a = softmax(f + "/%21", "seq2", s, &mask);
+            Tensor a = softmax(f + "/%21", "seq2", s, use_mask);
             o = ein(f + "/%22", {"batch", "seq", "groups", "per", "hd"}, {{"batch", "groups", "per", "seq", "seq2"}, {"batch", "seq2", "groups", "hd"}}, {&a, &v});
         }
         Tensor w2 = split(split(wo, "headhd", {{"groups", G}, {"rest", P * HD}}), "rest", {{"per", P}, {"hd", HD}});
@@ -1491,6 +1545,43 @@ struct psk_host {
         Tensor logits = llama_apply(ids);
         Tensor ce = cross_entropy("loss/%5", logits, y);
         return reduce_all("loss/%6", PSK_REDUCE_MEAN, ce);
+    }
+
+    // `prefill`: `apply` on a window, keeping every layer's keys and values. `step`: one new position a sequence.
+    Tensor llama_prefill(const Tensor &ids)
+    {
+        kv = KvCache();
+        kv.batch = ids.axes[0].len;
+        kv.tmax = C("TMAX");
+        if (ids.axes[1].len > kv.tmax) raise(PSK_E7001, "prefill: the window is longer than TMAX");
+        struct Restore { psk_host *h; ~Restore() { h->kv_mode = KV_OFF; } } restore{this};
+        kv_mode = KV_PREFILL;
+        Tensor logits = llama_apply(ids);
+        kv.len = ids.axes[1].len;
+        return logits;
+    }
+
+    Tensor llama_step(const Tensor &ids)
+    {
+        if (kv.k.empty()) raise(PSK_E7001, "step: no `prefill` came before");
+        if (ids.axes.size() != 2 || ids.axes[1].len != 1 || ids.axes[0].len != kv.batch) raise(PSK_E7001, "step: one new position a sequence of the prefilled batch: ids [batch, 1]");
+        if (kv.len + 1 > kv.tmax) raise(PSK_E7001, "step: the cache's TMAX = " + std::to_string(kv.tmax) + " positions are used up");
+        const std::string f = "Llama.apply";
+        const int64_t L = C("L");
+        struct Restore { psk_host *h; ~Restore() { h->kv_mode = KV_OFF; } } restore{this};
+        kv_mode = KV_STEP;
+        Tensor e = embed(f + "/%4", param("tok"), ids);
+        e.axes.back().name = "model";
+        // the angles of the new position: the last row of the window's table (a row depends on its position alone)
+        Tensor phi = slice_view("seq", kv.len, kv.len + 1, llama_angles(kv.len + 1));
+        Tensor none; // no mask: see llama_attention
+        Tensor x = e;
+        for (int64_t l = 0; l < L; ++l) x = llama_block(l, x, none, phi);
+        Tensor h = llama_rmsnorm(param("norm.γ"), x);
+        Tensor logits = dot(f + "/%11", h, param("head"));
+        logits.axes.back().name = "vocab";
+        kv.len += 1;
+        return logits;
     }
 
     // examples/spec/layernorm/layernorm.psk; numbering of
@@ -2436,6 +2527,8 @@ struct psk_host {
             if (entry == "apply") { need(1); return llama_apply(in[0]); }
             if (entry == "loss") { need(2); return llama_loss(in[0], in[1]); }
             if (entry == "loss_grad") { need(2); return llama_loss_grad(in[0], in[1]); }
+            if (entry == "prefill") { need(1); return llama_prefill(in[0]); }
+            if (entry == "step") { need(1); return llama_step(in[0]); }
             if (entry == "attention" || entry == "attention3") {
                 // one attention function on given activations [batch, seq, model], with the causal mask and the
                 // angles of its sequence length: examples/spec/rope/rope.psk `attention2` is this with G = H

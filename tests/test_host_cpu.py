@@ -233,3 +233,26 @@ def test_e4m3_weights_are_the_bf16_model_on_rounded_weights(oracle):
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
     plain = models.give(Host(oracle.vtable(), {"default": "bf16"}).prepare("llama", **c), p).call("apply", [ids], (2, 16, c["V"]))
     assert not np.array_equal(plain, want)
+
+
+@pytest.mark.parametrize("rz", ["f32", "bf16", {"default": "bf16", "order": {"kind": "sequential", "launches": "merged"}}])
+def test_step_after_prefill_is_the_whole_window_recomputed(oracle, rz):
+    """Generation with a cache of keys and values: `prefill` on a window, then `step` a new position at a time. The
+    reference recomputes the whole window for every token (presk-serve/src/lib.rs:241); under the sequential order
+    the cached step must give the bits of that recompute's last row, and `prefill` those of `apply`. GQA (G < H)."""
+    c = dict(V=100, D=32, H=4, G=2, FF=64, L=2)
+    p = models.llama_params(c)
+    rng = np.random.default_rng(12)
+    ids = rng.integers(0, c["V"], size=(3, 16), dtype=np.int64)
+    h = models.give(Host(oracle.vtable(), rz).prepare("llama", TMAX=16, **c), p)
+    ref = models.give(Host(oracle.vtable(), rz).prepare("llama", **c), p)
+    first = h.call("prefill", [ids[:, :11]], (3, 11, c["V"]))
+    assert np.array_equal(first.view(np.uint32), ref.call("apply", [ids[:, :11]], (3, 11, c["V"])).view(np.uint32))
+    for t in range(11, 16):
+        got = h.call("step", [ids[:, t:t + 1]], (3, 1, c["V"]))
+        want = ref.call("apply", [ids[:, :t + 1]], (3, t + 1, c["V"]))[:, -1:, :]
+        assert np.array_equal(got.view(np.uint32), np.ascontiguousarray(want).view(np.uint32)), t
+    with pytest.raises(PreskError, match="used up"):
+        h.call("step", [ids[:, :1]], (3, 1, c["V"]))
+    with pytest.raises(PreskError, match="no `prefill`"):
+        ref.prepare("llama", TMAX=8, **c).call("step", [ids[:, :1]], (3, 1, c["V"]))
