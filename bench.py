@@ -53,6 +53,10 @@ WORKLOADS = {
     "llama7b_e4m3w_prefill_b16_t1024": dict(consts=dict(V=32000, D=4096, H=32, G=32, FF=11008, L=32), B=16, T=1024, int8="e4m3fn"),
     # a small shape of the same program, for trying the script out
     "llama_small": dict(consts=dict(V=4096, D=1024, H=8, G=8, FF=2816, L=4), B=4, T=512),
+    # generation: one new token a sequence against a cache of 1024 positions' keys and values (the reference's serve loop
+    # recomputes the window for every token, presk-serve/src/lib.rs:241; this keeps them), batch 16 a GPU
+    "llama7b_decode_b16_ctx1024": dict(kind="decode", consts=dict(V=32000, D=4096, H=32, G=32, FF=11008, L=32), B=16, T=1024),
+    "llama_small_decode": dict(kind="decode", consts=dict(V=4096, D=1024, H=8, G=8, FF=2816, L=4), B=4, T=256),
     # the 2-layer ReLU MLP classifier: Linear{784,256}, ReLU, Linear{256,10}, cross-entropy; batch 4096; all f32 (sequential order: the reference's bits)
     "mlp_b4096": dict(kind="mlp", B=4096),
     # the small GPT decoder: 4 layers, d 128, 4 heads, context 64, vocabulary 65, batch 256; a mixed bf16/f32 assignment
@@ -651,6 +655,112 @@ def run_small(args, name, w):
     print(json.dumps(out, ensure_ascii=False))
 
 
+def run_decode(args, name, w):
+    """Generation with a key/value cache: `prefill` once (untimed), then timed `step` calls, one new token a sequence."""
+    consts, B, T = w["consts"], w["B"], w["T"]
+    rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
+    threads = os.cpu_count() or 1
+    warm = max(args.warmup, 3)
+    tmax = T + warm + 2 * args.steps + 8
+    config = {"workload": name, **consts, "batch_per_gpu": B, "context": T, "global_batch": B * world, "parallelism": f"dp{world} (sequences are independent: no collective)",
+              "realization": "bf16 storage, f32 norm statistics/logits, order device, launches merged; keys and values cached per layer",
+              "l2": "inputs_larger_than_l2 (13.5 GB of weights and the cache stream through every step)"}
+    D, FF, L, V, H = consts["D"], consts["FF"], consts["L"], consts["V"], consts["H"]
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        # the reference has no cache: a new token costs a whole window's prefill (presk-serve/src/lib.rs:241)
+        v, sample = cpu_prefill_tokens_per_s(consts, T, 1, threads, False, direct=True)
+        val = v / (T + 1)
+        print(json.dumps({"impl": "reference", "metric": "generated tokens/sec Llama-7B-shape decode", "value": val, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+                          "ms_per_step": 1e3 * B / val, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 storage, f32 arithmetic", "data": "synthetic", "config": config,
+                          "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": "one generated token = one whole window recomputed, as the reference's serve loop does (no cache): prefill rate / (context + 1); " + sample},
+                          "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        return
+    import torch
+    import torch.distributed as dist
+    from presk_b200 import Executor, Host, abi, shard
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    ex = Executor(local)
+    shapes = param_shapes(consts)
+    host = Host(ex, realization(shapes, False, "blockwise", "merged")).prepare("llama", TMAX=tmax, **consts)
+    for i, (path, (shape, std)) in enumerate(shapes.items()):
+        host.init_param(path, 1000 + i, std, shape)
+    rng = np.random.default_rng(rank)
+    ids = rng.integers(0, V, size=(B, T), dtype=np.int64)
+    nxt = rng.integers(0, V, size=(B, 1), dtype=np.int64)
+    host.call("prefill", [ids], (B, T, V))
+    nxt_dev = ex.upload(nxt)
+    dev_in = [(nxt_dev, abi.I64, (B, 1))]
+    stream = torch.cuda.ExternalStream(ex.stream(), device=torch.device("cuda", local))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        ex.sync()
+        torch.cuda.synchronize()
+
+    for _ in range(warm):
+        host.call_device("step", dev_in)
+    ex.sync()
+    _, k0 = ex.counts()
+    l0 = ex.counts()[0]
+    sampler = ClockSampler(local)
+    barrier()
+    sampler.start()
+    ex.set_profiling(True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        host.call_device("step", dev_in)
+    e1.record(stream)
+    barrier()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1)
+    rows = ex.profile()
+    ex.set_profiling(False)
+    l1, k1 = ex.counts()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        logits = host.call("step", [nxt], (B, 1, V))
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    ms = shard.max_over_ranks(ms, device="cuda")
+    e2e_ms = shard.max_over_ranks(e2e_s * 1e3, device="cuda")
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    peaks = load_peaks()
+    hbm_peak = peaks.get("hbm_gbs") or 6650.0
+    by = profile_table(rows)
+    # what a step must read: every weight once, and the cache's keys and values of the positions so far
+    ctx_mid = T + warm + args.steps / 2.0
+    weight_bytes = 2.0 * (L * (4 * D * D + 3 * D * FF) + D * V)
+    cache_bytes = 2.0 * 2.0 * L * B * ctx_mid * D
+    achieved = (weight_bytes + cache_bytes) * args.steps / (ms * 1e-3) / 1e9
+    tokens = B * world * args.steps
+    out = {"metric": "generated tokens/sec Llama-7B-shape decode", "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": ms / args.steps,
+           "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 storage, f32 accumulation", "data": "synthetic", "config": config,
+           "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": int(nxt.nbytes), "d2h_bytes_per_step": int(logits.nbytes)},
+           "gpu_launches": int(k1 - k0), "launches_per_step": int((l1 - l0) / args.steps), "clocks": clocks,
+           "roofline": {"bound": "hbm", "kernel": "the whole step (weights and cache read once)", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak, "traffic": None,
+                        "algorithmic_bytes_per_step": weight_bytes + cache_bytes, "peak_source": "measured (MEASURED_PEAKS.json, copy bandwidth)" if peaks else "fallback",
+                        "kernel_ms_per_step": sum(d[1] for d in by.values()) / args.steps},
+           "kernel_shares": shares_of(by)}
+    if world == 1 and not args.no_cpu_baseline:
+        try:
+            v, sample = cpu_prefill_tokens_per_s(consts, T, 1, threads, False)
+            out["cpu_baseline"] = {"value": v / (T + 1), "unit": "tokens/s", "cores": threads, "kind": "port", "sample": "one generated token = one whole window recomputed, as the reference's serve loop does (no cache): prefill rate / (context + 1); " + sample}
+        except Exception as e:
+            out["cpu_baseline"] = {"value": None, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": f"failed: {e}"}
+    print(json.dumps(out, ensure_ascii=False))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--micro", default=None, choices=["gemm", "gemm_i8", "softmax", "ew", "attn", "norm", "e8m15", "f32c", "train", "rmsnorm", "rope", "xent"])
@@ -670,6 +780,8 @@ def main():
     if args.micro:
         return microbench(args)
     w = WORKLOADS[args.workload]
+    if w.get("kind") == "decode":
+        return run_decode(args, args.workload, w)
     if w.get("kind", "llama") != "llama":
         return run_small(args, args.workload, w)
     consts, B, T = w["consts"], w["B"], w["T"]

@@ -400,6 +400,43 @@ int launch_tc(psk_exec *e, const psk_gemm &g, const void *a, const void *b, void
     return PSK_OK;
 }
 
+// A contraction of a few rows against a large second operand (one new position a sequence against a weight
+// matrix): the tensor-core kernel's tiles are 128 rows by 256 columns, so n / 256 CTAs would stream the whole
+// matrix while the other SMs idle. Here the summed axis is cut into `parts` runs, each a batch entry of one launch
+// (tiles = parts · n / 256), whose f32 partial sums k_sum_parts adds in the runs' order: a declared order of the
+// sum like any other of PSK_ORDER_DEVICE, fixed by the shape alone. Returns PSK_E7001 when the shape does not
+// take it (the caller then launches the contraction whole).
+int launch_tc_few_rows(psk_exec *e, const psk_gemm &g, const void *a, const void *b, void *c, uint32_t *flag, const float *col_scale, int64_t cs_stride, const void *addend, int site_dtype)
+{
+    static const bool on = getenv("PSK_GEMM_SPLITK") ? atoi(getenv("PSK_GEMM_SPLITK")) != 0 : true;
+    const bool a_m_major = (g.b_n_major & 2) != 0;
+    if (!on || g.batch != 1 || g.m > 32 || a_m_major || g.k < 1024 || g.n < 256) return PSK_E7001;
+    if (g.c_row_lo_count < g.m || g.c_col_lo_count < g.n) return PSK_E7001; // a result laid out in levels: not here
+    const int64_t tiles_n = (g.n + 255) / 256;
+    int64_t parts = 1;
+    while (parts * 2 * tiles_n <= (int64_t)e->sms + e->sms / 4 && g.k % (parts * 2) == 0 && (g.k / (parts * 2)) % 64 == 0 && g.k / (parts * 2) >= 256) parts *= 2;
+    if (parts < 2) return PSK_E7001;
+    const int64_t kc = g.k / parts;
+    float *partial = (float *)psk_exec_alloc(e, (size_t)parts * g.m * g.n * 4);
+    if (!partial) return fail(e, PSK_E10001, "tensor-core contraction: no memory for the partial sums");
+    psk_gemm pg = g;
+    pg.out_dtype = PSK_F32; pg.guarded = 0;
+    pg.k = kc; pg.batch = parts; pg.batch_lo = parts;
+    pg.a_lo = kc; pg.a_hi = 0;                                   // a run of the summed axis further along each row
+    pg.b_lo = (g.b_n_major & 1) ? kc * g.b_row : kc; pg.b_hi = 0; // N-major: kc rows down; K-major: kc along each row
+    pg.c_row_lo_count = g.m; pg.c_row_lo = g.n; pg.c_row_hi = 0;
+    pg.c_col_lo_count = g.n; pg.c_col_hi = 0;
+    pg.c_lo = g.m * g.n; pg.c_hi = 0;
+    pg.scale_on = 0;
+    int r = launch_tc(e, pg, a, b, partial, e->flags);
+    if (r == PSK_OK) {
+        k_sum_parts<<<grid_for(e, g.m * g.n, 256, 8), 256, 0, e->stream>>>(partial, (int)parts, g.m, g.n, c, g.out_dtype, site_dtype, g.c_row_lo, addend, g.c_row_lo, col_scale, cs_stride, g.guarded, flag);
+        e->kernels += 1;
+    }
+    psk_exec_free(e, partial); // handed out again only to later work of the same stream
+    return r;
+}
+
 // A tensor map over 8-bit codes: dimensions and strides in elements (= bytes).
 bool make_map_u8(psk_exec *e, CUtensorMap *map, const void *base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t d3, uint64_t s1, uint64_t s2, uint64_t s3, uint32_t box0, uint32_t box1)
 {
@@ -1010,7 +1047,8 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
                 pg.c_col_lo_count = g.c_col_lo_count; pg.c_col_hi = g.c_col_hi; pg.c_lo = g.c_lo; pg.c_hi = g.c_hi;
                 if (g.m == 1) pg.a_row = g.k;
                 std::string keep = e->error;
-                int r = launch_tc(e, pg, A.p, wide, const_cast<void *>(L.out.p), L.ovf, w8 ? B.scales : nullptr, w8 ? g.bs_n : 0, w8 ? g.bs_lo : 0, w8 ? g.bs_hi : 0);
+                int r = launch_tc_few_rows(e, pg, A.p, wide, const_cast<void *>(L.out.p), L.ovf, w8 ? B.scales : nullptr, w8 ? g.bs_n : 0, nullptr, L.out.dtype);
+                if (r == PSK_E7001) { e->error = keep; r = launch_tc(e, pg, A.p, wide, const_cast<void *>(L.out.p), L.ovf, w8 ? B.scales : nullptr, w8 ? g.bs_n : 0, w8 ? g.bs_lo : 0, w8 ? g.bs_hi : 0); }
                 if (r == PSK_OK) {
                     e->last_kernel = "k_gemm_tc";
                     e->last_flops = 2.0 * (double)g.m * (double)g.n * (double)g.k * (double)g.batch;
@@ -1081,7 +1119,8 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
             if (g.m == 1 && !a_m_major) pg.a_row = g.k; // a single row: any stride of 16 bytes will do
             if (g.n == 1) pg.b_row = g.k;
             std::string keep = e->error;
-            rc = launch_tc(e, pg, A.p, B.p, const_cast<void *>(L.out.p), L.ovf);
+            rc = launch_tc_few_rows(e, pg, A.p, B.p, const_cast<void *>(L.out.p), L.ovf, nullptr, 0, nullptr, L.out.dtype);
+            if (rc == PSK_E7001) { e->error = keep; rc = launch_tc(e, pg, A.p, B.p, const_cast<void *>(L.out.p), L.ovf); }
             e->last_kernel = "k_gemm_tc";
             e->last_flops = 2.0 * (double)g.m * (double)g.n * (double)g.k * (double)g.batch;
             if (rc == PSK_E7001) { rc = PSK_OK; e->error = keep; tc_ok = false; } // strides no tensor map takes: the exact kernel
@@ -1337,7 +1376,9 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
             bp = widened_weights(e, B.p, l->in[1].numel, b_int8);
             if (!bp) { rc = fail(e, PSK_E7005, nm + ": no memory for the weights' bf16 copy"); break; }
         }
-        int r = launch_tc(e, pg, A.p, bp, const_cast<void *>(L.out.p), L.ovf, b_int8 ? B.scales : nullptr, b_int8 ? g.bs_n : 0, b_int8 ? g.bs_lo : 0, b_int8 ? g.bs_hi : 0, 0, 2, X.p);
+        std::string keep_err = e->error;
+        int r = launch_tc_few_rows(e, pg, A.p, bp, const_cast<void *>(L.out.p), L.ovf, b_int8 ? B.scales : nullptr, b_int8 ? g.bs_n : 0, X.p, (int)l->iparam[1]);
+        if (r == PSK_E7001) { e->error = keep_err; r = launch_tc(e, pg, A.p, bp, const_cast<void *>(L.out.p), L.ovf, b_int8 ? B.scales : nullptr, b_int8 ? g.bs_n : 0, b_int8 ? g.bs_lo : 0, b_int8 ? g.bs_hi : 0, 0, 2, X.p); }
         if (r == PSK_E7001) { rc = fail(e, PSK_E7005, nm + ": " + e->error); break; } // strides no tensor map or staged epilogue takes: the caller's two launches
         rc = r;
         e->last_kernel = "k_gemm_tc";

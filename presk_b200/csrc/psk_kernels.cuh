@@ -1414,4 +1414,30 @@ __global__ void k_split_e8m15(const uint8_t *src, int64_t rows, int64_t cols, in
         d[plane_stride] = (uint16_t)lo;
     }
 }
+
+// The parts of a contraction whose summed axis was cut into `parts` runs (a few rows against a large weight matrix:
+// each run a tensor-core launch of its own batch entry, so that every SM streams a share of the weights): the f32
+// partial sums added in the runs' order, scaled by the column's scale when the weights are integers, rounded to
+// the contraction's own site's type, then, with an addend, added to it and rounded to the result's type
+// (PSK_OP_CONTRACT_ADD's two roundings). Rows of the result at `row_stride` elements.
+__global__ void __launch_bounds__(256) k_sum_parts(const float *parts_p, int parts, int64_t m, int64_t n, void *out, int out_dtype, int site_dtype, int64_t row_stride,
+                                                   const void *addend, int64_t add_row_stride, const float *col_scale, int64_t col_scale_stride, int guarded, uint32_t *ovf_flag)
+{
+    uint32_t ovf = 0;
+    const int64_t total = m * n, step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step) {
+        const int64_t r = i / n, c = i - r * n;
+        float acc = parts_p[i];
+        for (int p = 1; p < parts; ++p) acc = __fadd_rn(acc, parts_p[(int64_t)p * total + i]);
+        if (col_scale) acc = __fmul_rn(acc, col_scale[c * col_scale_stride]);
+        if (addend) {
+            uint32_t o2 = 0;
+            const float site = edge_round(acc, site_dtype, PSK_F32, &o2); // as the contraction's site would store it
+            ovf |= o2;
+            acc = __fadd_rn(load_real(addend, out_dtype, r * add_row_stride + c), site);
+        }
+        ovf |= store_real(out, out_dtype, r * row_stride + c, acc);
+    }
+    if (guarded && ovf) atomicOr(ovf_flag, 1u);
+}
 } // namespace psk

@@ -468,3 +468,43 @@ def test_llama_gradient_device_order_within_tolerance(cuda, oracle):
         want, got = want_h.result(k, np.shape(v)), h.result(k, np.shape(v))
         assert np.isfinite(got).all(), k
         assert np.abs(got - want).max() <= 0.06 * np.abs(want).max(), (k, np.abs(got - want).max(), np.abs(want).max())
+
+
+def test_step_after_prefill_on_the_gpu(cuda, oracle):
+    """Generation with a cache of keys and values on the CUDA executor. Sequential order: `prefill` then three
+    `step`s give the oracle's bits, which are those of recomputing the whole window (tests/test_host_cpu.py).
+    Device order at a width where a step's contractions are cut along the summed axis (k >= 1024, a few rows
+    against a large weight matrix, partial sums added in the runs' order): within the bf16 tolerance of the
+    sequential result, with bf16, int8 and e4m3fn weights."""
+    c = dict(V=512, D=1024, H=8, G=4, FF=2048, L=2)
+    p = models.llama_params(c)
+    rng = np.random.default_rng(21)
+    ids = rng.integers(0, c["V"], size=(4, 131), dtype=np.int64)
+    base = {"default": "bf16", "params": {k: "bf16" for k in p}, "storage": {"Llama.apply/%11": "f32", "RMSNorm.apply/%3": "f32", "RMSNorm.apply/%7": "f32"}}
+
+    def run(ex, rz):
+        h = models.give(Host(ex, rz).prepare("llama", TMAX=256, **c), p)
+        outs = [h.call("prefill", [ids[:, :128]], (4, 128, c["V"]))[:, -1:, :]]
+        for t in range(128, 131):
+            outs.append(h.call("step", [ids[:, t:t + 1]], (4, 1, c["V"])))
+        return np.concatenate(outs, axis=1)
+
+    want = run(oracle.vtable(), dict(base, order={"kind": "sequential"}))
+    got = run(cuda, dict(base, order={"kind": "sequential"}))
+    assert_same_bits(got, want)
+    cuda.set_profiling(True)
+    dev = run(cuda, dict(base, order={"kind": "device", "attention": "blockwise", "launches": "merged"}))
+    prof = cuda.profile()
+    cuda.set_profiling(False)
+    assert sum(1 for rec in prof if rec[0] == "k_gemm_tc") > 7 * c["L"] * 4
+    assert np.abs(dev - want).max() <= 2.0**-6 * np.abs(want).max()
+    for weights in ("int8", "e4m3fn"):
+        rz = dict(base, order={"kind": "sequential"})
+        if weights == "int8":
+            rz["params"] = {k: "bf16" for k in p if k not in NARROW}
+            rz["quant"] = {k: {"bits": 8, "over": -2} for k in NARROW}
+        else:
+            rz["params"] = {k: ("e4m3fn" if k in NARROW else "bf16") for k in p}
+        w_want = run(oracle.vtable(), rz)
+        w_dev = run(cuda, dict(rz, order={"kind": "device", "launches": "merged"}))
+        assert np.abs(w_dev - w_want).max() <= 2.0**-5 * np.abs(w_want).max(), weights
