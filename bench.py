@@ -540,7 +540,13 @@ def small_case(name, w):
     rng = np.random.default_rng(n)
     x = rng.standard_normal((n, n), dtype=np.float32)
     wt = rng.standard_normal((n, n), dtype=np.float32)
-    return dict(model="contract_ln", consts={}, rz={"default": dt, "order": {"kind": "device"}}, params={"ln.γ": np.ones(n, np.float32), "ln.β": np.zeros(n, np.float32)}, inputs=[x, wt], entry="apply",
+    rz = {"default": dt, "order": {"kind": "device"}}
+    if dt == "f16" and n >= 4096:
+        # a row of x·w has deviations of about sqrt(n) a term, so the squared deviations of LayerNorm pass binary16's
+        # largest number (65504) from n = 4096 on and the all-f16 program stops with E7007, as the reference's does;
+        # that one site is kept in f32 here (what a solved realization would do), everything else stays binary16
+        rz["storage"] = {"LayerNorm.apply/%5": "f32"}
+    return dict(model="contract_ln", consts={}, rz=rz, params={"ln.γ": np.ones(n, np.float32), "ln.β": np.zeros(n, np.float32)}, inputs=[x, wt], entry="apply",
                 units=2.0 * n * n * n / 1e12, unit="TFLOP/s", metric=f"TFLOP/s (2·N^3) of x·w + row LayerNorm, N={n}, stored {dt}", flops=2.0 * n * n * n, dtype=f"{dt} storage, f32 accumulation", order="device", out_shape=(n, n))
 
 
@@ -556,7 +562,7 @@ def small_cpu(case, w, threads):
     h = models.give(Host(orc.vtable(), rz).prepare(case["model"], **case["consts"]), case["params"])
     inputs, frac, note = case["inputs"], 1.0, "full size"
     if w["kind"] == "contract_ln" and w["N"] > 4096:
-        rows = 1024  # every row of x is an independent 1/N of the work (its row of the product, its LayerNorm)
+        rows = 256  # every row of x is an independent 1/N of the work (its row of the product, its LayerNorm)
         inputs = [np.ascontiguousarray(inputs[0][:rows]), inputs[1]]
         frac, note = rows / w["N"], f"{rows} of the {w['N']} rows of x (rows are independent; time scaled by {w['N'] // rows})"
     out_shape = case.get("out_shape", ())
@@ -601,7 +607,6 @@ def run_small(args, name, w):
     _, k0 = ex.counts()
     sampler = ClockSampler(local)
     sampler.start()
-    ex.set_profiling(True)
     ms = 0.0
     evs = []
     for _ in range(args.steps):
@@ -616,9 +621,13 @@ def run_small(args, name, w):
     torch.cuda.synchronize()
     clocks = sampler.stop()
     ms = sum(a.elapsed_time(b) for a, b in evs)
+    _, k1 = ex.counts()
+    # the kernels' shares from a pass of its own: events around every launch cost a launch-bound step more than they tell
+    ex.set_profiling(True)
+    for _ in range(args.steps):
+        host.call_device(case["entry"], dev_inputs)
     rows = ex.profile()
     ex.set_profiling(False)
-    _, k1 = ex.counts()
     # end to end: host arrays in, the result read back, every step
     out_shape = case.get("out_shape", ())
     for _ in range(2):

@@ -156,7 +156,16 @@ typedef struct {
  * bit-defining; DEVICE is this executor's declared reassociation (tensor-core
  * tiles for contractions, shuffle trees for row reductions), as `chunked` and
  * `interleaved` are the reference's. */
-typedef enum { PSK_ORDER_SEQUENTIAL = 0, PSK_ORDER_DEVICE = 1 } psk_order;
+typedef enum {
+    PSK_ORDER_SEQUENTIAL = 0,
+    PSK_ORDER_DEVICE = 1,
+    PSK_ORDER_CHUNKED = 2 /* the reference's `chunked(size)` (presk-rt/src/lib.rs:264-269; the nest at
+                             presk-kernel/src/lower.rs:424-457): a contraction over ONE summed axis adds its terms in
+                             chunks of `order_size` consecutive ones, each chunk from zero in index order, the chunks'
+                             sums then in order from zero, the last chunk shorter. Exact on this executor's scalar
+                             kernels: the reference's bits. Every other operation keeps the sequential order, as in
+                             the reference (lower.rs:262-266). */
+} psk_order;
 
 typedef enum {
     PSK_REDUCE_SUM = 0, PSK_REDUCE_MEAN = 1, PSK_REDUCE_SUMSQ = 2,
@@ -214,7 +223,7 @@ typedef struct {
                            operands are read as integer counts in their scales' unit, the products and the
                            sum are exact integers wrapped to 32 bits, and the store rounds the exact value
                            sum·s0·s1 once into the output's format */
-    int32_t reserved;
+    int32_t order_size; /* PSK_ORDER_CHUNKED: the chunk's length (at least 1) */
     int64_t iparam[4];  /* reduce: the divisor of a mean; copy/iota: see psk_host.cpp */
     double fparam[2];   /* fill: the value */
 } psk_launch;

@@ -695,6 +695,7 @@ int psk_oracle_run(const psk_launch *l, void *const *table, uint32_t *overflow)
     if (l->op == PSK_OP_ROPE) return rope_unfused(l, table, overflow);
     if (l->op == PSK_OP_ATTENTION) return attention_unfused(l, table, overflow);
     if (l->op == PSK_OP_RMSNORM) return rmsnorm_unfused(l, table, overflow);
+    if (l->op == PSK_OP_CONTRACT && l->order == PSK_ORDER_CHUNKED && l->n_inner != 1) return PSK_E7005; /* lower.rs:429-431: a chunked order sums ONE summed axis */
     if (l->op == PSK_OP_CONTRACT && l->n_inner > 1) {
         psk_launch m = *l;
         int no = l->n_outer, w = 0;
@@ -808,7 +809,8 @@ static int psk_oracle_run_merged(const psk_launch *l, void *const *table, uint32
          * is carried by operand 1 alone, contiguously, a block of JB results is summed at once, each still
          * adding its own terms in increasing k, so the bits are those of the loop below. It is the form the
          * reference's executors run, and what makes this restatement a fair CPU baseline. */
-        if (ni == 1 && l->n_inputs == 2 && no >= 1 && l->in[0].stride[no - 1] == 0 && l->in[1].stride[no - 1] == 1 && l->out.stride[no - 1] == 1
+        if (l->order == PSK_ORDER_CHUNKED && (ni != 1 || l->n_inputs != 2 || l->order_size < 1)) return PSK_E7005; /* lower.rs:429-431: one summed axis, two operands */
+        if (l->order != PSK_ORDER_CHUNKED && ni == 1 && l->n_inputs == 2 && no >= 1 && l->in[0].stride[no - 1] == 0 && l->in[1].stride[no - 1] == 1 && l->out.stride[no - 1] == 1
             && l->in[0].dtype != PSK_I8 && (l->in[1].dtype == PSK_BF16 || l->in[1].dtype == PSK_F32 || l->in[1].dtype == PSK_I8)
             && edge_is_identity(kd, l->in[1].dtype) && inner > 0) {
             enum { JB = 64, RB = 8 };
@@ -884,7 +886,21 @@ static int psk_oracle_run_merged(const psk_launch *l, void *const *table, uint32
                 sbase[i] = offset_of(l->in[i].scale_stride, l->dims, 0, no, lin);
             }
             float acc = 0.0f;
-            if (ni == 1 && l->n_inputs == 2) {
+            if (ni == 1 && l->n_inputs == 2 && l->order == PSK_ORDER_CHUNKED) {
+                /* lower.rs:424-457: part = 0; the chunk's terms in order; acc = acc + part; the last chunk shorter */
+                const int64_t s0 = l->in[0].stride[no], s1 = l->in[1].stride[no], q0 = l->in[0].scale_stride[no], q1 = l->in[1].scale_stride[no];
+                const int64_t size = l->order_size;
+                for (int64_t c0 = 0; c0 < inner; c0 += size) {
+                    float part = 0.0f;
+                    for (int64_t c = c0; c < inner && c < c0 + size; ++c) {
+                        float x = load_operand(&in[0], base[0] + c * s0, sbase[0] + c * q0, kd, &ovf);
+                        float w = load_operand(&in[1], base[1] + c * s1, sbase[1] + c * q1, kd, &ovf);
+                        float prod = x * w;
+                        part = part + prod;
+                    }
+                    acc = acc + part;
+                }
+            } else if (ni == 1 && l->n_inputs == 2) {
                 const int64_t s0 = l->in[0].stride[no], s1 = l->in[1].stride[no], q0 = l->in[0].scale_stride[no], q1 = l->in[1].scale_stride[no];
                 for (int64_t c = 0; c < inner; ++c) {
                     float x = load_operand(&in[0], base[0] + c * s0, sbase[0] + c * q0, kd, &ovf);

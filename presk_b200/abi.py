@@ -26,7 +26,7 @@ OP_FUSED, OP_CONTRACT, OP_REDUCE, OP_SOFTMAX, OP_XENT, OP_ARGMAX, OP_EMBED, OP_C
 # psk_prim
 (ADD, SUB, MUL, DIV, MAX, MIN, NEG, EXP, LOG, TANH, SQRT, SIN, COS, ABS, GELU, GELU_DERIV, RELU, HEAVISIDE, SIGN, SIGMOID, POW, REAL, DIV_N, ROUND) = range(24)
 
-ORDER_SEQUENTIAL, ORDER_DEVICE = 0, 1
+ORDER_SEQUENTIAL, ORDER_DEVICE, ORDER_CHUNKED = 0, 1, 2
 REDUCE_SUM, REDUCE_MEAN, REDUCE_SUMSQ, REDUCE_SUM_STORED = 0, 1, 2, 3
 COMM_U32 = 100
 COMM_SUM, COMM_MAX, COMM_MIN = 0, 1, 2
@@ -52,7 +52,7 @@ class Launch(C.Structure):
         ("n_inputs", C.c_int32), ("n_outer", C.c_int32), ("n_inner", C.c_int32),
         ("dims", C.c_int64 * MAX_AXES), ("inputs", Operand * MAX_INPUTS), ("out", Operand),
         ("n_steps", C.c_int32), ("steps", Step * MAX_STEPS),
-        ("kind", C.c_int32), ("masked", C.c_int32), ("int_accum", C.c_int32), ("reserved", C.c_int32), ("iparam", C.c_int64 * 4), ("fparam", C.c_double * 2),
+        ("kind", C.c_int32), ("masked", C.c_int32), ("int_accum", C.c_int32), ("order_size", C.c_int32), ("iparam", C.c_int64 * 4), ("fparam", C.c_double * 2),
     ]
 
 

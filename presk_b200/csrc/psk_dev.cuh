@@ -25,7 +25,7 @@ struct DevOperand {
 struct DevLaunch {
     int32_t n_in, n_outer, n_inner, kdtype;
     int32_t n_steps, kind, masked, guarded;
-    int32_t int_accum, pad;
+    int32_t int_accum, chunk; // chunk: 0, or the length of a chunk of a contraction's sum (PSK_ORDER_CHUNKED)
     int64_t dims[PSK_MAX_AXES];
     int64_t total; // product of the outer dims
     int64_t inner; // product of the inner dims

@@ -850,6 +850,15 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
     memset(&L, 0, sizeof L);
     L.n_in = l->n_inputs; L.n_outer = l->n_outer; L.n_inner = l->n_inner; L.kdtype = l->dtype;
     L.int_accum = l->int_accum;
+    L.chunk = 0;
+    if (l->order == PSK_ORDER_CHUNKED && (l->op == PSK_OP_CONTRACT || l->op == PSK_OP_CONTRACT_ADD)) {
+        // the reference's chunked(size) (lower.rs:424-457): two operands, one summed axis, on the scalar kernels
+        const std::string nm = l->name ? l->name : "?";
+        if (l->order_size < 1) return fail(e, PSK_E7001, nm + ": the order chunked(" + std::to_string(l->order_size) + ") has no chunk");
+        if (l->n_inner != 1 || l->n_inputs != 2 || l->op != PSK_OP_CONTRACT) return fail(e, PSK_E7005, nm + ": the order chunked(" + std::to_string(l->order_size) + ") sums the product of two operands over one summed axis in chunks");
+        if (l->int_accum) return fail(e, PSK_E7005, nm + ": integer sums are exact under every order; state none for them");
+        L.chunk = l->order_size;
+    }
     L.n_steps = l->n_steps; L.kind = l->kind; L.masked = l->masked; L.guarded = l->guarded && (l->out.dtype == PSK_F16 || l->out.dtype == PSK_E8M15 || l->dtype == PSK_F16 || l->dtype == PSK_E8M15);
     for (int a = 0; a < naxes; ++a) L.dims[a] = l->dims[a];
     int scale_slot = l->n_inputs + 1;
@@ -1138,10 +1147,11 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
                 G.c_col_lo_count = g.c_col_lo_count; G.c_col_lo = g.c_col_lo; G.c_col_hi = g.c_col_hi;
                 G.b_scales = B.scales; G.b_sj = g.bs_n; G.b_slo = g.bs_lo; G.b_shi = g.bs_hi;
                 G.ovf = L.ovf; G.guarded = L.guarded;
+                G.chunk = L.chunk;
                 dim3 grid((unsigned)((g.n + 63) / 64), (unsigned)((g.m + 63) / 64), (unsigned)g.batch);
                 e->last_flops = 2.0 * (double)g.m * (double)g.n * (double)g.k * (double)g.batch;
                 if (grid.y > 65535 || grid.z > 65535) { k_contract_generic<<<grid_for(e, L.total, 256, 8), 256, 0, e->stream>>>(L); e->last_kernel = "k_contract_generic"; }
-                else if (g.m >= 128 && g.n >= 128 && (A.dtype == PSK_F32 || A.dtype == PSK_BF16) && (B.dtype == PSK_F32 || B.dtype == PSK_BF16) && (g.m + 127) / 128 <= 65535) {
+                else if (!L.chunk && g.m >= 128 && g.n >= 128 && (A.dtype == PSK_F32 || A.dtype == PSK_BF16) && (B.dtype == PSK_F32 || B.dtype == PSK_BF16) && (g.m + 127) / 128 <= 65535) {
                     dim3 big((unsigned)((g.n + 127) / 128), (unsigned)((g.m + 127) / 128), (unsigned)g.batch);
                     if (A.dtype == PSK_F32 && B.dtype == PSK_F32) k_gemm_exact_big<PSK_F32, PSK_F32><<<big, 256, 0, e->stream>>>(G);
                     else if (A.dtype == PSK_BF16 && B.dtype == PSK_BF16) k_gemm_exact_big<PSK_BF16, PSK_BF16><<<big, 256, 0, e->stream>>>(G);
@@ -1178,6 +1188,7 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
         else if (may_regroup && L.n_inner == 1 && L.in[0].stride[L.n_outer] == 1 && L.inner >= 64 && (L.inner % 8 != 0 || vec8_operand(L.in[0], L.dims, L.n_outer + 1, false) ))
             k_reduce_rows_tree<<<grid_for(e, L.total * 32, 256, 8), 256, 0, e->stream>>>(L);
         else if (cols) k_reduce_cols_tree<<<(int)std::min<int64_t>((L.total + 31) / 32, (int64_t)e->sms * 2), 1024, 0, e->stream>>>(L);
+        else if (L.n_inner == 1 && L.inner >= 512 && L.total <= (int64_t)e->sms * 4) k_reduce_seq_staged<<<(int)std::max<int64_t>(1, L.total), 256, 0, e->stream>>>(L); // few long sums
         else k_reduce_seq<<<grid_for(e, L.total, 128, 16), 128, 0, e->stream>>>(L);
         e->kernels += 1;
         break;

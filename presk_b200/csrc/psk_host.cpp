@@ -155,6 +155,7 @@ struct Realization {
     std::map<std::string, AffineSpec> scaled;  // sites stored in an affine format (presk-rt/src/lib.rs:287-360)
     std::map<std::string, int> int_sums;        // sites whose `product` and `accum` are i32: 1 product, 2 accum, 3 both
     int order = PSK_ORDER_SEQUENTIAL;
+    int order_size = 0;               // chunked(size)
     bool blockwise_attention = false; // "order": {"kind": "device", "attention": "blockwise"} or "online"
     bool online_attention = false;    // "attention": "online": the one-pass form of the same launch
     bool merged_launches = false;     // "order": {..., "launches": "merged"}: bit-preserving rewrites of the launch list
@@ -208,7 +209,14 @@ struct Realization {
             std::string kind = k ? k->str : "sequential";
             if (kind == "sequential" || kind == "blocked") r.order = PSK_ORDER_SEQUENTIAL;
             else if (kind == "device") r.order = PSK_ORDER_DEVICE;
-            else raise(PSK_E7005, "realization: the order `" + kind + "` is not one this executor has kernels for (sequential, device)");
+            else if (kind == "chunked") {
+                // presk-rt/src/lib.rs:264-269: sums of `size` consecutive terms, then the chunks' sums
+                const Json *sz = o->get("size");
+                if (!sz || sz->kind != Json::Num || sz->num < 1 || sz->num != std::floor(sz->num) || sz->num > 2147483647.0) raise(PSK_E7001, "realization: the order chunked needs a whole `size` of at least 1");
+                r.order = PSK_ORDER_CHUNKED;
+                r.order_size = (int)sz->num;
+            }
+            else raise(PSK_E7005, "realization: the order `" + kind + "` is not one this executor has kernels for (sequential, chunked, device)");
             if (const Json *ml = o->get("launches")) {
                 if (ml->str == "merged") r.merged_launches = true;
                 else if (ml->str != "reference") raise(PSK_E7005, "realization: the launch list `" + ml->str + "` is not one this executor has (reference, merged)");
@@ -485,6 +493,14 @@ struct psk_host {
     {
         l.name = name.c_str();
         l.order = rz.order;
+        l.order_size = rz.order_size;
+        if (rz.order == PSK_ORDER_CHUNKED && !((l.op == PSK_OP_CONTRACT && l.n_inner == 1 && ins.size() == 2 && !l.int_accum))) {
+            // only a contraction of two operands over one summed axis takes a chunked order; every other
+            // launch keeps the sequential one (lower.rs:262-266 `chunked(order)`, 429-431)
+            if (l.op == PSK_OP_CONTRACT && !l.int_accum && l.n_inner > 1) raise(PSK_E7005, name + ": the order chunked(" + std::to_string(rz.order_size) + ") sums one summed axis in chunks, and this sum runs over " + std::to_string(l.n_inner) + " axes");
+            l.order = PSK_ORDER_SEQUENTIAL;
+            l.order_size = 0;
+        }
         l.guarded = 1;
         l.n_inputs = (int)ins.size();
         std::vector<void *> table;
@@ -592,7 +608,7 @@ struct psk_host {
         set_space(l, flat, {});
         set_operand(l.in[0], src, {1}, {0});
         set_operand(l.out, dst, {1}, {0});
-        l.order = rz.order;
+        l.order = rz.order == PSK_ORDER_CHUNKED ? PSK_ORDER_SEQUENTIAL : rz.order;
         l.guarded = 1;
         l.n_inputs = 1;
         l.name = "convert";

@@ -468,19 +468,6 @@ __global__ void __launch_bounds__(1024, 1) k_ew_lut(const __grid_constant__ EwPa
     }
 }
 
-// 16 bytes that will not be read again soon (activations streaming through a row kernel): loaded past the L1,
-// stored with the evict-first hint, so that they do not push the weights and tables others reuse out of the caches.
-PSK_DEV uint4 ld_stream(const void *p)
-{
-    uint4 v;
-    asm volatile("ld.global.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
-PSK_DEV void st_stream(void *p, uint4 v)
-{
-    asm volatile("st.global.cs.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-}
-
 // ---------------------------------------------------------------------------
 // PSK_OP_ROPE for bf16: a thread takes eight rotary positions of one row and
 // writes both halves, so x is read once and the result written once, both as
@@ -523,7 +510,7 @@ __global__ void __launch_bounds__(256, 4) k_rope_bf16(const __grid_constant__ Ro
 
 // ---------------------------------------------------------------------------
 // PSK_OP_RMSNORM under PSK_ORDER_DEVICE, bf16 rows: a warp a row, the row read
-// once into registers and kept there. The bits are those of the four launches it stands for,
+// once into registers. The bits are those of the four launches it stands for,
 // as this executor runs them under the same order:
 //   x*x rounded to bf16 (the square's site);
 //   their f32 sum in k_reduce_rows_tree's grouping (lane l adds the elements of
@@ -543,31 +530,33 @@ struct RmsParams {
 };
 
 template <int NV>
-__global__ void __launch_bounds__(256, NV >= 8 ? 2 : 4) k_rmsnorm_rows(const __grid_constant__ RmsParams P)
+__global__ void __launch_bounds__(256, 4) k_rmsnorm_rows(const __grid_constant__ RmsParams P)
 {
     const int lane = threadIdx.x & 31;
     const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
     const float eps = load_real(P.eps, P.eps_dtype, 0); // widened exactly: the root's group computes in f32
     const float nf = (float)(double)P.n;
-    const uint16_t *gr = P.gamma + lane * 8;
+    constexpr int G = NV < 4 ? NV : 4; // vectors loaded before any is used
     for (int64_t row = warp; row < P.rows; row += nwarps) {
         const uint16_t *xr = P.x + row * P.x_row + lane * 8;
-        // The row is read once, all of it before any of it is used (NV loads of 16 bytes a lane in flight), and
-        // stays in registers between the sum and the scaling: the memory sees x once and the result once.
-        uint4 v[NV];
-#pragma unroll
-        for (int j = 0; j < NV; ++j) v[j] = ld_stream(xr + j * 256);
-        // the sum of the rounded squares, vector by vector in index order
+        // pass 1: the sum of the rounded squares, vector by vector in index order. The row is not kept in
+        // registers (that would leave one block an SM); the second pass finds it in the L1 or the L2.
         float acc = 0.0f;
+#pragma unroll 1
+        for (int j0 = 0; j0 < NV; j0 += G) {
+            uint4 v[G];
 #pragma unroll
-        for (int j = 0; j < NV; ++j) {
-            const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+            for (int j = 0; j < G; ++j) v[j] = *reinterpret_cast<const uint4 *>(xr + (j0 + j) * 256);
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const float lo = bits_f32(w[q] << 16), hi = bits_f32(w[q] & 0xffff0000u);
-                const uint32_t sq = pack_bf16x2_hw(__fmul_rn(lo, lo), __fmul_rn(hi, hi));
-                acc = __fadd_rn(acc, bits_f32(sq << 16));
-                acc = __fadd_rn(acc, bits_f32(sq & 0xffff0000u));
+            for (int j = 0; j < G; ++j) {
+                const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float lo = bits_f32(w[q] << 16), hi = bits_f32(w[q] & 0xffff0000u);
+                    const uint32_t sq = pack_bf16x2_hw(__fmul_rn(lo, lo), __fmul_rn(hi, hi));
+                    acc = __fadd_rn(acc, bits_f32(sq << 16));
+                    acc = __fadd_rn(acc, bits_f32(sq & 0xffff0000u));
+                }
             }
         }
 #pragma unroll
@@ -577,18 +566,27 @@ __global__ void __launch_bounds__(256, NV >= 8 ? 2 : 4) k_rmsnorm_rows(const __g
         const float rr = __frcp_rn(root);
         const bool ok = div_by_in_range(root);
         uint16_t *orow = P.out + row * P.out_row + lane * 8;
+        const uint16_t *gr = P.gamma + lane * 8;
+#pragma unroll 1
+        for (int j0 = 0; j0 < NV; j0 += G) {
+            uint4 v[G], g[G];
 #pragma unroll
-        for (int j = 0; j < NV; ++j) {
-            const uint4 g = *reinterpret_cast<const uint4 *>(gr + j * 256); // gamma: 2·n bytes, in the L1 after the first row
-            const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
-            const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
-            uint32_t o[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const float lo = div_by_checked(bits_f32(w[q] << 16), root, rr, ok), hi = div_by_checked(bits_f32(w[q] & 0xffff0000u), root, rr, ok);
-                o[q] = pack_bf16x2_hw(__fmul_rn(lo, bits_f32(gw[q] << 16)), __fmul_rn(hi, bits_f32(gw[q] & 0xffff0000u)));
+            for (int j = 0; j < G; ++j) {
+                v[j] = *reinterpret_cast<const uint4 *>(xr + (j0 + j) * 256);
+                g[j] = *reinterpret_cast<const uint4 *>(gr + (j0 + j) * 256);
             }
-            st_stream(orow + j * 256, make_uint4(o[0], o[1], o[2], o[3]));
+#pragma unroll
+            for (int j = 0; j < G; ++j) {
+                const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+                const uint32_t gw[4] = {g[j].x, g[j].y, g[j].z, g[j].w};
+                uint32_t o[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float lo = div_by_checked(bits_f32(w[q] << 16), root, rr, ok), hi = div_by_checked(bits_f32(w[q] & 0xffff0000u), root, rr, ok);
+                    o[q] = pack_bf16x2_hw(__fmul_rn(lo, bits_f32(gw[q] << 16)), __fmul_rn(hi, bits_f32(gw[q] & 0xffff0000u)));
+                }
+                *reinterpret_cast<uint4 *>(orow + (j0 + j) * 256) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
         }
     }
 }

@@ -418,7 +418,8 @@ __global__ void __launch_bounds__(256) k_contract_generic(const __grid_constant_
             sbase[i] = scale_offset(L.in[i], L.dims, 0, L.n_outer, lin);
         }
         int64_t ooff = operand_offset(L.out, L.dims, 0, L.n_outer, lin);
-        float acc = 0.0f;
+        float acc = 0.0f, part = 0.0f;
+        const int64_t chunk = L.chunk; // 0: every term in index order; else the reference's chunked(size)
         for (int64_t c = 0; c < L.inner; ++c) {
             float prod = 1.0f;
             for (int i = 0; i < L.n_in; ++i) {
@@ -426,7 +427,12 @@ __global__ void __launch_bounds__(256) k_contract_generic(const __grid_constant_
                 int64_t so = sbase[i] + scale_offset(L.in[i], L.dims, L.n_outer, L.n_inner, c);
                 prod = __fmul_rn(prod, load_operand(L.in[i], o, so, L.kdtype, &ovf));
             }
-            acc = __fadd_rn(acc, prod);
+            if (chunk) {
+                part = __fadd_rn(part, prod);
+                if ((c + 1) % chunk == 0 || c + 1 == L.inner) { acc = __fadd_rn(acc, part); part = 0.0f; }
+            } else {
+                acc = __fadd_rn(acc, prod);
+            }
         }
         ovf |= store_real(const_cast<void *>(L.out.p), L.out.dtype, ooff, acc);
     }
@@ -454,6 +460,7 @@ struct DevGemmExact {
     int64_t b_sj, b_slo, b_shi;
     uint32_t *ovf;
     int guarded;
+    int64_t chunk;                        // 0, or the reference's chunked(size): partial sums of `chunk` terms (k_gemm_exact)
 };
 
 __global__ void __launch_bounds__(256) k_gemm_exact(const __grid_constant__ DevGemmExact G)
@@ -466,11 +473,11 @@ __global__ void __launch_bounds__(256) k_gemm_exact(const __grid_constant__ DevG
     const int64_t aoff = blo * G.a_lo + bhi * G.a_hi, boff = blo * G.b_lo + bhi * G.b_hi, coff = blo * G.c_lo + bhi * G.c_hi;
     const int64_t soff = blo * G.b_slo + bhi * G.b_shi;
     uint32_t ovf = 0;
-    float acc[4][4];
+    float acc[4][4], part[4][4];
 #pragma unroll
     for (int r = 0; r < 4; ++r)
 #pragma unroll
-        for (int c = 0; c < 4; ++c) acc[r][c] = 0.0f;
+        for (int c = 0; c < 4; ++c) acc[r][c] = part[r][c] = 0.0f;
     for (int64_t k0 = 0; k0 < G.k; k0 += 16) {
         // A tile: 64 rows x 16 k; B tile: 16 k x 64 columns; 4 elements a thread each
 #pragma unroll
@@ -505,10 +512,22 @@ __global__ void __launch_bounds__(256) k_gemm_exact(const __grid_constant__ DevG
             for (int r = 0; r < 4; ++r) a[r] = As[kk][ty * 4 + r];
 #pragma unroll
             for (int c = 0; c < 4; ++c) b[c] = Bs[kk][tx * 4 + c];
+            if (G.chunk) {
+                // chunked(size): the term joins its chunk's sum; a full chunk (or the last term) joins the total
+                const bool close = (k0 + kk + 1) % G.chunk == 0 || k0 + kk + 1 == G.k;
 #pragma unroll
-            for (int r = 0; r < 4; ++r)
+                for (int r = 0; r < 4; ++r)
 #pragma unroll
-                for (int c = 0; c < 4; ++c) acc[r][c] = __fadd_rn(acc[r][c], __fmul_rn(a[r], b[c]));
+                    for (int c = 0; c < 4; ++c) {
+                        part[r][c] = __fadd_rn(part[r][c], __fmul_rn(a[r], b[c]));
+                        if (close) { acc[r][c] = __fadd_rn(acc[r][c], part[r][c]); part[r][c] = 0.0f; }
+                    }
+            } else {
+#pragma unroll
+                for (int r = 0; r < 4; ++r)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) acc[r][c] = __fadd_rn(acc[r][c], __fmul_rn(a[r], b[c]));
+            }
         }
         __syncthreads();
     }
@@ -629,6 +648,36 @@ __global__ void __launch_bounds__(128) k_reduce_seq(const __grid_constant__ DevL
             }
         }
         ovf |= store_real(const_cast<void *>(L.out.p), L.out.dtype, ooff, reduce_finish(L, acc));
+    }
+    if (L.guarded && ovf) atomicOr(L.ovf, 1u);
+}
+
+// The sequential order for a few long sums (the mean over every position of a loss): one thread adding its terms
+// one after the other waits a memory latency a term. Here a block owns an output: its threads bring 2048 terms at a
+// time into shared memory, converted as the kernel's loads convert them, and thread 0 adds those in index order.
+// The same additions in the same order as k_reduce_seq; one summed axis, any stride.
+__global__ void __launch_bounds__(256) k_reduce_seq_staged(const __grid_constant__ DevLaunch L)
+{
+    __shared__ float buf[2048];
+    uint32_t ovf = 0;
+    const int64_t s = L.in[0].stride[L.n_outer];
+    for (int64_t lin = blockIdx.x; lin < L.total; lin += gridDim.x) {
+        const int64_t base = operand_offset(L.in[0], L.dims, 0, L.n_outer, lin);
+        float acc = 0.0f;
+        for (int64_t c0 = 0; c0 < L.inner; c0 += 2048) {
+            const int n = (int)(L.inner - c0 < 2048 ? L.inner - c0 : 2048);
+            for (int i = threadIdx.x; i < n; i += blockDim.x) buf[i] = load_operand(L.in[0], base + (c0 + i) * s, 0, L.kdtype, &ovf);
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                for (int i = 0; i < n; ++i) {
+                    const float x = buf[i];
+                    acc = __fadd_rn(acc, L.kind == PSK_REDUCE_SUMSQ ? __fmul_rn(x, x) : x);
+                    if (L.kind == PSK_REDUCE_SUM_STORED) { ovf |= store_overflows(L.out.dtype, acc); acc = prim_unary(PSK_ROUND, acc, L.out.dtype, L.status); }
+                }
+            }
+            __syncthreads();
+        }
+        if (threadIdx.x == 0) ovf |= store_real(const_cast<void *>(L.out.p), L.out.dtype, operand_offset(L.out, L.dims, 0, L.n_outer, lin), reduce_finish(L, acc));
     }
     if (L.guarded && ovf) atomicOr(L.ovf, 1u);
 }
