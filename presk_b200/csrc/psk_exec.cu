@@ -24,6 +24,7 @@
 #include "psk_hot.cuh"
 #include "psk_attn.cuh"
 #include "psk_gemm_i8.cuh"
+#include "psk_gemm_tc2.cuh"
 
 using namespace psk;
 
@@ -390,6 +391,29 @@ int launch_tc(psk_exec *e, const psk_gemm &g, const void *a, const void *b, void
     }
     const int64_t tiles = P.tiles_m * P.tiles_n * g.batch;
     const int grid = (int)std::min<int64_t>(tiles, e->sms);
+    {
+        // The same tiles on pairs of CTAs (psk_gemm_tc2.cuh), for the plain staged epilogues of large row counts.
+        static const bool pair_on = getenv("PSK_GEMM_PAIR") ? atoi(getenv("PSK_GEMM_PAIR")) != 0 : false;
+        const bool plain = P.vec_ok && !g.scale_on && !col_scale && !g.guarded && (g.out_dtype == PSK_BF16 || (g.out_dtype == PSK_F32 && !addend));
+        if (pair_on && mt_rows == 2 && !split_k && !a_m_major && plain && e->sms >= 2) {
+            CUtensorMap pa, pb;
+            bool okp = make_map(e, &pa, a, f16, kphys, (uint64_t)g.m, (uint64_t)g.batch_lo, (uint64_t)batch_hi, (uint64_t)g.a_row, (uint64_t)g.a_lo, (uint64_t)g.a_hi, tc::BK, 128);
+            if (b_n_major) pb = mb;
+            else okp = okp && make_map(e, &pb, b, f16, kphys, (uint64_t)g.n, (uint64_t)g.batch_lo, (uint64_t)batch_hi, (uint64_t)g.b_row, (uint64_t)g.b_lo, (uint64_t)g.b_hi, tc::BK, 128);
+            if (okp) {
+                static bool attr_set = false;
+                if (!attr_set) {
+                    CUDA_TRY(e, cudaFuncSetAttribute(tc2::k_gemm_tc2, cudaFuncAttributeMaxDynamicSharedMemorySize, tc2::SMEM_TOTAL));
+                    attr_set = true;
+                }
+                const int pairs = (int)std::min<int64_t>(tiles, e->sms / 2);
+                tc2::k_gemm_tc2<<<2 * pairs, tc2::THREADS, tc2::SMEM_TOTAL, e->stream>>>(pa, pb, P);
+                CUDA_TRY(e, cudaGetLastError());
+                e->kernels += 1;
+                return PSK_OK;
+            }
+        }
+    }
     if (mt_rows == 2 && col_scale) tc::k_gemm_tc<256, false, 2, true><<<grid, tc::THREADS, tc::Smem<256, 2>::TOTAL, e->stream>>>(ma, mb, P);
     else if (bn == 256 && col_scale) tc::k_gemm_tc<256, false, 1, true><<<grid, tc::THREADS, tc::Smem<256>::TOTAL, e->stream>>>(ma, mb, P);
     else if (mt_rows == 2) tc::k_gemm_tc<256, false, 2><<<grid, tc::THREADS, tc::Smem<256, 2>::TOTAL, e->stream>>>(ma, mb, P);
