@@ -299,6 +299,14 @@ const char *psk_exec_profile(psk_exec *e);
  * caller that times it with its own events. */
 void *psk_exec_stream(psk_exec *e);
 
+/* `presk solve --measure` without the host in the loop: the gap between two results that stay on the device
+ * (presk-driver/src/gap.rs:35-64, `leaf_gap` and `leaf_max`): *gap = the largest |a[i] - b[i]|, *max_abs = the
+ * largest |a[i]|, both in binary64 over the exactly widened elements, an element that is not finite counting as
+ * +infinity (so that a realization that overflowed is never measured on the rest). `a` is the reference result
+ * (budget_abs = budget x *max_abs, gap.rs:35), `b` the candidate's; any two real storage types. Sixteen bytes
+ * come back to the host. */
+int psk_exec_gap(psk_exec *e, const void *a, int32_t a_dtype, const void *b, int32_t b_dtype, int64_t n, double *gap, double *max_abs);
+
 /* A tensor-core contraction on its own, outside a launch: C[b] = A[b]·B[b]
  * with bf16/f16 operands and f32 sums; what PSK_OP_CONTRACT dispatches to
  * under PSK_ORDER_DEVICE. See psk_gemm in csrc/gemm_tc.cuh. */

@@ -135,6 +135,7 @@ PROTOTYPES = {
     "psk_host_launches": (C.c_int64, [C.c_void_p]),
     "psk_host_launch_log": (C.c_char_p, [C.c_void_p]),
     "psk_host_set_logging": (None, [C.c_void_p, C.c_int]),
+    "psk_exec_gap": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_int64, C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "psk_describe": (C.c_int, [C.c_char_p, C.c_int32, C.POINTER(Launch), C.c_char_p, C.c_size_t, C.POINTER(C.c_char_p), C.c_char_p, C.c_size_t]),
 }
 

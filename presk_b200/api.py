@@ -81,6 +81,12 @@ class Executor:
     def gemm(self, g, a, b, c):
         self._check(self.lib.psk_exec_gemm(self.handle, C.byref(g), a, b, c))
 
+    def gap(self, a, a_dtype, b, b_dtype, n):
+        """(largest |a - b|, largest |a|) of two device buffers of n reals: `presk solve --measure`'s gap on the device."""
+        g, m = C.c_double(), C.c_double()
+        self._check(self.lib.psk_exec_gap(self.handle, a, a_dtype, b, b_dtype, n, C.byref(g), C.byref(m)))
+        return g.value, m.value
+
     def sync(self):
         self._check(self.lib.psk_exec_sync(self.handle))
 

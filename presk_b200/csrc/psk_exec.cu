@@ -1516,6 +1516,34 @@ int psk_exec_init_normal(psk_exec *e, void *dst, int to, int64_t n, uint64_t see
     return PSK_OK;
 }
 
+// `presk solve --measure` on the device: the gap between a candidate realization's result and the reference
+// realization's, without bringing either to the host.
+int psk_exec_gap(psk_exec *e, const void *a, int32_t a_dtype, const void *b, int32_t b_dtype, int64_t n, double *gap, double *max_abs)
+{
+    cudaSetDevice(e->device);
+    auto real = [](int d) { return d == PSK_F64 || d == PSK_F32 || d == PSK_BF16 || d == PSK_F16 || d == PSK_E8M15 || d == PSK_E4M3; };
+    if (!real(a_dtype) || !real(b_dtype) || n < 0) return fail(e, PSK_E7001, "psk_exec_gap: two buffers of reals of the same number of elements");
+    unsigned long long *out = (unsigned long long *)psk_exec_alloc(e, 16);
+    if (!out) return PSK_E10001;
+    unsigned long long host[2] = {0, 0};
+    cudaError_t err = cudaMemsetAsync(out, 0, 16, e->stream);
+    if (err == cudaSuccess && n > 0) {
+        k_gap<<<grid_for(e, n, 256, 8), 256, 0, e->stream>>>(a, a_dtype, b, b_dtype, n, out);
+        e->kernels += 1;
+        err = cudaGetLastError();
+    }
+    if (err == cudaSuccess) err = cudaMemcpyAsync(host, out, 16, cudaMemcpyDeviceToHost, e->stream);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(e->stream);
+    psk_exec_free(e, out);
+    if (err != cudaSuccess) return fail(e, PSK_E10001, std::string("psk_exec_gap: ") + cudaGetErrorString(err));
+    double g, m;
+    memcpy(&g, &host[0], 8);
+    memcpy(&m, &host[1], 8);
+    if (gap) *gap = g;
+    if (max_abs) *max_abs = m;
+    return PSK_OK;
+}
+
 // ---- the executor as a table -------------------------------------------------
 static const char *vt_name(void *s) { return psk_exec_name((psk_exec *)s); }
 static void *vt_alloc(void *s, size_t b) { return psk_exec_alloc((psk_exec *)s, b); }

@@ -1489,4 +1489,33 @@ __global__ void __launch_bounds__(256) k_sum_parts(const float *parts_p, int par
     }
     if (guarded && ovf) atomicOr(ovf_flag, 1u);
 }
+
+// The gap between two results (presk-driver/src/gap.rs:35-64): the largest |p - q| over their elements and the
+// largest |p|, both taken in binary64 on the exactly widened values, an element that is not finite counting as
+// +infinity. out[0] = bits of the gap, out[1] = bits of max |p|: non-negative doubles order as their bit
+// patterns do, so the maximum over threads is an integer maximum and the result does not depend on any order.
+__global__ void __launch_bounds__(256) k_gap(const void *a, int a_dtype, const void *b, int b_dtype, int64_t n, unsigned long long *out)
+{
+    const double inf = __longlong_as_double(0x7ff0000000000000ll);
+    double gap = 0.0, mx = 0.0;
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) {
+        const double p = a_dtype == PSK_F64 ? ((const double *)a)[i] : (double)load_real(a, a_dtype, i);
+        const double q = b_dtype == PSK_F64 ? ((const double *)b)[i] : (double)load_real(b, b_dtype, i);
+        double d = fabs(p - q), m = fabs(p);
+        if (!(d <= 1.7976931348623157e308)) d = inf; // a NaN or an infinity
+        if (!(m <= 1.7976931348623157e308)) m = inf;
+        gap = fmax(gap, d);
+        mx = fmax(mx, m);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        gap = fmax(gap, __shfl_xor_sync(0xffffffffu, gap, o));
+        mx = fmax(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    }
+    if ((threadIdx.x & 31) == 0) {
+        atomicMax(out, (unsigned long long)__double_as_longlong(gap));
+        atomicMax(out + 1, (unsigned long long)__double_as_longlong(mx));
+    }
+}
 } // namespace psk

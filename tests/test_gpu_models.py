@@ -508,3 +508,28 @@ def test_step_after_prefill_on_the_gpu(cuda, oracle):
         w_want = run(oracle.vtable(), rz)
         w_dev = run(cuda, dict(rz, order={"kind": "device", "launches": "merged"}))
         assert np.abs(w_dev - w_want).max() <= 2.0**-5 * np.abs(w_want).max(), weights
+
+
+def test_gap_of_a_candidate_realization_measured_on_the_device(cuda):
+    """What `presk solve --measure` does for every candidate (presk-driver/src/gap.rs): the same entry under the
+    reference realization and under a candidate's, the largest difference of the results against budget x max |y|.
+    Both results stay on the executor; psk_exec_gap returns the two numbers, equal to numpy's on the downloads."""
+    from presk_b200 import abi
+    c = models.LLAMA_TINY
+    p = models.llama_params(c)
+    ids = np.random.default_rng(3).integers(0, c["V"], size=(2, 16), dtype=np.int64)
+    pid = cuda.upload(ids)
+    outs = {}
+    hosts = []
+    for name, rz in (("reference", "f32"), ("candidate", {"default": "bf16", "order": {"kind": "device"}})):
+        h = models.give(Host(cuda, rz).prepare("llama", **c), p)
+        hosts.append(h)
+        outs[name] = h.call_device("apply", [(pid, abi.I64, (2, 16))])
+    (pa, da, na), (pb, db, nb) = outs["reference"], outs["candidate"]
+    assert na == nb == 2 * 16 * c["V"] and da == abi.F32 and db == abi.BF16
+    gap, mx = cuda.gap(pa, da, pb, db, na)
+    a = cuda.download(pa, na * 4).view(np.float32).astype(np.float64)
+    b = (cuda.download(pb, nb * 2).view(np.uint16).astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+    assert gap == np.abs(a - b).max() and mx == np.abs(a).max()
+    assert 0 < gap <= 3e-2 * mx  # the bf16 candidate sits inside a 3e-2 budget, as against the exact evaluator
+    cuda.free(pid)

@@ -528,3 +528,26 @@ def test_embed_vjp_bit_exact(cuda, oracle, shape, vocab, d, dtype):
     if n:
         np.add.at(ref, ids.reshape(-1), oracle.widen(ct, dtype, n * d).reshape(n, d).astype(np.float64))
     assert np.abs(g - ref).max() <= (1e-5 if dtype == abi.F32 else 0.1) * max(1.0, np.abs(ref).max())
+
+
+def test_gap_between_two_results_on_the_device(cuda, oracle):
+    """`presk solve --measure`'s gap (presk-driver/src/gap.rs:35-64) without bringing the results back: max |a - b| and
+    max |a| in binary64 over exactly widened elements of any two storage types; one element that is not finite
+    makes the gap infinite."""
+    rng = np.random.default_rng(57)
+    n = 1_000_003
+    a = rng.standard_normal(n).astype(np.float32)
+    b16 = oracle.convert(a, abi.BF16)
+    bv = oracle.widen(b16, abi.BF16, n)
+    pa, pb = cuda.upload(a), cuda.upload(b16)
+    gap, mx = cuda.gap(pa, abi.F32, pb, abi.BF16, n)
+    assert gap == float(np.abs(a.astype(np.float64) - bv.astype(np.float64)).max())
+    assert mx == float(np.abs(a).astype(np.float64).max())
+    a[12345] = np.inf
+    cuda.free(pa)
+    pa = cuda.upload(a)
+    gap, mx = cuda.gap(pa, abi.F32, pb, abi.BF16, n)
+    assert gap == np.inf and mx == np.inf
+    assert cuda.gap(pa, abi.F32, pb, abi.BF16, 0) == (0.0, 0.0)
+    cuda.free(pa)
+    cuda.free(pb)
