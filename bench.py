@@ -164,8 +164,9 @@ def cpu_prefill_tokens_per_s(consts, T, B, threads, int8=False, direct=False, di
     """The CPU restatement of the prefill on a bounded sample of the workload, every timing a median of three
     after a warm-up call:
 
-      * one and two layers of the full width at B = 1, T = 128: the per-layer time and the rest (embedding, final
-        norm, head, loss), both proportional to the number of tokens;
+      * one and three layers of the full width at B = 1, T = 128 (a median of five each: the per-layer time is
+        half their difference, which is multiplied by the depth afterwards, so its noise matters most): the
+        per-layer time and the rest (embedding, final norm, head, loss), both proportional to the number of tokens;
       * the attention function at the workload's own T and at 128 on 16 heads of 128 (32 on a host of more than
         16 threads): the part of a layer that grows with T squared, per head (every head does the same work on
         its own [T, 128] operands);
@@ -187,17 +188,18 @@ def cpu_prefill_tokens_per_s(consts, T, B, threads, int8=False, direct=False, di
     weights = "int8" if int8 is True else ("e4m3fn" if int8 == "e4m3fn" else "bf16")
     fmt = lambda ts: "[" + ", ".join(f"{t:.2f}" for t in ts) + "]"
 
-    c2 = dict(consts, L=2)
+    LN = 3
+    c2 = dict(consts, L=LN)
     p2 = headline.llama_params_f32(c2, seed=0)
     ids = rng.integers(0, consts["V"], size=(1, Ts), dtype=np.int64)
     y = rng.integers(0, consts["V"], size=(1, Ts), dtype=np.int64)
     med, raw = {}, {}
     hosts = {}
-    for L in (1, 2):
+    for L in (1, LN):
         c = dict(consts, L=L)
         p = {k: (np.ascontiguousarray(v[:L]) if k.startswith("blocks.") else v) for k, v in p2.items()}
         h = headline.give(Host(orc.vtable(), headline.realization(p, headline.ORACLE_ORDER, weights)).prepare("llama", **c), p)
-        med[L], raw[L] = time_call(lambda: h.call("loss", [ids, y], ()))
+        med[L], raw[L] = time_call(lambda: h.call("loss", [ids, y], ()), reps=5)
         if L == 1 and direct:
             hosts[1] = h
         else:
@@ -216,13 +218,13 @@ def cpu_prefill_tokens_per_s(consts, T, B, threads, int8=False, direct=False, di
     else:
         quad_head = 0.0
     heads = consts["H"]
-    layer_s = max(med[2] - med[1], 1e-9)
+    layer_s = max((med[LN] - med[1]) / (LN - 1), 1e-9)
     rest_s = max(med[1] - layer_s, 0.0)
     lin_layer_s = max(layer_s - heads * quad_head * Ts * Ts, 0.0)
     up = T / Ts
     layer_T_model = lin_layer_s * up + heads * quad_head * T * T
     rest_T = rest_s * up
-    sample = (f"oracle (C restatement, OpenMP, {threads} threads), warm-up 1 + median of 3 each; B=1, T={Ts}: L=1 {fmt(raw[1])} s, L=2 {fmt(raw[2])} s"
+    sample = (f"oracle (C restatement, OpenMP, {threads} threads), warm-up 1 + median of 3 each (of 5 for the layers); B=1, T={Ts}: L=1 {fmt(raw[1])} s, L={LN} {fmt(raw[LN])} s"
               f" => layer {layer_s:.2f} s, rest {rest_s:.2f} s; attention function on {hs} heads of 128: T={Ts} {fmt(att[Ts][1])} s"
               + (f", T={T} {fmt(att[T][1])} s => {heads * quad_head * T * T:.1f} s a layer of {heads} heads at T={T}" if T > Ts else "")
               + f"; modelled layer at T={T}: {layer_T_model:.1f} s")
@@ -358,6 +360,51 @@ def microbench(args):
         l.out.dtype, l.out.stride[0], l.out.stride[1], l.out.numel = abi.BF16, n, 1, m * n
         ms = timed(lambda: ex.run(l, [a, b, c, sw]), args.steps)
         print(json.dumps({"micro": "gemm_i8", "shape": dims, "ms": ms, "TOP/s": 2.0 * m * n * k / ms / 1e9}))
+    elif args.micro == "contract":
+        # x[m, k] · w[k, n] in bf16 as a contraction launch (what a model's projection issues): with a few rows the
+        # executor cuts the summed axis into runs; the figure that matters then is the rate the weights stream at
+        m, n, k = dims[:3]
+        a, b = ex.upload(bf16((m, k))), ex.upload(bf16((k, n)))
+        c = ex.alloc(m * n * 2)
+        l = launch_desc(abi.OP_CONTRACT, abi.BF16, [m, n], [k], order=abi.ORDER_DEVICE, name=b"dot")
+        l.n_inputs = 2
+        l.inputs[0].dtype, l.inputs[0].stride[0], l.inputs[0].stride[2], l.inputs[0].numel = abi.BF16, k, 1, m * k
+        l.inputs[1].dtype, l.inputs[1].stride[1], l.inputs[1].stride[2], l.inputs[1].numel = abi.BF16, 1, n, k * n
+        l.out.dtype, l.out.stride[0], l.out.stride[1], l.out.numel = abi.BF16, n, 1, m * n
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if len(dims) > 3 and dims[3] else None  # 4th number 1: write 256 MB between calls, so that the weights come from HBM
+
+        def once():
+            if flush is not None:
+                with torch.cuda.stream(stream):
+                    flush.zero_()
+            ex.run(l, [a, b, c])
+
+        ex.set_profiling(True)
+        ms = timed(once, args.steps)
+        rows = ex.profile()
+        ex.set_profiling(False)
+        per = {}
+        for rec in rows[-args.steps:]:
+            per.setdefault(rec[0], []).append(rec[2])
+        print(json.dumps({"micro": "contract", "shape": dims, "ms a call (with the flush, if any)": ms, "kernel ms": {k_: float(np.median(v)) for k_, v in per.items()}, "weights GB": 2.0 * k * n / 1e9,
+                          "GB/s of the weights over the launch's kernels": 2.0 * k * n / 1e6 / sum(float(np.median(v)) for v in per.values())}))
+    elif args.micro == "attn_step":
+        # one new position against a cache: q [B, H, 1, 128], k [B, H, len, 128], v [B, len, H, 128]
+        B, H, t = dims[:3]
+        hd = 128
+        q, k, v = ex.upload(bf16((B, H, 1, hd))), ex.upload(bf16((B, H, t, hd))), ex.upload(bf16((B, t, H, hd)))
+        rt = ex.upload(np.array([0x4135], np.uint16))
+        out = ex.alloc(B * H * hd * 2)
+        l = launch_desc(abi.OP_ATTENTION, abi.BF16, [B, H, 1, hd], [t], order=abi.ORDER_DEVICE, name=b"attention[blockwise]")
+        l.n_inputs = 4
+        l.iparam[1] = l.iparam[2] = l.iparam[3] = abi.BF16
+        for o, st, n in ((l.inputs[0], (H * hd, hd, 0, 1, 0), B * H * hd), (l.inputs[1], (H * t * hd, t * hd, 0, 1, hd), B * H * t * hd), (l.inputs[2], (t * H * hd, hd, 0, 1, H * hd), B * H * t * hd), (l.out, (H * hd, hd, 0, 1, 0), B * H * hd)):
+            o.dtype, o.numel = abi.BF16, n
+            for a, x in enumerate(st):
+                o.stride[a] = x
+        l.inputs[3].dtype, l.inputs[3].numel = abi.BF16, 1
+        ms = timed(lambda: ex.run(l, [q, k, v, rt, out]), args.steps)
+        print(json.dumps({"micro": "attn_step", "shape": dims, "ms": ms, "GB/s of the cache": 2.0 * 2.0 * B * H * t * hd / ms / 1e6}))
     elif args.micro == "attn":
         B, H, t = dims[:3]
         hd = 128
@@ -544,8 +591,8 @@ def small_case(name, w):
     if dt == "f16" and n >= 4096:
         # a row of x·w has deviations of about sqrt(n) a term, so the squared deviations of LayerNorm pass binary16's
         # largest number (65504) from n = 4096 on and the all-f16 program stops with E7007, as the reference's does;
-        # that one site is kept in f32 here (what a solved realization would do), everything else stays binary16
-        rz["storage"] = {"LayerNorm.apply/%5": "f32"}
+        # those two sites are kept in f32 here (what a solved realization would do), everything else stays binary16
+        rz["storage"] = {"LayerNorm.apply/%5": "f32", "LayerNorm.apply/%6": "f32"}  # and their mean, which an f16 kernel would round at its edge
     return dict(model="contract_ln", consts={}, rz=rz, params={"ln.γ": np.ones(n, np.float32), "ln.β": np.zeros(n, np.float32)}, inputs=[x, wt], entry="apply",
                 units=2.0 * n * n * n / 1e12, unit="TFLOP/s", metric=f"TFLOP/s (2·N^3) of x·w + row LayerNorm, N={n}, stored {dt}", flops=2.0 * n * n * n, dtype=f"{dt} storage, f32 accumulation", order="device", out_shape=(n, n))
 
@@ -772,14 +819,14 @@ def run_decode(args, name, w):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--micro", default=None, choices=["gemm", "gemm_i8", "softmax", "ew", "attn", "norm", "e8m15", "f32c", "train", "rmsnorm", "rope", "xent"])
+    ap.add_argument("--micro", default=None, choices=["gemm", "gemm_i8", "contract", "softmax", "ew", "attn", "attn_step", "norm", "e8m15", "f32c", "train", "rmsnorm", "rope", "xent"])
     ap.add_argument("--shape", default="8192,8192,8192")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="llama7b_prefill_b8_t2048", choices=sorted(WORKLOADS))
-    ap.add_argument("--attention", default="blockwise", choices=["blockwise", "online", "unfused"], help="the declared order of the attention launches: one kernel in two passes over the keys (blockwise) or in one (online), or the reference's four launches")
+    ap.add_argument("--attention", default="online", choices=["blockwise", "online", "unfused"], help="the declared order of the attention launches: one kernel in two passes over the keys (blockwise) or in one (online), or the reference's four launches")
     ap.add_argument("--launches", default="merged", choices=["merged", "reference"], help="merged: bit-preserving rewrites of the launch list (views for slices, in-place concatenation, wider groups); reference: the reference's launch list")
     ap.add_argument("--comm", default="psk", choices=["psk", "torch"], help="what carries the loss gather of a sharded run: the library's psk_comm_* (NCCL on the executor's stream) or torch.distributed")
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -23,6 +23,7 @@
 #include "psk_kernels.cuh"
 #include "psk_hot.cuh"
 #include "psk_attn.cuh"
+#include "psk_attn_step.cuh"
 #include "psk_gemm_i8.cuh"
 #include "psk_gemm_tc2.cuh"
 
@@ -71,6 +72,7 @@ struct psk_exec {
     bool tc_attr_set = false;
     bool softmax_attr_set = false;
     bool attn_attr_set = false;
+    bool attn_step_attr_set = false;
     bool i8_attr_set = false;
     uint16_t *silu_table = nullptr; // silu of every bf16 code, computed once by the device's own exact function
 };
@@ -1271,6 +1273,36 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
         if ((no != 4 && no != 5) || L.n_inner != 1 || (L.n_in != 4 && L.n_in != 5)) { rc = fail(e, PSK_E7001, nm + ": q, k, v, the divisor and at most a mask over (batch, [groups,] heads, seq, hd | seq2)"); break; }
         const int ax_hd = no - 1, ax_seq = no - 2, ax_s2 = no, ax_b = 0, ax_g = 1, ax_p = no == 5 ? 2 : -1;
         const int64_t B = L.dims[ax_b], G = L.dims[ax_g], Pn = ax_p >= 0 ? L.dims[ax_p] : 1, T = L.dims[ax_seq], HD = L.dims[ax_hd];
+        if (T == 1 && L.n_in == 4) {
+            // one query position against a cache of keys and values (a decode step): a stream of the cache, see psk_attn_step.cuh
+            e->last_kernel = "k_attn_step";
+            const int64_t T2 = L.dims[ax_s2];
+            const DevOperand &Q = L.in[0], &K = L.in[1], &V = L.in[2], &O = L.out;
+            bool ok = HD == attn_step::HD && l->dtype == PSK_BF16 && l->out.dtype == PSK_BF16 && l->iparam[1] == PSK_BF16 && l->iparam[2] == PSK_BF16 && l->iparam[3] == PSK_BF16
+                && T2 >= 1 && T2 <= 49152 && B * G * Pn <= 0x7fffffff && G <= 0x7fffffff && Pn <= 0x7fffffff;
+            for (int i = 0; i < 3 && ok; ++i) ok = l->in[i].dtype == PSK_BF16 && L.in[i].stride[ax_hd] == 1 && ((uintptr_t)L.in[i].p % 8) == 0 && L.in[i].stride[ax_b] % 4 == 0 && L.in[i].stride[ax_g] % 4 == 0;
+            ok = ok && O.stride[ax_hd] == 1 && K.stride[ax_s2] % 4 == 0 && V.stride[ax_s2] % 4 == 0 && Q.stride[ax_s2] == 0 && O.stride[ax_s2] == 0 && K.stride[ax_seq] == 0 && V.stride[ax_seq] == 0;
+            if (ax_p >= 0) ok = ok && K.stride[ax_p] == 0 && V.stride[ax_p] == 0 && Q.stride[ax_p] % 4 == 0;
+            if (!ok) { rc = fail(e, PSK_E7005, nm + ": the step's attention runs bf16 sites, hd = 128 and no mask over a cache of at most 49152 positions"); break; }
+            attn_step::Params A;
+            memset(&A, 0, sizeof A);
+            A.q = (const uint16_t *)Q.p; A.k = (const uint16_t *)K.p; A.v = (const uint16_t *)V.p; A.out = (uint16_t *)const_cast<void *>(O.p);
+            A.q_b = Q.stride[ax_b]; A.q_g = Q.stride[ax_g]; A.q_p = ax_p >= 0 ? Q.stride[ax_p] : 0;
+            A.k_b = K.stride[ax_b]; A.k_g = K.stride[ax_g]; A.k_t = K.stride[ax_s2];
+            A.v_b = V.stride[ax_b]; A.v_g = V.stride[ax_g]; A.v_t = V.stride[ax_s2];
+            A.o_b = O.stride[ax_b]; A.o_g = O.stride[ax_g]; A.o_p = ax_p >= 0 ? O.stride[ax_p] : 0;
+            A.G = (int32_t)G; A.Pn = (int32_t)Pn; A.len = (int32_t)T2;
+            A.rt = L.in[3].p; A.rt_dtype = L.in[3].dtype;
+            const size_t smem = (size_t)T2 * sizeof(float);
+            if (smem > 48 * 1024 && !e->attn_step_attr_set) {
+                CUDA_TRY(e, cudaFuncSetAttribute(attn_step::k_attn_step, cudaFuncAttributeMaxDynamicSharedMemorySize, 49152 * (int)sizeof(float)));
+                e->attn_step_attr_set = true;
+            }
+            attn_step::k_attn_step<<<(unsigned)(B * G * Pn), attn_step::THREADS, smem, e->stream>>>(A);
+            e->last_flops = 4.0 * (double)(B * G * Pn) * (double)T2 * (double)HD;
+            e->kernels += 1;
+            break;
+        }
         bool fits = HD == attn::HD && T == L.dims[ax_s2] && T % attn::BM == 0 && l->dtype == PSK_BF16 && l->out.dtype == PSK_BF16
             && l->iparam[1] == PSK_BF16 && l->iparam[2] == PSK_BF16 && l->iparam[3] == PSK_BF16;
         for (int i = 0; i < 3 && fits; ++i) fits = l->in[i].dtype == PSK_BF16 && L.in[i].stride[ax_hd] == 1 && aligned16(L.in[i].p);

@@ -113,6 +113,19 @@ PSK_DEV uint32_t count_to_bf16(int32_t n, double base)
     return (fb + 0x7fffu + ((fb >> 16) & 1u)) >> 16;
 }
 
+// The same in binary32 arithmetic only, for the staged bf16 epilogue. `basef` is the column's base rounded to
+// binary32; n, basef and their product each carry at most 2^-24 of relative error, so f is within three of its own
+// units of n·base, and the two round to the same bf16 number unless f lies within three units of a midpoint (low
+// half 0x8000) or is subnormal. Those few go the exact way, with the base taken again from its two factors.
+PSK_DEV uint32_t count_to_bf16_quick(int32_t n, float basef, double sa, const float *scale_of_col)
+{
+    if (n == 0) return 0u;
+    const float f = (float)n * basef;
+    const uint32_t fb = __float_as_uint(f);
+    if ((((fb & 0xffffu) - 0x7ffcu) <= 8u) || !(fb & 0x7f800000u)) return round_count_to_float((int64_t)n, sa * (double)*scale_of_col, 7, 8);
+    return (fb + 0x7fffu + ((fb >> 16) & 1u)) >> 16;
+}
+
 PSK_DEV uint32_t count_to_f32(int32_t n, double base)
 {
     const double d = (double)n * base;
@@ -278,25 +291,38 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_i8(const __grid_constant__ 
 #pragma unroll 1
                 for (int c0 = half_id * 32; c0 < BN; c0 += 64) {
                     uint32_t v[32];
+                    const int64_t col = n0 + c0;
+                    // this lane fetches the scale (and the zero-point correction) of column col + lane while the
+                    // accumulators come out of tensor memory; the row's loop below takes them by shuffle
+                    const bool col_live = col + lane < P.n;
+                    const float *my_scale = cs_base + (col_live ? (col + lane) * P.col_scale_stride : 0);
+                    const float scale_l = col_live ? *my_scale : 0.0f;
+                    const uint32_t corr_l = (sum_base && col_live) ? (uint32_t)P.a_zero * (uint32_t)sum_base[col + lane] : 0u;
                     tc::tmem_ld32(tbase + c0, v);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    const int64_t col = n0 + c0;
                     if (col >= P.n) continue;
                     if (staged) {
                         // 32 columns of this lane's row: rescaled, packed, then through shared memory so that a store
                         // instruction writes whole runs of a row (bf16: 64 bytes; f32: 128 bytes)
                         uint32_t packed[32];
+                        const double base_l = sa * (double)scale_l;
+                        const float basef_l = __double2float_rn(base_l);
+                        if (P.out_dtype == PSK_BF16) {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            const int64_t cc = col + i;
-                            uint32_t code = 0;
-                            if (cc < P.n) {
-                                int32_t nsum = (int32_t)v[i];
-                                if (sum_base) nsum = (int32_t)((uint32_t)nsum - (uint32_t)P.a_zero * (uint32_t)sum_base[cc]);
-                                const double base = sa * (double)cs_base[cc * P.col_scale_stride];
-                                code = P.out_dtype == PSK_F32 ? count_to_f32(nsum, base) : count_to_bf16(nsum, base);
+                            for (int i = 0; i < 32; ++i) {
+                                const float bf = __shfl_sync(0xffffffffu, basef_l, i);
+                                const uint32_t corr = __shfl_sync(0xffffffffu, corr_l, i);
+                                const int32_t nsum = (int32_t)(v[i] - corr);
+                                packed[i] = col + i < P.n ? count_to_bf16_quick(nsum, bf, sa, cs_base + (col + i) * P.col_scale_stride) : 0u;
                             }
-                            packed[i] = code;
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) {
+                                const double base = __shfl_sync(0xffffffffu, base_l, i);
+                                const uint32_t corr = __shfl_sync(0xffffffffu, corr_l, i);
+                                const int32_t nsum = (int32_t)(v[i] - corr);
+                                packed[i] = col + i < P.n ? count_to_f32(nsum, base) : 0u;
+                            }
                         }
                         if (P.out_dtype == PSK_F32) {
 #pragma unroll

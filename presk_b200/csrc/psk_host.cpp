@@ -1482,11 +1482,12 @@ struct psk_host {
         Tensor o;
         bool fused_attention = false;
         Tensor hdr, rt;
-        if (rz.blockwise_attention && !calibrating && kv_mode != KV_STEP) {
+        if (rz.blockwise_attention && !calibrating) {
             // the root is computed before the scores here and after them below; neither reads the other
             hdr = scalar(f + "/%18", (double)HD);
             rt = unary(f + "/%19", PSK_SQRT, hdr);
-            o = attention_blockwise({f + "/%16", f + "/%20", f + "/%21", f + "/%22"}, q, k, v, rt, &mask, &fused_attention);
+            // (a decode step passes no mask: the executor then streams the cache for the one new position)
+            o = attention_blockwise({f + "/%16", f + "/%20", f + "/%21", f + "/%22"}, q, k, v, rt, use_mask, &fused_attention);
         }
         if (!fused_attention) {
             Tensor se = ein(f + "/%16", {"batch", "groups", "per", "seq", "seq2"}, {{"batch", "groups", "per", "seq", "hd"}, {"batch", "groups", "seq2", "hd"}}, {&q, &k});

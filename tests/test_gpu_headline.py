@@ -35,10 +35,38 @@ def test_one_layer_of_the_7b_width_under_the_benchmarks_realization(cuda, oracle
     assert "attention[blockwise]" in log and "rmsnorm[merged]" in log and "rope[merged]" in log and any(n.endswith("+add") for n in log), log
     assert r["finite"]
     tol = headline.LOGITS_TOL * (2.0 if weights != "bf16" else 1.0)  # narrow weights: the scale multiplies a reordered sum once more
-    assert r["logits_max_err"] <= tol * r["logits_scale"], r
-    assert r["logits_mean_err"] <= headline.LOGITS_MEAN_TOL * 2.0 * r["logits_scale"], r
+    summary = {k: v for k, v in r.items() if k != "gpu_launch_log"}
+    assert r["logits_max_err"] <= tol * r["logits_scale"], summary
+    assert r["logits_mean_err"] <= headline.LOGITS_MEAN_TOL * (2.0 if weights != "bf16" else 1.0) * r["logits_scale"], summary
     if weights == "bf16":
-        assert abs(r["loss_gpu"] - r["loss_oracle"]) <= headline.LOSS_RTOL * abs(r["loss_oracle"]), r
+        assert abs(r["loss_gpu"] - r["loss_oracle"]) <= headline.LOSS_RTOL * abs(r["loss_oracle"]), summary
+
+
+def test_the_7b_width_under_the_sequential_order_is_the_oracles_bits(cuda, oracle, wide_params):
+    """The same layer of the full width (d 4096, FFN 11008, vocabulary 32000), B = 1, T = 128, under the reference's
+    own order on both sides: every logit bit for bit, through the exact contraction kernels at their largest tiles."""
+    from presk_b200 import Host
+    c = dict(headline.WIDTH_7B, L=1)
+    rng = np.random.default_rng(9)
+    ids = rng.integers(0, c["V"], size=(1, 128), dtype=np.int64)
+    outs = []
+    for ex in (cuda, oracle.vtable()):
+        h = headline.give(Host(ex, headline.realization(wide_params, headline.ORACLE_ORDER)).prepare("llama", **c), wide_params)
+        outs.append(h.call("apply", [ids], (1, 128, c["V"])))
+        h.close()
+    assert np.array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32))
+
+
+@pytest.mark.parametrize("attention", ["online"])
+def test_one_layer_of_the_7b_width_with_the_one_pass_attention(cuda, oracle, wide_params, attention):
+    """The benchmark's default realization: as above with `attention: online`."""
+    r = headline.llama_width_parity(cuda, oracle, B=2, T=256, weights="bf16", params=wide_params, order=dict(headline.BENCH_ORDER, attention=attention))
+    summary = {k: v for k, v in r.items() if k != "gpu_launch_log"}
+    assert "attention[online]" in r["gpu_launch_log"]
+    assert r["finite"]
+    assert r["logits_max_err"] <= headline.LOGITS_TOL * r["logits_scale"], summary
+    assert r["logits_mean_err"] <= headline.LOGITS_MEAN_TOL * 1.5 * r["logits_scale"], summary
+    assert abs(r["loss_gpu"] - r["loss_oracle"]) <= headline.LOSS_RTOL * abs(r["loss_oracle"]), summary
 
 
 def test_blockwise_attention_at_the_benchmarks_sequence(cuda, oracle):
@@ -139,10 +167,12 @@ def test_the_ffn_contraction_of_the_timed_step(cuda, oracle, addend):
         exact = prod + bf16_value(res[rows]).astype(np.float64)
     err = np.abs(got[rows] - exact)
     scale = np.abs(exact).max()
-    # per entry: two bf16 roundings of values up to `scale` when a residual is added, one otherwise, plus the sum's own error
-    assert err.max() <= (2.0**-8 if addend else 2.0**-9) * scale + 4e-6 * np.sqrt(k), (err.max(), scale)
+    # bf16 keeps eight significant bits: a rounding moves a value by at most 2^-8 of its binade's top, and with a
+    # residual there are two of them (the product to its site, then the sum); plus the f32 accumulation's error
+    assert err.max() <= (2.0**-7 if addend else 2.0**-8) * scale + 4e-6 * np.sqrt(k), (err.max(), scale)
+    # and per entry, relative to the entry itself, for entries not far below the tensor's scale
     rel = err / np.maximum(np.abs(exact), 2.0**-4 * scale)
-    assert rel.max() <= 2.0**-7, rel.max()  # per entry, for entries not far below the tensor's scale
+    assert rel.max() <= (2.0**-5 if addend else 2.0**-7), rel.max()
 
 
 def e8m15_value(u8):
@@ -196,7 +226,8 @@ def test_contract_ln_at_the_stated_sizes(cuda, oracle, dtype, n):
     params = {"ln.γ": np.ones(n, np.float32), "ln.β": np.zeros(n, np.float32)}
     # binary16 cannot hold the squared deviations of such rows (up to about 25·n > 65504): all-f16 stops with E7007, on
     # the reference too; that site is f32 here, as a solved realization would have it
-    sites = {"LayerNorm.apply/%5": "f32"} if dtype == "f16" else {}
+    # (and their mean, which an f16 kernel would read rounded to binary16 at its edge)
+    sites = {"LayerNorm.apply/%5": "f32", "LayerNorm.apply/%6": "f32"} if dtype == "f16" else {}
     if dtype == "f16":
         hf = models.give(Host(cuda, {"default": "f16", "order": {"kind": "device"}}).prepare("contract_ln"), params)
         with pytest.raises(PreskError) as e:

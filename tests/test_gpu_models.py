@@ -497,6 +497,7 @@ def test_step_after_prefill_on_the_gpu(cuda, oracle):
     prof = cuda.profile()
     cuda.set_profiling(False)
     assert sum(1 for rec in prof if rec[0] == "k_gemm_tc") > 7 * c["L"] * 4
+    assert sum(1 for rec in prof if rec[0] == "k_attn_step") == 3 * c["L"]  # a step's attention: one stream of the cache a layer
     assert np.abs(dev - want).max() <= 2.0**-6 * np.abs(want).max()
     for weights in ("int8", "e4m3fn"):
         rz = dict(base, order={"kind": "sequential"})
