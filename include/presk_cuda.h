@@ -62,6 +62,10 @@ typedef enum {
     PSK_E7005 = 7005,  /* a realization this executor does not run */
     PSK_E7006 = 7006,  /* a scaled site whose scale is not computed yet */
     PSK_E7007 = 7007,  /* the overflow guard: a store rounded a finite value to an infinity */
+    PSK_E9002 = 9002,  /* psk_data: not a .psk.d file of version 1, 2 or 3, or a leaf in a format not held */
+    PSK_E9003 = 9003,  /* psk_data: truncated */
+    PSK_E9004 = 9004,  /* psk_data: an index not below its bound */
+    PSK_E9005 = 9005,  /* psk_data: another sample type, or a length that is not the layout's */
     PSK_E10001 = 10001 /* internal error of the backend (a CUDA call failed, a wait ran out) */
 } psk_status;
 
@@ -402,6 +406,31 @@ int psk_comm_allreduce(psk_comm *c, void *device_buf, int64_t count, int32_t dty
  * `name` (may be NULL) receives the kernel's name, which `out->name` then points at; `*rest` (may be NULL) is
  * left after the kernel read, for a listing of several. */
 int psk_describe(const char *kernel_text, int32_t order, psk_launch *out, char *name, size_t name_cap, const char **rest, char *err, size_t err_cap);
+
+/* ---------------------------------------------------------------------------
+ * Samples of a .psk.d file, read into device buffers (presk-data's container; the reference's C reader is
+ * presk_open / presk_read / presk_close, presk-export-c/c/presk_rt.c:295-530, whose header checks, error codes
+ * and conversions these keep). `leaves` are the sample type's leaves in order, as the reference's exports state
+ * them (presk_leaf, presk_rt.h:432-435): `bound` > 0 for idx[bound] elements, 0 for reals; `n` elements.
+ * psk_data_open parses and checks the header on the host (no GPU needed; errors 9002, 9003, 9005 with the
+ * reference's messages in `err`). psk_data_read moves samples first .. first + count - 1 to the device as the
+ * file holds them and takes them apart there: dst[i] (a device buffer of the executor, count x leaves[i].n
+ * elements of dtypes[i], dense, sample-major) receives leaf i of every sample; an index leaf's dtype is PSK_I64,
+ * a real leaf's PSK_F32, PSK_BF16, PSK_F16 or PSK_E8M15, each real rounded once from the file's encoding as the
+ * reference's store_real rounds. An index not below its bound: PSK_E9004 naming the first one in file order
+ * (that element is not written). The call returns when the buffers are complete. Messages: psk_data_error.
+ * ------------------------------------------------------------------------- */
+typedef struct psk_data psk_data;
+typedef struct {
+    uint64_t bound;
+    uint64_t n;
+} psk_data_leaf;
+int psk_data_open(const char *path, const char *type, const psk_data_leaf *leaves, size_t nleaves, psk_data **out, char *err, size_t err_cap);
+uint64_t psk_data_count(const psk_data *d);
+uint64_t psk_data_sample_bytes(const psk_data *d);
+int psk_data_read(psk_data *d, psk_exec *e, uint64_t first, uint64_t count, void *const *dst, const int32_t *dtypes);
+const char *psk_data_error(const psk_data *d);
+void psk_data_close(psk_data *d);
 
 /* ---------------------------------------------------------------------------
  * The executor as a table of functions, so that the host program can run

@@ -8,6 +8,6 @@ package is the thin Python face of that ABI: `Executor` is the reference's
 the GPU; when the library or a GPU is missing, construction raises.
 """
 from . import abi, build
-from .api import Comm, Executor, Host, PreskError, launch_desc
+from .api import Comm, DataFile, Executor, Host, PreskError, describe, launch_desc
 
-__all__ = ["abi", "build", "Comm", "Executor", "Host", "PreskError", "launch_desc"]
+__all__ = ["abi", "build", "Comm", "DataFile", "Executor", "Host", "PreskError", "describe", "launch_desc"]

@@ -82,6 +82,11 @@ class ExecVtable(C.Structure):
 
 
 # name -> (restype, argtypes): every function include/presk_cuda.h declares
+class DataLeaf(C.Structure):
+    """psk_data_leaf: a leaf of a .psk.d sample type (`bound` > 0: idx[bound] elements; `n` elements)."""
+    _fields_ = [("bound", C.c_uint64), ("n", C.c_uint64)]
+
+
 PROTOTYPES = {
     "psk_abi_sizeof": (C.c_size_t, [C.c_int]),
     "psk_exec_create": (C.c_void_p, [C.c_int]),
@@ -137,6 +142,12 @@ PROTOTYPES = {
     "psk_host_set_logging": (None, [C.c_void_p, C.c_int]),
     "psk_exec_gap": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_int64, C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "psk_describe": (C.c_int, [C.c_char_p, C.c_int32, C.POINTER(Launch), C.c_char_p, C.c_size_t, C.POINTER(C.c_char_p), C.c_char_p, C.c_size_t]),
+    "psk_data_open": (C.c_int, [C.c_char_p, C.c_char_p, C.POINTER(DataLeaf), C.c_size_t, C.POINTER(C.c_void_p), C.c_char_p, C.c_size_t]),
+    "psk_data_count": (C.c_uint64, [C.c_void_p]),
+    "psk_data_sample_bytes": (C.c_uint64, [C.c_void_p]),
+    "psk_data_read": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.POINTER(C.c_void_p), C.POINTER(C.c_int32)]),
+    "psk_data_error": (C.c_char_p, [C.c_void_p]),
+    "psk_data_close": (None, [C.c_void_p]),
 }
 
 

@@ -1,5 +1,6 @@
 """Executor and Host: numpy-facing wrappers over the C ABI."""
 import ctypes as C
+import os
 
 import numpy as np
 
@@ -328,6 +329,45 @@ def describe(kernel_text, order=abi.ORDER_SEQUENTIAL):
         out.append((name.value.decode(), l))
         text = rest.value or b""
     return out
+
+
+class DataFile:
+    """A .psk.d file open for reading into device buffers (`psk_data_*`). `leaves`: [(bound, n)] of the sample
+    type's leaves in order, bound 0 for reals."""
+
+    def __init__(self, path, sample_type, leaves):
+        self.lib = abi.load()
+        self.leaves = [(int(b), int(n)) for b, n in leaves]
+        arr = (abi.DataLeaf * max(len(self.leaves), 1))()
+        for i, (b, n) in enumerate(self.leaves):
+            arr[i].bound, arr[i].n = b, n
+        h = C.c_void_p()
+        err = C.create_string_buffer(1024)
+        rc = self.lib.psk_data_open(os.fsencode(path), sample_type.encode(), arr, len(self.leaves), C.byref(h), err, 1024)
+        if rc != abi.OK:
+            raise PreskError(rc, err.value.decode())
+        self.handle = h
+
+    @property
+    def count(self):
+        return self.lib.psk_data_count(self.handle)
+
+    @property
+    def sample_bytes(self):
+        return self.lib.psk_data_sample_bytes(self.handle)
+
+    def read(self, ex, first, count, dst, dtypes):
+        """Samples first .. first + count - 1 into the device buffers `dst` (one a leaf, count x n elements of dtypes[i])."""
+        ptrs = (C.c_void_p * max(len(dst), 1))(*dst)
+        dts = (C.c_int32 * max(len(dtypes), 1))(*dtypes)
+        rc = self.lib.psk_data_read(self.handle, ex.handle, first, count, ptrs, dts)
+        if rc != abi.OK:
+            raise PreskError(rc, self.lib.psk_data_error(self.handle).decode())
+
+    def close(self):
+        if self.handle:
+            self.lib.psk_data_close(self.handle)
+            self.handle = None
 
 
 def launch_desc(op, dtype, dims_outer, dims_inner=(), order=abi.ORDER_SEQUENTIAL, name=b"launch"):

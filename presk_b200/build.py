@@ -32,7 +32,7 @@ def _nvcc():
 
 
 def sources():
-    return [os.path.join(CSRC, f) for f in ("psk_exec.cu", "psk_host.cpp", "psk_noalloc.cu", "psk_comm.cpp", "psk_describe.cpp") if os.path.exists(os.path.join(CSRC, f))]
+    return [os.path.join(CSRC, f) for f in ("psk_exec.cu", "psk_host.cpp", "psk_noalloc.cu", "psk_comm.cpp", "psk_describe.cpp", "psk_data.cu") if os.path.exists(os.path.join(CSRC, f))]
 
 
 def stale():

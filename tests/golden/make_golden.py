@@ -11,6 +11,9 @@ Sources (paths within presk-lang/presk, read as text):
   crates/presk-kernel/tests/snapshots/conformance__linear_kernels.snap
                                                         the kernel text of a row-wise `dot` and an `add` (what an executor is handed)
   tests/run/minigpt_forward.snap, minigpt_loss.snap      seed-0 logits (all zero: the head is initialised to zeros) and loss of MiniGPT
+  examples/tests/data/windows.psk.d, examples/tests/train/reg.psk.d, examples/tutorial/data/pairs.psk.d,
+  examples/spec/minigpt/data/tokens.psk.d                the reference's own small data files (version 1), whole, with
+                                                        their sample types and leaves (written to data_files.json)
 Run:  python tests/golden/make_golden.py <path of the reference's tree>
 """
 import json
@@ -80,3 +83,20 @@ out["minigpt_loss"] = float(re.search(r"= ([-0-9.e]+)", text).group(1))
 with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_vectors.json"), "w") as f:
     json.dump(out, f, indent=1)
 print("wrote", list(out))
+
+# The reference's own .psk.d files: their bytes, and what the header says (presk-data's layout: magic, u16 version,
+# u32 length and text of the sample type, u64 count). The leaves are read off the type by hand.
+import base64
+import struct
+
+files = {}
+for rel, leaves in (("examples/tests/data/windows.psk.d", [(64, 8), (64, 8)]), ("examples/tests/train/reg.psk.d", [(0, 2), (0, 1)]),
+                    ("examples/tutorial/data/pairs.psk.d", [(0, 4), (0, 4)]), ("examples/spec/minigpt/data/tokens.psk.d", [(64, 8), (64, 8)])):
+    raw = open(os.path.join(ref, rel), "rb").read()
+    assert raw[:4] == b"PSKD"
+    version, tlen = struct.unpack("<HI", raw[4:10])
+    typ = raw[10:10 + tlen].decode()
+    count = struct.unpack("<Q", raw[10 + tlen:18 + tlen])[0]
+    files[os.path.basename(rel)] = {"source": rel, "version": version, "type": typ, "count": count, "leaves": leaves, "bytes": base64.b64encode(raw).decode()}
+with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "data_files.json"), "w") as f:
+    json.dump(files, f, indent=0)
