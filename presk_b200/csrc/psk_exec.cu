@@ -51,6 +51,8 @@ struct psk_exec {
     // int8 weights read by the tensor-core contraction: their integers as bf16, made once per buffer
     // (weights are never written after they are stored), keyed by the codes' address and count
     std::map<std::pair<const void *, int64_t>, void *> widened;
+    size_t widened_bytes = 0;                 // what the kept copies hold
+    size_t widened_budget = (size_t)4 << 30;  // beyond it a copy lives for one contraction only (PSK_WIDENED_MB)
     uint32_t *flags = nullptr;                         // kFlagSlots words of the overflow guard
     uint32_t *status = nullptr;                        // one word: kernel-side trouble
     std::vector<int64_t> flag_serial;                  // the launch each slot was last given to
@@ -679,7 +681,7 @@ static void forget_widened(psk_exec *e, const void *written)
     }
     for (auto w = e->widened.begin(); w != e->widened.end();) {
         const uint8_t *q = (const uint8_t *)w->first.first;
-        if (q >= lo && q < hi) { cudaFree(w->second); e->live -= (size_t)w->first.second * 2; w = e->widened.erase(w); }
+        if (q >= lo && q < hi) { cudaFree(w->second); e->live -= (size_t)w->first.second * 2; e->widened_bytes -= (size_t)w->first.second * 2; w = e->widened.erase(w); }
         else ++w;
     }
 }
@@ -694,7 +696,7 @@ void psk_exec_free(psk_exec *e, void *p)
     // widened copies of weights that lived in this buffer
     for (auto w = e->widened.begin(); w != e->widened.end();) {
         const uint8_t *q = (const uint8_t *)w->first.first;
-        if (q >= (const uint8_t *)p && q < (const uint8_t *)p + it->second) { cudaFree(w->second); e->live -= (size_t)w->first.second * 2; w = e->widened.erase(w); }
+        if (q >= (const uint8_t *)p && q < (const uint8_t *)p + it->second) { cudaFree(w->second); e->live -= (size_t)w->first.second * 2; e->widened_bytes -= (size_t)w->first.second * 2; w = e->widened.erase(w); }
         else ++w;
     }
     // The stream is in order and every kernel of this executor runs on it, so
@@ -844,21 +846,40 @@ int psk_exec_gemm(psk_exec *e, const psk_gemm *g, const void *a, const void *b, 
     return r;
 }
 
-// Integer or e4m3fn weights as the bf16 numbers they are: a copy made at the weights' first contraction on the
-// tensor cores and kept until the codes are written again or freed.
-static const void *widened_weights(psk_exec *e, const void *codes, int64_t count, bool int8)
+// Integer or e4m3fn weights as the bf16 numbers they are. While the copies kept so far stay within the budget
+// (4 GB, or PSK_WIDENED_MB), a copy is made at the weights' first contraction on the tensor cores and kept until the
+// codes are written again or freed. Beyond it (a model whose narrow weights are there to save memory) the copy is
+// made again for every contraction into a buffer of the pool, which the caller gives back once the contraction is
+// queued (`*transient`): the stream is in order, so the next matrix's copy may take the same bytes. That costs a
+// read of the codes and a write and a read of the copy a contraction, about 3 ms of a 7B prefill step, and the model
+// then holds one byte a weight, not three.
+static const void *widened_weights(psk_exec *e, const void *codes, int64_t count, bool int8, bool *transient)
 {
+    *transient = false;
     auto key = std::make_pair(codes, count);
     auto it = e->widened.find(key);
     if (it != e->widened.end()) return it->second;
+    const char *forced = getenv("PSK_WIDENED_MB"); // read at every new copy, so that a test can change it
+    const long forced_mb = forced ? atol(forced) : -1;
+    const size_t budget = forced_mb >= 0 ? (size_t)forced_mb << 20 : e->widened_budget, bytes = (size_t)count * 2;
     void *wb = nullptr;
-    if (cudaMalloc(&wb, (size_t)count * 2) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    if (e->widened_bytes + bytes > budget) {
+        wb = psk_exec_alloc(e, bytes);
+        if (!wb) return nullptr;
+        *transient = true;
+    } else if (cudaMalloc(&wb, bytes) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
     if (int8) k_int8_to_bf16<<<grid_for(e, count, 256, 8), 256, 0, e->stream>>>((const int8_t *)codes, (uint16_t *)wb, count);
     else k_e4m3_to_bf16<<<grid_for(e, count, 256, 8), 256, 0, e->stream>>>((const uint8_t *)codes, (uint16_t *)wb, count);
     e->kernels += 1;
-    e->widened.emplace(key, wb);
-    e->live += (size_t)count * 2; // the copy is device memory of this executor like any buffer of its pool
-    e->peak = std::max(e->peak, e->live);
+    if (!*transient) {
+        e->widened.emplace(key, wb);
+        e->widened_bytes += bytes;
+        e->live += bytes; // the copy is device memory of this executor like any buffer of its pool
+        e->peak = std::max(e->peak, e->live);
+    }
     return wb;
 }
 
@@ -1070,7 +1091,8 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
         const bool wf8 = mapped && device_order && e->encode && B.dtype == PSK_E4M3 && !B.affine && A.dtype == PSK_BF16 && !l->int_accum
             && (L.kdtype == PSK_BF16 || L.kdtype == PSK_F32) && g.a_k == 1 && (g.b_k == 1 || g.b_n == 1) && aligned16(A.p) && g.c_col_lo == 1 && g.n >= 8 && g.k >= 8;
         if (w8 || wf8) {
-            const void *wide = widened_weights(e, B.p, l->in[1].numel, w8);
+            bool wide_transient = false;
+            void *wide = const_cast<void *>(widened_weights(e, B.p, l->in[1].numel, w8, &wide_transient));
             if (wide) {
                 psk_gemm pg;
                 memset(&pg, 0, sizeof pg);
@@ -1084,6 +1106,7 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
                 std::string keep = e->error;
                 int r = launch_tc_few_rows(e, pg, A.p, wide, const_cast<void *>(L.out.p), L.ovf, w8 ? B.scales : nullptr, w8 ? g.bs_n : 0, nullptr, L.out.dtype);
                 if (r == PSK_E7001) { e->error = keep; r = launch_tc(e, pg, A.p, wide, const_cast<void *>(L.out.p), L.ovf, w8 ? B.scales : nullptr, w8 ? g.bs_n : 0, w8 ? g.bs_lo : 0, w8 ? g.bs_hi : 0); }
+                if (wide_transient) psk_exec_free(e, wide); // handed out again only to later work of the same stream
                 if (r == PSK_OK) {
                     e->last_kernel = "k_gemm_tc";
                     e->last_flops = 2.0 * (double)g.m * (double)g.n * (double)g.k * (double)g.batch;
@@ -1439,13 +1462,15 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
         pg.c_col_lo_count = g.c_col_lo_count; pg.c_col_hi = g.c_col_hi; pg.c_lo = g.c_lo; pg.c_hi = g.c_hi;
         if (g.m == 1) pg.a_row = g.k;
         const void *bp = B.p;
+        bool bp_transient = false;
         if (b_int8 || b_e4m3) {
-            bp = widened_weights(e, B.p, l->in[1].numel, b_int8);
+            bp = widened_weights(e, B.p, l->in[1].numel, b_int8, &bp_transient);
             if (!bp) { rc = fail(e, PSK_E7005, nm + ": no memory for the weights' bf16 copy"); break; }
         }
         std::string keep_err = e->error;
         int r = launch_tc_few_rows(e, pg, A.p, bp, const_cast<void *>(L.out.p), L.ovf, b_int8 ? B.scales : nullptr, b_int8 ? g.bs_n : 0, X.p, (int)l->iparam[1]);
         if (r == PSK_E7001) { e->error = keep_err; r = launch_tc(e, pg, A.p, bp, const_cast<void *>(L.out.p), L.ovf, b_int8 ? B.scales : nullptr, b_int8 ? g.bs_n : 0, b_int8 ? g.bs_lo : 0, b_int8 ? g.bs_hi : 0, 0, 2, X.p); }
+        if (bp_transient) psk_exec_free(e, const_cast<void *>(bp));
         if (r == PSK_E7001) { rc = fail(e, PSK_E7005, nm + ": " + e->error); break; } // strides no tensor map or staged epilogue takes: the caller's two launches
         rc = r;
         e->last_kernel = "k_gemm_tc";

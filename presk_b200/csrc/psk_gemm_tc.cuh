@@ -387,6 +387,23 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
             tile_of(r, P.tiles_m, P.tiles_n, P.panel, mt, nt);
             const int64_t m0 = mt * BM * MT, n0 = nt * BN;
             const int64_t blo = b % P.batch_lo, bhi = b / P.batch_lo;
+            // A residual addend: this lane's 128 bytes of the group (row half mh, columns c0 ..) it will add next. The
+            // first group's are asked for here, while the tile's products still run, and each later group's while the
+            // one before it is rounded, so that no group waits for its addend.
+            uint4 ad_next[8];
+            auto fetch_addend = [&](int mh_, int c0_) {
+                const int64_t arow = m0 + mh_ * BM + quad * 32 + lane, acol = n0 + c0_;
+                const uint32_t rcnt_ = (uint32_t)(P.c_row_lo_count < 0x7fffffffll ? P.c_row_lo_count : 0x7fffffffll);
+                const uint32_t ccnt_ = (uint32_t)(P.c_col_lo_count < 0x7fffffffll ? P.c_col_lo_count : 0x7fffffffll);
+                const uint32_t rq_ = (uint32_t)arow / rcnt_, cq_ = (uint32_t)acol / ccnt_;
+                const int64_t off = blo * P.c_lo + bhi * P.c_hi + (int64_t)rq_ * P.c_row_hi + (int64_t)((uint32_t)arow - rq_ * rcnt_) * P.c_row_lo
+                    + (int64_t)cq_ * P.c_col_hi + (int64_t)((uint32_t)acol - cq_ * ccnt_);
+                const bool live = arow < P.m;
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    ad_next[j] = (live && acol + j * 8 < P.n) ? *reinterpret_cast<const uint4 *>((const uint16_t *)P.addend + off + j * 8) : make_uint4(0u, 0u, 0u, 0u);
+            };
+            if (staged && plain_add) fetch_addend(0, half_id * group_cols);
             ok = mbar_wait(MT == 1 ? tfull0 + 8 * acc : tfull0, acc_phase, abort_flag, P.status, 4u);
             ok = __all_sync(0xffffffffu, ok); // the loads below want the whole warp
             if (!ok) break;
@@ -463,13 +480,13 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
                         tmem_ld32(tbase + c0 + 32, vb);
                         const bool cs_add = plain_cs_add && col + 64 <= P.n && (reinterpret_cast<uintptr_t>(cs_base + col) & 15) == 0;
                         if (plain_add) {
-                            // the residual of this lane's row, 128 bytes, fetched while tensor memory is being read (taking it
-                            // through the staging tile in whole lines was tried and is slower: 0.58 ms against 0.48 ms)
+                            // the residual of this lane's row, 128 bytes, asked for a group ahead (taking it through the
+                            // staging tile in whole lines was tried and is slower: 0.58 ms against 0.48 ms)
                             uint4 ad[8];
-                            const bool live = row < P.m;
 #pragma unroll
-                            for (int j = 0; j < 8; ++j)
-                                ad[j] = (live && col + j * 8 < P.n) ? *reinterpret_cast<const uint4 *>((const uint16_t *)P.addend + row_off + add_col_off + j * 8) : make_uint4(0u, 0u, 0u, 0u);
+                            for (int j = 0; j < 8; ++j) ad[j] = ad_next[j];
+                            if (c0 + 2 * group_cols < BN) fetch_addend(mh, c0 + 2 * group_cols);
+                            else if (mh + 1 < MT) fetch_addend(mh + 1, half_id * group_cols);
                             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                             for (int j = 0; j < 8; ++j) {

@@ -288,6 +288,25 @@ def test_narrow_weights_through_the_model(cuda, oracle, weights):
     assert any(n.endswith("+add") for n in log), log
     assert_same_bits(outs[1], outs[0])
     assert np.abs(outs[1] - want).max() <= 2.0**-5 * np.abs(want).max()
+    # with no room to keep the bf16 copies (a model whose narrow weights are there to save memory) each is made
+    # for its contraction only, from the pool: the same bits, and the executor's memory stays that of the codes
+    import os
+    before = os.environ.get("PSK_WIDENED_MB")
+    os.environ["PSK_WIDENED_MB"] = "0"
+    try:
+        h = models.give(Host(cuda, rz(dict(kind="device", launches="merged"))).prepare("llama", **c), p)
+        cuda.set_profiling(True)
+        lean = h.call("apply", [ids], (2, 128, c["V"]))
+        prof = cuda.profile()
+        cuda.set_profiling(False)
+        h.close()
+    finally:
+        if before is None:
+            del os.environ["PSK_WIDENED_MB"]
+        else:
+            os.environ["PSK_WIDENED_MB"] = before
+    assert sum(1 for rec in prof if rec[0] == "k_gemm_tc") >= 7 * c["L"]
+    assert_same_bits(lean, outs[1])
 
 
 @pytest.mark.parametrize("dtype", ["f32", "bf16", "f16"])
