@@ -322,11 +322,17 @@ def microbench(args):
         ex.set_profiling(True)
         one()
         agg = {}
-        for kern, name, kms, _, _ in ex.profile():
+        singles = []
+        for kern, name, kms, _, nbytes in ex.profile():
             a = agg.setdefault(kern + " | " + name, [0, 0.0])
             a[0] += 1
             a[1] += kms
+            singles.append((kms, kern + " | " + name, nbytes))
         ex.set_profiling(False)
+        if os.environ.get("PSK_BENCH_SINGLES"):
+            # the launches furthest below the memory's rate, one by one: where a generic kernel ran
+            worst = sorted(singles, key=lambda r: -r[0])[:int(os.environ["PSK_BENCH_SINGLES"])]
+            print(json.dumps({"slowest_launches [ms, name, MB, GB/s]": [[round(m_, 3), n_, round(b_ / 1e6, 1), round(b_ / 1e6 / m_, 1) if m_ else None] for m_, n_, b_ in worst]}))
         top = sorted(agg.items(), key=lambda kv: -kv[1][1])[:14]
         print(json.dumps({"top_launches_ms": {k: [v[0], round(v[1], 3)] for k, v in top}, "profiled_total_ms": round(sum(v[1] for v in agg.values()), 2)}))
         print(json.dumps({"micro": "train", "shape": dims, "ms_per_step": ms, "tokens/s": B * T / ms * 1e3, "model TFLOP/s (3x forward)": flops / ms / 1e9, "loss": float(host.call("loss", [ids, y], ()))}))

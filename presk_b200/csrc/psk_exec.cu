@@ -883,6 +883,35 @@ static const void *widened_weights(psk_exec *e, const void *codes, int64_t count
     return wb;
 }
 
+// Whether a group is AdamW's parameter update as the host issues it (inputs m', bc1, v', bc2, eps, θ, λ, lr; steps
+// div, div, sqrt, add, div, mul, add, mul, sub) over whole contiguous runs, in an f32 kernel with bf16 or f32 buffers.
+static bool adamw_update_program(const psk_launch *l, const DevLaunch &L)
+{
+    if (l->n_steps != 9 || L.n_in != 8 || L.kdtype != PSK_F32 || L.guarded) return false;
+    static const int prim[9] = {PSK_DIV, PSK_DIV, PSK_SQRT, PSK_ADD, PSK_DIV, PSK_MUL, PSK_ADD, PSK_MUL, PSK_SUB};
+    static const int nargs[9] = {2, 2, 1, 2, 2, 2, 2, 2, 2};
+    static const int src[9][2] = {{0, 1}, {2, 3}, {-2, 0}, {-3, 4}, {-1, -4}, {5, 6}, {-5, -6}, {-7, 7}, {5, -8}};
+    for (int s = 0; s < 9; ++s) {
+        const psk_step &st = l->steps[s];
+        if (st.prim != prim[s] || st.nargs != nargs[s] || st.src[0] != src[s][0] || (nargs[s] == 2 && st.src[1] != src[s][1])) return false;
+    }
+    const int tensors[3] = {0, 2, 5}, scalars[5] = {1, 3, 4, 6, 7};
+    auto run = [&](const DevOperand &o) { // one contiguous run over the whole space, 16-byte aligned
+        if (o.affine || (o.dtype != PSK_BF16 && o.dtype != PSK_F32) || !aligned16(o.p)) return false;
+        int64_t expect = 1;
+        for (int a = L.n_outer - 1; a >= 0; --a) { if (L.dims[a] != 1 && o.stride[a] != expect) return false; expect *= L.dims[a]; }
+        return true;
+    };
+    for (int i : tensors) if (!run(L.in[i])) return false;
+    if (!run(L.out)) return false;
+    for (int i : scalars) {
+        const DevOperand &o = L.in[i];
+        if (o.affine || o.dtype == PSK_I8 || o.dtype == PSK_I64 || o.dtype == PSK_F64) return false;
+        for (int a = 0; a < L.n_outer; ++a) if (o.stride[a] != 0) return false;
+    }
+    return L.total % 8 == 0;
+}
+
 int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
 {
     cudaSetDevice(e->device);
@@ -1024,6 +1053,18 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
                 default: k_ew<4><<<g, 256, 0, e->stream>>>(E); break;
                 }
             }
+        }
+        else if (vec && adamw_update_program(l, L)) {
+            // the optimizer's nine-step update on runs of bf16 or f32 numbers: its own compile-time kernel
+            AdamwUpdate U;
+            memset(&U, 0, sizeof U);
+            U.m = L.in[0].p; U.v = L.in[2].p; U.theta = L.in[5].p; U.out = const_cast<void *>(L.out.p);
+            U.m_bf16 = L.in[0].dtype == PSK_BF16; U.v_bf16 = L.in[2].dtype == PSK_BF16; U.t_bf16 = L.in[5].dtype == PSK_BF16; U.o_bf16 = L.out.dtype == PSK_BF16;
+            const int scalars[5] = {1, 3, 4, 6, 7};
+            for (int i = 0; i < 5; ++i) { U.sc[i] = L.in[scalars[i]].p; U.sdt[i] = L.in[scalars[i]].dtype; }
+            U.nvec = L.total / 8;
+            k_adamw_update<<<grid_for(e, U.nvec, 256, 8), 256, 0, e->stream>>>(U);
+            e->last_kernel = "k_adamw_update";
         }
         else if (vec && l->n_steps > 8) k_fused_vec8<12><<<grid_for(e, L.total / 8, 256, 8), 256, 0, e->stream>>>(L);
         else if (vec) k_fused_vec8<8><<<grid_for(e, L.total / 8, 256, 8), 256, 0, e->stream>>>(L);
@@ -1228,6 +1269,17 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
             const int blocks = std::min(e->sms * 2, 1024);
             float *partials = (float *)psk_exec_alloc(e, (size_t)blocks * 4);
             if (!partials) { rc = fail(e, PSK_E10001, "reduce: no memory for the partial sums"); break; }
+            // one contiguous run of numbers the kernel reads unrounded: sixteen bytes a load
+            const DevOperand &X = L.in[0];
+            bool lin = (L.kind == PSK_REDUCE_SUMSQ || L.kind == PSK_REDUCE_SUM) && !X.affine && L.inner % 8 == 0 && aligned16(X.p)
+                && ((X.dtype == PSK_BF16 && (L.kdtype == PSK_BF16 || L.kdtype == PSK_F32)) || (X.dtype == PSK_F32 && L.kdtype == PSK_F32));
+            {
+                int64_t expect = 1;
+                for (int a = L.n_inner - 1; a >= 0 && lin; --a) { lin = X.stride[a] == expect; expect *= L.dims[a]; }
+            }
+            if (lin && X.dtype == PSK_BF16) k_reduce_all_partials_lin<true><<<blocks, 512, 0, e->stream>>>(X.p, L.inner / 8, L.kind == PSK_REDUCE_SUMSQ ? 1 : 0, partials);
+            else if (lin) k_reduce_all_partials_lin<false><<<blocks, 512, 0, e->stream>>>(X.p, L.inner / 8, L.kind == PSK_REDUCE_SUMSQ ? 1 : 0, partials);
+            else
             k_reduce_all_partials<<<blocks, 1024, 0, e->stream>>>(L, partials);
             k_reduce_all_finish<<<1, 1024, 0, e->stream>>>(L, partials, blocks);
             psk_exec_free(e, partials); // handed out again only to later work of the same stream

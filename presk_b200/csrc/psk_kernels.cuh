@@ -791,6 +791,85 @@ __global__ void __launch_bounds__(1024) k_reduce_all_tree(const __grid_constant_
     if (L.guarded && ovf) atomicOr(L.ovf, 1u);
 }
 
+// A leaf's sum (or sum of squares) when the leaf is one contiguous run of bf16 or f32 numbers that the kernel
+// reads unrounded: sixteen bytes a load. The grid is fixed, so the order of the sum is too (a declared order of
+// PSK_ORDER_DEVICE: a thread's vectors in turn, then the block's tree, then k_reduce_all_finish).
+template <bool BF16>
+__global__ void __launch_bounds__(512) k_reduce_all_partials_lin(const void *p, int64_t nvec, int sumsq, float *partials)
+{
+    __shared__ float red[32];
+    float acc = 0.0f;
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < nvec; c += step) {
+        float x[8];
+        if (BF16) {
+            const uint4 w = reinterpret_cast<const uint4 *>(p)[c];
+            const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { x[2 * i] = bits_f32(u[i] << 16); x[2 * i + 1] = bits_f32(u[i] & 0xffff0000u); }
+        } else {
+            const float4 a = reinterpret_cast<const float4 *>(p)[2 * c], b = reinterpret_cast<const float4 *>(p)[2 * c + 1];
+            x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc = __fadd_rn(acc, sumsq ? __fmul_rn(x[i], x[i]) : x[i]);
+    }
+    acc = block_reduce<false>(acc, red);
+    if (threadIdx.x == 0) partials[blockIdx.x] = acc;
+}
+
+// AdamW's parameter update as one compile-time program (optim.rs:156-219, the group the host issues as nine steps:
+// m̂ = m'/bc1, v̂ = v'/bc2, √v̂, + ε, m̂ / that, θ·λ, their sum, × lr, θ − that): the same nine IEEE operations in
+// the same order on every element, so the bits of the generic group, at the memory's rate instead of the
+// interpreter's. m', v' and θ are bf16 or f32 runs of 8·nvec elements, the five scalars any real type.
+struct AdamwUpdate {
+    const void *m, *v, *theta, *sc[5]; // sc: bc1, bc2, eps, lambda, lr
+    void *out;
+    int32_t m_bf16, v_bf16, t_bf16, o_bf16, sdt[5];
+    int64_t nvec;
+};
+
+PSK_DEV void load8_real(const void *p, bool bf16, int64_t c, float (&x)[8])
+{
+    if (bf16) {
+        const uint4 w = reinterpret_cast<const uint4 *>(p)[c];
+        const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { x[2 * i] = bits_f32(u[i] << 16); x[2 * i + 1] = bits_f32(u[i] & 0xffff0000u); }
+    } else {
+        const float4 a = reinterpret_cast<const float4 *>(p)[2 * c], b = reinterpret_cast<const float4 *>(p)[2 * c + 1];
+        x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+    }
+}
+
+__global__ void __launch_bounds__(256) k_adamw_update(const __grid_constant__ AdamwUpdate P)
+{
+    const float bc1 = load_real(P.sc[0], P.sdt[0], 0), bc2 = load_real(P.sc[1], P.sdt[1], 0), eps = load_real(P.sc[2], P.sdt[2], 0);
+    const float lambda = load_real(P.sc[3], P.sdt[3], 0), lr = load_real(P.sc[4], P.sdt[4], 0);
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < P.nvec; c += step) {
+        float m[8], v[8], t[8], r[8];
+        load8_real(P.m, P.m_bf16, c, m);
+        load8_real(P.v, P.v_bf16, c, v);
+        load8_real(P.theta, P.t_bf16, c, t);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float mh = __fdiv_rn(m[i], bc1), vh = __fdiv_rn(v[i], bc2);
+            const float upd = __fdiv_rn(mh, __fadd_rn(__fsqrt_rn(vh), eps));
+            r[i] = __fsub_rn(t[i], __fmul_rn(__fadd_rn(upd, __fmul_rn(t[i], lambda)), lr));
+        }
+        if (P.o_bf16) {
+            uint4 w;
+            w.x = (uint32_t)f32_to_bf16(r[0]) | ((uint32_t)f32_to_bf16(r[1]) << 16); w.y = (uint32_t)f32_to_bf16(r[2]) | ((uint32_t)f32_to_bf16(r[3]) << 16);
+            w.z = (uint32_t)f32_to_bf16(r[4]) | ((uint32_t)f32_to_bf16(r[5]) << 16); w.w = (uint32_t)f32_to_bf16(r[6]) | ((uint32_t)f32_to_bf16(r[7]) << 16);
+            reinterpret_cast<uint4 *>(P.out)[c] = w;
+        } else {
+            reinterpret_cast<float4 *>(P.out)[2 * c] = make_float4(r[0], r[1], r[2], r[3]);
+            reinterpret_cast<float4 *>(P.out)[2 * c + 1] = make_float4(r[4], r[5], r[6], r[7]);
+        }
+    }
+}
+
 // The same for a large tensor (a parameter tree's leaf under `sum_squares`): every block sums its share into
 // `partials`, a second launch of one block sums those. The grid's size is fixed, so the sum's order is too.
 __global__ void __launch_bounds__(1024) k_reduce_all_partials(const __grid_constant__ DevLaunch L, float *partials)

@@ -455,7 +455,13 @@ def test_llama_gradient_bit_exact(cuda, oracle, dtype):
         h.call("loss_grad", [ids, y], p["tok"].shape)
         leaves = [h.result(k, np.shape(v)) for k, v in p.items()]
         for t in (1, 2):
+            if ex is cuda:
+                cuda.set_profiling(True)
             h.adamw_step(t, 2)
+            if ex is cuda:
+                # the nine-step update of every leaf ran as its compile-time kernel (the bits below are the generic group's)
+                assert sum(1 for rec in cuda.profile() if rec[0] == "k_adamw_update") == len(p)
+                cuda.set_profiling(False)
             h.call("loss_grad", [ids, y], p["tok"].shape)
         leaves += [h.result(k, np.shape(v)) for k, v in p.items()]
         runs.append(leaves)
