@@ -53,13 +53,13 @@ __global__ void __launch_bounds__(THREADS) k_attn_step(const __grid_constant__ P
     const uint16_t *kb = P.k + b * P.k_b + g * P.k_g + 4 * lane;
     const uint16_t *vb = P.v + b * P.v_b + g * P.v_g + 4 * lane;
 
-    // scores: a warp a position, four positions in flight a warp
-    for (int t0 = warp * 4; t0 < P.len; t0 += WARPS * 4) {
-        uint2 kw[4];
+    // scores: a warp a position, eight positions in flight a warp
+    for (int t0 = warp * 8; t0 < P.len; t0 += WARPS * 8) {
+        uint2 kw[8];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) kw[j] = t0 + j < P.len ? *reinterpret_cast<const uint2 *>(kb + (int64_t)(t0 + j) * P.k_t) : make_uint2(0u, 0u);
+        for (int j = 0; j < 8; ++j) kw[j] = t0 + j < P.len ? *reinterpret_cast<const uint2 *>(kb + (int64_t)(t0 + j) * P.k_t) : make_uint2(0u, 0u);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < 8; ++j) {
             float kf[4];
             unpack4(kw[j], kf);
             float s = __fadd_rn(__fadd_rn(__fmul_rn(qv[0], kf[0]), __fmul_rn(qv[1], kf[1])), __fadd_rn(__fmul_rn(qv[2], kf[2]), __fmul_rn(qv[3], kf[3])));
@@ -81,17 +81,20 @@ __global__ void __launch_bounds__(THREADS) k_attn_step(const __grid_constant__ P
     }
     z = block_reduce<false>(z, red);
     __syncthreads();
+    // the weights, rounded to bf16 as the softmax's site stores them: one division a position (not one a lane)
+    for (int t = threadIdx.x; t < P.len; t += THREADS) sc[t] = attn::bf16_round(__fdiv_rn(sc[t], z));
+    __syncthreads();
 
-    // the values: a warp a position again, the weight rounded to bf16 as the softmax's site stores it
+    // the values: a warp a position again, eight positions in flight a warp
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    for (int t0 = warp * 4; t0 < P.len; t0 += WARPS * 4) {
-        uint2 vw[4];
+    for (int t0 = warp * 8; t0 < P.len; t0 += WARPS * 8) {
+        uint2 vw[8];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) vw[j] = t0 + j < P.len ? *reinterpret_cast<const uint2 *>(vb + (int64_t)(t0 + j) * P.v_t) : make_uint2(0u, 0u);
+        for (int j = 0; j < 8; ++j) vw[j] = t0 + j < P.len ? *reinterpret_cast<const uint2 *>(vb + (int64_t)(t0 + j) * P.v_t) : make_uint2(0u, 0u);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < 8; ++j) {
             if (t0 + j >= P.len) break;
-            const float w = attn::bf16_round(__fdiv_rn(sc[t0 + j], z));
+            const float w = sc[t0 + j];
             float vf[4];
             unpack4(vw[j], vf);
 #pragma unroll

@@ -488,7 +488,12 @@ int launch_i8(psk_exec *e, const GemmMap &g, const DevOperand &A, const DevOpera
     const bool b_n_major = g.b_k != 1;
     const int64_t batch_hi = g.batch / g.batch_lo;
     CUtensorMap ma, mb;
-    if (!make_map_u8(e, &ma, A.p, (uint64_t)g.k, (uint64_t)g.m, (uint64_t)g.batch_lo, (uint64_t)batch_hi, (uint64_t)g.a_row, (uint64_t)g.a_lo, (uint64_t)g.a_hi, tci8::BKB, tci8::BM * tci8::MT))
+    // tiles of 128 rows with the rescale hidden behind the next tile's products, or of 256 with less traffic from
+    // the L2 and the rescale exposed (psk_gemm_i8.cuh); PSK_I8_MT chooses, for measurements
+    const char *mt_word = getenv("PSK_I8_MT"); // read at every launch, so that a test can run both forms
+    const int mt_env = mt_word ? atoi(mt_word) : 1;
+    const int mt_rows = (mt_env == 2 && g.m >= 256) ? 2 : 1;
+    if (!make_map_u8(e, &ma, A.p, (uint64_t)g.k, (uint64_t)g.m, (uint64_t)g.batch_lo, (uint64_t)batch_hi, (uint64_t)g.a_row, (uint64_t)g.a_lo, (uint64_t)g.a_hi, tci8::BKB, (uint32_t)(tci8::BM * mt_rows)))
         return fail(e, PSK_E7001, "integer contraction: operand 0's strides do not make a tensor map");
     const bool okb = b_n_major
         ? make_map_u8(e, &mb, B.p, (uint64_t)g.n, (uint64_t)g.k, (uint64_t)g.batch_lo, (uint64_t)batch_hi, (uint64_t)g.b_k, (uint64_t)g.b_lo, (uint64_t)g.b_hi, 128, tci8::BKB)
@@ -497,7 +502,7 @@ int launch_i8(psk_exec *e, const GemmMap &g, const DevOperand &A, const DevOpera
     tci8::Params P;
     memset(&P, 0, sizeof P);
     P.m = g.m; P.n = g.n; P.k = g.k; P.batch = g.batch; P.batch_lo = g.batch_lo;
-    P.tiles_m = (g.m + tci8::BM * tci8::MT - 1) / (tci8::BM * tci8::MT);
+    P.tiles_m = (g.m + tci8::BM * mt_rows - 1) / (tci8::BM * mt_rows);
     P.tiles_n = (g.n + tci8::BN - 1) / tci8::BN;
     {
         const int64_t col_bytes = (int64_t)tci8::BN * g.k;
@@ -524,12 +529,14 @@ int launch_i8(psk_exec *e, const GemmMap &g, const DevOperand &A, const DevOpera
         P.colsum = colsum;
     }
     if (!e->i8_attr_set) {
-        CUDA_TRY(e, cudaFuncSetAttribute(tci8::k_gemm_i8, cudaFuncAttributeMaxDynamicSharedMemorySize, tci8::SMEM_TOTAL));
+        CUDA_TRY(e, cudaFuncSetAttribute(tci8::k_gemm_i8<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, tci8::Cfg<1>::SMEM_TOTAL));
+        CUDA_TRY(e, cudaFuncSetAttribute(tci8::k_gemm_i8<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, tci8::Cfg<2>::SMEM_TOTAL));
         e->i8_attr_set = true;
     }
     const int64_t tiles = P.tiles_m * P.tiles_n * g.batch;
     const int grid = (int)std::min<int64_t>(tiles, e->sms);
-    tci8::k_gemm_i8<<<grid, tci8::THREADS, tci8::SMEM_TOTAL, e->stream>>>(ma, mb, P);
+    if (mt_rows == 2) tci8::k_gemm_i8<2><<<grid, tci8::THREADS, tci8::Cfg<2>::SMEM_TOTAL, e->stream>>>(ma, mb, P);
+    else tci8::k_gemm_i8<1><<<grid, tci8::THREADS, tci8::Cfg<1>::SMEM_TOTAL, e->stream>>>(ma, mb, P);
     if (colsum) psk_exec_free(e, colsum); // handed out again only to later work of the same stream
     CUDA_TRY(e, cudaGetLastError());
     e->kernels += 1;

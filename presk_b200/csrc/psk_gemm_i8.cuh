@@ -34,14 +34,21 @@ namespace psk {
 namespace tci8 {
 
 constexpr int BM = 128, BN = 256, BKB = 128; // BKB: bytes = elements of the summed axis a stage
-constexpr int MT = 2;
-constexpr int STAGES = 3;
-constexpr int A_BYTES = MT * BM * BKB, B_BYTES = BN * BKB;
-constexpr int TILE_BYTES = STAGES * (A_BYTES + B_BYTES);
+constexpr int B_BYTES = BN * BKB;
 constexpr int BAR_BYTES = 256;
 constexpr int STAGE_OUT = 8 * 32 * 128;
-constexpr int SMEM_TOTAL = TILE_BYTES + BAR_BYTES + STAGE_OUT + 1024;
 constexpr int THREADS = 320;
+// Two forms, as for the bf16 kernel. MT = 2: tiles of 256 rows, two accumulators sharing B's tile (a third less
+// traffic from the L2 a product, three stages of 64 KB), the accumulators fill tensor memory and the rescale runs
+// after the tile's products. MT = 1: tiles of 128 rows, the two accumulators used in turn, so that a tile's rescale
+// runs under the next tile's products (four stages of 48 KB).
+template <int MT>
+struct Cfg {
+    static constexpr int STAGES = MT == 2 ? 3 : 4;
+    static constexpr int A_BYTES = MT * BM * BKB;
+    static constexpr int TILE_BYTES = STAGES * (A_BYTES + B_BYTES);
+    static constexpr int SMEM_TOTAL = TILE_BYTES + BAR_BYTES + STAGE_OUT + 1024;
+};
 
 struct Params {
     int64_t m, n, k;
@@ -149,14 +156,16 @@ PSK_DEV int64_t count_to_affine(int32_t n, double base, float s)
     return quotient_round_exact(n < 0, (u128_t)(n < 0 ? -(int64_t)n : (int64_t)n) * (u128_t)mb, eb, s);
 }
 
+template <int MT>
 __global__ void __launch_bounds__(THREADS, 1) k_gemm_i8(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ Params P)
 {
+    constexpr int STAGES = Cfg<MT>::STAGES, A_BYTES = Cfg<MT>::A_BYTES, TILE_BYTES = Cfg<MT>::TILE_BYTES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t *smem_a = smem;
     uint8_t *smem_b = smem + STAGES * A_BYTES;
     uint64_t *bars = (uint64_t *)(smem + TILE_BYTES);
-    // bars: full[STAGES], empty[STAGES], tmem_full, (unused), tmem_empty[2]
+    // bars: full[STAGES], empty[STAGES], tmem_full[2] (MT = 2 uses the first), tmem_empty[2]
     uint32_t *tmem_slot = (uint32_t *)(bars + 2 * STAGES + 4);
     volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
 
@@ -220,7 +229,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_i8(const __grid_constant__ 
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = instr_desc_i8(P.a_unsigned, P.b_n_major);
-            uint32_t stage = 0, phase = 0, acc_phase = 0;
+            uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
             for (int64_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 for (int kb = 0; kb < num_kb; ++kb) {
@@ -231,9 +240,10 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_i8(const __grid_constant__ 
                     const uint32_t b_addr = tc::smem_u32(smem_b + stage * B_BYTES);
 #pragma unroll
                     for (int h = 0; h < MT; ++h) {
+                        const uint32_t slot = MT == 2 ? (uint32_t)h : acc; // the accumulator these products add into
                         if (kb == 0) {
-                            // this half's accumulator must have been drained by the epilogue of the tile before
-                            ok = tc::mbar_wait(tempty0 + 8 * h, acc_phase ^ 1u, abort_flag, P.status, 0x72u);
+                            // it must have been drained by the epilogue of the tile that used it before
+                            ok = tc::mbar_wait(tempty0 + 8 * slot, acc_phase ^ 1u, abort_flag, P.status, 0x72u);
                             if (!ok) break;
                             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                         }
@@ -243,7 +253,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_i8(const __grid_constant__ 
                             // 128 bytes of an N-major tile
                             const uint64_t ad = tc::smem_desc(a_addr + h * (BM * BKB) + k * 32, 16, 1024);
                             const uint64_t bd = P.b_n_major ? tc::smem_desc(b_addr + k * 4096, 16384, 1024) : tc::smem_desc(b_addr + k * 32, 16, 1024);
-                            umma_i8(tmem_base + h * BN, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+                            umma_i8(tmem_base + slot * BN, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
                         }
                     }
                     if (!ok) break;
@@ -251,13 +261,14 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_i8(const __grid_constant__ 
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
                 if (!ok) break;
-                tc::umma_commit(tfull0);
-                acc_phase ^= 1u;
+                tc::umma_commit(tfull0 + 8 * (MT == 2 ? 0u : acc));
+                if (MT == 2) acc_phase ^= 1u;
+                else if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
             }
         }
     } else {
         const int quad = warp & 3;
-        uint32_t acc_phase = 0, ovf = 0;
+        uint32_t acc = 0, acc_phase = 0, ovf = 0;
         bool ok = true;
         const int half_id = (warp - 2) >> 2;
         uint4 *stage_out = reinterpret_cast<uint4 *>(smem + TILE_BYTES + BAR_BYTES) + (warp - 2) * 32 * 8;
@@ -269,7 +280,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_i8(const __grid_constant__ 
             tc::tile_of(r, P.tiles_m, P.tiles_n, P.panel, mt, nt);
             const int64_t m0 = mt * BM * MT, n0 = nt * BN;
             const int64_t blo = b % P.batch_lo, bhi = b / P.batch_lo;
-            ok = tc::mbar_wait(tfull0, acc_phase, abort_flag, P.status, 0x74u);
+            ok = tc::mbar_wait(tfull0 + 8 * (MT == 2 ? 0u : acc), acc_phase, abort_flag, P.status, 0x74u);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -287,7 +298,8 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_i8(const __grid_constant__ 
                     const uint32_t rq = (uint32_t)row / rcnt;
                     row_off = boff + (int64_t)rq * P.c_row_hi + (int64_t)((uint32_t)row - rq * rcnt) * P.c_row_lo;
                 }
-                const uint32_t tbase = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)mh * BN;
+                const uint32_t slot = MT == 2 ? (uint32_t)mh : acc;
+                const uint32_t tbase = tmem_base + ((uint32_t)(quad * 32) << 16) + slot * BN;
 #pragma unroll 1
                 for (int c0 = half_id * 32; c0 < BN; c0 += 64) {
                     uint32_t v[32];
@@ -381,9 +393,10 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_i8(const __grid_constant__ 
                 }
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
-                if (lane == 0) tc::mbar_arrive(tempty0 + 8 * (uint32_t)mh);
+                if (lane == 0) tc::mbar_arrive(tempty0 + 8 * slot);
             }
-            acc_phase ^= 1u;
+            if (MT == 2) acc_phase ^= 1u;
+            else if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
         }
         if (P.guarded && ovf) atomicOr(P.ovf, 1u);
     }

@@ -395,8 +395,21 @@ def test_weight_gradient_contraction_reaches_the_tensor_cores(cuda, oracle):
         cuda.free(p)
 
 
-@pytest.mark.parametrize("m,k,n,b_n_major", [(300, 576, 272, True), (300, 576, 272, False), (512, 4096, 256, True), (129, 160, 48, True), (1, 1024, 512, True), (64, 65536, 32, False)])
-def test_integer_sums_on_the_tensor_cores_are_exact(cuda, oracle, m, k, n, b_n_major):
+@pytest.fixture(params=[1, 2])
+def i8_tile_form(request):
+    """Both forms of the integer kernel: tiles of 128 rows (the rescale hidden behind the next tile) and of 256."""
+    import os
+    before = os.environ.get("PSK_I8_MT")
+    os.environ["PSK_I8_MT"] = str(request.param)
+    yield request.param
+    if before is None:
+        del os.environ["PSK_I8_MT"]
+    else:
+        os.environ["PSK_I8_MT"] = before
+
+
+@pytest.mark.parametrize("m,k,n,b_n_major", [(300, 576, 272, True), (300, 576, 272, False), (512, 4096, 256, True), (129, 160, 48, True), (1, 1024, 512, True), (64, 65536, 32, False), (2600, 160, 2100, True)])
+def test_integer_sums_on_the_tensor_cores_are_exact(cuda, oracle, i8_tile_form, m, k, n, b_n_major):
     """`product: i32, accum: i32` at contraction scale: affine activations (u8 with a zero point, i8 without and
     with one) times int8 weights with a scale a column, on tcgen05's 8-bit integer kind. Sums modulo 2^32 are
     associative and the store rounds the exact value once, so every output is the oracle's, bit for bit, for every

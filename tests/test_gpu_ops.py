@@ -379,6 +379,55 @@ def test_blockwise_attention_against_its_four_launches(cuda, oracle, B, G, P, T,
         assert err.mean() <= 1.5 * oracle_err.mean() + 2.0**-9 * np.abs(exact).mean(), (err.mean(), oracle_err.mean())
 
 
+@pytest.mark.parametrize("B,G,P,T2", [(2, 2, 2, 1), (1, 2, 1, 7), (3, 2, 4, 1000), (1, 1, 2, 13001)])
+def test_one_position_against_a_cache(cuda, oracle, B, G, P, T2):
+    """PSK_OP_ATTENTION with seq = 1 and no mask (a decode step: `k_attn_step`) against the oracle's four launches.
+    The kernel keeps their three roundings (score, scaled score and normalised weight to bf16) and their exp; only
+    the order of the three sums differs, so the result is within a bf16 unit or two of an element: 2^-7 of the
+    result's scale at most, 2^-9 of the mean magnitude on average. Cache lengths of one position, of a few, of a
+    thousand and of more than fit the default 48 KB of shared memory; keys and values strided as a cache holds them
+    (a view of the first T2 positions of a longer buffer)."""
+    HD, TMAX = 128, T2 + 5
+    rng = np.random.default_rng(T2)
+    q = bf16_of(oracle, rng.standard_normal((B, G, P, 1, HD)) * 1.5)
+    kbuf = bf16_of(oracle, rng.standard_normal((B, G, TMAX, HD)) * 1.5)
+    vbuf = bf16_of(oracle, rng.standard_normal((B, TMAX, G, HD)))
+    rt = bf16_of(oracle, np.array(np.sqrt(np.float32(HD)), np.float32).reshape(()))
+    l = launch_desc(abi.OP_ATTENTION, abi.BF16, [B, G, P, 1, HD], [T2], order=abi.ORDER_DEVICE, name=b"attention[online]")
+    l.n_inputs, l.masked = 4, 0
+    l.iparam[0] = 1
+    l.iparam[1] = l.iparam[2] = l.iparam[3] = abi.BF16
+    set_operand(l.inputs[0], abi.BF16, [B, G, P, 1, HD], [0, 1, 2, 3, 4])
+    # the cache's views: the buffers' strides, T2 of their TMAX positions
+    for op, strides, n in ((l.inputs[1], {0: G * TMAX * HD, 1: TMAX * HD, 5: HD, 4: 1}, B * G * TMAX * HD), (l.inputs[2], {0: TMAX * G * HD, 5: G * HD, 1: HD, 4: 1}, B * TMAX * G * HD)):
+        op.dtype, op.numel = abi.BF16, n
+        for ax, st in strides.items():
+            op.stride[ax] = st
+    set_operand(l.inputs[3], abi.BF16, [], [])
+    set_operand(l.out, abi.BF16, [B, 1, G, P, HD], [0, 3, 1, 2, 4])
+    host_in = [q, kbuf, vbuf, rt]
+    dev = [cuda.upload(a) for a in host_in]
+    out_bytes = B * G * P * HD * 2
+    pout = cuda.alloc(out_bytes)
+    cuda.set_profiling(True)
+    cuda.run(l, dev + [pout])
+    cuda.sync()
+    assert [rec[0] for rec in cuda.profile()] == ["k_attn_step"]
+    cuda.set_profiling(False)
+    got = bf16_value(cuda.download(pout, out_bytes).view(np.uint16))
+    for p_ in dev + [pout]:
+        cuda.free(p_)
+    want_b = np.zeros(out_bytes, np.uint8)
+    oracle.run(l, [np.ascontiguousarray(a) for a in host_in] + [want_b])
+    want = bf16_value(want_b.view(np.uint16))
+    assert np.isfinite(got).all()
+    err = np.abs(got - want)
+    assert err.max() <= 2.0**-7 * np.abs(want).max(), (err.max(), np.abs(want).max())
+    assert err.mean() <= 2.0**-9 * np.abs(want).mean(), (err.mean(), np.abs(want).mean())
+    if T2 == 1:  # one position: its weight is 1 and the result is that position's values, exactly
+        assert np.array_equal(got.reshape(B, G, P, HD), np.broadcast_to(bf16_value(vbuf[:, 0])[:, :, None, :], (B, G, P, HD)))
+
+
 def test_blockwise_attention_is_refused_where_it_does_not_apply(cuda):
     """Under the sequential order, or with a head dimension other than 128, the launch is refused with
     E7005 and nothing runs: the host then keeps the four launches apart."""
