@@ -524,7 +524,12 @@ int launch_i8(psk_exec *e, const GemmMap &g, const DevOperand &A, const DevOpera
     if (A.affine_zero != 0) {
         colsum = (int32_t *)psk_exec_alloc(e, (size_t)g.n * g.batch * 4);
         if (!colsum) return fail(e, PSK_E10001, "integer contraction: no memory for the weights' column sums");
-        tci8::k_colsum_i8<<<grid_for(e, g.n * g.batch, 256, 8), 256, 0, e->stream>>>((const int8_t *)B.p, g.n, g.k, g.batch, g.batch_lo, g.b_n, g.b_k, g.b_lo, g.b_hi, colsum);
+        CUDA_TRY(e, cudaMemsetAsync(colsum, 0, (size_t)g.n * g.batch * 4, e->stream));
+        {
+            const int64_t work = g.b_k == 1 ? g.n * g.batch * 32 : g.n * g.batch; // threads: a warp or a thread a column
+            dim3 cgrid((unsigned)std::min<int64_t>((work + 255) / 256, 65535), (unsigned)((g.k + tci8::COLSUM_RUN - 1) / tci8::COLSUM_RUN));
+            tci8::k_colsum_i8<<<cgrid, 256, 0, e->stream>>>((const int8_t *)B.p, g.n, g.k, g.batch, g.batch_lo, g.b_n, g.b_k, g.b_lo, g.b_hi, colsum);
+        }
         e->kernels += 1;
         P.colsum = colsum;
     }

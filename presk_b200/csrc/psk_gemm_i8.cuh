@@ -96,16 +96,37 @@ PSK_DEV void umma_i8(uint32_t tmem_c, uint64_t adesc, uint64_t bdesc, uint32_t i
         : "memory");
 }
 
-// sum_k w[k, col] for every (batch entry, column), wrapped to 32 bits.
+// sum_k w[k, col] for every (batch entry, column), wrapped to 32 bits: `out` starts at zero and every block adds
+// its run of the summed axis (integer additions that wrap are associative, so the order the atomics land in does
+// not matter). blockIdx.y: the run. N-major weights (s_n = 1): a thread a column, neighbouring threads neighbouring
+// columns. K-major (s_k = 1): a warp a column, its lanes neighbouring k.
+constexpr int COLSUM_RUN = 512;
 static __global__ void __launch_bounds__(256) k_colsum_i8(const int8_t *w, int64_t n, int64_t k, int64_t batch, int64_t batch_lo, int64_t s_n, int64_t s_k, int64_t s_lo, int64_t s_hi, int32_t *out)
 {
-    const int64_t total = n * batch, step = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step) {
-        const int64_t b = i / n, c = i - b * n;
-        const int8_t *p = w + (b % batch_lo) * s_lo + (b / batch_lo) * s_hi + c * s_n;
-        uint32_t acc = 0;
-        for (int64_t t = 0; t < k; ++t) acc += (uint32_t)(int32_t)p[t * s_k];
-        out[i] = (int32_t)acc;
+    const int64_t k0 = (int64_t)blockIdx.y * COLSUM_RUN, k1 = k0 + COLSUM_RUN < k ? k0 + COLSUM_RUN : k;
+    const int64_t total = n * batch;
+    if (s_k != 1) {
+        const int64_t step = (int64_t)gridDim.x * blockDim.x;
+        for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step) {
+            const int64_t b = i / n, c = i - b * n;
+            const int8_t *p = w + (b % batch_lo) * s_lo + (b / batch_lo) * s_hi + c * s_n;
+            uint32_t acc = 0;
+#pragma unroll 8
+            for (int64_t t = k0; t < k1; ++t) acc += (uint32_t)(int32_t)p[t * s_k];
+            atomicAdd(reinterpret_cast<unsigned int *>(out) + i, acc);
+        }
+    } else {
+        const int lane = threadIdx.x & 31;
+        const int64_t warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+        for (int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; i < total; i += warps) {
+            const int64_t b = i / n, c = i - b * n;
+            const int8_t *p = w + (b % batch_lo) * s_lo + (b / batch_lo) * s_hi + c * s_n;
+            uint32_t acc = 0;
+            for (int64_t t = k0 + lane; t < k1; t += 32) acc += (uint32_t)(int32_t)p[t];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (lane == 0) atomicAdd(reinterpret_cast<unsigned int *>(out) + i, acc);
+        }
     }
 }
 
