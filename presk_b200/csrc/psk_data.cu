@@ -13,6 +13,7 @@
 // the buffer's type as the reference's store_real rounds (presk_rt.c:107-129: f32 by the machine's conversion,
 // bf16 by way of f32, binary16 and e8m15 directly from the double).
 #include <cuda_runtime.h>
+#include <algorithm>
 #include <cerrno>
 #include <cstdarg>
 #include <cstdio>
