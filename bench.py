@@ -48,6 +48,8 @@ WORKLOADS = {
     # its int8 variant: the same architecture, projection and FFN weights int8 with one f32 scale a
     # channel, bf16 activations, seq 1024, batch 16 a GPU
     "llama7b_int8_prefill_b16_t1024": dict(consts=dict(V=32000, D=4096, H=32, G=32, FF=11008, L=32), B=16, T=1024, int8=True),
+    "llama7b_w8a8_prefill_b16_t1024": dict(consts=dict(V=32000, D=4096, H=32, G=32, FF=11008, L=32), B=16, T=1024, int8="w8a8"),
+    "llama7b_w8a8_prefill_b8_t2048": dict(consts=dict(V=32000, D=4096, H=32, G=32, FF=11008, L=32), B=8, T=2048, int8="w8a8"),
     # and with those weights stored e4m3fn (a `params` entry; the reference has no scale for such weights, so N(0, 0.02)
     # keeps about three significant bits): the same launches, the weights widened exactly
     "llama7b_e4m3w_prefill_b16_t1024": dict(consts=dict(V=32000, D=4096, H=32, G=32, FF=11008, L=32), B=16, T=1024, int8="e4m3fn"),
@@ -90,6 +92,24 @@ def realization(paths, int8=False, attention="unfused", launches="reference"):
     }
     if int8 is True:
         rz["quant"] = {p: {"bits": 8, "over": -2} for p in QUANTISED}
+    return rz
+
+
+# W8A8: the projections' inputs (the norm's result, silu(gate)·up) stored as i8 codes with static scales, every
+# projection's weights and the head's as int8, those contractions' products and sums counted in i32: the integer-sum
+# kernel on tcgen05's 8-bit kind. The attention's result stays bf16 (the out-projection widens its int8 weights).
+W8A8_SCALED = ("RMSNorm.apply/%10", "SwiGLU.apply/%7")
+W8A8_INT_SUMS = ("Attention.apply/%7", "Attention.apply/%11", "Attention.apply/%14", "Dense.apply/%3", "Llama.apply/%11")
+
+
+def w8a8_realization(paths, attention, launches, scales):
+    quantised = QUANTISED + ("head",)
+    rz = realization(paths, False, attention, launches)
+    rz["params"] = {p: "bf16" for p in paths if p not in quantised}
+    rz["quant"] = {p: {"bits": 8, "over": -2} for p in quantised}
+    rz["scaled"] = {site: {"int": "i8/sat", "scale": float(np.float32(scales[site])), "zero": 0} for site in W8A8_SCALED}
+    rz["product"] = {site: "i32" for site in W8A8_INT_SUMS}
+    rz["accum"] = {site: "i32" for site in W8A8_INT_SUMS}
     return rz
 
 
@@ -185,7 +205,8 @@ def cpu_prefill_tokens_per_s(consts, T, B, threads, int8=False, direct=False, di
     orc = oracle_lib.load()
     rng = np.random.default_rng(0)
     Ts = min(T, 128)
-    weights = "int8" if int8 is True else ("e4m3fn" if int8 == "e4m3fn" else "bf16")
+    # (the W8A8 workload's CPU leg runs the W8A16 realization: the same int8 weights against bf16 activations)
+    weights = "int8" if int8 in (True, "w8a8") else ("e4m3fn" if int8 == "e4m3fn" else "bf16")
     fmt = lambda ts: "[" + ", ".join(f"{t:.2f}" for t in ts) + "]"
 
     LN = 3
@@ -857,7 +878,10 @@ def main():
     consts, B, T = w["consts"], w["B"], w["T"]
     rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
     threads = os.cpu_count() or 1
-    config = {"workload": args.workload, **{k: v for k, v in consts.items()}, "batch_per_gpu": B, "seq_len": T, "global_batch": B * world, "parallelism": f"dp{world}", "realization": "bf16 storage, f32 norm statistics/logits/loss, order device, attention " + args.attention + ", launches " + args.launches, "l2": "inputs_larger_than_l2 (13.5 GB of weights stream through every step)"}
+    config = {"workload": args.workload, **{k: v for k, v in consts.items()}, "batch_per_gpu": B, "seq_len": T, "global_batch": B * world, "parallelism": f"dp{world}", "realization": "bf16 storage, f32 norm statistics/logits/loss, order device, attention " + args.attention + ", launches " + args.launches
+              + {True: "; projection and FFN weights int8 with a scale a channel", "e4m3fn": "; projection and FFN weights stored e4m3fn",
+                 "w8a8": "; W8A8: the projections' inputs as i8 codes with static scales from a calibration pass, projection, FFN and head weights int8, those contractions' products and sums i32"}.get(w.get("int8", False), ""),
+              "l2": "inputs_larger_than_l2 (the weights stream through every step)"}
 
     if args.impl == "reference":
         if rank != 0:
@@ -900,17 +924,34 @@ def main():
                 comm = None
                 comm_kind = "torch.distributed (psk_comm failed on another rank)"
     shapes = param_shapes(consts)
-    host = Host(ex, realization(shapes, w.get("int8", False), args.attention, args.launches)).prepare("llama", **consts)
-    for i, (path, (shape, std)) in enumerate(shapes.items()):
-        host.init_param(path, 1000 + i, std, shape)
-    ex.sync()
-
     rng = np.random.default_rng(rank)
     ids_pinned = torch.from_numpy(rng.integers(0, consts["V"], size=(B, T), dtype=np.int64)).pin_memory()
     y_pinned = torch.from_numpy(rng.integers(0, consts["V"], size=(B, T), dtype=np.int64)).pin_memory()
     ids_np, y_np = ids_pinned.numpy(), y_pinned.numpy()
     ids_dev, y_dev = ex.upload(ids_np), ex.upload(y_np)
     dev_inputs = [(ids_dev, abi.I64, (B, T)), (y_dev, abi.I64, (B, T))]
+    w8a8_scales = None
+    if w.get("int8") == "w8a8":
+        # `presk calibrate` then `presk scales`: one pass of the bf16 realization with every launch's magnitudes
+        # folded into its site (all ranks' merged), and an absmax scale a scaled site from them; outside every
+        # timed region
+        cal = Host(ex, realization(shapes, False, "unfused", "reference")).prepare("llama", **consts)
+        for i, (path, (shape, std)) in enumerate(shapes.items()):
+            cal.init_param(path, 1000 + i, std, shape)
+        cal.set_calibrating(True)
+        cal.call_device("loss", dev_inputs)
+        ex.sync()
+        if comm is not None:
+            cal.envelope_allreduce(comm)
+        env = cal.envelope()
+        cal.close()
+        w8a8_scales = {site: float(np.float32(env[site][0]) / np.float32(127.0)) for site in W8A8_SCALED}
+        host = Host(ex, w8a8_realization(shapes, args.attention, args.launches, w8a8_scales)).prepare("llama", **consts)
+    else:
+        host = Host(ex, realization(shapes, w.get("int8", False), args.attention, args.launches)).prepare("llama", **consts)
+    for i, (path, (shape, std)) in enumerate(shapes.items()):
+        host.init_param(path, 1000 + i, std, shape)
+    ex.sync()
     stream = torch.cuda.ExternalStream(ex.stream(), device=torch.device("cuda", local))
 
     def barrier():
@@ -994,8 +1035,12 @@ def main():
             f.write("kernel | launch name | algorithmic bytes a launch\tlaunches\ttotal ms\tshare\tms/launch\tGB/s (algorithmic)\tTFLOP/s\n")
             for key, d in sorted(names.items(), key=lambda kv: -kv[1][1]):
                 f.write(f"{key}\t{d[0]}\t{d[1]:.3f}\t{d[1] / total_kernel_ms:.4f}\t{d[1] / d[0]:.4f}\t{d[3] / (d[1] * 1e-3) / 1e9:.1f}\t{d[2] / (d[1] * 1e-3) / 1e12:.1f}\n")
-    tc = by.get("k_gemm_tc", [0, 0.0, 0.0, 0.0])
+    roof_kernel = "k_gemm_i8" if w.get("int8") == "w8a8" else "k_gemm_tc"
+    tc = by.get(roof_kernel, [0, 0.0, 0.0, 0.0])
     achieved = tc[2] / (tc[1] * 1e-3) / 1e12 if tc[1] > 0 else 0.0
+    if roof_kernel == "k_gemm_i8":
+        # no 8-bit rate was measured on this pool: twice the measured bf16 rate, the nominal ratio of the two kinds
+        tf_peak, peak_kind = 2.0 * tf_peak, "2 x " + peak_kind + " (the 8-bit kind's nominal ratio to bf16; integer operations, not FLOP)"
     out = {
         "metric": "tokens/sec Llama-7B-shape prefill", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 storage, f32 accumulation", "data": "synthetic",
@@ -1003,7 +1048,7 @@ def main():
         "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": int(ids_np.nbytes + y_np.nbytes), "d2h_bytes_per_step": 8 if comm is not None else 4, "loss_gather": comm_kind},
         "gpu_launches": int(kernels_after - kernels_before),
         "clocks": clocks,
-        "roofline": {"bound": "tensor", "kernel": "k_gemm_tc", "achieved": achieved, "peak": tf_peak, "unit": "TFLOP/s", "frac": achieved / tf_peak, "traffic": GEMM_TRAFFIC.get(args.workload), "traffic_of": GEMM_TRAFFIC_OF if args.workload in GEMM_TRAFFIC else None, "peak_source": peak_kind,
+        "roofline": {"bound": "tensor", "kernel": roof_kernel, "achieved": achieved, "peak": tf_peak, "unit": "TFLOP/s", "frac": achieved / tf_peak, "traffic": GEMM_TRAFFIC.get(args.workload), "traffic_of": GEMM_TRAFFIC_OF if args.workload in GEMM_TRAFFIC else None, "peak_source": peak_kind,
                      "model_tflops": flops_per_token(consts, T) * B * T * args.steps / (ms * 1e-3) / 1e12, "hbm_peak_gbs": hbm_peak},
         "kernel_shares": shares_of(by),
         "loss": loss_all,
@@ -1031,7 +1076,7 @@ def parity_preflight(ex, consts, int8, attention="blockwise", launches="merged")
         import headline
         import oracle_lib
         os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
-        weights = "int8" if int8 is True else ("e4m3fn" if int8 == "e4m3fn" else "bf16")
+        weights = "int8" if int8 is True else (int8 if int8 in ("e4m3fn", "w8a8") else "bf16")
         r = headline.llama_width_parity(ex, oracle_lib.load(), B=1, T=256, weights=weights, consts={k: v for k, v in consts.items() if k != "L"}, order={"kind": "device", "attention": attention, "launches": launches})
         tol = headline.LOGITS_TOL * (2.0 if weights != "bf16" else 1.0) * r["logits_scale"]
         ok = r["finite"] and r["logits_max_err"] <= tol and abs(r["loss_gpu"] - r["loss_oracle"]) <= headline.LOSS_RTOL * abs(r["loss_oracle"])

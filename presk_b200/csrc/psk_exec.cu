@@ -75,6 +75,7 @@ struct psk_exec {
     bool softmax_attr_set = false;
     bool attn_attr_set = false;
     bool attn_step_attr_set = false;
+    bool lut_aff_attr_set = false;
     bool i8_attr_set = false;
     uint16_t *silu_table = nullptr; // silu of every bf16 code, computed once by the device's own exact function
 };
@@ -969,7 +970,8 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
     const bool device_order = l->order == PSK_ORDER_DEVICE;
     bool any_affine = l->out.affine != 0;
     for (int i = 0; i < l->n_inputs; ++i) any_affine = any_affine || l->in[i].affine != 0;
-    if (any_affine && l->op != PSK_OP_FUSED && l->op != PSK_OP_CONTRACT && l->op != PSK_OP_CONVERT && l->op != PSK_OP_CONTRACT_ADD)
+    const bool affine_norm = l->op == PSK_OP_RMSNORM && l->out.affine != 0 && !l->in[0].affine && !l->in[1].affine && !l->in[2].affine; // the merged norm writing a `scaled` site
+    if (any_affine && !affine_norm && l->op != PSK_OP_FUSED && l->op != PSK_OP_CONTRACT && l->op != PSK_OP_CONVERT && l->op != PSK_OP_CONTRACT_ADD)
         return fail(e, PSK_E7005, std::string(l->name ? l->name : "?") + ": values in an affine format are read and written by elementwise groups, contractions and conversions only");
     if (any_affine && l->op == PSK_OP_CONTRACT && !l->int_accum)
         return fail(e, PSK_E7005, std::string(l->name ? l->name : "?") + ": a contraction over affine values counts its sums in integers (product and accum i32) on this executor");
@@ -989,6 +991,37 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
     case PSK_OP_FUSED: {
         e->last_kernel = "k_fused";
         if (l->n_steps < 1 || l->n_steps > PSK_MAX_STEPS) { rc = fail(e, PSK_E7001, "fused: a group of no step or of too many"); break; }
+        // silu(g) · u into a `scaled` site (the down-projection's integer-sum operand): bf16 rows in, one-byte codes out,
+        // the silu from the table as for a bf16 result
+        if (l->out.affine && !l->in[0].affine && L.n_in == 2 && !l->in[1].affine && match_program(l) == EW_SILU_MUL && L.kdtype == PSK_BF16 && !L.guarded
+            && L.in[0].dtype == PSK_BF16 && L.in[1].dtype == PSK_BF16 && (L.out.dtype == PSK_I8 || L.out.dtype == PSK_U8) && L.n_outer >= 1 && L.n_outer <= 2
+            && L.dims[L.n_outer - 1] % 8 == 0 && L.total / 8 < 0xffffffffll && L.total >= (int64_t)e->sms * 4096 * 8) {
+            const int last = L.n_outer - 1;
+            bool rows_ok = L.in[0].stride[last] == 1 && L.in[1].stride[last] == 1 && L.out.stride[last] == 1 && aligned16(L.in[0].p) && aligned16(L.in[1].p) && ((uintptr_t)L.out.p % 8) == 0;
+            if (L.n_outer == 2) rows_ok = rows_ok && L.in[0].stride[0] % 8 == 0 && L.in[1].stride[0] % 8 == 0 && L.out.stride[0] % 8 == 0;
+            if (rows_ok) {
+                EwParams E;
+                memset(&E, 0, sizeof E);
+                for (int i = 0; i < 2; ++i) { E.in[i] = L.in[i].p; E.dt[i] = PSK_BF16; E.cs[i] = 1; E.rs[i] = L.n_outer == 2 ? L.in[i].stride[0] : 0; }
+                E.out = const_cast<void *>(L.out.p); E.odt = L.out.dtype; E.kdt = L.kdtype; E.ors = L.n_outer == 2 ? L.out.stride[0] : 0;
+                E.rows = L.n_outer == 2 ? (uint32_t)L.dims[0] : 1u; E.colv = (uint32_t)(L.dims[last] / 8); E.n_in = 2;
+                E.aff_kind = l->out.affine; E.aff_zero = l->out.affine_zero; E.aff_scale = l->out.affine_scale;
+                if (!e->silu_table) {
+                    CUDA_TRY(e, cudaMalloc(&e->silu_table, 65536 * sizeof(uint16_t)));
+                    k_table_silu<<<64, 1024, 0, e->stream>>>(e->silu_table);
+                    CUDA_TRY(e, cudaFuncSetAttribute(k_ew_lut<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536 * 2));
+                    CUDA_TRY(e, cudaFuncSetAttribute(k_ew_lut<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536 * 2));
+                }
+                if (!e->lut_aff_attr_set) {
+                    CUDA_TRY(e, cudaFuncSetAttribute(k_ew_lut<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536 * 2));
+                    e->lut_aff_attr_set = true;
+                }
+                k_ew_lut<true, true><<<e->sms, 1024, 65536 * 2, e->stream>>>(E, e->silu_table);
+                e->last_kernel = "k_ew_lut_affine";
+                e->kernels += 1;
+                break;
+            }
+        }
         bool vec = !any_affine && L.n_outer >= 1 && l->n_steps <= 12 && L.dims[L.n_outer - 1] % 8 == 0 && vec8_operand(L.out, L.dims, L.n_outer, true);
         for (int i = 0; vec && i < L.n_in; ++i) vec = vec8_operand(L.in[i], L.dims, L.n_outer, false);
         bool hot = vec && L.n_outer <= 3 && L.n_in <= 4 && l->n_steps <= 4 && L.total / 8 < 0xffffffffll;
@@ -1448,7 +1481,8 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
         if (no < 1 || L.n_inner != 0 || L.n_in != 3) { rc = fail(e, PSK_E7001, nm + ": x, eps and gamma over the axes of x"); break; }
         const int64_t n = L.dims[no - 1];
         // rows: every leading axis of x and of the result must walk whole rows one after the other
-        bool fits = device_order && l->dtype == PSK_BF16 && l->in[0].dtype == PSK_BF16 && l->in[2].dtype == PSK_BF16 && l->out.dtype == PSK_BF16
+        const bool aff_out = l->out.affine != 0; // the result as one-byte codes of an affine format
+        bool fits = device_order && l->dtype == PSK_BF16 && l->in[0].dtype == PSK_BF16 && l->in[2].dtype == PSK_BF16 && (aff_out ? (l->out.dtype == PSK_I8 || l->out.dtype == PSK_U8) : l->out.dtype == PSK_BF16)
             && l->iparam[0] == n && l->iparam[1] == PSK_BF16 && l->iparam[2] == PSK_F32 && l->iparam[3] == PSK_F32
             && n % 256 == 0 && (n / 256 == 1 || n / 256 == 2 || n / 256 == 4 || n / 256 == 8 || n / 256 == 16)
             && L.in[0].stride[no - 1] == 1 && L.out.stride[no - 1] == 1 && L.in[2].stride[no - 1] == 1
@@ -1465,7 +1499,17 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
         RmsParams R;
         R.x = (const uint16_t *)L.in[0].p; R.gamma = (const uint16_t *)L.in[2].p; R.eps = L.in[1].p; R.eps_dtype = L.in[1].dtype;
         R.out = (uint16_t *)const_cast<void *>(L.out.p); R.x_row = x_row; R.out_row = o_row; R.rows = rows; R.n = (int32_t)n;
+        R.aff_kind = l->out.affine; R.aff_zero = l->out.affine_zero; R.aff_scale = l->out.affine_scale;
         const int g = grid_for(e, rows * 32, 256, 8);
+        if (aff_out) {
+            switch (n / 256) {
+            case 1: k_rmsnorm_rows<1, true><<<g, 256, 0, e->stream>>>(R); break;
+            case 2: k_rmsnorm_rows<2, true><<<g, 256, 0, e->stream>>>(R); break;
+            case 4: k_rmsnorm_rows<4, true><<<g, 256, 0, e->stream>>>(R); break;
+            case 8: k_rmsnorm_rows<8, true><<<g, 256, 0, e->stream>>>(R); break;
+            default: k_rmsnorm_rows<16, true><<<g, 256, 0, e->stream>>>(R); break;
+            }
+        } else
         switch (n / 256) {
         case 1: k_rmsnorm_rows<1><<<g, 256, 0, e->stream>>>(R); break;
         case 2: k_rmsnorm_rows<2><<<g, 256, 0, e->stream>>>(R); break;

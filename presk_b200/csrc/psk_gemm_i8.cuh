@@ -145,13 +145,25 @@ PSK_DEV uint32_t count_to_bf16(int32_t n, double base)
 // binary32; n, basef and their product each carry at most 2^-24 of relative error, so f is within three of its own
 // units of n·base, and the two round to the same bf16 number unless f lies within three units of a midpoint (low
 // half 0x8000) or is subnormal. Those few go the exact way, with the base taken again from its two factors.
+// (The exact routine is kept out of line: inlined into each of the 32 unrolled elements of the epilogue it made the
+// loop some thousands of instructions long, and the warps waited on the instruction cache more than on anything.)
+static __device__ __noinline__ uint32_t count_to_bf16_exact(int32_t n, double sa, const float *scale_of_col)
+{
+    return round_count_to_float((int64_t)n, sa * (double)*scale_of_col, 7, 8);
+}
+
 PSK_DEV uint32_t count_to_bf16_quick(int32_t n, float basef, double sa, const float *scale_of_col)
 {
-    if (n == 0) return 0u;
     const float f = (float)n * basef;
     const uint32_t fb = __float_as_uint(f);
-    if ((((fb & 0xffffu) - 0x7ffcu) <= 8u) || !(fb & 0x7f800000u)) return round_count_to_float((int64_t)n, sa * (double)*scale_of_col, 7, 8);
+    // (a zero sum has a zero exponent field and goes the exact way, which answers +0)
+    if ((((fb & 0xffffu) - 0x7ffcu) <= 8u) || !(fb & 0x7f800000u)) return count_to_bf16_exact(n, sa, scale_of_col);
     return (fb + 0x7fffu + ((fb >> 16) & 1u)) >> 16;
+}
+
+static __device__ __noinline__ uint32_t count_to_f32_exact(int32_t n, double base)
+{
+    return round_count_to_float((int64_t)n, base, 23, 8);
 }
 
 PSK_DEV uint32_t count_to_f32(int32_t n, double base)
@@ -160,7 +172,7 @@ PSK_DEV uint32_t count_to_f32(int32_t n, double base)
     const uint64_t db = (uint64_t)__double_as_longlong(d);
     const uint32_t low = (uint32_t)(db & 0x1fffffffu); // the 29 bits binary32 drops from a normal number
     const double mag = fabs(d);
-    if (!(mag >= 1.1754943508222875e-38) || ((low - 0x0fffffffu) <= 2u)) return round_count_to_float((int64_t)n, base, 23, 8);
+    if (!(mag >= 1.1754943508222875e-38) || ((low - 0x0fffffffu) <= 2u)) return count_to_f32_exact(n, base);
     return __float_as_uint(__double2float_rn(d));
 }
 
@@ -339,6 +351,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_i8(const __grid_constant__ 
                         // instruction writes whole runs of a row (bf16: 64 bytes; f32: 128 bytes)
                         uint32_t packed[32];
                         const double base_l = sa * (double)scale_l;
+                        const bool whole = col + 32 <= P.n; // the group's 32 columns all exist
                         const float basef_l = __double2float_rn(base_l);
                         if (P.out_dtype == PSK_BF16) {
 #pragma unroll
@@ -346,7 +359,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_i8(const __grid_constant__ 
                                 const float bf = __shfl_sync(0xffffffffu, basef_l, i);
                                 const uint32_t corr = __shfl_sync(0xffffffffu, corr_l, i);
                                 const int32_t nsum = (int32_t)(v[i] - corr);
-                                packed[i] = col + i < P.n ? count_to_bf16_quick(nsum, bf, sa, cs_base + (col + i) * P.col_scale_stride) : 0u;
+                                packed[i] = (whole || col + i < P.n) ? count_to_bf16_quick(nsum, bf, sa, cs_base + (col + i) * P.col_scale_stride) : 0u;
                             }
                         } else {
 #pragma unroll
@@ -354,7 +367,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_i8(const __grid_constant__ 
                                 const double base = __shfl_sync(0xffffffffu, base_l, i);
                                 const uint32_t corr = __shfl_sync(0xffffffffu, corr_l, i);
                                 const int32_t nsum = (int32_t)(v[i] - corr);
-                                packed[i] = col + i < P.n ? count_to_f32(nsum, base) : 0u;
+                                packed[i] = (whole || col + i < P.n) ? count_to_f32(nsum, base) : 0u;
                             }
                         }
                         if (P.out_dtype == PSK_F32) {

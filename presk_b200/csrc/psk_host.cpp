@@ -1274,12 +1274,14 @@ struct psk_host {
         const std::string f = "RMSNorm.apply";
         if (rz.merged_launches && rz.order == PSK_ORDER_DEVICE && !calibrating && !x.affine) {
             bool plain = true;
-            for (auto site : {"/%2", "/%3", "/%5", "/%7", "/%10"}) plain = plain && !rz.scaled.count(f + site);
+            for (auto site : {"/%2", "/%3", "/%5", "/%7"}) plain = plain && !rz.scaled.count(f + site);
             if (plain) {
-                // the four launches below as one, when the executor takes it (PSK_OP_RMSNORM: their bits)
+                // the four launches below as one, when the executor takes it (PSK_OP_RMSNORM: their bits); the result's
+                // own site may be a `scaled` one (the operand of integer-sum projections): its codes are then what the
+                // last group's store writes
                 Tensor eps = scalar(f + "/%5", 1e-5);
                 const int d10 = site_dtype(f + "/%10");
-                Tensor out = fresh(x.axes, d10);
+                Tensor out = fresh_at(f + "/%10", x.axes);
                 psk_launch l;
                 memset(&l, 0, sizeof l);
                 l.op = PSK_OP_RMSNORM;
@@ -1510,7 +1512,7 @@ struct psk_host {
         Tensor wg = layer(param("blocks.ff.gate.w"), l), wu = layer(param("blocks.ff.up.w"), l), wd = layer(param("blocks.ff.down.w"), l);
         Tensor g = dot("Dense.apply/%3", x, wg);
         const int ds = rz.dtype_at("silu/%2"), dh = rz.dtype_at(f + "/%7");
-        if (rz.merged_launches && !calibrating && (ds == PSK_BF16 || ds == PSK_F32) && ds == dh && g.dtype == ds && !g.affine && !rz.scaled.count("silu/%2") && !rz.scaled.count(f + "/%7")) {
+        if (rz.merged_launches && !calibrating && (ds == PSK_BF16 || ds == PSK_F32) && ds == dh && g.dtype == ds && !g.affine && !rz.scaled.count("silu/%2")) {
             // silu's group and the product with `up` as one launch: silu's value is rounded to its site's type
             // inside the group (PSK_ROUND), so the product reads what the separate launch would have stored
             Tensor u = dot("Dense.apply/%3", x, wu);

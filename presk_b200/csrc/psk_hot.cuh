@@ -28,6 +28,8 @@ struct EwParams {
     int32_t n_in, guarded;
     psk_step steps[4];
     uint32_t *ovf, *status;
+    int32_t aff_kind, aff_zero; // k_ew_lut<.., AFF>: the result's affine format
+    float aff_scale;
 };
 
 // Eight consecutive stored elements widened to f32, or one broadcast to all eight.
@@ -425,8 +427,9 @@ __global__ void k_table_silu(uint16_t *table)
     if (c < 65536u) table[c] = f32_to_bf16(ew_eval<EW_SILU>(bf16_to_f32((uint16_t)c), 0.0f, 0.0f, 0.0f));
 }
 
-// out = T[in0] (MUL = false), or bf16(T[in0] * in1) (MUL = true: the group [.., round to bf16, mul s2,1])
-template <bool MUL>
+// out = T[in0] (MUL = false), or bf16(T[in0] * in1) (MUL = true: the group [.., round to bf16, mul s2,1]);
+// AFF: the product stored as one-byte codes of an affine format (E.aff_*), as the generic group's store does.
+template <bool MUL, bool AFF = false>
 __global__ void __launch_bounds__(1024, 1) k_ew_lut(const __grid_constant__ EwParams E, const uint16_t *__restrict__ table)
 {
     extern __shared__ uint16_t s_table[];
@@ -457,13 +460,21 @@ __global__ void __launch_bounds__(1024, 1) k_ew_lut(const __grid_constant__ EwPa
             const uint32_t w[4] = {a[u].x, a[u].y, a[u].z, a[u].w};
             const uint32_t v[4] = {b[u].x, b[u].y, b[u].z, b[u].w};
             uint32_t o[4];
+            uint32_t codes[2] = {0u, 0u};
+            const float aff_r = AFF ? __frcp_rn(E.aff_scale) : 0.0f;
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 const uint32_t lo = s_table[w[q] & 0xffffu], hi = s_table[w[q] >> 16];
-                if (MUL) o[q] = pack_bf16x2(__fmul_rn(bits_f32(lo << 16), bits_f32(v[q] << 16)), __fmul_rn(bits_f32(hi << 16), bits_f32(v[q] & 0xffff0000u)));
+                if (MUL && AFF) {
+                    const uint32_t c0 = (uint32_t)affine_code_quick(__fmul_rn(bits_f32(lo << 16), bits_f32(v[q] << 16)), E.aff_scale, aff_r, E.aff_kind, E.aff_zero) & 0xffu;
+                    const uint32_t c1 = (uint32_t)affine_code_quick(__fmul_rn(bits_f32(hi << 16), bits_f32(v[q] & 0xffff0000u)), E.aff_scale, aff_r, E.aff_kind, E.aff_zero) & 0xffu;
+                    codes[q >> 1] |= (c0 | (c1 << 8)) << ((q & 1) * 16);
+                }
+                else if (MUL) o[q] = pack_bf16x2(__fmul_rn(bits_f32(lo << 16), bits_f32(v[q] << 16)), __fmul_rn(bits_f32(hi << 16), bits_f32(v[q] & 0xffff0000u)));
                 else o[q] = lo | (hi << 16);
             }
-            *reinterpret_cast<uint4 *>((uint16_t *)E.out + oo[u]) = make_uint4(o[0], o[1], o[2], o[3]);
+            if (AFF) *reinterpret_cast<uint2 *>((uint8_t *)E.out + oo[u]) = make_uint2(codes[0], codes[1]);
+            else *reinterpret_cast<uint4 *>((uint16_t *)E.out + oo[u]) = make_uint4(o[0], o[1], o[2], o[3]);
         }
     }
 }
@@ -523,13 +534,17 @@ __global__ void __launch_bounds__(256, 4) k_rope_bf16(const __grid_constant__ Ro
 struct RmsParams {
     const uint16_t *x, *gamma;
     const void *eps;
-    uint16_t *out;
+    uint16_t *out;          // bf16 numbers, or (AFF) one-byte codes of an affine format
     int64_t x_row, out_row; // element strides from row to row
     int64_t rows;
     int32_t n, eps_dtype;
+    int32_t aff_kind, aff_zero; // AFF: 1 i8, 2 u8; the zero point
+    float aff_scale;
 };
 
-template <int NV>
+// AFF: the result's site is stored in an affine format (a `scaled` site feeding an integer-sum contraction): the
+// f32 value the last group computes goes straight into its code, as the generic group's store does.
+template <int NV, bool AFF = false>
 __global__ void __launch_bounds__(256, 4) k_rmsnorm_rows(const __grid_constant__ RmsParams P)
 {
     const int lane = threadIdx.x & 31;
@@ -566,6 +581,8 @@ __global__ void __launch_bounds__(256, 4) k_rmsnorm_rows(const __grid_constant__
         const float rr = __frcp_rn(root);
         const bool ok = div_by_in_range(root);
         uint16_t *orow = P.out + row * P.out_row + lane * 8;
+        uint8_t *crow = reinterpret_cast<uint8_t *>(P.out) + row * P.out_row + lane * 8;
+        const float aff_r = AFF ? __frcp_rn(P.aff_scale) : 0.0f;
         const uint16_t *gr = P.gamma + lane * 8;
 #pragma unroll 1
         for (int j0 = 0; j0 < NV; j0 += G) {
@@ -580,12 +597,21 @@ __global__ void __launch_bounds__(256, 4) k_rmsnorm_rows(const __grid_constant__
                 const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
                 const uint32_t gw[4] = {g[j].x, g[j].y, g[j].z, g[j].w};
                 uint32_t o[4];
+                uint32_t codes[2] = {0u, 0u};
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     const float lo = div_by_checked(bits_f32(w[q] << 16), root, rr, ok), hi = div_by_checked(bits_f32(w[q] & 0xffff0000u), root, rr, ok);
-                    o[q] = pack_bf16x2_hw(__fmul_rn(lo, bits_f32(gw[q] << 16)), __fmul_rn(hi, bits_f32(gw[q] & 0xffff0000u)));
+                    const float vlo = __fmul_rn(lo, bits_f32(gw[q] << 16)), vhi = __fmul_rn(hi, bits_f32(gw[q] & 0xffff0000u));
+                    if (AFF) {
+                        const uint32_t c0 = (uint32_t)affine_code_quick(vlo, P.aff_scale, aff_r, P.aff_kind, P.aff_zero) & 0xffu;
+                        const uint32_t c1 = (uint32_t)affine_code_quick(vhi, P.aff_scale, aff_r, P.aff_kind, P.aff_zero) & 0xffu;
+                        codes[q >> 1] |= (c0 | (c1 << 8)) << ((q & 1) * 16);
+                    } else {
+                        o[q] = pack_bf16x2_hw(vlo, vhi);
+                    }
                 }
-                *reinterpret_cast<uint4 *>(orow + (j0 + j) * 256) = make_uint4(o[0], o[1], o[2], o[3]);
+                if (AFF) *reinterpret_cast<uint2 *>(crow + (j0 + j) * 256) = make_uint2(codes[0], codes[1]);
+                else *reinterpret_cast<uint4 *>(orow + (j0 + j) * 256) = make_uint4(o[0], o[1], o[2], o[3]);
             }
         }
     }

@@ -135,6 +135,25 @@ PSK_DEV int64_t affine_code_of(double x, int kind, float scale, int zero)
     return affine_clamp(n + zero, kind);
 }
 
+// The same for a binary32 value in the kernels that store whole rows of codes, the quick way: with r = RN(1/s),
+// v = RN(x·r) is within 2^-23 of the quotient x/s relatively, so unless v lies within |v|·2^-21 of a tie the nearest
+// integer of v is that of the quotient; the few that do (and anything not a small finite number, which the clamp or
+// the NaN rule decides) go the exact way, kept out of line.
+static __device__ __noinline__ int affine_code_exact(float x, int kind, float scale, int zero)
+{
+    return (int)affine_code_of((double)x, kind, scale, zero);
+}
+
+PSK_DEV int affine_code_quick(float x, float scale, float rscale, int kind, int zero)
+{
+    const float v = __fmul_rn(x, rscale);
+    if (!(fabsf(v) < 1024.0f)) return affine_code_exact(x, kind, scale, zero);
+    const float r = rintf(v);
+    if (fabsf(fabsf(__fsub_rn(v, r)) - 0.5f) <= fabsf(v) * 4.76837158203125e-07f) return affine_code_exact(x, kind, scale, zero);
+    const int n = (int)r + zero;
+    return kind == 2 ? (n < 0 ? 0 : n > 255 ? 255 : n) : (n < -128 ? -128 : n > 127 ? 127 : n);
+}
+
 // The code of the IEEE format of t fraction and w exponent bits nearest sig·2^(exp - top), sig's leading
 // bit at position top: ties to even, overflow to the infinity's code.
 PSK_DEV uint32_t round_sig_to_format(uint64_t sig, int top, int exp, int t, int w)

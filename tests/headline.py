@@ -45,6 +45,32 @@ def realization(paths, order, weights="bf16"):
     return rz
 
 
+# W8A8: the activations that feed the projections stored as i8 codes with a static scale (`scaled` sites: the norm's
+# result and silu(gate)·up), every projection's weights and the head's as int8 (`quant`), and those contractions'
+# products and sums counted in i32 (`product`, `accum`), as examples/tests/formats/w8a8.json declares them for a Dense
+# layer. The attention's result stays bf16, so the out-projection reads it against int8 weights widened exactly.
+W8A8_SCALED_SITES = ("RMSNorm.apply/%10", "SwiGLU.apply/%7")
+W8A8_INT_SUMS = ("Attention.apply/%7", "Attention.apply/%11", "Attention.apply/%14", "Dense.apply/%3", "Llama.apply/%11")
+W8A8_QUANTISED = QUANTISED + ("head",)
+
+
+def w8a8_realization(paths, order, scales):
+    """`scales`: {site: scale} of W8A8_SCALED_SITES (from an envelope: largest magnitude / 127)."""
+    rz = {"default": "bf16", "order": order, "storage": dict(F32_SITES)}
+    rz["params"] = {p: "bf16" for p in paths if p not in W8A8_QUANTISED}
+    rz["quant"] = {p: {"bits": 8, "over": -2} for p in W8A8_QUANTISED}
+    rz["scaled"] = {site: {"int": "i8/sat", "scale": float(np.float32(scales[site])), "zero": 0} for site in W8A8_SCALED_SITES}
+    rz["product"] = {site: "i32" for site in W8A8_INT_SUMS}
+    rz["accum"] = {site: "i32" for site in W8A8_INT_SUMS}
+    return rz
+
+
+def w8a8_scales(envelope):
+    """A static scale a scaled site from a calibration's envelope {site: (max |x|, ...)}: absmax / 127, as `presk
+    scales` computes an absmax scheme's (presk-rt/src/lib.rs:287-360)."""
+    return {site: float(np.float32(envelope[site][0]) / np.float32(127.0)) for site in W8A8_SCALED_SITES}
+
+
 BENCH_ORDER = {"kind": "device", "attention": "blockwise", "launches": "merged"}
 ORACLE_ORDER = {"kind": "sequential"}
 
@@ -67,8 +93,18 @@ def llama_width_parity(cuda_executor, oracle, B=1, T=256, weights="bf16", consts
     y = rng.integers(0, c["V"], size=(B, T), dtype=np.int64)
     out = {"shape": f"llama L=1 V={c['V']} D={c['D']} H={c['H']} G={c['G']} FF={c['FF']} B={B} T={T}, weights {weights}"}
     res = {}
+    make = lambda how: realization(p, how, weights)
+    if weights == "w8a8":
+        # static scales from a calibration of the bf16 realization on the CUDA executor; both sides then run the same
+        # W8A8 realization
+        hc = give(Host(cuda_executor, realization(p, {"kind": "device"})).prepare("llama", **c), p)
+        hc.set_calibrating(True)
+        hc.call("apply", [ids], (B, T, c["V"]))
+        scales = w8a8_scales(hc.envelope())
+        hc.close()
+        make = lambda how: w8a8_realization(p, how, scales)
     for name, ex, how in (("gpu", cuda_executor, order or BENCH_ORDER), ("oracle", oracle.vtable(), ORACLE_ORDER)):
-        h = give(Host(ex, realization(p, how, weights)).prepare("llama", **c), p)
+        h = give(Host(ex, make(how)).prepare("llama", **c), p)
         if name == "gpu":
             h.set_logging(True)
         logits = h.call("apply", [ids], (B, T, c["V"]))

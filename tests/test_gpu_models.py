@@ -536,6 +536,49 @@ def test_step_after_prefill_on_the_gpu(cuda, oracle):
         assert np.abs(w_dev - w_want).max() <= 2.0**-5 * np.abs(w_want).max(), weights
 
 
+def test_w8a8_llama_on_the_integer_tensor_cores(cuda, oracle):
+    """The W8A8 realization of the Llama program (tests/headline.py): the norm and the silu group write i8 codes
+    with static scales (from a calibration on this executor), q, k, v, gate, up, down and the head are integer-sum
+    contractions on tcgen05's 8-bit kind, the out-projection reads bf16 against int8 weights. Sequential order: the
+    oracle's bits, the scalar integer kernel's among them. Device order: the merged launches (the norm and the silu
+    group writing their codes themselves) keep every bit of the unmerged list, and the logits stay within the bf16
+    tolerance of the sequential result (the integer sums are exact either way; what is reordered are the
+    out-projection's and the statistics' sums)."""
+    import headline
+    c = dict(V=512, D=256, H=2, G=2, FF=512, L=2)
+    p = models.llama_params(c)
+    ids = np.random.default_rng(14).integers(0, c["V"], size=(2, 128), dtype=np.int64)
+    h = models.give(Host(cuda, headline.realization(p, {"kind": "device"})).prepare("llama", **c), p)
+    h.set_calibrating(True)
+    h.call("apply", [ids], (2, 128, c["V"]))
+    scales = headline.w8a8_scales(h.envelope())
+    h.close()
+
+    def run(ex, order):
+        hw = models.give(Host(ex, headline.w8a8_realization(p, order, scales)).prepare("llama", **c), p)
+        hw.set_logging(True)
+        out = hw.call("apply", [ids], (2, 128, c["V"]))
+        log = hw.launch_log()
+        hw.close()
+        return out, log
+
+    want, _ = run(oracle.vtable(), {"kind": "sequential"})
+    got, _ = run(cuda, {"kind": "sequential"})
+    assert_same_bits(got, want)
+    cuda.set_profiling(True)
+    plain, plain_log = run(cuda, {"kind": "device"})
+    cuda.profile()
+    merged, merged_log = run(cuda, {"kind": "device", "attention": "online", "launches": "merged"})
+    prof = [rec[0] for rec in cuda.profile()]
+    cuda.set_profiling(False)
+    assert prof.count("k_gemm_i8") >= 6 * c["L"] + 1, prof
+    assert merged_log.count("rmsnorm[merged]") == 2 * c["L"] + 1 and len(merged_log) < len(plain_log)
+    unfused, _ = run(cuda, {"kind": "device", "launches": "merged"})  # the attention's four launches: merged launches alone keep every bit
+    assert_same_bits(unfused, plain)
+    assert np.abs(merged - want).max() <= 2.0**-5 * np.abs(want).max()
+    assert np.abs(plain - want).max() <= 2.0**-5 * np.abs(want).max()
+
+
 def test_gap_of_a_candidate_realization_measured_on_the_device(cuda):
     """What `presk solve --measure` does for every candidate (presk-driver/src/gap.rs): the same entry under the
     reference realization and under a candidate's, the largest difference of the results against budget x max |y|.

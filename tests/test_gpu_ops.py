@@ -482,6 +482,38 @@ def test_tabulated_silu_is_the_exact_one(cuda, oracle, with_mul):
     assert bad.size == 0, f"{bad.size} differ; first: code {g.ravel()[bad[0]]:#x}: {a[bad[0]]:#x} vs {b[bad[0]]:#x}"
 
 
+@pytest.mark.parametrize("kind,zero,scale", [(1, 0, 0.05), (2, 117, 0.0173), (1, -20, 3.0e-3)])
+def test_silu_times_up_into_an_affine_site(cuda, oracle, kind, zero, scale):
+    """The merged silu group writing a `scaled` site (the down-projection's integer-sum operand): bf16 rows in,
+    one-byte codes clamp(rne(x / s) + z) out. The kernel takes the quotient by a reciprocal and sends what lies near
+    a tie through the exact routine; every code of `gate` occurs, and `up` is laid out so that many products fall on
+    exact ties of the scale. The codes must be the oracle's, every one."""
+    rows, cols = 2560, 2048
+    rng = np.random.default_rng(kind * 100 + zero + 5)
+    g = rng.integers(0, 65536, size=(rows, cols), dtype=np.uint16)
+    g.ravel()[:65536] = np.arange(65536, dtype=np.uint16)
+    u = rng.standard_normal((rows, cols)) * 3.0
+    u[1::7] = 1.0   # silu(g) itself, a bf16 number: quotients by the scale of every kind, ties among them
+    u[2::7] = np.float32(scale) * 0.5
+    u = bf16_of(oracle, u)
+    l = launch_desc(abi.OP_FUSED, abi.BF16, [rows, cols], order=abi.ORDER_DEVICE)
+    l.n_inputs, l.n_steps = 2, 4
+    steps = [(abi.SIGMOID, 1, 0, 0, 0), (abi.MUL, 2, 0, -1, 0), (abi.ROUND, 1, -2, 0, abi.BF16), (abi.MUL, 2, -3, 1, 0)]
+    for k, (prim, nargs, a, b, imm) in enumerate(steps):
+        l.steps[k].prim, l.steps[k].nargs, l.steps[k].src[0], l.steps[k].src[1], l.steps[k].imm = prim, nargs, a, b, imm
+    set_operand(l.inputs[0], abi.BF16, [rows, cols], [0, 1])
+    set_operand(l.inputs[1], abi.BF16, [rows, cols], [0, 1])
+    set_operand(l.out, abi.I8 if kind == 1 else abi.U8, [rows, cols], [0, 1])
+    l.out.affine, l.out.affine_zero, l.out.affine_scale = kind, zero, scale
+    cuda.set_profiling(True)
+    got, want, _, _ = run_both(cuda, oracle, l, [g, u], rows * cols)
+    assert [rec[0] for rec in cuda.profile()] == ["k_ew_lut_affine"]
+    cuda.set_profiling(False)
+    bad = np.nonzero(got != want)[0]
+    assert bad.size == 0, f"{bad.size} differ; first: gate {g.ravel()[bad[0]]:#x}, up {u.ravel()[bad[0]]:#x}: {got[bad[0]]} vs {want[bad[0]]}"
+    assert len(np.unique(want)) > 100  # the codes spread over the format
+
+
 @pytest.mark.parametrize("with_mul", [False, True])
 def test_division_by_a_row_scalar_is_the_ieee_division(cuda, oracle, with_mul):
     """bf16 rows divided by one f32 value a row (a norm's root, rounded to bf16 at the kernel's edge), then

@@ -256,3 +256,30 @@ def test_step_after_prefill_is_the_whole_window_recomputed(oracle, rz):
         h.call("step", [ids[:, :1]], (3, 1, c["V"]))
     with pytest.raises(PreskError, match="no `prefill`"):
         ref.prepare("llama", TMAX=8, **c).call("step", [ids[:, :1]], (3, 1, c["V"]))
+
+
+def test_w8a8_llama_merged_launches_keep_every_bit(oracle):
+    """The W8A8 realization of the Llama program (tests/headline.py: i8 activations at the projections' inputs with
+    static scales from a calibration, int8 weights, i32 sums): under `launches: merged` the norm and the silu group
+    write their `scaled` sites themselves, and the logits are the bits of the reference's launch list."""
+    import headline
+    c = models.LLAMA_TINY
+    p = models.llama_params(c)
+    ids = np.random.default_rng(3).integers(0, c["V"], size=(2, 16), dtype=np.int64)
+    h = models.give(Host(oracle.vtable(), headline.realization(p, {"kind": "sequential"})).prepare("llama", **c), p)
+    h.set_calibrating(True)
+    h.call("apply", [ids], (2, 16, c["V"]))
+    scales = headline.w8a8_scales(h.envelope())
+    assert all(s > 0 for s in scales.values())
+    outs, logs = [], []
+    for order in ({"kind": "sequential"}, {"kind": "device"}, {"kind": "device", "launches": "merged"}):
+        hw = models.give(Host(oracle.vtable(), headline.w8a8_realization(p, order, scales)).prepare("llama", **c), p)
+        hw.set_logging(True)
+        outs.append(hw.call("apply", [ids], (2, 16, c["V"])))
+        logs.append(hw.launch_log())
+    assert np.isfinite(outs[0]).all() and np.abs(outs[0]).max() > 0
+    assert np.array_equal(outs[1].view(np.uint32), outs[2].view(np.uint32))
+    assert logs[2].count("rmsnorm[merged]") == 2 * c["L"] + 1 and len(logs[2]) < len(logs[1])
+    # against the bf16 realization: the quantisation's error, a few percent of the logits' scale
+    ref = models.give(Host(oracle.vtable(), headline.realization(p, {"kind": "sequential"})).prepare("llama", **c), p).call("apply", [ids], (2, 16, c["V"]))
+    assert np.abs(outs[0] - ref).max() <= 0.1 * np.abs(ref).max()
