@@ -718,6 +718,38 @@ int psk_oracle_run(const psk_launch *l, void *const *table, uint32_t *overflow)
     return psk_oracle_run_merged(l, table, overflow);
 }
 
+/* A counted sum n in the unit `base` (exact: the product of two binary32 scales), stored: rounded once into the
+ * output's float type, or into its affine format by the exact quotient (exec.rs:601-616). Returns the guard's test. */
+static uint32_t store_count(const psk_launch *l, uint8_t *outp, int64_t ooff, int64_t n, double base)
+{
+    if (l->out.affine) {
+        int64_t mb;
+        int eb;
+        take_apart(base, &mb, &eb);
+        int64_t nq = quotient_round_exact(n < 0, (u128)(n < 0 ? -n : n) * (u128)mb, eb, l->out.affine_scale);
+        int64_t q = nq + l->out.affine_zero;
+        q = q < affine_min(l->out.affine) ? affine_min(l->out.affine) : (q > affine_max(l->out.affine) ? affine_max(l->out.affine) : q);
+        if (l->out.affine == 2) ((uint8_t *)outp)[ooff] = (uint8_t)q;
+        else ((int8_t *)outp)[ooff] = (int8_t)q;
+        return 0;
+    }
+    switch (l->out.dtype) {
+    case PSK_F32: ((uint32_t *)outp)[ooff] = round_count_to_float(n, base, 23, 8); return 0;
+    case PSK_BF16: ((uint16_t *)outp)[ooff] = (uint16_t)round_count_to_float(n, base, 7, 8); return 0;
+    case PSK_F16: {
+        uint32_t c = round_count_to_float(n, base, 10, 5);
+        ((uint16_t *)outp)[ooff] = (uint16_t)c;
+        return (c & 0x7fffu) == 0x7c00u; /* a count is finite: an infinity here is an overflow */
+    }
+    default: { /* PSK_E8M15 */
+        uint32_t c = round_count_to_float(n, base, 15, 8);
+        uint8_t *q = outp + 3 * ooff;
+        q[0] = (uint8_t)c; q[1] = (uint8_t)(c >> 8); q[2] = (uint8_t)(c >> 16);
+        return (c & 0x7fffffu) == 0x7f8000u;
+    }
+    }
+}
+
 static int psk_oracle_run_merged(const psk_launch *l, void *const *table, uint32_t *overflow)
 {
     const int no = l->n_outer, ni = l->n_inner, kd = l->dtype;
@@ -758,6 +790,40 @@ static int psk_oracle_run_merged(const psk_launch *l, void *const *table, uint32
         if (l->int_accum) { /* exec.rs:493-526: counts in the scales' unit, i32 that wraps; :601-616 the store */
             if (l->n_inputs != 2) return PSK_E7005;
             for (int i = 0; i < 2; ++i) if (!l->in[i].affine && l->in[i].dtype != PSK_I8) return PSK_E7005;
+            if (!l->out.affine && l->out.dtype != PSK_F32 && l->out.dtype != PSK_BF16 && l->out.dtype != PSK_F16 && l->out.dtype != PSK_E8M15) return PSK_E7005;
+            /* The same sums by blocks of JB neighbouring results of one row, when the last output axis is carried
+             * by the integer weights alone, contiguously, with one scale a column (a projection's layout):
+             * sums that wrap in 32 bits do not depend on the order, so this is the loop below, only faster (the
+             * parity checks at a model's full width need it). */
+            if (ni == 1 && no >= 1 && inner > 0 && l->in[0].affine && !l->in[1].affine && in[1].scales && l->in[0].stride[no - 1] == 0 && l->in[1].stride[no - 1] == 1
+                && l->in[1].scale_stride[no] == 0) {
+                enum { JB = 64 };
+                const int64_t K = inner, N = l->dims[no - 1], rows = total / N;
+                const int64_t s0 = l->in[0].stride[no], s1 = l->in[1].stride[no], sj = l->in[1].scale_stride[no - 1], os = l->out.stride[no - 1];
+                const int zero0 = l->in[0].affine_zero, kind0 = l->in[0].affine;
+                const double unit0 = (double)l->in[0].affine_scale;
+#pragma omp parallel for schedule(dynamic, 1) reduction(| : ovf_all)
+                for (int64_t row = 0; row < rows; ++row) {
+                    const int64_t lin0 = row * N;
+                    const int64_t b0 = offset_of(l->in[0].stride, l->dims, 0, no, lin0), b1 = offset_of(l->in[1].stride, l->dims, 0, no, lin0);
+                    const int64_t q1 = offset_of(l->in[1].scale_stride, l->dims, 0, no, lin0), o0 = offset_of(l->out.stride, l->dims, 0, no, lin0);
+                    for (int64_t j0 = 0; j0 < N; j0 += JB) {
+                        const int nj = (int)(N - j0 < JB ? N - j0 : JB);
+                        uint32_t acc[JB];
+                        for (int j = 0; j < nj; ++j) acc[j] = 0;
+                        for (int64_t c = 0; c < K; ++c) {
+                            const int64_t off = b0 + c * s0;
+                            const int32_t a = (kind0 == 2 ? (int)((const uint8_t *)in[0].p)[off] : (int)((const int8_t *)in[0].p)[off]) - zero0;
+                            const int8_t *w = (const int8_t *)in[1].p + b1 + c * s1 + j0;
+                            for (int j = 0; j < nj; ++j) acc[j] += (uint32_t)(a * (int32_t)w[j]); /* the product fits; the sum wraps */
+                        }
+                        for (int j = 0; j < nj; ++j)
+                            ovf_all |= store_count(l, outp, o0 + (j0 + j) * os, (int64_t)(int32_t)acc[j], unit0 * (double)in[1].scales[q1 + (j0 + j) * sj]);
+                    }
+                }
+                break;
+            }
+#pragma omp parallel for schedule(static) reduction(| : ovf_all)
             for (int64_t lin = 0; lin < total; ++lin) {
                 int64_t b0 = offset_of(l->in[0].stride, l->dims, 0, no, lin), b1 = offset_of(l->in[1].stride, l->dims, 0, no, lin);
                 int64_t q0 = offset_of(l->in[0].scale_stride, l->dims, 0, no, lin), q1 = offset_of(l->in[1].scale_stride, l->dims, 0, no, lin);
@@ -770,38 +836,8 @@ static int psk_oracle_run_merged(const psk_launch *l, void *const *table, uint32
                     acc += (uint32_t)(a * b); /* the product fits; the sum wraps */
                 }
                 if (inner == 0) { load_count(&in[0], b0, q0, &u0); load_count(&in[1], b1, q1, &u1); }
-                int64_t n = (int32_t)acc;
-                double base = u0 * u1; /* exact: two 24-bit significands */
-                int64_t ooff = offset_of(l->out.stride, l->dims, 0, no, lin);
-                if (l->out.affine) {
-                    int64_t mb;
-                    int eb;
-                    take_apart(base, &mb, &eb);
-                    int64_t nq = quotient_round_exact(n < 0, (u128)(n < 0 ? -n : n) * (u128)mb, eb, l->out.affine_scale);
-                    int64_t q = nq + l->out.affine_zero;
-                    q = q < affine_min(l->out.affine) ? affine_min(l->out.affine) : (q > affine_max(l->out.affine) ? affine_max(l->out.affine) : q);
-                    if (l->out.affine == 2) ((uint8_t *)outp)[ooff] = (uint8_t)q;
-                    else ((int8_t *)outp)[ooff] = (int8_t)q;
-                } else {
-                    switch (l->out.dtype) {
-                    case PSK_F32: ((uint32_t *)outp)[ooff] = round_count_to_float(n, base, 23, 8); break;
-                    case PSK_BF16: ((uint16_t *)outp)[ooff] = (uint16_t)round_count_to_float(n, base, 7, 8); break;
-                    case PSK_F16: {
-                        uint32_t c = round_count_to_float(n, base, 10, 5);
-                        ((uint16_t *)outp)[ooff] = (uint16_t)c;
-                        if ((c & 0x7fffu) == 0x7c00u) ovf_all |= 1; /* a count is finite: an infinity here is an overflow */
-                        break;
-                    }
-                    case PSK_E8M15: {
-                        uint32_t c = round_count_to_float(n, base, 15, 8);
-                        uint8_t *q = outp + 3 * ooff;
-                        q[0] = (uint8_t)c; q[1] = (uint8_t)(c >> 8); q[2] = (uint8_t)(c >> 16);
-                        if ((c & 0x7fffffu) == 0x7f8000u) ovf_all |= 1;
-                        break;
-                    }
-                    default: return PSK_E7005;
-                    }
-                }
+                /* the base is exact: two 24-bit significands */
+                ovf_all |= store_count(l, outp, offset_of(l->out.stride, l->dims, 0, no, lin), (int64_t)(int32_t)acc, u0 * u1);
             }
             break;
         } /* lower.rs:465-474, 586-636: acc = acc + (x·w), the terms in lexicographic order */

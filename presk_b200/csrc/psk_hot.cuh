@@ -438,6 +438,7 @@ __global__ void __launch_bounds__(1024, 1) k_ew_lut(const __grid_constant__ EwPa
     __syncthreads();
     const uint32_t total = E.rows * E.colv;
     const uint32_t stride = gridDim.x * blockDim.x;
+    const AffineQuick aq = affine_quick_of(AFF ? E.aff_scale : 1.0f, E.aff_kind, E.aff_zero);
     constexpr int UNR = 2;
     for (uint32_t idx0 = blockIdx.x * blockDim.x + threadIdx.x; idx0 < total; idx0 += stride * UNR) {
         uint4 a[UNR], b[UNR];
@@ -461,13 +462,12 @@ __global__ void __launch_bounds__(1024, 1) k_ew_lut(const __grid_constant__ EwPa
             const uint32_t v[4] = {b[u].x, b[u].y, b[u].z, b[u].w};
             uint32_t o[4];
             uint32_t codes[2] = {0u, 0u};
-            const float aff_r = AFF ? __frcp_rn(E.aff_scale) : 0.0f;
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 const uint32_t lo = s_table[w[q] & 0xffffu], hi = s_table[w[q] >> 16];
                 if (MUL && AFF) {
-                    const uint32_t c0 = (uint32_t)affine_code_quick(__fmul_rn(bits_f32(lo << 16), bits_f32(v[q] << 16)), E.aff_scale, aff_r, E.aff_kind, E.aff_zero) & 0xffu;
-                    const uint32_t c1 = (uint32_t)affine_code_quick(__fmul_rn(bits_f32(hi << 16), bits_f32(v[q] & 0xffff0000u)), E.aff_scale, aff_r, E.aff_kind, E.aff_zero) & 0xffu;
+                    const uint32_t c0 = (uint32_t)affine_code_quick(__fmul_rn(bits_f32(lo << 16), bits_f32(v[q] << 16)), aq) & 0xffu;
+                    const uint32_t c1 = (uint32_t)affine_code_quick(__fmul_rn(bits_f32(hi << 16), bits_f32(v[q] & 0xffff0000u)), aq) & 0xffu;
                     codes[q >> 1] |= (c0 | (c1 << 8)) << ((q & 1) * 16);
                 }
                 else if (MUL) o[q] = pack_bf16x2(__fmul_rn(bits_f32(lo << 16), bits_f32(v[q] << 16)), __fmul_rn(bits_f32(hi << 16), bits_f32(v[q] & 0xffff0000u)));
@@ -582,7 +582,7 @@ __global__ void __launch_bounds__(256, 4) k_rmsnorm_rows(const __grid_constant__
         const bool ok = div_by_in_range(root);
         uint16_t *orow = P.out + row * P.out_row + lane * 8;
         uint8_t *crow = reinterpret_cast<uint8_t *>(P.out) + row * P.out_row + lane * 8;
-        const float aff_r = AFF ? __frcp_rn(P.aff_scale) : 0.0f;
+        const AffineQuick aq = affine_quick_of(AFF ? P.aff_scale : 1.0f, P.aff_kind, P.aff_zero);
         const uint16_t *gr = P.gamma + lane * 8;
 #pragma unroll 1
         for (int j0 = 0; j0 < NV; j0 += G) {
@@ -603,8 +603,8 @@ __global__ void __launch_bounds__(256, 4) k_rmsnorm_rows(const __grid_constant__
                     const float lo = div_by_checked(bits_f32(w[q] << 16), root, rr, ok), hi = div_by_checked(bits_f32(w[q] & 0xffff0000u), root, rr, ok);
                     const float vlo = __fmul_rn(lo, bits_f32(gw[q] << 16)), vhi = __fmul_rn(hi, bits_f32(gw[q] & 0xffff0000u));
                     if (AFF) {
-                        const uint32_t c0 = (uint32_t)affine_code_quick(vlo, P.aff_scale, aff_r, P.aff_kind, P.aff_zero) & 0xffu;
-                        const uint32_t c1 = (uint32_t)affine_code_quick(vhi, P.aff_scale, aff_r, P.aff_kind, P.aff_zero) & 0xffu;
+                        const uint32_t c0 = (uint32_t)affine_code_quick(vlo, aq) & 0xffu;
+                        const uint32_t c1 = (uint32_t)affine_code_quick(vhi, aq) & 0xffu;
                         codes[q >> 1] |= (c0 | (c1 << 8)) << ((q & 1) * 16);
                     } else {
                         o[q] = pack_bf16x2_hw(vlo, vhi);

@@ -135,23 +135,43 @@ PSK_DEV int64_t affine_code_of(double x, int kind, float scale, int zero)
     return affine_clamp(n + zero, kind);
 }
 
-// The same for a binary32 value in the kernels that store whole rows of codes, the quick way: with r = RN(1/s),
-// v = RN(x·r) is within 2^-23 of the quotient x/s relatively, so unless v lies within |v|·2^-21 of a tie the nearest
-// integer of v is that of the quotient; the few that do (and anything not a small finite number, which the clamp or
-// the NaN rule decides) go the exact way, kept out of line.
+// The same for a binary32 value in the kernels that store whole rows of codes, the quick way. With r = RN(1/s),
+// v = RN(x·r) is within 2^-23 of the quotient x/s relatively. Codes saturate, so v is first clamped to ±vmax, two
+// past the furthest code from the zero point (a quotient beyond it saturates whatever its fraction); then
+// v + 1.5·2^23 rounds v to the nearest integer, ties to even, and holds that integer in its low bits. Unless v lies
+// within vmax·2^-22 of a tie, that is the quotient's own nearest integer; the few that do, and NaNs (whose code is
+// the zero point), go the exact way, kept out of line.
 static __device__ __noinline__ int affine_code_exact(float x, int kind, float scale, int zero)
 {
     return (int)affine_code_of((double)x, kind, scale, zero);
 }
 
-PSK_DEV int affine_code_quick(float x, float scale, float rscale, int kind, int zero)
+struct AffineQuick {
+    float scale, rscale, vmax, tol;
+    int kind, zero, bias, lo, hi;
+};
+
+PSK_DEV AffineQuick affine_quick_of(float scale, int kind, int zero)
 {
-    const float v = __fmul_rn(x, rscale);
-    if (!(fabsf(v) < 1024.0f)) return affine_code_exact(x, kind, scale, zero);
-    const float r = rintf(v);
-    if (fabsf(fabsf(__fsub_rn(v, r)) - 0.5f) <= fabsf(v) * 4.76837158203125e-07f) return affine_code_exact(x, kind, scale, zero);
-    const int n = (int)r + zero;
-    return kind == 2 ? (n < 0 ? 0 : n > 255 ? 255 : n) : (n < -128 ? -128 : n > 127 ? 127 : n);
+    AffineQuick q;
+    q.scale = scale; q.rscale = __frcp_rn(scale); q.kind = kind; q.zero = zero;
+    q.lo = kind == 2 ? 0 : -128; q.hi = kind == 2 ? 255 : 127;
+    const int far = (q.hi - zero) > (zero - q.lo) ? (q.hi - zero) : (zero - q.lo);
+    q.vmax = (float)(far + 2);
+    q.tol = q.vmax * 2.384185791015625e-07f; // 2^-22
+    q.bias = zero - 0x4B400000;
+    return q;
+}
+
+PSK_DEV int affine_code_quick(float x, const AffineQuick &q)
+{
+    const float v = __fmul_rn(x, q.rscale);
+    const float vc = fminf(fmaxf(v, -q.vmax), q.vmax);
+    const float t = __fadd_rn(vc, 12582912.0f);
+    const float d = __fsub_rn(vc, __fsub_rn(t, 12582912.0f)); // exact
+    if (x != x || fabsf(fabsf(d) - 0.5f) <= q.tol) return affine_code_exact(x, q.kind, q.scale, q.zero);
+    const int n = __float_as_int(t) + q.bias;
+    return n < q.lo ? q.lo : (n > q.hi ? q.hi : n);
 }
 
 // The code of the IEEE format of t fraction and w exponent bits nearest sig·2^(exp - top), sig's leading
