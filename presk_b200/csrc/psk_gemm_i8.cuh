@@ -70,6 +70,7 @@ struct Params {
     const int32_t *colsum;    // sum_k w[k, col] per (batch entry, column), when a_zero != 0
     int guarded;
     int vec_ok;
+    int probe;                // measurements only (PSK_I8_PROBE): 1 leaves the rescale out, 2 the stores, 4 the shuffles
     uint32_t *ovf;
     uint32_t *status;
 };
@@ -353,11 +354,14 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_i8(const __grid_constant__ 
                         const double base_l = sa * (double)scale_l;
                         const bool whole = col + 32 <= P.n; // the group's 32 columns all exist
                         const float basef_l = __double2float_rn(base_l);
-                        if (P.out_dtype == PSK_BF16) {
+                        if (P.probe & 1) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) packed[i] = v[i] & 0xffffu;
+                        } else if (P.out_dtype == PSK_BF16) {
 #pragma unroll
                             for (int i = 0; i < 32; ++i) {
-                                const float bf = __shfl_sync(0xffffffffu, basef_l, i);
-                                const uint32_t corr = __shfl_sync(0xffffffffu, corr_l, i);
+                                const float bf = (P.probe & 4) ? basef_l : __shfl_sync(0xffffffffu, basef_l, i);
+                                const uint32_t corr = (P.probe & 4) ? 0u : __shfl_sync(0xffffffffu, corr_l, i);
                                 const int32_t nsum = (int32_t)(v[i] - corr);
                                 packed[i] = (whole || col + i < P.n) ? count_to_bf16_quick(nsum, bf, sa, cs_base + (col + i) * P.col_scale_stride) : 0u;
                             }
@@ -389,7 +393,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_i8(const __grid_constant__ 
                         for (int it = 0; it < units; ++it) {
                             const int rr = it * rows_a_pass + lane / units;
                             const int64_t rrow = row0 + rr;
-                            if (rrow < P.m && unit < live) {
+                            if (rrow < P.m && unit < live && !(P.probe & 2)) {
                                 const uint32_t rq = (uint32_t)rrow / rcnt;
                                 const int64_t off = boff + (int64_t)rq * P.c_row_hi + (int64_t)((uint32_t)rrow - rq * rcnt) * P.c_row_lo + col_off;
                                 const uint4 w = stage_out[rr * 8 + (unit ^ (rr & 7))];
