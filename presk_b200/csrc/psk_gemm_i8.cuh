@@ -37,6 +37,7 @@ constexpr int BM = 128, BN = 256, BKB = 128; // BKB: bytes = elements of the sum
 constexpr int B_BYTES = BN * BKB;
 constexpr int BAR_BYTES = 256;
 constexpr int STAGE_OUT = 8 * 32 * 128;
+constexpr int SCALE_BYTES = 8 * 32 * 4; // a warp's 32 column scales, read back by every lane
 constexpr int THREADS = 320;
 // Two forms, as for the bf16 kernel. MT = 2: tiles of 256 rows, two accumulators sharing B's tile (a third less
 // traffic from the L2 a product, three stages of 64 KB), the accumulators fill tensor memory and the rescale runs
@@ -47,7 +48,7 @@ struct Cfg {
     static constexpr int STAGES = MT == 2 ? 3 : 4;
     static constexpr int A_BYTES = MT * BM * BKB;
     static constexpr int TILE_BYTES = STAGES * (A_BYTES + B_BYTES);
-    static constexpr int SMEM_TOTAL = TILE_BYTES + BAR_BYTES + STAGE_OUT + 1024;
+    static constexpr int SMEM_TOTAL = TILE_BYTES + BAR_BYTES + STAGE_OUT + SCALE_BYTES + 1024;
 };
 
 struct Params {
@@ -306,6 +307,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_i8(const __grid_constant__ 
         bool ok = true;
         const int half_id = (warp - 2) >> 2;
         uint4 *stage_out = reinterpret_cast<uint4 *>(smem + TILE_BYTES + BAR_BYTES) + (warp - 2) * 32 * 8;
+        float *scale_area = reinterpret_cast<float *>(smem + TILE_BYTES + BAR_BYTES + STAGE_OUT);
         const bool staged = P.vec_ok && !P.out_affine && (P.out_dtype == PSK_BF16 || P.out_dtype == PSK_F32);
         const double sa = (double)P.a_scale;
         for (int64_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
@@ -354,25 +356,57 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_i8(const __grid_constant__ 
                         const double base_l = sa * (double)scale_l;
                         const bool whole = col + 32 <= P.n; // the group's 32 columns all exist
                         const float basef_l = __double2float_rn(base_l);
+                        // The zero point's correction first (a shuffle a column, only when there is one), then the
+                        // rescale in two phases: every element's quick result and whether it is certain, with no
+                        // branch in between, so that the 32 independent chains overlap (with a test and a call after
+                        // each element the warps ran them one after the other, and the rescale cost more than the
+                        // tile's products); then, for the few that are not certain, the exact routine.
+                        if (sum_base) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) v[i] -= __shfl_sync(0xffffffffu, corr_l, i);
+                        }
+                        float *wscale = scale_area + (warp - 2) * 32; // this warp's 32 columns: bases (bf16 result) or scales (f32)
+                        __syncwarp();
+                        wscale[lane] = P.out_dtype == PSK_BF16 ? basef_l : scale_l;
+                        __syncwarp();
+                        const uint32_t live_mask = whole ? 0xffffffffu : ((1u << (uint32_t)(P.n - col)) - 1u);
+                        uint32_t unsure = 0;
                         if (P.probe & 1) {
 #pragma unroll
                             for (int i = 0; i < 32; ++i) packed[i] = v[i] & 0xffffu;
                         } else if (P.out_dtype == PSK_BF16) {
 #pragma unroll
                             for (int i = 0; i < 32; ++i) {
-                                const float bf = (P.probe & 4) ? basef_l : __shfl_sync(0xffffffffu, basef_l, i);
-                                const uint32_t corr = (P.probe & 4) ? 0u : __shfl_sync(0xffffffffu, corr_l, i);
-                                const int32_t nsum = (int32_t)(v[i] - corr);
-                                packed[i] = (whole || col + i < P.n) ? count_to_bf16_quick(nsum, bf, sa, cs_base + (col + i) * P.col_scale_stride) : 0u;
+                                const uint32_t fb = __float_as_uint((float)(int32_t)v[i] * wscale[i]);
+                                // within three binary32 units of a midpoint between bf16 numbers, or subnormal or zero
+                                // (a sum of zero is +0 whatever the scale: rows past the operand's end are all zeros)
+                                unsure |= ((((fb & 0xffffu) - 0x7ffcu) <= 8u || !(fb & 0x7f800000u)) && v[i] != 0u) ? (1u << i) : 0u;
+                                packed[i] = v[i] != 0u ? (fb + 0x7fffu + ((fb >> 16) & 1u)) >> 16 : 0u;
+                            }
+                            unsure &= live_mask;
+                            if (unsure) {
+#pragma unroll
+                                for (int i = 0; i < 32; ++i)
+                                    if ((unsure >> i) & 1u) packed[i] = count_to_bf16_exact((int32_t)v[i], sa, cs_base + (col + i) * P.col_scale_stride);
                             }
                         } else {
 #pragma unroll
                             for (int i = 0; i < 32; ++i) {
-                                const double base = __shfl_sync(0xffffffffu, base_l, i);
-                                const uint32_t corr = __shfl_sync(0xffffffffu, corr_l, i);
-                                const int32_t nsum = (int32_t)(v[i] - corr);
-                                packed[i] = (whole || col + i < P.n) ? count_to_f32(nsum, base) : 0u;
+                                const double d = (double)(int32_t)v[i] * (sa * (double)wscale[i]);
+                                const uint32_t low = (uint32_t)((uint64_t)__double_as_longlong(d) & 0x1fffffffu); // the 29 bits binary32 drops from a normal number
+                                unsure |= ((!(fabs(d) >= 1.1754943508222875e-38) || (low - 0x0fffffffu) <= 2u) && v[i] != 0u) ? (1u << i) : 0u;
+                                packed[i] = v[i] != 0u ? __float_as_uint(__double2float_rn(d)) : 0u;
                             }
+                            unsure &= live_mask;
+                            if (unsure) {
+#pragma unroll
+                                for (int i = 0; i < 32; ++i)
+                                    if ((unsure >> i) & 1u) packed[i] = count_to_f32_exact((int32_t)v[i], sa * (double)wscale[i]);
+                            }
+                        }
+                        if (!whole) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) packed[i] = ((live_mask >> i) & 1u) ? packed[i] : 0u;
                         }
                         if (P.out_dtype == PSK_F32) {
 #pragma unroll

@@ -461,20 +461,38 @@ __global__ void __launch_bounds__(1024, 1) k_ew_lut(const __grid_constant__ EwPa
             const uint32_t w[4] = {a[u].x, a[u].y, a[u].z, a[u].w};
             const uint32_t v[4] = {b[u].x, b[u].y, b[u].z, b[u].w};
             uint32_t o[4];
-            uint32_t codes[2] = {0u, 0u};
+            float val[8];
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 const uint32_t lo = s_table[w[q] & 0xffffu], hi = s_table[w[q] >> 16];
                 if (MUL && AFF) {
-                    const uint32_t c0 = (uint32_t)affine_code_quick(__fmul_rn(bits_f32(lo << 16), bits_f32(v[q] << 16)), aq) & 0xffu;
-                    const uint32_t c1 = (uint32_t)affine_code_quick(__fmul_rn(bits_f32(hi << 16), bits_f32(v[q] & 0xffff0000u)), aq) & 0xffu;
-                    codes[q >> 1] |= (c0 | (c1 << 8)) << ((q & 1) * 16);
+                    val[2 * q] = __fmul_rn(bits_f32(lo << 16), bits_f32(v[q] << 16));
+                    val[2 * q + 1] = __fmul_rn(bits_f32(hi << 16), bits_f32(v[q] & 0xffff0000u));
                 }
                 else if (MUL) o[q] = pack_bf16x2(__fmul_rn(bits_f32(lo << 16), bits_f32(v[q] << 16)), __fmul_rn(bits_f32(hi << 16), bits_f32(v[q] & 0xffff0000u)));
                 else o[q] = lo | (hi << 16);
             }
-            if (AFF) *reinterpret_cast<uint2 *>((uint8_t *)E.out + oo[u]) = make_uint2(codes[0], codes[1]);
-            else *reinterpret_cast<uint4 *>((uint16_t *)E.out + oo[u]) = make_uint4(o[0], o[1], o[2], o[3]);
+            if (MUL && AFF) {
+                int code[8];
+                uint32_t unsure = 0;
+#pragma unroll
+                for (int t = 0; t < 8; ++t) {
+                    bool un;
+                    code[t] = affine_code_try(val[t], aq, un);
+                    unsure |= un ? (1u << t) : 0u;
+                }
+                if (unsure) {
+#pragma unroll
+                    for (int t = 0; t < 8; ++t)
+                        if ((unsure >> t) & 1u) code[t] = affine_code_exact(val[t], aq.kind, aq.scale, aq.zero);
+                }
+                uint32_t lo4 = 0, hi4 = 0;
+#pragma unroll
+                for (int t = 0; t < 4; ++t) { lo4 |= ((uint32_t)code[t] & 0xffu) << (8 * t); hi4 |= ((uint32_t)code[4 + t] & 0xffu) << (8 * t); }
+                *reinterpret_cast<uint2 *>((uint8_t *)E.out + oo[u]) = make_uint2(lo4, hi4);
+            } else {
+                *reinterpret_cast<uint4 *>((uint16_t *)E.out + oo[u]) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
         }
     }
 }
@@ -597,21 +615,36 @@ __global__ void __launch_bounds__(256, 4) k_rmsnorm_rows(const __grid_constant__
                 const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
                 const uint32_t gw[4] = {g[j].x, g[j].y, g[j].z, g[j].w};
                 uint32_t o[4];
-                uint32_t codes[2] = {0u, 0u};
+                float val[8];
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     const float lo = div_by_checked(bits_f32(w[q] << 16), root, rr, ok), hi = div_by_checked(bits_f32(w[q] & 0xffff0000u), root, rr, ok);
-                    const float vlo = __fmul_rn(lo, bits_f32(gw[q] << 16)), vhi = __fmul_rn(hi, bits_f32(gw[q] & 0xffff0000u));
-                    if (AFF) {
-                        const uint32_t c0 = (uint32_t)affine_code_quick(vlo, aq) & 0xffu;
-                        const uint32_t c1 = (uint32_t)affine_code_quick(vhi, aq) & 0xffu;
-                        codes[q >> 1] |= (c0 | (c1 << 8)) << ((q & 1) * 16);
-                    } else {
-                        o[q] = pack_bf16x2_hw(vlo, vhi);
-                    }
+                    val[2 * q] = __fmul_rn(lo, bits_f32(gw[q] << 16));
+                    val[2 * q + 1] = __fmul_rn(hi, bits_f32(gw[q] & 0xffff0000u));
+                    if (!AFF) o[q] = pack_bf16x2_hw(val[2 * q], val[2 * q + 1]);
                 }
-                if (AFF) *reinterpret_cast<uint2 *>(crow + (j0 + j) * 256) = make_uint2(codes[0], codes[1]);
-                else *reinterpret_cast<uint4 *>(orow + (j0 + j) * 256) = make_uint4(o[0], o[1], o[2], o[3]);
+                if (AFF) {
+                    // the eight codes without a branch, then the uncertain ones (rare) the exact way
+                    int code[8];
+                    uint32_t unsure = 0;
+#pragma unroll
+                    for (int t = 0; t < 8; ++t) {
+                        bool u;
+                        code[t] = affine_code_try(val[t], aq, u);
+                        unsure |= u ? (1u << t) : 0u;
+                    }
+                    if (unsure) {
+#pragma unroll
+                        for (int t = 0; t < 8; ++t)
+                            if ((unsure >> t) & 1u) code[t] = affine_code_exact(val[t], aq.kind, aq.scale, aq.zero);
+                    }
+                    uint32_t lo4 = 0, hi4 = 0;
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) { lo4 |= ((uint32_t)code[t] & 0xffu) << (8 * t); hi4 |= ((uint32_t)code[4 + t] & 0xffu) << (8 * t); }
+                    *reinterpret_cast<uint2 *>(crow + (j0 + j) * 256) = make_uint2(lo4, hi4);
+                } else {
+                    *reinterpret_cast<uint4 *>(orow + (j0 + j) * 256) = make_uint4(o[0], o[1], o[2], o[3]);
+                }
             }
         }
     }

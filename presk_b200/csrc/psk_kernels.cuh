@@ -163,15 +163,24 @@ PSK_DEV AffineQuick affine_quick_of(float scale, int kind, int zero)
     return q;
 }
 
-PSK_DEV int affine_code_quick(float x, const AffineQuick &q)
+// The quick code and whether it is certain, without a branch: a caller takes several elements this way, so that
+// their chains overlap, and then sends the uncertain ones (rare) through affine_code_exact.
+PSK_DEV int affine_code_try(float x, const AffineQuick &q, bool &unsure)
 {
     const float v = __fmul_rn(x, q.rscale);
     const float vc = fminf(fmaxf(v, -q.vmax), q.vmax);
     const float t = __fadd_rn(vc, 12582912.0f);
     const float d = __fsub_rn(vc, __fsub_rn(t, 12582912.0f)); // exact
-    if (x != x || fabsf(fabsf(d) - 0.5f) <= q.tol) return affine_code_exact(x, q.kind, q.scale, q.zero);
+    unsure = x != x || fabsf(fabsf(d) - 0.5f) <= q.tol;
     const int n = __float_as_int(t) + q.bias;
     return n < q.lo ? q.lo : (n > q.hi ? q.hi : n);
+}
+
+PSK_DEV int affine_code_quick(float x, const AffineQuick &q)
+{
+    bool unsure;
+    const int n = affine_code_try(x, q, unsure);
+    return unsure ? affine_code_exact(x, q.kind, q.scale, q.zero) : n;
 }
 
 // The code of the IEEE format of t fraction and w exponent bits nearest sig·2^(exp - top), sig's leading
