@@ -439,7 +439,7 @@ __global__ void __launch_bounds__(1024, 1) k_ew_lut(const __grid_constant__ EwPa
     const uint32_t total = E.rows * E.colv;
     const uint32_t stride = gridDim.x * blockDim.x;
     const AffineQuick aq = affine_quick_of(AFF ? E.aff_scale : 1.0f, E.aff_kind, E.aff_zero);
-    constexpr int UNR = 2;
+    constexpr int UNR = AFF ? 1 : 2; // (1024 threads a block: 64 registers each, which the codes' arithmetic fills)
     for (uint32_t idx0 = blockIdx.x * blockDim.x + threadIdx.x; idx0 < total; idx0 += stride * UNR) {
         uint4 a[UNR], b[UNR];
         int64_t oo[UNR];
@@ -563,13 +563,13 @@ struct RmsParams {
 // AFF: the result's site is stored in an affine format (a `scaled` site feeding an integer-sum contraction): the
 // f32 value the last group computes goes straight into its code, as the generic group's store does.
 template <int NV, bool AFF = false>
-__global__ void __launch_bounds__(256, 4) k_rmsnorm_rows(const __grid_constant__ RmsParams P)
+__global__ void __launch_bounds__(256, AFF ? 3 : 4) k_rmsnorm_rows(const __grid_constant__ RmsParams P)
 {
     const int lane = threadIdx.x & 31;
     const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
     const float eps = load_real(P.eps, P.eps_dtype, 0); // widened exactly: the root's group computes in f32
     const float nf = (float)(double)P.n;
-    constexpr int G = NV < 4 ? NV : 4; // vectors loaded before any is used
+    constexpr int G = AFF ? (NV < 2 ? NV : 2) : (NV < 4 ? NV : 4); // vectors loaded before any is used (the codes' arithmetic needs the registers)
     for (int64_t row = warp; row < P.rows; row += nwarps) {
         const uint16_t *xr = P.x + row * P.x_row + lane * 8;
         // pass 1: the sum of the rounded squares, vector by vector in index order. The row is not kept in
