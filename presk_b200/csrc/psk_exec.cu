@@ -521,7 +521,6 @@ int launch_i8(psk_exec *e, const GemmMap &g, const DevOperand &A, const DevOpera
     const int64_t va = O.dtype == PSK_F32 ? 4 : 8;
     P.vec_ok = aligned16(O.p) && g.c_row_lo % va == 0 && g.c_row_hi % va == 0 && g.c_col_hi % va == 0 && g.c_lo % va == 0 && g.c_hi % va == 0 && g.c_col_lo_count % 32 == 0 && g.n % va == 0;
     P.ovf = flag; P.status = e->status;
-    { const char *pr = getenv("PSK_I8_PROBE"); P.probe = pr ? atoi(pr) : 0; } // wrong results: for timing the epilogue's parts only
     int32_t *colsum = nullptr;
     if (A.affine_zero != 0) {
         colsum = (int32_t *)psk_exec_alloc(e, (size_t)g.n * g.batch * 4);

@@ -71,7 +71,6 @@ struct Params {
     const int32_t *colsum;    // sum_k w[k, col] per (batch entry, column), when a_zero != 0
     int guarded;
     int vec_ok;
-    int probe;                // measurements only (PSK_I8_PROBE): 1 leaves the rescale out, 2 the stores, 4 the shuffles
     uint32_t *ovf;
     uint32_t *status;
 };
@@ -371,10 +370,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_i8(const __grid_constant__ 
                         __syncwarp();
                         const uint32_t live_mask = whole ? 0xffffffffu : ((1u << (uint32_t)(P.n - col)) - 1u);
                         uint32_t unsure = 0;
-                        if (P.probe & 1) {
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) packed[i] = v[i] & 0xffffu;
-                        } else if (P.out_dtype == PSK_BF16) {
+                        if (P.out_dtype == PSK_BF16) {
 #pragma unroll
                             for (int i = 0; i < 32; ++i) {
                                 const uint32_t fb = __float_as_uint((float)(int32_t)v[i] * wscale[i]);
@@ -427,7 +423,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_i8(const __grid_constant__ 
                         for (int it = 0; it < units; ++it) {
                             const int rr = it * rows_a_pass + lane / units;
                             const int64_t rrow = row0 + rr;
-                            if (rrow < P.m && unit < live && !(P.probe & 2)) {
+                            if (rrow < P.m && unit < live) {
                                 const uint32_t rq = (uint32_t)rrow / rcnt;
                                 const int64_t off = boff + (int64_t)rq * P.c_row_hi + (int64_t)((uint32_t)rrow - rq * rcnt) * P.c_row_lo + col_off;
                                 const uint4 w = stage_out[rr * 8 + (unit ^ (rr & 7))];
