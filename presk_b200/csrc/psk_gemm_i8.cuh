@@ -97,6 +97,18 @@ PSK_DEV void umma_i8(uint32_t tmem_c, uint64_t adesc, uint64_t bdesc, uint32_t i
         : "memory");
 }
 
+// Sixteen columns of this thread's row of an accumulator.
+PSK_DEV void tmem_ld16(uint32_t taddr, uint32_t (&r)[16])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+
 // sum_k w[k, col] for every (batch entry, column), wrapped to 32 bits: `out` starts at zero and every block adds
 // its run of the summed axis (integer additions that wrap are associative, so the order the atomics land in does
 // not matter). blockIdx.y: the run. N-major weights (s_n = 1): a thread a column, neighbouring threads neighbouring
@@ -335,71 +347,79 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_i8(const __grid_constant__ 
                 }
                 const uint32_t slot = MT == 2 ? (uint32_t)mh : acc;
                 const uint32_t tbase = tmem_base + ((uint32_t)(quad * 32) << 16) + slot * BN;
+                if (staged) {
+                    // Groups of 32 columns of this lane's row, each rescaled, packed and sent through shared memory so
+                    // that a store instruction writes whole runs of a row (bf16: 64 bytes; f32: 128 bytes). The
+                    // accumulators come out of tensor memory sixteen columns at a time into two buffers in turn, the
+                    // next sixteen on their way while these are rescaled.
+                    uint32_t va[16], vb[16];
+                    tmem_ld16(tbase + half_id * 32, va);
 #pragma unroll 1
-                for (int c0 = half_id * 32; c0 < BN; c0 += 64) {
-                    uint32_t v[32];
-                    const int64_t col = n0 + c0;
-                    // this lane fetches the scale (and the zero-point correction) of column col + lane while the
-                    // accumulators come out of tensor memory; the row's loop below takes them by shuffle
-                    const bool col_live = col + lane < P.n;
-                    const float *my_scale = cs_base + (col_live ? (col + lane) * P.col_scale_stride : 0);
-                    const float scale_l = col_live ? *my_scale : 0.0f;
-                    const uint32_t corr_l = (sum_base && col_live) ? (uint32_t)P.a_zero * (uint32_t)sum_base[col + lane] : 0u;
-                    tc::tmem_ld32(tbase + c0, v);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (col >= P.n) continue;
-                    if (staged) {
-                        // 32 columns of this lane's row: rescaled, packed, then through shared memory so that a store
-                        // instruction writes whole runs of a row (bf16: 64 bytes; f32: 128 bytes)
+                    for (int c0 = half_id * 32; c0 < BN; c0 += 64) {
+                        const int64_t col = n0 + c0;
+                        const bool any = col < P.n;
+                        // this lane fetches the scale (and the zero-point correction) of column col + lane
+                        const bool col_live = col + lane < P.n;
+                        const float *my_scale = cs_base + (col_live ? (col + lane) * P.col_scale_stride : 0);
+                        const float scale_l = col_live ? *my_scale : 0.0f;
+                        const uint32_t corr_l = (sum_base && col_live) ? (uint32_t)P.a_zero * (uint32_t)sum_base[col + lane] : 0u;
                         uint32_t packed[32];
                         const double base_l = sa * (double)scale_l;
                         const bool whole = col + 32 <= P.n; // the group's 32 columns all exist
                         const float basef_l = __double2float_rn(base_l);
-                        // The zero point's correction first (a shuffle a column, only when there is one), then the
-                        // rescale in two phases: every element's quick result and whether it is certain, with no
-                        // branch in between, so that the 32 independent chains overlap (with a test and a call after
-                        // each element the warps ran them one after the other, and the rescale cost more than the
-                        // tile's products); then, for the few that are not certain, the exact routine.
-                        if (sum_base) {
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) v[i] -= __shfl_sync(0xffffffffu, corr_l, i);
-                        }
                         float *wscale = scale_area + (warp - 2) * 32; // this warp's 32 columns: bases (bf16 result) or scales (f32)
                         __syncwarp();
                         wscale[lane] = P.out_dtype == PSK_BF16 ? basef_l : scale_l;
                         __syncwarp();
-                        const uint32_t live_mask = whole ? 0xffffffffu : ((1u << (uint32_t)(P.n - col)) - 1u);
-                        uint32_t unsure = 0;
-                        if (P.out_dtype == PSK_BF16) {
+                        const uint32_t live_mask = !any ? 0u : whole ? 0xffffffffu : ((1u << (uint32_t)(P.n - col)) - 1u);
+                        // The rescale of sixteen sums in two phases: every element's quick result and whether it is
+                        // certain, with no branch in between, so that the independent chains overlap (with a test and
+                        // a call after each element the warps ran them one after the other, and the rescale cost more
+                        // than the tile's products); then, for the few that are not certain, the exact routine.
+                        auto rescale16 = [&](uint32_t (&vh)[16], int off) {
+                            if (sum_base) { // the zero point's correction first (a shuffle a column)
 #pragma unroll
-                            for (int i = 0; i < 32; ++i) {
-                                const uint32_t fb = __float_as_uint((float)(int32_t)v[i] * wscale[i]);
-                                // within three binary32 units of a midpoint between bf16 numbers, or subnormal or zero
-                                // (a sum of zero is +0 whatever the scale: rows past the operand's end are all zeros)
-                                unsure |= ((((fb & 0xffffu) - 0x7ffcu) <= 8u || !(fb & 0x7f800000u)) && v[i] != 0u) ? (1u << i) : 0u;
-                                packed[i] = v[i] != 0u ? (fb + 0x7fffu + ((fb >> 16) & 1u)) >> 16 : 0u;
+                                for (int j = 0; j < 16; ++j) vh[j] -= __shfl_sync(0xffffffffu, corr_l, off + j);
                             }
-                            unsure &= live_mask;
-                            if (unsure) {
+                            uint32_t unsure = 0;
+                            if (P.out_dtype == PSK_BF16) {
 #pragma unroll
-                                for (int i = 0; i < 32; ++i)
-                                    if ((unsure >> i) & 1u) packed[i] = count_to_bf16_exact((int32_t)v[i], sa, cs_base + (col + i) * P.col_scale_stride);
-                            }
-                        } else {
+                                for (int j = 0; j < 16; ++j) {
+                                    const uint32_t fb = __float_as_uint((float)(int32_t)vh[j] * wscale[off + j]);
+                                    // within three binary32 units of a midpoint between bf16 numbers, or subnormal or zero
+                                    // (a sum of zero is +0 whatever the scale: rows past the operand's end are all zeros)
+                                    unsure |= ((((fb & 0xffffu) - 0x7ffcu) <= 8u || !(fb & 0x7f800000u)) && vh[j] != 0u) ? (1u << j) : 0u;
+                                    packed[off + j] = vh[j] != 0u ? (fb + 0x7fffu + ((fb >> 16) & 1u)) >> 16 : 0u;
+                                }
+                                unsure &= live_mask >> off;
+                                if (unsure) {
 #pragma unroll
-                            for (int i = 0; i < 32; ++i) {
-                                const double d = (double)(int32_t)v[i] * (sa * (double)wscale[i]);
-                                const uint32_t low = (uint32_t)((uint64_t)__double_as_longlong(d) & 0x1fffffffu); // the 29 bits binary32 drops from a normal number
-                                unsure |= ((!(fabs(d) >= 1.1754943508222875e-38) || (low - 0x0fffffffu) <= 2u) && v[i] != 0u) ? (1u << i) : 0u;
-                                packed[i] = v[i] != 0u ? __float_as_uint(__double2float_rn(d)) : 0u;
-                            }
-                            unsure &= live_mask;
-                            if (unsure) {
+                                    for (int j = 0; j < 16; ++j)
+                                        if ((unsure >> j) & 1u) packed[off + j] = count_to_bf16_exact((int32_t)vh[j], sa, cs_base + (col + off + j) * P.col_scale_stride);
+                                }
+                            } else {
 #pragma unroll
-                                for (int i = 0; i < 32; ++i)
-                                    if ((unsure >> i) & 1u) packed[i] = count_to_f32_exact((int32_t)v[i], sa * (double)wscale[i]);
+                                for (int j = 0; j < 16; ++j) {
+                                    const double d = (double)(int32_t)vh[j] * (sa * (double)wscale[off + j]);
+                                    const uint32_t low = (uint32_t)((uint64_t)__double_as_longlong(d) & 0x1fffffffu); // the 29 bits binary32 drops from a normal number
+                                    unsure |= ((!(fabs(d) >= 1.1754943508222875e-38) || (low - 0x0fffffffu) <= 2u) && vh[j] != 0u) ? (1u << j) : 0u;
+                                    packed[off + j] = vh[j] != 0u ? __float_as_uint(__double2float_rn(d)) : 0u;
+                                }
+                                unsure &= live_mask >> off;
+                                if (unsure) {
+#pragma unroll
+                                    for (int j = 0; j < 16; ++j)
+                                        if ((unsure >> j) & 1u) packed[off + j] = count_to_f32_exact((int32_t)vh[j], sa * (double)wscale[off + j]);
+                                }
                             }
-                        }
+                        };
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); // va: columns c0 .. c0 + 15
+                        tmem_ld16(tbase + c0 + 16, vb);
+                        rescale16(va, 0);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); // vb: columns c0 + 16 .. c0 + 31
+                        if (c0 + 64 < BN) tmem_ld16(tbase + c0 + 64, va);             // the next group's first half
+                        rescale16(vb, 16);
+                        if (!any) continue;
                         if (!whole) {
 #pragma unroll
                             for (int i = 0; i < 32; ++i) packed[i] = ((live_mask >> i) & 1u) ? packed[i] : 0u;
@@ -431,7 +451,22 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_i8(const __grid_constant__ 
                             }
                         }
                         __syncwarp();
-                    } else if (row < P.m) {
+                    }
+                } else {
+#pragma unroll 1
+                for (int c0 = half_id * 32; c0 < BN; c0 += 64) {
+                    uint32_t v[32];
+                    const int64_t col = n0 + c0;
+                    // this lane fetches the scale (and the zero-point correction) of column col + lane while the
+                    // accumulators come out of tensor memory; the row's loop below takes them by shuffle
+                    const bool col_live = col + lane < P.n;
+                    const float *my_scale = cs_base + (col_live ? (col + lane) * P.col_scale_stride : 0);
+                    const float scale_l = col_live ? *my_scale : 0.0f;
+                    const uint32_t corr_l = (sum_base && col_live) ? (uint32_t)P.a_zero * (uint32_t)sum_base[col + lane] : 0u;
+                    tc::tmem_ld32(tbase + c0, v);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (col >= P.n) continue;
+                    if (row < P.m) {
                         for (int i = 0; i < 32; ++i) {
                             const int64_t cc = col + i;
                             if (cc >= P.n) break;
@@ -458,6 +493,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_i8(const __grid_constant__ 
                             }
                         }
                     }
+                }
                 }
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
