@@ -408,7 +408,6 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
             ok = __all_sync(0xffffffffu, ok); // the loads below want the whole warp
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            uint32_t va[32], vb[32]; // a 16-bit group's 64 accumulators of this lane's row (kept across the half-tiles: see below)
 #pragma unroll 1
             for (int mh = 0; mh < MT; ++mh) { // the tile's 128-row halves, each with its own accumulator
             const int64_t row0 = m0 + mh * BM + quad * 32;
@@ -444,15 +443,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
             }
             if (staged) {
                 // 128 bytes of every row at a time: through shared memory, so that a store
-                // instruction writes whole 128-byte lines (8 lanes a row, 4 rows an instruction).
-                // The 64 accumulators of a 16-bit group are asked of tensor memory a group ahead: the first group's
-                // here, each later one's (the other half-tile's first among them) once this group's are rounded and
-                // on their way through shared memory, so that the load's latency runs beside the stores.
-                const bool two_loads = P.out_dtype != PSK_F32;
-                if (two_loads && mh == 0) {
-                    tmem_ld32(tbase + half_id * group_cols, va);
-                    tmem_ld32(tbase + half_id * group_cols + 32, vb);
-                }
+                // instruction writes whole 128-byte lines (8 lanes a row, 4 rows an instruction)
 #pragma unroll 1
                 for (int c0 = half_id * group_cols; c0 < BN; c0 += 2 * group_cols) {
                     const int64_t col = n0 + c0;
@@ -484,6 +475,9 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
                             const uint32_t cq = (uint32_t)col / ccnt;
                             add_col_off = (int64_t)cq * P.c_col_hi + (int64_t)((uint32_t)col - cq * ccnt);
                         }
+                        uint32_t va[32], vb[32];
+                        tmem_ld32(tbase + c0, va);
+                        tmem_ld32(tbase + c0 + 32, vb);
                         const bool cs_add = plain_cs_add && col + 64 <= P.n && (reinterpret_cast<uintptr_t>(cs_base + col) & 15) == 0;
                         if (plain_add) {
                             // the residual of this lane's row, 128 bytes, asked for a group ahead (taking it through the
@@ -601,15 +595,6 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
                             }
                         }
                         } // not plain_add
-                    }
-                    if (two_loads) {
-                        if (c0 + 2 * group_cols < BN) {
-                            tmem_ld32(tbase + c0 + 2 * group_cols, va);
-                            tmem_ld32(tbase + c0 + 2 * group_cols + 32, vb);
-                        } else if (MT == 2 && mh + 1 < MT) { // the other half-tile's accumulator lies BN columns on
-                            tmem_ld32(tbase + BN + half_id * group_cols, va);
-                            tmem_ld32(tbase + BN + half_id * group_cols + 32, vb);
-                        }
                     }
                     __syncwarp();
                     if (col < P.n) {
