@@ -97,18 +97,6 @@ PSK_DEV void umma_i8(uint32_t tmem_c, uint64_t adesc, uint64_t bdesc, uint32_t i
         : "memory");
 }
 
-// Sixteen columns of this thread's row of an accumulator.
-PSK_DEV void tmem_ld16(uint32_t taddr, uint32_t (&r)[16])
-{
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr)
-        : "memory");
-}
-
 // sum_k w[k, col] for every (batch entry, column), wrapped to 32 bits: `out` starts at zero and every block adds
 // its run of the summed axis (integer additions that wrap are associative, so the order the atomics land in does
 // not matter). blockIdx.y: the run. N-major weights (s_n = 1): a thread a column, neighbouring threads neighbouring
@@ -353,7 +341,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_i8(const __grid_constant__ 
                     // accumulators come out of tensor memory sixteen columns at a time into two buffers in turn, the
                     // next sixteen on their way while these are rescaled.
                     uint32_t va[16], vb[16];
-                    tmem_ld16(tbase + half_id * 32, va);
+                    tc::tmem_ld16(tbase + half_id * 32, va);
 #pragma unroll 1
                     for (int c0 = half_id * 32; c0 < BN; c0 += 64) {
                         const int64_t col = n0 + c0;
@@ -414,10 +402,10 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_i8(const __grid_constant__ 
                             }
                         };
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); // va: columns c0 .. c0 + 15
-                        tmem_ld16(tbase + c0 + 16, vb);
+                        tc::tmem_ld16(tbase + c0 + 16, vb);
                         rescale16(va, 0);
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); // vb: columns c0 + 16 .. c0 + 31
-                        if (c0 + 64 < BN) tmem_ld16(tbase + c0 + 64, va);             // the next group's first half
+                        if (c0 + 64 < BN) tc::tmem_ld16(tbase + c0 + 64, va);             // the next group's first half
                         rescale16(vb, 16);
                         if (!any) continue;
                         if (!whole) {

@@ -183,6 +183,18 @@ PSK_DEV void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
         : "memory");
 }
 
+// Sixteen columns of this thread's row of an accumulator.
+PSK_DEV void tmem_ld16(uint32_t taddr, uint32_t (&r)[16])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+
 // Where tile `r` of a batch lies. Tiles are handed out in panels of PANEL
 // tile-columns, down every tile-row of a panel before the next panel: the
 // CTAs running at one time then share a few columns of B and a band of rows of
@@ -236,7 +248,11 @@ struct Smem {
 // one word a launch, for a caller that wants to know which entry overflowed.
 // CS: the instantiation launched when columns carry a scale (integer weights); it alone holds the epilogue's
 // vector paths for scales, so that the plain instantiation keeps its registers.
-template <int BN, bool PER_BATCH = false, int MT = 1, bool CS = false>
+// PLAIN: the instantiation for a plain bf16 result (whole 16-byte runs, no scale, no column scales, no addend, no
+// guard: what the host checks before it launches it): its epilogue takes the accumulators out of tensor memory
+// sixteen columns at a time into two buffers in turn, the next sixteen (the next group's, the other half-tile's) on
+// their way while these are rounded and staged, so that the load's latency is not waited for once a group.
+template <int BN, bool PER_BATCH = false, int MT = 1, bool CS = false, bool PLAIN = false>
 __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ Params P)
 {
     static_assert(MT == 1 || (MT == 2 && BN == 256), "two halves fill tensor memory with 256 columns each");
@@ -390,8 +406,9 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
             // A residual addend: this lane's 128 bytes of the group (row half mh, columns c0 ..) it will add next. The
             // first group's are asked for here, while the tile's products still run, and each later group's while the
             // one before it is rounded, so that no group waits for its addend.
-            uint4 ad_next[8];
+            uint4 ad_next[PLAIN ? 1 : 8];
             auto fetch_addend = [&](int mh_, int c0_) {
+                if constexpr (PLAIN) return;
                 const int64_t arow = m0 + mh_ * BM + quad * 32 + lane, acol = n0 + c0_;
                 const uint32_t rcnt_ = (uint32_t)(P.c_row_lo_count < 0x7fffffffll ? P.c_row_lo_count : 0x7fffffffll);
                 const uint32_t ccnt_ = (uint32_t)(P.c_col_lo_count < 0x7fffffffll ? P.c_col_lo_count : 0x7fffffffll);
@@ -408,6 +425,8 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
             ok = __all_sync(0xffffffffu, ok); // the loads below want the whole warp
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint32_t ca[16], cb[16]; // PLAIN: the two buffers; `primed`: the group about to start has its first sixteen on their way
+            bool primed = false;
 #pragma unroll 1
             for (int mh = 0; mh < MT; ++mh) { // the tile's 128-row halves, each with its own accumulator
             const int64_t row0 = m0 + mh * BM + quad * 32;
@@ -475,6 +494,33 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
                             const uint32_t cq = (uint32_t)col / ccnt;
                             add_col_off = (int64_t)cq * P.c_col_hi + (int64_t)((uint32_t)col - cq * ccnt);
                         }
+                        if constexpr (PLAIN) {
+                            // columns 16k .. 16k + 15 of the group: two 16-byte units of the staged row
+                            auto emit = [&](const uint32_t (&ch)[16], int k) {
+#pragma unroll
+                                for (int h = 0; h < 2; ++h) {
+                                    uint32_t u[4];
+#pragma unroll
+                                    for (int i = 0; i < 4; ++i) u[i] = pack_bf16x2_hw(__uint_as_float(ch[8 * h + 2 * i]), __uint_as_float(ch[8 * h + 2 * i + 1]));
+                                    stage_out[lane * 8 + ((2 * k + h) ^ (lane & 7))] = make_uint4(u[0], u[1], u[2], u[3]);
+                                }
+                            };
+                            if (!primed) tmem_ld16(tbase + c0, ca);
+                            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                            tmem_ld16(tbase + c0 + 16, cb);
+                            emit(ca, 0);
+                            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                            tmem_ld16(tbase + c0 + 32, ca);
+                            emit(cb, 1);
+                            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                            tmem_ld16(tbase + c0 + 48, cb);
+                            emit(ca, 2);
+                            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                            if (c0 + 2 * group_cols < BN) { tmem_ld16(tbase + c0 + 2 * group_cols, ca); primed = true; }
+                            else if (MT == 2 && mh + 1 < MT) { tmem_ld16(tbase + BN + half_id * group_cols, ca); primed = true; } // the other half-tile's accumulator lies BN columns on
+                            else primed = false;
+                            emit(cb, 3);
+                        } else {
                         uint32_t va[32], vb[32];
                         tmem_ld32(tbase + c0, va);
                         tmem_ld32(tbase + c0 + 32, vb);
@@ -595,6 +641,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
                             }
                         }
                         } // not plain_add
+                        } // not PLAIN
                     }
                     __syncwarp();
                     if (col < P.n) {
