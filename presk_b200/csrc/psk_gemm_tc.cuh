@@ -248,11 +248,11 @@ struct Smem {
 // one word a launch, for a caller that wants to know which entry overflowed.
 // CS: the instantiation launched when columns carry a scale (integer weights); it alone holds the epilogue's
 // vector paths for scales, so that the plain instantiation keeps its registers.
-// PLAIN: the instantiation for a plain bf16 result (whole 16-byte runs, no scale, no column scales, no addend, no
-// guard: what the host checks before it launches it): its epilogue takes the accumulators out of tensor memory
+// PLAIN: the instantiations for a plain bf16 result (whole 16-byte runs, no scale, no column scales, no guard: what
+// the host checks before it launches them), 1 without and 2 with a residual addend: their epilogue takes the accumulators out of tensor memory
 // sixteen columns at a time into two buffers in turn, the next sixteen (the next group's, the other half-tile's) on
 // their way while these are rounded and staged, so that the load's latency is not waited for once a group.
-template <int BN, bool PER_BATCH = false, int MT = 1, bool CS = false, bool PLAIN = false>
+template <int BN, bool PER_BATCH = false, int MT = 1, bool CS = false, int PLAIN = 0>
 __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ Params P)
 {
     static_assert(MT == 1 || (MT == 2 && BN == 256), "two halves fill tensor memory with 256 columns each");
@@ -406,9 +406,9 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
             // A residual addend: this lane's 128 bytes of the group (row half mh, columns c0 ..) it will add next. The
             // first group's are asked for here, while the tile's products still run, and each later group's while the
             // one before it is rounded, so that no group waits for its addend.
-            uint4 ad_next[PLAIN ? 1 : 8];
+            uint4 ad_next[PLAIN == 1 ? 1 : 8];
             auto fetch_addend = [&](int mh_, int c0_) {
-                if constexpr (PLAIN) return;
+                if constexpr (PLAIN == 1) return;
                 const int64_t arow = m0 + mh_ * BM + quad * 32 + lane, acol = n0 + c0_;
                 const uint32_t rcnt_ = (uint32_t)(P.c_row_lo_count < 0x7fffffffll ? P.c_row_lo_count : 0x7fffffffll);
                 const uint32_t ccnt_ = (uint32_t)(P.c_col_lo_count < 0x7fffffffll ? P.c_col_lo_count : 0x7fffffffll);
@@ -494,14 +494,22 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
                             const uint32_t cq = (uint32_t)col / ccnt;
                             add_col_off = (int64_t)cq * P.c_col_hi + (int64_t)((uint32_t)col - cq * ccnt);
                         }
-                        if constexpr (PLAIN) {
-                            // columns 16k .. 16k + 15 of the group: two 16-byte units of the staged row
+                        if constexpr (PLAIN != 0) {
+                            // columns 16k .. 16k + 15 of the group: two 16-byte units of the staged row (PLAIN 2: the
+                            // product rounded to bf16, the residual added, the sum rounded again)
                             auto emit = [&](const uint32_t (&ch)[16], int k) {
 #pragma unroll
                                 for (int h = 0; h < 2; ++h) {
                                     uint32_t u[4];
 #pragma unroll
-                                    for (int i = 0; i < 4; ++i) u[i] = pack_bf16x2_hw(__uint_as_float(ch[8 * h + 2 * i]), __uint_as_float(ch[8 * h + 2 * i + 1]));
+                                    for (int i = 0; i < 4; ++i) {
+                                        u[i] = pack_bf16x2_hw(__uint_as_float(ch[8 * h + 2 * i]), __uint_as_float(ch[8 * h + 2 * i + 1]));
+                                        if constexpr (PLAIN == 2) {
+                                            const uint4 a4 = ad_next[(2 * k + h) & 7];
+                                            const uint32_t aw = i == 0 ? a4.x : i == 1 ? a4.y : i == 2 ? a4.z : a4.w;
+                                            u[i] = pack_bf16x2_hw(__fadd_rn(bits_f32(aw << 16), bits_f32(u[i] << 16)), __fadd_rn(bits_f32(aw & 0xffff0000u), bits_f32(u[i] & 0xffff0000u)));
+                                        }
+                                    }
                                     stage_out[lane * 8 + ((2 * k + h) ^ (lane & 7))] = make_uint4(u[0], u[1], u[2], u[3]);
                                 }
                             };
@@ -520,6 +528,10 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_tc(const __grid_constant__ 
                             else if (MT == 2 && mh + 1 < MT) { tmem_ld16(tbase + BN + half_id * group_cols, ca); primed = true; } // the other half-tile's accumulator lies BN columns on
                             else primed = false;
                             emit(cb, 3);
+                            if constexpr (PLAIN == 2) { // the next group's residual, on its way during this group's stores
+                                if (c0 + 2 * group_cols < BN) fetch_addend(mh, c0 + 2 * group_cols);
+                                else if (mh + 1 < MT) fetch_addend(mh + 1, half_id * group_cols);
+                            }
                         } else {
                         uint32_t va[32], vb[32];
                         tmem_ld32(tbase + c0, va);
