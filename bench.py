@@ -75,8 +75,9 @@ QUANTISED = ("blocks.attn.wq", "blocks.attn.wk", "blocks.attn.wv", "blocks.attn.
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel's heaviest frequent shape, from the
 # ncu capture summarised in profiles/k_gemm_tc_ffn_16384x11008x4096.md (bytes a launch; algorithmic bytes: 585 MB)
-GEMM_TRAFFIC = {"llama7b_prefill_b8_t2048": 796489216 + 334924800}
-GEMM_TRAFFIC_OF = "k_gemm_tc<256, false, 2>, dot [16384, 4096] x [4096, 11008] (gate/up projections: 64 of a step's 225 contractions), one launch under ncu"
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the step's dominant kernel under ncu (profiles/)
+GEMM_TRAFFIC = {"llama7b_prefill_b8_t2048": 791255040 + 335562752, "llama7b_w8a8_prefill_b8_t2048": 188421120 + 325028096, "llama7b_w8a8_prefill_b16_t1024": 188421120 + 325028096}
+GEMM_TRAFFIC_OF = "dot [16384, 4096] x [4096, 11008] (gate/up projections: 64 of a step's 225 contractions), one launch under ncu: k_gemm_tc<256, false, 2, false, 1> for bf16, k_gemm_i8<1> for the W8A8 workloads"
 
 
 def realization(paths, int8=False, attention="unfused", launches="reference"):
