@@ -424,9 +424,8 @@ int launch_tc(psk_exec *e, const psk_gemm &g, const void *a, const void *b, void
         }
     }
     // a plain bf16 result in whole 16-byte runs: the instantiation whose epilogue keeps tensor memory's loads ahead
-    static const bool plain_on = getenv("PSK_GEMM_PLAIN") ? atoi(getenv("PSK_GEMM_PLAIN")) != 0 : true;
-    const int plain_mode = atoi(getenv("PSK_GEMM_PLAIN") ? getenv("PSK_GEMM_PLAIN") : "3"); // bit 0: without an addend, bit 1: with one
-    const bool plain_any = plain_on && P.vec_ok && g.out_dtype == PSK_BF16 && !g.scale_on && !col_scale && !split_k && !a_m_major && bn == 256;
+    static const int plain_mode = getenv("PSK_GEMM_PLAIN") ? atoi(getenv("PSK_GEMM_PLAIN")) : 3; // bit 0: results without an addend, bit 1: with one
+    const bool plain_any = P.vec_ok && g.out_dtype == PSK_BF16 && !g.scale_on && !col_scale && !split_k && !a_m_major && bn == 256;
     const bool plain_bf16 = plain_any && !addend && (plain_mode & 1), plain_add = plain_any && addend && (plain_mode & 2);
     if (plain_bf16 && mt_rows == 2) tc::k_gemm_tc<256, false, 2, false, 1><<<grid, tc::THREADS, tc::Smem<256, 2>::TOTAL, e->stream>>>(ma, mb, P);
     else if (plain_bf16) tc::k_gemm_tc<256, false, 1, false, 1><<<grid, tc::THREADS, tc::Smem<256>::TOTAL, e->stream>>>(ma, mb, P);
