@@ -95,9 +95,10 @@ typedef enum {
                              over (seq, seq2) when n_inputs is 5. iparam[1..3]: the storage types of the three
                              sites in between. iparam[0]: how an executor may fuse them: 0 blockwise (two passes
                              over the keys, each stored site's rounding kept in registers), 1 online (one pass
-                             against a running reference maximum, the sites in between not rounded). The value is DEFINED as that of the four launches run one after
-                             the other; an executor may only fuse them under PSK_ORDER_DEVICE, and then agrees
-                             with them within a tolerance. No counterpart among the reference's kernels: its
+                             against a running reference maximum, the sites in between not rounded). The value is
+                             DEFINED as that of the four launches run one after the other; an executor may only fuse
+                             them under PSK_ORDER_DEVICE, and then agrees with them within a tolerance. The result
+                             may be a `scaled` site (out.affine): the last launch's binary32 sum stored as its code. No counterpart among the reference's kernels: its
                              fusion (presk-core/src/fusion.rs) never crosses a contraction or a softmax. */
     PSK_OP_RMSNORM = 12,  /* the four launches of RMSNorm.apply as one (examples/coverage/llama.psk:34-40): x*x, its
                              mean over the last axis, sqrt(mean + eps), x / root * gamma. Space: the axes of x, no
@@ -119,7 +120,8 @@ typedef enum {
                              Inputs 0 and 1 as in PSK_OP_CONTRACT, input 2 over the outer axes. iparam[1]: the storage
                              type of the contraction's own site; dtype: the sum's. The value is DEFINED as that of the
                              two launches (contraction stored in its type, then in[2] + it); an executor that takes
-                             it must give their bits under the launch's order. */
+                             it must give their bits under the launch's order. With int_accum the contraction counts
+                             in integers as PSK_OP_CONTRACT does (inputs 0 and 1 affine values or integer weights). */
     PSK_OP_XENT_VJP = 15, /* lower.rs:1472-1488: cross_entropy_vjp. Space as PSK_OP_XENT (outer axes, one inner axis:
                              the classes). Inputs: logits, labels, the cotangent over the outer axes. Output over the
                              whole space: (exp(x - m) / z - [k == y]) * ct, m and z as in PSK_OP_XENT (the maximum from

@@ -904,7 +904,7 @@ static int psk_oracle_run_merged(const psk_launch *l, void *const *table, uint32
                                 }
                             }
                             for (int r = 0; r < rn; ++r)
-                                for (int jj = 0; jj < jb; ++jj) ovf |= store_real(outp, l->out.dtype, ob[r0 + r] + j0 + jj, acc[r][jj]);
+                                for (int jj = 0; jj < jb; ++jj) ovf |= store_out(l, outp, ob[r0 + r] + j0 + jj, acc[r][jj]);
                         }
                     }
                 }
@@ -952,7 +952,7 @@ static int psk_oracle_run_merged(const psk_launch *l, void *const *table, uint32
                     acc = acc + prod;
                 }
             }
-            ovf |= store_real(outp, l->out.dtype, offset_of(l->out.stride, l->dims, 0, no, lin), acc);
+            ovf |= store_out(l, outp, offset_of(l->out.stride, l->dims, 0, no, lin), acc);
             ovf_all |= ovf;
         }
         break;
@@ -971,7 +971,7 @@ static int psk_oracle_run_merged(const psk_launch *l, void *const *table, uint32
                 }
             }
             if (l->kind == PSK_REDUCE_MEAN) acc = acc / (float)(double)l->iparam[0];
-            ovf |= store_real(outp, l->out.dtype, offset_of(l->out.stride, l->dims, 0, no, lin), acc);
+            ovf |= store_out(l, outp, offset_of(l->out.stride, l->dims, 0, no, lin), acc);
             ovf_all |= ovf;
         }
         break;
@@ -988,7 +988,7 @@ static int psk_oracle_run_merged(const psk_launch *l, void *const *table, uint32
                 for (int64_t k = 0; k < n; ++k) if (X(k) > m) m = X(k);
                 float z = 0.0f;
                 for (int64_t k = 0; k < n; ++k) z = z + presk_expf(X(k) - m);
-                for (int64_t k = 0; k < n; ++k) ovf |= store_real(outp, l->out.dtype, obase + k * os, presk_expf(X(k) - m) / z);
+                for (int64_t k = 0; k < n; ++k) ovf |= store_out(l, outp, obase + k * os, presk_expf(X(k) - m) / z);
             } else {
                 int64_t mbase = offset_of(l->in[1].stride, l->dims, 0, no, row), ms = l->in[1].stride[no];
                 const int64_t *mk = (const int64_t *)in[1].p;
@@ -1000,7 +1000,7 @@ static int psk_oracle_run_merged(const psk_launch *l, void *const *table, uint32
                 }
                 float z = 0.0f;
                 for (int64_t k = 0; k < n; ++k) z = z + (ALLOWED(k) ? presk_expf(X(k) - mx) : 0.0f);
-                for (int64_t k = 0; k < n; ++k) ovf |= store_real(outp, l->out.dtype, obase + k * os, ALLOWED(k) ? presk_expf(X(k) - mx) / z : 0.0f);
+                for (int64_t k = 0; k < n; ++k) ovf |= store_out(l, outp, obase + k * os, ALLOWED(k) ? presk_expf(X(k) - mx) / z : 0.0f);
 #undef ALLOWED
             }
 #undef X
@@ -1026,7 +1026,7 @@ static int psk_oracle_run_merged(const psk_launch *l, void *const *table, uint32
             float xy = 0.0f;
             if (y >= 0 && y < n) xy = load_operand(&in[0], base + y * s, 0, kd, &ovf);
             else bad |= 1;
-            ovf |= store_real(outp, l->out.dtype, offset_of(l->out.stride, l->dims, 0, no, row), (presk_logf(z) + m) - xy);
+            ovf |= store_out(l, outp, offset_of(l->out.stride, l->dims, 0, no, row), (presk_logf(z) + m) - xy);
             ovf_all |= ovf;
         }
         if (bad) return PSK_E7001;
@@ -1052,7 +1052,7 @@ static int psk_oracle_run_merged(const psk_launch *l, void *const *table, uint32
                 /* the reference compares the two integers as reals of the kernel's type */
                 float hot = (float)k == (float)y ? 1.0f : 0.0f;
                 float sm = presk_expf(load_operand(&in[0], base + k * s, 0, kd, &ovf) - m) / z;
-                ovf |= store_real(outp, l->out.dtype, obase + k * os, (sm - hot) * ct);
+                ovf |= store_out(l, outp, obase + k * os, (sm - hot) * ct);
             }
             ovf_all |= ovf;
         }
@@ -1064,7 +1064,7 @@ static int psk_oracle_run_merged(const psk_launch *l, void *const *table, uint32
         uint32_t ovf = 0;
         int bad = 0;
         for (int64_t v = 0; v < vocab; ++v)
-            for (int64_t j = 0; j < d; ++j) store_real(outp, l->out.dtype, v * l->out.stride[0] + j * l->out.stride[1], 0.0f);
+            for (int64_t j = 0; j < d; ++j) store_out(l, outp, v * l->out.stride[0] + j * l->out.stride[1], 0.0f);
         for (int64_t row = 0; row < rows; ++row) {
             int64_t id = ((const int64_t *)in[1].p)[offset_of(l->in[1].stride, l->dims, 0, last, row)];
             if (id < 0 || id >= vocab) { bad = 1; continue; }
@@ -1072,7 +1072,7 @@ static int psk_oracle_run_merged(const psk_launch *l, void *const *table, uint32
             for (int64_t j = 0; j < d; ++j) {
                 int64_t o = id * l->out.stride[0] + j * l->out.stride[1];
                 float acc = load_real(outp, l->out.dtype, o) + load_operand(&in[2], cbase + j * l->in[2].stride[last], 0, kd, &ovf);
-                ovf |= store_real(outp, l->out.dtype, o, acc);
+                ovf |= store_out(l, outp, o, acc);
             }
         }
         ovf_all |= ovf;
@@ -1105,7 +1105,7 @@ static int psk_oracle_run_merged(const psk_launch *l, void *const *table, uint32
             int64_t obase = offset_of(l->out.stride, l->dims, 0, last, row);
             if (id < 0 || id >= l->iparam[0]) { bad |= 1; id = 0; }
             for (int64_t j = 0; j < d; ++j)
-                ovf |= store_real(outp, l->out.dtype, obase + j * l->out.stride[last], load_operand(&in[0], id * l->in[0].stride[0] + j * l->in[0].stride[1], 0, kd, &ovf));
+                ovf |= store_out(l, outp, obase + j * l->out.stride[last], load_operand(&in[0], id * l->in[0].stride[0] + j * l->in[0].stride[1], 0, kd, &ovf));
             ovf_all |= ovf;
         }
         if (bad) return PSK_E7001;
@@ -1117,7 +1117,7 @@ static int psk_oracle_run_merged(const psk_launch *l, void *const *table, uint32
             uint32_t ovf = 0;
             int64_t off = offset_of(l->in[0].stride, l->dims, 0, no, lin), ooff = offset_of(l->out.stride, l->dims, 0, no, lin);
             if (l->in[0].is_index) ((int64_t *)outp)[ooff] = ((const int64_t *)in[0].p)[off];
-            else ovf |= store_real(outp, l->out.dtype, ooff, load_operand(&in[0], off, 0, kd, &ovf));
+            else ovf |= store_out(l, outp, ooff, load_operand(&in[0], off, 0, kd, &ovf));
             ovf_all |= ovf;
         }
         break;
@@ -1133,10 +1133,10 @@ static int psk_oracle_run_merged(const psk_launch *l, void *const *table, uint32
             case PSK_IOTA_ONE_HOT: {
                 int64_t v = l->dims[no - 1], row = lin / v, j = lin % v;
                 int64_t id = ((const int64_t *)in[0].p)[offset_of(l->in[0].stride, l->dims, 0, no - 1, row)];
-                ovf_all |= store_real(outp, l->out.dtype, lin, (float)(double)id == (float)(double)j ? 1.0f : 0.0f);
+                ovf_all |= store_out(l, outp, lin, (float)(double)id == (float)(double)j ? 1.0f : 0.0f);
                 break;
             }
-            default: ovf_all |= store_real(outp, l->out.dtype, lin, (float)l->fparam[0]); break;
+            default: ovf_all |= store_out(l, outp, lin, (float)l->fparam[0]); break;
             }
         }
         break;
@@ -1146,7 +1146,7 @@ static int psk_oracle_run_merged(const psk_launch *l, void *const *table, uint32
                 int q = l->in[0].affine == 2 ? (int)((const uint8_t *)in[0].p)[i] : (int)((const int8_t *)in[0].p)[i];
                 double x = (double)(q - l->in[0].affine_zero) * (double)l->in[0].affine_scale;
                 if (l->out.dtype == PSK_F64) ((double *)outp)[i] = x;
-                else ovf_all |= store_real(outp, l->out.dtype, i, (float)x);
+                else ovf_all |= store_out(l, outp, i, (float)x);
             } else if (l->in[0].dtype == PSK_F64) {
                 double x = ((const double *)in[0].p)[i];
                 switch (l->out.dtype) {
@@ -1159,10 +1159,10 @@ static int psk_oracle_run_merged(const psk_launch *l, void *const *table, uint32
                     ovf_all |= (fabs(x) >= 0x1.ffffp127 && fabs(x) < INFINITY);
                     break;
                 }
-                default: ovf_all |= store_real(outp, l->out.dtype, i, (float)x); break; /* to bf16 by way of f32 */
+                default: ovf_all |= store_out(l, outp, i, (float)x); break; /* to bf16 by way of f32 */
                 }
             } else {
-                ovf_all |= store_real(outp, l->out.dtype, i, load_real(in[0].p, l->in[0].dtype, i));
+                ovf_all |= store_out(l, outp, i, load_real(in[0].p, l->in[0].dtype, i));
             }
         }
         break;

@@ -55,6 +55,8 @@ struct Params {
     const void *rt;        // the divisor, a rank-0 tensor
     int32_t rt_dtype;
     uint32_t *status;
+    int32_t aff_kind, aff_zero; // k_attn_fwd3 only: the result as one-byte codes of an affine format (kind 1 i8, 2 u8; 0: bf16)
+    float aff_scale;
 };
 
 PSK_DEV float bf16_round(float x) { return bits_f32(pack_bf16x2_hw(x, 0.0f) << 16); }
@@ -819,18 +821,50 @@ __global__ void __launch_bounds__(THREADS3, 2) k_attn_fwd3(const __grid_constant
             const int64_t t = (int64_t)qb * BM + row;
             uint16_t *orow = (uint16_t *)P.out + (int64_t)b * P.o_b + (int64_t)g * P.o_g + t * P.o_t;
             const float rz = __frcp_rn(z);
+            if (P.aff_kind) {
+                // The row as codes of the site's affine format, 32 bytes a group: clamp(rne(acc / (z s)) + zero), the
+                // quotient taken as acc times RN(RN(1/z) RN(1/s)) (a few units of binary32 from the quotient: this kernel
+                // agrees with the separate launches within a tolerance anyway, and a code differs from theirs only
+                // where the value lies that near a tie), clamped to the codes' range before 1.5 * 2^23 is added to
+                // round it to an integer, ties to even, held in the sum's low bits. A NaN is the zero point.
+                const int lo = P.aff_kind == 2 ? 0 : -128, hi = P.aff_kind == 2 ? 255 : 127;
+                const float vlo = (float)(lo - P.aff_zero), vhi = (float)(hi - P.aff_zero);
+                const float kq = __fmul_rn(rz, __frcp_rn(P.aff_scale));
+                const int bias = P.aff_zero - 0x4B400000;
+                uint8_t *crow = (uint8_t *)P.out + (int64_t)b * P.o_b + (int64_t)g * P.o_g + t * P.o_t;
 #pragma unroll 1
-            for (int c0 = 0; c0 < HD; c0 += 32) {
-                uint32_t v[32];
-                tc::tmem_ld32(tO + lane_base + (uint32_t)c0, v);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                for (int c0 = 0; c0 < HD; c0 += 32) {
+                    uint32_t v[32];
+                    tc::tmem_ld32(tO + lane_base + (uint32_t)c0, v);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    uint32_t w[8];
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    uint32_t w[4];
+                    for (int i = 0; i < 32; ++i) {
+                        float q = __fmul_rn(__uint_as_float(v[i]), kq);
+                        q = q == q ? q : 0.0f;
+                        q = fminf(fmaxf(q, vlo), vhi);
+                        v[i] = (uint32_t)(__float_as_int(__fadd_rn(q, 12582912.0f)) + bias);
+                    }
 #pragma unroll
-                    for (int i = 0; i < 4; ++i)
-                        w[i] = pack_bf16x2_hw(div_by(__uint_as_float(v[u * 8 + 2 * i]), z, rz), div_by(__uint_as_float(v[u * 8 + 2 * i + 1]), z, rz));
-                    *reinterpret_cast<uint4 *>(orow + c0 + u * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                    for (int u = 0; u < 8; ++u)
+                        w[u] = __byte_perm(__byte_perm(v[4 * u], v[4 * u + 1], 0x0040), __byte_perm(v[4 * u + 2], v[4 * u + 3], 0x0040), 0x5410);
+                    *reinterpret_cast<uint4 *>(crow + c0) = make_uint4(w[0], w[1], w[2], w[3]);
+                    *reinterpret_cast<uint4 *>(crow + c0 + 16) = make_uint4(w[4], w[5], w[6], w[7]);
+                }
+            } else {
+#pragma unroll 1
+                for (int c0 = 0; c0 < HD; c0 += 32) {
+                    uint32_t v[32];
+                    tc::tmem_ld32(tO + lane_base + (uint32_t)c0, v);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            w[i] = pack_bf16x2_hw(__fmul_rn(__uint_as_float(v[u * 8 + 2 * i]), rz), __fmul_rn(__uint_as_float(v[u * 8 + 2 * i + 1]), rz)); // (by the reciprocal: a unit or two of binary32 from the quotient, far inside this kernel's tolerance)
+                        *reinterpret_cast<uint4 *>(orow + c0 + u * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
                 }
             }
         }

@@ -28,6 +28,8 @@ struct Params {
     int32_t G, Pn, len;
     const void *rt;
     int32_t rt_dtype;
+    int32_t aff_kind, aff_zero; // the result as one-byte codes of an affine format (kind 1 i8, 2 u8; 0: bf16)
+    float aff_scale;
 };
 
 PSK_DEV void unpack4(uint2 w, float *f)
@@ -108,7 +110,9 @@ __global__ void __launch_bounds__(THREADS) k_attn_step(const __grid_constant__ P
         float s = 0.0f;
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) s = __fadd_rn(s, part[w][threadIdx.x]);
-        P.out[b * P.o_b + g * P.o_g + p * P.o_p + threadIdx.x] = f32_to_bf16(s);
+        const int64_t o = b * P.o_b + g * P.o_g + p * P.o_p + threadIdx.x;
+        if (P.aff_kind) ((uint8_t *)P.out)[o] = (uint8_t)affine_code_quick(s, affine_quick_of(P.aff_scale, P.aff_kind, P.aff_zero)); // the binary32 sum's code, as the separate launch stores it
+        else P.out[o] = f32_to_bf16(s);
     }
 }
 

@@ -494,8 +494,9 @@ bool make_map_u8(psk_exec *e, CUtensorMap *map, const void *base, uint64_t d0, u
 }
 
 // The integer-sum contraction on the tensor cores (psk_gemm_i8.cuh). PSK_E7001: strides no tensor map takes
-// (the caller then runs the scalar kernel).
-int launch_i8(psk_exec *e, const GemmMap &g, const DevOperand &A, const DevOperand &B, const DevOperand &O, const psk_operand &out_desc, uint32_t *flag, bool guarded)
+// (the caller then runs the scalar kernel). `addend`: a bf16 tensor laid out as a bf16 result, added to the rounded
+// product; only the staged stores add it, so other layouts answer PSK_E7001 too.
+int launch_i8(psk_exec *e, const GemmMap &g, const DevOperand &A, const DevOperand &B, const DevOperand &O, const psk_operand &out_desc, uint32_t *flag, bool guarded, const void *addend = nullptr)
 {
     if (!e->encode) return fail(e, PSK_E10001, "cuTensorMapEncodeTiled is not available from this driver");
     const bool b_n_major = g.b_k != 1;
@@ -505,7 +506,7 @@ int launch_i8(psk_exec *e, const GemmMap &g, const DevOperand &A, const DevOpera
     // the L2 and the rescale exposed (psk_gemm_i8.cuh); PSK_I8_MT chooses, for measurements
     const char *mt_word = getenv("PSK_I8_MT"); // read at every launch, so that a test can run both forms
     const int mt_env = mt_word ? atoi(mt_word) : 1;
-    const int mt_rows = (mt_env == 2 && g.m >= 256) ? 2 : 1;
+    const int mt_rows = (mt_env == 2 && g.m >= 256 && !addend) ? 2 : 1; // (the addend's instance has tiles of 128 rows)
     if (!make_map_u8(e, &ma, A.p, (uint64_t)g.k, (uint64_t)g.m, (uint64_t)g.batch_lo, (uint64_t)batch_hi, (uint64_t)g.a_row, (uint64_t)g.a_lo, (uint64_t)g.a_hi, tci8::BKB, (uint32_t)(tci8::BM * mt_rows)))
         return fail(e, PSK_E7001, "integer contraction: operand 0's strides do not make a tensor map");
     const bool okb = b_n_major
@@ -533,6 +534,10 @@ int launch_i8(psk_exec *e, const GemmMap &g, const DevOperand &A, const DevOpera
     const int64_t va = O.dtype == PSK_F32 ? 4 : 8;
     P.vec_ok = aligned16(O.p) && g.c_row_lo % va == 0 && g.c_row_hi % va == 0 && g.c_col_hi % va == 0 && g.c_lo % va == 0 && g.c_hi % va == 0 && g.c_col_lo_count % 32 == 0 && g.n % va == 0;
     P.ovf = flag; P.status = e->status;
+    if (addend) {
+        if (!P.vec_ok || O.dtype != PSK_BF16 || out_desc.affine) return fail(e, PSK_E7001, "integer contraction: an addend needs a bf16 result in rows of 16-byte runs");
+        P.addend = addend;
+    }
     int32_t *colsum = nullptr;
     if (A.affine_zero != 0) {
         colsum = (int32_t *)psk_exec_alloc(e, (size_t)g.n * g.batch * 4);
@@ -549,11 +554,13 @@ int launch_i8(psk_exec *e, const GemmMap &g, const DevOperand &A, const DevOpera
     if (!e->i8_attr_set) {
         CUDA_TRY(e, cudaFuncSetAttribute(tci8::k_gemm_i8<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, tci8::Cfg<1>::SMEM_TOTAL));
         CUDA_TRY(e, cudaFuncSetAttribute(tci8::k_gemm_i8<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, tci8::Cfg<2>::SMEM_TOTAL));
+        CUDA_TRY(e, cudaFuncSetAttribute(tci8::k_gemm_i8<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tci8::Cfg<1>::SMEM_TOTAL));
         e->i8_attr_set = true;
     }
     const int64_t tiles = P.tiles_m * P.tiles_n * g.batch;
     const int grid = (int)std::min<int64_t>(tiles, e->sms);
-    if (mt_rows == 2) tci8::k_gemm_i8<2><<<grid, tci8::THREADS, tci8::Cfg<2>::SMEM_TOTAL, e->stream>>>(ma, mb, P);
+    if (addend) tci8::k_gemm_i8<1, true><<<grid, tci8::THREADS, tci8::Cfg<1>::SMEM_TOTAL, e->stream>>>(ma, mb, P);
+    else if (mt_rows == 2) tci8::k_gemm_i8<2><<<grid, tci8::THREADS, tci8::Cfg<2>::SMEM_TOTAL, e->stream>>>(ma, mb, P);
     else tci8::k_gemm_i8<1><<<grid, tci8::THREADS, tci8::Cfg<1>::SMEM_TOTAL, e->stream>>>(ma, mb, P);
     if (colsum) psk_exec_free(e, colsum); // handed out again only to later work of the same stream
     CUDA_TRY(e, cudaGetLastError());
@@ -983,7 +990,8 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
     bool any_affine = l->out.affine != 0;
     for (int i = 0; i < l->n_inputs; ++i) any_affine = any_affine || l->in[i].affine != 0;
     const bool affine_norm = l->op == PSK_OP_RMSNORM && l->out.affine != 0 && !l->in[0].affine && !l->in[1].affine && !l->in[2].affine; // the merged norm writing a `scaled` site
-    if (any_affine && !affine_norm && l->op != PSK_OP_FUSED && l->op != PSK_OP_CONTRACT && l->op != PSK_OP_CONVERT && l->op != PSK_OP_CONTRACT_ADD)
+    const bool affine_attn = l->op == PSK_OP_ATTENTION && l->out.affine != 0 && !l->in[0].affine && !l->in[1].affine && !l->in[2].affine && !l->in[3].affine && (l->n_inputs < 5 || !l->in[4].affine); // the weighted values into a `scaled` site
+    if (any_affine && !affine_norm && !affine_attn && l->op != PSK_OP_FUSED && l->op != PSK_OP_CONTRACT && l->op != PSK_OP_CONVERT && l->op != PSK_OP_CONTRACT_ADD)
         return fail(e, PSK_E7005, std::string(l->name ? l->name : "?") + ": values in an affine format are read and written by elementwise groups, contractions and conversions only");
     if (any_affine && l->op == PSK_OP_CONTRACT && !l->int_accum)
         return fail(e, PSK_E7005, std::string(l->name ? l->name : "?") + ": a contraction over affine values counts its sums in integers (product and accum i32) on this executor");
@@ -1405,12 +1413,13 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
         if ((no != 4 && no != 5) || L.n_inner != 1 || (L.n_in != 4 && L.n_in != 5)) { rc = fail(e, PSK_E7001, nm + ": q, k, v, the divisor and at most a mask over (batch, [groups,] heads, seq, hd | seq2)"); break; }
         const int ax_hd = no - 1, ax_seq = no - 2, ax_s2 = no, ax_b = 0, ax_g = 1, ax_p = no == 5 ? 2 : -1;
         const int64_t B = L.dims[ax_b], G = L.dims[ax_g], Pn = ax_p >= 0 ? L.dims[ax_p] : 1, T = L.dims[ax_seq], HD = L.dims[ax_hd];
+        const bool aff_out = l->out.affine != 0; // the result as one-byte codes of an affine format (the `scaled` site of the weighted values)
         if (T == 1 && L.n_in == 4) {
             // one query position against a cache of keys and values (a decode step): a stream of the cache, see psk_attn_step.cuh
             e->last_kernel = "k_attn_step";
             const int64_t T2 = L.dims[ax_s2];
             const DevOperand &Q = L.in[0], &K = L.in[1], &V = L.in[2], &O = L.out;
-            bool ok = HD == attn_step::HD && l->dtype == PSK_BF16 && l->out.dtype == PSK_BF16 && l->iparam[1] == PSK_BF16 && l->iparam[2] == PSK_BF16 && l->iparam[3] == PSK_BF16
+            bool ok = HD == attn_step::HD && l->dtype == PSK_BF16 && (aff_out ? (l->out.dtype == PSK_I8 || l->out.dtype == PSK_U8) : l->out.dtype == PSK_BF16) && l->iparam[1] == PSK_BF16 && l->iparam[2] == PSK_BF16 && l->iparam[3] == PSK_BF16
                 && T2 >= 1 && T2 <= 49152 && B * G * Pn <= 0x7fffffff && G <= 0x7fffffff && Pn <= 0x7fffffff;
             for (int i = 0; i < 3 && ok; ++i) ok = l->in[i].dtype == PSK_BF16 && L.in[i].stride[ax_hd] == 1 && ((uintptr_t)L.in[i].p % 8) == 0 && L.in[i].stride[ax_b] % 4 == 0 && L.in[i].stride[ax_g] % 4 == 0;
             ok = ok && O.stride[ax_hd] == 1 && K.stride[ax_s2] % 4 == 0 && V.stride[ax_s2] % 4 == 0 && Q.stride[ax_s2] == 0 && O.stride[ax_s2] == 0 && K.stride[ax_seq] == 0 && V.stride[ax_seq] == 0;
@@ -1425,6 +1434,7 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
             A.o_b = O.stride[ax_b]; A.o_g = O.stride[ax_g]; A.o_p = ax_p >= 0 ? O.stride[ax_p] : 0;
             A.G = (int32_t)G; A.Pn = (int32_t)Pn; A.len = (int32_t)T2;
             A.rt = L.in[3].p; A.rt_dtype = L.in[3].dtype;
+            A.aff_kind = l->out.affine; A.aff_zero = l->out.affine_zero; A.aff_scale = l->out.affine_scale;
             const size_t smem = (size_t)T2 * sizeof(float);
             if (smem > 48 * 1024 && !e->attn_step_attr_set) {
                 CUDA_TRY(e, cudaFuncSetAttribute(attn_step::k_attn_step, cudaFuncAttributeMaxDynamicSharedMemorySize, 49152 * (int)sizeof(float)));
@@ -1435,11 +1445,14 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
             e->kernels += 1;
             break;
         }
-        bool fits = HD == attn::HD && T == L.dims[ax_s2] && T % attn::BM == 0 && l->dtype == PSK_BF16 && l->out.dtype == PSK_BF16
+        // (codes come out of the one-pass kernel only: 16-byte stores of sixteen codes)
+        bool fits = HD == attn::HD && T == L.dims[ax_s2] && T % attn::BM == 0 && l->dtype == PSK_BF16
+            && (aff_out ? ((l->out.dtype == PSK_I8 || l->out.dtype == PSK_U8) && l->iparam[0] == 1) : l->out.dtype == PSK_BF16)
             && l->iparam[1] == PSK_BF16 && l->iparam[2] == PSK_BF16 && l->iparam[3] == PSK_BF16;
         for (int i = 0; i < 3 && fits; ++i) fits = l->in[i].dtype == PSK_BF16 && L.in[i].stride[ax_hd] == 1 && aligned16(L.in[i].p);
         const DevOperand &Q = L.in[0], &K = L.in[1], &V = L.in[2], &O = L.out;
-        fits = fits && O.stride[ax_hd] == 1 && aligned16(O.p) && O.stride[ax_seq] % 8 == 0 && O.stride[ax_b] % 8 == 0 && O.stride[ax_g] % 8 == 0;
+        const int64_t o_unit = aff_out ? 16 : 8; // elements of a 16-byte store
+        fits = fits && O.stride[ax_hd] == 1 && aligned16(O.p) && O.stride[ax_seq] % o_unit == 0 && O.stride[ax_b] % o_unit == 0 && O.stride[ax_g] % o_unit == 0;
         fits = fits && Q.stride[ax_s2] == 0 && K.stride[ax_seq] == 0 && V.stride[ax_seq] == 0 && O.stride[ax_s2] == 0;
         int64_t q_head = Q.stride[ax_g], o_head = O.stride[ax_g];
         if (ax_p >= 0) {
@@ -1469,6 +1482,7 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
         A.out = const_cast<void *>(O.p); A.o_b = O.stride[ax_b]; A.o_g = o_head; A.o_t = O.stride[ax_seq];
         A.rt = L.in[3].p; A.rt_dtype = L.in[3].dtype;
         A.status = e->status;
+        A.aff_kind = l->out.affine; A.aff_zero = l->out.affine_zero; A.aff_scale = l->out.affine_scale;
         if (!e->attn_attr_set) {
             CUDA_TRY(e, cudaFuncSetAttribute(attn::k_attn_fwd, cudaFuncAttributeMaxDynamicSharedMemorySize, attn::SMEM_TOTAL));
             CUDA_TRY(e, cudaFuncSetAttribute(attn::v2::k_attn_fwd2, cudaFuncAttributeMaxDynamicSharedMemorySize, attn::v2::SMEM_TOTAL2));
@@ -1560,12 +1574,30 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
     }
     case PSK_OP_CONTRACT_ADD: {
         const std::string nm = l->name ? l->name : "contract+add";
-        if (L.n_in != 3 || l->int_accum) { rc = fail(e, PSK_E7001, nm + ": two operands of a contraction and an addend"); break; }
+        if (L.n_in != 3) { rc = fail(e, PSK_E7001, nm + ": two operands of a contraction and an addend"); break; }
         DevLaunch L2 = L;
         L2.n_in = 2;
         GemmMap g;
         const bool mapped = map_gemm(L2, g);
         const DevOperand &A = L.in[0], &B = L.in[1], &X = L.in[2];
+        if (l->int_accum) {
+            // Integer sums (tcgen05 kind::i8), their rescaled product rounded to bf16, then the addend: both steps are
+            // exact per element whatever the order of the sums, so every order takes this path.
+            bool fits = mapped && e->encode && A.affine != 0 && !B.affine && B.dtype == PSK_I8 && B.scales && X.dtype == PSK_BF16 && !X.affine && !L.out.affine
+                && l->dtype == PSK_BF16 && l->out.dtype == PSK_BF16 && l->iparam[1] == PSK_BF16
+                && g.a_k == 1 && (g.b_k == 1 || g.b_n == 1) && g.k >= 16 && g.k <= 65536 && g.c_col_lo == 1 && g.m >= 1 && g.n >= 16
+                && aligned16(A.p) && aligned16(B.p) && aligned16(X.p);
+            for (int a = L.n_outer; fits && a < L.n_outer + L.n_inner; ++a) fits = B.sstride[a] == 0;
+            for (int a = 0; a < L.n_outer && fits; ++a) fits = L.dims[a] == 1 || X.stride[a] == L.out.stride[a];
+            if (!fits) { rc = fail(e, PSK_E7005, nm + ": the merged integer contraction and addition take an affine operand, integer weights, a bf16 addend laid out as the bf16 result"); break; }
+            if (g.m == 1) g.a_row = (g.k + 15) / 16 * 16;
+            const int r = launch_i8(e, g, A, B, L.out, l->out, L.ovf, false, X.p);
+            if (r == PSK_E7001) { rc = fail(e, PSK_E7005, nm + ": " + e->error); break; }
+            rc = r;
+            e->last_kernel = "k_gemm_i8";
+            e->last_flops = 2.0 * (double)g.m * (double)g.n * (double)g.k * (double)g.batch;
+            break;
+        }
         const bool b_int8 = B.dtype == PSK_I8 && B.scales, b_e4m3 = B.dtype == PSK_E4M3; // as in a plain contraction: read through a widened copy
         bool fits = mapped && device_order && e->encode && A.dtype == PSK_BF16 && (B.dtype == PSK_BF16 || b_int8 || b_e4m3) && X.dtype == PSK_BF16 && !any_affine
             && l->dtype == PSK_BF16 && l->out.dtype == PSK_BF16 && l->iparam[1] == PSK_BF16

@@ -69,6 +69,7 @@ struct Params {
     const float *col_scale;   // the weights' scales: one a column (and batch entry)
     int64_t col_scale_stride, col_scale_lo, col_scale_hi;
     const int32_t *colsum;    // sum_k w[k, col] per (batch entry, column), when a_zero != 0
+    const void *addend;       // a bf16 tensor laid out as the result, added to the rounded bf16 product (staged stores only)
     int guarded;
     int vec_ok;
     uint32_t *ovf;
@@ -85,6 +86,12 @@ PSK_DEV uint32_t instr_desc_i8(int a_unsigned, int b_n_major)
     d |= (uint32_t)(BN >> 3) << 17;
     d |= (uint32_t)(BM >> 4) << 24;
     return d;
+}
+
+// Two bf16 sums of a 32-bit word's halves, each rounded to nearest even.
+PSK_DEV uint32_t add_bf16x2(uint32_t a, uint32_t b)
+{
+    return pack_bf16x2_hw(__fadd_rn(bits_f32(a << 16), bits_f32(b << 16)), __fadd_rn(bits_f32(a & 0xffff0000u), bits_f32(b & 0xffff0000u)));
 }
 
 PSK_DEV void umma_i8(uint32_t tmem_c, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
@@ -190,7 +197,8 @@ PSK_DEV int64_t count_to_affine(int32_t n, double base, float s)
     return quotient_round_exact(n < 0, (u128_t)(n < 0 ? -(int64_t)n : (int64_t)n) * (u128_t)mb, eb, s);
 }
 
-template <int MT>
+// ADD: the instance that adds P.addend to a bf16 result (its own instance so that the plain one keeps its registers).
+template <int MT, bool ADD = false>
 __global__ void __launch_bounds__(THREADS, 1) k_gemm_i8(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ Params P)
 {
     constexpr int STAGES = Cfg<MT>::STAGES, A_BYTES = Cfg<MT>::A_BYTES, TILE_BYTES = Cfg<MT>::TILE_BYTES;
@@ -309,12 +317,37 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_i8(const __grid_constant__ 
         float *scale_area = reinterpret_cast<float *>(smem + TILE_BYTES + BAR_BYTES + STAGE_OUT);
         const bool staged = P.vec_ok && !P.out_affine && (P.out_dtype == PSK_BF16 || P.out_dtype == PSK_F32);
         const double sa = (double)P.a_scale;
+        // A tile's part of the addend, asked into the L2 a tile ahead: this lane's row, the 64 bytes of each of this
+        // warp's column groups. The loads that add it (below) then find it there.
+        auto prefetch_addend = [&](int64_t t) {
+            if (t >= total_tiles) return;
+            const int64_t b = t / tiles_per_batch, r = t % tiles_per_batch;
+            int64_t mt, nt;
+            tc::tile_of(r, P.tiles_m, P.tiles_n, P.panel, mt, nt);
+            const int64_t prow = mt * BM * MT + quad * 32 + lane, n0 = nt * BN;
+            if (prow >= P.m) return;
+            const uint32_t rcnt = (uint32_t)(P.c_row_lo_count < 0x7fffffffll ? P.c_row_lo_count : 0x7fffffffll);
+            const uint32_t ccnt = (uint32_t)(P.c_col_lo_count < 0x7fffffffll ? P.c_col_lo_count : 0x7fffffffll);
+            const uint32_t rq = (uint32_t)prow / rcnt;
+            const int64_t roff = (b % P.batch_lo) * P.c_lo + (b / P.batch_lo) * P.c_hi + (int64_t)rq * P.c_row_hi + (int64_t)((uint32_t)prow - rq * rcnt) * P.c_row_lo;
+#pragma unroll
+            for (int c0 = half_id * 32; c0 < BN; c0 += 64) {
+                const int64_t pcol = n0 + c0;
+                if (pcol < P.n) {
+                    const uint32_t cq = (uint32_t)pcol / ccnt;
+                    const uint16_t *pa = (const uint16_t *)P.addend + roff + (int64_t)cq * P.c_col_hi + (int64_t)((uint32_t)pcol - cq * ccnt);
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(pa));
+                }
+            }
+        };
+        if constexpr (ADD) prefetch_addend(blockIdx.x);
         for (int64_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
             const int64_t b = t / tiles_per_batch, r = t % tiles_per_batch;
             int64_t mt, nt;
             tc::tile_of(r, P.tiles_m, P.tiles_n, P.panel, mt, nt);
             const int64_t m0 = mt * BM * MT, n0 = nt * BN;
             const int64_t blo = b % P.batch_lo, bhi = b / P.batch_lo;
+            if constexpr (ADD) prefetch_addend(t + gridDim.x); // the next tile's, while this one is rescaled and stored
             ok = tc::mbar_wait(tfull0 + 8 * (MT == 2 ? 0u : acc), acc_phase, abort_flag, P.status, 0x74u);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
@@ -428,14 +461,44 @@ __global__ void __launch_bounds__(THREADS, 1) k_gemm_i8(const __grid_constant__ 
                         const int live = (int)(((P.n - col) >= 32 ? 32 : (P.n - col)) * eb / 16);
                         const int rows_a_pass = 32 / units;                      // rows one store instruction covers
                         const int unit = lane % units;
-                        for (int it = 0; it < units; ++it) {
-                            const int rr = it * rows_a_pass + lane / units;
-                            const int64_t rrow = row0 + rr;
-                            if (rrow < P.m && unit < live) {
-                                const uint32_t rq = (uint32_t)rrow / rcnt;
-                                const int64_t off = boff + (int64_t)rq * P.c_row_hi + (int64_t)((uint32_t)rrow - rq * rcnt) * P.c_row_lo + col_off;
-                                const uint4 w = stage_out[rr * 8 + (unit ^ (rr & 7))];
-                                *reinterpret_cast<uint4 *>((uint8_t *)P.c + off * eb + unit * 16) = w;
+                        if constexpr (ADD) {
+                            // bf16 (units = 4): the addend plus the rounded product, rounded again. The addend's lines were
+                            // asked into the L2 a tile ahead; the four passes' loads go out together. (Loading them
+                            // earlier, at the group's start or before its second half, made the compiler spill around
+                            // them and was slower.)
+                            int64_t offs[4];
+                            uint4 ad[4];
+#pragma unroll
+                            for (int it = 0; it < 4; ++it) {
+                                const int rr = it * 8 + lane / 4;
+                                const int64_t rrow = row0 + rr;
+                                offs[it] = -1;
+                                ad[it] = make_uint4(0u, 0u, 0u, 0u);
+                                if (rrow < P.m && unit < live) {
+                                    const uint32_t rq = (uint32_t)rrow / rcnt;
+                                    offs[it] = boff + (int64_t)rq * P.c_row_hi + (int64_t)((uint32_t)rrow - rq * rcnt) * P.c_row_lo + col_off + unit * 8;
+                                    ad[it] = *reinterpret_cast<const uint4 *>((const uint16_t *)P.addend + offs[it]);
+                                }
+                            }
+#pragma unroll
+                            for (int it = 0; it < 4; ++it) {
+                                const int rr = it * 8 + lane / 4;
+                                if (offs[it] >= 0) {
+                                    uint4 w = stage_out[rr * 8 + (unit ^ (rr & 7))];
+                                    w.x = add_bf16x2(ad[it].x, w.x); w.y = add_bf16x2(ad[it].y, w.y); w.z = add_bf16x2(ad[it].z, w.z); w.w = add_bf16x2(ad[it].w, w.w);
+                                    *reinterpret_cast<uint4 *>((uint16_t *)P.c + offs[it]) = w;
+                                }
+                            }
+                        } else {
+                            for (int it = 0; it < units; ++it) {
+                                const int rr = it * rows_a_pass + lane / units;
+                                const int64_t rrow = row0 + rr;
+                                if (rrow < P.m && unit < live) {
+                                    const uint32_t rq = (uint32_t)rrow / rcnt;
+                                    const int64_t off = boff + (int64_t)rq * P.c_row_hi + (int64_t)((uint32_t)rrow - rq * rcnt) * P.c_row_lo + col_off;
+                                    const uint4 w = stage_out[rr * 8 + (unit ^ (rr & 7))];
+                                    *reinterpret_cast<uint4 *>((uint8_t *)P.c + off * eb + unit * 16) = w;
+                                }
                             }
                         }
                         __syncwarp();

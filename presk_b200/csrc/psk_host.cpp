@@ -727,7 +727,7 @@ struct psk_host {
             for (size_t i = 0; i < output.size(); ++i) name += (i ? ", " : "") + output[i];
             name += "]";
         }
-        if (addend && rz.merged_launches && !calibrating && !out.affine && !addend->affine && !rz.scaled.count(add_site) && !l.int_accum) {
+        if (addend && rz.merged_launches && !calibrating && !out.affine && !addend->affine && !rz.scaled.count(add_site)) {
             std::vector<int> amap;
             if (align(addend->axes, out_axes, amap) && addend->axes.size() == out_axes.size()) {
                 psk_launch m = l;

@@ -48,27 +48,32 @@ def realization(paths, order, weights="bf16"):
 # W8A8: the activations that feed the projections stored as i8 codes with a static scale (`scaled` sites: the norm's
 # result and silu(gate)·up), every projection's weights and the head's as int8 (`quant`), and those contractions'
 # products and sums counted in i32 (`product`, `accum`), as examples/tests/formats/w8a8.json declares them for a Dense
-# layer. The attention's result stays bf16, so the out-projection reads it against int8 weights widened exactly.
+# layer. In the first form the attention's result stays bf16, so the out-projection reads it against int8 weights
+# widened exactly; with `attn_out` the weighted values are a scaled site too and the out-projection counts in i32 like
+# the other six.
 W8A8_SCALED_SITES = ("RMSNorm.apply/%10", "SwiGLU.apply/%7")
 W8A8_INT_SUMS = ("Attention.apply/%7", "Attention.apply/%11", "Attention.apply/%14", "Dense.apply/%3", "Llama.apply/%11")
+W8A8_ATTN_OUT_SITE, W8A8_ATTN_OUT_SUMS = "Attention.apply/%22", "Attention.apply/%26"
 W8A8_QUANTISED = QUANTISED + ("head",)
 
 
-def w8a8_realization(paths, order, scales):
-    """`scales`: {site: scale} of W8A8_SCALED_SITES (from an envelope: largest magnitude / 127)."""
+def w8a8_realization(paths, order, scales, attn_out=False):
+    """`scales`: {site: scale} of the scaled sites (from an envelope: largest magnitude / 127)."""
+    scaled = W8A8_SCALED_SITES + ((W8A8_ATTN_OUT_SITE,) if attn_out else ())
+    sums = W8A8_INT_SUMS + ((W8A8_ATTN_OUT_SUMS,) if attn_out else ())
     rz = {"default": "bf16", "order": order, "storage": dict(F32_SITES)}
     rz["params"] = {p: "bf16" for p in paths if p not in W8A8_QUANTISED}
     rz["quant"] = {p: {"bits": 8, "over": -2} for p in W8A8_QUANTISED}
-    rz["scaled"] = {site: {"int": "i8/sat", "scale": float(np.float32(scales[site])), "zero": 0} for site in W8A8_SCALED_SITES}
-    rz["product"] = {site: "i32" for site in W8A8_INT_SUMS}
-    rz["accum"] = {site: "i32" for site in W8A8_INT_SUMS}
+    rz["scaled"] = {site: {"int": "i8/sat", "scale": float(np.float32(scales[site])), "zero": 0} for site in scaled}
+    rz["product"] = {site: "i32" for site in sums}
+    rz["accum"] = {site: "i32" for site in sums}
     return rz
 
 
 def w8a8_scales(envelope):
     """A static scale a scaled site from a calibration's envelope {site: (max |x|, ...)}: absmax / 127, as `presk
     scales` computes an absmax scheme's (presk-rt/src/lib.rs:287-360)."""
-    return {site: float(np.float32(envelope[site][0]) / np.float32(127.0)) for site in W8A8_SCALED_SITES}
+    return {site: float(np.float32(envelope[site][0]) / np.float32(127.0)) for site in W8A8_SCALED_SITES + (W8A8_ATTN_OUT_SITE,)}
 
 
 BENCH_ORDER = {"kind": "device", "attention": "blockwise", "launches": "merged"}
@@ -94,7 +99,7 @@ def llama_width_parity(cuda_executor, oracle, B=1, T=256, weights="bf16", consts
     out = {"shape": f"llama L=1 V={c['V']} D={c['D']} H={c['H']} G={c['G']} FF={c['FF']} B={B} T={T}, weights {weights}"}
     res = {}
     make = lambda how: realization(p, how, weights)
-    if weights == "w8a8":
+    if weights in ("w8a8", "w8a8_attn_out"):
         # static scales from a calibration of the bf16 realization on the CUDA executor; both sides then run the same
         # W8A8 realization
         hc = give(Host(cuda_executor, realization(p, {"kind": "device"})).prepare("llama", **c), p)
@@ -102,7 +107,7 @@ def llama_width_parity(cuda_executor, oracle, B=1, T=256, weights="bf16", consts
         hc.call("apply", [ids], (B, T, c["V"]))
         scales = w8a8_scales(hc.envelope())
         hc.close()
-        make = lambda how: w8a8_realization(p, how, scales)
+        make = lambda how: w8a8_realization(p, how, scales, attn_out=weights == "w8a8_attn_out")
     for name, ex, how in (("gpu", cuda_executor, order or BENCH_ORDER), ("oracle", oracle.vtable(), ORACLE_ORDER)):
         h = give(Host(ex, make(how)).prepare("llama", **c), p)
         if name == "gpu":

@@ -467,3 +467,63 @@ def test_integer_sums_on_the_tensor_cores_are_exact(cuda, oracle, i8_tile_form, 
             acc = ((acc + 2**31) % 2**32) - 2**31
             ref = acc.astype(np.float64) * float(s_a) * sw.astype(np.float64)[None, :]
             np.testing.assert_allclose(got.view(np.float32).reshape(m, n), ref, rtol=1e-6)
+
+
+@pytest.mark.parametrize("m,k,n,b_n_major,inner", [(300, 576, 288, True, None), (512, 4096, 256, False, None), (129, 384, 64, True, (2, 3, 64)), (1, 1024, 512, True, None)])
+def test_integer_sums_take_a_residual_along(cuda, oracle, m, k, n, b_n_major, inner):
+    """PSK_OP_CONTRACT_ADD with `product: i32, accum: i32`: the W8A8 projections that end in a residual addition
+    (out-projection, down-projection), as one launch of the integer tensor-core kernel. The sums are exact, their
+    rescaled value is rounded once to bf16, and the addition rounds once more, so every bit is the oracle's two
+    launches' under any order; ragged rows and columns, both layouts of the weights, a summed axis given as three
+    (groups, per, hd), one row. A result whose rows are not made of 16-byte runs is refused (E7005) and left to the
+    caller's two launches."""
+    from presk_b200 import PreskError, abi, launch_desc
+    rng = np.random.default_rng(m + k + n)
+    for kind, zero in ((1, 0), (2, 77)):
+        lo, hi = (0, 255) if kind == 2 else (-128, 127)
+        codes = rng.integers(lo, hi + 1, size=(m, k)).astype(np.uint8 if kind == 2 else np.int8)
+        qw = rng.integers(-127, 128, size=(k, n) if b_n_major else (n, k)).astype(np.int8)
+        s_a = np.float32(rng.uniform(1.0, 2.0) * 2.0**-6)
+        sw = (rng.uniform(1.0, 2.0, size=n) * 2.0**-9).astype(np.float32)
+        x = oracle.convert((rng.standard_normal((m, n)) * 4.0).astype(np.float32), abi.BF16)
+
+        def launch(n_cols):
+            dims_in = list(inner) if inner else [k]
+            l = launch_desc(abi.OP_CONTRACT_ADD, abi.BF16, [m, n_cols], dims_in, order=abi.ORDER_DEVICE, name=b"dot+add")
+            l.n_inputs, l.int_accum = 3, 1
+            l.iparam[1] = abi.BF16
+            l.inputs[0].dtype = abi.U8 if kind == 2 else abi.I8
+            l.inputs[0].affine, l.inputs[0].affine_zero, l.inputs[0].affine_scale = kind, zero, float(s_a)
+            l.inputs[0].stride[0], l.inputs[0].numel = k, m * k
+            l.inputs[1].dtype, l.inputs[1].numel = abi.I8, k * n
+            l.inputs[1].stride[1] = 1 if b_n_major else k
+            run = 1  # the summed axes, innermost last, walk k as one
+            for a in range(len(dims_in) - 1, -1, -1):
+                l.inputs[0].stride[2 + a] = run
+                l.inputs[1].stride[2 + a] = run * (n if b_n_major else 1)
+                run *= dims_in[a]
+            l.inputs[1].scale_stride[1] = 1
+            l.inputs[2].dtype, l.inputs[2].numel, l.inputs[2].stride[0], l.inputs[2].stride[1] = abi.BF16, m * n, n, 1
+            l.out.dtype, l.out.stride[0], l.out.stride[1], l.out.numel = abi.BF16, n, 1, m * n
+            return l
+
+        l = launch(n)
+        dev = [cuda.upload(codes), cuda.upload(qw), cuda.upload(x)]
+        pout, psw = cuda.alloc(m * n * 2), cuda.upload(sw)
+        cuda.set_profiling(True)
+        cuda.run(l, dev + [pout, psw])
+        cuda.sync()
+        kinds = [rec[0] for rec in cuda.profile()]
+        cuda.set_profiling(False)
+        assert kinds[-1] == "k_gemm_i8", kinds
+        got = cuda.download(pout, m * n * 2)
+        want = np.zeros(m * n * 2, np.uint8)
+        oracle.run(l, [codes, qw, np.ascontiguousarray(x), want, sw])
+        bad = np.nonzero(got.view(np.uint16) != want.view(np.uint16))[0]
+        assert bad.size == 0, (kind, zero, bad.size, bad[:4])
+        assert np.any(want)
+        if n > 20:  # the first 20 columns of the same buffers: rows of 40 bytes, no 16-byte runs
+            with pytest.raises(PreskError, match="E7005"):
+                cuda.run(launch(20), dev + [pout, psw])
+        for p in dev + [pout, psw]:
+            cuda.free(p)

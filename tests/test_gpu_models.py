@@ -607,3 +607,45 @@ def test_gap_of_a_candidate_realization_measured_on_the_device(cuda):
     assert gap == np.abs(a - b).max() and mx == np.abs(a).max()
     assert 0 < gap <= 3e-2 * mx  # the bf16 candidate sits inside a 3e-2 budget, as against the exact evaluator
     cuda.free(pid)
+
+
+def test_w8a8_llama_with_the_attention_result_in_codes(cuda, oracle):
+    """The fuller W8A8 form (tests/headline.py, `attn_out`): the weighted values are a scaled site too, written by the
+    one-pass attention kernel as i8 codes, and the out-projection counts its sums in i32 like the other six; it and
+    the down-projection take their residual along in the integer kernel's epilogue. Against the oracle's sequential
+    run of the same realization, within the W8A8 tolerance (one more i8 site than the other form). The site is written
+    by the fused attention only: without it the contraction that would store the codes sums in floats, which this
+    executor refuses (E7005) rather than run elsewhere."""
+    import headline
+    from presk_b200 import PreskError
+    c = dict(V=512, D=256, H=2, G=2, FF=512, L=2)
+    p = models.llama_params(c)
+    ids = np.random.default_rng(15).integers(0, c["V"], size=(2, 128), dtype=np.int64)
+    h = models.give(Host(cuda, headline.realization(p, {"kind": "device"})).prepare("llama", **c), p)
+    h.set_calibrating(True)
+    h.call("apply", [ids], (2, 128, c["V"]))
+    scales = headline.w8a8_scales(h.envelope())
+    h.close()
+    assert scales[headline.W8A8_ATTN_OUT_SITE] > 0
+
+    def run(ex, order):
+        hw = models.give(Host(ex, headline.w8a8_realization(p, order, scales, attn_out=True)).prepare("llama", **c), p)
+        hw.set_logging(True)
+        try:
+            return hw.call("apply", [ids], (2, 128, c["V"])), hw.launch_log()
+        finally:
+            hw.close()
+
+    want, _ = run(oracle.vtable(), {"kind": "sequential"})
+    cuda.set_profiling(True)
+    cuda.profile()
+    got, log = run(cuda, {"kind": "device", "attention": "online", "launches": "merged"})
+    prof = [rec[0] for rec in cuda.profile()]
+    cuda.set_profiling(False)
+    assert log.count("attention[online]") == c["L"] and sum(1 for n in log if n.endswith("+add")) == 2 * c["L"], log
+    assert prof.count("k_gemm_i8") == 7 * c["L"] + 1 and prof.count("k_attn_fwd3") == c["L"], prof
+    assert np.isfinite(got).all()
+    assert np.abs(got - want).max() <= 2.0**-3.5 * np.abs(want).max(), (np.abs(got - want).max(), np.abs(want).max())
+    assert np.abs(got - want).mean() <= 2.0**-6.5 * np.abs(want).max(), (np.abs(got - want).mean(), np.abs(want).max())
+    with pytest.raises(PreskError, match="E7005"):
+        run(cuda, {"kind": "device"})

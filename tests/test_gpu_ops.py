@@ -428,6 +428,83 @@ def test_one_position_against_a_cache(cuda, oracle, B, G, P, T2):
         assert np.array_equal(got.reshape(B, G, P, HD), np.broadcast_to(bf16_value(vbuf[:, 0])[:, :, None, :], (B, G, P, HD)))
 
 
+@pytest.mark.parametrize("B,G,P,T,T2,kind,zero,shrink", [(1, 2, 2, 256, 256, 1, 0, 1.0), (2, 1, 1, 384, 384, 2, 131, 0.6), (2, 2, 2, 1, 777, 1, 0, 1.0), (1, 1, 4, 1, 40, 2, 120, 0.5)])
+def test_attention_into_a_scaled_site(cuda, oracle, B, G, P, T, T2, kind, zero, shrink):
+    """The weighted values stored as one-byte codes of an affine format (a `scaled` site: the W8A8 out-projection's
+    operand): the one-pass kernel over a window (causal) and the decode step's kernel over a cache, each writing
+    clamp(rne(x / s) + z) of its binary32 result x as the oracle's last launch stores its sum (the one-pass kernel
+    takes the quotient by a reciprocal, a few binary32 units off: inside its tolerance). `shrink` < 1 makes
+    the scale too small for the largest values, so that codes saturate at both ends. Stated against the exact
+    attention in f64: a decoded code is within half a step plus the kernel's own distance (2^-7 of the scale, as for
+    the bf16 result), or saturated where the exact value is past the format's end; and against the oracle's codes,
+    which differ by what its bf16 roundings of the scores move a value."""
+    HD = 128
+    rng = np.random.default_rng(T * 31 + T2 + kind)
+    step = T == 1
+    q = bf16_of(oracle, rng.standard_normal((B, G, P, T, HD)) * 1.5)
+    k = bf16_of(oracle, rng.standard_normal((B, G, T2, HD)) * 1.5)
+    v = bf16_of(oracle, rng.standard_normal((B, T2, G, HD)))
+    rt = bf16_of(oracle, np.array(np.sqrt(np.float32(HD)), np.float32).reshape(()))
+    qf, kf, vf = bf16_value(q).astype(np.float64), bf16_value(k).astype(np.float64), bf16_value(v).astype(np.float64)
+    sc = np.einsum("bgpsh,bgth->bgpst", qf, kf) / np.sqrt(HD)
+    if not step:
+        sc = np.where(np.tril(np.ones((T, T), bool)), sc, -np.inf)
+    a = np.exp(sc - sc.max(-1, keepdims=True))
+    a /= a.sum(-1, keepdims=True)
+    exact = np.einsum("bgpst,btgh->bsgph", a, vf).reshape(-1)
+    lo, hi = (0, 255) if kind == 2 else (-128, 127)
+    scale = np.float32(np.abs(exact).max() / 127.0 * shrink)
+    l = launch_desc(abi.OP_ATTENTION, abi.BF16, [B, G, P, T, HD], [T2], order=abi.ORDER_DEVICE, name=b"attention[online]")
+    l.n_inputs = 4 if step else 5
+    l.masked = 0 if step else 1
+    l.iparam[0] = 1
+    l.iparam[1] = l.iparam[2] = l.iparam[3] = abi.BF16
+    set_operand(l.inputs[0], abi.BF16, [B, G, P, T, HD], [0, 1, 2, 3, 4])
+    set_operand(l.inputs[1], abi.BF16, [B, G, T2, HD], [0, 1, 5, 4])
+    set_operand(l.inputs[2], abi.BF16, [B, T2, G, HD], [0, 5, 1, 4])
+    set_operand(l.inputs[3], abi.BF16, [], [])
+    set_operand(l.out, abi.U8 if kind == 2 else abi.I8, [B, T, G, P, HD], [0, 3, 1, 2, 4])
+    l.out.affine, l.out.affine_zero, l.out.affine_scale = kind, zero, float(scale)
+    host_in = [q, k, v, rt]
+    dev = [cuda.upload(x) for x in host_in]
+    if not step:
+        set_operand(l.inputs[4], abi.I64, [T, T], [3, 5], is_index=True)
+        mask_dev = cuda.alloc(T * T * 8)
+        m = launch_desc(abi.OP_IOTA, abi.BF16, [T, T], name=b"causal_mask seq")
+        m.kind = abi.IOTA_CAUSAL
+        set_operand(m.out, abi.I64, [T, T], [0, 1], is_index=True)
+        cuda.run(m, [mask_dev])
+        dev.append(mask_dev)
+        host_in.append(np.tril(np.ones((T, T), np.int64)))
+    out_bytes = B * T * G * P * HD
+    pout = cuda.alloc(out_bytes)
+    cuda.set_profiling(True)
+    cuda.run(l, dev + [pout])
+    cuda.sync()
+    assert [rec[0] for rec in cuda.profile()] == ["k_attn_step" if step else "k_attn_fwd3"]
+    cuda.set_profiling(False)
+    code_type = np.uint8 if kind == 2 else np.int8
+    got = cuda.download(pout, out_bytes).view(code_type).astype(np.int64)
+    for p_ in dev + [pout]:
+        cuda.free(p_)
+    want_b = np.zeros(out_bytes, np.uint8)
+    oracle.run(l, [np.ascontiguousarray(x) for x in host_in] + [want_b])
+    want = want_b.view(code_type).astype(np.int64)
+    s64 = float(scale)
+    slack = 2.0**-7 * np.abs(exact).max()
+    ideal = exact / s64 + zero  # the exact value on the codes' axis
+    inside = (ideal > lo) & (ideal < hi)
+    assert np.all(np.abs(got - ideal)[inside] <= 0.5 + slack / s64 + 1e-6), np.abs(got - ideal)[inside].max()
+    assert np.all(got[ideal >= hi + 0.5 + slack / s64] == hi) and np.all(got[ideal <= lo - 0.5 - slack / s64] == lo)
+    if shrink < 1.0:
+        assert (got == hi).any() and (got == lo).any()
+    oracle_off = np.abs(np.clip(ideal, lo, hi) - want).max()  # the four launches' own distance, in steps
+    diff = np.abs(got - want)
+    assert diff.max() <= oracle_off + 0.5 + slack / s64 + 1e-6, (diff.max(), oracle_off)
+    assert diff.mean() <= 0.6, diff.mean()
+    assert (diff == 0).mean() >= (0.9 if step else 0.4), (diff == 0).mean()  # (the step's kernel keeps the launches' roundings)
+
+
 def test_blockwise_attention_is_refused_where_it_does_not_apply(cuda):
     """Under the sequential order, or with a head dimension other than 128, the launch is refused with
     E7005 and nothing runs: the host then keeps the four launches apart."""

@@ -283,3 +283,16 @@ def test_w8a8_llama_merged_launches_keep_every_bit(oracle):
     # against the bf16 realization: the quantisation's error, a few percent of the logits' scale
     ref = models.give(Host(oracle.vtable(), headline.realization(p, {"kind": "sequential"})).prepare("llama", **c), p).call("apply", [ids], (2, 16, c["V"]))
     assert np.abs(outs[0] - ref).max() <= 0.1 * np.abs(ref).max()
+    # The fuller form: the weighted values a scaled site too, the out-projection's sums in i32. Merged, the
+    # out-projection and the down-projection each take their residual along (one launch with the integer sums), and
+    # the fused attention writes the codes: the same bits as the launch list.
+    outs2, logs2 = [], []
+    for order in ({"kind": "device"}, {"kind": "device", "launches": "merged", "attention": "blockwise"}):
+        hw = models.give(Host(oracle.vtable(), headline.w8a8_realization(p, order, scales, attn_out=True)).prepare("llama", **c), p)
+        hw.set_logging(True)
+        outs2.append(hw.call("apply", [ids], (2, 16, c["V"])))
+        logs2.append(hw.launch_log())
+    assert np.array_equal(outs2[0].view(np.uint32), outs2[1].view(np.uint32))
+    assert sum(1 for n in logs2[1] if n.endswith("+add")) == 2 * c["L"] and logs2[1].count("attention[blockwise]") == c["L"]
+    assert not np.array_equal(outs2[0], outs[1]) # (another realization: the out-projection's operand is rounded to codes)
+    assert np.abs(outs2[0] - ref).max() <= 0.1 * np.abs(ref).max()
