@@ -392,14 +392,20 @@ def microbench(args):
         b = ex.upload(rng.integers(-127, 128, size=(k, n), dtype=np.int8))
         sw = ex.upload((rng.uniform(1.0, 2.0, size=n) * 2.0 ** -8).astype(np.float32))
         c = ex.alloc(m * n * 2)
-        l = launch_desc(abi.OP_CONTRACT, abi.BF16, [m, n], [k], order=abi.ORDER_DEVICE, name=b"dot")
-        l.n_inputs, l.int_accum = 2, 1
+        add = len(dims) > 4 and dims[4] == 1  # 5th number 1: a bf16 residual [m, n] added in the kernel's epilogue (PSK_OP_CONTRACT_ADD)
+        l = launch_desc(abi.OP_CONTRACT_ADD if add else abi.OP_CONTRACT, abi.BF16, [m, n], [k], order=abi.ORDER_DEVICE, name=b"dot+add" if add else b"dot")
+        l.n_inputs, l.int_accum = 3 if add else 2, 1
+        l.iparam[1] = abi.BF16
         l.inputs[0].dtype, l.inputs[0].affine, l.inputs[0].affine_zero, l.inputs[0].affine_scale = abi.I8, 1, int(dims[3]) if len(dims) > 3 else 0, 0.03125
         l.inputs[0].stride[0], l.inputs[0].stride[2], l.inputs[0].numel = k, 1, m * k
         l.inputs[1].dtype, l.inputs[1].stride[1], l.inputs[1].stride[2], l.inputs[1].numel = abi.I8, 1, n, k * n
         l.inputs[1].scale_stride[1] = 1
         l.out.dtype, l.out.stride[0], l.out.stride[1], l.out.numel = abi.BF16, n, 1, m * n
-        ms = timed(lambda: ex.run(l, [a, b, c, sw]), args.steps)
+        table = [a, b, c, sw]
+        if add:
+            l.inputs[2].dtype, l.inputs[2].stride[0], l.inputs[2].stride[1], l.inputs[2].numel = abi.BF16, n, 1, m * n
+            table = [a, b, ex.upload(bf16((m, n))), c, sw]
+        ms = timed(lambda: ex.run(l, table), args.steps)
         print(json.dumps({"micro": "gemm_i8", "shape": dims, "ms": ms, "TOP/s": 2.0 * m * n * k / ms / 1e9}))
     elif args.micro == "contract":
         # x[m, k] · w[k, n] in bf16 as a contraction launch (what a model's projection issues): with a few rows the
@@ -467,6 +473,8 @@ def microbench(args):
             for a, x in enumerate(st):
                 o.stride[a] = x
         l.inputs[3].dtype, l.inputs[3].numel = abi.BF16, 1
+        if len(dims) > 4 and dims[4] == 1:  # 5th number 1: the result as i8 codes of a scaled site (the one-pass kernel only)
+            l.out.dtype, l.out.affine, l.out.affine_zero, l.out.affine_scale = abi.I8, 1, 0, 0.02
         l.inputs[4].dtype, l.inputs[4].is_index, l.inputs[4].stride[2], l.inputs[4].stride[4], l.inputs[4].numel = abi.I64, 1, t, 1, t * t
         ms = timed(lambda: ex.run(l, [q, k, v, rt, mask, out]), args.steps)
         nqb = t // 128
