@@ -993,7 +993,9 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
     const bool affine_attn = l->op == PSK_OP_ATTENTION && l->out.affine != 0 && !l->in[0].affine && !l->in[1].affine && !l->in[2].affine && !l->in[3].affine && (l->n_inputs < 5 || !l->in[4].affine); // the weighted values into a `scaled` site
     if (any_affine && !affine_norm && !affine_attn && l->op != PSK_OP_FUSED && l->op != PSK_OP_CONTRACT && l->op != PSK_OP_CONVERT && l->op != PSK_OP_CONTRACT_ADD)
         return fail(e, PSK_E7005, std::string(l->name ? l->name : "?") + ": values in an affine format are read and written by elementwise groups, contractions and conversions only");
-    if (any_affine && l->op == PSK_OP_CONTRACT && !l->int_accum)
+    bool affine_in = false;
+    for (int i = 0; i < l->n_inputs; ++i) affine_in = affine_in || l->in[i].affine != 0;
+    if (affine_in && l->op == PSK_OP_CONTRACT && !l->int_accum)
         return fail(e, PSK_E7005, std::string(l->name ? l->name : "?") + ": a contraction over affine values counts its sums in integers (product and accum i32) on this executor");
     cudaEvent_t pa = nullptr, pb = nullptr;
     if (e->profiling) {
@@ -1180,6 +1182,15 @@ int psk_exec_run(psk_exec *e, const psk_launch *l, void *const *table)
             }
             k_contract_int<<<grid_for(e, L.total, 128, 16), 128, 0, e->stream>>>(L);
             e->last_kernel = "k_contract_int";
+            e->last_flops = 2.0 * (double)L.total * (double)L.inner;
+            e->kernels += 1;
+            break;
+        }
+        if (l->out.affine) {
+            // Float sums stored into a `scaled` site (the attention's weighted values when its launches run apart):
+            // the nest in index order, every order's permitted choice, its binary32 sum stored as the site's code.
+            k_contract_generic<<<grid_for(e, L.total, 256, 8), 256, 0, e->stream>>>(L);
+            e->last_kernel = "k_contract_generic";
             e->last_flops = 2.0 * (double)L.total * (double)L.inner;
             e->kernels += 1;
             break;

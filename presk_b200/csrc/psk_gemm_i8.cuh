@@ -21,6 +21,9 @@
 //     128-bit routine of k_contract_int decides; so every stored code is the exact routine's. Affine codes likewise
 //     (the quotient by the result's scale in binary64, the exact routine near a tie); binary16 and e8m15 results
 //     always take the exact routine.
+//   * A residual (PSK_OP_CONTRACT_ADD with integer sums, the ADD instance): the bf16 result as above, then
+//     addend + result in binary32 rounded to bf16, element by element as the separate addition does, so the two
+//     launches' bits under every order.
 //
 // Shape of the kernel: psk_gemm_tc.cuh's 256 x 256 form. One persistent CTA an SM, 320 threads: warp 0 issues TMA
 // loads (A 256 rows x 128 bytes, B 256 columns x 128 bytes a stage, 128-byte swizzle, three stages, no multicast),

@@ -482,7 +482,7 @@ __global__ void __launch_bounds__(256) k_contract_generic(const __grid_constant_
                 acc = __fadd_rn(acc, prod);
             }
         }
-        ovf |= store_real(const_cast<void *>(L.out.p), L.out.dtype, ooff, acc);
+        ovf |= store_out(L.out, ooff, acc); // (a `scaled` site's codes too: exec.rs:758-782 stores any kernel's value through its output's format)
     }
     if (L.guarded && ovf) atomicOr(L.ovf, 1u);
 }

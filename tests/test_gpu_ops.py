@@ -269,6 +269,34 @@ def test_contraction_exact_generic_strides(cuda, oracle):
     assert np.array_equal(got, want)
 
 
+@pytest.mark.parametrize("order", [abi.ORDER_SEQUENTIAL, abi.ORDER_DEVICE])
+@pytest.mark.parametrize("dtype", [abi.BF16, abi.F32])
+def test_float_sums_into_a_scaled_site(cuda, oracle, dtype, order):
+    """A contraction that sums in floats and stores into a `scaled` site (exec.rs:758-782 stores any kernel's value
+    through its output's format): the binary32 sum of the index-order nest, stored as clamp(rne(x / s) + z). The
+    oracle's codes, every one, under both orders (the executor runs the index-order nest for it whatever the order);
+    i8 without and u8 with a zero point, a scale that saturates some of them, two summed axes."""
+    rng = np.random.default_rng(int(dtype) * 2 + int(order))
+    B, S, M, N = 3, 17, 40, 24
+    x = rng.standard_normal((B, S, 5, M // 5)).astype(np.float32)
+    w = rng.standard_normal((5, M // 5, N)).astype(np.float32)
+    if dtype == abi.BF16:
+        x, w = bf16_of(oracle, x), bf16_of(oracle, w)
+    for kind, zero, scale in ((1, 0, 0.11), (2, 131, 0.05), (1, -7, 0.02)):
+        l = launch_desc(abi.OP_CONTRACT, dtype, [B, S, N], [5, M // 5], order=order)
+        l.n_inputs = 2
+        set_operand(l.inputs[0], dtype, [B, S, 5, M // 5], [0, 1, 3, 4])
+        set_operand(l.inputs[1], dtype, [5, M // 5, N], [3, 4, 2])
+        set_operand(l.out, abi.U8 if kind == 2 else abi.I8, [B, S, N], [0, 1, 2])
+        l.out.affine, l.out.affine_zero, l.out.affine_scale = kind, zero, scale
+        got, want, _, _ = run_both(cuda, oracle, l, [x, w], B * S * N)
+        assert np.array_equal(got, want), (kind, zero, scale, np.nonzero(got != want)[0][:5])
+        codes = want.view(np.uint8 if kind == 2 else np.int8)
+        assert len(np.unique(codes)) > 20
+        if scale <= 0.05:
+            assert (codes == codes.max()).sum() > 1 and int(codes.max()) == (255 if kind == 2 else 127)
+
+
 def test_integer_sums_over_scaled_values_are_exact(cuda, oracle):
     """`product: i32, accum: i32`: affine activations times int8 weights summed in 32 bits that wrap,
     stored once from the exact value into f16, bf16, f32, e8m15 or an affine format: the bits of
