@@ -522,7 +522,8 @@ def microbench(args):
         ms = timed(lambda: ex.run(l, [x, root, gam, out]), args.steps)
         print(json.dumps({"micro": "norm", "shape": dims, "ms": ms, "GB/s": rows * n * 4 / ms / 1e6}))
     elif args.micro == "rmsnorm":
-        # the merged RMSNorm launch: x[rows, n] bf16, f32 statistics, gamma[n]; --shape rows,n
+        # the merged RMSNorm launch: x[rows, n] bf16, f32 statistics, gamma[n]; --shape rows,n[,s]: with a third
+        # number the result is a scaled site's i8 codes with the scale s / 1000
         rows, n = dims[:2]
         x, gam = ex.upload(bf16((rows, n))), ex.upload(bf16((n,)))
         eps = ex.upload(np.array([1e-5], np.float32))
@@ -534,8 +535,11 @@ def microbench(args):
             o.dtype, o.stride[0], o.stride[1], o.numel = abi.BF16, n, 1, rows * n
         l.inputs[1].dtype, l.inputs[1].numel = abi.F32, 1
         l.inputs[2].dtype, l.inputs[2].stride[1], l.inputs[2].numel = abi.BF16, 1, n
+        codes = len(dims) > 2 and dims[2] > 0
+        if codes:
+            l.out.dtype, l.out.affine, l.out.affine_zero, l.out.affine_scale = abi.I8, 1, 0, dims[2] / 1000.0
         ms = timed(lambda: ex.run(l, [x, eps, gam, out]), args.steps)
-        print(json.dumps({"micro": "rmsnorm", "shape": dims, "ms": ms, "GB/s": rows * n * 4 / ms / 1e6}))
+        print(json.dumps({"micro": "rmsnorm", "shape": dims, "ms": ms, "GB/s": rows * n * (3 if codes else 4) / ms / 1e6}))
     elif args.micro == "rope":
         # the merged rotation: x[rows, seq, 2, rot] bf16 with cos and sin over [seq, rot]; --shape rows,seq,rot
         rows, seq, rot = dims[:3]

@@ -569,19 +569,22 @@ __global__ void __launch_bounds__(256, AFF ? 3 : 4) k_rmsnorm_rows(const __grid_
     const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
     const float eps = load_real(P.eps, P.eps_dtype, 0); // widened exactly: the root's group computes in f32
     const float nf = (float)(double)P.n;
-    constexpr int G = AFF ? (NV < 2 ? NV : 2) : (NV < 4 ? NV : 4); // vectors loaded before any is used (the codes' arithmetic needs the registers)
+    // vectors loaded before any is used: in the second pass the codes' arithmetic needs the registers (one vector at a
+    // time there keeps the kernel free of spills); the first pass, which is the one that waits for memory, has room for eight
+    constexpr int G = AFF ? 1 : (NV < 4 ? NV : 4);
+    constexpr int G1 = AFF ? (NV < 8 ? NV : 8) : G;
     for (int64_t row = warp; row < P.rows; row += nwarps) {
         const uint16_t *xr = P.x + row * P.x_row + lane * 8;
         // pass 1: the sum of the rounded squares, vector by vector in index order. The row is not kept in
         // registers (that would leave one block an SM); the second pass finds it in the L1 or the L2.
         float acc = 0.0f;
 #pragma unroll 1
-        for (int j0 = 0; j0 < NV; j0 += G) {
-            uint4 v[G];
+        for (int j0 = 0; j0 < NV; j0 += G1) {
+            uint4 v[G1];
 #pragma unroll
-            for (int j = 0; j < G; ++j) v[j] = *reinterpret_cast<const uint4 *>(xr + (j0 + j) * 256);
+            for (int j = 0; j < G1; ++j) v[j] = *reinterpret_cast<const uint4 *>(xr + (j0 + j) * 256);
 #pragma unroll
-            for (int j = 0; j < G; ++j) {
+            for (int j = 0; j < G1; ++j) {
                 const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {

@@ -651,3 +651,28 @@ def test_w8a8_llama_with_the_attention_result_in_codes(cuda, oracle):
     plain, _ = run(cuda, {"kind": "device"})
     assert np.abs(plain - want).max() <= 2.0**-3.5 * np.abs(want).max()
     assert np.abs(plain - want).mean() <= 2.0**-6.5 * np.abs(want).max()
+
+
+def test_w8a8_merged_launches_keep_every_bit_at_the_7b_width(cuda):
+    """The kernels that write a scaled site's codes themselves (the merged norm over rows of 4096 elements, sixteen
+    vectors a lane, and the silu-times-up group) against the reference's launch list on this executor, one layer of
+    the 7B model's width: the same logits, bit for bit."""
+    import headline
+    c = dict(V=256, D=4096, H=32, G=32, FF=512, L=1)
+    p = models.llama_params(c)
+    ids = np.random.default_rng(16).integers(0, c["V"], size=(1, 128), dtype=np.int64)
+    h = models.give(Host(cuda, headline.realization(p, {"kind": "device"})).prepare("llama", **c), p)
+    h.set_calibrating(True)
+    h.call("apply", [ids], (1, 128, c["V"]))
+    scales = headline.w8a8_scales(h.envelope())
+    h.close()
+    outs = []
+    for order in ({"kind": "device"}, {"kind": "device", "launches": "merged"}):
+        hw = models.give(Host(cuda, headline.w8a8_realization(p, order, scales)).prepare("llama", **c), p)
+        hw.set_logging(True)
+        outs.append(hw.call("apply", [ids], (1, 128, c["V"])))
+        log = hw.launch_log()
+        hw.close()
+    assert log.count("rmsnorm[merged]") == 2 * c["L"] + 1
+    assert np.isfinite(outs[0]).all() and np.abs(outs[0]).max() > 0
+    assert_same_bits(outs[1], outs[0])
