@@ -39,6 +39,52 @@ def test_affine_store_of_reals(oracle):
     assert oracle.lib.psk_o_affine_code(float("-inf"), 1, 0.5, 7) == -128
 
 
+def test_float_sums_stored_into_a_scaled_site(oracle):
+    """exec.rs:758-782 stores any kernel's value through its output's format: a contraction that sums in f32 and
+    writes a `scaled` site stores clamp(rne(acc / s) + z) of its binary32 sum. The sum is taken from the same
+    contraction with an f32 result; the code expected of it is exact arithmetic's (fractions), both saturated ends
+    of both formats among them. Likewise a reduction into a scaled site."""
+    from presk_b200 import launch_desc
+    rng = np.random.default_rng(11)
+    m, k, n = 9, 33, 14
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    w = rng.standard_normal((k, n)).astype(np.float32)
+
+    def contract(out_dtype, affine=None):
+        l = launch_desc(abi.OP_CONTRACT, abi.F32, [m, n], [k])
+        l.n_inputs = 2
+        l.inputs[0].dtype, l.inputs[0].numel, l.inputs[0].stride[0], l.inputs[0].stride[2] = abi.F32, m * k, k, 1
+        l.inputs[1].dtype, l.inputs[1].numel, l.inputs[1].stride[1], l.inputs[1].stride[2] = abi.F32, k * n, 1, n
+        l.out.dtype, l.out.numel, l.out.stride[0], l.out.stride[1] = out_dtype, m * n, n, 1
+        if affine:
+            l.out.affine, l.out.affine_zero, l.out.affine_scale = affine
+        return l
+
+    acc = np.zeros(m * n, np.float32)
+    oracle.run(contract(abi.F32), [x, w, acc.view(np.uint8)])
+    np.testing.assert_allclose(acc.reshape(m, n), x.astype(np.float64) @ w.astype(np.float64), rtol=0, atol=1e-4)
+    seen = set()
+    for kind, zero, scale in ((1, 0, 0.05), (2, 131, 0.05), (1, -7, 0.5), (2, 0, 0.02)):
+        codes = np.full(m * n, 0xA5, np.uint8)
+        oracle.run(contract(abi.U8 if kind == 2 else abi.I8, (kind, zero, scale)), [x, w, codes])
+        got = codes.view(np.uint8 if kind == 2 else np.int8).astype(np.int64)
+        want = np.array([exact.affine_code(exact.Fraction(float(a)), kind, np.float32(scale), zero) for a in acc])
+        assert np.array_equal(got, want), (kind, zero, scale, np.nonzero(got != want)[0][:5])
+        seen |= set(got.tolist())
+    assert {-128, 127, 0, 255} <= seen  # both formats saturated at both ends
+    # a reduction (sum over the last axis) into a scaled site
+    r = launch_desc(abi.OP_REDUCE, abi.F32, [m], [k])
+    r.n_inputs, r.kind = 1, abi.REDUCE_SUM
+    r.inputs[0].dtype, r.inputs[0].numel, r.inputs[0].stride[0], r.inputs[0].stride[1] = abi.F32, m * k, k, 1
+    r.out.dtype, r.out.numel, r.out.stride[0] = abi.F32, m, 1
+    sums = np.zeros(m, np.float32)
+    oracle.run(r, [x, sums.view(np.uint8)])
+    r.out.dtype, r.out.affine, r.out.affine_zero, r.out.affine_scale = abi.I8, 1, 3, 0.25
+    codes = np.zeros(m, np.uint8)
+    oracle.run(r, [x, codes])
+    assert np.array_equal(codes.view(np.int8).astype(np.int64), [exact.affine_code(exact.Fraction(float(a)), 1, np.float32(0.25), 3) for a in sums])
+
+
 def w8a8_dense_case(seed=0, rows=4, k=16, n=8):
     """examples/tests/formats/w8a8.json on examples/tests/formats/w8a8.psk: relu stored u8/sat, the
     product's sums in i32, the result stored i8/sat, weights int8 over axis 0; with static scales."""
