@@ -258,6 +258,34 @@ def test_step_after_prefill_is_the_whole_window_recomputed(oracle, rz):
         ref.prepare("llama", TMAX=8, **c).call("step", [ids[:, :1]], (3, 1, c["V"]))
 
 
+def test_w8a8_step_after_prefill_is_the_whole_window_recomputed(oracle):
+    """The same with the W8A8 realization in its fuller form (tests/headline.py, `attn_out`: the weighted values a
+    scaled site, every projection's sums in i32): static scales make a position's codes independent of the window's
+    other positions, so a cached step is still the recompute's last row, bit for bit, with the launches apart and
+    with the attention issued as one launch that writes the codes."""
+    import headline
+    c = dict(V=100, D=32, H=4, G=2, FF=64, L=2)
+    p = models.llama_params(c)
+    ids = np.random.default_rng(13).integers(0, c["V"], size=(2, 12), dtype=np.int64)
+    cal = models.give(Host(oracle.vtable(), headline.realization(p, {"kind": "sequential"})).prepare("llama", **c), p)
+    cal.set_calibrating(True)
+    cal.call("apply", [ids], (2, 12, c["V"]))
+    scales = headline.w8a8_scales(cal.envelope())
+    for order in ({"kind": "sequential"}, {"kind": "device", "attention": "online", "launches": "merged"}):
+        rz = headline.w8a8_realization(p, order, scales, attn_out=True)
+        h = models.give(Host(oracle.vtable(), rz).prepare("llama", TMAX=12, **c), p)
+        ref = models.give(Host(oracle.vtable(), rz).prepare("llama", **c), p)
+        h.set_logging(True)
+        first = h.call("prefill", [ids[:, :8]], (2, 8, c["V"]))
+        assert np.array_equal(first.view(np.uint32), ref.call("apply", [ids[:, :8]], (2, 8, c["V"])).view(np.uint32))
+        for t in range(8, 12):
+            got = h.call("step", [ids[:, t:t + 1]], (2, 1, c["V"]))
+            want = ref.call("apply", [ids[:, :t + 1]], (2, t + 1, c["V"]))[:, -1:, :]
+            assert np.array_equal(got.view(np.uint32), np.ascontiguousarray(want).view(np.uint32)), (order, t)
+        if order["kind"] == "device":
+            assert h.launch_log().count("attention[online]") == c["L"]  # the step's attention is one launch, codes out
+
+
 def test_w8a8_llama_merged_launches_keep_every_bit(oracle):
     """The W8A8 realization of the Llama program (tests/headline.py: i8 activations at the projections' inputs with
     static scales from a calibration, int8 weights, i32 sums): under `launches: merged` the norm and the silu group
